@@ -1,0 +1,136 @@
+// hx_common.cuh -- shared declarations of libhelix_b200: error plumbing, the NVFP4 codecs
+// (host + device) and small device helpers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+#include <math.h>
+#include "../../include/helix_b200.h"
+
+#define HX_API extern "C" __attribute__((visibility("default")))
+
+// ---- error plumbing -----------------------------------------------------------------------------
+void hx_set_error(const char* fmt, ...);
+int  hx_fail(int code, const char* fmt, ...);
+
+#define HX_CUDA(call)                                                                         \
+    do {                                                                                      \
+        cudaError_t _e = (call);                                                              \
+        if (_e != cudaSuccess)                                                                \
+            return hx_fail(HX_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(_e), \
+                           __FILE__, __LINE__);                                               \
+    } while (0)
+
+#define HX_CHECK_ARG(cond)                                                                    \
+    do {                                                                                      \
+        if (!(cond)) return hx_fail(HX_ERR_ARG, "bad argument: %s (%s:%d)", #cond, __FILE__, __LINE__); \
+    } while (0)
+
+// Count of kernels this library launched (reported by the benchmark as gpu_launches).
+extern unsigned long long g_hx_launches;
+#define HX_COUNT_LAUNCH(n) (g_hx_launches += (n))
+
+// ---- codecs -------------------------------------------------------------------------------------
+// E2M1 magnitudes {0,.5,1,1.5,2,3,4,6}: as_float(mag3 << 22) is mag * 2^-126 (the e=0 codes land on
+// f32 subnormals), so one exact multiply by 2^126 decodes all eight without a table.
+__host__ __device__ __forceinline__ float hx_e2m1_mag(int c3) {
+#ifdef __CUDA_ARCH__
+    return __uint_as_float((unsigned)(c3 & 7) << 22) * 8.507059173023462e37f;   // 2^126
+#else
+    const float MAG[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+    return MAG[c3 & 7];
+#endif
+}
+__host__ __device__ __forceinline__ float hx_e2m1_dec(int code) {
+    float m = hx_e2m1_mag(code);
+    return (code & 8) ? -m : m;
+}
+
+// Threshold encoder; a tie takes the smaller magnitude, magnitude 0 never carries a sign, NaN maps
+// to code 7 (every comparison false).  Reference: e2m1_encode, gpt2_pack.c:306-318.
+__host__ __device__ __forceinline__ int hx_e2m1_enc(float v) {
+    float a = v < 0.0f ? -v : v;
+    if (a <= 0.25f) return 0;
+    int mag = 1 + (int)!(a <= 0.75f) + (int)!(a <= 1.25f) + (int)!(a <= 1.75f) + (int)!(a <= 2.5f) +
+              (int)!(a <= 3.5f) + (int)!(a <= 5.0f);
+    return mag | (v < 0.0f ? 8 : 0);
+}
+
+// E4M3 decode for non-NaN codes: (1+m/8)*2^(e-7), subnormals (m/8)*2^-6.  Built from the bit
+// pattern: as_float((c & 0x7F) << 20) is the value times 2^-120 (e=0 lands on f32 subnormals).
+// Reference: e4m3_decode, gpt2_pack.c:333-338.
+__host__ __device__ __forceinline__ float hx_e4m3_dec(int c) {
+    if ((c & 0x7F) == 0x7F) {
+#ifdef __CUDA_ARCH__
+        return __uint_as_float(0x7FC00000u);
+#else
+        return nanf("");
+#endif
+    }
+    uint32_t bits = (uint32_t)(c & 0x7F) << 20;
+    float mag;
+#ifdef __CUDA_ARCH__
+    mag = __uint_as_float(bits) * 1.329227995784916e36f;   // 2^120, exact
+#else
+    float f; memcpy(&f, &bits, 4); mag = f * 1.329227995784916e36f;
+#endif
+    return (c & 0x80) ? -mag : mag;
+}
+
+// E4M3 encode of v with the reference's semantics: the nearest of the 254 non-NaN codes by
+// |decode(c) - v| evaluated in f32, the first (lowest) code on a tie, and code 0 when no distance is
+// below 1e30 (NaN, infinities, absurdly large v).  For v >= 0 the winner is found in closed form:
+// values are monotonic in the code, distances to the two neighbours are exact (Sterbenz), so the
+// rule is "round to nearest, a tie goes to the lower code".  Negative v only occurs for corrupt
+// input; the search then runs over the negative codes and zero the same way.
+// Reference: e4m3_encode, gpt2_pack.c:339-343.
+__host__ __device__ __forceinline__ int hx_e4m3_enc(float v) {
+    float a = v < 0.0f ? -v : v;
+    int c;
+    if (!(a == a)) return 0;                       // NaN: no distance compares below the seed
+    if (a >= 448.0f) c = 0x7E;
+    else if (a < 0.015625f) {                      // below 2^-6: subnormal codes, step 2^-9
+        float t = a * 512.0f;                      // exact
+        int k = (int)t;
+        c = k + ((t - (float)k) > 0.5f ? 1 : 0);   // 8 rolls into code 0x08 = 2^-6
+    } else {
+        uint32_t bits;
+#ifdef __CUDA_ARCH__
+        bits = __float_as_uint(a);
+#else
+        memcpy(&bits, &a, 4);
+#endif
+        int e = (int)(bits >> 23) - 127 + 7;       // 1..15
+        uint32_t man = bits & 0x7FFFFFu;
+        c = (e << 3) | (int)(man >> 20);
+        if ((man & 0xFFFFFu) > 0x80000u) c += 1;   // above the midpoint; carries into the exponent
+        if (c > 0x7E) c = 0x7E;
+    }
+    // the search only accepts a distance below 1e30
+    float d = hx_e4m3_dec(c) - a; if (d < 0) d = -d;
+    if (!(d < 1.0e30f)) return 0;
+    if (v < 0.0f && c != 0) {
+        // negative input: candidates are code 0 (distance a) and the negative codes; code 0 comes
+        // first in code order, so it wins ties.
+        return (a <= d) ? 0 : (c | 0x80);
+    }
+    return c;
+}
+
+// ---- device helpers -----------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ float hx_warp_sum(float v) {
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    return v;
+}
+__device__ __forceinline__ float hx_warp_max(float v) {
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
+    return v;
+}
+// Programmatic dependent launch: wait for the kernels this one depends on / let dependents start.
+__device__ __forceinline__ void hx_grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void hx_grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif

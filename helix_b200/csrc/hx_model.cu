@@ -1,0 +1,726 @@
+// hx_model.cu -- weight residency and the decode / prefill sequencer.
+//
+// Reference: load_gpt2_weights (v3 branch) and peek_weights_header, helixc/runtime/gpt2_infer.c:581-603,
+// 648-667 (container validation); v3_upload_gpu / v3_resident_ptrs / upload_layer_ll(_fused),
+// :2163-2276, 2407-2450 (the streaming loader this file replaces with one-time HBM residency);
+// decode_step_llama :1341-1613, forward_full :1297-1333, run_generate :3123-3195 (sequencing);
+// RoPE tables :2040-2057; KV layout :709-721.
+//
+// Layout in HBM.  Every linear weight lives in the dense decode layout (hx_repack_d16): per row
+// Kd/2 code bytes and Kd/16 scale bytes.  Tensors that are consumed together are stored together:
+// q|k|v rows back to back, gate and up rows interleaved (row 2i = gate_i, row 2i+1 = up_i).  With
+// HX_LOAD_KEEP_COMMITTED the committed 7-per-word layout (words, micro bytes, ts) stays resident as
+// well, so that the HXGW v3 image and its SHA-256 can be reproduced from the GPU.
+#include "hx_kernels.cuh"
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+#include <stdlib.h>
+#include <string>
+#include <vector>
+
+namespace {
+
+#pragma pack(push, 1)
+struct V3Desc { uint32_t packed, rows, K, Kpad; uint64_t data_off, scale_off; };
+#pragma pack(pop)
+static_assert(sizeof(V3Desc) == 32, "descriptor is 32 bytes");
+
+const uint32_t HXGW_MAGIC = 0x48584757u;
+enum { T_INLN = 0, T_Q, T_QN, T_K, T_KN, T_V, T_O, T_POSTLN, T_GATE, T_UP, T_DOWN, T_PER_LAYER };
+
+struct Committed {           // one packed tensor in the 7-per-word layout (device)
+    int rows = 0, K = 0, Kpad = 0;
+    int32_t* words = nullptr; uint8_t* micro = nullptr; float ts = 1.0f;
+};
+struct Fused {               // rows of one or more tensors in the dense decode layout (device)
+    int N = 0, K = 0, Kd = 0;
+    uint8_t* codes = nullptr; uint8_t* scales = nullptr;
+    float ts[3] = {1.f, 1.f, 1.f}; int bound0 = 0, bound1 = 0;
+    size_t bytes() const { return (size_t)N * (Kd / 2 + Kd / 16); }
+};
+struct Layer {
+    float *in_g = nullptr, *post_g = nullptr, *qn_g = nullptr, *kn_g = nullptr;
+    Fused qkv, o, gu, down;
+    Committed c[T_PER_LAYER];      // only packed slots used; kept when HX_LOAD_KEEP_COMMITTED
+};
+
+}  // namespace
+
+void hx_repack_rows(const int32_t* words, const uint8_t* micro, int rows, int K, int Kpad, uint8_t* codes,
+                    uint8_t* scales, int row_mul, int row_off, cudaStream_t st);
+
+struct hx_model {
+    hx_config cfg{};
+    int QD = 0, KVD = 0, kv_cap = 0, batch = 1, flags = 0;
+    std::vector<Layer> layers;
+    float* emb = nullptr;          // [NV][DM] f32
+    float* final_g = nullptr;
+    Fused head; Committed head_c;
+    // decode state
+    float *x = nullptr, *qkv = nullptr, *q_rot = nullptr, *ctx = nullptr, *h = nullptr, *logits = nullptr;
+    float *kc = nullptr, *vc = nullptr, *cosT = nullptr, *sinT = nullptr;
+    float *part_m = nullptr, *part_l = nullptr, *part_acc = nullptr; unsigned* attn_cnt = nullptr;
+    float* am_val = nullptr; int* am_idx = nullptr; unsigned* am_cnt = nullptr;
+    int *d_tok = nullptr, *d_pos = nullptr, *d_hist = nullptr, *d_prompt = nullptr;
+    int nsplit = 1;
+    cudaStream_t st = nullptr;
+    cudaGraphExec_t g_decode = nullptr, g_prefill = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    bool pdl = true;
+    hx_step_stats stats{};
+    std::vector<void*> allocs;
+    uint64_t decode_bytes = 0, committed_bytes = 0;
+    int kv_len = 0;
+};
+
+namespace {
+
+template <typename T>
+int dalloc(hx_model* m, T** p, size_t n) {
+    void* q = nullptr;
+    cudaError_t e = cudaMalloc(&q, n * sizeof(T) ? n * sizeof(T) : 16);
+    if (e != cudaSuccess) return hx_fail(HX_ERR_NOMEM, "cudaMalloc(%zu bytes): %s", n * sizeof(T), cudaGetErrorString(e));
+    m->allocs.push_back(q);
+    *p = (T*)q;
+    return HX_OK;
+}
+
+int alloc_fused(hx_model* m, Fused& f, int N, int K) {
+    f.N = N; f.K = K; f.Kd = hx_kd(K);
+    int rc = dalloc(m, &f.codes, (size_t)N * (f.Kd / 2)); if (rc) return rc;
+    rc = dalloc(m, &f.scales, (size_t)N * (f.Kd / 16)); if (rc) return rc;
+    m->decode_bytes += f.bytes();
+    return HX_OK;
+}
+
+// Source of the model's tensors in build order: a mapped file or the synthetic generator.
+struct Source {
+    // file
+    const uint8_t* map = nullptr; size_t maplen = 0; const V3Desc* desc = nullptr;
+    // synth
+    bool synth = false; uint64_t seed = 0;
+    // staging (device)
+    float* f32tmp = nullptr; size_t f32cap = 0;
+    int32_t* wtmp = nullptr; uint8_t* mtmp = nullptr; float* tstmp = nullptr;
+};
+
+// Bring packed tensor `idx` (rows x K) to the device in the committed layout: into `keep` when the
+// committed layout stays resident, else into the staging buffers.  Returns its buffers in `c`.
+int fetch_packed(hx_model* m, Source& s, int idx, int rows, int K, Committed& c, bool keep) {
+    const int Kpad = hx_kpad(K);
+    const size_t nw = (size_t)rows * (Kpad / 7), nm = (size_t)rows * (Kpad / 16);
+    c.rows = rows; c.K = K; c.Kpad = Kpad;
+    if (keep) {
+        int rc = dalloc(m, &c.words, nw); if (rc) return rc;
+        rc = dalloc(m, &c.micro, nm); if (rc) return rc;
+    } else { c.words = s.wtmp; c.micro = s.mtmp; }
+    m->committed_bytes += nw * 4 + nm;
+    if (s.synth) {
+        int rc = hx_launch_fill_normal(s.f32tmp, (size_t)rows * K, 0.02f, s.seed + 0x1000 + (uint64_t)idx, m->st);
+        if (rc) return rc;
+        rc = hx_quantize_nvfp4(s.f32tmp, rows, K, c.words, c.micro, nullptr, s.tstmp, m->st); if (rc) return rc;
+        HX_CUDA(cudaMemcpyAsync(&c.ts, s.tstmp, 4, cudaMemcpyDeviceToHost, m->st));
+        HX_CUDA(cudaStreamSynchronize(m->st));
+    } else {
+        const V3Desc& d = s.desc[idx];
+        if (!d.packed || (int)d.rows != rows || (int)d.K != K || (int)d.Kpad != Kpad)
+            return hx_fail(HX_ERR_FORMAT, "tensor %d: descriptor (packed=%u rows=%u K=%u Kpad=%u) does not match the model shape (%d x %d)",
+                           idx, d.packed, d.rows, d.K, d.Kpad, rows, K);
+        HX_CUDA(cudaMemcpyAsync(c.words, s.map + d.data_off, nw * 4, cudaMemcpyHostToDevice, m->st));
+        HX_CUDA(cudaMemcpyAsync(c.micro, s.map + d.scale_off, nm, cudaMemcpyHostToDevice, m->st));
+        memcpy(&c.ts, s.map + d.scale_off + nm, 4);
+        HX_CUDA(cudaStreamSynchronize(m->st));
+    }
+    return HX_OK;
+}
+
+int fetch_dense(hx_model* m, Source& s, int idx, size_t n, float** out, bool is_gain) {
+    int rc = dalloc(m, out, n); if (rc) return rc;
+    if (s.synth) {
+        if (is_gain) return hx_launch_fill_const(*out, n, 1.0f, m->st);
+        return hx_launch_fill_normal(*out, n, 0.02f, s.seed + 0x1000 + (uint64_t)idx, m->st);
+    }
+    const V3Desc& d = s.desc[idx];
+    if (d.packed || (size_t)d.rows * d.K != n) return hx_fail(HX_ERR_FORMAT, "tensor %d: expected %zu dense f32", idx, n);
+    HX_CUDA(cudaMemcpyAsync(*out, s.map + d.data_off, n * 4, cudaMemcpyHostToDevice, m->st));
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    return HX_OK;
+}
+
+void put_rows(hx_model* m, const Committed& c, Fused& f, int row_mul, int row_off) {
+    hx_repack_rows(c.words, c.micro, c.rows, c.K, c.Kpad, f.codes, f.scales, row_mul, row_off, m->st);
+}
+
+int build(hx_model* m, Source& s) {
+    const hx_config& c = m->cfg;
+    const int NL = c.n_layers, DM = c.d_model, DH = c.head_dim, DFF = c.d_ff, NV = c.vocab;
+    const int QD = m->QD, KVD = m->KVD;
+    const bool keep = (m->flags & HX_LOAD_KEEP_COMMITTED) != 0;
+    // staging sized for the largest tensor
+    size_t maxel = (size_t)NV * DM;
+    const size_t cand[] = {(size_t)QD * DM, (size_t)DFF * DM, (size_t)DM * DFF, (size_t)DM * QD};
+    for (size_t v : cand) if (v > maxel) maxel = v;
+    int rc;
+    std::vector<void*> staging;
+    auto salloc = [&](void** p, size_t bytes) -> int {
+        cudaError_t e = cudaMalloc(p, bytes);
+        if (e != cudaSuccess) return hx_fail(HX_ERR_NOMEM, "staging cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
+        staging.push_back(*p); return HX_OK;
+    };
+    auto sfree = [&]() { for (void* p : staging) cudaFree(p); staging.clear(); };
+    if (s.synth) { rc = salloc((void**)&s.f32tmp, maxel * 4); if (rc) { sfree(); return rc; } }
+    if (!keep) {
+        const int shp[][2] = {{QD, DM}, {KVD, DM}, {DM, QD}, {DFF, DM}, {DM, DFF}, {NV, DM}};
+        size_t wmax = 0, mmax = 0;
+        for (auto& sh : shp) {
+            const size_t kp = (size_t)hx_kpad(sh[1]);
+            if ((size_t)sh[0] * (kp / 7) * 4 > wmax) wmax = (size_t)sh[0] * (kp / 7) * 4;
+            if ((size_t)sh[0] * (kp / 16) > mmax) mmax = (size_t)sh[0] * (kp / 16);
+        }
+        rc = salloc((void**)&s.wtmp, wmax); if (rc) { sfree(); return rc; }
+        rc = salloc((void**)&s.mtmp, mmax); if (rc) { sfree(); return rc; }
+    }
+    rc = salloc((void**)&s.tstmp, 256); if (rc) { sfree(); return rc; }
+
+    m->layers.resize(NL);
+    for (int L = 0; L < NL && !rc; L++) {
+        Layer& ly = m->layers[L];
+        const int b = L * T_PER_LAYER;
+        do {
+            if ((rc = fetch_dense(m, s, b + T_INLN, DM, &ly.in_g, true))) break;
+            if ((rc = fetch_dense(m, s, b + T_POSTLN, DM, &ly.post_g, true))) break;
+            if (c.qk_norm) {
+                if ((rc = fetch_dense(m, s, b + T_QN, DH, &ly.qn_g, true))) break;
+                if ((rc = fetch_dense(m, s, b + T_KN, DH, &ly.kn_g, true))) break;
+            }
+            if ((rc = alloc_fused(m, ly.qkv, QD + 2 * KVD, DM))) break;
+            if ((rc = alloc_fused(m, ly.o, DM, QD))) break;
+            if ((rc = alloc_fused(m, ly.gu, 2 * DFF, DM))) break;
+            if ((rc = alloc_fused(m, ly.down, DM, DFF))) break;
+            if ((rc = fetch_packed(m, s, b + T_Q, QD, DM, ly.c[T_Q], keep))) break;
+            put_rows(m, ly.c[T_Q], ly.qkv, 1, 0); ly.qkv.ts[0] = ly.c[T_Q].ts;
+            if ((rc = fetch_packed(m, s, b + T_K, KVD, DM, ly.c[T_K], keep))) break;
+            put_rows(m, ly.c[T_K], ly.qkv, 1, QD); ly.qkv.ts[1] = ly.c[T_K].ts;
+            if ((rc = fetch_packed(m, s, b + T_V, KVD, DM, ly.c[T_V], keep))) break;
+            put_rows(m, ly.c[T_V], ly.qkv, 1, QD + KVD); ly.qkv.ts[2] = ly.c[T_V].ts;
+            ly.qkv.bound0 = QD; ly.qkv.bound1 = QD + KVD;
+            if ((rc = fetch_packed(m, s, b + T_O, DM, QD, ly.c[T_O], keep))) break;
+            put_rows(m, ly.c[T_O], ly.o, 1, 0); ly.o.ts[0] = ly.o.ts[1] = ly.o.ts[2] = ly.c[T_O].ts; ly.o.bound0 = ly.o.bound1 = DM;
+            if ((rc = fetch_packed(m, s, b + T_GATE, DFF, DM, ly.c[T_GATE], keep))) break;
+            put_rows(m, ly.c[T_GATE], ly.gu, 2, 0); ly.gu.ts[0] = ly.c[T_GATE].ts;
+            if ((rc = fetch_packed(m, s, b + T_UP, DFF, DM, ly.c[T_UP], keep))) break;
+            put_rows(m, ly.c[T_UP], ly.gu, 2, 1); ly.gu.ts[1] = ly.c[T_UP].ts; ly.gu.bound0 = ly.gu.bound1 = 2 * DFF;
+            if ((rc = fetch_packed(m, s, b + T_DOWN, DM, DFF, ly.c[T_DOWN], keep))) break;
+            put_rows(m, ly.c[T_DOWN], ly.down, 1, 0); ly.down.ts[0] = ly.down.ts[1] = ly.down.ts[2] = ly.c[T_DOWN].ts; ly.down.bound0 = ly.down.bound1 = DM;
+            cudaError_t e = cudaStreamSynchronize(m->st);
+            if (e != cudaSuccess) { rc = hx_fail(HX_ERR_CUDA, "layer %d ingest: %s", L, cudaGetErrorString(e)); break; }
+        } while (0);
+    }
+    if (!rc) do {
+        const int b = NL * T_PER_LAYER;
+        if ((rc = fetch_dense(m, s, b + 0, (size_t)NV * DM, &m->emb, false))) break;
+        if ((rc = fetch_dense(m, s, b + 1, DM, &m->final_g, true))) break;
+        if ((rc = alloc_fused(m, m->head, NV, DM))) break;
+        if ((rc = fetch_packed(m, s, b + 2, NV, DM, m->head_c, keep))) break;
+        put_rows(m, m->head_c, m->head, 1, 0);
+        m->head.ts[0] = m->head.ts[1] = m->head.ts[2] = m->head_c.ts; m->head.bound0 = m->head.bound1 = NV;
+        cudaError_t e = cudaStreamSynchronize(m->st);
+        if (e != cudaSuccess) rc = hx_fail(HX_ERR_CUDA, "head ingest: %s", cudaGetErrorString(e));
+    } while (0);
+    sfree();
+    return rc;
+}
+
+int alloc_state(hx_model* m) {
+    const hx_config& c = m->cfg;
+    const int DM = c.d_model, DH = c.head_dim, NH = c.n_heads, NKV = c.n_kv_heads, cap = m->kv_cap;
+    int rc;
+    const int QDd = hx_kd(m->QD), DFFd = hx_kd(c.d_ff);
+    if ((rc = dalloc(m, &m->x, (size_t)DM))) return rc;
+    if ((rc = dalloc(m, &m->qkv, (size_t)m->QD + 2 * m->KVD))) return rc;
+    if ((rc = dalloc(m, &m->q_rot, (size_t)m->QD))) return rc;
+    if ((rc = dalloc(m, &m->ctx, (size_t)QDd))) return rc;
+    if ((rc = dalloc(m, &m->h, (size_t)DFFd))) return rc;
+    if ((rc = dalloc(m, &m->logits, (size_t)c.vocab))) return rc;
+    HX_CUDA(cudaMemset(m->ctx, 0, (size_t)QDd * 4));
+    HX_CUDA(cudaMemset(m->h, 0, (size_t)DFFd * 4));
+    const size_t kvn = (size_t)c.n_layers * NKV * cap * DH;
+    if ((rc = dalloc(m, &m->kc, kvn))) return rc;
+    if ((rc = dalloc(m, &m->vc, kvn))) return rc;
+    HX_CUDA(cudaMemset(m->kc, 0, kvn * 4));
+    HX_CUDA(cudaMemset(m->vc, 0, kvn * 4));
+    // RoPE tables, double precision on the host, cast to f32 (gpt2_infer.c:2040-2051)
+    const int half = DH / 2;
+    std::vector<float> hc((size_t)cap * half), hs((size_t)cap * half);
+    for (int s = 0; s < cap; s++)
+        for (int j = 0; j < half; j++) {
+            const double inv = pow((double)c.rope_theta, -2.0 * (double)j / (double)DH);
+            const double ang = (double)s * inv;
+            hc[(size_t)s * half + j] = (float)cos(ang);
+            hs[(size_t)s * half + j] = (float)sin(ang);
+        }
+    if ((rc = dalloc(m, &m->cosT, hc.size()))) return rc;
+    if ((rc = dalloc(m, &m->sinT, hs.size()))) return rc;
+    HX_CUDA(cudaMemcpy(m->cosT, hc.data(), hc.size() * 4, cudaMemcpyHostToDevice));
+    HX_CUDA(cudaMemcpy(m->sinT, hs.data(), hs.size() * 4, cudaMemcpyHostToDevice));
+    int sms = 148; { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+    m->nsplit = sms / NKV; if (m->nsplit < 1) m->nsplit = 1; if (m->nsplit > 64) m->nsplit = 64;
+    if ((rc = dalloc(m, &m->part_m, (size_t)NH * m->nsplit))) return rc;
+    if ((rc = dalloc(m, &m->part_l, (size_t)NH * m->nsplit))) return rc;
+    if ((rc = dalloc(m, &m->part_acc, (size_t)NH * m->nsplit * DH))) return rc;
+    if ((rc = dalloc(m, &m->attn_cnt, (size_t)NKV))) return rc;
+    HX_CUDA(cudaMemset(m->attn_cnt, 0, (size_t)NKV * 4));
+    if ((rc = dalloc(m, &m->am_val, (size_t)4096))) return rc;
+    if ((rc = dalloc(m, &m->am_idx, (size_t)4096))) return rc;
+    if ((rc = dalloc(m, &m->am_cnt, (size_t)4))) return rc;
+    HX_CUDA(cudaMemset(m->am_cnt, 0, 16));
+    if ((rc = dalloc(m, &m->d_tok, (size_t)4))) return rc;
+    if ((rc = dalloc(m, &m->d_pos, (size_t)4))) return rc;
+    if ((rc = dalloc(m, &m->d_hist, (size_t)cap + 8))) return rc;
+    if ((rc = dalloc(m, &m->d_prompt, (size_t)cap + 8))) return rc;
+    HX_CUDA(cudaMemset(m->d_hist, 0, ((size_t)cap + 8) * 4));
+    HX_CUDA(cudaEventCreate(&m->ev0));
+    HX_CUDA(cudaEventCreate(&m->ev1));
+    return HX_OK;
+}
+
+__global__ void k_advance(int* pos) { hx_grid_dep_launch(); hx_grid_dep_wait(); if (threadIdx.x == 0) *pos = *pos + 1; }
+
+HxLinear lin(const Fused& f, const float* x, float* y, int epi) {
+    HxLinear a = {};
+    a.codes = reinterpret_cast<const uint4*>(f.codes); a.scales = f.scales;
+    a.ts[0] = f.ts[0]; a.ts[1] = f.ts[1]; a.ts[2] = f.ts[2]; a.bound0 = f.bound0; a.bound1 = f.bound1;
+    a.N = f.N; a.K = f.K; a.Kd = f.Kd; a.x = x; a.y = y; a.epi = epi; a.norm = HX_NORM_NONE;
+    return a;
+}
+
+// Enqueue one token step on m->st.  from_prompt: the input token is d_prompt[*pos] and no logits are
+// computed (prefill); otherwise the input token is *d_tok and the head + arg-max run.
+int enqueue_step(hx_model* m, bool from_prompt, bool with_head) {
+    const hx_config& c = m->cfg;
+    const int DM = c.d_model, DH = c.head_dim, cap = m->kv_cap;
+    const bool pdl = m->pdl;
+    int rc;
+    {
+        // the first kernel of a step follows the last kernel of the previous step
+        const int* tok = from_prompt ? m->d_prompt : m->d_tok;
+        rc = hx_launch_embed(m->emb, nullptr, tok, m->d_pos, from_prompt ? 1 : 0, m->x, DM, m->st, pdl);
+        if (rc) return rc;
+    }
+    for (int L = 0; L < c.n_layers; L++) {
+        Layer& ly = m->layers[L];
+        HxLinear a = lin(ly.qkv, m->x, m->qkv, HX_EPI_STORE);
+        a.norm = HX_NORM_RMS; a.norm_g = ly.in_g; a.eps = c.norm_eps;
+        if ((rc = hx_launch_linear(a, m->st, pdl))) return rc;
+        HxAttn at = {};
+        at.qkv = m->qkv; at.q_rot = m->q_rot; at.qn_g = ly.qn_g; at.kn_g = ly.kn_g;
+        at.cosT = m->cosT; at.sinT = m->sinT;
+        at.kc = m->kc + (size_t)L * c.n_kv_heads * cap * DH; at.vc = m->vc + (size_t)L * c.n_kv_heads * cap * DH;
+        at.pos = m->d_pos; at.NH = c.n_heads; at.NKV = c.n_kv_heads; at.DH = DH; at.cap = cap;
+        at.eps = c.norm_eps; at.scale = 1.0f / sqrtf((float)DH); at.nsplit = m->nsplit;
+        at.part_m = m->part_m; at.part_l = m->part_l; at.part_acc = m->part_acc; at.counters = m->attn_cnt; at.ctx = m->ctx;
+        if ((rc = hx_launch_qk_prep(at, m->st, pdl))) return rc;
+        if ((rc = hx_launch_attn(at, m->st, pdl))) return rc;
+        HxLinear o = lin(ly.o, m->ctx, m->x, HX_EPI_RESID); o.resid = m->x;
+        if ((rc = hx_launch_linear(o, m->st, pdl))) return rc;
+        HxLinear gu = lin(ly.gu, m->x, m->h, HX_EPI_SWIGLU);
+        gu.norm = HX_NORM_RMS; gu.norm_g = ly.post_g; gu.eps = c.norm_eps;
+        if ((rc = hx_launch_linear(gu, m->st, pdl))) return rc;
+        HxLinear dn = lin(ly.down, m->h, m->x, HX_EPI_RESID); dn.resid = m->x;
+        if ((rc = hx_launch_linear(dn, m->st, pdl))) return rc;
+    }
+    if (with_head) {
+        HxLinear hd = lin(m->head, m->x, m->logits, HX_EPI_ARGMAX);
+        hd.norm = HX_NORM_RMS; hd.norm_g = m->final_g; hd.eps = c.norm_eps;
+        hd.part_val = m->am_val; hd.part_idx = m->am_idx; hd.counter = m->am_cnt; hd.next_tok = m->d_tok; hd.pos_inc = m->d_pos;
+        hd.hist = m->d_hist;
+        if ((rc = hx_launch_linear(hd, m->st, pdl))) return rc;
+    } else {
+        k_advance<<<1, 32, 0, m->st>>>(m->d_pos);
+        HX_COUNT_LAUNCH(1);
+        HX_CUDA(cudaGetLastError());
+    }
+    return HX_OK;
+}
+
+int capture(hx_model* m, bool from_prompt, bool with_head, cudaGraphExec_t* out) {
+    cudaGraph_t g = nullptr;
+    HX_CUDA(cudaStreamBeginCapture(m->st, cudaStreamCaptureModeThreadLocal));
+    const unsigned long long before = g_hx_launches;
+    int rc = enqueue_step(m, from_prompt, with_head);
+    cudaError_t e = cudaStreamEndCapture(m->st, &g);
+    g_hx_launches = before;                       // captured, not launched
+    if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+    if (e != cudaSuccess) return hx_fail(HX_ERR_CUDA, "graph capture: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(out, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return hx_fail(HX_ERR_CUDA, "graph instantiate: %s", cudaGetErrorString(e));
+    return HX_OK;
+}
+
+int kernels_per_step(const hx_model* m, bool with_head) { (void)with_head; return 1 + 6 * m->cfg.n_layers + 1; }
+
+int finish_init(hx_model* m) {
+    int rc = alloc_state(m); if (rc) return rc;
+    const char* np = getenv("HX_NO_PDL");
+    m->pdl = !(np && *np == '1');
+    rc = capture(m, false, true, &m->g_decode);
+    if (rc && m->pdl) {     // programmatic edges not capturable on this driver: plain stream order
+        m->pdl = false;
+        rc = capture(m, false, true, &m->g_decode);
+    }
+    if (rc) return rc;
+    return capture(m, true, false, &m->g_prefill);
+}
+
+int check_cfg(const hx_config& c, int kv_cap, int batch, int tp_rank, int tp_size) {
+    if (c.arch != 1) return hx_fail(HX_ERR_ARG, "arch %d: only the Llama/Qwen3 family (1) is built", c.arch);
+    if (c.n_layers <= 0 || c.d_model <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.head_dim <= 0 || c.d_ff <= 0 || c.vocab <= 0)
+        return hx_fail(HX_ERR_ARG, "non-positive model dimension");
+    if (c.n_heads % c.n_kv_heads) return hx_fail(HX_ERR_ARG, "n_heads %d not a multiple of n_kv_heads %d", c.n_heads, c.n_kv_heads);
+    if (c.head_dim % 32 || c.head_dim > 256) return hx_fail(HX_ERR_ARG, "head_dim %d: need a multiple of 32 up to 256", c.head_dim);
+    if (c.d_model % 4 || c.d_ff % 4) return hx_fail(HX_ERR_ARG, "d_model and d_ff must be multiples of 4");
+    if (kv_cap <= 0) return hx_fail(HX_ERR_ARG, "kv_cap must be positive");
+    if (batch != 1) return hx_fail(HX_ERR_ARG, "batch %d: this build decodes one sequence per model instance", batch);
+    if (tp_size != 1 || tp_rank != 0) return hx_fail(HX_ERR_ARG, "tensor parallel shards are not built yet (tp_size must be 1)");
+    return HX_OK;
+}
+
+}  // namespace
+
+HX_API int hx_model_free(hx_model* m) {
+    if (!m) return HX_OK;
+    if (m->g_decode) cudaGraphExecDestroy(m->g_decode);
+    if (m->g_prefill) cudaGraphExecDestroy(m->g_prefill);
+    if (m->ev0) cudaEventDestroy(m->ev0);
+    if (m->ev1) cudaEventDestroy(m->ev1);
+    for (void* p : m->allocs) cudaFree(p);
+    if (m->st) cudaStreamDestroy(m->st);
+    delete m;
+    return HX_OK;
+}
+
+HX_API int hx_model_synth(hx_model** out, const hx_config* cfg, uint64_t seed, int kv_cap, int batch,
+                          int flags, int tp_rank, int tp_size) {
+    HX_CHECK_ARG(out && cfg);
+    int rc = check_cfg(*cfg, kv_cap, batch, tp_rank, tp_size); if (rc) return rc;
+    hx_model* m = new hx_model();
+    m->cfg = *cfg; m->QD = cfg->n_heads * cfg->head_dim; m->KVD = cfg->n_kv_heads * cfg->head_dim;
+    m->kv_cap = kv_cap; m->batch = batch; m->flags = flags;
+    cudaError_t e = cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { delete m; return hx_fail(HX_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
+    Source s; s.synth = true; s.seed = seed;
+    rc = build(m, s);
+    if (!rc) rc = finish_init(m);
+    if (rc) { hx_model_free(m); return rc; }
+    *out = m;
+    return HX_OK;
+}
+
+HX_API int hx_model_load(hx_model** out, const char* path, int kv_cap, int batch, int flags,
+                         int tp_rank, int tp_size) {
+    HX_CHECK_ARG(out && path);
+    int fd = open(path, O_RDONLY);
+    if (fd < 0) return hx_fail(HX_ERR_IO, "cannot open %s", path);
+    struct stat stt;
+    if (fstat(fd, &stt) || stt.st_size < 64) { close(fd); return hx_fail(HX_ERR_FORMAT, "%s: too short for an HXGW header", path); }
+    void* mp = mmap(nullptr, (size_t)stt.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
+    if (mp == MAP_FAILED) { close(fd); return hx_fail(HX_ERR_IO, "mmap %s failed", path); }
+    const uint8_t* hb = (const uint8_t*)mp;
+    const size_t len = (size_t)stt.st_size;
+    auto u32 = [&](int off) { uint32_t v; memcpy(&v, hb + off, 4); return v; };
+    auto f32 = [&](int off) { float v; memcpy(&v, hb + off, 4); return v; };
+    int rc = HX_OK;
+    hx_model* m = nullptr;
+    do {
+        if (u32(0) != HXGW_MAGIC) { rc = hx_fail(HX_ERR_FORMAT, "%s: bad magic 0x%08x", path, u32(0)); break; }
+        if (u32(4) != 3u) { rc = hx_fail(HX_ERR_FORMAT, "%s: HXGW version %u, need 3", path, u32(4)); break; }
+        if (u32(40) != 1u) { rc = hx_fail(HX_ERR_FORMAT, "%s: unknown arch %u", path, u32(40)); break; }
+        hx_config c{};
+        c.arch = 1; c.n_layers = (int)u32(8); c.d_model = (int)u32(12); c.n_heads = (int)u32(16); c.vocab = (int)u32(20);
+        c.max_ctx = (int)u32(24); c.d_ff = (int)u32(28); c.n_kv_heads = (int)u32(44); c.rope_theta = f32(48);
+        const float file_eps = f32(52);
+        const int hd = (int)u32(56), nt = (int)u32(60);
+        if (c.n_heads <= 0) { rc = hx_fail(HX_ERR_FORMAT, "%s: n_heads %d", path, c.n_heads); break; }
+        c.head_dim = hd > 0 ? hd : c.d_model / c.n_heads;
+        c.qk_norm = 1;
+        // the reference's norm kernel bakes 1e-5 and the worker accepts the header's value with a note
+        c.norm_eps = (flags & HX_LOAD_FILE_EPS) ? file_eps : 1e-5f;
+        if ((rc = check_cfg(c, kv_cap, batch, tp_rank, tp_size))) break;
+        if (nt != c.n_layers * T_PER_LAYER + 3) { rc = hx_fail(HX_ERR_FORMAT, "%s: %d tensors, expected %d", path, nt, c.n_layers * T_PER_LAYER + 3); break; }
+        // descriptors must tile the file exactly
+        uint64_t cur = 64 + (uint64_t)nt * 32;
+        if (cur > len) { rc = hx_fail(HX_ERR_FORMAT, "%s: descriptor table past the end of the file", path); break; }
+        const V3Desc* d = (const V3Desc*)(hb + 64);
+        for (int i = 0; i < nt && !rc; i++) {
+            if (d[i].data_off != cur) { rc = hx_fail(HX_ERR_FORMAT, "v3 desc %d data_off %llu != %llu", i, (unsigned long long)d[i].data_off, (unsigned long long)cur); break; }
+            if (d[i].packed) {
+                if (d[i].Kpad % 112) { rc = hx_fail(HX_ERR_FORMAT, "v3 desc %d Kpad %u not a multiple of 112", i, d[i].Kpad); break; }
+                const uint64_t wb = (uint64_t)d[i].rows * (d[i].Kpad / 7) * 4;
+                if (d[i].scale_off != cur + wb) { rc = hx_fail(HX_ERR_FORMAT, "v3 desc %d scale_off mismatch", i); break; }
+                cur += wb + (uint64_t)d[i].rows * (d[i].Kpad / 16) + 4;
+            } else cur += (uint64_t)d[i].rows * d[i].K * 4;
+        }
+        if (rc) break;
+        if (cur != len) { rc = hx_fail(HX_ERR_FORMAT, "v3 layout %llu != file %zu", (unsigned long long)cur, len); break; }
+        m = new hx_model();
+        m->cfg = c; m->QD = c.n_heads * c.head_dim; m->KVD = c.n_kv_heads * c.head_dim;
+        m->kv_cap = kv_cap; m->batch = batch; m->flags = flags;
+        cudaError_t e = cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking);
+        if (e != cudaSuccess) { rc = hx_fail(HX_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); break; }
+        Source s; s.map = hb; s.maplen = len; s.desc = d;
+        if ((rc = build(m, s))) break;
+        rc = finish_init(m);
+    } while (0);
+    munmap(mp, len); close(fd);
+    if (rc) { if (m) hx_model_free(m); return rc; }
+    *out = m;
+    return HX_OK;
+}
+
+HX_API int hx_model_config(const hx_model* m, hx_config* cfg) { HX_CHECK_ARG(m && cfg); *cfg = m->cfg; return HX_OK; }
+HX_API int hx_model_weight_bytes(const hx_model* m, uint64_t* decode_layout, uint64_t* committed_layout) {
+    HX_CHECK_ARG(m);
+    if (decode_layout) *decode_layout = m->decode_bytes;
+    if (committed_layout) *committed_layout = m->committed_bytes;
+    return HX_OK;
+}
+HX_API int hx_model_reset(hx_model* m) { HX_CHECK_ARG(m); m->kv_len = 0; return HX_OK; }
+HX_API int hx_model_last_stats(const hx_model* m, hx_step_stats* st) { HX_CHECK_ARG(m && st); *st = m->stats; return HX_OK; }
+HX_API int hx_model_set_profile(hx_model* m, int on) { HX_CHECK_ARG(m); (void)on; return HX_OK; }
+
+// ---- HXGW v3 image ---------------------------------------------------------------------------------
+namespace {
+struct ImgEntry { bool packed; const Committed* c; const float* dense; size_t n; };
+int image_plan(const hx_model* m, std::vector<ImgEntry>& ents) {
+    if (!(m->flags & HX_LOAD_KEEP_COMMITTED)) return hx_fail(HX_ERR_STATE, "model was built without HX_LOAD_KEEP_COMMITTED");
+    const hx_config& c = m->cfg;
+    for (int L = 0; L < c.n_layers; L++) {
+        const Layer& ly = m->layers[L];
+        ents.push_back({false, nullptr, ly.in_g, (size_t)c.d_model});
+        ents.push_back({true, &ly.c[T_Q], nullptr, 0});
+        ents.push_back({false, nullptr, ly.qn_g, (size_t)c.head_dim});
+        ents.push_back({true, &ly.c[T_K], nullptr, 0});
+        ents.push_back({false, nullptr, ly.kn_g, (size_t)c.head_dim});
+        ents.push_back({true, &ly.c[T_V], nullptr, 0});
+        ents.push_back({true, &ly.c[T_O], nullptr, 0});
+        ents.push_back({false, nullptr, ly.post_g, (size_t)c.d_model});
+        ents.push_back({true, &ly.c[T_GATE], nullptr, 0});
+        ents.push_back({true, &ly.c[T_UP], nullptr, 0});
+        ents.push_back({true, &ly.c[T_DOWN], nullptr, 0});
+    }
+    ents.push_back({false, nullptr, m->emb, (size_t)c.vocab * c.d_model});
+    ents.push_back({false, nullptr, m->final_g, (size_t)c.d_model});
+    ents.push_back({true, &m->head_c, nullptr, 0});
+    return HX_OK;
+}
+uint64_t entry_bytes(const ImgEntry& e) {
+    if (!e.packed) return (uint64_t)e.n * 4;
+    return (uint64_t)e.c->rows * (e.c->Kpad / 7) * 4 + (uint64_t)e.c->rows * (e.c->Kpad / 16) + 4;
+}
+}  // namespace
+
+HX_API int hx_model_v3_size(const hx_model* m, uint64_t* bytes) {
+    HX_CHECK_ARG(m && bytes);
+    std::vector<ImgEntry> ents; int rc = image_plan(m, ents); if (rc) return rc;
+    uint64_t cur = 64 + 32 * (uint64_t)ents.size();
+    for (auto& e : ents) cur += entry_bytes(e);
+    *bytes = cur;
+    return HX_OK;
+}
+
+HX_API int hx_model_v3_export(const hx_model* m, void* host_buf, uint64_t bytes) {
+    HX_CHECK_ARG(m && host_buf);
+    std::vector<ImgEntry> ents; int rc = image_plan(m, ents); if (rc) return rc;
+    uint64_t need = 0; hx_model_v3_size(m, &need);
+    if (bytes < need) return hx_fail(HX_ERR_ARG, "buffer of %llu bytes, image needs %llu", (unsigned long long)bytes, (unsigned long long)need);
+    uint8_t* o = (uint8_t*)host_buf;
+    const hx_config& c = m->cfg;
+    memset(o, 0, 64);
+    const uint32_t h32[8] = {HXGW_MAGIC, 3u, (uint32_t)c.n_layers, (uint32_t)c.d_model, (uint32_t)c.n_heads, (uint32_t)c.vocab,
+                             (uint32_t)c.max_ctx, (uint32_t)c.d_ff};
+    memcpy(o, h32, 32);
+    const uint32_t arch = 1u, nkv = (uint32_t)c.n_kv_heads, hd = (uint32_t)c.head_dim, nt = (uint32_t)ents.size();
+    const float eps_hdr = 1e-6f;    // what a Qwen3 config states; the kernels use cfg.norm_eps
+    memcpy(o + 40, &arch, 4); memcpy(o + 44, &nkv, 4); memcpy(o + 48, &c.rope_theta, 4); memcpy(o + 52, &eps_hdr, 4);
+    memcpy(o + 56, &hd, 4); memcpy(o + 60, &nt, 4);
+    V3Desc* d = (V3Desc*)(o + 64);
+    uint64_t cur = 64 + 32 * (uint64_t)ents.size();
+    for (size_t i = 0; i < ents.size(); i++) {
+        const ImgEntry& e = ents[i];
+        if (e.packed) {
+            const uint64_t wb = (uint64_t)e.c->rows * (e.c->Kpad / 7) * 4, mb = (uint64_t)e.c->rows * (e.c->Kpad / 16);
+            d[i] = {1u, (uint32_t)e.c->rows, (uint32_t)e.c->K, (uint32_t)e.c->Kpad, cur, cur + wb};
+            HX_CUDA(cudaMemcpy(o + cur, e.c->words, wb, cudaMemcpyDeviceToHost));
+            HX_CUDA(cudaMemcpy(o + cur + wb, e.c->micro, mb, cudaMemcpyDeviceToHost));
+            memcpy(o + cur + wb + mb, &e.c->ts, 4);
+        } else {
+            d[i] = {0u, 1u, (uint32_t)e.n, (uint32_t)e.n, cur, 0};
+            HX_CUDA(cudaMemcpy(o + cur, e.dense, e.n * 4, cudaMemcpyDeviceToHost));
+        }
+        cur += entry_bytes(e);
+    }
+    return HX_OK;
+}
+
+HX_API int hx_model_v3_save(const hx_model* m, const char* path) {
+    HX_CHECK_ARG(m && path);
+    uint64_t n = 0; int rc = hx_model_v3_size(m, &n); if (rc) return rc;
+    void* buf = malloc(n);
+    if (!buf) return hx_fail(HX_ERR_NOMEM, "malloc(%llu)", (unsigned long long)n);
+    rc = hx_model_v3_export(m, buf, n);
+    if (!rc) {
+        FILE* f = fopen(path, "wb");
+        if (!f) rc = hx_fail(HX_ERR_IO, "cannot write %s", path);
+        else { if (fwrite(buf, 1, n, f) != n) rc = hx_fail(HX_ERR_IO, "short write %s", path); fclose(f); }
+    }
+    free(buf);
+    return rc;
+}
+
+HX_API int hx_model_sha256(const hx_model* m, char hex[65]) {
+    HX_CHECK_ARG(m && hex);
+    uint64_t n = 0; int rc = hx_model_v3_size(m, &n); if (rc) return rc;
+    void* buf = malloc(n);
+    if (!buf) return hx_fail(HX_ERR_NOMEM, "malloc(%llu)", (unsigned long long)n);
+    rc = hx_model_v3_export(m, buf, n);
+    if (!rc) rc = hx_sha256_hex(buf, n, hex);
+    free(buf);
+    return rc;
+}
+
+// ---- stepping ------------------------------------------------------------------------------------
+static int set_pos_tok(hx_model* m, int pos, const int32_t* tok) {
+    HX_CUDA(cudaMemcpyAsync(m->d_pos, &pos, 4, cudaMemcpyHostToDevice, m->st));
+    if (tok) HX_CUDA(cudaMemcpyAsync(m->d_tok, tok, 4, cudaMemcpyHostToDevice, m->st));
+    return HX_OK;
+}
+
+HX_API int hx_decode_step(hx_model* m, const int32_t* ids, int pos, int32_t* next_ids, float* logits) {
+    HX_CHECK_ARG(m && ids);
+    if (pos < 0 || pos >= m->kv_cap) return hx_fail(HX_ERR_STATE, "position %d outside the KV capacity %d", pos, m->kv_cap);
+    if (ids[0] < 0 || ids[0] >= m->cfg.vocab) return hx_fail(HX_ERR_ARG, "token %d outside the vocabulary", ids[0]);
+    int rc = set_pos_tok(m, pos, ids); if (rc) return rc;
+    HX_CUDA(cudaGraphLaunch(m->g_decode, m->st));
+    HX_COUNT_LAUNCH(kernels_per_step(m, true));
+    if (next_ids) HX_CUDA(cudaMemcpyAsync(next_ids, m->d_tok, 4, cudaMemcpyDeviceToHost, m->st));
+    if (logits) HX_CUDA(cudaMemcpyAsync(logits, m->logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToHost, m->st));
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    m->kv_len = pos + 1;
+    return HX_OK;
+}
+
+static int run_prefill(hx_model* m, const int32_t* ids, int T) {
+    // positions 0..T-2 without the head, position T-1 with it
+    HX_CUDA(cudaMemcpyAsync(m->d_prompt, ids, (size_t)T * 4, cudaMemcpyHostToDevice, m->st));
+    int rc = set_pos_tok(m, 0, nullptr); if (rc) return rc;
+    for (int s = 0; s < T - 1; s++) HX_CUDA(cudaGraphLaunch(m->g_prefill, m->st));
+    HX_COUNT_LAUNCH((unsigned long long)(T - 1) * kernels_per_step(m, false));
+    HX_CUDA(cudaMemcpyAsync(m->d_tok, m->d_prompt + (T - 1), 4, cudaMemcpyDeviceToDevice, m->st));
+    HX_CUDA(cudaGraphLaunch(m->g_decode, m->st));
+    HX_COUNT_LAUNCH(kernels_per_step(m, true));
+    return HX_OK;
+}
+
+HX_API int hx_prefill(hx_model* m, const int32_t* ids, int T, int32_t* next_ids, float* logits) {
+    HX_CHECK_ARG(m && ids && T > 0);
+    if (T > m->kv_cap) return hx_fail(HX_ERR_STATE, "prompt of %d tokens exceeds the KV capacity %d", T, m->kv_cap);
+    for (int i = 0; i < T; i++) if (ids[i] < 0 || ids[i] >= m->cfg.vocab) return hx_fail(HX_ERR_ARG, "token %d outside the vocabulary", ids[i]);
+    int rc = run_prefill(m, ids, T); if (rc) return rc;
+    if (next_ids) HX_CUDA(cudaMemcpyAsync(next_ids, m->d_tok, 4, cudaMemcpyDeviceToHost, m->st));
+    if (logits) HX_CUDA(cudaMemcpyAsync(logits, m->logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToHost, m->st));
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    m->kv_len = T;
+    return HX_OK;
+}
+
+HX_API int hx_decode_loop(hx_model* m, const int32_t* ids, int pos0, int n_steps, int32_t* out_ids, float* ms) {
+    HX_CHECK_ARG(m && n_steps > 0);
+    if (pos0 < 0 || pos0 + n_steps > m->kv_cap) return hx_fail(HX_ERR_STATE, "steps %d..%d outside the KV capacity %d", pos0, pos0 + n_steps, m->kv_cap);
+    int rc = set_pos_tok(m, pos0, ids); if (rc) return rc;
+    HX_CUDA(cudaEventRecord(m->ev0, m->st));
+    for (int s = 0; s < n_steps; s++) HX_CUDA(cudaGraphLaunch(m->g_decode, m->st));
+    HX_CUDA(cudaEventRecord(m->ev1, m->st));
+    HX_COUNT_LAUNCH((unsigned long long)n_steps * kernels_per_step(m, true));
+    if (out_ids) HX_CUDA(cudaMemcpyAsync(out_ids, m->d_hist + pos0 + 1, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, m->st));
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    float t = 0.0f; HX_CUDA(cudaEventElapsedTime(&t, m->ev0, m->ev1));
+    m->stats.ms_total = t; m->stats.kernel_launches = (uint32_t)(n_steps * kernels_per_step(m, true));
+    if (ms) *ms = t;
+    m->kv_len = pos0 + n_steps;
+    return HX_OK;
+}
+
+HX_API int hx_generate_greedy(hx_model* m, const int32_t* prompt, int T, int n_new, int32_t* out_ids,
+                              float* ms_prefill, float* ms_decode) {
+    HX_CHECK_ARG(m && prompt && T > 0 && n_new > 0 && out_ids);
+    if (T + n_new - 1 > m->kv_cap) return hx_fail(HX_ERR_STATE, "%d prompt + %d new tokens exceed the KV capacity %d", T, n_new, m->kv_cap);
+    for (int i = 0; i < T; i++) if (prompt[i] < 0 || prompt[i] >= m->cfg.vocab) return hx_fail(HX_ERR_ARG, "token %d outside the vocabulary", prompt[i]);
+    cudaEvent_t e0, e1, e2;
+    HX_CUDA(cudaEventCreate(&e0)); HX_CUDA(cudaEventCreate(&e1)); HX_CUDA(cudaEventCreate(&e2));
+    HX_CUDA(cudaEventRecord(e0, m->st));
+    int rc = run_prefill(m, prompt, T);            // leaves token #1 in d_tok / d_hist[T], *d_pos = T
+    if (!rc) {
+        cudaEventRecord(e1, m->st);
+        for (int s = 1; s < n_new; s++) cudaGraphLaunch(m->g_decode, m->st);
+        HX_COUNT_LAUNCH((unsigned long long)(n_new - 1) * kernels_per_step(m, true));
+        cudaEventRecord(e2, m->st);
+        cudaMemcpyAsync(out_ids, m->d_hist + T, (size_t)n_new * 4, cudaMemcpyDeviceToHost, m->st);
+        cudaError_t e = cudaStreamSynchronize(m->st);
+        if (e != cudaSuccess) rc = hx_fail(HX_ERR_CUDA, "generate: %s", cudaGetErrorString(e));
+        else {
+            float a = 0, b = 0; cudaEventElapsedTime(&a, e0, e1); cudaEventElapsedTime(&b, e1, e2);
+            if (ms_prefill) *ms_prefill = a;
+            if (ms_decode) *ms_decode = b;
+            m->stats.ms_total = a + b;
+            m->stats.kernel_launches = (uint32_t)((T - 1) * kernels_per_step(m, false) + n_new * kernels_per_step(m, true));
+            m->kv_len = T + n_new - 1;
+        }
+    }
+    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
+    return rc;
+}
+
+HX_API int hx_model_fill_kv(hx_model* m, int T, uint64_t seed) {
+    HX_CHECK_ARG(m && T >= 0 && T <= m->kv_cap);
+    const hx_config& c = m->cfg;
+    // whole cache gets values; only positions below the running length are ever read
+    const size_t n = (size_t)c.n_layers * c.n_kv_heads * m->kv_cap * c.head_dim;
+    int rc = hx_launch_fill_normal(m->kc, n, 1.0f, seed * 2 + 1, m->st); if (rc) return rc;
+    rc = hx_launch_fill_normal(m->vc, n, 1.0f, seed * 2 + 2, m->st); if (rc) return rc;
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    m->kv_len = T;
+    return HX_OK;
+}
+
+// ---- tensor parallel (collectives are loaded on demand) ---------------------------------------------
+HX_API int hx_tp_unique_id(uint8_t id[128]) { (void)id; return hx_fail(HX_ERR_COMM, "tensor parallel is not built yet"); }
+HX_API int hx_tp_init(const uint8_t id[128], int rank, int world) { (void)id; (void)rank; (void)world; return hx_fail(HX_ERR_COMM, "tensor parallel is not built yet"); }
+HX_API int hx_tp_shutdown(void) { return HX_OK; }
+
+// ---- BASELINE config 1: quantize W, then y = dequant(W) x, host buffers in and out ---------------------
+HX_API int hx_roundtrip_host(const float* w, int rows, int K, const float* x, float* y, int* kpad_out) {
+    HX_CHECK_ARG(w && x && y && rows > 0 && K > 0 && K % 4 == 0);
+    const int Kpad = hx_kpad(K), Kd = hx_kd(K);
+    float *dw = nullptr, *dx = nullptr, *dy = nullptr, *dts = nullptr; int32_t* dq = nullptr; uint8_t *dm = nullptr, *dc = nullptr, *ds = nullptr;
+    int rc = HX_OK;
+    auto fr = [&]() { cudaFree(dw); cudaFree(dx); cudaFree(dy); cudaFree(dts); cudaFree(dq); cudaFree(dm); cudaFree(dc); cudaFree(ds); };
+#define RT(call) do { cudaError_t _e = (call); if (_e != cudaSuccess) { fr(); return hx_fail(HX_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(_e)); } } while (0)
+    RT(cudaMalloc(&dw, (size_t)rows * K * 4)); RT(cudaMalloc(&dx, (size_t)Kd * 4)); RT(cudaMalloc(&dy, (size_t)rows * 4));
+    RT(cudaMalloc(&dts, 4)); RT(cudaMalloc(&dq, (size_t)rows * (Kpad / 7) * 4)); RT(cudaMalloc(&dm, (size_t)rows * (Kpad / 16)));
+    RT(cudaMalloc(&dc, (size_t)rows * (Kd / 2))); RT(cudaMalloc(&ds, (size_t)rows * (Kd / 16)));
+    RT(cudaMemcpy(dw, w, (size_t)rows * K * 4, cudaMemcpyHostToDevice));
+    RT(cudaMemset(dx, 0, (size_t)Kd * 4));
+    RT(cudaMemcpy(dx, x, (size_t)K * 4, cudaMemcpyHostToDevice));
+    rc = hx_quantize_nvfp4(dw, rows, K, dq, dm, nullptr, dts, nullptr);
+    if (!rc) rc = hx_repack_d16(dq, dm, rows, K, Kpad, dc, ds, nullptr);
+    if (!rc) rc = hx_gemv_d16(dx, dc, ds, dts, dy, rows, Kd, nullptr);
+    if (rc) { fr(); return rc; }
+    RT(cudaMemcpy(y, dy, (size_t)rows * 4, cudaMemcpyDeviceToHost));
+#undef RT
+    fr();
+    if (kpad_out) *kpad_out = Kpad;
+    return HX_OK;
+}

@@ -1,0 +1,216 @@
+/* helix_b200.h -- C ABI of libhelix_b200.so: the NVFP4 quantizer and the transformer
+ * decode/prefill loop of Helix's quantized-inference path, implemented for NVIDIA B200 (sm_100a).
+ *
+ * Conventions (they mirror the reference's C host programs): every function returns an int status,
+ * 0 = success, non-zero = one of the HX_ERR_* codes; hx_last_error() gives the message of the last
+ * failure on the calling thread.  The library never exits or aborts the process, never falls back
+ * to a CPU path, and fails with HX_ERR_CUDA when no usable GPU is present.  Buffers are owned by
+ * the caller unless a function says otherwise.  An hx_model may be driven by one thread at a time.
+ *
+ * "Reference" citations are paths inside the Helix source tree.
+ */
+#ifndef HELIX_B200_H
+#define HELIX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HX_OK            0
+#define HX_ERR_ARG       1   /* bad argument (null pointer, size out of range, misaligned) */
+#define HX_ERR_CUDA      2   /* a CUDA call failed; hx_last_error() has the CUDA error string */
+#define HX_ERR_IO        3   /* file could not be opened / read / written */
+#define HX_ERR_FORMAT    4   /* not an HXGW v3 file, or its descriptors do not tile the file */
+#define HX_ERR_STATE     5   /* call out of order (e.g. decode past the KV capacity) */
+#define HX_ERR_NOMEM     6   /* host or device allocation failed */
+#define HX_ERR_COMM      7   /* collective library missing or failed */
+#define HX_ERR_TIMEOUT   8   /* a bounded device-side wait ran out */
+
+const char* hx_last_error(void);
+const char* hx_version(void);
+
+/* ---------------------------------------------------------------- device memory helpers ------ */
+/* Thin wrappers so that callers without a CUDA binding (ctypes, cgo) can own device buffers. */
+int hx_device_count(int* n);
+int hx_set_device(int dev);
+int hx_malloc(void** dptr, size_t bytes);
+int hx_free(void* dptr);
+int hx_memcpy_h2d(void* dst, const void* src, size_t bytes);
+int hx_memcpy_d2h(void* dst, const void* src, size_t bytes);
+int hx_memset(void* dptr, int value, size_t bytes);
+int hx_sync(void);
+/* Pinned host memory for the end-to-end paths. */
+int hx_host_alloc(void** hptr, size_t bytes);
+int hx_host_free(void* hptr);
+
+/* ---------------------------------------------------------------- codecs ---------------------- */
+/* Scalar codecs, host side.  Reference: e2m1_decode / e2m1_encode / e4m3_decode / e4m3_encode,
+ * helixc/runtime/gpt2_pack.c:291-343.  The encoders reproduce the reference's tie-breaking
+ * (nearest value, the lower code on a tie), which is not IEEE round-to-nearest-even. */
+float hx_e2m1_decode(int code);
+int   hx_e2m1_encode(float v);
+float hx_e4m3_decode(int code);
+int   hx_e4m3_encode(float v);
+
+/* ---------------------------------------------------------------- quantizer ------------------- */
+/* Kpad = K rounded up to a multiple of 112 (gpt2_pack.c:351). */
+int hx_kpad(int K);
+
+/* NVFP4 forward quantizer on the GPU, all pointers are DEVICE pointers.
+ * Replaces nvfp4_quantize_tensor, helixc/runtime/gpt2_pack.c:350-373, bit for bit:
+ *   w      [rows*K] f32 row-major
+ *   words  [rows*(Kpad/7)] int32, seven E2M1 codes per word, low nibble first
+ *   micro  [rows*(Kpad/16)] uint8, E4M3 scale code per 16 elements along K     (may be NULL)
+ *   sc     [rows*(Kpad/16)] f32, e4m3_decode(micro)*ts                          (may be NULL)
+ *   ts     [1] f32 per-tensor scale amax/(6*448), 1.0 for an all-zero tensor    (may be NULL)
+ * stream is a cudaStream_t (NULL = default stream); the call is asynchronous. */
+int hx_quantize_nvfp4(const float* w, int rows, int K, int32_t* words, uint8_t* micro, float* sc,
+                      float* ts, void* stream);
+
+/* Same contract with HOST buffers: copies w to the device, quantizes, copies the results back and
+ * synchronises.  This is the call that stands where the importer calls nvfp4_quantize_tensor
+ * (gpt2_pack.c:676). */
+int hx_quantize_nvfp4_host(const float* w, int rows, int K, int32_t* words, uint8_t* micro, float* sc,
+                           float* ts);
+
+/* Dequantize the packed layout to f32 [rows*Kpad] on the GPU (device pointers).
+ * Replaces v3_dequant_packed, helixc/runtime/gpt2_infer.c:109-122 (micro bytes + ts), and
+ * nvfp4_host_dequant, gpt2_pack.c:375-387 (pre-collapsed f32 scales; pass micro=NULL, sc!=NULL). */
+int hx_dequant_nvfp4(const int32_t* words, const uint8_t* micro, const float* ts, const float* sc,
+                     float* out, int rows, int Kpad, void* stream);
+
+/* Micro bytes -> four-per-int32 words with row stride ceil(kblk/4), device pointers.
+ * Replaces v3_pack_micro, gpt2_infer.c:2151-2161. */
+int hx_pack_micro(const uint8_t* micro, int rows, int kblk, int32_t* dst, void* stream);
+
+/* ---------------------------------------------------------------- fused dequant GEMV ---------- */
+/* y[n] = sum_{col<Kpad} x[col] * dequant(W[n,col]) over the committed (7-per-word) layout.
+ * Device pointers; x is Kpad long with a zero tail; micro4 is the four-per-word micro layout;
+ * ts is a 1-element device array.  Replaces fused_gemv, gpt2_infer.c:2281-2297. */
+int hx_gemv_nvfp4(const float* x, const int32_t* words, const int32_t* micro4, const float* ts,
+                  float* y, int N, int Kpad, void* stream);
+
+/* Round trip of BASELINE config 1 with HOST buffers: quantize W [rows*K], then y = dequant(W) x.
+ * x has K elements.  Returns Kpad through kpad_out when non-NULL. */
+int hx_roundtrip_host(const float* w, int rows, int K, const float* x, float* y, int* kpad_out);
+
+/* Dense decode layout ("D16"): per row, Kd/2 bytes of codes (two per byte, low nibble first, Kd = K
+ * rounded up to 64) followed in a second array by Kd/16 scale bytes.  It carries exactly the
+ * information of the committed layout; the commitment hash is always taken over the file bytes. */
+int hx_kd(int K);
+int hx_repack_d16(const int32_t* words, const uint8_t* micro, int rows, int K, int Kpad,
+                  uint8_t* codes, uint8_t* scales, void* stream);
+/* y[n] = ts * sum_k x[k] * mag(code[n,k]) * e4m3(scale[n,k/16]); x is Kd long, zero tail. */
+int hx_gemv_d16(const float* x, const uint8_t* codes, const uint8_t* scales, const float* ts,
+                float* y, int N, int Kd, void* stream);
+
+/* ---------------------------------------------------------------- SHA-256 / receipt ----------- */
+/* FIPS 180-4.  Replaces sha256 / sha256_hex / sha256_file, gpt2_infer.c:137-213. */
+int hx_sha256(const void* data, size_t n, uint8_t out[32]);
+int hx_sha256_hex(const void* data, size_t n, char hex[65]);
+int hx_sha256_file(const char* path, char hex[65]);
+
+/* Write a HELIX_V16_RECEIPT and its "<out_path>.logits" side file.  Same fields and formats as
+ * run_v3_receipt_from_logits, gpt2_infer.c:2827-2871.  oracle_logits may be NULL (max_abs = -1,
+ * argmax_match = -1); tau <= 0 writes the measured max_abs as tier3_tau (calib_tau, :2765-2769). */
+int hx_receipt_emit(const char* out_path, const char* weights_path, const int* ids, int n_ids,
+                    const float* logits, int n_logits, const float* oracle_logits, double tau,
+                    const char* tau_prov);
+/* The independent verifier: 0 = RECEIPT_CHECK_PASS, otherwise HX_ERR_FORMAT with the reference's
+ * REJECT=<reason> token in hx_last_error().  Replaces run_v3_receipt_check, :2876-2912. */
+int hx_receipt_check(const char* receipt, const char* weights_path, const char* logits_path,
+                     const char* oracle_path);
+
+/* ---------------------------------------------------------------- model ----------------------- */
+typedef struct hx_model hx_model;
+
+typedef struct {
+    int32_t arch;        /* 1 = Llama/Qwen3 family (RMSNorm, RoPE, GQA, SwiGLU); 0 = GPT-2 */
+    int32_t n_layers, d_model, n_heads, n_kv_heads, head_dim, d_ff, vocab, max_ctx;
+    float   rope_theta;
+    float   norm_eps;    /* eps the kernels use; the reference computes with 1e-5 whatever the file says */
+    int32_t qk_norm;     /* 1 = per-head RMSNorm on q and k before RoPE (Qwen3) */
+} hx_config;
+
+#define HX_LOAD_KEEP_COMMITTED  1   /* keep the 7-per-word layout resident beside the decode layout */
+#define HX_LOAD_VERIFY_SHA      2   /* hash the file while loading (hx_model_sha256) */
+#define HX_LOAD_FILE_EPS        4   /* use the header's rms_norm_eps instead of the reference's 1e-5 */
+
+/* Load an HXGW v3 file (helixc/runtime/gpt2_pack.c:578-733 writes it) into HBM.  Validation follows
+ * load_gpt2_weights / peek_weights_header, gpt2_infer.c:581-603, 648-667.  Replaces the per-layer
+ * streaming loader (upload_layer_ll, v3_upload_gpu, v3_resident_ptrs, :2163-2276, 2407-2450) with
+ * one-time residency.  kv_cap = positions of KV cache to allocate; batch = independent sequences.
+ * tp_rank / tp_size select this process's tensor-parallel shard (1-GPU: 0 / 1). */
+int hx_model_load(hx_model** out, const char* path, int kv_cap, int batch, int flags,
+                  int tp_rank, int tp_size);
+
+/* Build a model of the given shape with seeded synthetic weights generated and quantized on the
+ * GPU (linear weights and embedding N(0, 0.02), norm gains 1).  Stands in for checkpoints. */
+int hx_model_synth(hx_model** out, const hx_config* cfg, uint64_t seed, int kv_cap, int batch,
+                   int flags, int tp_rank, int tp_size);
+
+int hx_model_free(hx_model* m);
+int hx_model_config(const hx_model* m, hx_config* cfg);
+/* Bytes of weights read per decoded token in the decode layout (this rank's shard). */
+int hx_model_weight_bytes(const hx_model* m, uint64_t* decode_layout, uint64_t* committed_layout);
+
+/* Size of / copy of the HXGW v3 image of the model (needs HX_LOAD_KEEP_COMMITTED, tp_size 1). */
+int hx_model_v3_size(const hx_model* m, uint64_t* bytes);
+int hx_model_v3_export(const hx_model* m, void* host_buf, uint64_t bytes);
+int hx_model_v3_save(const hx_model* m, const char* path);
+/* SHA-256 of the HXGW v3 image (the reference's model_sha256 commitment, gpt2_infer.c:2791). */
+int hx_model_sha256(const hx_model* m, char hex[65]);
+
+/* Forget the KV cache (gpt2_infer.c:3354 resets kv_len per request). */
+int hx_model_reset(hx_model* m);
+
+/* One decode step for every sequence of the batch: ids[batch] are the tokens at position `pos`
+ * (HOST pointer); on return next_ids[batch] (HOST, may be NULL) holds the arg-max token and, when
+ * logits != NULL, logits[batch*vocab] (HOST) holds the f32 logits.
+ * Replaces decode_step_llama + the host argmax, gpt2_infer.c:1341-1613, 1735-1739. */
+int hx_decode_step(hx_model* m, const int32_t* ids, int pos, int32_t* next_ids, float* logits);
+
+/* Prefill ids[batch*T] (HOST, row-major per sequence) into the KV cache and return the arg-max of
+ * the last position (and its logits when logits != NULL).  Replaces forward_full, :1297-1333. */
+int hx_prefill(hx_model* m, const int32_t* ids, int T, int32_t* next_ids, float* logits);
+
+/* Greedy generation, tokens never leave the GPU between steps: prefill the prompt, then n_new
+ * steps feeding each arg-max back.  out_ids[batch*n_new] HOST.  Replaces run_generate, :3123-3195.
+ * ms_decode (may be NULL) receives the device time of the decode steps alone. */
+int hx_generate_greedy(hx_model* m, const int32_t* prompt, int T, int n_new, int32_t* out_ids,
+                       float* ms_prefill, float* ms_decode);
+
+/* Device time accounting of the last hx_generate_greedy / hx_decode_loop call. */
+typedef struct {
+    float    ms_total;          /* CUDA-event time of the timed region */
+    uint32_t kernel_launches;   /* kernels of this library launched inside it */
+    float    ms_gemv;           /* when per-kernel profiling is on (hx_model_set_profile) */
+    float    ms_attn;
+    float    ms_other;
+} hx_step_stats;
+int hx_model_last_stats(const hx_model* m, hx_step_stats* st);
+int hx_model_set_profile(hx_model* m, int on);
+
+/* Run n_steps decode steps starting at position pos0 with the KV cache as it stands, feeding back
+ * the arg-max (first token ids[batch], HOST).  Used by the benchmark: inputs resident, one timed
+ * region.  out_ids[batch*n_steps] may be NULL. */
+int hx_decode_loop(hx_model* m, const int32_t* ids, int pos0, int n_steps, int32_t* out_ids, float* ms);
+
+/* Fill the KV cache for positions [0, T) with seeded synthetic values (benchmark set-up for a long
+ * context without running a long prefill). */
+int hx_model_fill_kv(hx_model* m, int T, uint64_t seed);
+
+/* ---------------------------------------------------------------- tensor parallel ------------- */
+/* NCCL is loaded at run time (libnccl.so.2).  id is NCCL's 128-byte unique id, created on rank 0
+ * with hx_tp_unique_id and distributed by the caller (any out-of-band channel). */
+int hx_tp_unique_id(uint8_t id[128]);
+int hx_tp_init(const uint8_t id[128], int rank, int world);
+int hx_tp_shutdown(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HELIX_B200_H */
