@@ -1,0 +1,332 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 decode path: greedy batch-1 decode of a Qwen3-8B-shaped model with seeded
+synthetic weights (BASELINE.json config 3: 512-token prompt, 256 new tokens).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one 256-token greedy continuation from position 512 of the prompt's KV cache.  `value`
+is decoded tokens per second with everything resident in HBM (CUDA events around the K steps, max over
+ranks); `e2e` is the same metric through the public per-token call hx_decode_step with host buffers
+(token id in, next id and the logits row out, every token).  With N > 1 each GPU holds a full weight
+copy and decodes its own sequence (independent sequences, no data-path collective): weak scaling.
+
+`--impl reference` times the CPU restatement of the reference worker's decode (oracle/hx_oracle.c, all
+host threads) on the same model shape; rank 0 alone runs it.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PROMPT_LEN, NEW_TOKENS = 512, 256
+WORKLOAD = "qwen3-8b-shape nvfp4 greedy decode, batch 1, 512-token prompt + 256 new tokens"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, dev):
+        self.dev, self.proc, self.lines = dev, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.dev), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_init(n):
+    if n <= 1:
+        return None
+    import torch.distributed as dist
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("gloo", rank=int(os.environ["RANK"]), world_size=int(os.environ["WORLD_SIZE"]))
+    return dist
+
+
+def all_max(dist, v):
+    if dist is None:
+        return v
+    import torch
+    t = torch.tensor([v], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def all_sum(dist, v):
+    if dist is None:
+        return v
+    import torch
+    t = torch.tensor([v], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t[0])
+
+
+def algorithmic_bytes_per_token(cfg, T):
+    """0.5625 B per logical weight of every linear incl. lm_head + the fp32 KV rows read + one embedding row."""
+    NL, DM, NH, NKV, DH, DFF, NV = (cfg[k] for k in ("n_layers", "d_model", "n_heads", "n_kv_heads", "head_dim", "d_ff", "vocab"))
+    QD, KVD = NH * DH, NKV * DH
+    weights = NL * (QD * DM + 2 * KVD * DM + DM * QD + 2 * DFF * DM + DM * DFF) + NV * DM
+    return weights * 0.5625, 2 * NL * NKV * DH * 4 * T, DM * 4
+
+
+def synth_image_on_host(shape, seed):
+    """An HXGW v3 image of the given shape built on the host without the GPU: codes and scale bytes are
+    drawn directly in the committed layout (uniform codes, scale bytes in the range the quantizer emits
+    for N(0, 0.02) weights).  It costs the CPU decode exactly what a quantized checkpoint costs."""
+    import struct
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    cfg = dict(NL=shape["n_layers"], DM=shape["d_model"], NH=shape["n_heads"], NKV=shape["n_kv_heads"], DH=shape["head_dim"],
+               DFF=shape["d_ff"], NV=shape["vocab"])
+    order = ol.qwen3_tensor_order(cfg)
+    rng = np.random.default_rng(seed)
+    sizes, cur = [], 64 + 32 * len(order)
+    for name, shp, packed in order:
+        if packed:
+            kp = ol.kpad(shp[1]); n = shp[0] * (kp // 7) * 4 + shp[0] * (kp // 16) + 4
+        else:
+            n = int(np.prod(shp)) * 4
+        sizes.append(n); cur += n
+    img = np.empty(cur, np.uint8)
+    hdr = bytearray(64)
+    struct.pack_into("<8I", hdr, 0, 0x48584757, 3, cfg["NL"], cfg["DM"], cfg["NH"], cfg["NV"], 40960, cfg["DFF"])
+    struct.pack_into("<II", hdr, 40, 1, cfg["NKV"]); struct.pack_into("<ff", hdr, 48, 1e6, 1e-6)
+    struct.pack_into("<II", hdr, 56, cfg["DH"], len(order))
+    img[:64] = np.frombuffer(bytes(hdr), np.uint8)
+    off, dpos = 64 + 32 * len(order), 64
+    for (name, shp, packed), n in zip(order, sizes):
+        if packed:
+            rows, K = shp; kp = ol.kpad(K); wb = rows * (kp // 7) * 4; mb = rows * (kp // 16)
+            img[dpos:dpos + 32] = np.frombuffer(struct.pack("<IIIIQQ", 1, rows, K, kp, off, off + wb), np.uint8)
+            img[off:off + wb] = rng.integers(0, 256, wb, dtype=np.uint8)
+            img[off + 3:off + wb:4] &= 0x0F                       # 28-bit words: the top nibble is empty
+            img[off + wb:off + wb + mb] = rng.integers(0x28, 0x7F, mb, dtype=np.uint8)
+            img[off + wb + mb:off + n] = np.frombuffer(struct.pack("<f", 4.2e-5), np.uint8)
+        else:
+            cnt = int(np.prod(shp))
+            img[dpos:dpos + 32] = np.frombuffer(struct.pack("<IIIIQQ", 0, 1, cnt, cnt, off, 0), np.uint8)
+            v = img[off:off + n].view(np.float32)
+            if len(shp) == 1:
+                v[:] = 1.0
+            else:
+                step = 1 << 24
+                for s in range(0, cnt, step):
+                    e = min(cnt, s + step)
+                    v[s:e] = rng.standard_normal(e - s, dtype=np.float32) * np.float32(0.02)
+        off += n; dpos += 32
+    return img
+
+
+def cpu_decode_tok_s(image, n_tokens, kv_cap=64):
+    """tokens/s of the CPU restatement decoding n_tokens greedy tokens from an empty cache."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    om = ol.OracleModel(image=image, kv_cap=kv_cap)
+    tok, t0 = 1, time.perf_counter()
+    for pos in range(n_tokens):
+        tok = int(np.argmax(om.decode(tok, pos)))
+    dt = time.perf_counter() - t0
+    om.close()
+    return n_tokens / dt, ol.oracle().orc_num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import helix_b200 as hb
+    shape = dict(hb.QWEN3_8B)
+    image = synth_image_on_host(shape, seed=1)
+    n_tok = 2
+    for _ in range(args.warmup):
+        cpu_decode_tok_s(image, 1)
+    t0 = time.perf_counter()
+    vals = []
+    cores = 1
+    for _ in range(args.steps):
+        v, cores = cpu_decode_tok_s(image, n_tok)
+        vals.append(v)
+    wall = time.perf_counter() - t0
+    value = args.steps * n_tok / sum(n_tok / v for v in vals)
+    sample = f"{n_tok} greedy tokens per step from an empty KV cache (positions 0..{n_tok - 1}), full 36-layer model + lm_head"
+    line = {"metric": "nvfp4_decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
+            "config": {"workload": WORKLOAD, "reference_arm": "CPU restatement of the reference decode (oracle/hx_oracle.c); "
+                       "the reference's own CPU build covers GPT-2 f32 only"},
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import helix_b200 as hb
+    from helix_b200.lib import check, lib
+    dist = dist_init(args.gpus)
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    L = lib()
+    check(L.hx_set_device(local))
+    shape = dict(hb.QWEN3_8B)
+    keep = 1 if (rank == 0 and not args.no_cpu_baseline) else 0
+    model = hb.Model.synth(shape, seed=1, kv_cap=PROMPT_LEN + NEW_TOKENS + 8, flags=keep)
+    cfgd = model.cfg.as_dict()
+    rng = np.random.default_rng(2 + rank)
+    prompt = rng.integers(0, shape["vocab"], PROMPT_LEN).astype(np.int32)
+    first = model.prefill(prompt)                      # real KV for positions 0..511 + the first new token
+    dbytes, cbytes = model.weight_bytes()
+
+    def one_step():
+        return model.decode_loop(first, PROMPT_LEN, NEW_TOKENS)
+
+    for _ in range(args.warmup):
+        one_step()
+    if dist is not None:
+        dist.barrier()
+    check(L.hx_sync())
+    sampler = ClockSampler(local); sampler.start()
+    l0 = hb.launch_count()
+    ms_total, toks = 0.0, None
+    for _ in range(args.steps):
+        toks, ms = one_step()
+        ms_total += ms
+    check(L.hx_sync())
+    launches = hb.launch_count() - l0
+    clocks = sampler.stop()
+    if dist is not None:
+        dist.barrier()
+    ms_max = all_max(dist, ms_total)
+    n_tok_all = args.gpus * args.steps * NEW_TOKENS
+    value = n_tok_all / (ms_max * 1e-3)
+
+    # per-kernel device time of the dominant kernel (k_linear), event pair around every launch
+    model.set_profile(True)
+    model.decode_loop(first, PROMPT_LEN, 8)
+    _, _ = model.decode_loop(first, PROMPT_LEN, 32)
+    st = model.last_stats()
+    model.set_profile(False)
+    wbytes, kvbytes_mid, embbytes = algorithmic_bytes_per_token(cfgd, PROMPT_LEN + NEW_TOKENS // 2)
+    n_lin = 4 * shape["n_layers"] + 1
+    peak, peak_src = peaks()
+    gemv_ms_tok = st["ms_gemv"] / 32
+    achieved = wbytes / (gemv_ms_tok * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "k_linear (fused dequant GEMV, all 4*NL+1 launches of a token)",
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "peak_source": peak_src, "algorithmic_bytes_per_launch": wbytes / n_lin,
+                "avg_launch_us": gemv_ms_tok * 1e3 / n_lin,
+                "token_bytes": {"weights": wbytes, "kv_mid_run": kvbytes_mid, "embedding_row": embbytes},
+                "whole_token_frac": (wbytes + kvbytes_mid + embbytes) * value / args.gpus / 1e9 / peak,
+                "per_token_ms": {"gemv": gemv_ms_tok, "attention": st["ms_attn"] / 32, "other": st["ms_other"] / 32}}
+
+    # end to end through the per-token public call, host buffers both ways
+    check(L.hx_sync())
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    e2e_steps = max(1, min(args.steps, 2))
+    for _ in range(e2e_steps):
+        tok = first
+        for i in range(NEW_TOKENS):
+            tok, lg = model.decode_step(tok, PROMPT_LEN + i, want_logits=True)
+    e2e_s = all_max(dist, time.perf_counter() - t0)
+    e2e = {"value": args.gpus * e2e_steps * NEW_TOKENS / e2e_s, "unit": "tok/s",
+           "h2d_bytes_per_step": NEW_TOKENS * 4, "d2h_bytes_per_step": NEW_TOKENS * (4 + shape["vocab"] * 4),
+           "api": "hx_decode_step per token: token id H2D, next id + f32 logits row D2H (what the reference worker reads back)"}
+
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline:
+        image = model.v3_image()                       # the same weights, HXGW v3 bytes exported from HBM
+        v1, cores = cpu_decode_tok_s(image, 1)
+        n = int(max(2, min(16, 20.0 * v1)))
+        v, cores = cpu_decode_tok_s(image, n)
+        cpu = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port",
+               "sample": f"{n} greedy tokens from an empty KV cache on the same weights (HXGW v3 image exported from the GPU), "
+                         "full model + lm_head; CPU restatement of the reference decode, OpenMP over rows"}
+        del image
+    if rank == 0:
+        line = {"metric": "nvfp4_decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": WORKLOAD, "weights": "nvfp4 (e2m1 + e4m3/16 + f32 tensor scale), HBM resident",
+                           "kv_cache": "f32", "parallelism": f"replicas x{args.gpus} (one sequence per GPU)" if args.gpus > 1 else "single GPU",
+                           "l2": "weights (4.26 GB per token) exceed the 126 MB L2, no flush needed",
+                           "tokens_per_step": NEW_TOKENS, "weight_bytes_decode_layout": dbytes, "weight_bytes_committed_layout": cbytes},
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+                "ms_per_token": ms_max / args.steps / NEW_TOKENS, "last_tokens": [int(t) for t in toks[-4:]]}
+        print(json.dumps(line), flush=True)
+    model.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

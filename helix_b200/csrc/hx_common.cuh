@@ -79,43 +79,41 @@ __host__ __device__ __forceinline__ float hx_e4m3_dec(int c) {
 }
 
 // E4M3 encode of v with the reference's semantics: the nearest of the 254 non-NaN codes by
-// |decode(c) - v| evaluated in f32, the first (lowest) code on a tie, and code 0 when no distance is
-// below 1e30 (NaN, infinities, absurdly large v).  For v >= 0 the winner is found in closed form:
-// values are monotonic in the code, distances to the two neighbours are exact (Sterbenz), so the
-// rule is "round to nearest, a tie goes to the lower code".  Negative v only occurs for corrupt
-// input; the search then runs over the negative codes and zero the same way.
+// |decode(c) - v| evaluated in f32, the first (lowest) code on a tie, code 0 when no distance is
+// below 1e30.  For 0 <= v <= 512 (everything the quantizer can produce: the ratio never exceeds
+// 448 by more than rounding) the winner is found in closed form: values are monotonic in the code
+// and the distances to the two neighbours are exact (Sterbenz), so the rule is "round to nearest, a
+// tie goes to the lower code".  Outside that range f32 rounding of the distances themselves creates
+// ties between far-apart codes, so the search is run as written.
 // Reference: e4m3_encode, gpt2_pack.c:339-343.
+__host__ __device__ __forceinline__ int hx_e4m3_enc_search(float v) {
+    int best = 0; float bd = 1.0e30f;
+    for (int c = 0; c < 256; c++) {
+        if ((c & 0x7F) == 0x7F) continue;
+        float d = hx_e4m3_dec(c) - v; if (d < 0) d = -d;
+        if (d < bd) { bd = d; best = c; }
+    }
+    return best;
+}
 __host__ __device__ __forceinline__ int hx_e4m3_enc(float v) {
-    float a = v < 0.0f ? -v : v;
-    int c;
-    if (!(a == a)) return 0;                       // NaN: no distance compares below the seed
-    if (a >= 448.0f) c = 0x7E;
-    else if (a < 0.015625f) {                      // below 2^-6: subnormal codes, step 2^-9
-        float t = a * 512.0f;                      // exact
-        int k = (int)t;
-        c = k + ((t - (float)k) > 0.5f ? 1 : 0);   // 8 rolls into code 0x08 = 2^-6
-    } else {
-        uint32_t bits;
+    if (!(v >= 0.0f && v <= 512.0f)) return hx_e4m3_enc_search(v);   // negative, huge or NaN: rare
+    if (v >= 448.0f) return 0x7E;
+    if (v < 0.015625f) {                           // below 2^-6: subnormal codes, step 2^-9
+        const float t = v * 512.0f;                // exact
+        const int k = (int)t;
+        return k + ((t - (float)k) > 0.5f ? 1 : 0);   // 8 rolls into code 0x08 = 2^-6
+    }
+    uint32_t bits;
 #ifdef __CUDA_ARCH__
-        bits = __float_as_uint(a);
+    bits = __float_as_uint(v);
 #else
-        memcpy(&bits, &a, 4);
+    memcpy(&bits, &v, 4);
 #endif
-        int e = (int)(bits >> 23) - 127 + 7;       // 1..15
-        uint32_t man = bits & 0x7FFFFFu;
-        c = (e << 3) | (int)(man >> 20);
-        if ((man & 0xFFFFFu) > 0x80000u) c += 1;   // above the midpoint; carries into the exponent
-        if (c > 0x7E) c = 0x7E;
-    }
-    // the search only accepts a distance below 1e30
-    float d = hx_e4m3_dec(c) - a; if (d < 0) d = -d;
-    if (!(d < 1.0e30f)) return 0;
-    if (v < 0.0f && c != 0) {
-        // negative input: candidates are code 0 (distance a) and the negative codes; code 0 comes
-        // first in code order, so it wins ties.
-        return (a <= d) ? 0 : (c | 0x80);
-    }
-    return c;
+    const int e = (int)(bits >> 23) - 127 + 7;     // 1..15
+    const uint32_t man = bits & 0x7FFFFFu;
+    int c = (e << 3) | (int)(man >> 20);
+    if ((man & 0xFFFFFu) > 0x80000u) c += 1;       // above the midpoint; carries into the exponent
+    return c > 0x7E ? 0x7E : c;
 }
 
 // ---- device helpers -----------------------------------------------------------------------------

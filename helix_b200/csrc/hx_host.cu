@@ -210,3 +210,81 @@ HX_API int hx_receipt_check(const char* receipt, const char* weights_path, const
     hx_set_error("RECEIPT_CHECK_PASS");
     return HX_OK;
 }
+
+// ---- kernel-image launcher ---------------------------------------------------------------------------
+// Loads a module image (fatbin, cubin or PTX text) and launches entries by name exactly the way the
+// reference's host programs do: cuModuleLoadData + cuModuleGetFunction + cuLaunchKernel with the
+// caller's grid/block, zero dynamic shared memory, the NULL stream
+// (helixc/runtime/gpt2_infer.c:373-375, 1944-1964; helixc/runtime/cuda_launch.c:1058-1088).
+// The driver library is bound at run time so that the shared object loads on machines without one.
+#include <dlfcn.h>
+namespace {
+typedef int (*cuModuleLoadData_t)(void**, const void*);
+typedef int (*cuModuleGetFunction_t)(void**, void*, const char*);
+typedef int (*cuLaunchKernel_t)(void*, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, void*, void**, void**);
+typedef int (*cuModuleUnload_t)(void*);
+typedef int (*cuCtxSynchronize_t)(void);
+typedef int (*cuGetErrorString_t)(int, const char**);
+struct Drv {
+    void* so = nullptr; cuModuleLoadData_t load; cuModuleGetFunction_t getf; cuLaunchKernel_t launch;
+    cuModuleUnload_t unload; cuCtxSynchronize_t sync; cuGetErrorString_t errstr;
+};
+Drv* drv() {
+    static Drv d; static bool tried = false;
+    if (tried) return d.so ? &d : nullptr;
+    tried = true;
+    void* so = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+    if (!so) return nullptr;
+    d.load = (cuModuleLoadData_t)dlsym(so, "cuModuleLoadData");
+    d.getf = (cuModuleGetFunction_t)dlsym(so, "cuModuleGetFunction");
+    d.launch = (cuLaunchKernel_t)dlsym(so, "cuLaunchKernel");
+    d.unload = (cuModuleUnload_t)dlsym(so, "cuModuleUnload");
+    d.sync = (cuCtxSynchronize_t)dlsym(so, "cuCtxSynchronize");
+    d.errstr = (cuGetErrorString_t)dlsym(so, "cuGetErrorString");
+    if (!d.load || !d.getf || !d.launch || !d.unload || !d.sync) return nullptr;
+    d.so = so;
+    return &d;
+}
+int drv_fail(Drv* d, int rc, const char* what) {
+    const char* s = nullptr;
+    if (d->errstr) d->errstr(rc, &s);
+    return hx_fail(HX_ERR_CUDA, "%s failed: %s (CUresult %d)", what, s ? s : "?", rc);
+}
+}  // namespace
+
+HX_API int hx_image_open(void** module, const char* path) {
+    HX_CHECK_ARG(module && path);
+    Drv* d = drv();
+    if (!d) return hx_fail(HX_ERR_CUDA, "libcuda.so.1 is not available");
+    HX_CUDA(cudaFree(0));                       // make the primary context current
+    FILE* f = fopen(path, "rb");
+    if (!f) return hx_fail(HX_ERR_IO, "cannot open %s", path);
+    std::vector<char> buf;
+    char tmp[65536]; size_t got;
+    while ((got = fread(tmp, 1, sizeof(tmp), f)) > 0) buf.insert(buf.end(), tmp, tmp + got);
+    fclose(f);
+    buf.push_back(0);                           // the reference appends a NUL (PTX is text)
+    int rc = d->load(module, buf.data());
+    if (rc) return drv_fail(d, rc, "cuModuleLoadData");
+    return HX_OK;
+}
+HX_API int hx_image_launch(void* module, const char* entry, unsigned gx, unsigned gy, unsigned gz,
+                           unsigned bx, unsigned by, unsigned bz, void** args) {
+    HX_CHECK_ARG(module && entry && args);
+    Drv* d = drv();
+    if (!d) return hx_fail(HX_ERR_CUDA, "libcuda.so.1 is not available");
+    void* fn = nullptr;
+    int rc = d->getf(&fn, module, entry);
+    if (rc) return drv_fail(d, rc, "cuModuleGetFunction");
+    rc = d->launch(fn, gx, gy, gz, bx, by, bz, 0, nullptr, args, nullptr);
+    if (rc) return drv_fail(d, rc, "cuLaunchKernel");
+    rc = d->sync();
+    if (rc) return drv_fail(d, rc, "cuCtxSynchronize");
+    g_hx_launches += 1;
+    return HX_OK;
+}
+HX_API int hx_image_close(void* module) {
+    Drv* d = drv();
+    if (d && module) d->unload(module);
+    return HX_OK;
+}

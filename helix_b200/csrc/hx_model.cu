@@ -69,6 +69,8 @@ struct hx_model {
     cudaGraphExec_t g_decode = nullptr, g_prefill = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     bool pdl = true;
+    bool profile = false;
+    std::vector<cudaEvent_t> prof_ev; std::vector<int> prof_cat; size_t prof_n = 0;
     hx_step_stats stats{};
     std::vector<void*> allocs;
     uint64_t decode_bytes = 0, committed_bytes = 0;
@@ -296,16 +298,33 @@ HxLinear lin(const Fused& f, const float* x, float* y, int epi) {
     return a;
 }
 
+// Per-kernel timing (hx_model_set_profile): an event before and after every launch, eager stream order.
+enum { CAT_GEMV = 0, CAT_ATTN = 1, CAT_OTHER = 2 };
+struct ProfScope {
+    hx_model* m; int cat; bool on;
+    ProfScope(hx_model* mm, int c, bool active) : m(mm), cat(c), on(active) {
+        if (!on) return;
+        if (m->prof_n + 2 > m->prof_ev.size()) {
+            for (int i = 0; i < 2; i++) { cudaEvent_t e; cudaEventCreate(&e); m->prof_ev.push_back(e); }
+            m->prof_cat.push_back(cat);
+        }
+        m->prof_cat[m->prof_n / 2] = cat;
+        cudaEventRecord(m->prof_ev[m->prof_n], m->st);
+    }
+    ~ProfScope() { if (on) { cudaEventRecord(m->prof_ev[m->prof_n + 1], m->st); m->prof_n += 2; } }
+};
+
 // Enqueue one token step on m->st.  from_prompt: the input token is d_prompt[*pos] and no logits are
 // computed (prefill); otherwise the input token is *d_tok and the head + arg-max run.
-int enqueue_step(hx_model* m, bool from_prompt, bool with_head) {
+int enqueue_step(hx_model* m, bool from_prompt, bool with_head, bool prof = false) {
     const hx_config& c = m->cfg;
     const int DM = c.d_model, DH = c.head_dim, cap = m->kv_cap;
-    const bool pdl = m->pdl;
+    const bool pdl = m->pdl && !prof;
     int rc;
     {
         // the first kernel of a step follows the last kernel of the previous step
         const int* tok = from_prompt ? m->d_prompt : m->d_tok;
+        ProfScope ps(m, CAT_OTHER, prof);
         rc = hx_launch_embed(m->emb, nullptr, tok, m->d_pos, from_prompt ? 1 : 0, m->x, DM, m->st, pdl);
         if (rc) return rc;
     }
@@ -313,7 +332,7 @@ int enqueue_step(hx_model* m, bool from_prompt, bool with_head) {
         Layer& ly = m->layers[L];
         HxLinear a = lin(ly.qkv, m->x, m->qkv, HX_EPI_STORE);
         a.norm = HX_NORM_RMS; a.norm_g = ly.in_g; a.eps = c.norm_eps;
-        if ((rc = hx_launch_linear(a, m->st, pdl))) return rc;
+        { ProfScope ps(m, CAT_GEMV, prof); if ((rc = hx_launch_linear(a, m->st, pdl))) return rc; }
         HxAttn at = {};
         at.qkv = m->qkv; at.q_rot = m->q_rot; at.qn_g = ly.qn_g; at.kn_g = ly.kn_g;
         at.cosT = m->cosT; at.sinT = m->sinT;
@@ -321,22 +340,22 @@ int enqueue_step(hx_model* m, bool from_prompt, bool with_head) {
         at.pos = m->d_pos; at.NH = c.n_heads; at.NKV = c.n_kv_heads; at.DH = DH; at.cap = cap;
         at.eps = c.norm_eps; at.scale = 1.0f / sqrtf((float)DH); at.nsplit = m->nsplit;
         at.part_m = m->part_m; at.part_l = m->part_l; at.part_acc = m->part_acc; at.counters = m->attn_cnt; at.ctx = m->ctx;
-        if ((rc = hx_launch_qk_prep(at, m->st, pdl))) return rc;
-        if ((rc = hx_launch_attn(at, m->st, pdl))) return rc;
+        { ProfScope ps(m, CAT_OTHER, prof); if ((rc = hx_launch_qk_prep(at, m->st, pdl))) return rc; }
+        { ProfScope ps(m, CAT_ATTN, prof); if ((rc = hx_launch_attn(at, m->st, pdl))) return rc; }
         HxLinear o = lin(ly.o, m->ctx, m->x, HX_EPI_RESID); o.resid = m->x;
-        if ((rc = hx_launch_linear(o, m->st, pdl))) return rc;
+        { ProfScope ps(m, CAT_GEMV, prof); if ((rc = hx_launch_linear(o, m->st, pdl))) return rc; }
         HxLinear gu = lin(ly.gu, m->x, m->h, HX_EPI_SWIGLU);
         gu.norm = HX_NORM_RMS; gu.norm_g = ly.post_g; gu.eps = c.norm_eps;
-        if ((rc = hx_launch_linear(gu, m->st, pdl))) return rc;
+        { ProfScope ps(m, CAT_GEMV, prof); if ((rc = hx_launch_linear(gu, m->st, pdl))) return rc; }
         HxLinear dn = lin(ly.down, m->h, m->x, HX_EPI_RESID); dn.resid = m->x;
-        if ((rc = hx_launch_linear(dn, m->st, pdl))) return rc;
+        { ProfScope ps(m, CAT_GEMV, prof); if ((rc = hx_launch_linear(dn, m->st, pdl))) return rc; }
     }
     if (with_head) {
         HxLinear hd = lin(m->head, m->x, m->logits, HX_EPI_ARGMAX);
         hd.norm = HX_NORM_RMS; hd.norm_g = m->final_g; hd.eps = c.norm_eps;
         hd.part_val = m->am_val; hd.part_idx = m->am_idx; hd.counter = m->am_cnt; hd.next_tok = m->d_tok; hd.pos_inc = m->d_pos;
         hd.hist = m->d_hist;
-        if ((rc = hx_launch_linear(hd, m->st, pdl))) return rc;
+        { ProfScope ps(m, CAT_GEMV, prof); if ((rc = hx_launch_linear(hd, m->st, pdl))) return rc; }
     } else {
         k_advance<<<1, 32, 0, m->st>>>(m->d_pos);
         HX_COUNT_LAUNCH(1);
@@ -397,6 +416,7 @@ HX_API int hx_model_free(hx_model* m) {
     if (m->ev0) cudaEventDestroy(m->ev0);
     if (m->ev1) cudaEventDestroy(m->ev1);
     for (void* p : m->allocs) cudaFree(p);
+    for (cudaEvent_t e : m->prof_ev) cudaEventDestroy(e);
     if (m->st) cudaStreamDestroy(m->st);
     delete m;
     return HX_OK;
@@ -489,7 +509,7 @@ HX_API int hx_model_weight_bytes(const hx_model* m, uint64_t* decode_layout, uin
 }
 HX_API int hx_model_reset(hx_model* m) { HX_CHECK_ARG(m); m->kv_len = 0; return HX_OK; }
 HX_API int hx_model_last_stats(const hx_model* m, hx_step_stats* st) { HX_CHECK_ARG(m && st); *st = m->stats; return HX_OK; }
-HX_API int hx_model_set_profile(hx_model* m, int on) { HX_CHECK_ARG(m); (void)on; return HX_OK; }
+HX_API int hx_model_set_profile(hx_model* m, int on) { HX_CHECK_ARG(m); m->profile = on != 0; return HX_OK; }
 
 // ---- HXGW v3 image ---------------------------------------------------------------------------------
 namespace {
@@ -641,9 +661,24 @@ HX_API int hx_decode_loop(hx_model* m, const int32_t* ids, int pos0, int n_steps
     if (pos0 < 0 || pos0 + n_steps > m->kv_cap) return hx_fail(HX_ERR_STATE, "steps %d..%d outside the KV capacity %d", pos0, pos0 + n_steps, m->kv_cap);
     int rc = set_pos_tok(m, pos0, ids); if (rc) return rc;
     HX_CUDA(cudaEventRecord(m->ev0, m->st));
-    for (int s = 0; s < n_steps; s++) HX_CUDA(cudaGraphLaunch(m->g_decode, m->st));
+    if (m->profile) {
+        // eager launches with an event pair around each kernel: per-kernel device time by category
+        m->stats.ms_gemv = m->stats.ms_attn = m->stats.ms_other = 0.0f;
+        for (int s = 0; s < n_steps; s++) {
+            m->prof_n = 0;
+            if ((rc = enqueue_step(m, false, true, true))) return rc;
+            HX_CUDA(cudaStreamSynchronize(m->st));
+            for (size_t i = 0; i < m->prof_n; i += 2) {
+                float t = 0.0f; cudaEventElapsedTime(&t, m->prof_ev[i], m->prof_ev[i + 1]);
+                const int cat = m->prof_cat[i / 2];
+                (cat == CAT_GEMV ? m->stats.ms_gemv : cat == CAT_ATTN ? m->stats.ms_attn : m->stats.ms_other) += t;
+            }
+        }
+    } else {
+        for (int s = 0; s < n_steps; s++) HX_CUDA(cudaGraphLaunch(m->g_decode, m->st));
+        HX_COUNT_LAUNCH((unsigned long long)n_steps * kernels_per_step(m, true));
+    }
     HX_CUDA(cudaEventRecord(m->ev1, m->st));
-    HX_COUNT_LAUNCH((unsigned long long)n_steps * kernels_per_step(m, true));
     if (out_ids) HX_CUDA(cudaMemcpyAsync(out_ids, m->d_hist + pos0 + 1, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, m->st));
     HX_CUDA(cudaStreamSynchronize(m->st));
     float t = 0.0f; HX_CUDA(cudaEventElapsedTime(&t, m->ev0, m->ev1));

@@ -101,6 +101,9 @@ _SIGS = {
     "hx_model_set_profile": (C.c_int, [C.c_void_p, C.c_int]),
     "hx_decode_loop": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float)]),
     "hx_model_fill_kv": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64]),
+    "hx_image_open": (C.c_int, [C.POINTER(C.c_void_p), C.c_char_p]),
+    "hx_image_launch": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_void_p]),
+    "hx_image_close": (C.c_int, [C.c_void_p]),
     "hx_tp_unique_id": (C.c_int, [C.c_void_p]),
     "hx_tp_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
     "hx_tp_shutdown": (C.c_int, []),
@@ -198,6 +201,29 @@ def roundtrip_host(w, x):
     return y
 
 
+class KernelImage:
+    """The kernel-entry image loaded and launched the way the reference's C launchers do it."""
+
+    def __init__(self, path=None):
+        self.mod = C.c_void_p()
+        check(lib().hx_image_open(C.byref(self.mod), (path or fatbin_path()).encode()))
+
+    def launch(self, entry, grid, block, args):
+        """args: DeviceBuffer -> its pointer, int -> 32-bit scalar (the reference's kernel ABI has only those)."""
+        grid = tuple(grid) + (1,) * (3 - len(grid))
+        block = tuple(block) + (1,) * (3 - len(block))
+        holders = []
+        for a in args:
+            holders.append(C.c_void_p(a.ptr.value) if isinstance(a, DeviceBuffer) else C.c_int32(int(a)))
+        arr = (C.c_void_p * len(holders))(*[C.cast(C.pointer(h), C.c_void_p) for h in holders])
+        check(lib().hx_image_launch(self.mod, entry.encode(), *grid, *block, arr))
+
+    def close(self):
+        if self.mod:
+            lib().hx_image_close(self.mod)
+            self.mod = C.c_void_p()
+
+
 class Model:
     """hx_model: HBM-resident NVFP4 weights + KV cache + the captured decode step."""
 
@@ -264,6 +290,14 @@ class Model:
         ms = C.c_float()
         check(lib().hx_decode_loop(self.h, ids.ctypes.data, pos0, n_steps, out.ctypes.data, C.byref(ms)))
         return out, ms.value
+
+    def set_profile(self, on):
+        check(lib().hx_model_set_profile(self.h, 1 if on else 0))
+
+    def last_stats(self):
+        st = HxStepStats()
+        check(lib().hx_model_last_stats(self.h, C.byref(st)))
+        return {k: getattr(st, k) for k, _ in st._fields_}
 
     def fill_kv(self, T, seed=0):
         check(lib().hx_model_fill_kv(self.h, T, seed))

@@ -203,6 +203,22 @@ int hx_decode_loop(hx_model* m, const int32_t* ids, int pos0, int n_steps, int32
  * context without running a long prefill). */
 int hx_model_fill_kv(hx_model* m, int T, uint64_t seed);
 
+/* ---------------------------------------------------------------- kernel-entry image ---------- */
+/* helix_b200_kernels.fatbin exports, for sm_100a, the entry names and parameter lists of the kernels
+ * the reference's worker loads from its emitted PTX (dequant_gemv_warp, dequant_gemv_blockred,
+ * nvfp4_dequant_tiled, fused_decode_attn, gpu_rmsnorm_fwd_eps, ... 21 entries), so the file can be
+ * given to the reference's launchers in place of that PTX.  These three calls are the launcher
+ * side: they do what cuda_launch.c:1058-1088 and gpt2_infer.c:373-375 do (cuModuleLoadData,
+ * cuModuleGetFunction, cuLaunchKernel with the caller's grid and block, no dynamic shared memory,
+ * the NULL stream, then a synchronize).  args is the usual array of pointers to the arguments. */
+int hx_image_open(void** module, const char* path);
+int hx_image_launch(void* module, const char* entry, unsigned gx, unsigned gy, unsigned gz,
+                    unsigned bx, unsigned by, unsigned bz, void** args);
+int hx_image_close(void* module);
+
+/* Kernels launched by this library since it was loaded (all streams). */
+unsigned long long hx_launch_count(void);
+
 /* ---------------------------------------------------------------- tensor parallel ------------- */
 /* NCCL is loaded at run time (libnccl.so.2).  id is NCCL's 128-byte unique id, created on rank 0
  * with hx_tp_unique_id and distributed by the caller (any out-of-band channel). */

@@ -511,18 +511,13 @@ ORC_API int orc_v3_validate(const uint8_t* file, size_t len) {
 
 ORC_API void orc_model_close(OrcModel* m);
 
-/* Open an HXGW v3 file.  use_file_eps = 0 uses 1e-5, which is what the reference computes whatever
- * the header says (gpt2_infer.c:661-664); 1 uses the header's rms_norm_eps. */
-ORC_API OrcModel* orc_model_open(const char* path, int kv_cap, int use_file_eps) {
-    int fd = open(path, O_RDONLY);
-    if (fd < 0) return NULL;
-    struct stat st; if (fstat(fd, &st)) { close(fd); return NULL; }
-    void* mp = mmap(NULL, (size_t)st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
-    if (mp == MAP_FAILED) { close(fd); return NULL; }
-    if (orc_v3_validate((const uint8_t*)mp, (size_t)st.st_size)) { munmap(mp, (size_t)st.st_size); close(fd); return NULL; }
+/* Build the model over an HXGW v3 image already in memory (fd < 0: the caller keeps the bytes alive
+ * and owns them).  use_file_eps = 0 uses 1e-5, which is what the reference computes whatever the
+ * header says (gpt2_infer.c:661-664); 1 uses the header's rms_norm_eps. */
+static OrcModel* model_from_image(const uint8_t* hb, size_t len, int fd, int kv_cap, int use_file_eps) {
+    if (orc_v3_validate(hb, len)) return NULL;
     OrcModel* m = (OrcModel*)calloc(1, sizeof(OrcModel));
-    const uint8_t* hb = (const uint8_t*)mp;
-    m->map = hb; m->maplen = (size_t)st.st_size; m->fd = fd;
+    m->map = hb; m->maplen = len; m->fd = fd;
     m->NL = (int)rd32(hb + 8); m->DM = (int)rd32(hb + 12); m->NH = (int)rd32(hb + 16); m->NV = (int)rd32(hb + 20);
     m->NC = (int)rd32(hb + 24); m->DFF = (int)rd32(hb + 28); m->NKV = (int)rd32(hb + 44);
     m->theta = rdf32(hb + 48); m->eps_file = rdf32(hb + 52);
@@ -531,7 +526,7 @@ ORC_API OrcModel* orc_model_open(const char* path, int kv_cap, int use_file_eps)
     m->attn_scale = 1.0f / sqrtf((float)m->DH);
     m->eps_used = use_file_eps ? m->eps_file : 1e-5f;
     m->desc = (const OrcDesc*)(hb + 64);
-    if (m->ntens != m->NL * T_PER_LAYER + 3 || m->NKV <= 0 || m->NH % m->NKV) { orc_model_close(m); return NULL; }
+    if (m->ntens != m->NL * T_PER_LAYER + 3 || m->NKV <= 0 || m->NH % m->NKV) { free(m); return NULL; }
     m->kv_cap = kv_cap; m->kv_len = 0;
     size_t kvn = (size_t)m->NL * m->NKV * kv_cap * m->DH;
     m->kc = (float*)calloc(kvn, 4); m->vc = (float*)calloc(kvn, 4);
@@ -547,13 +542,28 @@ ORC_API OrcModel* orc_model_open(const char* path, int kv_cap, int use_file_eps)
     return m;
 }
 
+ORC_API OrcModel* orc_model_open_image(const uint8_t* image, size_t len, int kv_cap, int use_file_eps) {
+    return model_from_image(image, len, -1, kv_cap, use_file_eps);
+}
+
+/* Open an HXGW v3 file (mapped read-only, as load_gpt2_weights does, gpt2_infer.c:564-603). */
+ORC_API OrcModel* orc_model_open(const char* path, int kv_cap, int use_file_eps) {
+    int fd = open(path, O_RDONLY);
+    if (fd < 0) return NULL;
+    struct stat st; if (fstat(fd, &st)) { close(fd); return NULL; }
+    void* mp = mmap(NULL, (size_t)st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
+    if (mp == MAP_FAILED) { close(fd); return NULL; }
+    OrcModel* m = model_from_image((const uint8_t*)mp, (size_t)st.st_size, fd, kv_cap, use_file_eps);
+    if (!m) { munmap(mp, (size_t)st.st_size); close(fd); }
+    return m;
+}
+
 ORC_API void orc_model_close(OrcModel* m) {
     if (!m) return;
     free(m->kc); free(m->vc); free(m->cosT); free(m->sinT);
     free(m->x); free(m->xn); free(m->q); free(m->k); free(m->v); free(m->ctx); free(m->pj);
     free(m->g); free(m->u); free(m->m); free(m->mo); free(m->sc); free(m->pr);
-    if (m->map) munmap((void*)m->map, m->maplen);
-    if (m->fd >= 0) close(m->fd);
+    if (m->map && m->fd >= 0) { munmap((void*)m->map, m->maplen); close(m->fd); }
     free(m);
 }
 

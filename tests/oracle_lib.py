@@ -68,6 +68,9 @@ def oracle():
     lib.orc_v3_validate.argtypes = [C.c_void_p, C.c_size_t]
     lib.orc_model_open.restype = C.c_void_p
     lib.orc_model_open.argtypes = [C.c_char_p, C.c_int, C.c_int]
+    lib.orc_model_open_image.restype = C.c_void_p
+    lib.orc_model_open_image.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_int]
+    lib.orc_num_threads.restype = C.c_int
     lib.orc_model_close.argtypes = [C.c_void_p]
     lib.orc_model_reset.argtypes = [C.c_void_p]
     lib.orc_model_dims.argtypes = [C.c_void_p, i32p]
@@ -242,11 +245,16 @@ def write_qwen3_config(path, cfg):
 class OracleModel:
     """The fp32 CPU restatement of the worker's decode/prefill over an HXGW v3 file."""
 
-    def __init__(self, path, kv_cap=256, use_file_eps=False):
+    def __init__(self, path=None, kv_cap=256, use_file_eps=False, image=None):
         self.lib = oracle()
-        self.h = self.lib.orc_model_open(path.encode(), kv_cap, 1 if use_file_eps else 0)
+        if image is not None:
+            self._image = np.ascontiguousarray(image, np.uint8)      # kept alive: the oracle reads it in place
+            self.h = self.lib.orc_model_open_image(self._image.ctypes.data, self._image.nbytes, kv_cap,
+                                                   1 if use_file_eps else 0)
+        else:
+            self.h = self.lib.orc_model_open(path.encode(), kv_cap, 1 if use_file_eps else 0)
         if not self.h:
-            raise RuntimeError(f"oracle could not open {path}")
+            raise RuntimeError(f"oracle could not open {path or 'the image'}")
         d = np.zeros(9, np.int32)
         self.lib.orc_model_dims(self.h, d)
         self.NL, self.DM, self.NH, self.NKV, self.DH, self.DFF, self.NV, self.QD, self.KVD = (int(v) for v in d)
