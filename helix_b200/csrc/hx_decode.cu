@@ -495,9 +495,13 @@ int hx_launch_attn(const HxAttn& a, cudaStream_t st, bool pdl) {
     switch (grp) {
         case 1: e = launch_ex(k_attn<1>, grid, block, 0, st, pdl, a); break;
         case 2: e = launch_ex(k_attn<2>, grid, block, 0, st, pdl, a); break;
+        case 3: e = launch_ex(k_attn<3>, grid, block, 0, st, pdl, a); break;
         case 4: e = launch_ex(k_attn<4>, grid, block, 0, st, pdl, a); break;
+        case 5: e = launch_ex(k_attn<5>, grid, block, 0, st, pdl, a); break;
+        case 6: e = launch_ex(k_attn<6>, grid, block, 0, st, pdl, a); break;
+        case 7: e = launch_ex(k_attn<7>, grid, block, 0, st, pdl, a); break;
         case 8: e = launch_ex(k_attn<8>, grid, block, 0, st, pdl, a); break;
-        default: return hx_fail(HX_ERR_ARG, "unsupported GQA group size %d (1, 2, 4 or 8)", grp);
+        default: return hx_fail(HX_ERR_ARG, "unsupported GQA group size %d (1..8)", grp);
     }
     HX_CUDA(e);
     return HX_OK;
