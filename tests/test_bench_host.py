@@ -40,7 +40,7 @@ def test_two_rank_reduction_over_gloo(tmp_path):
         "m = bench.all_max(d, 10.0 + r); s = bench.all_sum(d, 1.0 + r)\n"
         "assert m == 11.0 and s == 3.0, (m, s)\n"
         "d.barrier(); d.destroy_process_group()\n"
-        "print('rank', r, 'ok')\n")
+        "sys.stdout.write('rank-%d-ok\\n' % r); sys.stdout.flush()\n")
     import socket
     with socket.socket() as sk:
         sk.bind(("127.0.0.1", 0))
@@ -49,4 +49,4 @@ def test_two_rank_reduction_over_gloo(tmp_path):
                         "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
                        capture_output=True, text=True, timeout=300)
     assert p.returncode == 0, p.stdout + p.stderr
-    assert "rank 0 ok" in p.stdout and "rank 1 ok" in p.stdout
+    assert "rank-0-ok" in p.stdout and "rank-1-ok" in p.stdout
