@@ -12,6 +12,7 @@
 // HX_LOAD_KEEP_COMMITTED the committed 7-per-word layout (words, micro bytes, ts) stays resident as
 // well, so that the HXGW v3 image and its SHA-256 can be reproduced from the GPU.
 #include "hx_kernels.cuh"
+#include "hx_persist.cuh"
 #include <fcntl.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -38,6 +39,7 @@ struct Fused {               // rows of one or more tensors in the dense decode 
     int N = 0, K = 0, Kd = 0;
     uint8_t* codes = nullptr; uint8_t* scales = nullptr;
     float ts[3] = {1.f, 1.f, 1.f}; int bound0 = 0, bound1 = 0;
+    uint8_t* t16 = nullptr; int KG = 0, ntiles = 0;      // tile layout for the persistent kernel
     size_t bytes() const { return (size_t)N * (Kd / 2 + Kd / 16); }
 };
 struct Layer {
@@ -69,6 +71,11 @@ struct hx_model {
     cudaGraphExec_t g_decode = nullptr, g_prefill = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     bool pdl = true;
+    bool persist = true;                 // one cooperative kernel per token instead of the launch graph
+    HxPhase *ph_decode = nullptr, *ph_prefill = nullptr; int nph_decode = 0, nph_prefill = 0;
+    unsigned long long* d_bar = nullptr; unsigned long long bar_count = 0; int* d_err = nullptr;
+    int grid_persist = 0, dig_bytes = 0, nsplit_persist = 1;
+    unsigned long long* d_dbg = nullptr;
     bool profile = false;
     std::vector<cudaEvent_t> prof_ev; std::vector<int> prof_cat; size_t prof_n = 0;
     hx_step_stats stats{};
@@ -94,6 +101,9 @@ int alloc_fused(hx_model* m, Fused& f, int N, int K) {
     int rc = dalloc(m, &f.codes, (size_t)N * (f.Kd / 2)); if (rc) return rc;
     rc = dalloc(m, &f.scales, (size_t)N * (f.Kd / 16)); if (rc) return rc;
     m->decode_bytes += f.bytes();
+    f.KG = hx_t16_kgroups(K); f.ntiles = hx_t16_tiles(N);
+    rc = dalloc(m, &f.t16, hx_t16_bytes(N, K)); if (rc) return rc;
+    HX_CUDA(cudaMemsetAsync(f.t16, 0, hx_t16_bytes(N, K), m->st));
     return HX_OK;
 }
 
@@ -153,6 +163,9 @@ int fetch_dense(hx_model* m, Source& s, int idx, size_t n, float** out, bool is_
 
 void put_rows(hx_model* m, const Committed& c, Fused& f, int row_mul, int row_off) {
     hx_repack_rows(c.words, c.micro, c.rows, c.K, c.Kpad, f.codes, f.scales, row_mul, row_off, m->st);
+    // tile layout: plain offset, or gate/up interleaved tile by tile (16 rows of gate, 16 rows of up)
+    if (row_mul == 1) hx_repack_t16(c.words, c.micro, c.rows, c.K, c.Kpad, f.t16, f.KG, 1, 1, row_off, m->st);
+    else hx_repack_t16(c.words, c.micro, c.rows, c.K, c.Kpad, f.t16, f.KG, 16, row_mul, row_off, m->st);
 }
 
 int build(hx_model* m, Source& s) {
@@ -200,6 +213,11 @@ int build(hx_model* m, Source& s) {
             if ((rc = alloc_fused(m, ly.qkv, QD + 2 * KVD, DM))) break;
             if ((rc = alloc_fused(m, ly.o, DM, QD))) break;
             if ((rc = alloc_fused(m, ly.gu, 2 * DFF, DM))) break;
+            if (DFF % 16) {   // tile-interleaved pairs need whole tiles for gate and for up
+                ly.gu.ntiles = 2 * hx_t16_tiles(DFF);
+                if ((rc = dalloc(m, &ly.gu.t16, (size_t)ly.gu.ntiles * ly.gu.KG * HX_T16_CELL))) break;
+                HX_CUDA(cudaMemsetAsync(ly.gu.t16, 0, (size_t)ly.gu.ntiles * ly.gu.KG * HX_T16_CELL, m->st));
+            }
             if ((rc = alloc_fused(m, ly.down, DM, DFF))) break;
             if ((rc = fetch_packed(m, s, b + T_Q, QD, DM, ly.c[T_Q], keep))) break;
             put_rows(m, ly.c[T_Q], ly.qkv, 1, 0); ly.qkv.ts[0] = ly.c[T_Q].ts;
@@ -381,10 +399,118 @@ int capture(hx_model* m, bool from_prompt, bool with_head, cudaGraphExec_t* out)
 
 int kernels_per_step(const hx_model* m, bool with_head) { (void)with_head; return 1 + 6 * m->cfg.n_layers + 1; }
 
+// Phase table of one token for the persistent kernel: per layer qkv, attention, o_proj, gate+up, down;
+// then (with_head) the lm_head.  from_prompt: layer 0 reads the token from the prompt array.
+int build_phases(hx_model* m, bool from_prompt, bool with_head, HxPhase** out, int* nout) {
+    const hx_config& c = m->cfg;
+    const int DH = c.head_dim, cap = m->kv_cap;
+    std::vector<HxPhase> v;
+    auto linear = [&](const Fused& f, const float* x, float* y, int epi, int N) {
+        HxPhase p = {};
+        p.type = HX_PH_LINEAR; p.w = f.t16; p.ntiles = f.ntiles; p.KG = f.KG; p.unit = (epi == HX_EPI_SWIGLU) ? 2 : 1;
+        p.N = N; p.x = x; p.K = f.K; p.norm = HX_NORM_NONE; p.epi = epi; p.y = y;
+        p.ts[0] = f.ts[0]; p.ts[1] = f.ts[1]; p.ts[2] = f.ts[2]; p.bound0 = f.bound0; p.bound1 = f.bound1;
+        return p;
+    };
+    int maxK = 0;
+    for (int L = 0; L < c.n_layers; L++) {
+        Layer& ly = m->layers[L];
+        HxPhase a = linear(ly.qkv, m->x, m->qkv, HX_EPI_STORE, ly.qkv.N);
+        a.norm = HX_NORM_RMS; a.g = ly.in_g; a.eps = c.norm_eps;
+        if (L == 0) { a.x = m->emb; a.tok = from_prompt ? m->d_prompt : m->d_tok; a.x_out = m->x; }
+        v.push_back(a);
+        HxPhase at = {};
+        at.type = HX_PH_ATTN; at.qkv = m->qkv; at.qn_g = ly.qn_g; at.kn_g = ly.kn_g; at.cosT = m->cosT; at.sinT = m->sinT;
+        at.kc = m->kc + (size_t)L * c.n_kv_heads * cap * DH; at.vc = m->vc + (size_t)L * c.n_kv_heads * cap * DH;
+        at.ctx = m->ctx; at.NH = c.n_heads; at.NKV = c.n_kv_heads; at.DH = DH; at.cap = cap;
+        at.nsplit = m->nsplit_persist; at.scale = 1.0f / sqrtf((float)DH); at.eps = c.norm_eps;
+        v.push_back(at);
+        HxPhase o = linear(ly.o, m->ctx, m->x, HX_EPI_RESID, ly.o.N);
+        v.push_back(o);
+        HxPhase gu = linear(ly.gu, m->x, m->h, HX_EPI_SWIGLU, c.d_ff);
+        gu.norm = HX_NORM_RMS; gu.g = ly.post_g; gu.eps = c.norm_eps;
+        v.push_back(gu);
+        HxPhase dn = linear(ly.down, m->h, m->x, HX_EPI_RESID, ly.down.N);
+        v.push_back(dn);
+        if (ly.down.K > maxK) maxK = ly.down.K;
+        if (ly.o.K > maxK) maxK = ly.o.K;
+        if (ly.qkv.K > maxK) maxK = ly.qkv.K;
+    }
+    if (with_head) {
+        HxPhase hd = linear(m->head, m->x, m->logits, HX_EPI_ARGMAX, m->head.N);
+        hd.norm = HX_NORM_RMS; hd.g = m->final_g; hd.eps = c.norm_eps;
+        v.push_back(hd);
+    }
+    const int dig = 3 * hx_t16_kgroups(maxK) * HX_T16_KG * 2;
+    if (dig > m->dig_bytes) m->dig_bytes = dig;
+    HxPhase* d = nullptr;
+    int rc = dalloc(m, &d, v.size()); if (rc) return rc;
+    HX_CUDA(cudaMemcpy(d, v.data(), v.size() * sizeof(HxPhase), cudaMemcpyHostToDevice));
+    *out = d; *nout = (int)v.size();
+    return HX_OK;
+}
+
+int init_persist(hx_model* m) {
+    int dev = 0, sms = 0, coop = 0;
+    HX_CUDA(cudaGetDevice(&dev));
+    HX_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    HX_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+    if (!coop) return hx_fail(HX_ERR_CUDA, "device does not support cooperative launches");
+    m->grid_persist = sms;
+    m->nsplit_persist = sms / m->cfg.n_kv_heads; if (m->nsplit_persist < 1) m->nsplit_persist = 1;
+    if (m->nsplit_persist > m->nsplit) m->nsplit_persist = m->nsplit;      // scratch is sized for nsplit
+    if (256 % m->cfg.head_dim) return hx_fail(HX_ERR_ARG, "persistent decode needs head_dim dividing 256");
+    int rc = build_phases(m, false, true, &m->ph_decode, &m->nph_decode); if (rc) return rc;
+    rc = build_phases(m, true, false, &m->ph_prefill, &m->nph_prefill); if (rc) return rc;
+    if ((rc = dalloc(m, &m->d_bar, (size_t)2))) return rc;
+    if ((rc = dalloc(m, &m->d_err, (size_t)4))) return rc;
+    HX_CUDA(cudaMemset(m->d_bar, 0, 16));
+    HX_CUDA(cudaMemset(m->d_err, 0, 16));
+    m->bar_count = 0;
+    if (getenv("HX_PERSIST_DBG")) { if ((rc = dalloc(m, &m->d_dbg, (size_t)16 * (m->nph_decode + 4)))) return rc; }
+    if (hx_persist_smem(m->dig_bytes) > 227 * 1024)
+        return hx_fail(HX_ERR_ARG, "persistent decode: K too large for shared memory (%zu bytes)", hx_persist_smem(m->dig_bytes));
+    return HX_OK;
+}
+
+// One token through the persistent kernel.
+int persist_step(hx_model* m, bool from_prompt, bool with_head) {
+    HxPersist P = {};
+    P.phases = from_prompt ? m->ph_prefill : m->ph_decode;
+    P.nphases = from_prompt ? m->nph_prefill : m->nph_decode;
+    (void)with_head;
+    P.pos = m->d_pos; P.bar = m->d_bar; P.bar_base = m->bar_count; P.err = m->d_err;
+    P.part_m = m->part_m; P.part_l = m->part_l; P.part_acc = m->part_acc; P.attn_cnt = m->attn_cnt;
+    P.am_val = m->am_val; P.am_idx = m->am_idx; P.am_cnt = m->am_cnt; P.next_tok = m->d_tok; P.pos_inc = m->d_pos;
+    P.hist = m->d_hist; P.logits = m->logits; P.dig_bytes = m->dig_bytes;
+    P.tok_by_pos = from_prompt ? 1 : 0; P.advance_pos = from_prompt ? 1 : 0;
+    P.dbg = m->d_dbg;
+    m->bar_count += (unsigned long long)m->grid_persist * (unsigned long long)(P.nphases - 1);
+    return hx_persist_launch(P, m->grid_persist, m->st);
+}
+
+// After a synchronize: did any bounded wait of the persistent kernel run out?
+int persist_check(hx_model* m) {
+    if (!m->persist) return HX_OK;
+    int e = 0;
+    HX_CUDA(cudaMemcpy(&e, m->d_err, 4, cudaMemcpyDeviceToHost));
+    if (e) {
+        cudaMemset(m->d_err, 0, 4); cudaMemset(m->d_bar, 0, 8); m->bar_count = 0;
+        return hx_fail(HX_ERR_TIMEOUT, "a bounded wait in the persistent decode kernel ran out");
+    }
+    return HX_OK;
+}
+
 int finish_init(hx_model* m) {
     int rc = alloc_state(m); if (rc) return rc;
     const char* np = getenv("HX_NO_PDL");
     m->pdl = !(np && *np == '1');
+    const char* dm = getenv("HX_DECODE");
+    m->persist = !(dm && strcmp(dm, "graph") == 0);
+    if (m->persist) {
+        rc = init_persist(m);
+        if (rc) return rc;
+    }
     rc = capture(m, false, true, &m->g_decode);
     if (rc && m->pdl) {     // programmatic edges not capturable on this driver: plain stream order
         m->pdl = false;
@@ -392,6 +518,20 @@ int finish_init(hx_model* m) {
     }
     if (rc) return rc;
     return capture(m, true, false, &m->g_prefill);
+}
+
+// One decode / prefill token on the model's stream, whichever engine is selected.
+int step_decode(hx_model* m) {
+    if (m->persist) return persist_step(m, false, true);
+    HX_CUDA(cudaGraphLaunch(m->g_decode, m->st));
+    HX_COUNT_LAUNCH(kernels_per_step(m, true));
+    return HX_OK;
+}
+int step_prefill(hx_model* m) {
+    if (m->persist) return persist_step(m, true, false);
+    HX_CUDA(cudaGraphLaunch(m->g_prefill, m->st));
+    HX_COUNT_LAUNCH(kernels_per_step(m, false));
+    return HX_OK;
 }
 
 int check_cfg(const hx_config& c, int kv_cap, int batch, int tp_rank, int tp_size) {
@@ -509,6 +649,15 @@ HX_API int hx_model_weight_bytes(const hx_model* m, uint64_t* decode_layout, uin
 }
 HX_API int hx_model_reset(hx_model* m) { HX_CHECK_ARG(m); m->kv_len = 0; return HX_OK; }
 HX_API int hx_model_last_stats(const hx_model* m, hx_step_stats* st) { HX_CHECK_ARG(m && st); *st = m->stats; return HX_OK; }
+// Debug: per-phase time stamps of CTA 0 from the last persistent launch (4 per phase, nanoseconds).
+HX_API int hx_model_phase_stamps(hx_model* m, unsigned long long* out, int max_phases, int* nphases) {
+    HX_CHECK_ARG(m && out && nphases);
+    if (!m->d_dbg) return hx_fail(HX_ERR_STATE, "set HX_PERSIST_DBG=1 before creating the model");
+    const int n = m->nph_decode < max_phases ? m->nph_decode : max_phases;
+    HX_CUDA(cudaMemcpy(out, m->d_dbg, (size_t)n * 16 * 8, cudaMemcpyDeviceToHost));
+    *nphases = n;
+    return HX_OK;
+}
 HX_API int hx_model_set_profile(hx_model* m, int on) { HX_CHECK_ARG(m); m->profile = on != 0; return HX_OK; }
 
 // ---- HXGW v3 image ---------------------------------------------------------------------------------
@@ -623,11 +772,11 @@ HX_API int hx_decode_step(hx_model* m, const int32_t* ids, int pos, int32_t* nex
     if (pos < 0 || pos >= m->kv_cap) return hx_fail(HX_ERR_STATE, "position %d outside the KV capacity %d", pos, m->kv_cap);
     if (ids[0] < 0 || ids[0] >= m->cfg.vocab) return hx_fail(HX_ERR_ARG, "token %d outside the vocabulary", ids[0]);
     int rc = set_pos_tok(m, pos, ids); if (rc) return rc;
-    HX_CUDA(cudaGraphLaunch(m->g_decode, m->st));
-    HX_COUNT_LAUNCH(kernels_per_step(m, true));
+    if ((rc = step_decode(m))) return rc;
     if (next_ids) HX_CUDA(cudaMemcpyAsync(next_ids, m->d_tok, 4, cudaMemcpyDeviceToHost, m->st));
     if (logits) HX_CUDA(cudaMemcpyAsync(logits, m->logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToHost, m->st));
     HX_CUDA(cudaStreamSynchronize(m->st));
+    if ((rc = persist_check(m))) return rc;
     m->kv_len = pos + 1;
     return HX_OK;
 }
@@ -636,12 +785,9 @@ static int run_prefill(hx_model* m, const int32_t* ids, int T) {
     // positions 0..T-2 without the head, position T-1 with it
     HX_CUDA(cudaMemcpyAsync(m->d_prompt, ids, (size_t)T * 4, cudaMemcpyHostToDevice, m->st));
     int rc = set_pos_tok(m, 0, nullptr); if (rc) return rc;
-    for (int s = 0; s < T - 1; s++) HX_CUDA(cudaGraphLaunch(m->g_prefill, m->st));
-    HX_COUNT_LAUNCH((unsigned long long)(T - 1) * kernels_per_step(m, false));
+    for (int s = 0; s < T - 1; s++) if ((rc = step_prefill(m))) return rc;
     HX_CUDA(cudaMemcpyAsync(m->d_tok, m->d_prompt + (T - 1), 4, cudaMemcpyDeviceToDevice, m->st));
-    HX_CUDA(cudaGraphLaunch(m->g_decode, m->st));
-    HX_COUNT_LAUNCH(kernels_per_step(m, true));
-    return HX_OK;
+    return step_decode(m);
 }
 
 HX_API int hx_prefill(hx_model* m, const int32_t* ids, int T, int32_t* next_ids, float* logits) {
@@ -652,6 +798,7 @@ HX_API int hx_prefill(hx_model* m, const int32_t* ids, int T, int32_t* next_ids,
     if (next_ids) HX_CUDA(cudaMemcpyAsync(next_ids, m->d_tok, 4, cudaMemcpyDeviceToHost, m->st));
     if (logits) HX_CUDA(cudaMemcpyAsync(logits, m->logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToHost, m->st));
     HX_CUDA(cudaStreamSynchronize(m->st));
+    if ((rc = persist_check(m))) return rc;
     m->kv_len = T;
     return HX_OK;
 }
@@ -661,7 +808,7 @@ HX_API int hx_decode_loop(hx_model* m, const int32_t* ids, int pos0, int n_steps
     if (pos0 < 0 || pos0 + n_steps > m->kv_cap) return hx_fail(HX_ERR_STATE, "steps %d..%d outside the KV capacity %d", pos0, pos0 + n_steps, m->kv_cap);
     int rc = set_pos_tok(m, pos0, ids); if (rc) return rc;
     HX_CUDA(cudaEventRecord(m->ev0, m->st));
-    if (m->profile) {
+    if (m->profile && !m->persist) {
         // eager launches with an event pair around each kernel: per-kernel device time by category
         m->stats.ms_gemv = m->stats.ms_attn = m->stats.ms_other = 0.0f;
         for (int s = 0; s < n_steps; s++) {
@@ -675,15 +822,15 @@ HX_API int hx_decode_loop(hx_model* m, const int32_t* ids, int pos0, int n_steps
             }
         }
     } else {
-        for (int s = 0; s < n_steps; s++) HX_CUDA(cudaGraphLaunch(m->g_decode, m->st));
-        HX_COUNT_LAUNCH((unsigned long long)n_steps * kernels_per_step(m, true));
+        for (int s = 0; s < n_steps; s++) if ((rc = step_decode(m))) return rc;
     }
     HX_CUDA(cudaEventRecord(m->ev1, m->st));
     if (out_ids) HX_CUDA(cudaMemcpyAsync(out_ids, m->d_hist + pos0 + 1, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, m->st));
     HX_CUDA(cudaStreamSynchronize(m->st));
     float t = 0.0f; HX_CUDA(cudaEventElapsedTime(&t, m->ev0, m->ev1));
-    m->stats.ms_total = t; m->stats.kernel_launches = (uint32_t)(n_steps * kernels_per_step(m, true));
+    m->stats.ms_total = t; m->stats.kernel_launches = (uint32_t)(m->persist ? n_steps : n_steps * kernels_per_step(m, true));
     if (ms) *ms = t;
+    if ((rc = persist_check(m))) return rc;
     m->kv_len = pos0 + n_steps;
     return HX_OK;
 }
@@ -699,13 +846,13 @@ HX_API int hx_generate_greedy(hx_model* m, const int32_t* prompt, int T, int n_n
     int rc = run_prefill(m, prompt, T);            // leaves token #1 in d_tok / d_hist[T], *d_pos = T
     if (!rc) {
         cudaEventRecord(e1, m->st);
-        for (int s = 1; s < n_new; s++) cudaGraphLaunch(m->g_decode, m->st);
-        HX_COUNT_LAUNCH((unsigned long long)(n_new - 1) * kernels_per_step(m, true));
+        for (int s = 1; s < n_new && !rc; s++) rc = step_decode(m);
         cudaEventRecord(e2, m->st);
         cudaMemcpyAsync(out_ids, m->d_hist + T, (size_t)n_new * 4, cudaMemcpyDeviceToHost, m->st);
         cudaError_t e = cudaStreamSynchronize(m->st);
         if (e != cudaSuccess) rc = hx_fail(HX_ERR_CUDA, "generate: %s", cudaGetErrorString(e));
-        else {
+        else if ((rc = persist_check(m))) {}
+        else if (!rc) {
             float a = 0, b = 0; cudaEventElapsedTime(&a, e0, e1); cudaEventElapsedTime(&b, e1, e2);
             if (ms_prefill) *ms_prefill = a;
             if (ms_decode) *ms_decode = b;

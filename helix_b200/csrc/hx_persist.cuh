@@ -1,0 +1,72 @@
+// hx_persist.cuh -- interface of the persistent decode-step kernel (hx_persist.cu).
+#pragma once
+#include "hx_common.cuh"
+
+// ---- "T16" tile layout of a linear weight ----------------------------------------------------------
+// Rows are grouped in m-tiles of 16, columns in k-groups of 128 elements (8 scale blocks).  One
+// (m-tile, k-group) cell is 1152 bytes: 16 rows x 64 code bytes, then 16 rows x 8 E4M3 scale bytes.
+// Cells of one m-tile are contiguous in k, so any run of k-groups of a tile is one bulk copy.
+// Inside a row's 64 code bytes the 16-byte quarter t (0..3) holds, for mma step m (0..7), two bytes:
+//   byte0 = codes of (block 2p, element t+8h) | (block 2p+1, element t+8h) << 4
+//   byte1 = codes of (block 2p, element t+4+8h) | (block 2p+1, element t+4+8h) << 4      p = m/2, h = m%2
+// which is exactly what lane (row, t) of an m16n8k16 A fragment consumes, with the two halves of every
+// f16x2 register coming from two neighbouring scale blocks (so one cvt.e4m3x2 scales both).
+#define HX_T16_ROWS 16
+#define HX_T16_KG 128
+#define HX_T16_CELL 1152
+#define HX_SLOT_CELLS 16           // k-groups per ring slot = consumer warps
+#define HX_RING_SLOT (HX_SLOT_CELLS * HX_T16_CELL)    // 18432 B; also 36 cache rows of 128 floats
+#define HX_RING_SLOTS 7
+
+static inline int hx_t16_kgroups(int K) { return (K + HX_T16_KG - 1) / HX_T16_KG; }
+static inline int hx_t16_tiles(int N) { return (N + HX_T16_ROWS - 1) / HX_T16_ROWS; }
+static inline size_t hx_t16_bytes(int N, int K) { return (size_t)hx_t16_tiles(N) * hx_t16_kgroups(K) * HX_T16_CELL; }
+
+// committed layout -> T16.  Source row r goes to destination row (r / grp) * grp * row_mul + row_off * grp + r % grp
+// (grp = 16, row_mul = 2 interleaves gate and up tile by tile; grp = 1 is a plain offset).
+void hx_repack_t16(const int32_t* words, const uint8_t* micro, int rows, int K, int Kpad, uint8_t* dst,
+                   int dstKG, int grp, int row_mul, int row_off, cudaStream_t st);
+
+enum { HX_PH_LINEAR = 0, HX_PH_ATTN = 1 };
+
+struct HxPhase {
+    int type;
+    // ---- linear ----
+    const uint8_t* w;         // T16 base
+    int ntiles;               // m-tiles
+    int KG;                   // k-groups per row
+    int unit;                 // m-tiles per assignment unit (2 for gate/up pairs)
+    int N;                    // valid output rows (SwiGLU: hidden size = rows / 2)
+    const float* x;           // input vector, K floats (or the embedding table when tok != null)
+    const int* tok;           // when set: input = x + (*tok) * K, and it is copied to x_out
+    float* x_out;
+    int K;
+    int norm;                 // HX_NORM_NONE / HX_NORM_RMS
+    const float* g; float eps;
+    int epi;                  // HX_EPI_STORE / RESID / SWIGLU / ARGMAX
+    float* y;
+    float ts[3]; int bound0, bound1;
+    // ---- attention ----
+    const float* qkv; const float* qn_g; const float* kn_g; const float* cosT; const float* sinT;
+    float* kc; float* vc; float* ctx;
+    int NH, NKV, DH, cap, nsplit; float scale;   // attention also uses eps (per-head RMSNorm)
+};
+
+struct HxPersist {
+    const HxPhase* phases; int nphases;
+    const int* pos;                       // device scalar, position of the token being decoded
+    unsigned long long* bar;              // grid barrier counter (monotonic over launches)
+    unsigned long long bar_base;          // value of the counter when this launch starts
+    int* err;                             // set non-zero when a bounded wait ran out
+    // attention scratch
+    float* part_m; float* part_l; float* part_acc; unsigned* attn_cnt;
+    // arg-max
+    float* am_val; int* am_idx; unsigned* am_cnt; int* next_tok; int* pos_inc; int* hist; float* logits;
+    int dig_bytes;                        // shared-memory bytes reserved for the f16 split of x
+    int tok_by_pos;                       // the input token is tok[pos] (prompt) instead of tok[0]
+    int advance_pos;                      // no head in this launch: CTA 0 advances *pos_inc at the end
+    unsigned long long* dbg;              // optional: CTA 0 writes 4 globaltimer stamps per phase
+};
+
+int hx_persist_launch(const HxPersist& p, int grid, cudaStream_t st);
+size_t hx_persist_smem(int dig_bytes);
