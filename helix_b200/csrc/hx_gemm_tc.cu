@@ -1,0 +1,206 @@
+// hx_gemm_tc.cu -- block-scaled NVFP4 GEMM on the 5th-generation tensor cores (tcgen05, TMEM).
+//
+//   D[row, n] = sum_k  A[row,k] * SFA[row,k/16]  *  B[n,k] * SFB[n,k/16]         (f32 accumulate in TMEM)
+//
+// A = weights, E2M1 codes with one UE4M3 scale per 16 elements along K: exactly the information of
+// the committed NVFP4 layout (helixc/runtime/gpt2_pack.c:350-373), so the weights feed the tensor
+// cores without any per-weight instruction.  B = activations as E2M1 columns with UE4M3 block scales:
+// either the activation quantized once to NVFP4 (batched prefill, replaces tiled_matmul_abt of
+// forward_layer_llama, helixc/runtime/gpt2_infer.c:1231-1287) or several exact base-8 digit columns
+// of one f32 vector (decode, replaces fused_gemv :2281-2297).
+//
+// One CTA per 128-row tile of A.  Warp 0 streams A and B cells into a shared-memory ring with
+// cp.async.bulk; warp 1 copies the scale factors to TMEM (tcgen05.cp) and issues
+// tcgen05.mma.kind::mxf4nvf4.block_scale (M=128, N=ncols, K=64 per instruction); warps 2-5 read the
+// accumulator with tcgen05.ld and store it.  Tensor-bound for large N, HBM-bound for small N.
+//
+// "T128" layout of A: per (128-row tile, 64-column step) one 4608-byte cell: 2 x 128 x 16 bytes of
+// codes ([k-half][row][32 codes], the canonical K-major no-swizzle operand layout) followed by the
+// 512-byte scale chunk (byte (row%32)*16 + (row/32)*4 + block).  B cells: 2 x N x 16 bytes of codes
+// + a 512-byte scale chunk indexed by n.  Every wait is bounded.
+#include "hx_common.cuh"
+#include "hx_gemm_tc.cuh"
+
+#define TC_WAIT_LIMIT (1u << 22)
+
+namespace {
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mb_init(uint64_t* b, uint32_t n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(s_u32(b)), "r"(n) : "memory"); }
+__device__ __forceinline__ void mb_expect(uint64_t* b, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(s_u32(b)), "r"(bytes) : "memory"); }
+__device__ __forceinline__ void mb_arrive(uint64_t* b) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(s_u32(b)) : "memory"); }
+__device__ __forceinline__ bool mb_try(uint64_t* b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(s_u32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mb_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < TC_WAIT_LIMIT; i++) {
+        if (mb_try(b, parity)) return true;
+        if ((i & 255) == 255 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(s_u32(dst)), "l"(src), "r"(bytes), "r"(s_u32(bar)) : "memory");
+}
+// K-major, no swizzle: 8 rows x 16 bytes core matrices; lbo = byte distance between the two 16-byte
+// K halves, sbo = byte distance between 8-row groups.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) |
+           (1ull << 46);
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" :: "r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+                 :: "r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc), "r"(sfa), "r"(sfb) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(s_u32(bar)) : "memory");
+}
+
+struct TcSmem {
+    uint64_t full[HX_TC_STAGES], empty[HX_TC_STAGES], accum;
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+
+__global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGemmTC g) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    TcSmem& S = *reinterpret_cast<TcSmem*>(smem_raw);
+    uint8_t* ring = smem_raw + 256;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int NB = g.ncols, Sk = g.stage_ksteps;
+    const uint32_t a_cell = HX_T128_CELL, b_cell = (uint32_t)NB * 32u + 512u;
+    const uint32_t stage_bytes = (uint32_t)Sk * (a_cell + b_cell);
+    const int nstage_iters = (g.ksteps + Sk - 1) / Sk;
+
+    if (tid == 0) {
+        for (int i = 0; i < HX_TC_STAGES; i++) { mb_init(&S.full[i], 1); mb_init(&S.empty[i], 1); }
+        mb_init(&S.accum, 1);
+        S.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {    // one warp owns the TMEM allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" :: "r"(s_u32(&S.tmem_base)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = S.tmem_base;
+    // TMEM columns: [0, 256) accumulator (ncols used), then per ring slot Sk*4 columns of SFA and of SFB
+    const uint32_t col_sfa = 256, col_sfb = 256 + HX_TC_STAGES * HX_TC_MAX_SK * 4;
+
+    for (int mt = blockIdx.x; mt < g.ntiles; mt += gridDim.x) {
+        // tiles after the first reuse the barriers: phase bookkeeping continues across tiles
+        const int tile_iter = (mt - blockIdx.x) / gridDim.x;
+        const uint32_t base_it = (uint32_t)tile_iter * (uint32_t)nstage_iters;
+        if (warp == 0 && lane == 0) {
+            // ------------------------------ producer ------------------------------
+            for (int it = 0; it < nstage_iters; it++) {
+                const uint32_t git = base_it + it, slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
+                if (round > 0 && !mb_wait(&S.empty[slot], (round - 1) & 1, &S.abort_flag)) break;
+                const int ks0 = it * Sk, nk = min(Sk, g.ksteps - ks0);
+                uint8_t* sa = ring + (size_t)slot * stage_bytes;
+                uint8_t* sb = sa + (size_t)Sk * a_cell;
+                mb_expect(&S.full[slot], (uint32_t)nk * (a_cell + b_cell));
+                bulk_load(sa, g.a + ((size_t)mt * g.ksteps + ks0) * a_cell, (uint32_t)nk * a_cell, &S.full[slot]);
+                bulk_load(sb, g.b + (size_t)ks0 * b_cell, (uint32_t)nk * b_cell, &S.full[slot]);
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ------------------------------ MMA issuer ------------------------------
+            // instruction descriptor: E2M1 x E2M1, UE4M3 scales, K-major both, N = NB, M = 128, K = 64
+            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | (8u << 24);
+            for (int it = 0; it < nstage_iters; it++) {
+                const uint32_t git = base_it + it, slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
+                if (!mb_wait(&S.full[slot], round & 1, &S.abort_flag)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int ks0 = it * Sk, nk = min(Sk, g.ksteps - ks0);
+                const uint32_t sa = s_u32(ring + (size_t)slot * stage_bytes), sb = sa + (uint32_t)Sk * a_cell;
+                for (int k = 0; k < nk; k++) {
+                    const uint32_t ta = tmem + col_sfa + (slot * HX_TC_MAX_SK + k) * 4;
+                    const uint32_t tb = tmem + col_sfb + (slot * HX_TC_MAX_SK + k) * 4;
+                    tc_cp_sf(ta, smem_desc(sa + k * a_cell + 4096, 16, 128));
+                    tc_cp_sf(tb, smem_desc(sb + k * b_cell + (uint32_t)NB * 32u, 16, 128));
+                    tc_mma(tmem, smem_desc(sa + k * a_cell, 2048, 128), smem_desc(sb + k * b_cell, (uint32_t)NB * 16u, 128), idesc, ta, tb,
+                           (it > 0 || k > 0) ? 1u : 0u);
+                }
+                tc_commit(&S.empty[slot]);          // the slot is free once these MMAs have read it
+            }
+            tc_commit(&S.accum);                    // accumulator complete
+        } else if (warp >= 2) {
+            // ------------------------------ epilogue: TMEM -> registers -> global ------------------------------
+            if (mb_wait(&S.accum, (uint32_t)tile_iter & 1u, &S.abort_flag)) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int sub = warp & 3;                          // TMEM lanes 32*sub .. 32*sub+31
+                const int row = mt * 128 + sub * 32 + lane;
+                for (int c0 = 0; c0 < NB; c0 += 8) {
+                    uint32_t r[8];
+                    const uint32_t ta = tmem + ((uint32_t)(sub * 32) << 16) + (uint32_t)c0;
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(ta));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (row < g.rows) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) g.y[(size_t)row * NB + c0 + j] = __uint_as_float(r[j]);
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+        }
+        // all roles meet before the next tile (the accumulator is reused)
+        __syncthreads();
+    }
+    if (S.abort_flag && tid == 0 && g.err) *g.err = 1;
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" :: "r"(tmem) : "memory");
+}
+
+}  // namespace
+
+size_t hx_gemm_tc_smem(int ncols, int stage_ksteps) {
+    return 256 + (size_t)HX_TC_STAGES * stage_ksteps * (HX_T128_CELL + (size_t)ncols * 32 + 512);
+}
+
+int hx_gemm_tc_launch(const HxGemmTC& g, cudaStream_t st) {
+    HX_CHECK_ARG(g.a && g.b && g.y && g.ntiles > 0 && g.ksteps > 0);
+    HX_CHECK_ARG(g.ncols >= 8 && g.ncols <= 256 && g.ncols % 8 == 0);
+    HX_CHECK_ARG(g.stage_ksteps >= 1 && g.stage_ksteps <= HX_TC_MAX_SK);
+    const size_t smem = hx_gemm_tc_smem(g.ncols, g.stage_ksteps);
+    if (smem > 227 * 1024) return hx_fail(HX_ERR_ARG, "tensor-core GEMM stage too large (%zu bytes of shared memory)", smem);
+    static bool attr = false;
+    if (!attr) { HX_CUDA(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); attr = true; }
+    int grid = g.ntiles; if (grid > 148) grid = 148;
+    k_gemm_tc<<<grid, 192, smem, st>>>(g);
+    HX_COUNT_LAUNCH(1);
+    HX_CUDA(cudaGetLastError());
+    return HX_OK;
+}
+
+// C-ABI entry for tests and tools: all pointers are device pointers.
+HX_API int hx_gemm_nvfp4_tc(const uint8_t* a_t128, int rows, int K, const uint8_t* b_cells, int ncols, float* y,
+                            int stage_ksteps, void* stream) {
+    HX_CHECK_ARG(rows > 0 && K > 0 && K % 64 == 0);
+    HxGemmTC g = {};
+    g.a = a_t128; g.b = b_cells; g.y = y; g.rows = rows; g.ntiles = (rows + 127) / 128; g.ksteps = K / 64;
+    g.ncols = ncols; g.stage_ksteps = stage_ksteps > 0 ? stage_ksteps : 4;
+    int* derr = nullptr;
+    HX_CUDA(cudaMalloc(&derr, 4));
+    HX_CUDA(cudaMemsetAsync(derr, 0, 4, (cudaStream_t)stream));
+    g.err = derr;
+    int rc = hx_gemm_tc_launch(g, (cudaStream_t)stream);
+    int e = 0;
+    if (!rc) {
+        cudaError_t ce = cudaStreamSynchronize((cudaStream_t)stream);
+        if (ce != cudaSuccess) rc = hx_fail(HX_ERR_CUDA, "tensor-core GEMM: %s", cudaGetErrorString(ce));
+        else { cudaMemcpy(&e, derr, 4, cudaMemcpyDeviceToHost); if (e) rc = hx_fail(HX_ERR_TIMEOUT, "tensor-core GEMM: a bounded wait ran out"); }
+    }
+    cudaFree(derr);
+    return rc;
+}

@@ -184,6 +184,209 @@ struct Smem {
     volatile int abort_flag;
 };
 
+#define STAMP(i) do { if (P.dbg && cta == 0 && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg[pi * 16 + (i)] = _t; } } while (0)
+
+// ------------------------------------------------------------------------------------------------
+// Attention phase of one CTA: (kv head, split of the cached positions); the GRP query heads of the kv
+// head share the K and V rows.  Kept out of line and specialised per group size so that only the
+// variant in use occupies the instruction cache.
+// ------------------------------------------------------------------------------------------------
+template <int GRP>
+__device__ __noinline__ bool attention_phase(const HxPersist& P, const HxPhase& ph, Smem& S, uint8_t* ring, uint8_t* digb,
+                                             uint32_t& ctr, int pi, int pos) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, cta = blockIdx.x;
+    const AttPlan ap = att_plan(ph, cta, pos);
+    const int DH = ph.DH, half = DH >> 1;
+    float* sq = reinterpret_cast<float*>(digb);                 // [GRP][DH] rotated queries
+    float* knew = sq + 8 * 256;                                  // [DH] current k (normed, rotated)
+    float* vnew = knew + 256;                                    // [DH]
+    float* sp = vnew + 256;                                      // [GRP][rows_per_slot + 1] scores / probabilities
+    float* accx = sp + 8 * 160;                                  // [nsub][GRP][DH] partial outputs
+    const int spitch = ap.rows_per_slot + 1;
+    const int nsub = NCT / DH;                                   // threads per output dimension
+    const int d = tid % DH, sub = tid / DH;
+    float acc[GRP];
+#pragma unroll
+    for (int i = 0; i < GRP; i++) acc[i] = 0.0f;
+    if (ap.active && ap.t1 > ap.t0) {
+        // q (GRP heads) and, where the current position falls in this split, k and v:
+        // per-head RMSNorm then rotate_half RoPE with table row pos (all loads of a lane first)
+        const int nvec = GRP + (ap.has_new ? 2 : 0);
+        #pragma unroll 1
+        for (int v = warp; v < nvec; v += NCW) {
+            const bool isq = v < GRP, isv = v == GRP + 1;
+            const float* src = isq ? ph.qkv + (size_t)(ap.kv * GRP + v) * DH
+                                   : ph.qkv + (size_t)ph.NH * DH + (size_t)(isv ? ph.NKV : 0) * DH + (size_t)ap.kv * DH;
+            const float* gg = isv ? nullptr : (isq ? ph.qn_g : ph.kn_g);
+            float* dst = isq ? sq + v * DH : (isv ? vnew : knew);
+            float xv[8];
+            float ssq = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { const int e = lane + 32 * j; xv[j] = e < DH ? __ldcg(src + e) : 0.0f; ssq = fmaf(xv[j], xv[j], ssq); }
+            ssq = hx_warp_sum(ssq);
+            const float inv = gg ? rsqrtf(ssq / (float)DH + ph.eps) : 1.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { const int e = lane + 32 * j; if (e < DH) dst[e] = gg ? gg[e] * (xv[j] * inv) : xv[j]; }
+            __syncwarp();
+            if (ph.cosT && !isv) {
+                for (int e = lane; e < half; e += 32) {
+                    const float lo = dst[e], hi = dst[e + half];
+                    const float cs = ph.cosT[(size_t)pos * half + e], sn = ph.sinT[(size_t)pos * half + e];
+                    dst[e] = lo * cs - hi * sn; dst[e + half] = hi * cs + lo * sn;
+                }
+            }
+        }
+        if (tid < 8) { S.att_m[tid] = -100000000.0f; S.att_l[tid] = 0.0f; }
+        consumer_sync();
+        STAMP(4);
+        if (ap.has_new) {        // append to the cache for the tokens to come
+            const size_t o = ((size_t)ap.kv * ph.cap + pos) * DH;
+            for (int e = tid; e < DH; e += NCT) { ph.kc[o + e] = knew[e]; ph.vc[o + e] = vnew[e]; }
+        }
+        const int ntile = ap.nslots + ((ap.has_new && ap.n_old % ap.rows_per_slot == 0) ? 1 : 0);
+        #pragma unroll 1
+        for (int s = 0; s < ntile; s++) {
+            const bool ring_tile = s < ap.nslots;
+            int nr = ring_tile ? min(ap.rows_per_slot, ap.n_old - s * ap.rows_per_slot) : 0;
+            // the current position rides on the last tile (room is guaranteed: spitch = rows + 1)
+            const bool add_new = ap.has_new && (s == ntile - 1);
+            uint32_t kslot = 0, vslot = 0;
+            const float* kt = nullptr; const float* vt = nullptr;
+            if (ring_tile) {
+                kslot = ctr % HX_RING_SLOTS; const uint32_t kround = ctr / HX_RING_SLOTS; ctr++;
+                if (!mbar_wait(&S.full[kslot], kround & 1, &S.abort_flag)) return false;
+                kt = reinterpret_cast<const float*>(ring + (size_t)kslot * HX_RING_SLOT);
+            }
+            if (s == 0) STAMP(8);
+            const int ntot = nr + (add_new ? 1 : 0);
+            // scores: a warp per position, lanes over the head dimension
+            #pragma unroll 1
+            for (int r = warp; r < ntot; r += NCW) {
+                const float* kr = (r < nr) ? kt + (size_t)r * DH : knew;
+                float dot[GRP];
+#pragma unroll
+                for (int i = 0; i < GRP; i++) dot[i] = 0.0f;
+                #pragma unroll 1
+                for (int e = lane * 4; e < DH; e += 128) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(kr + e);
+#pragma unroll
+                    for (int i = 0; i < GRP; i++) {
+                        const float4 q4 = *reinterpret_cast<const float4*>(sq + i * DH + e);
+                        dot[i] = fmaf(q4.x, k4.x, dot[i]); dot[i] = fmaf(q4.y, k4.y, dot[i]);
+                        dot[i] = fmaf(q4.z, k4.z, dot[i]); dot[i] = fmaf(q4.w, k4.w, dot[i]);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < GRP; i++) {
+                    const float sc = hx_warp_sum(dot[i]);
+                    if (lane == 0) sp[i * spitch + r] = sc * ph.scale;
+                }
+            }
+            __syncwarp();
+            if (ring_tile && lane == 0) mbar_arrive(&S.empty[kslot]);
+            consumer_sync();
+            if (s == 0) STAMP(9);
+            // online softmax state per head (fused_decode_attn_kernel.hx:74-102)
+            #pragma unroll 1
+            for (int i = warp; i < GRP; i += NCW) {
+                float tm = -INFINITY;
+                for (int r = lane; r < ntot; r += 32) tm = fmaxf(tm, sp[i * spitch + r]);
+                tm = hx_warp_max(tm);
+                const float mo = S.att_m[i], mn = fmaxf(mo, tm);
+                float ls = 0.0f;
+                for (int r = lane; r < ntot; r += 32) { const float pr = __expf(sp[i * spitch + r] - mn); sp[i * spitch + r] = pr; ls += pr; }
+                ls = hx_warp_sum(ls);
+                if (lane == 0) { const float rr = __expf(mo - mn); S.att_r[i] = rr; S.att_l[i] = S.att_l[i] * rr + ls; S.att_m[i] = mn; }
+            }
+            consumer_sync();
+            if (ring_tile) {
+                vslot = ctr % HX_RING_SLOTS; const uint32_t vround = ctr / HX_RING_SLOTS; ctr++;
+                if (!mbar_wait(&S.full[vslot], vround & 1, &S.abort_flag)) return false;
+                vt = reinterpret_cast<const float*>(ring + (size_t)vslot * HX_RING_SLOT);
+            }
+            if (s == 0) STAMP(10);
+#pragma unroll
+            for (int i = 0; i < GRP; i++) acc[i] *= S.att_r[i];
+            #pragma unroll 1
+            for (int r = sub; r < ntot; r += nsub) {
+                const float vv = (r < nr) ? vt[(size_t)r * DH + d] : vnew[d];
+#pragma unroll
+                for (int i = 0; i < GRP; i++) acc[i] = fmaf(sp[i * spitch + r], vv, acc[i]);
+            }
+            __syncwarp();
+            if (ring_tile && lane == 0) mbar_arrive(&S.empty[vslot]);
+            consumer_sync();
+        }
+        STAMP(5);
+        // fold the position subsets, write this split's partial
+#pragma unroll
+        for (int i = 0; i < GRP; i++) accx[(sub * 8 + i) * DH + d] = acc[i];
+        consumer_sync();
+        if (sub == 0) {
+#pragma unroll
+            for (int i = 0; i < GRP; i++) {
+                float v = 0.0f;
+                for (int u = 0; u < nsub; u++) v += accx[(u * 8 + i) * DH + d];
+                const size_t hs = (size_t)(ap.kv * GRP + i) * ph.nsplit + ap.split;
+                P.part_acc[hs * DH + d] = v;
+                if (d == 0) { P.part_m[hs] = S.att_m[i]; P.part_l[hs] = S.att_l[i]; }
+            }
+        }
+    } else if (ap.active) {
+        // empty split: neutral partial
+        for (int i = tid; i < GRP; i += NCT) {
+            const size_t hs = (size_t)(ap.kv * GRP + i) * ph.nsplit + ap.split;
+            P.part_m[hs] = -100000000.0f; P.part_l[hs] = 0.0f;
+        }
+        for (int i = tid; i < GRP * DH; i += NCT) {
+            const size_t hs = (size_t)(ap.kv * GRP + i / DH) * ph.nsplit + ap.split;
+            P.part_acc[hs * DH + i % DH] = 0.0f;
+        }
+    }
+    if (ap.active) {
+        STAMP(6);
+        __threadfence();
+        consumer_sync();
+        if (tid == 0) S.ticket = atomicAdd(P.attn_cnt + ap.kv, 1u);
+        consumer_sync();
+        STAMP(7);
+        if (S.ticket == (unsigned)ph.nsplit - 1) {
+            __threadfence();
+            // merge of the splits: weights w_s = exp(m_s - M) / sum_s l_s exp(m_s - M), then one pass
+            // of independent loads over the partial outputs
+            float* wgt = sp;                                   // [GRP][nsplit]
+            const size_t hbase = (size_t)(ap.kv * GRP) * ph.nsplit;
+            #pragma unroll 1
+            for (int i = warp; i < GRP; i += NCW) {
+                float mv[2], lv[2];
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int sidx = lane + 32 * j;
+                    mv[j] = sidx < ph.nsplit ? __ldcg(P.part_m + hbase + (size_t)i * ph.nsplit + sidx) : -INFINITY;
+                    lv[j] = sidx < ph.nsplit ? __ldcg(P.part_l + hbase + (size_t)i * ph.nsplit + sidx) : 0.0f;
+                }
+                const float M = hx_warp_max(fmaxf(mv[0], mv[1]));
+                const float w0 = __expf(mv[0] - M), w1 = __expf(mv[1] - M);
+                const float Lsum = hx_warp_sum(lv[0] * w0 + lv[1] * w1);
+                if (lane < ph.nsplit) wgt[i * ph.nsplit + lane] = w0 / Lsum;
+                if (lane + 32 < ph.nsplit) wgt[i * ph.nsplit + lane + 32] = w1 / Lsum;
+            }
+            consumer_sync();
+            #pragma unroll 1
+            for (int o = tid; o < GRP * DH; o += NCT) {
+                const int i = o / DH, dd = o % DH;
+                const float* pa = P.part_acc + (hbase + (size_t)i * ph.nsplit) * DH + dd;
+                float ov = 0.0f;
+#pragma unroll 6
+                for (int sidx = 0; sidx < ph.nsplit; sidx++) ov = fmaf(__ldcg(pa + (size_t)sidx * DH), wgt[i * ph.nsplit + sidx], ov);
+                ph.ctx[(size_t)(ap.kv * GRP + i) * DH + dd] = ov;
+            }
+            if (tid == 0) P.attn_cnt[ap.kv] = 0u;
+        }
+    }
+    return true;
+}
+
 __global__ void __launch_bounds__(PT, 1) k_decode_persist(const __grid_constant__ HxPersist P) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Smem& S = *reinterpret_cast<Smem*>(smem_raw);
@@ -212,14 +415,17 @@ __global__ void __launch_bounds__(PT, 1) k_decode_persist(const __grid_constant_
             ctr++;
             return true;
         };
+        #pragma unroll 1
         for (int pi = 0; pi < P.nphases; pi++) {
             const HxPhase& ph = P.phases[pi];
             if (ph.type == HX_PH_LINEAR) {
                 const LinPlan lp = lin_plan(ph, cta, grid);
                 for (int i = 0; i < lp.nunits; i++)
+                    #pragma unroll 1
                     for (int tu = 0; tu < ph.unit; tu++) {
                         const int mt = (cta + i * grid) * ph.unit + tu;
                         const uint8_t* tb = ph.w + (size_t)mt * ph.KG * HX_T16_CELL;
+                        #pragma unroll 1
                         for (int s = 0; s < lp.nst; s++) {
                             const int kg0 = s * lp.kg_per, nkg = min(lp.kg_per, ph.KG - kg0);
                             if (!push(tb + (size_t)kg0 * HX_T16_CELL, (uint32_t)nkg * HX_T16_CELL)) return;
@@ -228,6 +434,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_persist(const __grid_constant_
             } else {
                 const AttPlan ap = att_plan(ph, cta, pos);
                 const size_t rowb = (size_t)ph.DH * 4;
+                #pragma unroll 1
                 for (int s = 0; s < ap.nslots; s++) {
                     const int r0 = ap.t0 + s * ap.rows_per_slot, nr = min(ap.rows_per_slot, ap.t0 + ap.n_old - r0);
                     const size_t off = ((size_t)ap.kv * ph.cap + r0) * ph.DH;
@@ -245,7 +452,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_persist(const __grid_constant_
     const int g = lane >> 2, t = lane & 3;
     float best_v = -INFINITY; int best_i = INT_MAX;
 
-#define STAMP(i) do { if (P.dbg && cta == 0 && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg[pi * 16 + (i)] = _t; } } while (0)
+    #pragma unroll 1
     for (int pi = 0; pi < P.nphases; pi++) {
         const HxPhase& ph = P.phases[pi];
         STAMP(0);
@@ -258,6 +465,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_persist(const __grid_constant_
             __half* dig = reinterpret_cast<__half*>(digb);
             float inv = 1.0f, Sx = 1.0f;
             constexpr int XQ = 6;                                  // float4 per thread per chunk: 512*4*6 = 12288 elements
+            #pragma unroll 1
             for (int c0 = 0; c0 < Kt; c0 += NCT * 4 * XQ) {
                 const bool single = (Kt <= NCT * 4 * XQ);
                 float4 xr[XQ];
@@ -345,10 +553,13 @@ __global__ void __launch_bounds__(PT, 1) k_decode_persist(const __grid_constant_
             long long wait_cycles = 0;
             const float total_scale = Sx;
             int pbuf = 0;
+            #pragma unroll 1
             for (int i = 0; i < lp.nunits; i++) {
+                #pragma unroll 1
                 for (int tu = 0; tu < ph.unit; tu++) {
                     const int mt = (cta + i * grid) * ph.unit + tu;
                     float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};   // two chains: mma latency overlaps
+                    #pragma unroll 1
                     for (int s = 0; s < lp.nst; s++) {
                         const int kg0 = s * lp.kg_per, nkg = min(lp.kg_per, ph.KG - kg0);
                         const uint32_t slot = ctr % HX_RING_SLOTS, round = ctr / HX_RING_SLOTS;
@@ -461,189 +672,19 @@ __global__ void __launch_bounds__(PT, 1) k_decode_persist(const __grid_constant_
             }
         } else {
             // ------------------------------- attention -------------------------------
-            const AttPlan ap = att_plan(ph, cta, pos);
-            const int DH = ph.DH, GRP = ph.NH / ph.NKV, half = DH >> 1;
-            float* sq = reinterpret_cast<float*>(digb);                 // [GRP][DH] rotated queries
-            float* knew = sq + 8 * 256;                                  // [DH] current k (normed, rotated)
-            float* vnew = knew + 256;                                    // [DH]
-            float* sp = vnew + 256;                                      // [GRP][rows_per_slot + 1] scores / probabilities
-            float* accx = sp + 8 * 160;                                  // [nsub][GRP][DH] partial outputs
-            const int spitch = ap.rows_per_slot + 1;
-            const int nsub = NCT / DH;                                   // threads per output dimension
-            const int d = tid % DH, sub = tid / DH;
-            float acc[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) acc[i] = 0.0f;
-            if (ap.active && ap.t1 > ap.t0) {
-                // q (GRP heads) and, where the current position falls in this split, k and v:
-                // per-head RMSNorm then rotate_half RoPE with table row pos (all loads of a lane first)
-                const int nvec = GRP + (ap.has_new ? 2 : 0);
-                for (int v = warp; v < nvec; v += NCW) {
-                    const bool isq = v < GRP, isv = v == GRP + 1;
-                    const float* src = isq ? ph.qkv + (size_t)(ap.kv * GRP + v) * DH
-                                           : ph.qkv + (size_t)ph.NH * DH + (size_t)(isv ? ph.NKV : 0) * DH + (size_t)ap.kv * DH;
-                    const float* gg = isv ? nullptr : (isq ? ph.qn_g : ph.kn_g);
-                    float* dst = isq ? sq + v * DH : (isv ? vnew : knew);
-                    float xv[8];
-                    float ssq = 0.0f;
-#pragma unroll
-                    for (int j = 0; j < 8; j++) { const int e = lane + 32 * j; xv[j] = e < DH ? __ldcg(src + e) : 0.0f; ssq = fmaf(xv[j], xv[j], ssq); }
-                    ssq = hx_warp_sum(ssq);
-                    const float inv = gg ? rsqrtf(ssq / (float)DH + ph.eps) : 1.0f;
-#pragma unroll
-                    for (int j = 0; j < 8; j++) { const int e = lane + 32 * j; if (e < DH) dst[e] = gg ? gg[e] * (xv[j] * inv) : xv[j]; }
-                    __syncwarp();
-                    if (ph.cosT && !isv) {
-                        for (int e = lane; e < half; e += 32) {
-                            const float lo = dst[e], hi = dst[e + half];
-                            const float cs = ph.cosT[(size_t)pos * half + e], sn = ph.sinT[(size_t)pos * half + e];
-                            dst[e] = lo * cs - hi * sn; dst[e + half] = hi * cs + lo * sn;
-                        }
-                    }
-                }
-                if (tid < 8) { S.att_m[tid] = -100000000.0f; S.att_l[tid] = 0.0f; }
-                consumer_sync();
-                STAMP(4);
-                if (ap.has_new) {        // append to the cache for the tokens to come
-                    const size_t o = ((size_t)ap.kv * ph.cap + pos) * DH;
-                    for (int e = tid; e < DH; e += NCT) { ph.kc[o + e] = knew[e]; ph.vc[o + e] = vnew[e]; }
-                }
-                const int ntile = ap.nslots + ((ap.has_new && ap.n_old % ap.rows_per_slot == 0) ? 1 : 0);
-                for (int s = 0; s < ntile; s++) {
-                    const bool ring_tile = s < ap.nslots;
-                    int nr = ring_tile ? min(ap.rows_per_slot, ap.n_old - s * ap.rows_per_slot) : 0;
-                    // the current position rides on the last tile (room is guaranteed: spitch = rows + 1)
-                    const bool add_new = ap.has_new && (s == ntile - 1);
-                    uint32_t kslot = 0, vslot = 0;
-                    const float* kt = nullptr; const float* vt = nullptr;
-                    if (ring_tile) {
-                        kslot = ctr % HX_RING_SLOTS; const uint32_t kround = ctr / HX_RING_SLOTS; ctr++;
-                        if (!mbar_wait(&S.full[kslot], kround & 1, &S.abort_flag)) goto aborted;
-                        kt = reinterpret_cast<const float*>(ring + (size_t)kslot * HX_RING_SLOT);
-                    }
-                    if (s == 0) STAMP(8);
-                    const int ntot = nr + (add_new ? 1 : 0);
-                    // scores: a warp per position, lanes over the head dimension
-                    for (int r = warp; r < ntot; r += NCW) {
-                        const float* kr = (r < nr) ? kt + (size_t)r * DH : knew;
-                        float dot[8];
-#pragma unroll
-                        for (int i = 0; i < 8; i++) dot[i] = 0.0f;
-                        for (int e = lane * 4; e < DH; e += 128) {
-                            const float4 k4 = *reinterpret_cast<const float4*>(kr + e);
-#pragma unroll
-                            for (int i = 0; i < 8; i++) if (i < GRP) {
-                                const float4 q4 = *reinterpret_cast<const float4*>(sq + i * DH + e);
-                                dot[i] = fmaf(q4.x, k4.x, dot[i]); dot[i] = fmaf(q4.y, k4.y, dot[i]);
-                                dot[i] = fmaf(q4.z, k4.z, dot[i]); dot[i] = fmaf(q4.w, k4.w, dot[i]);
-                            }
-                        }
-#pragma unroll
-                        for (int i = 0; i < 8; i++) if (i < GRP) {
-                            const float sc = hx_warp_sum(dot[i]);
-                            if (lane == 0) sp[i * spitch + r] = sc * ph.scale;
-                        }
-                    }
-                    __syncwarp();
-                    if (ring_tile && lane == 0) mbar_arrive(&S.empty[kslot]);
-                    consumer_sync();
-                    if (s == 0) STAMP(9);
-                    // online softmax state per head (fused_decode_attn_kernel.hx:74-102)
-                    for (int i = warp; i < GRP; i += NCW) {
-                        float tm = -INFINITY;
-                        for (int r = lane; r < ntot; r += 32) tm = fmaxf(tm, sp[i * spitch + r]);
-                        tm = hx_warp_max(tm);
-                        const float mo = S.att_m[i], mn = fmaxf(mo, tm);
-                        float ls = 0.0f;
-                        for (int r = lane; r < ntot; r += 32) { const float pr = __expf(sp[i * spitch + r] - mn); sp[i * spitch + r] = pr; ls += pr; }
-                        ls = hx_warp_sum(ls);
-                        if (lane == 0) { const float rr = __expf(mo - mn); S.att_r[i] = rr; S.att_l[i] = S.att_l[i] * rr + ls; S.att_m[i] = mn; }
-                    }
-                    consumer_sync();
-                    if (ring_tile) {
-                        vslot = ctr % HX_RING_SLOTS; const uint32_t vround = ctr / HX_RING_SLOTS; ctr++;
-                        if (!mbar_wait(&S.full[vslot], vround & 1, &S.abort_flag)) goto aborted;
-                        vt = reinterpret_cast<const float*>(ring + (size_t)vslot * HX_RING_SLOT);
-                    }
-                    if (s == 0) STAMP(10);
-#pragma unroll
-                    for (int i = 0; i < 8; i++) if (i < GRP) acc[i] *= S.att_r[i];
-                    for (int r = sub; r < ntot; r += nsub) {
-                        const float vv = (r < nr) ? vt[(size_t)r * DH + d] : vnew[d];
-#pragma unroll
-                        for (int i = 0; i < 8; i++) if (i < GRP) acc[i] = fmaf(sp[i * spitch + r], vv, acc[i]);
-                    }
-                    __syncwarp();
-                    if (ring_tile && lane == 0) mbar_arrive(&S.empty[vslot]);
-                    consumer_sync();
-                }
-                STAMP(5);
-                // fold the position subsets, write this split's partial
-#pragma unroll
-                for (int i = 0; i < 8; i++) if (i < GRP) accx[(sub * 8 + i) * DH + d] = acc[i];
-                consumer_sync();
-                if (sub == 0) {
-#pragma unroll
-                    for (int i = 0; i < 8; i++) if (i < GRP) {
-                        float v = 0.0f;
-                        for (int u = 0; u < nsub; u++) v += accx[(u * 8 + i) * DH + d];
-                        const size_t hs = (size_t)(ap.kv * GRP + i) * ph.nsplit + ap.split;
-                        P.part_acc[hs * DH + d] = v;
-                        if (d == 0) { P.part_m[hs] = S.att_m[i]; P.part_l[hs] = S.att_l[i]; }
-                    }
-                }
-            } else if (ap.active) {
-                // empty split: neutral partial
-                for (int i = tid; i < GRP; i += NCT) {
-                    const size_t hs = (size_t)(ap.kv * GRP + i) * ph.nsplit + ap.split;
-                    P.part_m[hs] = -100000000.0f; P.part_l[hs] = 0.0f;
-                }
-                for (int i = tid; i < GRP * DH; i += NCT) {
-                    const size_t hs = (size_t)(ap.kv * GRP + i / DH) * ph.nsplit + ap.split;
-                    P.part_acc[hs * DH + i % DH] = 0.0f;
-                }
+            bool ok;
+            switch (ph.NH / ph.NKV) {
+                case 1: ok = attention_phase<1>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                case 2: ok = attention_phase<2>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                case 3: ok = attention_phase<3>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                case 4: ok = attention_phase<4>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                case 5: ok = attention_phase<5>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                case 6: ok = attention_phase<6>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                case 7: ok = attention_phase<7>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                default: ok = attention_phase<8>(P, ph, S, ring, digb, ctr, pi, pos); break;
             }
-            if (ap.active) {
-                STAMP(6);
-                __threadfence();
-                consumer_sync();
-                if (tid == 0) S.ticket = atomicAdd(P.attn_cnt + ap.kv, 1u);
-                consumer_sync();
-                STAMP(7);
-                if (S.ticket == (unsigned)ph.nsplit - 1) {
-                    __threadfence();
-                    // merge of the splits: weights w_s = exp(m_s - M) / sum_s l_s exp(m_s - M), then one pass
-                    // of independent loads over the partial outputs
-                    float* wgt = sp;                                   // [GRP][nsplit]
-                    const size_t hbase = (size_t)(ap.kv * GRP) * ph.nsplit;
-                    for (int i = warp; i < GRP; i += NCW) {
-                        float mv[2], lv[2];
-#pragma unroll
-                        for (int j = 0; j < 2; j++) {
-                            const int sidx = lane + 32 * j;
-                            mv[j] = sidx < ph.nsplit ? __ldcg(P.part_m + hbase + (size_t)i * ph.nsplit + sidx) : -INFINITY;
-                            lv[j] = sidx < ph.nsplit ? __ldcg(P.part_l + hbase + (size_t)i * ph.nsplit + sidx) : 0.0f;
-                        }
-                        const float M = hx_warp_max(fmaxf(mv[0], mv[1]));
-                        const float w0 = __expf(mv[0] - M), w1 = __expf(mv[1] - M);
-                        const float Lsum = hx_warp_sum(lv[0] * w0 + lv[1] * w1);
-                        if (lane < ph.nsplit) wgt[i * ph.nsplit + lane] = w0 / Lsum;
-                        if (lane + 32 < ph.nsplit) wgt[i * ph.nsplit + lane + 32] = w1 / Lsum;
-                    }
-                    consumer_sync();
-                    for (int o = tid; o < GRP * DH; o += NCT) {
-                        const int i = o / DH, dd = o % DH;
-                        const float* pa = P.part_acc + (hbase + (size_t)i * ph.nsplit) * DH + dd;
-                        float ov = 0.0f;
-#pragma unroll 6
-                        for (int sidx = 0; sidx < ph.nsplit; sidx++) ov = fmaf(__ldcg(pa + (size_t)sidx * DH), wgt[i * ph.nsplit + sidx], ov);
-                        ph.ctx[(size_t)(ap.kv * GRP + i) * DH + dd] = ov;
-                    }
-                    if (tid == 0) P.attn_cnt[ap.kv] = 0u;
-                }
-            }
+            if (!ok) goto aborted;
         }
-
         STAMP(2);
         // ---------- grid barrier: every CTA's writes of this phase are visible before the next ----------
         if (pi + 1 < P.nphases) {

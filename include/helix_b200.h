@@ -107,6 +107,16 @@ int hx_repack_d16(const int32_t* words, const uint8_t* micro, int rows, int K, i
 int hx_gemv_d16(const float* x, const uint8_t* codes, const uint8_t* scales, const float* ts,
                 float* y, int N, int Kd, void* stream);
 
+/* Block-scaled NVFP4 GEMM on the tensor cores (tcgen05.mma kind::mxf4nvf4, TMEM accumulators), device
+ * pointers: y[rows][ncols] = sum_k A[row,k]*SFA[row,k/16] * B[n,k]*SFB[n,k/16].
+ *   a_t128  weights in 4608-byte cells [tile of 128 rows][step of 64 columns]: 2 x 128 x 16 B of codes
+ *           ([k half][row][32 codes, low nibble first]) + 512 B of E4M3 scales (byte (row%32)*16+(row/32)*4+blk)
+ *   b_cells activations, per 64-column step: 2 x ncols x 16 B of codes + a 512 B scale chunk indexed by n
+ * K % 64 == 0, ncols % 8 == 0, 8 <= ncols <= 256.  Replaces the f32 tiled_matmul_abt projections of
+ * forward_layer_llama (gpt2_infer.c:1231-1287) for batched prefill.  Synchronous. */
+int hx_gemm_nvfp4_tc(const uint8_t* a_t128, int rows, int K, const uint8_t* b_cells, int ncols, float* y,
+                     int stage_ksteps, void* stream);
+
 /* ---------------------------------------------------------------- SHA-256 / receipt ----------- */
 /* FIPS 180-4.  Replaces sha256 / sha256_hex / sha256_file, gpt2_infer.c:137-213. */
 int hx_sha256(const void* data, size_t n, uint8_t out[32]);
