@@ -14,12 +14,16 @@
 // tcgen05.mma.kind::mxf4nvf4.block_scale (M=128, N=ncols, K=64 per instruction); warps 2-5 read the
 // accumulator with tcgen05.ld and store it.  Tensor-bound for large N, HBM-bound for small N.
 //
-// "T128" layout of A: per (128-row tile, 64-column step) one 4608-byte cell: 2 x 128 x 16 bytes of
-// codes ([k-half][row][32 codes], the canonical K-major no-swizzle operand layout) followed by the
-// 512-byte scale chunk (byte (row%32)*16 + (row/32)*4 + block).  B cells: 2 x N x 16 bytes of codes
-// + a 512-byte scale chunk indexed by n.  Every wait is bounded.
+// "T128" layout of A: per (128-row tile, group of 256 columns = four MMA K steps) one 18432-byte cell:
+// 128 rows x 128 bytes of codes in the canonical K-major 128-byte-swizzle operand layout (row r at
+// r*128, its 16-byte chunk j stored at position j ^ (r & 7)), then four 512-byte scale chunks, one per
+// K step (byte (row%32)*16 + (row/32)*4 + block).  B cells: N rows x 128 swizzled bytes + four scale
+// chunks indexed by n.  The cells are the shared-memory image, so plain bulk copies load them; the
+// 128-byte swizzle lets the tensor core fetch operands at full shared-memory width (the unswizzled
+// layout measured 8x slower per instruction).  Every wait is bounded.
 #include "hx_common.cuh"
 #include "hx_gemm_tc.cuh"
+#include <stdlib.h>
 
 #define TC_WAIT_LIMIT (1u << 22)
 
@@ -48,10 +52,11 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 }
 // K-major, no swizzle: 8 rows x 16 bytes core matrices; lbo = byte distance between the two 16-byte
 // K halves, sbo = byte distance between 8-row groups.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo, uint32_t layout = 0) {
     return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) |
-           (1ull << 46);
+           (1ull << 46) | ((uint64_t)layout << 61);
 }
+#define SW128 2u
 __device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t desc) {
     asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" :: "r"(taddr), "l"(desc) : "memory");
 }
@@ -73,10 +78,12 @@ struct TcSmem {
 __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGemmTC g) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     TcSmem& S = *reinterpret_cast<TcSmem*>(smem_raw);
-    uint8_t* ring = smem_raw + 256;
+    // swizzled operands need 1024-byte aligned cells (the swizzle is a function of the shared-memory address)
+    uint8_t* ring = smem_raw + (((s_u32(smem_raw) + 256u + 1023u) & ~1023u) - s_u32(smem_raw));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NB = g.ncols, Sk = g.stage_ksteps;
-    const uint32_t a_cell = HX_T128_CELL, b_cell = (uint32_t)NB * 32u + 512u;
+    // a stage holds Sk K steps = Sk/4 cells of 256 columns
+    const uint32_t a_cell = HX_T128_CELL / 4, b_cell = ((uint32_t)NB * 128u + 2048u) / 4;   // bytes per K step
     const uint32_t stage_bytes = (uint32_t)Sk * (a_cell + b_cell);
     const int nstage_iters = (g.ksteps + Sk - 1) / Sk;
 
@@ -123,13 +130,18 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int ks0 = it * Sk, nk = min(Sk, g.ksteps - ks0);
                 const uint32_t sa = s_u32(ring + (size_t)slot * stage_bytes), sb = sa + (uint32_t)Sk * a_cell;
+                for (int rep = 0; rep < ((g.dbg & 8) ? 4 : 1); rep++)
                 for (int k = 0; k < nk; k++) {
                     const uint32_t ta = tmem + col_sfa + (slot * HX_TC_MAX_SK + k) * 4;
                     const uint32_t tb = tmem + col_sfb + (slot * HX_TC_MAX_SK + k) * 4;
-                    tc_cp_sf(ta, smem_desc(sa + k * a_cell + 4096, 16, 128));
-                    tc_cp_sf(tb, smem_desc(sb + k * b_cell + (uint32_t)NB * 32u, 16, 128));
-                    tc_mma(tmem, smem_desc(sa + k * a_cell, 2048, 128), smem_desc(sb + k * b_cell, (uint32_t)NB * 16u, 128), idesc, ta, tb,
-                           (it > 0 || k > 0) ? 1u : 0u);
+                    const uint32_t acell = sa + (uint32_t)(k >> 2) * HX_T128_CELL, bcell = sb + (uint32_t)(k >> 2) * ((uint32_t)NB * 128u + 2048u);
+                    const uint32_t e = (uint32_t)(k & 3);
+                    if (!(g.dbg & 1) || (it == 0 && k == 0)) {
+                        tc_cp_sf(ta, smem_desc(acell + 16384 + e * 512, 16, 128));
+                        tc_cp_sf(tb, smem_desc(bcell + (uint32_t)NB * 128u + e * 512, 16, 128));
+                    }
+                    tc_mma(tmem + ((g.dbg & 4) ? (uint32_t)(k & 3) * 64u : 0u), smem_desc(acell + e * 32, 16, 1024, SW128), smem_desc(bcell + e * 32, 16, 1024, SW128), idesc,
+                           (g.dbg & 2) ? tmem + col_sfa : ta, (g.dbg & 2) ? tmem + col_sfb : tb, (it > 0 || k > 0) ? 1u : 0u);
                 }
                 tc_commit(&S.empty[slot]);          // the slot is free once these MMAs have read it
             }
@@ -165,13 +177,13 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
 }  // namespace
 
 size_t hx_gemm_tc_smem(int ncols, int stage_ksteps) {
-    return 256 + (size_t)HX_TC_STAGES * stage_ksteps * (HX_T128_CELL + (size_t)ncols * 32 + 512);
+    return 2048 + (size_t)HX_TC_STAGES * (stage_ksteps / 4) * (HX_T128_CELL + (size_t)ncols * 128 + 2048);
 }
 
 int hx_gemm_tc_launch(const HxGemmTC& g, cudaStream_t st) {
     HX_CHECK_ARG(g.a && g.b && g.y && g.ntiles > 0 && g.ksteps > 0);
     HX_CHECK_ARG(g.ncols >= 8 && g.ncols <= 256 && g.ncols % 8 == 0);
-    HX_CHECK_ARG(g.stage_ksteps >= 1 && g.stage_ksteps <= HX_TC_MAX_SK);
+    HX_CHECK_ARG(g.stage_ksteps >= 4 && g.stage_ksteps <= HX_TC_MAX_SK && g.stage_ksteps % 4 == 0 && g.ksteps % 4 == 0);
     const size_t smem = hx_gemm_tc_smem(g.ncols, g.stage_ksteps);
     if (smem > 227 * 1024) return hx_fail(HX_ERR_ARG, "tensor-core GEMM stage too large (%zu bytes of shared memory)", smem);
     static bool attr = false;
@@ -186,7 +198,7 @@ int hx_gemm_tc_launch(const HxGemmTC& g, cudaStream_t st) {
 // C-ABI entry for tests and tools: all pointers are device pointers.
 HX_API int hx_gemm_nvfp4_tc(const uint8_t* a_t128, int rows, int K, const uint8_t* b_cells, int ncols, float* y,
                             int stage_ksteps, void* stream) {
-    HX_CHECK_ARG(rows > 0 && K > 0 && K % 64 == 0);
+    HX_CHECK_ARG(rows > 0 && K > 0 && K % 256 == 0);
     HxGemmTC g = {};
     g.a = a_t128; g.b = b_cells; g.y = y; g.rows = rows; g.ntiles = (rows + 127) / 128; g.ksteps = K / 64;
     g.ncols = ncols; g.stage_ksteps = stage_ksteps > 0 ? stage_ksteps : 4;
@@ -202,5 +214,34 @@ HX_API int hx_gemm_nvfp4_tc(const uint8_t* a_t128, int rows, int K, const uint8_
         else { cudaMemcpy(&e, derr, 4, cudaMemcpyDeviceToHost); if (e) rc = hx_fail(HX_ERR_TIMEOUT, "tensor-core GEMM: a bounded wait ran out"); }
     }
     cudaFree(derr);
+    return rc;
+}
+
+// Timing helper: `reps` back-to-back launches between two CUDA events (device pointers as above).
+HX_API int hx_gemm_nvfp4_tc_bench(const uint8_t* a_t128, int rows, int K, const uint8_t* b_cells, int ncols, float* y,
+                                  int stage_ksteps, int reps, float* ms_per_launch) {
+    HX_CHECK_ARG(rows > 0 && K > 0 && K % 256 == 0 && reps > 0 && ms_per_launch);
+    HxGemmTC g = {};
+    g.a = a_t128; g.b = b_cells; g.y = y; g.rows = rows; g.ntiles = (rows + 127) / 128; g.ksteps = K / 64;
+    g.ncols = ncols; g.stage_ksteps = stage_ksteps > 0 ? stage_ksteps : 4;
+    { const char* d = getenv("HX_TC_DBG"); g.dbg = d ? atoi(d) : 0; }
+    int* derr = nullptr;
+    HX_CUDA(cudaMalloc(&derr, 4));
+    HX_CUDA(cudaMemset(derr, 0, 4));
+    g.err = derr;
+    cudaEvent_t e0, e1;
+    HX_CUDA(cudaEventCreate(&e0)); HX_CUDA(cudaEventCreate(&e1));
+    int rc = hx_gemm_tc_launch(g, nullptr);
+    if (!rc) {
+        cudaEventRecord(e0, nullptr);
+        for (int i = 0; i < reps && !rc; i++) rc = hx_gemm_tc_launch(g, nullptr);
+        cudaEventRecord(e1, nullptr);
+        cudaError_t ce = cudaEventSynchronize(e1);
+        if (ce != cudaSuccess) rc = hx_fail(HX_ERR_CUDA, "tensor-core GEMM: %s", cudaGetErrorString(ce));
+        else { float t = 0; cudaEventElapsedTime(&t, e0, e1); *ms_per_launch = t / reps; }
+    }
+    int e = 0; cudaMemcpy(&e, derr, 4, cudaMemcpyDeviceToHost);
+    if (!rc && e) rc = hx_fail(HX_ERR_TIMEOUT, "tensor-core GEMM: a bounded wait ran out");
+    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaFree(derr);
     return rc;
 }

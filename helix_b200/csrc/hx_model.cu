@@ -13,6 +13,7 @@
 // well, so that the HXGW v3 image and its SHA-256 can be reproduced from the GPU.
 #include "hx_kernels.cuh"
 #include "hx_persist.cuh"
+#include "hx_gemm_tc.cuh"
 #include <fcntl.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -39,7 +40,8 @@ struct Fused {               // rows of one or more tensors in the dense decode 
     int N = 0, K = 0, Kd = 0;
     uint8_t* codes = nullptr; uint8_t* scales = nullptr;
     float ts[3] = {1.f, 1.f, 1.f}; int bound0 = 0, bound1 = 0;
-    uint8_t* t16 = nullptr; int KG = 0, ntiles = 0;      // tile layout for the persistent kernel
+    uint8_t* t16 = nullptr; int KG = 0, ntiles = 0;      // tile layout for the persistent kernel (mma.sync path)
+    uint8_t* t128 = nullptr; int ksteps = 0, tiles128 = 0;   // T128 cells for the tensor-core path
     size_t bytes() const { return (size_t)N * (Kd / 2 + Kd / 16); }
 };
 struct Layer {
@@ -72,6 +74,8 @@ struct hx_model {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     bool pdl = true;
     bool persist = true;                 // one cooperative kernel per token instead of the launch graph
+    bool want_t128 = true, use_tc = true; // linear phases on the tensor cores (tcgen05) inside the persistent kernel
+    float* tc_partial = nullptr; unsigned* tc_cnt = nullptr; int bdig_bytes = 0; size_t tc_units_max = 0; int tc_tiles_max = 0;
     HxPhase *ph_decode = nullptr, *ph_prefill = nullptr; int nph_decode = 0, nph_prefill = 0;
     unsigned long long* d_bar = nullptr; unsigned long long bar_count = 0; int* d_err = nullptr;
     int grid_persist = 0, dig_bytes = 0, nsplit_persist = 1;
@@ -104,6 +108,12 @@ int alloc_fused(hx_model* m, Fused& f, int N, int K) {
     f.KG = hx_t16_kgroups(K); f.ntiles = hx_t16_tiles(N);
     rc = dalloc(m, &f.t16, hx_t16_bytes(N, K)); if (rc) return rc;
     HX_CUDA(cudaMemsetAsync(f.t16, 0, hx_t16_bytes(N, K), m->st));
+    f.ksteps = 4 * ((K + 255) / 256); f.tiles128 = (N + 63) / 64;       // whole 256-column cells, 64-row tiles
+    if (m->want_t128) {
+        const size_t tb = (size_t)f.tiles128 * (f.ksteps / 4) * HX_T64_CELL;
+        rc = dalloc(m, &f.t128, tb); if (rc) return rc;
+        HX_CUDA(cudaMemsetAsync(f.t128, 0, tb, m->st));
+    }
     return HX_OK;
 }
 
@@ -166,6 +176,10 @@ void put_rows(hx_model* m, const Committed& c, Fused& f, int row_mul, int row_of
     // tile layout: plain offset, or gate/up interleaved tile by tile (16 rows of gate, 16 rows of up)
     if (row_mul == 1) hx_repack_t16(c.words, c.micro, c.rows, c.K, c.Kpad, f.t16, f.KG, 1, 1, row_off, m->st);
     else hx_repack_t16(c.words, c.micro, c.rows, c.K, c.Kpad, f.t16, f.KG, 16, row_mul, row_off, m->st);
+    if (f.t128) {   // gate/up: 64 gate rows then the matching 64 up rows per 128-row tile
+        if (row_mul == 1) hx_repack_t128(c.words, c.micro, c.rows, c.K, c.Kpad, f.t128, f.ksteps / 4, 1, 1, row_off, m->st);
+        else hx_repack_t128(c.words, c.micro, c.rows, c.K, c.Kpad, f.t128, f.ksteps / 4, 32, row_mul, row_off, m->st);
+    }
 }
 
 int build(hx_model* m, Source& s) {
@@ -213,6 +227,12 @@ int build(hx_model* m, Source& s) {
             if ((rc = alloc_fused(m, ly.qkv, QD + 2 * KVD, DM))) break;
             if ((rc = alloc_fused(m, ly.o, DM, QD))) break;
             if ((rc = alloc_fused(m, ly.gu, 2 * DFF, DM))) break;
+            if (m->want_t128 && (2 * DFF) % 64) {   // 32 gate + 32 up rows per tile: round the hidden size up to 32
+                ly.gu.tiles128 = (DFF + 31) / 32;
+                const size_t tb = (size_t)ly.gu.tiles128 * (ly.gu.ksteps / 4) * HX_T64_CELL;
+                if ((rc = dalloc(m, &ly.gu.t128, tb))) break;
+                HX_CUDA(cudaMemsetAsync(ly.gu.t128, 0, tb, m->st));
+            }
             if (DFF % 16) {   // tile-interleaved pairs need whole tiles for gate and for up
                 ly.gu.ntiles = 2 * hx_t16_tiles(DFF);
                 if ((rc = dalloc(m, &ly.gu.t16, (size_t)ly.gu.ntiles * ly.gu.KG * HX_T16_CELL))) break;
@@ -408,6 +428,13 @@ int build_phases(hx_model* m, bool from_prompt, bool with_head, HxPhase** out, i
     auto linear = [&](const Fused& f, const float* x, float* y, int epi, int N) {
         HxPhase p = {};
         p.type = HX_PH_LINEAR; p.w = f.t16; p.ntiles = f.ntiles; p.KG = f.KG; p.unit = (epi == HX_EPI_SWIGLU) ? 2 : 1;
+        if (m->use_tc) {
+            p.type = HX_PH_LINEAR_TC; p.w = f.t128; p.ntiles = f.tiles128; p.ksteps = f.ksteps;
+            p.pieces = 1;
+            if ((size_t)p.ntiles > m->tc_units_max) m->tc_units_max = (size_t)p.ntiles;
+            if (p.ntiles > m->tc_tiles_max) m->tc_tiles_max = p.ntiles;
+            if (p.ksteps * 512 > m->bdig_bytes) m->bdig_bytes = p.ksteps * 512;
+        }
         p.N = N; p.x = x; p.K = f.K; p.norm = HX_NORM_NONE; p.epi = epi; p.y = y;
         p.ts[0] = f.ts[0]; p.ts[1] = f.ts[1]; p.ts[2] = f.ts[2]; p.bound0 = f.bound0; p.bound1 = f.bound1;
         return p;
@@ -468,7 +495,13 @@ int init_persist(hx_model* m) {
     HX_CUDA(cudaMemset(m->d_err, 0, 16));
     m->bar_count = 0;
     if (getenv("HX_PERSIST_DBG")) { if ((rc = dalloc(m, &m->d_dbg, (size_t)16 * (m->nph_decode + 4)))) return rc; }
-    if (hx_persist_smem(m->dig_bytes) > 227 * 1024)
+    if (m->use_tc) {
+        if ((rc = dalloc(m, &m->tc_partial, m->tc_units_max * 128 + 128))) return rc;
+        if ((rc = dalloc(m, &m->tc_cnt, (size_t)m->tc_tiles_max + 8))) return rc;
+        HX_CUDA(cudaMemset(m->tc_cnt, 0, ((size_t)m->tc_tiles_max + 8) * 4));
+        if (hx_persist_tc_smem(m->bdig_bytes) > 227 * 1024)
+            return hx_fail(HX_ERR_ARG, "tensor-core decode: K too large for shared memory (%zu bytes)", hx_persist_tc_smem(m->bdig_bytes));
+    } else if (hx_persist_smem(m->dig_bytes) > 227 * 1024)
         return hx_fail(HX_ERR_ARG, "persistent decode: K too large for shared memory (%zu bytes)", hx_persist_smem(m->dig_bytes));
     return HX_OK;
 }
@@ -485,7 +518,9 @@ int persist_step(hx_model* m, bool from_prompt, bool with_head) {
     P.hist = m->d_hist; P.logits = m->logits; P.dig_bytes = m->dig_bytes;
     P.tok_by_pos = from_prompt ? 1 : 0; P.advance_pos = from_prompt ? 1 : 0;
     P.dbg = m->d_dbg;
+    P.tc_partial = m->tc_partial; P.tc_cnt = m->tc_cnt; P.bdig_bytes = m->bdig_bytes;
     m->bar_count += (unsigned long long)m->grid_persist * (unsigned long long)(P.nphases - 1);
+    if (m->use_tc) return hx_persist_tc_launch(P, m->grid_persist, m->st);
     return hx_persist_launch(P, m->grid_persist, m->st);
 }
 
@@ -505,8 +540,6 @@ int finish_init(hx_model* m) {
     int rc = alloc_state(m); if (rc) return rc;
     const char* np = getenv("HX_NO_PDL");
     m->pdl = !(np && *np == '1');
-    const char* dm = getenv("HX_DECODE");
-    m->persist = !(dm && strcmp(dm, "graph") == 0);
     if (m->persist) {
         rc = init_persist(m);
         if (rc) return rc;
@@ -569,6 +602,10 @@ HX_API int hx_model_synth(hx_model** out, const hx_config* cfg, uint64_t seed, i
     hx_model* m = new hx_model();
     m->cfg = *cfg; m->QD = cfg->n_heads * cfg->head_dim; m->KVD = cfg->n_kv_heads * cfg->head_dim;
     m->kv_cap = kv_cap; m->batch = batch; m->flags = flags;
+    { const char* dm = getenv("HX_DECODE"); const char* lm = getenv("HX_LINEAR");
+      m->persist = !(dm && strcmp(dm, "graph") == 0);
+      m->use_tc = m->persist && !(lm && strcmp(lm, "mma") == 0);
+      m->want_t128 = m->use_tc; }
     cudaError_t e = cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking);
     if (e != cudaSuccess) { delete m; return hx_fail(HX_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
     Source s; s.synth = true; s.seed = seed;
@@ -628,6 +665,10 @@ HX_API int hx_model_load(hx_model** out, const char* path, int kv_cap, int batch
         m = new hx_model();
         m->cfg = c; m->QD = c.n_heads * c.head_dim; m->KVD = c.n_kv_heads * c.head_dim;
         m->kv_cap = kv_cap; m->batch = batch; m->flags = flags;
+    { const char* dm = getenv("HX_DECODE"); const char* lm = getenv("HX_LINEAR");
+      m->persist = !(dm && strcmp(dm, "graph") == 0);
+      m->use_tc = m->persist && !(lm && strcmp(lm, "mma") == 0);
+      m->want_t128 = m->use_tc; }
         cudaError_t e = cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking);
         if (e != cudaSuccess) { rc = hx_fail(HX_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); break; }
         Source s; s.map = hb; s.maplen = len; s.desc = d;

@@ -15,16 +15,13 @@
 //
 // Every wait (mbarrier, grid barrier) is bounded: when it runs out the kernel records an error code
 // and all roles drain without touching the ring again.
-#include "hx_persist.cuh"
-#include "hx_kernels.cuh"
-#include <cuda_fp16.h>
-#include <cooperative_groups.h>
-#include <limits.h>
-
+#define RING_SLOTS HX_RING_SLOTS
 #define NCW 16                      // consumer warps (one k-group of a slot each)
 #define NCT (NCW * 32)              // consumer threads
 #define PT (NCT + 32)               // + one producer warp
 #define WAIT_LIMIT (1u << 24)
+#include "hx_persist.cuh"
+#include "hx_persist_common.cuh"
 
 // ------------------------------------------------------------------------------------------------
 // T16 repack
@@ -77,40 +74,6 @@ void hx_repack_t16(const int32_t* words, const uint8_t* micro, int rows, int K, 
     HX_COUNT_LAUNCH(1);
 }
 
-// ------------------------------------------------------------------------------------------------
-// PTX helpers
-// ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* b, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(b)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(b)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(b)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait; returns false (and latches *abort) when the limit is hit or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-        if (mbar_try(b, parity)) return true;
-        if ((i & 1023) == 1023 && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
-}
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 :: "r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" :: "n"(NCT) : "memory"); }
-
 __device__ __forceinline__ void cvt_e2m1x8(uint32_t w, uint32_t& h0, uint32_t& h1, uint32_t& h2, uint32_t& h3) {
     asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
         "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
@@ -135,14 +98,6 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ float pz_silu_mul(float g, float u) {
-    const float sgn = g < 0.0f ? -1.0f : 1.0f;
-    const float e = __expf(-(sgn * g));
-    const float th = sgn * ((1.0f - e) / (1.0f + e));
-    return g * (0.5f * (1.0f + th)) * u;
-}
-__device__ __forceinline__ bool pz_better(float av, int ai, float bv, int bi) { return av > bv || (av == bv && ai < bi); }
-
 // ------------------------------------------------------------------------------------------------
 // Work assignment, shared by the producer and the consumers so both walk the same slot sequence.
 // Linear phase: units (1 or 2 m-tiles) are dealt round-robin, unit u = cta + i*grid; a tile is cut
@@ -158,20 +113,6 @@ __device__ __forceinline__ LinPlan lin_plan(const HxPhase& ph, int cta, int grid
     p.kg_per = (ph.KG + p.nst - 1) / p.nst;
     return p;
 }
-struct AttPlan { int active, kv, split, t0, t1, n_old, rows_per_slot, nslots, has_new; };
-__device__ __forceinline__ AttPlan att_plan(const HxPhase& ph, int cta, int pos) {
-    AttPlan a;
-    a.active = cta < ph.NKV * ph.nsplit;
-    a.kv = cta / ph.nsplit; a.split = cta % ph.nsplit;
-    const int T = pos + 1, chunk = (T + ph.nsplit - 1) / ph.nsplit;
-    a.t0 = a.split * chunk; a.t1 = min(T, a.t0 + chunk);
-    if (!a.active || a.t0 >= a.t1) { a.t0 = a.t1 = 0; a.n_old = 0; a.has_new = 0; }
-    else { a.has_new = (pos >= a.t0 && pos < a.t1); a.n_old = (a.t1 - a.t0) - a.has_new; }
-    a.rows_per_slot = HX_RING_SLOT / (ph.DH * 4);
-    a.nslots = (a.n_old + a.rows_per_slot - 1) / a.rows_per_slot;      // K slots == V slots
-    return a;
-}
-
 struct Smem {
     uint64_t full[HX_RING_SLOTS];
     uint64_t empty[HX_RING_SLOTS];
@@ -184,208 +125,6 @@ struct Smem {
     volatile int abort_flag;
 };
 
-#define STAMP(i) do { if (P.dbg && cta == 0 && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg[pi * 16 + (i)] = _t; } } while (0)
-
-// ------------------------------------------------------------------------------------------------
-// Attention phase of one CTA: (kv head, split of the cached positions); the GRP query heads of the kv
-// head share the K and V rows.  Kept out of line and specialised per group size so that only the
-// variant in use occupies the instruction cache.
-// ------------------------------------------------------------------------------------------------
-template <int GRP>
-__device__ __noinline__ bool attention_phase(const HxPersist& P, const HxPhase& ph, Smem& S, uint8_t* ring, uint8_t* digb,
-                                             uint32_t& ctr, int pi, int pos) {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, cta = blockIdx.x;
-    const AttPlan ap = att_plan(ph, cta, pos);
-    const int DH = ph.DH, half = DH >> 1;
-    float* sq = reinterpret_cast<float*>(digb);                 // [GRP][DH] rotated queries
-    float* knew = sq + 8 * 256;                                  // [DH] current k (normed, rotated)
-    float* vnew = knew + 256;                                    // [DH]
-    float* sp = vnew + 256;                                      // [GRP][rows_per_slot + 1] scores / probabilities
-    float* accx = sp + 8 * 160;                                  // [nsub][GRP][DH] partial outputs
-    const int spitch = ap.rows_per_slot + 1;
-    const int nsub = NCT / DH;                                   // threads per output dimension
-    const int d = tid % DH, sub = tid / DH;
-    float acc[GRP];
-#pragma unroll
-    for (int i = 0; i < GRP; i++) acc[i] = 0.0f;
-    if (ap.active && ap.t1 > ap.t0) {
-        // q (GRP heads) and, where the current position falls in this split, k and v:
-        // per-head RMSNorm then rotate_half RoPE with table row pos (all loads of a lane first)
-        const int nvec = GRP + (ap.has_new ? 2 : 0);
-        #pragma unroll 1
-        for (int v = warp; v < nvec; v += NCW) {
-            const bool isq = v < GRP, isv = v == GRP + 1;
-            const float* src = isq ? ph.qkv + (size_t)(ap.kv * GRP + v) * DH
-                                   : ph.qkv + (size_t)ph.NH * DH + (size_t)(isv ? ph.NKV : 0) * DH + (size_t)ap.kv * DH;
-            const float* gg = isv ? nullptr : (isq ? ph.qn_g : ph.kn_g);
-            float* dst = isq ? sq + v * DH : (isv ? vnew : knew);
-            float xv[8];
-            float ssq = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 8; j++) { const int e = lane + 32 * j; xv[j] = e < DH ? __ldcg(src + e) : 0.0f; ssq = fmaf(xv[j], xv[j], ssq); }
-            ssq = hx_warp_sum(ssq);
-            const float inv = gg ? rsqrtf(ssq / (float)DH + ph.eps) : 1.0f;
-#pragma unroll
-            for (int j = 0; j < 8; j++) { const int e = lane + 32 * j; if (e < DH) dst[e] = gg ? gg[e] * (xv[j] * inv) : xv[j]; }
-            __syncwarp();
-            if (ph.cosT && !isv) {
-                for (int e = lane; e < half; e += 32) {
-                    const float lo = dst[e], hi = dst[e + half];
-                    const float cs = ph.cosT[(size_t)pos * half + e], sn = ph.sinT[(size_t)pos * half + e];
-                    dst[e] = lo * cs - hi * sn; dst[e + half] = hi * cs + lo * sn;
-                }
-            }
-        }
-        if (tid < 8) { S.att_m[tid] = -100000000.0f; S.att_l[tid] = 0.0f; }
-        consumer_sync();
-        STAMP(4);
-        if (ap.has_new) {        // append to the cache for the tokens to come
-            const size_t o = ((size_t)ap.kv * ph.cap + pos) * DH;
-            for (int e = tid; e < DH; e += NCT) { ph.kc[o + e] = knew[e]; ph.vc[o + e] = vnew[e]; }
-        }
-        const int ntile = ap.nslots + ((ap.has_new && ap.n_old % ap.rows_per_slot == 0) ? 1 : 0);
-        #pragma unroll 1
-        for (int s = 0; s < ntile; s++) {
-            const bool ring_tile = s < ap.nslots;
-            int nr = ring_tile ? min(ap.rows_per_slot, ap.n_old - s * ap.rows_per_slot) : 0;
-            // the current position rides on the last tile (room is guaranteed: spitch = rows + 1)
-            const bool add_new = ap.has_new && (s == ntile - 1);
-            uint32_t kslot = 0, vslot = 0;
-            const float* kt = nullptr; const float* vt = nullptr;
-            if (ring_tile) {
-                kslot = ctr % HX_RING_SLOTS; const uint32_t kround = ctr / HX_RING_SLOTS; ctr++;
-                if (!mbar_wait(&S.full[kslot], kround & 1, &S.abort_flag)) return false;
-                kt = reinterpret_cast<const float*>(ring + (size_t)kslot * HX_RING_SLOT);
-            }
-            if (s == 0) STAMP(8);
-            const int ntot = nr + (add_new ? 1 : 0);
-            // scores: a warp per position, lanes over the head dimension
-            #pragma unroll 1
-            for (int r = warp; r < ntot; r += NCW) {
-                const float* kr = (r < nr) ? kt + (size_t)r * DH : knew;
-                float dot[GRP];
-#pragma unroll
-                for (int i = 0; i < GRP; i++) dot[i] = 0.0f;
-                #pragma unroll 1
-                for (int e = lane * 4; e < DH; e += 128) {
-                    const float4 k4 = *reinterpret_cast<const float4*>(kr + e);
-#pragma unroll
-                    for (int i = 0; i < GRP; i++) {
-                        const float4 q4 = *reinterpret_cast<const float4*>(sq + i * DH + e);
-                        dot[i] = fmaf(q4.x, k4.x, dot[i]); dot[i] = fmaf(q4.y, k4.y, dot[i]);
-                        dot[i] = fmaf(q4.z, k4.z, dot[i]); dot[i] = fmaf(q4.w, k4.w, dot[i]);
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < GRP; i++) {
-                    const float sc = hx_warp_sum(dot[i]);
-                    if (lane == 0) sp[i * spitch + r] = sc * ph.scale;
-                }
-            }
-            __syncwarp();
-            if (ring_tile && lane == 0) mbar_arrive(&S.empty[kslot]);
-            consumer_sync();
-            if (s == 0) STAMP(9);
-            // online softmax state per head (fused_decode_attn_kernel.hx:74-102)
-            #pragma unroll 1
-            for (int i = warp; i < GRP; i += NCW) {
-                float tm = -INFINITY;
-                for (int r = lane; r < ntot; r += 32) tm = fmaxf(tm, sp[i * spitch + r]);
-                tm = hx_warp_max(tm);
-                const float mo = S.att_m[i], mn = fmaxf(mo, tm);
-                float ls = 0.0f;
-                for (int r = lane; r < ntot; r += 32) { const float pr = __expf(sp[i * spitch + r] - mn); sp[i * spitch + r] = pr; ls += pr; }
-                ls = hx_warp_sum(ls);
-                if (lane == 0) { const float rr = __expf(mo - mn); S.att_r[i] = rr; S.att_l[i] = S.att_l[i] * rr + ls; S.att_m[i] = mn; }
-            }
-            consumer_sync();
-            if (ring_tile) {
-                vslot = ctr % HX_RING_SLOTS; const uint32_t vround = ctr / HX_RING_SLOTS; ctr++;
-                if (!mbar_wait(&S.full[vslot], vround & 1, &S.abort_flag)) return false;
-                vt = reinterpret_cast<const float*>(ring + (size_t)vslot * HX_RING_SLOT);
-            }
-            if (s == 0) STAMP(10);
-#pragma unroll
-            for (int i = 0; i < GRP; i++) acc[i] *= S.att_r[i];
-            #pragma unroll 1
-            for (int r = sub; r < ntot; r += nsub) {
-                const float vv = (r < nr) ? vt[(size_t)r * DH + d] : vnew[d];
-#pragma unroll
-                for (int i = 0; i < GRP; i++) acc[i] = fmaf(sp[i * spitch + r], vv, acc[i]);
-            }
-            __syncwarp();
-            if (ring_tile && lane == 0) mbar_arrive(&S.empty[vslot]);
-            consumer_sync();
-        }
-        STAMP(5);
-        // fold the position subsets, write this split's partial
-#pragma unroll
-        for (int i = 0; i < GRP; i++) accx[(sub * 8 + i) * DH + d] = acc[i];
-        consumer_sync();
-        if (sub == 0) {
-#pragma unroll
-            for (int i = 0; i < GRP; i++) {
-                float v = 0.0f;
-                for (int u = 0; u < nsub; u++) v += accx[(u * 8 + i) * DH + d];
-                const size_t hs = (size_t)(ap.kv * GRP + i) * ph.nsplit + ap.split;
-                P.part_acc[hs * DH + d] = v;
-                if (d == 0) { P.part_m[hs] = S.att_m[i]; P.part_l[hs] = S.att_l[i]; }
-            }
-        }
-    } else if (ap.active) {
-        // empty split: neutral partial
-        for (int i = tid; i < GRP; i += NCT) {
-            const size_t hs = (size_t)(ap.kv * GRP + i) * ph.nsplit + ap.split;
-            P.part_m[hs] = -100000000.0f; P.part_l[hs] = 0.0f;
-        }
-        for (int i = tid; i < GRP * DH; i += NCT) {
-            const size_t hs = (size_t)(ap.kv * GRP + i / DH) * ph.nsplit + ap.split;
-            P.part_acc[hs * DH + i % DH] = 0.0f;
-        }
-    }
-    if (ap.active) {
-        STAMP(6);
-        __threadfence();
-        consumer_sync();
-        if (tid == 0) S.ticket = atomicAdd(P.attn_cnt + ap.kv, 1u);
-        consumer_sync();
-        STAMP(7);
-        if (S.ticket == (unsigned)ph.nsplit - 1) {
-            __threadfence();
-            // merge of the splits: weights w_s = exp(m_s - M) / sum_s l_s exp(m_s - M), then one pass
-            // of independent loads over the partial outputs
-            float* wgt = sp;                                   // [GRP][nsplit]
-            const size_t hbase = (size_t)(ap.kv * GRP) * ph.nsplit;
-            #pragma unroll 1
-            for (int i = warp; i < GRP; i += NCW) {
-                float mv[2], lv[2];
-#pragma unroll
-                for (int j = 0; j < 2; j++) {
-                    const int sidx = lane + 32 * j;
-                    mv[j] = sidx < ph.nsplit ? __ldcg(P.part_m + hbase + (size_t)i * ph.nsplit + sidx) : -INFINITY;
-                    lv[j] = sidx < ph.nsplit ? __ldcg(P.part_l + hbase + (size_t)i * ph.nsplit + sidx) : 0.0f;
-                }
-                const float M = hx_warp_max(fmaxf(mv[0], mv[1]));
-                const float w0 = __expf(mv[0] - M), w1 = __expf(mv[1] - M);
-                const float Lsum = hx_warp_sum(lv[0] * w0 + lv[1] * w1);
-                if (lane < ph.nsplit) wgt[i * ph.nsplit + lane] = w0 / Lsum;
-                if (lane + 32 < ph.nsplit) wgt[i * ph.nsplit + lane + 32] = w1 / Lsum;
-            }
-            consumer_sync();
-            #pragma unroll 1
-            for (int o = tid; o < GRP * DH; o += NCT) {
-                const int i = o / DH, dd = o % DH;
-                const float* pa = P.part_acc + (hbase + (size_t)i * ph.nsplit) * DH + dd;
-                float ov = 0.0f;
-#pragma unroll 6
-                for (int sidx = 0; sidx < ph.nsplit; sidx++) ov = fmaf(__ldcg(pa + (size_t)sidx * DH), wgt[i * ph.nsplit + sidx], ov);
-                ph.ctx[(size_t)(ap.kv * GRP + i) * DH + dd] = ov;
-            }
-            if (tid == 0) P.attn_cnt[ap.kv] = 0u;
-        }
-    }
-    return true;
-}
 
 __global__ void __launch_bounds__(PT, 1) k_decode_persist(const __grid_constant__ HxPersist P) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -674,14 +413,14 @@ __global__ void __launch_bounds__(PT, 1) k_decode_persist(const __grid_constant_
             // ------------------------------- attention -------------------------------
             bool ok;
             switch (ph.NH / ph.NKV) {
-                case 1: ok = attention_phase<1>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                case 2: ok = attention_phase<2>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                case 3: ok = attention_phase<3>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                case 4: ok = attention_phase<4>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                case 5: ok = attention_phase<5>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                case 6: ok = attention_phase<6>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                case 7: ok = attention_phase<7>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                default: ok = attention_phase<8>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                case 1: ok = attention_phase<1, NCW>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                case 2: ok = attention_phase<2, NCW>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                case 3: ok = attention_phase<3, NCW>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                case 4: ok = attention_phase<4, NCW>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                case 5: ok = attention_phase<5, NCW>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                case 6: ok = attention_phase<6, NCW>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                case 7: ok = attention_phase<7, NCW>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                default: ok = attention_phase<8, NCW>(P, ph, S, ring, digb, ctr, pi, pos); break;
             }
             if (!ok) goto aborted;
         }

@@ -14,6 +14,7 @@
 #define HX_T16_ROWS 16
 #define HX_T16_KG 128
 #define HX_T16_CELL 1152
+#define HX_T64_CELL 9216            // tensor-core decode layout: (64-row tile, four 64-column steps) = 8192 B swizzled codes + 2 x 512 B scales
 #define HX_SLOT_CELLS 16           // k-groups per ring slot = consumer warps
 #define HX_RING_SLOT (HX_SLOT_CELLS * HX_T16_CELL)    // 18432 B; also 36 cache rows of 128 floats
 #define HX_RING_SLOTS 7
@@ -27,7 +28,7 @@ static inline size_t hx_t16_bytes(int N, int K) { return (size_t)hx_t16_tiles(N)
 void hx_repack_t16(const int32_t* words, const uint8_t* micro, int rows, int K, int Kpad, uint8_t* dst,
                    int dstKG, int grp, int row_mul, int row_off, cudaStream_t st);
 
-enum { HX_PH_LINEAR = 0, HX_PH_ATTN = 1 };
+enum { HX_PH_LINEAR = 0, HX_PH_ATTN = 1, HX_PH_LINEAR_TC = 2 };
 
 struct HxPhase {
     int type;
@@ -46,6 +47,9 @@ struct HxPhase {
     int epi;                  // HX_EPI_STORE / RESID / SWIGLU / ARGMAX
     float* y;
     float ts[3]; int bound0, bound1;
+    // ---- linear on the tensor cores (HX_PH_LINEAR_TC): w = T128 cells, ntiles = 128-row tiles ----
+    int ksteps;               // 64-column steps per row
+    int pieces;               // split of K over work units; partial sums are merged in a fixed order
     // ---- attention ----
     const float* qkv; const float* qn_g; const float* kn_g; const float* cosT; const float* sinT;
     float* kc; float* vc; float* ctx;
@@ -66,7 +70,14 @@ struct HxPersist {
     int tok_by_pos;                       // the input token is tok[pos] (prompt) instead of tok[0]
     int advance_pos;                      // no head in this launch: CTA 0 advances *pos_inc at the end
     unsigned long long* dbg;              // optional: CTA 0 writes 4 globaltimer stamps per phase
+    float* tc_partial; unsigned* tc_cnt;  // split-K scratch of the tensor-core linear phases
+    int bdig_bytes;                       // shared-memory bytes for the digit columns of x (tensor-core path)
 };
 
 int hx_persist_launch(const HxPersist& p, int grid, cudaStream_t st);
+int hx_persist_tc_launch(const HxPersist& p, int grid, cudaStream_t st);
+size_t hx_persist_tc_smem(int bdig_bytes);
+// committed layout -> T128 cells (see hx_gemm_tc.cu); destination row = (r/grp)*grp*row_mul + row_off*grp + r%grp
+void hx_repack_t128(const int32_t* words, const uint8_t* micro, int rows, int K, int Kpad, uint8_t* dst,
+                    int dst_kgroups, int grp, int row_mul, int row_off, cudaStream_t st);
 size_t hx_persist_smem(int dig_bytes);

@@ -80,6 +80,7 @@ _SIGS = {
     "hx_repack_d16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "hx_gemv_d16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "hx_gemm_nvfp4_tc": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "hx_gemm_nvfp4_tc_bench": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "hx_sha256": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
     "hx_sha256_hex": (C.c_int, [C.c_void_p, C.c_size_t, C.c_char_p]),
     "hx_sha256_file": (C.c_int, [C.c_char_p, C.c_char_p]),

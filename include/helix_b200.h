@@ -116,6 +116,9 @@ int hx_gemv_d16(const float* x, const uint8_t* codes, const uint8_t* scales, con
  * forward_layer_llama (gpt2_infer.c:1231-1287) for batched prefill.  Synchronous. */
 int hx_gemm_nvfp4_tc(const uint8_t* a_t128, int rows, int K, const uint8_t* b_cells, int ncols, float* y,
                      int stage_ksteps, void* stream);
+/* Same GEMM launched `reps` times between two CUDA events; *ms_per_launch receives the device time. */
+int hx_gemm_nvfp4_tc_bench(const uint8_t* a_t128, int rows, int K, const uint8_t* b_cells, int ncols, float* y,
+                           int stage_ksteps, int reps, float* ms_per_launch);
 
 /* ---------------------------------------------------------------- SHA-256 / receipt ----------- */
 /* FIPS 180-4.  Replaces sha256 / sha256_hex / sha256_file, gpt2_infer.c:137-213. */
