@@ -75,7 +75,7 @@ struct hx_model {
     bool pdl = true;
     bool persist = true;                 // one cooperative kernel per token instead of the launch graph
     bool want_t128 = true, use_tc = true; // linear phases on the tensor cores (tcgen05) inside the persistent kernel
-    float* tc_partial = nullptr; unsigned* tc_cnt = nullptr; int bdig_bytes = 0; size_t tc_units_max = 0; int tc_tiles_max = 0;
+    float* tc_partial = nullptr; unsigned* tc_cnt = nullptr; int bdig_bytes = 0, tc_ring = 0; size_t tc_units_max = 0; int tc_tiles_max = 0;
     HxPhase *ph_decode = nullptr, *ph_prefill = nullptr; int nph_decode = 0, nph_prefill = 0;
     unsigned long long* d_bar = nullptr; unsigned long long bar_count = 0; int* d_err = nullptr;
     int grid_persist = 0, dig_bytes = 0, nsplit_persist = 1;
@@ -108,9 +108,9 @@ int alloc_fused(hx_model* m, Fused& f, int N, int K) {
     f.KG = hx_t16_kgroups(K); f.ntiles = hx_t16_tiles(N);
     rc = dalloc(m, &f.t16, hx_t16_bytes(N, K)); if (rc) return rc;
     HX_CUDA(cudaMemsetAsync(f.t16, 0, hx_t16_bytes(N, K), m->st));
-    f.ksteps = 4 * ((K + 255) / 256); f.tiles128 = (N + 63) / 64;       // whole 256-column cells, 64-row tiles
+    f.ksteps = 4 * ((K + 255) / 256); f.tiles128 = (N + 127) / 128;     // whole 256-column cells, 128-row tiles
     if (m->want_t128) {
-        const size_t tb = (size_t)f.tiles128 * (f.ksteps / 4) * HX_T64_CELL;
+        const size_t tb = (size_t)f.tiles128 * (f.ksteps / 4) * HX_T128_CELL;
         rc = dalloc(m, &f.t128, tb); if (rc) return rc;
         HX_CUDA(cudaMemsetAsync(f.t128, 0, tb, m->st));
     }
@@ -178,7 +178,7 @@ void put_rows(hx_model* m, const Committed& c, Fused& f, int row_mul, int row_of
     else hx_repack_t16(c.words, c.micro, c.rows, c.K, c.Kpad, f.t16, f.KG, 16, row_mul, row_off, m->st);
     if (f.t128) {   // gate/up: 64 gate rows then the matching 64 up rows per 128-row tile
         if (row_mul == 1) hx_repack_t128(c.words, c.micro, c.rows, c.K, c.Kpad, f.t128, f.ksteps / 4, 1, 1, row_off, m->st);
-        else hx_repack_t128(c.words, c.micro, c.rows, c.K, c.Kpad, f.t128, f.ksteps / 4, 32, row_mul, row_off, m->st);
+        else hx_repack_t128(c.words, c.micro, c.rows, c.K, c.Kpad, f.t128, f.ksteps / 4, 64, row_mul, row_off, m->st);
     }
 }
 
@@ -227,12 +227,6 @@ int build(hx_model* m, Source& s) {
             if ((rc = alloc_fused(m, ly.qkv, QD + 2 * KVD, DM))) break;
             if ((rc = alloc_fused(m, ly.o, DM, QD))) break;
             if ((rc = alloc_fused(m, ly.gu, 2 * DFF, DM))) break;
-            if (m->want_t128 && (2 * DFF) % 64) {   // 32 gate + 32 up rows per tile: round the hidden size up to 32
-                ly.gu.tiles128 = (DFF + 31) / 32;
-                const size_t tb = (size_t)ly.gu.tiles128 * (ly.gu.ksteps / 4) * HX_T64_CELL;
-                if ((rc = dalloc(m, &ly.gu.t128, tb))) break;
-                HX_CUDA(cudaMemsetAsync(ly.gu.t128, 0, tb, m->st));
-            }
             if (DFF % 16) {   // tile-interleaved pairs need whole tiles for gate and for up
                 ly.gu.ntiles = 2 * hx_t16_tiles(DFF);
                 if ((rc = dalloc(m, &ly.gu.t16, (size_t)ly.gu.ntiles * ly.gu.KG * HX_T16_CELL))) break;
@@ -430,10 +424,12 @@ int build_phases(hx_model* m, bool from_prompt, bool with_head, HxPhase** out, i
         p.type = HX_PH_LINEAR; p.w = f.t16; p.ntiles = f.ntiles; p.KG = f.KG; p.unit = (epi == HX_EPI_SWIGLU) ? 2 : 1;
         if (m->use_tc) {
             p.type = HX_PH_LINEAR_TC; p.w = f.t128; p.ntiles = f.tiles128; p.ksteps = f.ksteps;
-            p.pieces = 1;
-            if ((size_t)p.ntiles > m->tc_units_max) m->tc_units_max = (size_t)p.ntiles;
+            int maxp = 1, maxrun = 1;
+            hx_tc_split(p.ntiles, p.ksteps / 4, m->grid_persist, &maxp, &maxrun);
+            p.pieces = maxp;
+            if ((size_t)p.ntiles * maxp > m->tc_units_max) m->tc_units_max = (size_t)p.ntiles * maxp;
             if (p.ntiles > m->tc_tiles_max) m->tc_tiles_max = p.ntiles;
-            if (p.ksteps * 512 > m->bdig_bytes) m->bdig_bytes = p.ksteps * 512;
+            if (maxrun * 2048 > m->bdig_bytes) m->bdig_bytes = maxrun * 2048;
         }
         p.N = N; p.x = x; p.K = f.K; p.norm = HX_NORM_NONE; p.epi = epi; p.y = y;
         p.ts[0] = f.ts[0]; p.ts[1] = f.ts[1]; p.ts[2] = f.ts[2]; p.bound0 = f.bound0; p.bound1 = f.bound1;
@@ -499,8 +495,10 @@ int init_persist(hx_model* m) {
         if ((rc = dalloc(m, &m->tc_partial, m->tc_units_max * 128 + 128))) return rc;
         if ((rc = dalloc(m, &m->tc_cnt, (size_t)m->tc_tiles_max + 8))) return rc;
         HX_CUDA(cudaMemset(m->tc_cnt, 0, ((size_t)m->tc_tiles_max + 8) * 4));
-        if (hx_persist_tc_smem(m->bdig_bytes) > 227 * 1024)
-            return hx_fail(HX_ERR_ARG, "tensor-core decode: K too large for shared memory (%zu bytes)", hx_persist_tc_smem(m->bdig_bytes));
+        m->tc_ring = hx_persist_tc_ring(m->bdig_bytes);
+        if (const char* e = getenv("HX_TC_RING")) { const int r = atoi(e); if (r >= 3 && r < m->tc_ring) m->tc_ring = r; }
+        if (m->tc_ring < 3)
+            return hx_fail(HX_ERR_ARG, "tensor-core decode: K too large for shared memory (%zu bytes besides the ring)", hx_persist_tc_smem(m->bdig_bytes));
     } else if (hx_persist_smem(m->dig_bytes) > 227 * 1024)
         return hx_fail(HX_ERR_ARG, "persistent decode: K too large for shared memory (%zu bytes)", hx_persist_smem(m->dig_bytes));
     return HX_OK;
@@ -518,7 +516,7 @@ int persist_step(hx_model* m, bool from_prompt, bool with_head) {
     P.hist = m->d_hist; P.logits = m->logits; P.dig_bytes = m->dig_bytes;
     P.tok_by_pos = from_prompt ? 1 : 0; P.advance_pos = from_prompt ? 1 : 0;
     P.dbg = m->d_dbg;
-    P.tc_partial = m->tc_partial; P.tc_cnt = m->tc_cnt; P.bdig_bytes = m->bdig_bytes;
+    P.tc_partial = m->tc_partial; P.tc_cnt = m->tc_cnt; P.bdig_bytes = m->bdig_bytes; P.tc_ring = m->tc_ring;
     m->bar_count += (unsigned long long)m->grid_persist * (unsigned long long)(P.nphases - 1);
     if (m->use_tc) return hx_persist_tc_launch(P, m->grid_persist, m->st);
     return hx_persist_launch(P, m->grid_persist, m->st);

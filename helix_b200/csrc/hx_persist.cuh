@@ -14,7 +14,6 @@
 #define HX_T16_ROWS 16
 #define HX_T16_KG 128
 #define HX_T16_CELL 1152
-#define HX_T64_CELL 9216            // tensor-core decode layout: (64-row tile, four 64-column steps) = 8192 B swizzled codes + 2 x 512 B scales
 #define HX_SLOT_CELLS 16           // k-groups per ring slot = consumer warps
 #define HX_RING_SLOT (HX_SLOT_CELLS * HX_T16_CELL)    // 18432 B; also 36 cache rows of 128 floats
 #define HX_RING_SLOTS 7
@@ -48,8 +47,8 @@ struct HxPhase {
     float* y;
     float ts[3]; int bound0, bound1;
     // ---- linear on the tensor cores (HX_PH_LINEAR_TC): w = T128 cells, ntiles = 128-row tiles ----
-    int ksteps;               // 64-column steps per row
-    int pieces;               // split of K over work units; partial sums are merged in a fixed order
+    int ksteps;               // 64-column steps per row (a multiple of 4: whole 256-column cells)
+    int pieces;               // most pieces a tile is cut into = stride of its partial sums in tc_partial
     // ---- attention ----
     const float* qkv; const float* qn_g; const float* kn_g; const float* cosT; const float* sinT;
     float* kc; float* vc; float* ctx;
@@ -72,12 +71,16 @@ struct HxPersist {
     unsigned long long* dbg;              // optional: CTA 0 writes 4 globaltimer stamps per phase
     float* tc_partial; unsigned* tc_cnt;  // split-K scratch of the tensor-core linear phases
     int bdig_bytes;                       // shared-memory bytes for the digit columns of x (tensor-core path)
+    int tc_ring;                          // ring depth of the tensor-core kernel (3..10 slots)
 };
 
 int hx_persist_launch(const HxPersist& p, int grid, cudaStream_t st);
 int hx_persist_tc_launch(const HxPersist& p, int grid, cudaStream_t st);
-size_t hx_persist_tc_smem(int bdig_bytes);
-// committed layout -> T128 cells (see hx_gemm_tc.cu); destination row = (r/grp)*grp*row_mul + row_off*grp + r%grp
+size_t hx_persist_tc_smem(int bdig_bytes);            // shared memory besides the ring
+int hx_persist_tc_ring(int bdig_bytes);               // ring depth that fits (0: the digit columns do not fit)
+// how the tensor-core kernel cuts ntiles x kcells cells over `grid` CTAs: most pieces of one tile, most K cells of one CTA
+void hx_tc_split(int ntiles, int kcells, int grid, int* max_pieces, int* max_run);
+// committed layout -> T128 cells (hx_persist_tc.cu); destination row = (r/grp)*grp*row_mul + row_off*grp + r%grp
 void hx_repack_t128(const int32_t* words, const uint8_t* micro, int rows, int K, int Kpad, uint8_t* dst,
-                    int dst_kgroups, int grp, int row_mul, int row_off, cudaStream_t st);
+                    int kcells, int grp, int row_mul, int row_off, cudaStream_t st);
 size_t hx_persist_smem(int dig_bytes);

@@ -3,8 +3,8 @@
 // Same structure as hx_persist.cu (one cooperative CTA per SM, phases separated by a grid barrier, a
 // producer thread streaming weights and KV rows through a shared-memory ring with cp.async.bulk that
 // runs ahead of the barriers), but the weights are never touched by a CUDA core: the ring holds
-// "T128" cells (128 rows x 64 columns of E2M1 codes + their UE4M3 scales, hx_gemm_tc.cu) and a
-// dedicated warp feeds them to tcgen05.mma kind::mxf4nvf4 with the accumulator in TMEM.
+// "T128" cells (128 rows x 256 columns of E2M1 codes + their UE4M3 scales, hx_gemm_tc.cuh) and a
+// dedicated thread feeds them to tcgen05.mma kind::mxf4nvf4 with the accumulator in TMEM.
 //
 // The f32 activation vector is made exact for the FP4 tensor path by digit slicing: after the
 // (optional) RMSNorm, x = Sg * sum_j (d_j/2) 4^-j with sixteen base-4 digits d_j in {0..3} carrying the
@@ -13,10 +13,13 @@
 // epilogue recombines y = Sg*ts * sum_j 4^-j D_j.  32 bits below the vector's largest magnitude are
 // kept, the products and the f32 accumulation in TMEM are exact for these operands.
 //
-// Work units are (128-row tile, K piece) so that every SM streams a similar number of bytes; the
-// partial sums of a tile are merged in piece order by the last unit to finish (ticket, no waiting), so
-// results do not depend on timing.
-#define RING_SLOTS 6
+// Work split of a linear phase: the cells of the weight, in storage order (tile-major, K-minor), are cut
+// into gridDim equal contiguous runs, so every SM streams the same number of bytes as one linear read.
+// A run covers the tail of one tile, whole tiles, and the head of another; each piece of a tile yields a
+// partial sum of 128 rows, and the last piece of a tile to finish (ticket, nobody waits) adds the pieces
+// in K order and applies the epilogue, so results do not depend on timing.
+#define HX_TC_MAX_RING 10
+#define RING_SLOTS ((uint32_t)P.tc_ring)
 #define NCW 16
 #define NCT (NCW * 32)
 #define PT (NCT + 64)               // + producer warp (16) + MMA warp (17)
@@ -25,23 +28,23 @@
 #include "hx_persist_common.cuh"
 #include "hx_gemm_tc.cuh"
 
-#define SLOT_CELLS 2                // cells per ring slot (2 * 9216 = 18432 = HX_RING_SLOT): 8 steps of 64 columns
 #define TC_NDIG 16
 #define TM_COLS 256
 #define TM_D0 0                     // two accumulators of TC_NDIG columns
 #define TM_SFB 32                   // constant unit scales for the digit columns
-#define TM_SFA 64                   // + slot * 16 + (cell * 2 + step pair) * 4
+#define TM_SFA 64                   // + slot * 16 + K step * 4
+#define EPI_WARPS 4                 // warps 0..3 own TMEM lanes 0..127 = the rows of a tile
 
 // ------------------------------------------------------------------------------------------------
-// committed layout -> T64 cells
+// committed layout -> T128 cells
 // ------------------------------------------------------------------------------------------------
-// "T64" cells: per (64-row tile, group of 256 columns = four K steps) 9216 bytes: 64 rows x 128 bytes of
-// codes in the K-major 128-byte-swizzle operand layout (row r at r*128, its 16-byte chunk j at position
-// j ^ (r & 7)), then two 512-byte scale chunks, one per pair of K steps: inside a chunk the even step uses
-// the slots of rows 0..63 and the odd step those of rows 64..127 (byte (rho%32)*16 + (rho/32)*4 + blk,
-// rho = row + 64*(step&1)).  Same density as the committed information: 0.5625 B per weight.
+// One cell per (128-row tile, group of 256 columns = four K steps of the MMA), HX_T128_CELL = 18432 bytes:
+// 128 rows x 128 bytes of codes in the K-major 128-byte-swizzle operand layout (row r at r*128, its
+// 16-byte chunk j at position j ^ (r & 7)), then four 512-byte scale chunks, one per K step, in the
+// 32x128b layout tcgen05.cp expects (byte (r%32)*16 + (r/32)*4 + blk).  0.5625 B per weight, the density
+// of the committed data.  Cells of a tile are contiguous in K, tiles follow one another.
 __global__ void __launch_bounds__(256) k_repack_t128(const int32_t* __restrict__ words, const uint8_t* __restrict__ micro,
-                                                      int rows, int K, int Kpad, uint8_t* __restrict__ dst, int dst_kgroups,
+                                                      int rows, int K, int Kpad, uint8_t* __restrict__ dst, int kcells,
                                                       int grp, int row_mul, int row_off) {
     const int kwords = Kpad / 7, kblk = Kpad / 16, ksteps = (K + 63) / 64;
     const size_t items = (size_t)rows * ksteps * 2;
@@ -59,8 +62,8 @@ __global__ void __launch_bounds__(256) k_repack_t128(const int32_t* __restrict__
             if (e < K) { const int wd = e / 7, s = e - wd * 7; code = ((uint32_t)wr[wd] >> (4 * s)) & 15u; }
             out[j >> 3] |= code << (4 * (j & 7));
         }
-        uint8_t* cell = dst + ((size_t)(dr / 64) * dst_kgroups + (ks >> 2)) * HX_T64_CELL;
-        const int rl = dr % 64, chunk = (ks & 3) * 2 + c;
+        uint8_t* cell = dst + ((size_t)(dr / 128) * kcells + (ks >> 2)) * HX_T128_CELL;
+        const int rl = dr % 128, chunk = (ks & 3) * 2 + c;
         *reinterpret_cast<uint4*>(cell + rl * 128 + ((chunk ^ (rl & 7)) * 16)) = make_uint4(out[0], out[1], out[2], out[3]);
         if (c == 0) {
             uint32_t sv = 0u;
@@ -70,18 +73,34 @@ __global__ void __launch_bounds__(256) k_repack_t128(const int32_t* __restrict__
                 const uint32_t v = (blk * 16 < K && blk < kblk) ? micro[(size_t)r * kblk + blk] : 0u;
                 sv |= v << (8 * b);
             }
-            const int rho = rl + 64 * (ks & 1);
-            *reinterpret_cast<uint32_t*>(cell + 8192 + ((ks >> 1) & 1) * 512 + (rho % 32) * 16 + (rho / 32) * 4) = sv;
+            *reinterpret_cast<uint32_t*>(cell + 16384 + (ks & 3) * 512 + (rl % 32) * 16 + (rl / 32) * 4) = sv;
         }
     }
 }
 
 void hx_repack_t128(const int32_t* words, const uint8_t* micro, int rows, int K, int Kpad, uint8_t* dst,
-                    int dst_kgroups, int grp, int row_mul, int row_off, cudaStream_t st) {
+                    int kcells, int grp, int row_mul, int row_off, cudaStream_t st) {
     const size_t items = (size_t)rows * ((K + 63) / 64) * 2;
     int g = (int)((items + 255) / 256); if (g > 148 * 16) g = 148 * 16; if (g < 1) g = 1;
-    k_repack_t128<<<g, 256, 0, st>>>(words, micro, rows, K, Kpad, dst, dst_kgroups, grp, row_mul, row_off);
+    k_repack_t128<<<g, 256, 0, st>>>(words, micro, rows, K, Kpad, dst, kcells, grp, row_mul, row_off);
     HX_COUNT_LAUNCH(1);
+}
+
+// The run of cells of CTA `cta` in a phase of ntiles x C cells, and how a tile is cut into pieces.
+void hx_tc_split(int ntiles, int C, int grid, int* max_pieces, int* max_run) {
+    const long long total = (long long)ntiles * C;
+    if (total < grid) grid = (int)total;          // fewer cells than CTAs: the first `total` CTAs take one cell each
+    int mp = 1, mr = 1;
+    for (int c = 0; c < grid; c++) {
+        const long long b0 = c * total / grid, b1 = (c + 1) * total / grid;
+        if (b1 - b0 > mr) mr = (int)(b1 - b0);
+    }
+    for (int t = 0; t < ntiles; t++) {
+        const long long x0 = (long long)t * C, x1 = x0 + C - 1;
+        const int c0 = (int)(((x0 + 1) * grid + total - 1) / total) - 1, c1 = (int)(((x1 + 1) * grid + total - 1) / total) - 1;
+        if (c1 - c0 + 1 > mp) mp = c1 - c0 + 1;
+    }
+    *max_pieces = mp; *max_run = mr < C ? mr : C;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -103,22 +122,29 @@ __device__ __forceinline__ void tc_mma(uint32_t d, uint64_t a, uint64_t b, uint3
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 2, 64;" ::: "memory"); }
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 2, %0;" :: "n"(EPI_WARPS * 32) : "memory"); }
 
-// Units of a tensor-core linear phase: 64-row tiles over the whole K, dealt round-robin to the CTAs.
-// A unit streams kpairs pair-cells, SLOT_CELLS per ring slot.
-struct TcPlan { int nunits, kpairs, nslots; };   // kpairs counts 256-column cells
+// This CTA's run of cells [b0, b1) of the phase; k0 = K cell of the first one; run = distinct K cells it touches.
+// With fewer cells than CTAs the first `total` CTAs take one cell each (geff = CTAs that hold cells).
+struct TcPlan { long long b0, b1, total; int C, k0, run, geff; };
 __device__ __forceinline__ TcPlan tc_plan(const HxPhase& ph, int cta, int grid) {
     TcPlan p;
-    p.nunits = cta < ph.ntiles ? (ph.ntiles - cta + grid - 1) / grid : 0;
-    p.kpairs = ph.ksteps >> 2;
-    p.nslots = (p.kpairs + SLOT_CELLS - 1) / SLOT_CELLS;
+    p.C = ph.ksteps >> 2;
+    p.total = (long long)ph.ntiles * p.C;
+    p.geff = p.total < grid ? (int)p.total : grid;
+    if (cta < p.geff) { p.b0 = (long long)cta * p.total / p.geff; p.b1 = (long long)(cta + 1) * p.total / p.geff; }
+    else { p.b0 = p.b1 = 0; }
+    p.k0 = (int)(p.b0 % p.C);
+    const long long n = p.b1 - p.b0;
+    p.run = n < p.C ? (int)n : p.C;
     return p;
 }
+// CTA whose run holds cell x
+__device__ __forceinline__ int tc_owner(long long x, long long total, int grid) { return (int)(((x + 1) * grid + total - 1) / total) - 1; }
 
 struct SmemTc {
-    uint64_t full[RING_SLOTS];
-    uint64_t empty[RING_SLOTS];
+    uint64_t full[HX_TC_MAX_RING];
+    uint64_t empty[HX_TC_MAX_RING];
     uint64_t acc_full[2], acc_empty[2], b_ready;
     float red[NCW * 2];
     float att_m[8], att_l[8], att_r[8];
@@ -133,17 +159,18 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
     extern __shared__ __align__(128) uint8_t smem_raw[];
     SmemTc& S = *reinterpret_cast<SmemTc*>(smem_raw);
     // swizzled operands need 1024-byte aligned cells (the swizzle is a function of the shared-memory address)
+    uint8_t* sfb1 = smem_raw + ((sizeof(SmemTc) + 15) & ~(size_t)15);    // 512 bytes of 0x38 (scale 1.0)
     uint8_t* ring = smem_raw + (((smem_u32(smem_raw) + (uint32_t)sizeof(SmemTc) + 16u + 512u + 1023u) & ~1023u) - smem_u32(smem_raw));
-    uint8_t* digb = ring + (size_t)RING_SLOTS * HX_RING_SLOT;            // digit columns / attention scratch (1024-aligned)
-    uint8_t* sfb1 = smem_raw + ((sizeof(SmemTc) + 15) & ~(size_t)15);    // 512 bytes of 0x38 (scale 1.0), ahead of the ring
+    uint8_t* digb = ring + (size_t)P.tc_ring * HX_RING_SLOT;              // digit columns / attention scratch (1024-aligned)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x, grid = gridDim.x;
     const int pos = *P.pos;
+    const uint32_t nring = (uint32_t)P.tc_ring;
 
     if (tid == 0) {
-        for (int i = 0; i < RING_SLOTS; i++) { mbar_init(&S.full[i], 1); mbar_init(&S.empty[i], 1); }
+        for (int i = 0; i < HX_TC_MAX_RING; i++) { mbar_init(&S.full[i], 1); mbar_init(&S.empty[i], 1); }
         mbar_init(&S.acc_full[0], 1); mbar_init(&S.acc_full[1], 1);
-        mbar_init(&S.acc_empty[0], 2); mbar_init(&S.acc_empty[1], 2);
+        mbar_init(&S.acc_empty[0], EPI_WARPS); mbar_init(&S.acc_empty[1], EPI_WARPS);
         mbar_init(&S.b_ready, 1);
         S.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -162,13 +189,13 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
     if (warp == NCW) {
         // =========================== producer ===========================
         if (lane == 0) {
-            uint32_t ctr = 0;
+            uint32_t slot = 0, par = 0;          // parity the empty barrier of `slot` completes when its previous use is over
+            bool first_round = true;
             auto push = [&](const void* src, uint32_t bytes) -> bool {
-                const uint32_t slot = ctr % RING_SLOTS, round = ctr / RING_SLOTS;
-                if (round > 0 && !mbar_wait(&S.empty[slot], (round - 1) & 1, &S.abort_flag)) return false;
+                if (!first_round && !mbar_wait(&S.empty[slot], par, &S.abort_flag)) return false;
                 mbar_expect_tx(&S.full[slot], bytes);
                 bulk_g2s(ring + (size_t)slot * HX_RING_SLOT, src, bytes, &S.full[slot]);
-                ctr++;
+                if (++slot == nring) { slot = 0; if (first_round) first_round = false; else par ^= 1u; }
                 return true;
             };
             bool ok = true;
@@ -177,13 +204,9 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 const HxPhase& ph = P.phases[pi];
                 if (ph.type == HX_PH_LINEAR_TC) {
                     const TcPlan tp = tc_plan(ph, cta, grid);
+                    const uint8_t* src = ph.w + (size_t)tp.b0 * HX_T128_CELL;
 #pragma unroll 1
-                    for (int i = 0; i < tp.nunits && ok; i++) {
-                        const uint8_t* base = ph.w + (size_t)(cta + i * grid) * tp.kpairs * HX_T64_CELL;
-#pragma unroll 1
-                        for (int q = 0; q < tp.kpairs && ok; q += SLOT_CELLS)
-                            ok = push(base + (size_t)q * HX_T64_CELL, (uint32_t)min(SLOT_CELLS, tp.kpairs - q) * HX_T64_CELL);
-                    }
+                    for (long long g = tp.b0; g < tp.b1 && ok; g++, src += HX_T128_CELL) ok = push(src, HX_T128_CELL);
                 } else if (ph.type == HX_PH_ATTN) {
                     const AttPlan ap = att_plan(ph, cta, pos);
                     const size_t rowb = (size_t)ph.DH * 4;
@@ -203,9 +226,9 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
             tc_cp_sf(tmem + TM_SFB, tc_desc(smem_u32(sfb1), 16, 128));
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(TC_NDIG >> 3) << 17) | (8u << 24);
             const uint64_t a_ring = tc_desc(smem_u32(ring), 16, 1024, TC_SW128);    // 8-row groups 1024 B apart, 128-byte swizzle
-            const uint64_t sf_ring = tc_desc(smem_u32(ring) + 8192, 16, 128);
+            const uint64_t sf_ring = tc_desc(smem_u32(ring) + 16384, 16, 128);
             const uint64_t b_base = tc_desc(smem_u32(digb), 16, 1024, TC_SW128);
-            uint32_t ctr = 0, uc = 0, tcph = 0;
+            uint32_t ctr = 0, slot = 0, par = 0, uc = 0, tcph = 0;
             bool ok = true;
 #pragma unroll 1
             for (int pi = 0; pi < P.nphases && ok; pi++) {
@@ -215,51 +238,47 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                     tcph++;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const TcPlan tp = tc_plan(ph, cta, grid);
+                    int kc = tp.k0, dp = 0;              // K cell of the tile, its position among the digit cells
+                    bool fresh = true;
+                    uint32_t dcol = 0;
 #pragma unroll 1
-                    for (int i = 0; i < tp.nunits && ok; i++) {
-                        const uint32_t buf = uc & 1u;
-                        if (uc >= 2) ok = mbar_wait(&S.acc_empty[buf], ((uc >> 1) - 1) & 1, &S.abort_flag);
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const uint32_t dcol = tmem + TM_D0 + buf * TC_NDIG;
-                        uint64_t b_run = b_base;                       // digit columns, step 0
-#pragma unroll 1
-                        for (int q0 = 0; q0 < tp.kpairs && ok; q0 += SLOT_CELLS) {
-                            const uint32_t slot = ctr % RING_SLOTS, round = ctr / RING_SLOTS;
-                            ctr++;
-                            ok = mbar_wait(&S.full[slot], round & 1, &S.abort_flag);
+                    for (long long g = tp.b0; g < tp.b1 && ok; g++) {
+                        if (fresh) {
+                            const uint32_t buf = uc & 1u;
+                            if (uc >= 2) ok = mbar_wait(&S.acc_empty[buf], ((uc >> 1) - 1) & 1, &S.abort_flag);
                             if (!ok) break;
-                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                            // descriptors advance by constants (16-byte units): a cell is 9216 B = 576 units, a K step inside
-                            // it 32 B = 2 units, its scale chunks at +8192 B and +8704 B; the digit columns are 2048 B per cell
-                            const uint64_t a_slot = a_ring + (uint64_t)(slot * (HX_RING_SLOT >> 4));
-                            const uint64_t sf_slot = sf_ring + (uint64_t)(slot * (HX_RING_SLOT >> 4));
-                            const uint32_t tsf_slot = tmem + TM_SFA + slot * 16;
-                            const int np = min(SLOT_CELLS, tp.kpairs - q0);
-#pragma unroll
-                            for (int c = 0; c < SLOT_CELLS; c++) {
-                                if (c < np) {
-                                    tc_cp_sf(tsf_slot + c * 8, sf_slot + (uint64_t)(c * 576));
-                                    tc_cp_sf(tsf_slot + c * 8 + 4, sf_slot + (uint64_t)(c * 576 + 32));
-                                }
-                            }
-#pragma unroll
-                            for (int c = 0; c < SLOT_CELLS; c++) {
-                                if (c < np) {
-#pragma unroll
-                                    for (int e = 0; e < 4; e++)
-                                        tc_mma(dcol, a_slot + (uint64_t)(c * 576 + e * 2), b_run + (uint64_t)(e * 2), idesc,
-                                               tsf_slot + c * 8 + (e >> 1) * 4 + (e & 1) * 2, tmem + TM_SFB, (q0 + c + e) > 0 ? 1u : 0u);
-                                    b_run += 128;
-                                }
-                            }
-                            tc_commit(&S.empty[slot]);
+                            dcol = tmem + TM_D0 + buf * TC_NDIG;
                         }
-                        tc_commit(&S.acc_full[buf]);
-                        uc++;
+                        ok = mbar_wait(&S.full[slot], par, &S.abort_flag);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        // descriptors advance in 16-byte units: a K step is 32 B of a swizzled row, a scale chunk 512 B
+                        const uint64_t a_slot = a_ring + (uint64_t)(slot * (HX_RING_SLOT >> 4));
+                        const uint64_t sf_slot = sf_ring + (uint64_t)(slot * (HX_RING_SLOT >> 4));
+                        const uint64_t b_cell = b_base + (uint64_t)(dp * 128);
+                        const uint32_t tsf = tmem + TM_SFA + slot * 16;
+#pragma unroll
+                        for (int e = 0; e < 4; e++) tc_cp_sf(tsf + e * 4, sf_slot + (uint64_t)(e * 32));
+#pragma unroll
+                        for (int e = 0; e < 4; e++)
+                            tc_mma(dcol, a_slot + (uint64_t)(e * 2), b_cell + (uint64_t)(e * 2), idesc, tsf + e * 4, tmem + TM_SFB,
+                                   (fresh && e == 0) ? 0u : 1u);
+                        tc_commit(&S.empty[slot]);
+                        fresh = false;
+                        if (++slot == nring) { slot = 0; par ^= 1u; }
+                        ctr++;
+                        if (++dp == tp.C) dp = 0;
+                        if (++kc == tp.C || g + 1 == tp.b1) {          // last cell of this tile's piece
+                            tc_commit(&S.acc_full[uc & 1u]);
+                            uc++; kc = 0; fresh = true;
+                        }
                     }
                 } else if (ph.type == HX_PH_ATTN) {
                     const AttPlan ap = att_plan(ph, cta, pos);
-                    ctr += 2u * (uint32_t)ap.nslots;             // ring slots the consumers use for K and V rows
+                    const uint32_t adv = 2u * (uint32_t)ap.nslots;             // ring slots the consumers use for K and V rows
+                    ctr += adv;
+                    const uint32_t s2 = slot + adv;
+                    slot = s2 % nring; if ((s2 / nring) & 1u) par ^= 1u;
                 }
             }
         }
@@ -278,6 +297,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 // A thread owns items of 8 consecutive elements; up to XI items stay in registers between the
                 // statistics pass and the digit pass (one L2 round trip); longer vectors are read twice.
                 const int K = ph.K, Kt = ph.ksteps * 64;
+                const TcPlan tp = tc_plan(ph, cta, grid);
                 const float* xin = ph.x;
                 if (ph.tok) xin = ph.x + (size_t)(ph.tok[P.tok_by_pos ? pos : 0]) * K;
                 constexpr int XI = 3;
@@ -336,14 +356,16 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 }
                 const float mul = (inv / Sg) * 2147483648.0f;             // |x_n| / Sg * 2^31 < 2^32
                 auto emit = [&](int k, const float (&v)[8]) {
+                    const int j = (k >> 5) & 7, w = (k >> 3) & 3;                 // 16-byte chunk, word
+                    int dp = (k >> 8) - tp.k0; if (dp < 0) dp += tp.C;             // position of the 256-column cell in this CTA's run
+                    if (dp >= tp.run) return;                                      // a cell this CTA does not stream
                     uint32_t M[8]; uint32_t sg = 0u;
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
                         M[e] = __float2uint_rn(fabsf(v[e]) * mul);
                         sg |= (v[e] < 0.0f ? 8u : 0u) << (4 * e);
                     }
-                    const int kg = k >> 8, j = (k >> 5) & 7, w = (k >> 3) & 3;     // 256-column cell, 16-byte chunk, word
-                    uint8_t* dst = digb + (size_t)kg * 2048 + w * 4;
+                    uint8_t* dst = digb + (size_t)dp * 2048 + w * 4;
 #pragma unroll
                     for (int n = 0; n < TC_NDIG; n++) {
                         uint32_t word = 0u;
@@ -365,7 +387,9 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                     }
                 } else {
 #pragma unroll 1
-                    for (int k = tid * 8; k < Kt; k += NCT * 8) {
+                    for (int it = tid; it < tp.run * 32; it += NCT) {
+                        int kc = tp.k0 + (it >> 5); if (kc >= tp.C) kc -= tp.C;
+                        const int k = kc * 256 + (it & 31) * 8;
                         float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                         if (k < K) {
                             float4 a = __ldcg(reinterpret_cast<const float4*>(xin + k)), b = __ldcg(reinterpret_cast<const float4*>(xin + k + 4));
@@ -383,14 +407,15 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 if (tid == 0) mbar_arrive(&S.b_ready);
                 STAMP(1);
 
-                // ---------- units: accumulator -> digits recombined -> epilogue ----------
-                const TcPlan tp = tc_plan(ph, cta, grid);
-                ctr += (uint32_t)(tp.nunits * tp.nslots);
-                if (warp < 2) {
+                // ---------- pieces of tiles: accumulator -> digits recombined -> (merge) -> epilogue ----------
+                ctr += (uint32_t)(tp.b1 - tp.b0);
+                // number of pieces this CTA produces: one per tile its run touches
+                const int t_first = (int)(tp.b0 / tp.C), t_last = tp.b1 > tp.b0 ? (int)((tp.b1 - 1) / tp.C) : t_first - 1;
+                if (warp < EPI_WARPS) {
                     const float out_scale = Sg;       // x_n = Sg * sum_j 4^-j * (digit_j / 2), and digit/2 is the E2M1 value
+                    const int rl = warp * 32 + lane;
 #pragma unroll 1
-                    for (int i = 0; i < tp.nunits; i++) {
-                        const int tile = cta + i * grid;
+                    for (int tile = t_first; tile <= t_last; tile++) {
                         const uint32_t buf = uc & 1u;
                         if (!mbar_wait(&S.acc_full[buf], (uc >> 1) & 1, &S.abort_flag)) goto aborted;
                         uc++;
@@ -409,16 +434,31 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
 #pragma unroll
                         for (int j = TC_NDIG - 1; j >= 0; j--) v = fmaf(v, 0.25f, __uint_as_float(r[j]));
                         v *= out_scale;
-                        const int rl = warp * 32 + lane;
-                        if (ph.epi == HX_EPI_SWIGLU) {
-                            // rows 0..31 of a tile are gate rows, 32..63 the matching up rows
-                            S.swi[rl] = v * (rl < 32 ? ph.ts[0] : ph.ts[1]);
+                        // which CTAs share this tile
+                        const long long x0 = (long long)tile * tp.C;
+                        const int c0 = tc_owner(x0, tp.total, tp.geff), c1 = tc_owner(x0 + tp.C - 1, tp.total, tp.geff);
+                        if (c1 != c0) {
+                            float* pp = P.tc_partial + ((size_t)tile * ph.pieces) * 128;
+                            pp[(size_t)(cta - c0) * 128 + rl] = v;
+                            __threadfence();
                             epi_sync();
-                            const int hi = tile * 32 + rl;
-                            if (rl < 32 && hi < ph.N) ph.y[hi] = pz_silu_mul(S.swi[rl], S.swi[rl + 32]);
+                            if (tid == 0) S.eticket = atomicAdd(P.tc_cnt + tile, 1u);
+                            epi_sync();
+                            if (S.eticket != (unsigned)(c1 - c0)) continue;          // a later piece finishes the tile
+                            __threadfence();
+                            v = 0.0f;
+                            for (int q = 0; q <= c1 - c0; q++) v += __ldcg(pp + (size_t)q * 128 + rl);
+                            if (tid == 0) P.tc_cnt[tile] = 0u;
+                        }
+                        if (ph.epi == HX_EPI_SWIGLU) {
+                            // rows 0..63 of a tile are gate rows, 64..127 the matching up rows
+                            S.swi[rl] = v * (rl < 64 ? ph.ts[0] : ph.ts[1]);
+                            epi_sync();
+                            const int hi = tile * 64 + rl;
+                            if (rl < 64 && hi < ph.N) ph.y[hi] = pz_silu_mul(S.swi[rl], S.swi[rl + 64]);
                             epi_sync();
                         } else {
-                            const int row = tile * 64 + rl;
+                            const int row = tile * 128 + rl;
                             if (row < ph.N) {
                                 v *= (row < ph.bound0) ? ph.ts[0] : (row < ph.bound1 ? ph.ts[1] : ph.ts[2]);
                                 if (ph.epi == HX_EPI_RESID) v = __ldcg(ph.y + row) + v;
@@ -427,9 +467,9 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                             }
                         }
                     }
-                } else uc += (uint32_t)tp.nunits;
+                } else uc += (uint32_t)(t_last - t_first + 1);
                 if (ph.epi == HX_EPI_ARGMAX) {
-                    // per-CTA best (held by warps 0-1), then the last CTA to arrive folds all of them
+                    // per-CTA best (held by warps 0-3), then the last CTA to arrive folds all of them
 #pragma unroll
                     for (int d = 16; d >= 1; d >>= 1) {
                         const float ov = __shfl_xor_sync(0xffffffffu, best_v, d);
@@ -440,7 +480,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                     consumer_sync();
                     if (tid == 0) {
                         float bv = S.bv[0]; int bi = S.bi[0];
-                        for (int i = 1; i < 2; i++) if (pz_better(S.bv[i], S.bi[i], bv, bi)) { bv = S.bv[i]; bi = S.bi[i]; }
+                        for (int i = 1; i < 4; i++) if (pz_better(S.bv[i], S.bi[i], bv, bi)) { bv = S.bv[i]; bi = S.bi[i]; }
                         P.am_val[cta] = bv; P.am_idx[cta] = bi;
                         __threadfence();
                         S.ticket = atomicAdd(P.am_cnt, 1u);
@@ -521,11 +561,20 @@ done:   ;
 size_t hx_persist_tc_smem(int bdig_bytes) {
     const size_t att = (size_t)(8 * 256 + 256 + 256 + 8 * 160 + 8 * NCT) * 4;
     const size_t d = (size_t)bdig_bytes > att ? (size_t)bdig_bytes : att;
-    return ((sizeof(SmemTc) + 15) & ~(size_t)15) + 512 + 1024 + (size_t)RING_SLOTS * HX_RING_SLOT + d;
+    return ((sizeof(SmemTc) + 15) & ~(size_t)15) + 512 + 1024 + d;      // + ring slots
+}
+
+// Ring depth that fits beside the digit columns (0 = does not fit).
+int hx_persist_tc_ring(int bdig_bytes) {
+    const size_t fixed = hx_persist_tc_smem(bdig_bytes);
+    if (fixed + 3 * (size_t)HX_RING_SLOT > 227 * 1024) return 0;
+    size_t n = (227 * 1024 - fixed) / HX_RING_SLOT;
+    return (int)(n > HX_TC_MAX_RING ? HX_TC_MAX_RING : n);
 }
 
 int hx_persist_tc_launch(const HxPersist& p, int grid, cudaStream_t st) {
-    const size_t smem = hx_persist_tc_smem(p.bdig_bytes);
+    if (p.tc_ring < 3 || p.tc_ring > HX_TC_MAX_RING) return hx_fail(HX_ERR_ARG, "tensor-core decode: ring depth %d", p.tc_ring);
+    const size_t smem = hx_persist_tc_smem(p.bdig_bytes) + (size_t)p.tc_ring * HX_RING_SLOT;
     if (smem > 227 * 1024) return hx_fail(HX_ERR_ARG, "tensor-core decode needs %zu bytes of shared memory", smem);
     static bool attr = false;
     if (!attr) {
