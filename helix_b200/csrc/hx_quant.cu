@@ -153,6 +153,127 @@ HX_API int hx_quantize_nvfp4(const float* w, int rows, int K, int32_t* words, ui
     return HX_OK;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Quantizer that allocates nothing.
+//
+// hx_quantize_nvfp4 takes its amax word from cudaMalloc on its first call per device.  Some hosts cannot
+// accept that: a worker that gave all device memory to its own arena when it started (the reference's
+// worker sizes every buffer once and never allocates inside its token loop), or a service that shares the
+// GPU with other streams and cannot afford the device-wide stall an allocation implies.  This variant finds
+// the tensor's amax through a scratch array that is part of the library image: one word per row, then one
+// word for the whole tensor.  The array is obtained with cudaGetSymbolAddress, which only looks a symbol
+// up; it is looked up once per device and cached.
+//
+//   * size limit: rows <= HX_NOALLOC_MAX_ROWS (1 MiB of row maxima + 256 B); more rows are refused.
+//   * the first call on a device performs the symbol look-up (and loads the library's device code if
+//     nothing did before); make that call during start-up, before any stream capture.
+//   * the array is shared by every caller of the process and keeps what the last call left; nothing has to
+//     start at zero, because a call writes words [0, rows) and the tensor word before it reads them and
+//     never reads beyond.
+//   * two calls that overlap in time on one device (different streams or threads) race on the array; calls
+//     on one stream are ordered by the stream.
+// ------------------------------------------------------------------------------------------------
+#define HX_NOALLOC_MAX_ROWS (1 << 18)
+static __device__ __align__(256) unsigned g_noalloc_scratch[HX_NOALLOC_MAX_ROWS + 64];
+
+// amax of each row: G threads per row (32 or 256), rows dealt to groups grid-stride.
+template <int G>
+__global__ void __launch_bounds__(256) k_row_amax(const float* __restrict__ w, int rows, int K, unsigned* __restrict__ row_bits) {
+    const int groups_per_block = 256 / G, gl = threadIdx.x / G, t = threadIdx.x % G;
+    __shared__ float sm[8];
+    for (int r = blockIdx.x * groups_per_block + gl; r < rows; r += gridDim.x * groups_per_block) {   // uniform per block when G = 256
+        const float* wr = w + (size_t)r * K;
+        float m = 0.0f;
+        if (((((uintptr_t)wr) & 15) == 0)) {
+            const float4* w4 = reinterpret_cast<const float4*>(wr);
+            const int n4 = K / 4;
+            for (int i = t; i < n4; i += G) {
+                const float4 v = __ldg(w4 + i);
+                m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            }
+            for (int i = n4 * 4 + t; i < K; i += G) m = fmaxf(m, fabsf(wr[i]));
+        } else {
+            for (int i = t; i < K; i += G) m = fmaxf(m, fabsf(wr[i]));
+        }
+        m = hx_warp_max(m);
+        if (G == 32) {
+            if (t == 0) row_bits[r] = __float_as_uint(m);
+        } else {
+            if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = m;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                float mm = sm[0];
+#pragma unroll
+                for (int i = 1; i < 8; i++) mm = fmaxf(mm, sm[i]);
+                row_bits[r] = __float_as_uint(mm);
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// max of the row words -> tensor_bits[0]; one block.  Non-negative floats order like their bit patterns.
+__global__ void __launch_bounds__(1024) k_fold_amax(const unsigned* __restrict__ row_bits, int rows, unsigned* __restrict__ tensor_bits) {
+    unsigned m = 0u;
+    for (int i = threadIdx.x; i < rows; i += 1024) m = max(m, row_bits[i]);
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, d));
+    __shared__ unsigned sm[32];
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        m = sm[threadIdx.x];
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, d));
+        if (threadIdx.x == 0) tensor_bits[0] = m;
+    }
+}
+
+// Address of the library's scratch array on the current device (looked up once per device).
+static int noalloc_scratch(unsigned** out) {
+    static unsigned* cached[64] = {0};
+    int dev = 0;
+    HX_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return hx_fail(HX_ERR_ARG, "device index %d not supported", dev);
+    if (!cached[dev]) {
+        unsigned* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || !ptr) return hx_fail(HX_ERR_CUDA, "cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return HX_OK;
+}
+
+HX_API int hx_noalloc_max_rows(void) { return HX_NOALLOC_MAX_ROWS; }
+
+HX_API int hx_quantize_nvfp4_noalloc(const float* w, int rows, int K, int32_t* words, uint8_t* micro, float* sc,
+                                     float* ts, void* stream) {
+    HX_CHECK_ARG(w && words && rows > 0 && K > 0);
+    if (rows > HX_NOALLOC_MAX_ROWS)
+        return hx_fail(HX_ERR_ARG, "hx_quantize_nvfp4_noalloc: %d rows exceed the built-in scratch of %d rows; "
+                                   "quantize the tensor with hx_quantize_nvfp4", rows, HX_NOALLOC_MAX_ROWS);
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned* scr = nullptr;
+    int rc = noalloc_scratch(&scr); if (rc) return rc;
+    unsigned* tensor_bits = scr + HX_NOALLOC_MAX_ROWS;
+    const int Kpad = hx_kpad(K);
+    if (K >= 2048) {
+        int g = rows < 148 * 8 ? rows : 148 * 8;
+        k_row_amax<256><<<g, 256, 0, st>>>(w, rows, K, scr);
+    } else {
+        int g = (rows + 7) / 8; if (g > 148 * 8) g = 148 * 8;
+        k_row_amax<32><<<g, 256, 0, st>>>(w, rows, K, scr);
+    }
+    k_fold_amax<<<1, 1024, 0, st>>>(scr, rows, tensor_bits);
+    long items = (long)rows * ((Kpad + QSPAN - 1) / QSPAN);
+    int g2 = (int)(items < 148L * 16 ? items : 148L * 16);
+    k_quantize<<<g2, QTHREADS, 0, st>>>(w, rows, K, Kpad, tensor_bits, words, micro, sc, ts);
+    HX_COUNT_LAUNCH(3);
+    HX_CUDA(cudaGetLastError());
+    return HX_OK;
+}
+
 HX_API int hx_quantize_nvfp4_host(const float* w, int rows, int K, int32_t* words, uint8_t* micro, float* sc,
                                   float* ts) {
     HX_CHECK_ARG(w && words && rows > 0 && K > 0);

@@ -72,6 +72,8 @@ _SIGS = {
     "hx_kpad": (C.c_int, [C.c_int]),
     "hx_kd": (C.c_int, [C.c_int]),
     "hx_quantize_nvfp4": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "hx_quantize_nvfp4_noalloc": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "hx_noalloc_max_rows": (C.c_int, []),
     "hx_quantize_nvfp4_host": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "hx_dequant_nvfp4": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "hx_pack_micro": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),

@@ -70,6 +70,20 @@ int hx_kpad(int K);
 int hx_quantize_nvfp4(const float* w, int rows, int K, int32_t* words, uint8_t* micro, float* sc,
                       float* ts, void* stream);
 
+/* hx_quantize_nvfp4 for callers that must not allocate device memory (a host that owns all of it in an
+ * arena of its own, a service that cannot take the device-wide stall of an allocation).  Same arguments,
+ * same bytes out.  No counterpart in the reference: its quantizer runs on the CPU.
+ * The per-row maxima live in an array inside the library (1 MiB, found with cudaGetSymbolAddress):
+ *   - rows <= hx_noalloc_max_rows() (262144), else HX_ERR_ARG;
+ *   - the first call on a device looks the array up (and loads the device code if nothing has yet): make
+ *     it during start-up, ahead of any stream capture;
+ *   - the array is shared by all callers and keeps the last call's contents; nothing needs clearing, a
+ *     call only reads what it wrote;
+ *   - calls that overlap in time on one device race on it: keep them on one stream or serialise them. */
+int hx_quantize_nvfp4_noalloc(const float* w, int rows, int K, int32_t* words, uint8_t* micro, float* sc,
+                              float* ts, void* stream);
+int hx_noalloc_max_rows(void);
+
 /* Same contract with HOST buffers: copies w to the device, quantizes, copies the results back and
  * synchronises.  This is the call that stands where the importer calls nvfp4_quantize_tensor
  * (gpt2_pack.c:676). */
