@@ -10,7 +10,8 @@ enum {
     HX_EPI_RESID = 1,     // y[n] = resid[n] + acc (+ bias)      (y may alias resid)
     HX_EPI_SWIGLU = 2,    // rows are (gate_i, up_i) pairs: y[i] = silu(gate_i) * up_i
     HX_EPI_GELU = 3,      // y[n] = gelu_new(acc + bias)
-    HX_EPI_ARGMAX = 4     // y[n] = acc; the last CTA to finish writes the arg-max row to *next_tok
+    HX_EPI_ARGMAX = 4,    // y[n] = acc; the last CTA to finish writes the arg-max row to *next_tok
+    HX_EPI_QKV = 5        // fused q|k|v rows: per-head RMSNorm + RoPE on q and k; q -> y, k and v -> the cache row of the position
 };
 
 struct HxLinear {

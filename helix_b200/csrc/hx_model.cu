@@ -441,8 +441,16 @@ int build_phases(hx_model* m, bool from_prompt, bool with_head, HxPhase** out, i
         HxPhase a = linear(ly.qkv, m->x, m->qkv, HX_EPI_STORE, ly.qkv.N);
         a.norm = HX_NORM_RMS; a.g = ly.in_g; a.eps = c.norm_eps;
         if (L == 0) { a.x = m->emb; a.tok = from_prompt ? m->d_prompt : m->d_tok; a.x_out = m->x; }
+        // tensor-core path: the qkv epilogue norms and rotates q and k and writes k, v into the cache
+        const bool fuse_qk = m->use_tc && (DH == 32 || DH == 64 || DH == 128);
+        if (fuse_qk) {
+            a.epi = HX_EPI_QKV; a.qn_g = ly.qn_g; a.kn_g = ly.kn_g; a.cosT = m->cosT; a.sinT = m->sinT;
+            a.kc = m->kc + (size_t)L * c.n_kv_heads * cap * DH; a.vc = m->vc + (size_t)L * c.n_kv_heads * cap * DH;
+            a.NH = c.n_heads; a.NKV = c.n_kv_heads; a.DH = DH; a.cap = cap;
+        }
         v.push_back(a);
         HxPhase at = {};
+        if (fuse_qk) at.epi = HX_EPI_QKV;          // q arrives prepared, the position's k and v are cached
         at.type = HX_PH_ATTN; at.qkv = m->qkv; at.qn_g = ly.qn_g; at.kn_g = ly.kn_g; at.cosT = m->cosT; at.sinT = m->sinT;
         at.kc = m->kc + (size_t)L * c.n_kv_heads * cap * DH; at.vc = m->vc + (size_t)L * c.n_kv_heads * cap * DH;
         at.ctx = m->ctx; at.NH = c.n_heads; at.NKV = c.n_kv_heads; at.DH = DH; at.cap = cap;
@@ -490,7 +498,7 @@ int init_persist(hx_model* m) {
     HX_CUDA(cudaMemset(m->d_bar, 0, 16));
     HX_CUDA(cudaMemset(m->d_err, 0, 16));
     m->bar_count = 0;
-    if (getenv("HX_PERSIST_DBG")) { if ((rc = dalloc(m, &m->d_dbg, (size_t)16 * (m->nph_decode + 4)))) return rc; }
+    if (getenv("HX_PERSIST_DBG")) { if ((rc = dalloc(m, &m->d_dbg, (size_t)16 * (m->nph_decode + 4) + (size_t)m->nph_decode * m->grid_persist))) return rc; }
     if (m->use_tc) {
         if ((rc = dalloc(m, &m->tc_partial, m->tc_units_max * 128 + 128))) return rc;
         if ((rc = dalloc(m, &m->tc_cnt, (size_t)m->tc_tiles_max + 8))) return rc;
@@ -515,7 +523,7 @@ int persist_step(hx_model* m, bool from_prompt, bool with_head) {
     P.am_val = m->am_val; P.am_idx = m->am_idx; P.am_cnt = m->am_cnt; P.next_tok = m->d_tok; P.pos_inc = m->d_pos;
     P.hist = m->d_hist; P.logits = m->logits; P.dig_bytes = m->dig_bytes;
     P.tok_by_pos = from_prompt ? 1 : 0; P.advance_pos = from_prompt ? 1 : 0;
-    P.dbg = m->d_dbg;
+    P.dbg = m->d_dbg; P.dbg_all = m->d_dbg ? m->d_dbg + (size_t)16 * (m->nph_decode + 4) : nullptr; { const char* dc = getenv("HX_PERSIST_DBG"); P.dbg_cta = dc ? atoi(dc) - 1 : 0; if (P.dbg_cta < 0) P.dbg_cta = 0; }
     P.tc_partial = m->tc_partial; P.tc_cnt = m->tc_cnt; P.bdig_bytes = m->bdig_bytes; P.tc_ring = m->tc_ring;
     m->bar_count += (unsigned long long)m->grid_persist * (unsigned long long)(P.nphases - 1);
     if (m->use_tc) return hx_persist_tc_launch(P, m->grid_persist, m->st);
@@ -695,6 +703,16 @@ HX_API int hx_model_phase_stamps(hx_model* m, unsigned long long* out, int max_p
     const int n = m->nph_decode < max_phases ? m->nph_decode : max_phases;
     HX_CUDA(cudaMemcpy(out, m->d_dbg, (size_t)n * 16 * 8, cudaMemcpyDeviceToHost));
     *nphases = n;
+    return HX_OK;
+}
+// Debug: the time every CTA finished each phase's work in the last persistent launch: out[phase * grid + cta].
+HX_API int hx_model_phase_stamps_all(hx_model* m, unsigned long long* out, size_t max_words, int* nphases, int* grid) {
+    HX_CHECK_ARG(m && out && nphases && grid);
+    if (!m->d_dbg) return hx_fail(HX_ERR_STATE, "set HX_PERSIST_DBG=1 before creating the model");
+    const size_t n = (size_t)m->nph_decode * m->grid_persist;
+    HX_CHECK_ARG(n <= max_words);
+    HX_CUDA(cudaMemcpy(out, m->d_dbg + (size_t)16 * (m->nph_decode + 4), n * 8, cudaMemcpyDeviceToHost));
+    *nphases = m->nph_decode; *grid = m->grid_persist;
     return HX_OK;
 }
 HX_API int hx_model_set_profile(hx_model* m, int on) { HX_CHECK_ARG(m); m->profile = on != 0; return HX_OK; }

@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_persist(const __grid_constant_
                     pbuf ^= 1;
                 }
             }
-            if (P.dbg && cta == 0 && tid == 0) P.dbg[pi * 16 + 4] = (unsigned long long)wait_cycles;
+            if (P.dbg && cta == P.dbg_cta && tid == 0) P.dbg[pi * 16 + 4] = (unsigned long long)wait_cycles;
             if (ph.epi == HX_EPI_ARGMAX) {
                 // per-CTA best, then the last CTA to arrive folds all of them (no waiting)
                 if (warp == 0) {

@@ -29,7 +29,7 @@ void hx_repack_t16(const int32_t* words, const uint8_t* micro, int rows, int K, 
 
 enum { HX_PH_LINEAR = 0, HX_PH_ATTN = 1, HX_PH_LINEAR_TC = 2 };
 
-struct HxPhase {
+struct alignas(16) HxPhase {
     int type;
     // ---- linear ----
     const uint8_t* w;         // T16 base
@@ -68,7 +68,9 @@ struct HxPersist {
     int dig_bytes;                        // shared-memory bytes reserved for the f16 split of x
     int tok_by_pos;                       // the input token is tok[pos] (prompt) instead of tok[0]
     int advance_pos;                      // no head in this launch: CTA 0 advances *pos_inc at the end
-    unsigned long long* dbg;              // optional: CTA 0 writes 4 globaltimer stamps per phase
+    unsigned long long* dbg;              // optional: CTA dbg_cta writes globaltimer stamps per phase
+    int dbg_cta;
+    unsigned long long* dbg_all;          // optional: every CTA writes the time it finished the work of each phase
     float* tc_partial; unsigned* tc_cnt;  // split-K scratch of the tensor-core linear phases
     int bdig_bytes;                       // shared-memory bytes for the digit columns of x (tensor-core path)
     int tc_ring;                          // ring depth of the tensor-core kernel (3..10 slots)

@@ -39,6 +39,10 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  :: "r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+// asks L2 to fetch [p, p+bytes): p 16-byte aligned, bytes a multiple of 16
+__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(p), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" :: "n"(NCT) : "memory"); }
 
 __device__ __forceinline__ float pz_silu_mul(float g, float u) {
@@ -63,7 +67,8 @@ __device__ __forceinline__ AttPlan att_plan(const HxPhase& ph, int cta, int pos)
     return a;
 }
 
-#define STAMP(i) do { if (P.dbg && cta == 0 && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg[pi * 16 + (i)] = _t; } } while (0)
+#define STAMP_ALL() do { if (P.dbg_all && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg_all[(size_t)pi * gridDim.x + blockIdx.x] = _t; } } while (0)
+#define STAMP(i) do { if (P.dbg && cta == P.dbg_cta && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg[pi * 16 + (i)] = _t; } } while (0)
 
 // ------------------------------------------------------------------------------------------------
 // Attention phase of one CTA: (kv head, split of the cached positions); the GRP query heads of the kv
@@ -268,3 +273,191 @@ __device__ __noinline__ bool attention_phase(const HxPersist& P, const HxPhase& 
     return true;
 }
 
+// One release-acquire ticket: the caller's CTA has met at a barrier after writing its partial results; the
+// returned value tells how many arrived before.  The last arrival may read every other CTA's partials.
+__device__ __forceinline__ unsigned ticket_acq_rel(unsigned* cnt) {
+    unsigned old;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(cnt) : "memory");
+    return old;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Attention phase when q arrives already normed and rotated and the current position's k and v are
+// already in the cache (the qkv phase's epilogue did both).  One CTA per (kv head, split of the cached
+// positions).  Per ring tile of positions: scores with one thread per (head, position) -- lanes walk the
+// head dimension rotated by their position so that shared-memory accesses do not collide --, soft-max
+// statistics by one warp per head, then P*V with one thread per (head, dimension).
+// ------------------------------------------------------------------------------------------------
+template <int GRP, class SM>
+__device__ __noinline__ bool attention_phase2(const HxPersist& P, const HxPhase& ph, SM& S, uint8_t* ring, uint8_t* digb,
+                                              uint32_t& ctr, int pi, int pos) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, cta = blockIdx.x;
+    const AttPlan ap = att_plan(ph, cta, pos);
+    const int DH = ph.DH;
+    float* sq = reinterpret_cast<float*>(digb);                 // [GRP][DH] queries
+    float* knew = sq + 8 * 256;                                  // [DH] current k
+    float* vnew = knew + 256;                                    // [DH] current v
+    float* sp = vnew + 256;                                      // [GRP][rows_per_slot + 1] scores / probabilities
+    float* accx = sp + 8 * 160;                                  // [nsub][GRP*DH] partial outputs (small heads only)
+    const int spitch = ap.rows_per_slot + 1;
+    const int HD = GRP * DH;
+    constexpr int NACC = (GRP * 256 + NCT - 1) / NCT;           // (head, dim) pairs per thread when GRP*DH > NCT
+    const int nsub = HD < NCT ? NCT / HD : 1;                    // position subsets when threads outnumber the pairs
+    const int sub = HD < NCT ? tid / HD : 0;
+    float acc[NACC];
+#pragma unroll
+    for (int i = 0; i < NACC; i++) acc[i] = 0.0f;
+    if (ap.active && ap.t1 > ap.t0) {
+        for (int i = tid; i < HD; i += NCT) sq[i] = __ldcg(ph.qkv + (size_t)ap.kv * HD + i);
+        if (ap.has_new) {
+            const size_t o = ((size_t)ap.kv * ph.cap + pos) * DH;
+            for (int e = tid; e < DH; e += NCT) { knew[e] = __ldcg(ph.kc + o + e); vnew[e] = __ldcg(ph.vc + o + e); }
+        }
+        if (tid < 8) { S.att_m[tid] = -100000000.0f; S.att_l[tid] = 0.0f; }
+        consumer_sync();
+        STAMP(4);
+        const int ntile = ap.nslots + ((ap.has_new && ap.n_old % ap.rows_per_slot == 0) ? 1 : 0);
+        #pragma unroll 1
+        for (int s = 0; s < ntile; s++) {
+            const bool ring_tile = s < ap.nslots;
+            const int nr = ring_tile ? min(ap.rows_per_slot, ap.n_old - s * ap.rows_per_slot) : 0;
+            const bool add_new = ap.has_new && (s == ntile - 1);       // the current position rides on the last tile
+            uint32_t kslot = 0, vslot = 0;
+            const float* kt = nullptr; const float* vt = nullptr;
+            if (ring_tile) {
+                kslot = ctr % RING_SLOTS; const uint32_t kround = ctr / RING_SLOTS; ctr++;
+                if (!mbar_wait(&S.full[kslot], kround & 1, &S.abort_flag)) return false;
+                kt = reinterpret_cast<const float*>(ring + (size_t)kslot * HX_RING_SLOT);
+            }
+            if (s == 0) STAMP(8);
+            const int ntot = nr + (add_new ? 1 : 0);
+            // scores: thread (head i, position r)
+            #pragma unroll 1
+            for (int it = tid; it < GRP * ntot; it += NCT) {
+                const int i = it / ntot, r = it - i * ntot;
+                const float* kr = (r < nr) ? kt + (size_t)r * DH : knew;
+                const float* qi = sq + i * DH;
+                float d0 = 0.0f, d1 = 0.0f;
+                int e = (4 * r) % DH;
+                #pragma unroll 4
+                for (int j = 0; j < DH; j += 4) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(kr + e);
+                    const float4 q4 = *reinterpret_cast<const float4*>(qi + e);
+                    d0 = fmaf(q4.x, k4.x, d0); d1 = fmaf(q4.y, k4.y, d1); d0 = fmaf(q4.z, k4.z, d0); d1 = fmaf(q4.w, k4.w, d1);
+                    e += 4; if (e >= DH) e = 0;
+                }
+                sp[i * spitch + r] = (d0 + d1) * ph.scale;
+            }
+            consumer_sync();
+            if (ring_tile && tid == 0) mbar_arrive(&S.empty[kslot]);
+            if (s == 0) STAMP(9);
+            // online softmax state per head (fused_decode_attn_kernel.hx:74-102)
+            if (warp < GRP) {
+                const int i = warp;
+                float tm = -INFINITY;
+                for (int r = lane; r < ntot; r += 32) tm = fmaxf(tm, sp[i * spitch + r]);
+                tm = hx_warp_max(tm);
+                const float mo = S.att_m[i], mn = fmaxf(mo, tm);
+                float ls = 0.0f;
+                for (int r = lane; r < ntot; r += 32) { const float pr = __expf(sp[i * spitch + r] - mn); sp[i * spitch + r] = pr; ls += pr; }
+                ls = hx_warp_sum(ls);
+                if (lane == 0) { const float rr = __expf(mo - mn); S.att_r[i] = rr; S.att_l[i] = S.att_l[i] * rr + ls; S.att_m[i] = mn; }
+            }
+            if (ring_tile) {
+                vslot = ctr % RING_SLOTS; const uint32_t vround = ctr / RING_SLOTS; ctr++;
+                if (!mbar_wait(&S.full[vslot], vround & 1, &S.abort_flag)) return false;
+                vt = reinterpret_cast<const float*>(ring + (size_t)vslot * HX_RING_SLOT);
+            }
+            consumer_sync();
+            if (s == 0) STAMP(10);
+            // P*V: thread (head, dimension) [x position subset]
+#pragma unroll
+            for (int a = 0; a < NACC; a++) {
+                const int hd = (HD < NCT ? tid % HD : tid + a * NCT);
+                if (hd < HD && sub < nsub) {
+                    const int i = hd / DH, d = hd - i * DH;
+                    float v = acc[a] * S.att_r[i];
+                    #pragma unroll 4
+                    for (int r = sub; r < ntot; r += nsub) {
+                        const float vv = (r < nr) ? vt[(size_t)r * DH + d] : vnew[d];
+                        v = fmaf(sp[i * spitch + r], vv, v);
+                    }
+                    acc[a] = v;
+                }
+            }
+            consumer_sync();
+            if (ring_tile && tid == 0) mbar_arrive(&S.empty[vslot]);
+        }
+        STAMP(5);
+        // write this split's partial (position subsets folded through shared memory first)
+        if (nsub > 1) {
+            if (sub < nsub) accx[sub * HD + tid % HD] = acc[0];
+            consumer_sync();
+            if (tid < HD) {
+                float v = 0.0f;
+                for (int u = 0; u < nsub; u++) v += accx[u * HD + tid];
+                acc[0] = v;
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < NACC; a++) {
+            const int hd = (HD < NCT ? tid : tid + a * NCT);
+            if (hd < HD && (HD >= NCT || tid < HD)) {
+                const int i = hd / DH, d = hd - i * DH;
+                const size_t hs = (size_t)(ap.kv * GRP + i) * ph.nsplit + ap.split;
+                P.part_acc[hs * DH + d] = acc[a];
+                if (d == 0) { P.part_m[hs] = S.att_m[i]; P.part_l[hs] = S.att_l[i]; }
+            }
+        }
+    } else if (ap.active) {
+        // empty split: neutral partial
+        for (int i = tid; i < GRP; i += NCT) {
+            const size_t hs = (size_t)(ap.kv * GRP + i) * ph.nsplit + ap.split;
+            P.part_m[hs] = -100000000.0f; P.part_l[hs] = 0.0f;
+        }
+        for (int i = tid; i < GRP * DH; i += NCT) {
+            const size_t hs = (size_t)(ap.kv * GRP + i / DH) * ph.nsplit + ap.split;
+            P.part_acc[hs * DH + i % DH] = 0.0f;
+        }
+    }
+    if (ap.active) {
+        STAMP(6);
+        consumer_sync();
+        if (tid == 0) S.ticket = ticket_acq_rel(P.attn_cnt + ap.kv);
+        consumer_sync();
+        STAMP(7);
+        if (S.ticket == (unsigned)ph.nsplit - 1) {
+            // merge of the splits: weights w_s = exp(m_s - M) / sum_s l_s exp(m_s - M), then one pass
+            // of independent loads over the partial outputs
+            float* wgt = sp;                                   // [GRP][nsplit]
+            const size_t hbase = (size_t)(ap.kv * GRP) * ph.nsplit;
+            #pragma unroll 1
+            for (int i = warp; i < GRP; i += NCW) {
+                float mv[2], lv[2];
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int sidx = lane + 32 * j;
+                    mv[j] = sidx < ph.nsplit ? __ldcg(P.part_m + hbase + (size_t)i * ph.nsplit + sidx) : -INFINITY;
+                    lv[j] = sidx < ph.nsplit ? __ldcg(P.part_l + hbase + (size_t)i * ph.nsplit + sidx) : 0.0f;
+                }
+                const float M = hx_warp_max(fmaxf(mv[0], mv[1]));
+                const float w0 = __expf(mv[0] - M), w1 = __expf(mv[1] - M);
+                const float Lsum = hx_warp_sum(lv[0] * w0 + lv[1] * w1);
+                if (lane < ph.nsplit) wgt[i * ph.nsplit + lane] = w0 / Lsum;
+                if (lane + 32 < ph.nsplit) wgt[i * ph.nsplit + lane + 32] = w1 / Lsum;
+            }
+            consumer_sync();
+            #pragma unroll 1
+            for (int o = tid; o < GRP * DH; o += NCT) {
+                const int i = o / DH, dd = o % DH;
+                const float* pa = P.part_acc + (hbase + (size_t)i * ph.nsplit) * DH + dd;
+                float ov = 0.0f;
+#pragma unroll 6
+                for (int sidx = 0; sidx < ph.nsplit; sidx++) ov = fmaf(__ldcg(pa + (size_t)sidx * DH), wgt[i * ph.nsplit + sidx], ov);
+                ph.ctx[(size_t)(ap.kv * GRP + i) * DH + dd] = ov;
+            }
+            if (tid == 0) P.attn_cnt[ap.kv] = 0u;
+        }
+    }
+    return true;
+}

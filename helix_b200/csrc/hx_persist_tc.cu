@@ -150,6 +150,7 @@ struct SmemTc {
     float att_m[8], att_l[8], att_r[8];
     float bv[NCW]; int bi[NCW];
     float swi[128];
+    HxPhase ph[2];                  // descriptor of the running phase (pi & 1), the next one is fetched during the grid barrier
     unsigned ticket, eticket;
     uint32_t tmem_base;
     volatile int abort_flag;
@@ -199,9 +200,27 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 return true;
             };
             bool ok = true;
+            // the descriptor of the next phase is loaded one phase early so that streaming never waits for it
+            HxPhase nxt = P.phases[0];
 #pragma unroll 1
             for (int pi = 0; pi < P.nphases && ok; pi++) {
-                const HxPhase& ph = P.phases[pi];
+                const HxPhase ph = nxt;
+                if (pi + 1 < P.nphases) {
+                    nxt = P.phases[pi + 1];
+                    // one CTA per phase pulls the small vectors of the next phase into L2 (they were evicted by a
+                    // token's worth of weights since their last use)
+                    if (cta == (pi % grid)) {
+                        const HxPhase& q = P.phases[pi + 1];
+                        if (q.type == HX_PH_LINEAR_TC) {
+                            if (q.norm == HX_NORM_RMS && q.g) l2_prefetch(q.g, (uint32_t)q.K * 4u);
+                            if (q.epi == HX_EPI_QKV) {
+                                if (q.qn_g) l2_prefetch(q.qn_g, (uint32_t)q.DH * 4u);
+                                if (q.kn_g) l2_prefetch(q.kn_g, (uint32_t)q.DH * 4u);
+                                if (q.cosT) { l2_prefetch(q.cosT + (size_t)pos * (q.DH >> 1), (uint32_t)q.DH * 2u); l2_prefetch(q.sinT + (size_t)pos * (q.DH >> 1), (uint32_t)q.DH * 2u); }
+                            }
+                        }
+                    }
+                }
                 if (ph.type == HX_PH_LINEAR_TC) {
                     const TcPlan tp = tc_plan(ph, cta, grid);
                     const uint8_t* src = ph.w + (size_t)tp.b0 * HX_T128_CELL;
@@ -237,7 +256,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                     ok = mbar_wait(&S.b_ready, tcph & 1, &S.abort_flag);        // digit columns of this phase are in place
                     tcph++;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const TcPlan tp = tc_plan(ph, cta, grid);
+                    const TcPlan tp = tc_plan(S.ph[pi & 1], cta, grid);          // the consumers' copy is in place with the digits
                     int kc = tp.k0, dp = 0;              // K cell of the tile, its position among the digit cells
                     bool fresh = true;
                     uint32_t dcol = 0;
@@ -288,60 +307,60 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
         unsigned long long bar_target = P.bar_base;
         float best_v = -INFINITY; int best_i = INT_MAX;
 
+        constexpr int PH_CHUNKS = (int)(sizeof(HxPhase) / 16);
+        if (tid < PH_CHUNKS) reinterpret_cast<uint4*>(&S.ph[0])[tid] = __ldg(reinterpret_cast<const uint4*>(P.phases) + tid);
+        consumer_sync();
 #pragma unroll 1
         for (int pi = 0; pi < P.nphases; pi++) {
-            const HxPhase& ph = P.phases[pi];
+            const HxPhase& ph = S.ph[pi & 1];
             STAMP(0);
             if (ph.type == HX_PH_LINEAR_TC) {
                 // ---------- prologue: x -> (norm) -> sixteen base-4 digit columns in operand layout ----------
-                // A thread owns items of 8 consecutive elements; up to XI items stay in registers between the
-                // statistics pass and the digit pass (one L2 round trip); longer vectors are read twice.
-                const int K = ph.K, Kt = ph.ksteps * 64;
+                // Pass 1 (all of x): sum of squares and largest magnitude of x*g.  Pass 2: every thread turns items
+                // of 8 consecutive elements of the K cells this CTA streams into digit words; the first item is
+                // fetched before pass 1 so that its latency hides behind it.  Loops are kept rolled: this code runs
+                // once per phase and is bound by instruction fetch, not by arithmetic.
+                const int K = ph.K;
                 const TcPlan tp = tc_plan(ph, cta, grid);
                 const float* xin = ph.x;
                 if (ph.tok) xin = ph.x + (size_t)(ph.tok[P.tok_by_pos ? pos : 0]) * K;
-                constexpr int XI = 3;
-                const bool inreg = Kt <= NCT * 8 * XI;
-                float xv[XI][8];
+                const bool rms = ph.norm == HX_NORM_RMS;
+                const int nitems = tp.run * 32;
+                auto item_k = [&](int it) { int kc = tp.k0 + (it >> 5); if (kc >= tp.C) kc -= tp.C; return kc * 256 + (it & 31) * 8; };
+                float4 ia = make_float4(0.f, 0.f, 0.f, 0.f), ib = ia, ja = make_float4(1.f, 1.f, 1.f, 1.f), jb = ja;
+                if (tid < nitems) {
+                    const int k = item_k(tid);
+                    if (k < K) {
+                        ia = __ldcg(reinterpret_cast<const float4*>(xin + k));
+                        if (k + 4 < K) ib = __ldcg(reinterpret_cast<const float4*>(xin + k + 4));
+                        if (rms) { ja = *reinterpret_cast<const float4*>(ph.g + k); if (k + 4 < K) jb = *reinterpret_cast<const float4*>(ph.g + k + 4); }
+                    }
+                }
                 float inv = 1.0f, Sg = 1.0f;
                 {
                     float ss = 0.0f, mx = 0.0f;
-                    if (inreg) {
+#pragma unroll 1
+                    for (int k0 = tid * 4; k0 < K; k0 += NCT * 4 * 3) {
+                        float4 v[3], gq[3];
 #pragma unroll
-                        for (int i = 0; i < XI; i++) {
-                            const int k = (tid + i * NCT) * 8;
-                            float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-                            if (k < K) { a = __ldcg(reinterpret_cast<const float4*>(xin + k)); b = __ldcg(reinterpret_cast<const float4*>(xin + k + 4)); }
-                            xv[i][0] = a.x; xv[i][1] = a.y; xv[i][2] = a.z; xv[i][3] = a.w; xv[i][4] = b.x; xv[i][5] = b.y; xv[i][6] = b.z; xv[i][7] = b.w;
-                        }
-#pragma unroll
-                        for (int i = 0; i < XI; i++) {
-                            const int k = (tid + i * NCT) * 8;
+                        for (int u = 0; u < 3; u++) {
+                            const int k = k0 + u * NCT * 4;
+                            v[u] = make_float4(0.f, 0.f, 0.f, 0.f); gq[u] = v[u];
                             if (k < K) {
-                                if (ph.tok && ph.x_out && ((k >> 3) % grid) == cta) {
-                                    *reinterpret_cast<float4*>(ph.x_out + k) = make_float4(xv[i][0], xv[i][1], xv[i][2], xv[i][3]);
-                                    *reinterpret_cast<float4*>(ph.x_out + k + 4) = make_float4(xv[i][4], xv[i][5], xv[i][6], xv[i][7]);
-                                }
-                                if (ph.norm == HX_NORM_RMS) {
-                                    const float4 ga = *reinterpret_cast<const float4*>(ph.g + k), gb = *reinterpret_cast<const float4*>(ph.g + k + 4);
-                                    const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
-#pragma unroll
-                                    for (int e = 0; e < 8; e++) { ss = fmaf(xv[i][e], xv[i][e], ss); xv[i][e] *= gg[e]; }
-                                }
-#pragma unroll
-                                for (int e = 0; e < 8; e++) mx = fmaxf(mx, fabsf(xv[i][e]));
+                                v[u] = __ldcg(reinterpret_cast<const float4*>(xin + k));
+                                if (rms) gq[u] = *reinterpret_cast<const float4*>(ph.g + k);
                             }
                         }
-                    } else {
-#pragma unroll 1
-                        for (int k = tid * 4; k < K; k += NCT * 4) {
-                            const float4 v = __ldcg(reinterpret_cast<const float4*>(xin + k));
-                            if (ph.tok && ph.x_out && ((k >> 2) % grid) == cta) *reinterpret_cast<float4*>(ph.x_out + k) = v;
-                            if (ph.norm == HX_NORM_RMS) {
-                                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                                const float4 gg = *reinterpret_cast<const float4*>(ph.g + k);
-                                mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x * gg.x), fabsf(v.y * gg.y)), fmaxf(fabsf(v.z * gg.z), fabsf(v.w * gg.w))));
-                            } else mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+#pragma unroll
+                        for (int u = 0; u < 3; u++) {
+                            const int k = k0 + u * NCT * 4;
+                            if (k < K) {
+                                if (ph.tok && ph.x_out && ((k >> 2) % grid) == cta) *reinterpret_cast<float4*>(ph.x_out + k) = v[u];
+                                if (rms) {
+                                    ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+                                    mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v[u].x * gq[u].x), fabsf(v[u].y * gq[u].y)), fmaxf(fabsf(v[u].z * gq[u].z), fabsf(v[u].w * gq[u].w))));
+                                } else mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
+                            }
                         }
                     }
                     ss = hx_warp_sum(ss); mx = hx_warp_max(mx);
@@ -350,56 +369,40 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                     float tss = 0.0f, tmx = 0.0f;
 #pragma unroll
                     for (int i = 0; i < NCW; i++) { tss += S.red[i]; tmx = fmaxf(tmx, S.red[NCW + i]); }
-                    if (ph.norm == HX_NORM_RMS) inv = rsqrtf(tss / (float)K + ph.eps);
+                    if (rms) inv = rsqrtf(tss / (float)K + ph.eps);
                     const float vmax = tmx * inv * 1.0000005f;            // margin for the rounding of x*g*inv
                     if (vmax > 0.0f && vmax < INFINITY) Sg = __uint_as_float(__float_as_uint(vmax) & 0x7F800000u);   // vmax/Sg in [1,2)
                 }
                 const float mul = (inv / Sg) * 2147483648.0f;             // |x_n| / Sg * 2^31 < 2^32
-                auto emit = [&](int k, const float (&v)[8]) {
-                    const int j = (k >> 5) & 7, w = (k >> 3) & 3;                 // 16-byte chunk, word
-                    int dp = (k >> 8) - tp.k0; if (dp < 0) dp += tp.C;             // position of the 256-column cell in this CTA's run
-                    if (dp >= tp.run) return;                                      // a cell this CTA does not stream
+#pragma unroll 1
+                for (int it = tid; it < nitems; it += NCT) {
+                    const int k = item_k(it);
+                    if (it != tid) {                                       // later items of a long run: fetched here
+                        ia = make_float4(0.f, 0.f, 0.f, 0.f); ib = ia; ja = make_float4(1.f, 1.f, 1.f, 1.f); jb = ja;
+                        if (k < K) {
+                            ia = __ldcg(reinterpret_cast<const float4*>(xin + k));
+                            if (k + 4 < K) ib = __ldcg(reinterpret_cast<const float4*>(xin + k + 4));
+                            if (rms) { ja = *reinterpret_cast<const float4*>(ph.g + k); if (k + 4 < K) jb = *reinterpret_cast<const float4*>(ph.g + k + 4); }
+                        }
+                    }
+                    const float v[8] = {ia.x * ja.x, ia.y * ja.y, ia.z * ja.z, ia.w * ja.w, ib.x * jb.x, ib.y * jb.y, ib.z * jb.z, ib.w * jb.w};
                     uint32_t M[8]; uint32_t sg = 0u;
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
                         M[e] = __float2uint_rn(fabsf(v[e]) * mul);
                         sg |= (v[e] < 0.0f ? 8u : 0u) << (4 * e);
                     }
-                    uint8_t* dst = digb + (size_t)dp * 2048 + w * 4;
-#pragma unroll
+                    // digit n of element e is bits 31-2n, 30-2n of M[e]; it lands on bits 4e+1, 4e of the word of row n
+                    const int j = (it >> 2) & 7, w = it & 3;               // 16-byte chunk and word of this item in its cell
+                    uint8_t* dst = digb + (size_t)(it >> 5) * 2048 + w * 4;
+#pragma unroll 2
                     for (int n = 0; n < TC_NDIG; n++) {
                         uint32_t word = 0u;
 #pragma unroll
-                        for (int e = 0; e < 8; e++) {
-                            const int sh = 30 - 2 * n - 4 * e;           // digit n of element e lands on nibble e
-                            word |= (sh >= 0 ? (M[e] >> sh) : (M[e] << (-sh))) & (3u << (4 * e));
-                        }
+                        for (int e = 0; e < 8; e++) word |= ((M[e] >> (30 - 2 * n)) & 3u) << (4 * e);
                         const uint32_t nz = (word | (word >> 1)) & 0x11111111u;   // a zero digit carries no sign
                         word |= sg & (nz << 3);
                         *reinterpret_cast<uint32_t*>(dst + n * 128 + ((j ^ (n & 7)) << 4)) = word;
-                    }
-                };
-                if (inreg) {
-#pragma unroll
-                    for (int i = 0; i < XI; i++) {
-                        const int k = (tid + i * NCT) * 8;
-                        if (k < Kt) emit(k, xv[i]);                        // elements at or beyond K are zero
-                    }
-                } else {
-#pragma unroll 1
-                    for (int it = tid; it < tp.run * 32; it += NCT) {
-                        int kc = tp.k0 + (it >> 5); if (kc >= tp.C) kc -= tp.C;
-                        const int k = kc * 256 + (it & 31) * 8;
-                        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        if (k < K) {
-                            float4 a = __ldcg(reinterpret_cast<const float4*>(xin + k)), b = __ldcg(reinterpret_cast<const float4*>(xin + k + 4));
-                            if (ph.norm == HX_NORM_RMS) {
-                                const float4 ga = *reinterpret_cast<const float4*>(ph.g + k), gb = *reinterpret_cast<const float4*>(ph.g + k + 4);
-                                a.x *= ga.x; a.y *= ga.y; a.z *= ga.z; a.w *= ga.w; b.x *= gb.x; b.y *= gb.y; b.z *= gb.z; b.w *= gb.w;
-                            }
-                            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-                        }
-                        emit(k, v);
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -417,7 +420,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
 #pragma unroll 1
                     for (int tile = t_first; tile <= t_last; tile++) {
                         const uint32_t buf = uc & 1u;
-                        if (!mbar_wait(&S.acc_full[buf], (uc >> 1) & 1, &S.abort_flag)) goto aborted;
+                        if (!mbar_wait(&S.acc_full[buf], (uc >> 1) & 1, &S.abort_flag)) break;   // flag is latched; leave with the others at the barrier
                         uc++;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         uint32_t r[16];
@@ -440,17 +443,52 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                         if (c1 != c0) {
                             float* pp = P.tc_partial + ((size_t)tile * ph.pieces) * 128;
                             pp[(size_t)(cta - c0) * 128 + rl] = v;
-                            __threadfence();
                             epi_sync();
-                            if (tid == 0) S.eticket = atomicAdd(P.tc_cnt + tile, 1u);
+                            if (tid == 0) S.eticket = ticket_acq_rel(P.tc_cnt + tile);
                             epi_sync();
                             if (S.eticket != (unsigned)(c1 - c0)) continue;          // a later piece finishes the tile
-                            __threadfence();
                             v = 0.0f;
                             for (int q = 0; q <= c1 - c0; q++) v += __ldcg(pp + (size_t)q * 128 + rl);
                             if (tid == 0) P.tc_cnt[tile] = 0u;
                         }
-                        if (ph.epi == HX_EPI_SWIGLU) {
+                        if (ph.epi == HX_EPI_QKV) {
+                            // A tile holds 128 / DH whole heads (DH is 32, 64 or 128).  Per-head RMSNorm and rotate_half
+                            // RoPE on q and k; q goes to the qkv buffer, k and v to the cache row of this position.
+                            const int DH = ph.DH, half = DH >> 1, QD = ph.NH * DH, KVD = ph.NKV * DH;
+                            const int row = tile * 128 + rl;
+                            const bool valid = row < ph.N;
+                            const int sec = row < QD ? 0 : (row < QD + KVD ? 1 : 2);
+                            const int e = row % DH;
+                            v = valid ? v * ph.ts[sec] : 0.0f;
+                            const float* gg = sec == 0 ? ph.qn_g : (sec == 1 ? ph.kn_g : nullptr);
+                            float ssq = hx_warp_sum(v * v);
+                            if (DH > 32) {
+                                if (lane == 0) S.swi[warp] = ssq;
+                                epi_sync();
+                                const int w0 = (rl / DH) * (DH >> 5);
+                                ssq = 0.0f;
+                                for (int j = 0; j < (DH >> 5); j++) ssq += S.swi[w0 + j];
+                                epi_sync();
+                            }
+                            if (gg) v = gg[e] * (v * rsqrtf(ssq / (float)DH + ph.eps));
+                            if (ph.cosT) {                       // every thread meets the barriers, v rows keep their value
+                                S.swi[rl] = v;
+                                epi_sync();
+                                const float other = S.swi[e < half ? rl + half : rl - half];
+                                const float cs = ph.cosT[(size_t)pos * half + (e < half ? e : e - half)];
+                                const float sn = ph.sinT[(size_t)pos * half + (e < half ? e : e - half)];
+                                if (sec < 2) v = e < half ? v * cs - other * sn : v * cs + other * sn;
+                                epi_sync();
+                            }
+                            if (valid) {
+                                if (sec == 0) ph.y[row] = v;
+                                else {
+                                    const int hrow = row - QD - (sec == 2 ? KVD : 0);
+                                    float* dst = sec == 1 ? ph.kc : ph.vc;
+                                    dst[((size_t)(hrow / DH) * ph.cap + pos) * DH + e] = v;
+                                }
+                            }
+                        } else if (ph.epi == HX_EPI_SWIGLU) {
                             // rows 0..63 of a tile are gate rows, 64..127 the matching up rows
                             S.swi[rl] = v * (rl < 64 ? ph.ts[0] : ph.ts[1]);
                             epi_sync();
@@ -510,7 +548,17 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 }
             } else if (ph.type == HX_PH_ATTN) {
                 bool ok;
-                switch (ph.NH / ph.NKV) {
+                if (ph.epi == HX_EPI_QKV) switch (ph.NH / ph.NKV) {
+                    case 1: ok = attention_phase2<1>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                    case 2: ok = attention_phase2<2>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                    case 3: ok = attention_phase2<3>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                    case 4: ok = attention_phase2<4>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                    case 5: ok = attention_phase2<5>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                    case 6: ok = attention_phase2<6>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                    case 7: ok = attention_phase2<7>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                    default: ok = attention_phase2<8>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                }
+                else switch (ph.NH / ph.NKV) {
                     case 1: ok = attention_phase<1, 1>(P, ph, S, ring, digb, ctr, pi, pos); break;
                     case 2: ok = attention_phase<2, 1>(P, ph, S, ring, digb, ctr, pi, pos); break;
                     case 3: ok = attention_phase<3, 1>(P, ph, S, ring, digb, ctr, pi, pos); break;
@@ -523,13 +571,17 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 if (!ok) goto aborted;
             }
             STAMP(2);
+            STAMP_ALL();
             // ---------- grid barrier ----------
             if (pi + 1 < P.nphases) {
-                __threadfence();
-                consumer_sync();
+                // the next descriptor travels to shared memory while the barrier is pending
+                if (tid < PH_CHUNKS)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(reinterpret_cast<uint4*>(&S.ph[(pi + 1) & 1]) + tid)),
+                                 "l"(reinterpret_cast<const uint4*>(P.phases + pi + 1) + tid) : "memory");
+                consumer_sync();                 // every thread's results are ordered before thread 0's release below
                 bar_target += (unsigned long long)grid;
                 if (tid == 0) {
-                    atomicAdd(P.bar, 1ull);
+                    asm volatile("red.release.gpu.global.add.u64 [%0], 1;" :: "l"(P.bar) : "memory");
                     bool ok = false;
                     for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
                         unsigned long long v;
@@ -539,11 +591,13 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                     }
                     if (!ok) S.abort_flag = 1;
                 }
+                asm volatile("cp.async.wait_all;" ::: "memory");
                 consumer_sync();
                 if (S.abort_flag) goto aborted;
             }
             STAMP(3);
         }
+        if (S.abort_flag) goto aborted;
         if (P.advance_pos && cta == 0 && tid == 0) *P.pos_inc = pos + 1;
         goto done;
 aborted:
