@@ -4,7 +4,8 @@
 #include "hx_common.cuh"
 
 // ---- fused dequant linear over the dense decode layout -----------------------------------------
-enum { HX_NORM_NONE = 0, HX_NORM_RMS = 1, HX_NORM_LAYER = 2 };
+enum { HX_NORM_NONE = 0, HX_NORM_RMS = 1, HX_NORM_LAYER = 2,
+       HX_NORM_ATTN = 3 };   // persistent tensor-core kernel: x is the merge of the attention splits' partial outputs
 enum {
     HX_EPI_STORE = 0,     // y[n] = acc (+ bias)
     HX_EPI_RESID = 1,     // y[n] = resid[n] + acc (+ bias)      (y may alias resid)

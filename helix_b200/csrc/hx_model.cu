@@ -65,7 +65,7 @@ struct hx_model {
     // decode state
     float *x = nullptr, *qkv = nullptr, *q_rot = nullptr, *ctx = nullptr, *h = nullptr, *logits = nullptr;
     float *kc = nullptr, *vc = nullptr, *cosT = nullptr, *sinT = nullptr;
-    float *part_m = nullptr, *part_l = nullptr, *part_acc = nullptr; unsigned* attn_cnt = nullptr;
+    float *part_m = nullptr, *part_l = nullptr, *part_acc = nullptr, *part_amax = nullptr; unsigned* attn_cnt = nullptr;
     float* am_val = nullptr; int* am_idx = nullptr; unsigned* am_cnt = nullptr;
     int *d_tok = nullptr, *d_pos = nullptr, *d_hist = nullptr, *d_prompt = nullptr;
     int nsplit = 1;
@@ -304,6 +304,7 @@ int alloc_state(hx_model* m) {
     if ((rc = dalloc(m, &m->part_m, (size_t)NH * m->nsplit))) return rc;
     if ((rc = dalloc(m, &m->part_l, (size_t)NH * m->nsplit))) return rc;
     if ((rc = dalloc(m, &m->part_acc, (size_t)NH * m->nsplit * DH))) return rc;
+    if ((rc = dalloc(m, &m->part_amax, (size_t)NH * m->nsplit))) return rc;
     if ((rc = dalloc(m, &m->attn_cnt, (size_t)NKV))) return rc;
     HX_CUDA(cudaMemset(m->attn_cnt, 0, (size_t)NKV * 4));
     if ((rc = dalloc(m, &m->am_val, (size_t)4096))) return rc;
@@ -457,6 +458,12 @@ int build_phases(hx_model* m, bool from_prompt, bool with_head, HxPhase** out, i
         at.nsplit = m->nsplit_persist; at.scale = 1.0f / sqrtf((float)DH); at.eps = c.norm_eps;
         v.push_back(at);
         HxPhase o = linear(ly.o, m->ctx, m->x, HX_EPI_RESID, ly.o.N);
+        // the o_proj prologue merges the attention splits itself (no merging CTA on the critical path)
+        const bool defer_merge = fuse_qk && (size_t)c.n_heads * m->nsplit_persist <= 2304 && DH % 8 == 0;
+        if (defer_merge) {
+            v.back().pieces = 1;                       // attention phase: leave the partials unmerged
+            o.norm = HX_NORM_ATTN; o.NH = c.n_heads; o.NKV = c.n_kv_heads; o.DH = DH; o.nsplit = m->nsplit_persist;
+        }
         v.push_back(o);
         HxPhase gu = linear(ly.gu, m->x, m->h, HX_EPI_SWIGLU, c.d_ff);
         gu.norm = HX_NORM_RMS; gu.g = ly.post_g; gu.eps = c.norm_eps;
@@ -519,7 +526,7 @@ int persist_step(hx_model* m, bool from_prompt, bool with_head) {
     P.nphases = from_prompt ? m->nph_prefill : m->nph_decode;
     (void)with_head;
     P.pos = m->d_pos; P.bar = m->d_bar; P.bar_base = m->bar_count; P.err = m->d_err;
-    P.part_m = m->part_m; P.part_l = m->part_l; P.part_acc = m->part_acc; P.attn_cnt = m->attn_cnt;
+    P.part_m = m->part_m; P.part_l = m->part_l; P.part_acc = m->part_acc; P.part_amax = m->part_amax; P.attn_cnt = m->attn_cnt;
     P.am_val = m->am_val; P.am_idx = m->am_idx; P.am_cnt = m->am_cnt; P.next_tok = m->d_tok; P.pos_inc = m->d_pos;
     P.hist = m->d_hist; P.logits = m->logits; P.dig_bytes = m->dig_bytes;
     P.tok_by_pos = from_prompt ? 1 : 0; P.advance_pos = from_prompt ? 1 : 0;

@@ -63,6 +63,7 @@ struct HxPersist {
     int* err;                             // set non-zero when a bounded wait ran out
     // attention scratch
     float* part_m; float* part_l; float* part_acc; unsigned* attn_cnt;
+    float* part_amax;                     // per (head, split): largest |partial output| / l, bounds the merged output
     // arg-max
     float* am_val; int* am_idx; unsigned* am_cnt; int* next_tok; int* pos_inc; int* hist; float* logits;
     int dig_bytes;                        // shared-memory bytes reserved for the f16 split of x

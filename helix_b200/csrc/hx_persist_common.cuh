@@ -288,18 +288,31 @@ __device__ __forceinline__ unsigned ticket_acq_rel(unsigned* cnt) {
 // head dimension rotated by their position so that shared-memory accesses do not collide --, soft-max
 // statistics by one warp per head, then P*V with one thread per (head, dimension).
 // ------------------------------------------------------------------------------------------------
+// Tiles of attention_phase2: up to ATT2_TR ring slots of K rows, then as many of V rows.
+#define ATT2_TR 4
+struct AttPlan2 { int tr, tile_rows, ntiles; };
+__device__ __forceinline__ AttPlan2 att_plan2(const AttPlan& ap, int nring) {
+    AttPlan2 q;
+    q.tr = min(min(ATT2_TR, nring / 2), 159 / ap.rows_per_slot);
+    if (q.tr < 1) q.tr = 1;
+    q.tile_rows = q.tr * ap.rows_per_slot;
+    q.ntiles = (ap.n_old + q.tile_rows - 1) / q.tile_rows;
+    return q;
+}
+
 template <int GRP, class SM>
 __device__ __noinline__ bool attention_phase2(const HxPersist& P, const HxPhase& ph, SM& S, uint8_t* ring, uint8_t* digb,
                                               uint32_t& ctr, int pi, int pos) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, cta = blockIdx.x;
     const AttPlan ap = att_plan(ph, cta, pos);
-    const int DH = ph.DH;
+    const AttPlan2 ap2 = att_plan2(ap, (int)RING_SLOTS);
+    const int DH = ph.DH, rps = ap.rows_per_slot;
     float* sq = reinterpret_cast<float*>(digb);                 // [GRP][DH] queries
     float* knew = sq + 8 * 256;                                  // [DH] current k
     float* vnew = knew + 256;                                    // [DH] current v
-    float* sp = vnew + 256;                                      // [GRP][rows_per_slot + 1] scores / probabilities
+    float* sp = vnew + 256;                                      // [GRP][160] scores / probabilities
     float* accx = sp + 8 * 160;                                  // [nsub][GRP*DH] partial outputs (small heads only)
-    const int spitch = ap.rows_per_slot + 1;
+    constexpr int spitch = 160;
     const int HD = GRP * DH;
     constexpr int NACC = (GRP * 256 + NCT - 1) / NCT;           // (head, dim) pairs per thread when GRP*DH > NCT
     const int nsub = HD < NCT ? NCT / HD : 1;                    // position subsets when threads outnumber the pairs
@@ -313,21 +326,25 @@ __device__ __noinline__ bool attention_phase2(const HxPersist& P, const HxPhase&
             const size_t o = ((size_t)ap.kv * ph.cap + pos) * DH;
             for (int e = tid; e < DH; e += NCT) { knew[e] = __ldcg(ph.kc + o + e); vnew[e] = __ldcg(ph.vc + o + e); }
         }
-        if (tid < 8) { S.att_m[tid] = -100000000.0f; S.att_l[tid] = 0.0f; }
+        if (tid < 8) { S.att_m[tid] = -100000000.0f; S.att_l[tid] = 0.0f; S.att_ax[tid] = 0u; }
         consumer_sync();
         STAMP(4);
-        const int ntile = ap.nslots + ((ap.has_new && ap.n_old % ap.rows_per_slot == 0) ? 1 : 0);
+        const int ntile = ap2.ntiles + ((ap.has_new && ap.n_old % ap2.tile_rows == 0) ? 1 : 0);
         #pragma unroll 1
         for (int s = 0; s < ntile; s++) {
-            const bool ring_tile = s < ap.nslots;
-            const int nr = ring_tile ? min(ap.rows_per_slot, ap.n_old - s * ap.rows_per_slot) : 0;
+            const bool ring_tile = s < ap2.ntiles;
+            const int nr = ring_tile ? min(ap2.tile_rows, ap.n_old - s * ap2.tile_rows) : 0;
+            const int nsl = (nr + rps - 1) / rps;                       // ring slots of this tile (K, then as many of V)
             const bool add_new = ap.has_new && (s == ntile - 1);       // the current position rides on the last tile
-            uint32_t kslot = 0, vslot = 0;
-            const float* kt = nullptr; const float* vt = nullptr;
-            if (ring_tile) {
-                kslot = ctr % RING_SLOTS; const uint32_t kround = ctr / RING_SLOTS; ctr++;
-                if (!mbar_wait(&S.full[kslot], kround & 1, &S.abort_flag)) return false;
-                kt = reinterpret_cast<const float*>(ring + (size_t)kslot * HX_RING_SLOT);
+            const float* kp[ATT2_TR]; uint32_t ks[ATT2_TR];
+#pragma unroll
+            for (int j = 0; j < ATT2_TR; j++) {
+                kp[j] = knew; ks[j] = 0;
+                if (j < nsl) {
+                    ks[j] = ctr % RING_SLOTS; const uint32_t round = ctr / RING_SLOTS; ctr++;
+                    if (!mbar_wait(&S.full[ks[j]], round & 1, &S.abort_flag)) return false;
+                    kp[j] = reinterpret_cast<const float*>(ring + (size_t)ks[j] * HX_RING_SLOT);
+                }
             }
             if (s == 0) STAMP(8);
             const int ntot = nr + (add_new ? 1 : 0);
@@ -335,12 +352,13 @@ __device__ __noinline__ bool attention_phase2(const HxPersist& P, const HxPhase&
             #pragma unroll 1
             for (int it = tid; it < GRP * ntot; it += NCT) {
                 const int i = it / ntot, r = it - i * ntot;
-                const float* kr = (r < nr) ? kt + (size_t)r * DH : knew;
+                const int j = (r >= rps) + (r >= 2 * rps) + (r >= 3 * rps);
+                const float* kr = (r < nr) ? (j == 0 ? kp[0] : j == 1 ? kp[1] : j == 2 ? kp[2] : kp[3]) + (size_t)(r - j * rps) * DH : knew;
                 const float* qi = sq + i * DH;
                 float d0 = 0.0f, d1 = 0.0f;
                 int e = (4 * r) % DH;
                 #pragma unroll 4
-                for (int j = 0; j < DH; j += 4) {
+                for (int jj = 0; jj < DH; jj += 4) {
                     const float4 k4 = *reinterpret_cast<const float4*>(kr + e);
                     const float4 q4 = *reinterpret_cast<const float4*>(qi + e);
                     d0 = fmaf(q4.x, k4.x, d0); d1 = fmaf(q4.y, k4.y, d1); d0 = fmaf(q4.z, k4.z, d0); d1 = fmaf(q4.w, k4.w, d1);
@@ -349,7 +367,7 @@ __device__ __noinline__ bool attention_phase2(const HxPersist& P, const HxPhase&
                 sp[i * spitch + r] = (d0 + d1) * ph.scale;
             }
             consumer_sync();
-            if (ring_tile && tid == 0) mbar_arrive(&S.empty[kslot]);
+            if (tid < nsl) mbar_arrive(&S.empty[tid == 0 ? ks[0] : tid == 1 ? ks[1] : tid == 2 ? ks[2] : ks[3]]);
             if (s == 0) STAMP(9);
             // online softmax state per head (fused_decode_attn_kernel.hx:74-102)
             if (warp < GRP) {
@@ -363,10 +381,14 @@ __device__ __noinline__ bool attention_phase2(const HxPersist& P, const HxPhase&
                 ls = hx_warp_sum(ls);
                 if (lane == 0) { const float rr = __expf(mo - mn); S.att_r[i] = rr; S.att_l[i] = S.att_l[i] * rr + ls; S.att_m[i] = mn; }
             }
-            if (ring_tile) {
-                vslot = ctr % RING_SLOTS; const uint32_t vround = ctr / RING_SLOTS; ctr++;
-                if (!mbar_wait(&S.full[vslot], vround & 1, &S.abort_flag)) return false;
-                vt = reinterpret_cast<const float*>(ring + (size_t)vslot * HX_RING_SLOT);
+#pragma unroll
+            for (int j = 0; j < ATT2_TR; j++) {
+                kp[j] = vnew;
+                if (j < nsl) {
+                    ks[j] = ctr % RING_SLOTS; const uint32_t round = ctr / RING_SLOTS; ctr++;
+                    if (!mbar_wait(&S.full[ks[j]], round & 1, &S.abort_flag)) return false;
+                    kp[j] = reinterpret_cast<const float*>(ring + (size_t)ks[j] * HX_RING_SLOT);
+                }
             }
             consumer_sync();
             if (s == 0) STAMP(10);
@@ -377,16 +399,19 @@ __device__ __noinline__ bool attention_phase2(const HxPersist& P, const HxPhase&
                 if (hd < HD && sub < nsub) {
                     const int i = hd / DH, d = hd - i * DH;
                     float v = acc[a] * S.att_r[i];
-                    #pragma unroll 4
-                    for (int r = sub; r < ntot; r += nsub) {
-                        const float vv = (r < nr) ? vt[(size_t)r * DH + d] : vnew[d];
-                        v = fmaf(sp[i * spitch + r], vv, v);
+#pragma unroll
+                    for (int j = 0; j < ATT2_TR; j++) {
+                        const int r1 = min(nr, (j + 1) * rps);
+                        const float* vj = kp[j] + d - (size_t)(j * rps) * DH;
+                        #pragma unroll 4
+                        for (int r = j * rps + sub; r < r1; r += nsub) v = fmaf(sp[i * spitch + r], vj[(size_t)r * DH], v);
                     }
+                    if (add_new && (nr % nsub) == sub) v = fmaf(sp[i * spitch + nr], vnew[d], v);
                     acc[a] = v;
                 }
             }
             consumer_sync();
-            if (ring_tile && tid == 0) mbar_arrive(&S.empty[vslot]);
+            if (tid < nsl) mbar_arrive(&S.empty[tid == 0 ? ks[0] : tid == 1 ? ks[1] : tid == 2 ? ks[2] : ks[3]]);
         }
         STAMP(5);
         // write this split's partial (position subsets folded through shared memory first)
@@ -407,6 +432,15 @@ __device__ __noinline__ bool attention_phase2(const HxPersist& P, const HxPhase&
                 const size_t hs = (size_t)(ap.kv * GRP + i) * ph.nsplit + ap.split;
                 P.part_acc[hs * DH + d] = acc[a];
                 if (d == 0) { P.part_m[hs] = S.att_m[i]; P.part_l[hs] = S.att_l[i]; }
+                if (ph.pieces) atomicMax(&S.att_ax[i], __float_as_uint(fabsf(acc[a])));
+            }
+        }
+        if (ph.pieces) {          // bound of this split's contribution to the merged output: max |acc| / l
+            consumer_sync();
+            if (tid < GRP) {
+                const size_t hs = (size_t)(ap.kv * GRP + tid) * ph.nsplit + ap.split;
+                const float l = S.att_l[tid];
+                P.part_amax[hs] = l > 0.0f ? __uint_as_float(S.att_ax[tid]) / l : 0.0f;
             }
         }
     } else if (ap.active) {
@@ -414,23 +448,32 @@ __device__ __noinline__ bool attention_phase2(const HxPersist& P, const HxPhase&
         for (int i = tid; i < GRP; i += NCT) {
             const size_t hs = (size_t)(ap.kv * GRP + i) * ph.nsplit + ap.split;
             P.part_m[hs] = -100000000.0f; P.part_l[hs] = 0.0f;
+            if (ph.pieces) P.part_amax[hs] = 0.0f;
         }
         for (int i = tid; i < GRP * DH; i += NCT) {
             const size_t hs = (size_t)(ap.kv * GRP + i / DH) * ph.nsplit + ap.split;
             P.part_acc[hs * DH + i % DH] = 0.0f;
         }
     }
-    if (ap.active) {
+    if (ap.active && !ph.pieces) {
         STAMP(6);
         consumer_sync();
         if (tid == 0) S.ticket = ticket_acq_rel(P.attn_cnt + ap.kv);
         consumer_sync();
         STAMP(7);
         if (S.ticket == (unsigned)ph.nsplit - 1) {
-            // merge of the splits: weights w_s = exp(m_s - M) / sum_s l_s exp(m_s - M), then one pass
-            // of independent loads over the partial outputs
+            // merge of the splits: weights w_s = exp(m_s - M) / sum_s l_s exp(m_s - M).  The loads of the partial
+            // outputs are issued first so that the weights are computed while they travel.
             float* wgt = sp;                                   // [GRP][nsplit]
             const size_t hbase = (size_t)(ap.kv * GRP) * ph.nsplit;
+            constexpr int MCH = 24;
+            float pv[MCH];
+            const int o0 = tid, i0 = o0 / DH, dd0 = o0 - i0 * DH;
+            const float* pa0 = P.part_acc + (hbase + (size_t)i0 * ph.nsplit) * DH + dd0;
+            if (o0 < HD) {
+#pragma unroll
+                for (int u = 0; u < MCH; u++) pv[u] = u < ph.nsplit ? __ldcg(pa0 + (size_t)u * DH) : 0.0f;
+            }
             #pragma unroll 1
             for (int i = warp; i < GRP; i += NCW) {
                 float mv[2], lv[2];
@@ -446,16 +489,25 @@ __device__ __noinline__ bool attention_phase2(const HxPersist& P, const HxPhase&
                 if (lane < ph.nsplit) wgt[i * ph.nsplit + lane] = w0 / Lsum;
                 if (lane + 32 < ph.nsplit) wgt[i * ph.nsplit + lane + 32] = w1 / Lsum;
             }
+            STAMP(11);
             consumer_sync();
+            STAMP(12);
             #pragma unroll 1
-            for (int o = tid; o < GRP * DH; o += NCT) {
-                const int i = o / DH, dd = o % DH;
+            for (int o = tid; o < HD; o += NCT) {
+                const int i = o / DH, dd = o - i * DH;
                 const float* pa = P.part_acc + (hbase + (size_t)i * ph.nsplit) * DH + dd;
                 float ov = 0.0f;
-#pragma unroll 6
-                for (int sidx = 0; sidx < ph.nsplit; sidx++) ov = fmaf(__ldcg(pa + (size_t)sidx * DH), wgt[i * ph.nsplit + sidx], ov);
+                int s0 = 0;
+                if (o == o0) {
+#pragma unroll
+                    for (int u = 0; u < MCH; u++) if (u < ph.nsplit) ov = fmaf(pv[u], wgt[i * ph.nsplit + u], ov);
+                    s0 = MCH;
+                }
+#pragma unroll 4
+                for (int sidx = s0; sidx < ph.nsplit; sidx++) ov = fmaf(__ldcg(pa + (size_t)sidx * DH), wgt[i * ph.nsplit + sidx], ov);
                 ph.ctx[(size_t)(ap.kv * GRP + i) * DH + dd] = ov;
             }
+            STAMP(13);
             if (tid == 0) P.attn_cnt[ap.kv] = 0u;
         }
     }

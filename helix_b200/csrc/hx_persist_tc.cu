@@ -86,9 +86,19 @@ void hx_repack_t128(const int32_t* words, const uint8_t* micro, int rows, int K,
     HX_COUNT_LAUNCH(1);
 }
 
-// The run of cells of CTA `cta` in a phase of ntiles x C cells, and how a tile is cut into pieces.
+// How a phase of ntiles x C cells is cut over `grid` CTAs.
+//  * few tiles (2 * ntiles <= grid): every tile is cut into P = min(grid / ntiles, C) pieces of nearly equal
+//    length and CTA tile * P + q takes piece q, so each CTA produces exactly one partial sum;
+//  * many tiles: the cells in storage order are cut into `grid` equal contiguous runs (a run may cover the
+//    tail of one tile, whole tiles and the head of another).
+// Returns the most pieces of one tile and the most K cells one CTA touches.
 void hx_tc_split(int ntiles, int C, int grid, int* max_pieces, int* max_run) {
     const long long total = (long long)ntiles * C;
+    if (2 * ntiles <= grid) {
+        int P = grid / ntiles; if (P > C) P = C;
+        *max_pieces = P; *max_run = (C + P - 1) / P;
+        return;
+    }
     if (total < grid) grid = (int)total;          // fewer cells than CTAs: the first `total` CTAs take one cell each
     int mp = 1, mr = 1;
     for (int c = 0; c < grid; c++) {
@@ -125,21 +135,31 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 2, %0;" :: "n"(EPI_WARPS * 32) : "memory"); }
 
 // This CTA's run of cells [b0, b1) of the phase; k0 = K cell of the first one; run = distinct K cells it touches.
-// With fewer cells than CTAs the first `total` CTAs take one cell each (geff = CTAs that hold cells).
-struct TcPlan { long long b0, b1, total; int C, k0, run, geff; };
+// P > 0: every tile is cut into P pieces, CTA tile * P + q takes piece q.  P = 0: equal contiguous runs over geff
+// CTAs (with fewer cells than CTAs the first `total` CTAs take one cell each).
+struct TcPlan { long long b0, b1, total; int C, k0, run, geff, P; };
 __device__ __forceinline__ TcPlan tc_plan(const HxPhase& ph, int cta, int grid) {
     TcPlan p;
     p.C = ph.ksteps >> 2;
     p.total = (long long)ph.ntiles * p.C;
-    p.geff = p.total < grid ? (int)p.total : grid;
-    if (cta < p.geff) { p.b0 = (long long)cta * p.total / p.geff; p.b1 = (long long)(cta + 1) * p.total / p.geff; }
-    else { p.b0 = p.b1 = 0; }
+    p.P = 0; p.geff = grid;
+    if (2 * ph.ntiles <= grid) {
+        p.P = min(grid / ph.ntiles, p.C);
+        if (cta < ph.ntiles * p.P) {
+            const int tile = cta / p.P, q = cta - tile * p.P;
+            p.b0 = (long long)tile * p.C + (q * p.C) / p.P; p.b1 = (long long)tile * p.C + ((q + 1) * p.C) / p.P;
+        } else { p.b0 = p.b1 = 0; }
+    } else {
+        p.geff = p.total < grid ? (int)p.total : grid;
+        if (cta < p.geff) { p.b0 = (long long)cta * p.total / p.geff; p.b1 = (long long)(cta + 1) * p.total / p.geff; }
+        else { p.b0 = p.b1 = 0; }
+    }
     p.k0 = (int)(p.b0 % p.C);
     const long long n = p.b1 - p.b0;
     p.run = n < p.C ? (int)n : p.C;
     return p;
 }
-// CTA whose run holds cell x
+// CTA whose run holds cell x (contiguous runs)
 __device__ __forceinline__ int tc_owner(long long x, long long total, int grid) { return (int)(((x + 1) * grid + total - 1) / total) - 1; }
 
 struct SmemTc {
@@ -147,7 +167,8 @@ struct SmemTc {
     uint64_t empty[HX_TC_MAX_RING];
     uint64_t acc_full[2], acc_empty[2], b_ready;
     float red[NCW * 2];
-    float att_m[8], att_l[8], att_r[8];
+    float att_m[8], att_l[8], att_r[8]; unsigned att_ax[8];
+    float wgt[2304];                // merge weights of the attention splits, [head][split] (o_proj prologue)
     float bv[NCW]; int bi[NCW];
     float swi[128];
     HxPhase ph[2];                  // descriptor of the running phase (pi & 1), the next one is fetched during the grid barrier
@@ -229,6 +250,22 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 } else if (ph.type == HX_PH_ATTN) {
                     const AttPlan ap = att_plan(ph, cta, pos);
                     const size_t rowb = (size_t)ph.DH * 4;
+                    if (ph.epi == HX_EPI_QKV) {
+                        // tiles of up to tr slots of K rows followed by as many of V rows (attention_phase2)
+                        const AttPlan2 ap2 = att_plan2(ap, (int)nring);
+#pragma unroll 1
+                        for (int t = 0; t < ap2.ntiles && ok; t++) {
+                            const int r0 = ap.t0 + t * ap2.tile_rows, nrt = min(ap2.tile_rows, ap.t0 + ap.n_old - r0);
+#pragma unroll 1
+                            for (int kv2 = 0; kv2 < 2 && ok; kv2++) {
+#pragma unroll 1
+                                for (int r = 0; r < nrt && ok; r += ap.rows_per_slot) {
+                                    const size_t off = ((size_t)ap.kv * ph.cap + r0 + r) * ph.DH;
+                                    ok = push((kv2 ? ph.vc : ph.kc) + off, (uint32_t)(min(ap.rows_per_slot, nrt - r) * rowb));
+                                }
+                            }
+                        }
+                    } else
 #pragma unroll 1
                     for (int s = 0; s < ap.nslots && ok; s++) {
                         const int r0 = ap.t0 + s * ap.rows_per_slot, nr = min(ap.rows_per_slot, ap.t0 + ap.n_old - r0);
@@ -328,7 +365,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 const int nitems = tp.run * 32;
                 auto item_k = [&](int it) { int kc = tp.k0 + (it >> 5); if (kc >= tp.C) kc -= tp.C; return kc * 256 + (it & 31) * 8; };
                 float4 ia = make_float4(0.f, 0.f, 0.f, 0.f), ib = ia, ja = make_float4(1.f, 1.f, 1.f, 1.f), jb = ja;
-                if (tid < nitems) {
+                if (tid < nitems && ph.norm != HX_NORM_ATTN) {
                     const int k = item_k(tid);
                     if (k < K) {
                         ia = __ldcg(reinterpret_cast<const float4*>(xin + k));
@@ -337,7 +374,38 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                     }
                 }
                 float inv = 1.0f, Sg = 1.0f;
-                {
+                const bool merge_in = ph.norm == HX_NORM_ATTN;
+                if (merge_in) {
+                    // x is the merge of the attention splits: x[h*DH + d] = sum_s w[h][s] * acc[h][s][d] with
+                    // w[h][s] = exp(m_s - M_h) / sum_s l_s exp(m_s - M_h).  Weights of all heads go to shared memory;
+                    // the magnitude bound comes from the per-split bounds (the merge is a convex combination).
+                    const int NS = ph.nsplit;
+                    float mx = 0.0f;
+                    for (int i = tid; i < ph.NH * NS; i += NCT) mx = fmaxf(mx, __ldcg(P.part_amax + i));
+                    #pragma unroll 1
+                    for (int h = warp; h < ph.NH; h += NCW) {
+                        float mv[2], lv[2];
+#pragma unroll
+                        for (int j = 0; j < 2; j++) {
+                            const int sidx = lane + 32 * j;
+                            mv[j] = sidx < NS ? __ldcg(P.part_m + (size_t)h * NS + sidx) : -INFINITY;
+                            lv[j] = sidx < NS ? __ldcg(P.part_l + (size_t)h * NS + sidx) : 0.0f;
+                        }
+                        const float M = hx_warp_max(fmaxf(mv[0], mv[1]));
+                        const float w0 = __expf(mv[0] - M), w1 = __expf(mv[1] - M);
+                        const float Lsum = hx_warp_sum(lv[0] * w0 + lv[1] * w1);
+                        if (lane < NS) S.wgt[h * NS + lane] = w0 / Lsum;
+                        if (lane + 32 < NS) S.wgt[h * NS + lane + 32] = w1 / Lsum;
+                    }
+                    mx = hx_warp_max(mx);
+                    if (lane == 0) S.red[NCW + warp] = mx;
+                    consumer_sync();
+                    float tmx = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < NCW; i++) tmx = fmaxf(tmx, S.red[NCW + i]);
+                    const float vmax = tmx * 1.0001f;                      // margin for the rounding of the merge
+                    if (vmax > 0.0f && vmax < INFINITY) Sg = __uint_as_float(__float_as_uint(vmax) & 0x7F800000u);
+                } else {
                     float ss = 0.0f, mx = 0.0f;
 #pragma unroll 1
                     for (int k0 = tid * 4; k0 < K; k0 += NCT * 4 * 3) {
@@ -374,6 +442,51 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                     if (vmax > 0.0f && vmax < INFINITY) Sg = __uint_as_float(__float_as_uint(vmax) & 0x7F800000u);   // vmax/Sg in [1,2)
                 }
                 const float mul = (inv / Sg) * 2147483648.0f;             // |x_n| / Sg * 2^31 < 2^32
+                if (merge_in) {
+                    // TPI threads share an item: each sums every TPI-th split, a butterfly adds them up (all lanes
+                    // end with the same bits), then each lane writes its share of the sixteen digit rows.
+                    const int NS = ph.nsplit, DH = ph.DH;
+                    int tpi = 1; while (tpi < 8 && nitems * tpi * 2 <= NCT) tpi *= 2;
+                    const int sub = tid & (tpi - 1);
+#pragma unroll 1
+                    for (int it = tid / tpi; it < nitems; it += NCT / tpi) {
+                        const int k = item_k(it);
+                        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                        if (k < K) {
+                            const int h = k / DH, d = k - h * DH;
+                            const float* pa = P.part_acc + ((size_t)h * NS) * DH + d;
+#pragma unroll 3
+                            for (int sp2 = sub; sp2 < NS; sp2 += tpi) {
+                                const float4 a = __ldcg(reinterpret_cast<const float4*>(pa + (size_t)sp2 * DH));
+                                const float4 b = __ldcg(reinterpret_cast<const float4*>(pa + (size_t)sp2 * DH + 4));
+                                const float w = S.wgt[h * NS + sp2];
+                                v[0] = fmaf(a.x, w, v[0]); v[1] = fmaf(a.y, w, v[1]); v[2] = fmaf(a.z, w, v[2]); v[3] = fmaf(a.w, w, v[3]);
+                                v[4] = fmaf(b.x, w, v[4]); v[5] = fmaf(b.y, w, v[5]); v[6] = fmaf(b.z, w, v[6]); v[7] = fmaf(b.w, w, v[7]);
+                            }
+                        }
+                        for (int dlt = 1; dlt < tpi; dlt <<= 1) {
+#pragma unroll
+                            for (int e = 0; e < 8; e++) v[e] += __shfl_xor_sync(0xffffffffu, v[e], dlt);
+                        }
+                        uint32_t M[8]; uint32_t sg = 0u;
+#pragma unroll
+                        for (int e = 0; e < 8; e++) {
+                            M[e] = __float2uint_rn(fabsf(v[e]) * mul);
+                            sg |= (v[e] < 0.0f ? 8u : 0u) << (4 * e);
+                        }
+                        const int j = (it >> 2) & 7, w = it & 3;
+                        uint8_t* dst = digb + (size_t)(it >> 5) * 2048 + w * 4;
+#pragma unroll 2
+                        for (int n = sub; n < TC_NDIG; n += tpi) {
+                            uint32_t word = 0u;
+#pragma unroll
+                            for (int e = 0; e < 8; e++) word |= ((M[e] >> (30 - 2 * n)) & 3u) << (4 * e);
+                            const uint32_t nz = (word | (word >> 1)) & 0x11111111u;
+                            word |= sg & (nz << 3);
+                            *reinterpret_cast<uint32_t*>(dst + n * 128 + ((j ^ (n & 7)) << 4)) = word;
+                        }
+                    }
+                } else
 #pragma unroll 1
                 for (int it = tid; it < nitems; it += NCT) {
                     const int k = item_k(it);
@@ -439,7 +552,8 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                         v *= out_scale;
                         // which CTAs share this tile
                         const long long x0 = (long long)tile * tp.C;
-                        const int c0 = tc_owner(x0, tp.total, tp.geff), c1 = tc_owner(x0 + tp.C - 1, tp.total, tp.geff);
+                        const int c0 = tp.P ? tile * tp.P : tc_owner(x0, tp.total, tp.geff);
+                        const int c1 = tp.P ? c0 + tp.P - 1 : tc_owner(x0 + tp.C - 1, tp.total, tp.geff);
                         if (c1 != c0) {
                             float* pp = P.tc_partial + ((size_t)tile * ph.pieces) * 128;
                             pp[(size_t)(cta - c0) * 128 + rl] = v;
