@@ -29,6 +29,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 PROMPT_LEN, NEW_TOKENS = 512, 256
+NCU_TRAFFIC_RATIO = 1.010      # measured DRAM bytes / algorithmic bytes of k_decode_tc (profiles/)
 WORKLOAD = "qwen3-8b-shape nvfp4 greedy decode, batch 1, 512-token prompt + 256 new tokens"
 
 
@@ -221,6 +222,8 @@ def run_ours(args):
     L = lib()
     check(L.hx_set_device(local))
     shape = dict(hb.QWEN3_8B)
+    if args.layers:
+        shape["n_layers"] = args.layers                 # reduced-depth case for profiler captures; not a bench line
     keep = 1 if (rank == 0 and not args.no_cpu_baseline) else 0
     model = hb.Model.synth(shape, seed=1, kv_cap=PROMPT_LEN + NEW_TOKENS + 8, flags=keep)
     cfgd = model.cfg.as_dict()
@@ -252,37 +255,58 @@ def run_ours(args):
     n_tok_all = args.gpus * args.steps * NEW_TOKENS
     value = n_tok_all / (ms_max * 1e-3)
 
-    # per-kernel device time of the dominant kernel (k_linear), event pair around every launch
-    model.set_profile(True)
-    model.decode_loop(first, PROMPT_LEN, 8)
-    _, _ = model.decode_loop(first, PROMPT_LEN, 32)
-    st = model.last_stats()
-    model.set_profile(False)
     wbytes, kvbytes_mid, embbytes = algorithmic_bytes_per_token(cfgd, PROMPT_LEN + NEW_TOKENS // 2)
-    n_lin = 4 * shape["n_layers"] + 1
+    token_bytes = wbytes + kvbytes_mid + embbytes
     peak, peak_src = peaks()
-    gemv_ms_tok = st["ms_gemv"] / 32
-    achieved = wbytes / (gemv_ms_tok * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "k_linear (fused dequant GEMV, all 4*NL+1 launches of a token)",
-                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                "peak_source": peak_src, "algorithmic_bytes_per_launch": wbytes / n_lin,
-                "avg_launch_us": gemv_ms_tok * 1e3 / n_lin,
-                "token_bytes": {"weights": wbytes, "kv_mid_run": kvbytes_mid, "embedding_row": embbytes},
-                "whole_token_frac": (wbytes + kvbytes_mid + embbytes) * value / args.gpus / 1e9 / peak,
-                "per_token_ms": {"gemv": gemv_ms_tok, "attention": st["ms_attn"] / 32, "other": st["ms_other"] / 32}}
+    engine = model.engine()
+    if engine.startswith("persistent"):
+        # The whole token is ONE cooperative launch of the persistent kernel, so the dominant kernel's average
+        # launch duration is the timed region (CUDA events on the launching stream inside hx_decode_loop) over
+        # the launches in it, and its algorithmic bytes are the token's.
+        n_launch = args.steps * NEW_TOKENS
+        avg_ms = ms_total / n_launch
+        achieved = token_bytes / (avg_ms * 1e-3) / 1e9
+        kname = "k_decode_tc" if engine.endswith("tcgen05") else "k_decode_persist"
+        roofline = {"bound": "hbm", "kernel": f"{kname} (persistent cooperative kernel, one launch = one decoded token: all "
+                    f"{4 * cfgd['n_layers'] + 1} linears, attention, norms, arg-max)",
+                    "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                    "traffic": token_bytes * NCU_TRAFFIC_RATIO if kname == "k_decode_tc" else None,
+                    "traffic_source": "ncu dram__bytes_read+write of one launch of the 4-layer case (profiles/"
+                                      "k_decode_tc_qwen3-8b-shape_4layers.md) = 1.010 x its algorithmic bytes, scaled to "
+                                      "this launch's algorithmic bytes (traffic grows with the layers streamed)",
+                    "peak_source": peak_src, "algorithmic_bytes_per_launch": token_bytes, "avg_launch_us": avg_ms * 1e3,
+                    "token_bytes": {"weights": wbytes, "kv_mid_run": kvbytes_mid, "embedding_row": embbytes},
+                    "whole_token_frac": token_bytes * value / args.gpus / 1e9 / peak}
+    else:
+        # per-kernel device time of the dominant kernel (k_linear), event pair around every launch
+        model.set_profile(True)
+        model.decode_loop(first, PROMPT_LEN, 8)
+        _, _ = model.decode_loop(first, PROMPT_LEN, 32)
+        st = model.last_stats()
+        model.set_profile(False)
+        n_lin = 4 * cfgd["n_layers"] + 1
+        gemv_ms_tok = st["ms_gemv"] / 32
+        achieved = wbytes / (gemv_ms_tok * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "k_linear (fused dequant GEMV, all 4*NL+1 launches of a token)",
+                    "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                    "peak_source": peak_src, "algorithmic_bytes_per_launch": wbytes / n_lin,
+                    "avg_launch_us": gemv_ms_tok * 1e3 / n_lin,
+                    "token_bytes": {"weights": wbytes, "kv_mid_run": kvbytes_mid, "embedding_row": embbytes},
+                    "whole_token_frac": token_bytes * value / args.gpus / 1e9 / peak,
+                    "per_token_ms": {"gemv": gemv_ms_tok, "attention": st["ms_attn"] / 32, "other": st["ms_other"] / 32}}
 
     # end to end through the per-token public call, host buffers both ways
     check(L.hx_sync())
     if dist is not None:
         dist.barrier()
     t0 = time.perf_counter()
-    e2e_steps = max(1, min(args.steps, 2))
+    e2e_steps = 0 if args.no_e2e else max(1, min(args.steps, 2))
     for _ in range(e2e_steps):
         tok = first
         for i in range(NEW_TOKENS):
             tok, lg = model.decode_step(tok, PROMPT_LEN + i, want_logits=True)
     e2e_s = all_max(dist, time.perf_counter() - t0)
-    e2e = {"value": args.gpus * e2e_steps * NEW_TOKENS / e2e_s, "unit": "tok/s",
+    e2e = None if args.no_e2e else {"value": args.gpus * e2e_steps * NEW_TOKENS / e2e_s, "unit": "tok/s",
            "h2d_bytes_per_step": NEW_TOKENS * 4, "d2h_bytes_per_step": NEW_TOKENS * (4 + shape["vocab"] * 4),
            "api": "hx_decode_step per token: token id H2D, next id + f32 logits row D2H (what the reference worker reads back)"}
 
@@ -301,7 +325,7 @@ def run_ours(args):
                 "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": WORKLOAD, "weights": "nvfp4 (e2m1 + e4m3/16 + f32 tensor scale), HBM resident",
-                           "kv_cache": "f32", "parallelism": f"replicas x{args.gpus} (one sequence per GPU)" if args.gpus > 1 else "single GPU",
+                           "kv_cache": "f32", "engine": engine, "layers": cfgd["n_layers"], "parallelism": f"replicas x{args.gpus} (one sequence per GPU)" if args.gpus > 1 else "single GPU",
                            "l2": "weights (4.26 GB per token) exceed the 126 MB L2, no flush needed",
                            "tokens_per_step": NEW_TOKENS, "weight_bytes_decode_layout": dbytes, "weight_bytes_committed_layout": cbytes},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
@@ -320,8 +344,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the per-token host-buffer loop (profiler captures)")
+    ap.add_argument("--layers", type=int, default=0, help="reduced depth for profiler captures (0 = the full 36)")
+    ap.add_argument("--new-tokens", type=int, default=0, help="tokens per step for profiler captures (0 = 256)")
+    ap.add_argument("--prompt-len", type=int, default=0, help="prompt length for profiler captures (0 = 512)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    global PROMPT_LEN, NEW_TOKENS
+    if args.new_tokens:
+        NEW_TOKENS = args.new_tokens
+    if args.prompt_len:
+        PROMPT_LEN = args.prompt_len
+    reduced = bool(args.layers or args.new_tokens or args.prompt_len)
+    args.warmup = max(args.warmup, 3) if (args.impl == "ours" and not reduced) else args.warmup
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -722,6 +722,12 @@ HX_API int hx_model_phase_stamps_all(hx_model* m, unsigned long long* out, size_
     *nphases = m->nph_decode; *grid = m->grid_persist;
     return HX_OK;
 }
+// Which decode engine this model runs: "persistent-tcgen05", "persistent-mma" or "graph".
+HX_API const char* hx_model_engine(const hx_model* m) {
+    if (!m) return "";
+    if (!m->persist) return "graph";
+    return m->use_tc ? "persistent-tcgen05" : "persistent-mma";
+}
 HX_API int hx_model_set_profile(hx_model* m, int on) { HX_CHECK_ARG(m); m->profile = on != 0; return HX_OK; }
 
 // ---- HXGW v3 image ---------------------------------------------------------------------------------

@@ -102,6 +102,7 @@ _SIGS = {
     "hx_prefill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "hx_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "hx_model_last_stats": (C.c_int, [C.c_void_p, C.POINTER(HxStepStats)]),
+    "hx_model_engine": (C.c_char_p, [C.c_void_p]),
     "hx_model_set_profile": (C.c_int, [C.c_void_p, C.c_int]),
     "hx_decode_loop": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float)]),
     "hx_model_fill_kv": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64]),
@@ -294,6 +295,9 @@ class Model:
         ms = C.c_float()
         check(lib().hx_decode_loop(self.h, ids.ctypes.data, pos0, n_steps, out.ctypes.data, C.byref(ms)))
         return out, ms.value
+
+    def engine(self):
+        return lib().hx_model_engine(self.h).decode()
 
     def set_profile(self, on):
         check(lib().hx_model_set_profile(self.h, 1 if on else 0))

@@ -122,11 +122,15 @@ int hx_gemv_d16(const float* x, const uint8_t* codes, const uint8_t* scales, con
                 float* y, int N, int Kd, void* stream);
 
 /* Block-scaled NVFP4 GEMM on the tensor cores (tcgen05.mma kind::mxf4nvf4, TMEM accumulators), device
- * pointers: y[rows][ncols] = sum_k A[row,k]*SFA[row,k/16] * B[n,k]*SFB[n,k/16].
- *   a_t128  weights in 4608-byte cells [tile of 128 rows][step of 64 columns]: 2 x 128 x 16 B of codes
- *           ([k half][row][32 codes, low nibble first]) + 512 B of E4M3 scales (byte (row%32)*16+(row/32)*4+blk)
- *   b_cells activations, per 64-column step: 2 x ncols x 16 B of codes + a 512 B scale chunk indexed by n
- * K % 64 == 0, ncols % 8 == 0, 8 <= ncols <= 256.  Replaces the f32 tiled_matmul_abt projections of
+ * pointers: y[rows][ncols] = sum_k A[row,k]*SFA[row,k/16] * B[n,k]*SFB[n,k/16], f32 accumulation.
+ *   a_t128  weights as 18432-byte cells [tile of 128 rows][group of 256 columns]: 128 rows x 128 bytes of codes
+ *           (two per byte, low nibble first) in the K-major 128-byte-swizzle operand layout (the 16-byte chunk j
+ *           of row r sits at position j ^ (r & 7)), then four 512-byte chunks of E4M3 scales, one per 64 columns
+ *           (byte (row%32)*16 + (row/32)*4 + block)
+ *   b_cells activations, per group of 256 columns: ncols rows x 128 swizzled bytes, then four scale chunks
+ *           indexed by n the same way
+ *   stage_ksteps  64-column steps per pipeline stage (4, 8, ... ; 0 = 4)
+ * K % 256 == 0, ncols % 8 == 0, 8 <= ncols <= 256.  Replaces the f32 tiled_matmul_abt projections of
  * forward_layer_llama (gpt2_infer.c:1231-1287) for batched prefill.  Synchronous. */
 int hx_gemm_nvfp4_tc(const uint8_t* a_t128, int rows, int K, const uint8_t* b_cells, int ncols, float* y,
                      int stage_ksteps, void* stream);
@@ -219,6 +223,10 @@ typedef struct {
     float    ms_other;
 } hx_step_stats;
 int hx_model_last_stats(const hx_model* m, hx_step_stats* st);
+/* Name of the decode engine in use: "persistent-tcgen05" (one cooperative launch per token, linear phases on
+ * tcgen05.mma), "persistent-mma" (same kernel structure, mma.sync) or "graph" (one CUDA graph of per-op kernels;
+ * the only engine for which hx_model_set_profile yields per-category times). */
+const char* hx_model_engine(const hx_model* m);
 int hx_model_set_profile(hx_model* m, int on);
 
 /* Run n_steps decode steps starting at position pos0 with the KV cache as it stands, feeding back
