@@ -365,8 +365,9 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 const int nitems = tp.run * 32;
                 auto item_k = [&](int it) { int kc = tp.k0 + (it >> 5); if (kc >= tp.C) kc -= tp.C; return kc * 256 + (it & 31) * 8; };
                 float4 ia = make_float4(0.f, 0.f, 0.f, 0.f), ib = ia, ja = make_float4(1.f, 1.f, 1.f, 1.f), jb = ja;
-                if (tid < nitems && ph.norm != HX_NORM_ATTN) {
-                    const int k = item_k(tid);
+                int tpi0 = 1; while (tpi0 < 4 && nitems * tpi0 * 2 <= NCT) tpi0 *= 2;      // threads per item in pass 2
+                if (tid % (NCT / tpi0) < nitems && ph.norm != HX_NORM_ATTN) {
+                    const int k = item_k(tid % (NCT / tpi0));
                     if (k < K) {
                         ia = __ldcg(reinterpret_cast<const float4*>(xin + k));
                         if (k + 4 < K) ib = __ldcg(reinterpret_cast<const float4*>(xin + k + 4));
@@ -441,6 +442,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                     const float vmax = tmx * inv * 1.0000005f;            // margin for the rounding of x*g*inv
                     if (vmax > 0.0f && vmax < INFINITY) Sg = __uint_as_float(__float_as_uint(vmax) & 0x7F800000u);   // vmax/Sg in [1,2)
                 }
+                STAMP(14);
                 const float mul = (inv / Sg) * 2147483648.0f;             // |x_n| / Sg * 2^31 < 2^32
                 if (merge_in) {
                     // TPI threads share an item: each sums every TPI-th split, a butterfly adds them up (all lanes
@@ -486,38 +488,47 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                             *reinterpret_cast<uint32_t*>(dst + n * 128 + ((j ^ (n & 7)) << 4)) = word;
                         }
                     }
-                } else
+                } else {
+                    // TPI threads of different warps share an item (each fetches it itself) and write 16 / TPI digit
+                    // rows each; the row loop is unrolled so that every shift amount is a constant.
+                    const int ipt = NCT / tpi0, sub = tid / ipt;
 #pragma unroll 1
-                for (int it = tid; it < nitems; it += NCT) {
-                    const int k = item_k(it);
-                    if (it != tid) {                                       // later items of a long run: fetched here
-                        ia = make_float4(0.f, 0.f, 0.f, 0.f); ib = ia; ja = make_float4(1.f, 1.f, 1.f, 1.f); jb = ja;
-                        if (k < K) {
-                            ia = __ldcg(reinterpret_cast<const float4*>(xin + k));
-                            if (k + 4 < K) ib = __ldcg(reinterpret_cast<const float4*>(xin + k + 4));
-                            if (rms) { ja = *reinterpret_cast<const float4*>(ph.g + k); if (k + 4 < K) jb = *reinterpret_cast<const float4*>(ph.g + k + 4); }
+                    for (int it = tid - sub * ipt; it < nitems; it += ipt) {
+                        const int k = item_k(it);
+                        if (it >= ipt) {                                   // not the item fetched ahead of pass 1
+                            ia = make_float4(0.f, 0.f, 0.f, 0.f); ib = ia; ja = make_float4(1.f, 1.f, 1.f, 1.f); jb = ja;
+                            if (k < K) {
+                                ia = __ldcg(reinterpret_cast<const float4*>(xin + k));
+                                if (k + 4 < K) ib = __ldcg(reinterpret_cast<const float4*>(xin + k + 4));
+                                if (rms) { ja = *reinterpret_cast<const float4*>(ph.g + k); if (k + 4 < K) jb = *reinterpret_cast<const float4*>(ph.g + k + 4); }
+                            }
+                        }
+                        const float v[8] = {ia.x * ja.x, ia.y * ja.y, ia.z * ja.z, ia.w * ja.w, ib.x * jb.x, ib.y * jb.y, ib.z * jb.z, ib.w * jb.w};
+                        uint32_t M[8]; uint32_t sg = 0u;
+#pragma unroll
+                        for (int e = 0; e < 8; e++) {
+                            M[e] = __float2uint_rn(fabsf(v[e]) * mul);
+                            sg |= (v[e] < 0.0f ? 8u : 0u) << (4 * e);
+                        }
+                        // digit n of element e is bits 31-2n, 30-2n of M[e]; it lands on bits 4e+1, 4e of the word of row n
+                        const int j = (it >> 2) & 7, w = it & 3;           // 16-byte chunk and word of this item in its cell
+                        uint8_t* dst = digb + (size_t)(it >> 5) * 2048 + w * 4;
+#pragma unroll
+                        for (int n = 0; n < TC_NDIG; n++) {
+                            if ((n & (tpi0 - 1)) != sub) continue;         // uniform per warp
+                            uint32_t word = 0u;
+#pragma unroll
+                            for (int e = 0; e < 8; e++) {
+                                const int sh = 30 - 2 * n - 4 * e;
+                                word |= (sh >= 0 ? (M[e] >> sh) : (M[e] << (-sh))) & (3u << (4 * e));
+                            }
+                            const uint32_t nz = (word | (word >> 1)) & 0x11111111u;   // a zero digit carries no sign
+                            word |= sg & (nz << 3);
+                            *reinterpret_cast<uint32_t*>(dst + n * 128 + ((j ^ (n & 7)) << 4)) = word;
                         }
                     }
-                    const float v[8] = {ia.x * ja.x, ia.y * ja.y, ia.z * ja.z, ia.w * ja.w, ib.x * jb.x, ib.y * jb.y, ib.z * jb.z, ib.w * jb.w};
-                    uint32_t M[8]; uint32_t sg = 0u;
-#pragma unroll
-                    for (int e = 0; e < 8; e++) {
-                        M[e] = __float2uint_rn(fabsf(v[e]) * mul);
-                        sg |= (v[e] < 0.0f ? 8u : 0u) << (4 * e);
-                    }
-                    // digit n of element e is bits 31-2n, 30-2n of M[e]; it lands on bits 4e+1, 4e of the word of row n
-                    const int j = (it >> 2) & 7, w = it & 3;               // 16-byte chunk and word of this item in its cell
-                    uint8_t* dst = digb + (size_t)(it >> 5) * 2048 + w * 4;
-#pragma unroll 2
-                    for (int n = 0; n < TC_NDIG; n++) {
-                        uint32_t word = 0u;
-#pragma unroll
-                        for (int e = 0; e < 8; e++) word |= ((M[e] >> (30 - 2 * n)) & 3u) << (4 * e);
-                        const uint32_t nz = (word | (word >> 1)) & 0x11111111u;   // a zero digit carries no sign
-                        word |= sg & (nz << 3);
-                        *reinterpret_cast<uint32_t*>(dst + n * 128 + ((j ^ (n & 7)) << 4)) = word;
-                    }
                 }
+                STAMP(15);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 consumer_sync();
                 if (tid == 0) mbar_arrive(&S.b_ready);
