@@ -79,14 +79,17 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
     extern __shared__ __align__(128) uint8_t smem_raw[];
     TcSmem& S = *reinterpret_cast<TcSmem*>(smem_raw);
     // swizzled operands need 1024-byte aligned cells (the swizzle is a function of the shared-memory address)
-    uint8_t* ring = smem_raw + (((s_u32(smem_raw) + 256u + 1023u) & ~1023u) - s_u32(smem_raw));
+    uint8_t* ring = smem_raw + (((s_u32(smem_raw) + 1024u + 1023u) & ~1023u) - s_u32(smem_raw));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NB = g.ncols, Sk = g.stage_ksteps;
     // a stage holds Sk K steps = Sk/4 cells of 256 columns
-    const uint32_t a_cell = HX_T128_CELL / 4, b_cell = ((uint32_t)NB * 128u + 2048u) / 4;   // bytes per K step
+    const uint32_t b_cell_bytes = (uint32_t)NB * 128u + (g.digit_mode ? 0u : 2048u);       // one 256-column cell of B
+    const uint32_t a_cell = HX_T128_CELL / 4, b_cell = b_cell_bytes / 4;                     // bytes per K step
     const uint32_t stage_bytes = (uint32_t)Sk * (a_cell + b_cell);
     const int nstage_iters = (g.ksteps + Sk - 1) / Sk;
 
+    if (tid < 128) reinterpret_cast<uint32_t*>(smem_raw + 512)[tid] = 0x38383838u;      // a chunk of unit scales (digit mode)
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (tid == 0) {
         for (int i = 0; i < HX_TC_STAGES; i++) { mb_init(&S.full[i], 1); mb_init(&S.empty[i], 1); }
         mb_init(&S.accum, 1);
@@ -124,6 +127,10 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
             // ------------------------------ MMA issuer ------------------------------
             // instruction descriptor: E2M1 x E2M1, UE4M3 scales, K-major both, N = NB, M = 128, K = 64
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | (8u << 24);
+            if (g.digit_mode && mt == (int)blockIdx.x) {
+                // unit scales (E4M3 1.0) for every digit column: sixteen TMEM columns cover any N up to 256
+                for (int c = 0; c < 4; c++) tc_cp_sf(tmem + col_sfb + c * 4, smem_desc(s_u32(smem_raw + 512), 16, 128));
+            }
             for (int it = 0; it < nstage_iters; it++) {
                 const uint32_t git = base_it + it, slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
                 if (!mb_wait(&S.full[slot], round & 1, &S.abort_flag)) break;
@@ -134,14 +141,14 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
                 for (int k = 0; k < nk; k++) {
                     const uint32_t ta = tmem + col_sfa + (slot * HX_TC_MAX_SK + k) * 4;
                     const uint32_t tb = tmem + col_sfb + (slot * HX_TC_MAX_SK + k) * 4;
-                    const uint32_t acell = sa + (uint32_t)(k >> 2) * HX_T128_CELL, bcell = sb + (uint32_t)(k >> 2) * ((uint32_t)NB * 128u + 2048u);
+                    const uint32_t acell = sa + (uint32_t)(k >> 2) * HX_T128_CELL, bcell = sb + (uint32_t)(k >> 2) * b_cell_bytes;
                     const uint32_t e = (uint32_t)(k & 3);
                     if (!(g.dbg & 1) || (it == 0 && k == 0)) {
                         tc_cp_sf(ta, smem_desc(acell + 16384 + e * 512, 16, 128));
-                        tc_cp_sf(tb, smem_desc(bcell + (uint32_t)NB * 128u + e * 512, 16, 128));
+                        if (!g.digit_mode) tc_cp_sf(tb, smem_desc(bcell + (uint32_t)NB * 128u + e * 512, 16, 128));
                     }
                     tc_mma(tmem + ((g.dbg & 4) ? (uint32_t)(k & 3) * 64u : 0u), smem_desc(acell + e * 32, 16, 1024, SW128), smem_desc(bcell + e * 32, 16, 1024, SW128), idesc,
-                           (g.dbg & 2) ? tmem + col_sfa : ta, (g.dbg & 2) ? tmem + col_sfb : tb, (it > 0 || k > 0) ? 1u : 0u);
+                           (g.dbg & 2) ? tmem + col_sfa : ta, ((g.dbg & 2) || g.digit_mode) ? tmem + col_sfb : tb, (it > 0 || k > 0) ? 1u : 0u);
                 }
                 tc_commit(&S.empty[slot]);          // the slot is free once these MMAs have read it
             }
@@ -152,6 +159,27 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int sub = warp & 3;                          // TMEM lanes 32*sub .. 32*sub+31
                 const int row = mt * 128 + sub * 32 + lane;
+                if (g.digit_mode) {
+                    const float tsr = g.pair64 ? (((row & 127) < 64) ? g.ts[0] : g.ts[1])
+                                               : (row < g.bound0 ? g.ts[0] : (row < g.bound1 ? g.ts[1] : g.ts[2]));
+                    for (int t = 0; t < NB / 16; t++) {
+                        uint32_t r[16];
+                        const uint32_t ta = tmem + ((uint32_t)(sub * 32) << 16) + (uint32_t)(t * 16);
+                        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                                       "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                                     : "r"(ta));
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        float v = 0.0f;
+#pragma unroll
+                        for (int j = 15; j >= 0; j--) v = fmaf(v, 0.25f, __uint_as_float(r[j]));
+                        v = v * g.col_scale[t] * tsr;
+                        if (row < g.rows) {
+                            float* o = g.out + (size_t)t * g.ld_out + row;
+                            *o = g.resid ? *o + v : v;
+                        }
+                    }
+                } else
                 for (int c0 = 0; c0 < NB; c0 += 8) {
                     uint32_t r[8];
                     const uint32_t ta = tmem + ((uint32_t)(sub * 32) << 16) + (uint32_t)c0;
@@ -177,11 +205,11 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
 }  // namespace
 
 size_t hx_gemm_tc_smem(int ncols, int stage_ksteps) {
-    return 2048 + (size_t)HX_TC_STAGES * (stage_ksteps / 4) * (HX_T128_CELL + (size_t)ncols * 128 + 2048);
+    return 3072 + (size_t)HX_TC_STAGES * (stage_ksteps / 4) * (HX_T128_CELL + (size_t)ncols * 128 + 2048);
 }
 
 int hx_gemm_tc_launch(const HxGemmTC& g, cudaStream_t st) {
-    HX_CHECK_ARG(g.a && g.b && g.y && g.ntiles > 0 && g.ksteps > 0);
+    HX_CHECK_ARG(g.a && g.b && (g.digit_mode ? (g.out && g.col_scale && g.ncols % 16 == 0) : g.y != nullptr) && g.ntiles > 0 && g.ksteps > 0);
     HX_CHECK_ARG(g.ncols >= 8 && g.ncols <= 256 && g.ncols % 8 == 0);
     HX_CHECK_ARG(g.stage_ksteps >= 4 && g.stage_ksteps <= HX_TC_MAX_SK && g.stage_ksteps % 4 == 0 && g.ksteps % 4 == 0);
     const size_t smem = hx_gemm_tc_smem(g.ncols, g.stage_ksteps);

@@ -13,6 +13,15 @@ struct HxGemmTC {
     int rows, ntiles, ksteps, ncols, stage_ksteps;
     int* err;                      // set when a bounded wait ran out
     int dbg;                       // timing probes (bit 0: copy scale factors once, bit 1: fixed scale columns)
+    // ---- digit mode (batched prefill): B holds sixteen base-4 digit columns per token with unit scales (cells of
+    // ncols x 128 bytes, no scale chunks); the epilogue recombines them per token:
+    //   out[t * ld_out + row] (+)= col_scale[t] * ts(row) * sum_j 4^-j D[row][16 t + j]
+    int digit_mode;                // 0: raw accumulators to y
+    const float* col_scale;        // [ncols / 16] power-of-two scale of each token's digits
+    float* out; int ld_out;        // token-major output
+    int resid;                     // 1: add to out instead of storing
+    float ts[3]; int bound0, bound1;   // per-row tensor scale: rows < bound0 ts[0], < bound1 ts[1], else ts[2]
+    int pair64;                    // 1: ts[0] for rows with (row % 128) < 64, ts[1] for the others (gate/up tiles)
 };
 
 int hx_gemm_tc_launch(const HxGemmTC& g, cudaStream_t st);

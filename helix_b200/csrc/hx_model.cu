@@ -14,6 +14,7 @@
 #include "hx_kernels.cuh"
 #include "hx_persist.cuh"
 #include "hx_gemm_tc.cuh"
+#include "hx_prefill.cuh"
 #include <fcntl.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -86,6 +87,9 @@ struct hx_model {
     std::vector<void*> allocs;
     uint64_t decode_bytes = 0, committed_bytes = 0;
     int kv_len = 0;
+    // batched prefill (chunks of HX_PF_TB tokens through the tcgen05 GEMM); buffers are created on first use
+    float *pf_x = nullptr, *pf_qkv = nullptr, *pf_ctx = nullptr, *pf_gu = nullptr, *pf_scale = nullptr; uint8_t* pf_cells = nullptr; int* pf_err = nullptr;
+    int pf_gu_ld = 0; bool pf_batched = true;
 };
 
 namespace {
@@ -539,6 +543,11 @@ int persist_step(hx_model* m, bool from_prompt, bool with_head) {
 
 // After a synchronize: did any bounded wait of the persistent kernel run out?
 int persist_check(hx_model* m) {
+    if (m->pf_err) {
+        int pe = 0;
+        HX_CUDA(cudaMemcpy(&pe, m->pf_err, 4, cudaMemcpyDeviceToHost));
+        if (pe) { cudaMemset(m->pf_err, 0, 4); return hx_fail(HX_ERR_TIMEOUT, "a bounded wait in the prefill GEMM ran out"); }
+    }
     if (!m->persist) return HX_OK;
     int e = 0;
     HX_CUDA(cudaMemcpy(&e, m->d_err, 4, cudaMemcpyDeviceToHost));
@@ -618,7 +627,8 @@ HX_API int hx_model_synth(hx_model** out, const hx_config* cfg, uint64_t seed, i
     { const char* dm = getenv("HX_DECODE"); const char* lm = getenv("HX_LINEAR");
       m->persist = !(dm && strcmp(dm, "graph") == 0);
       m->use_tc = m->persist && !(lm && strcmp(lm, "mma") == 0);
-      m->want_t128 = m->use_tc; }
+      m->want_t128 = m->use_tc;
+      { const char* pf = getenv("HX_PREFILL"); m->pf_batched = !(pf && strcmp(pf, "token") == 0); } }
     cudaError_t e = cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking);
     if (e != cudaSuccess) { delete m; return hx_fail(HX_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
     Source s; s.synth = true; s.seed = seed;
@@ -681,7 +691,8 @@ HX_API int hx_model_load(hx_model** out, const char* path, int kv_cap, int batch
     { const char* dm = getenv("HX_DECODE"); const char* lm = getenv("HX_LINEAR");
       m->persist = !(dm && strcmp(dm, "graph") == 0);
       m->use_tc = m->persist && !(lm && strcmp(lm, "mma") == 0);
-      m->want_t128 = m->use_tc; }
+      m->want_t128 = m->use_tc;
+      { const char* pf = getenv("HX_PREFILL"); m->pf_batched = !(pf && strcmp(pf, "token") == 0); } }
         cudaError_t e = cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking);
         if (e != cudaSuccess) { rc = hx_fail(HX_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); break; }
         Source s; s.map = hb; s.maplen = len; s.desc = d;
@@ -851,9 +862,70 @@ HX_API int hx_decode_step(hx_model* m, const int32_t* ids, int pos, int32_t* nex
     return HX_OK;
 }
 
+// ---- batched prefill ---------------------------------------------------------------------------------
+static int pf_alloc(hx_model* m) {
+    if (m->pf_x) return HX_OK;
+    const hx_config& c = m->cfg;
+    int maxK = c.d_model > m->QD ? c.d_model : m->QD; if (c.d_ff > maxK) maxK = c.d_ff;
+    const size_t cells = (size_t)((maxK + 255) / 256) * (16 * HX_PF_TB) * 128;
+    m->pf_gu_ld = m->layers.empty() ? 128 : m->layers[0].gu.tiles128 * 128;
+    int rc;
+    if ((rc = dalloc(m, &m->pf_x, (size_t)HX_PF_TB * c.d_model))) return rc;
+    if ((rc = dalloc(m, &m->pf_qkv, (size_t)HX_PF_TB * (m->QD + 2 * m->KVD)))) return rc;
+    if ((rc = dalloc(m, &m->pf_ctx, (size_t)HX_PF_TB * m->QD))) return rc;
+    if ((rc = dalloc(m, &m->pf_gu, (size_t)HX_PF_TB * m->pf_gu_ld))) return rc;
+    if ((rc = dalloc(m, &m->pf_scale, (size_t)HX_PF_TB))) return rc;
+    if ((rc = dalloc(m, &m->pf_cells, cells))) return rc;
+    if ((rc = dalloc(m, &m->pf_err, (size_t)4))) return rc;
+    HX_CUDA(cudaMemsetAsync(m->pf_err, 0, 16, m->st));
+    return HX_OK;
+}
+
+// one linear of a chunk: digits of `src` -> GEMM against f -> out (token-major)
+static int pf_linear(hx_model* m, const Fused& f, const float* src, int ld_src, int n, int swiglu, const float* g,
+                     float* out, int ld_out, int rows, int resid, int pair64) {
+    hx_pf_digits(src, ld_src, n, f.K, swiglu, g, m->cfg.norm_eps, m->pf_cells, 16 * n, m->pf_scale, m->st);
+    HxGemmTC q = {};
+    q.a = f.t128; q.b = m->pf_cells; q.rows = rows; q.ntiles = f.tiles128; q.ksteps = f.ksteps; q.ncols = 16 * n; q.stage_ksteps = 4;
+    q.err = m->pf_err; q.digit_mode = 1; q.col_scale = m->pf_scale; q.out = out; q.ld_out = ld_out; q.resid = resid;
+    q.ts[0] = f.ts[0]; q.ts[1] = f.ts[1]; q.ts[2] = f.ts[2]; q.bound0 = f.bound0; q.bound1 = f.bound1; q.pair64 = pair64;
+    return hx_gemm_tc_launch(q, m->st);
+}
+
+// Prompt positions [0, T) in chunks of HX_PF_TB tokens; ends like the token-by-token path: KV rows written,
+// logits of the last position in m->logits, its arg-max in d_tok / d_hist[T], *d_pos = T.
+static int run_prefill_batched(hx_model* m, int T) {
+    const hx_config& c = m->cfg;
+    const int DH = c.head_dim, DM = c.d_model, QD = m->QD, KVD = m->KVD, cap = m->kv_cap;
+    int rc = pf_alloc(m); if (rc) return rc;
+    const int ldq = QD + 2 * KVD;
+    const float att_scale = 1.0f / sqrtf((float)DH);
+    for (int p0 = 0; p0 < T; p0 += HX_PF_TB) {
+        const int n = T - p0 < HX_PF_TB ? T - p0 : HX_PF_TB;
+        hx_pf_embed(m->d_prompt + p0, m->emb, m->pf_x, n, DM, m->st);
+        for (int L = 0; L < c.n_layers; L++) {
+            Layer& ly = m->layers[L];
+            float* kc = m->kc + (size_t)L * c.n_kv_heads * cap * DH; float* vc = m->vc + (size_t)L * c.n_kv_heads * cap * DH;
+            if ((rc = pf_linear(m, ly.qkv, m->pf_x, DM, n, 0, ly.in_g, m->pf_qkv, ldq, ly.qkv.N, 0, 0))) return rc;
+            hx_pf_qkpost(m->pf_qkv, ldq, n, p0, c.n_heads, c.n_kv_heads, DH, ly.qn_g, ly.kn_g, c.norm_eps, m->cosT, m->sinT, kc, vc, cap, m->st);
+            if ((rc = hx_pf_attn(m->pf_qkv, ldq, n, p0, c.n_heads, c.n_kv_heads, DH, kc, vc, cap, att_scale, m->pf_ctx, QD, m->st))) return rc;
+            if ((rc = pf_linear(m, ly.o, m->pf_ctx, QD, n, 0, nullptr, m->pf_x, DM, ly.o.N, 1, 0))) return rc;
+            if ((rc = pf_linear(m, ly.gu, m->pf_x, DM, n, 0, ly.post_g, m->pf_gu, m->pf_gu_ld, ly.gu.tiles128 * 128, 0, 1))) return rc;
+            if ((rc = pf_linear(m, ly.down, m->pf_gu, m->pf_gu_ld, n, 1, nullptr, m->pf_x, DM, ly.down.N, 1, 0))) return rc;
+        }
+        if (p0 + n == T) {        // logits and arg-max of the last position
+            if ((rc = pf_linear(m, m->head, m->pf_x + (size_t)(n - 1) * DM, DM, 1, 0, m->final_g, m->logits, 0, m->head.N, 0, 0))) return rc;
+            hx_pf_argmax(m->logits, c.vocab, m->d_tok, m->d_hist, m->d_pos, T - 1, m->st);
+        }
+    }
+    HX_CUDA(cudaGetLastError());
+    return HX_OK;
+}
+
 static int run_prefill(hx_model* m, const int32_t* ids, int T) {
     // positions 0..T-2 without the head, position T-1 with it
     HX_CUDA(cudaMemcpyAsync(m->d_prompt, ids, (size_t)T * 4, cudaMemcpyHostToDevice, m->st));
+    if (m->use_tc && m->pf_batched && m->head.t128) return run_prefill_batched(m, T);
     int rc = set_pos_tok(m, 0, nullptr); if (rc) return rc;
     for (int s = 0; s < T - 1; s++) if ((rc = step_prefill(m))) return rc;
     HX_CUDA(cudaMemcpyAsync(m->d_tok, m->d_prompt + (T - 1), 4, cudaMemcpyDeviceToDevice, m->st));

@@ -1,0 +1,246 @@
+// hx_prefill.cu -- batched prefill around the tcgen05 GEMM.
+//
+// Replaces forward_layer_llama / forward_full (helixc/runtime/gpt2_infer.c:1231-1333): where the reference runs
+// f32 tiled_matmul_abt over a dequantized weight copy per layer, a chunk of HX_PF_TB prompt tokens here is one
+// block-scaled NVFP4 GEMM per linear with the weights read in their packed form.  The activations enter the FP4
+// tensor path exactly: after the optional RMSNorm each vector is x = S * sum_j (d_j/2) 4^-j with sixteen base-4
+// digits carrying the sign, every digit row being an E2M1 column with unit block scale (the scheme of the decode
+// kernel, hx_persist_tc.cu); the GEMM epilogue recombines the sixteen accumulators of a token.
+// Norm, RoPE, KV append and attention are small f32 kernels over the chunk.
+#include "hx_prefill.cuh"
+#include "hx_kernels.cuh"
+#include <math.h>
+
+namespace {
+
+__device__ __forceinline__ float pf_silu_mul(float g, float u) {      // same formula as the decode epilogue (silu_mul_k)
+    const float sgn = g < 0.0f ? -1.0f : 1.0f;
+    const float e = __expf(-(sgn * g));
+    const float th = sgn * ((1.0f - e) / (1.0f + e));
+    return g * (0.5f * (1.0f + th)) * u;
+}
+
+__global__ void __launch_bounds__(256) k_pf_embed(const int* __restrict__ ids, const float* __restrict__ emb, float* __restrict__ X, int DM) {
+    const float4* src = reinterpret_cast<const float4*>(emb + (size_t)ids[blockIdx.x] * DM);
+    float4* dst = reinterpret_cast<float4*>(X + (size_t)blockIdx.x * DM);
+    for (int i = threadIdx.x; i < DM / 4; i += blockDim.x) dst[i] = src[i];
+}
+
+// One CTA per token.
+__global__ void __launch_bounds__(512) k_pf_digits(const float* __restrict__ src, int ld, int K, int swiglu, const float* __restrict__ g,
+                                                    float eps, uint8_t* __restrict__ cells, int ncols, float* __restrict__ scale) {
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* x = src + (size_t)t * ld;
+    __shared__ float red[32];
+    auto value = [&](int k) -> float {        // element k of the vector before the norm scale (gain applied)
+        float v;
+        if (swiglu) { const int tile = k >> 6, r = k & 63; v = pf_silu_mul(x[tile * 128 + r], x[tile * 128 + 64 + r]); }
+        else v = x[k];
+        return v;
+    };
+    // pass 1: sum of squares (of x) and largest |x * g|
+    float ss = 0.0f, mx = 0.0f;
+    for (int k = tid; k < K; k += 512) {
+        const float v = value(k);
+        ss = fmaf(v, v, ss);
+        mx = fmaxf(mx, fabsf(g ? v * g[k] : v));
+    }
+    ss = hx_warp_sum(ss); mx = hx_warp_max(mx);
+    if (lane == 0) { red[warp] = ss; red[16 + warp] = mx; }
+    __syncthreads();
+    float tss = 0.0f, tmx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; i++) { tss += red[i]; tmx = fmaxf(tmx, red[16 + i]); }
+    const float inv = g ? rsqrtf(tss / (float)K + eps) : 1.0f;
+    float Sg = 1.0f;
+    const float vmax = tmx * inv * 1.0000005f;
+    if (vmax > 0.0f && vmax < INFINITY) Sg = __uint_as_float(__float_as_uint(vmax) & 0x7F800000u);
+    if (tid == 0) scale[t] = Sg;
+    const float mul = (inv / Sg) * 2147483648.0f;
+    // pass 2: items of 8 consecutive elements -> sixteen digit words
+    const int Kc = ((K + 255) / 256) * 256;
+    const size_t cell_bytes = (size_t)ncols * 128;
+    for (int it = tid; it < Kc / 8; it += 512) {
+        const int k = it * 8;
+        uint32_t M[8]; uint32_t sg = 0u;
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            float v = 0.0f;
+            if (k + e < K) { v = value(k + e); if (g) v *= g[k + e]; }
+            M[e] = __float2uint_rn(fabsf(v) * mul);
+            sg |= (v < 0.0f ? 8u : 0u) << (4 * e);
+        }
+        const int j = (it >> 2) & 7, w = it & 3;
+        uint8_t* dst = cells + (size_t)(it >> 5) * cell_bytes + (size_t)(t * 16) * 128 + w * 4;
+#pragma unroll
+        for (int n = 0; n < 16; n++) {
+            uint32_t word = 0u;
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const int sh = 30 - 2 * n - 4 * e;
+                word |= (sh >= 0 ? (M[e] >> sh) : (M[e] << (-sh))) & (3u << (4 * e));
+            }
+            const uint32_t nz = (word | (word >> 1)) & 0x11111111u;
+            word |= sg & (nz << 3);
+            *reinterpret_cast<uint32_t*>(dst + n * 128 + ((j ^ (n & 7)) << 4)) = word;     // (16 t + n) & 7 == n & 7
+        }
+    }
+}
+
+// grid (NH + 2 NKV, n_tok), block DH threads (DH <= 256)
+__global__ void __launch_bounds__(256) k_pf_qkpost(float* __restrict__ qkv, int ld, int pos0, int NH, int NKV, int DH,
+                                                    const float* __restrict__ qn_g, const float* __restrict__ kn_g, float eps,
+                                                    const float* __restrict__ cosT, const float* __restrict__ sinT,
+                                                    float* __restrict__ kc, float* __restrict__ vc, int cap) {
+    const int hs = blockIdx.x, t = blockIdx.y, e = threadIdx.x, half = DH >> 1, pos = pos0 + t;
+    const int sec = hs < NH ? 0 : (hs < NH + NKV ? 1 : 2);
+    float* row = qkv + (size_t)t * ld + (size_t)hs * DH;
+    __shared__ float sm[256]; __shared__ float red[8];
+    float v = e < DH ? row[e] : 0.0f;
+    const float* gg = sec == 0 ? qn_g : (sec == 1 ? kn_g : nullptr);
+    float ssq = hx_warp_sum(v * v);
+    if ((e & 31) == 0) red[e >> 5] = ssq;
+    __syncthreads();
+    ssq = 0.0f;
+    for (int i = 0; i < (DH + 31) / 32; i++) ssq += red[i];
+    if (gg) v = gg[e] * (v * rsqrtf(ssq / (float)DH + eps));
+    if (cosT && sec < 2) {
+        sm[e] = v;
+        __syncthreads();
+        const float other = sm[e < half ? e + half : e - half];
+        const float cs = cosT[(size_t)pos * half + (e < half ? e : e - half)], sn = sinT[(size_t)pos * half + (e < half ? e : e - half)];
+        v = e < half ? v * cs - other * sn : v * cs + other * sn;
+    }
+    if (e < DH) {
+        if (sec == 0) row[e] = v;
+        else {
+            const int kvh = hs - NH - (sec == 2 ? NKV : 0);
+            (sec == 1 ? kc : vc)[((size_t)kvh * cap + pos) * DH + e] = v;
+        }
+    }
+}
+
+// grid (NKV, n_tok), 128 threads, dynamic shared memory: GRP*DH queries + GRP*(pos0 + n_tok) scores
+template <int GRP>
+__global__ void __launch_bounds__(128) k_pf_attn(const float* __restrict__ qkv, int ld, int pos0, int NH, int DH,
+                                                  const float* __restrict__ kc, const float* __restrict__ vc, int cap, float scale,
+                                                  float* __restrict__ ctx, int ld_ctx, int spitch) {
+    extern __shared__ float smf[];
+    const int kvh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int T = pos0 + t + 1;
+    float* sq = smf;                   // [GRP][DH]
+    float* sp = smf + GRP * DH;        // [GRP][spitch]
+    __shared__ float sm_m[GRP], sm_l[GRP];
+    for (int i = tid; i < GRP * DH; i += 128) sq[i] = qkv[(size_t)t * ld + (size_t)kvh * GRP * DH + i];
+    __syncthreads();
+    const float* kbase = kc + (size_t)kvh * cap * DH;
+    const float* vbase = vc + (size_t)kvh * cap * DH;
+    // scores: a warp per key, lanes over the head dimension
+    for (int j = warp; j < T; j += 4) {
+        float dot[GRP];
+#pragma unroll
+        for (int i = 0; i < GRP; i++) dot[i] = 0.0f;
+        for (int e = lane * 4; e < DH; e += 128) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kbase + (size_t)j * DH + e);
+#pragma unroll
+            for (int i = 0; i < GRP; i++) {
+                const float4 q4 = *reinterpret_cast<const float4*>(sq + i * DH + e);
+                dot[i] = fmaf(q4.x, k4.x, dot[i]); dot[i] = fmaf(q4.y, k4.y, dot[i]);
+                dot[i] = fmaf(q4.z, k4.z, dot[i]); dot[i] = fmaf(q4.w, k4.w, dot[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < GRP; i++) { const float s = hx_warp_sum(dot[i]); if (lane == 0) sp[i * spitch + j] = s * scale; }
+    }
+    __syncthreads();
+    // softmax statistics: a warp per head (m seeded -1e8 like fused_decode_attn_kernel.hx:74-102)
+    for (int i = warp; i < GRP; i += 4) {
+        float m = -100000000.0f;
+        for (int j = lane; j < T; j += 32) m = fmaxf(m, sp[i * spitch + j]);
+        m = hx_warp_max(m);
+        float l = 0.0f;
+        for (int j = lane; j < T; j += 32) { const float p = __expf(sp[i * spitch + j] - m); sp[i * spitch + j] = p; l += p; }
+        l = hx_warp_sum(l);
+        if (lane == 0) { sm_m[i] = m; sm_l[i] = l; }
+    }
+    __syncthreads();
+    // P*V: thread per dimension, all heads of the group share the V row
+    for (int d = tid; d < DH; d += 128) {
+        float acc[GRP];
+#pragma unroll
+        for (int i = 0; i < GRP; i++) acc[i] = 0.0f;
+        for (int j = 0; j < T; j++) {
+            const float vv = vbase[(size_t)j * DH + d];
+#pragma unroll
+            for (int i = 0; i < GRP; i++) acc[i] = fmaf(sp[i * spitch + j], vv, acc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < GRP; i++) ctx[(size_t)t * ld_ctx + (size_t)(kvh * GRP + i) * DH + d] = acc[i] / sm_l[i];
+    }
+}
+
+__global__ void __launch_bounds__(1024) k_pf_argmax(const float* __restrict__ logits, int n, int* tok, int* hist, int* pos_out, int pos) {
+    float bv = -INFINITY; int bi = INT_MAX;
+    for (int i = threadIdx.x; i < n; i += 1024) { const float v = logits[i]; if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
+    __shared__ float sv[1024]; __shared__ int si[1024];
+    sv[threadIdx.x] = bv; si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int s = 512; s >= 1; s >>= 1) {
+        if (threadIdx.x < s) {
+            const float ov = sv[threadIdx.x + s]; const int oi = si[threadIdx.x + s];
+            if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) { sv[threadIdx.x] = ov; si[threadIdx.x] = oi; }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const int nt = si[0] == INT_MAX ? 0 : si[0];
+        *tok = nt; if (hist) hist[pos + 1] = nt; *pos_out = pos + 1;
+    }
+}
+
+}  // namespace
+
+void hx_pf_embed(const int* ids, const float* emb, float* X, int n_tok, int DM, cudaStream_t st) {
+    k_pf_embed<<<n_tok, 256, 0, st>>>(ids, emb, X, DM);
+    HX_COUNT_LAUNCH(1);
+}
+
+void hx_pf_digits(const float* src, int ld, int n_tok, int K, int swiglu, const float* g, float eps,
+                  uint8_t* cells, int ncols, float* scale, cudaStream_t st) {
+    k_pf_digits<<<n_tok, 512, 0, st>>>(src, ld, K, swiglu, g, eps, cells, ncols, scale);
+    HX_COUNT_LAUNCH(1);
+}
+
+void hx_pf_qkpost(float* qkv, int ld, int n_tok, int pos0, int NH, int NKV, int DH, const float* qn_g, const float* kn_g,
+                  float eps, const float* cosT, const float* sinT, float* kc, float* vc, int cap, cudaStream_t st) {
+    const int threads = ((DH + 31) / 32) * 32;
+    k_pf_qkpost<<<dim3(NH + 2 * NKV, n_tok), threads, 0, st>>>(qkv, ld, pos0, NH, NKV, DH, qn_g, kn_g, eps, cosT, sinT, kc, vc, cap);
+    HX_COUNT_LAUNCH(1);
+}
+
+int hx_pf_attn(const float* qkv, int ld, int n_tok, int pos0, int NH, int NKV, int DH, const float* kc, const float* vc,
+               int cap, float scale, float* ctx, int ld_ctx, cudaStream_t st) {
+    const int GRP = NH / NKV, spitch = pos0 + n_tok + 1;
+    const size_t smem = ((size_t)GRP * DH + (size_t)GRP * spitch) * 4;
+    if (smem > 200 * 1024) return hx_fail(HX_ERR_ARG, "batched prefill attention: %d positions exceed its shared-memory score buffer", pos0 + n_tok);
+    dim3 grid(NKV, n_tok);
+#define HX_PF_ATTN(G)                                                                                                   \
+    case G: {                                                                                                           \
+        static size_t cur = 0;                                                                                          \
+        if (smem > 48 * 1024 && smem > cur) { HX_CUDA(cudaFuncSetAttribute(k_pf_attn<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); cur = 200 * 1024; } \
+        k_pf_attn<G><<<grid, 128, smem, st>>>(qkv, ld, pos0, NH, DH, kc, vc, cap, scale, ctx, ld_ctx, spitch);          \
+    } break;
+    switch (GRP) {
+        HX_PF_ATTN(1) HX_PF_ATTN(2) HX_PF_ATTN(3) HX_PF_ATTN(4) HX_PF_ATTN(5) HX_PF_ATTN(6) HX_PF_ATTN(7) HX_PF_ATTN(8)
+        default: return hx_fail(HX_ERR_ARG, "batched prefill attention: group of %d query heads per kv head not supported", GRP);
+    }
+#undef HX_PF_ATTN
+    HX_COUNT_LAUNCH(1);
+    HX_CUDA(cudaGetLastError());
+    return HX_OK;
+}
+
+void hx_pf_argmax(const float* logits, int n, int* tok, int* hist, int* pos_out, int pos, cudaStream_t st) {
+    k_pf_argmax<<<1, 1024, 0, st>>>(logits, n, tok, hist, pos_out, pos);
+    HX_COUNT_LAUNCH(1);
+}
