@@ -70,8 +70,10 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 }
 
 struct TcSmem {
-    uint64_t full[HX_TC_STAGES], empty[HX_TC_STAGES], accum;
+    uint64_t full[HX_TC_STAGES], empty[HX_TC_STAGES], accum, bfull;
     uint32_t tmem_base;
+    unsigned ticket;
+    float swi[128];
     volatile int abort_flag;
 };
 
@@ -79,20 +81,23 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
     extern __shared__ __align__(128) uint8_t smem_raw[];
     TcSmem& S = *reinterpret_cast<TcSmem*>(smem_raw);
     // swizzled operands need 1024-byte aligned cells (the swizzle is a function of the shared-memory address)
-    uint8_t* ring = smem_raw + (((s_u32(smem_raw) + 1024u + 1023u) & ~1023u) - s_u32(smem_raw));
+    static_assert(sizeof(TcSmem) <= 1024, "header overlaps the unit-scale chunk");
+    uint8_t* ring = smem_raw + (((s_u32(smem_raw) + 1536u + 1023u) & ~1023u) - s_u32(smem_raw));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NB = g.ncols, Sk = g.stage_ksteps;
     // a stage holds Sk K steps = Sk/4 cells of 256 columns
     const uint32_t b_cell_bytes = (uint32_t)NB * 128u + (g.digit_mode ? 0u : 2048u);       // one 256-column cell of B
     const uint32_t a_cell = HX_T128_CELL / 4, b_cell = b_cell_bytes / 4;                     // bytes per K step
-    const uint32_t stage_bytes = (uint32_t)Sk * (a_cell + b_cell);
-    const int nstage_iters = (g.ksteps + Sk - 1) / Sk;
+    // b_resident: the B cells of this CTA's K piece stay in shared memory across its units (the ring holds A only)
+    const int BR = g.b_resident;
+    const uint32_t stage_bytes = (uint32_t)Sk * (a_cell + (BR ? 0u : b_cell));
+    uint8_t* bres = ring + (size_t)HX_TC_STAGES * stage_bytes;      // [cells of a piece][NB * 128]
 
-    if (tid < 128) reinterpret_cast<uint32_t*>(smem_raw + 512)[tid] = 0x38383838u;      // a chunk of unit scales (digit mode)
+    if (tid < 128) reinterpret_cast<uint32_t*>(smem_raw + 1024)[tid] = 0x38383838u;      // a chunk of unit scales (digit mode)
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (tid == 0) {
         for (int i = 0; i < HX_TC_STAGES; i++) { mb_init(&S.full[i], 1); mb_init(&S.empty[i], 1); }
-        mb_init(&S.accum, 1);
+        mb_init(&S.accum, 1); mb_init(&S.bfull, 1);
         S.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -107,36 +112,53 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
     // TMEM columns: [0, 256) accumulator (ncols used), then per ring slot Sk*4 columns of SFA and of SFB
     const uint32_t col_sfa = 256, col_sfb = 256 + HX_TC_STAGES * HX_TC_MAX_SK * 4;
 
-    for (int mt = blockIdx.x; mt < g.ntiles; mt += gridDim.x) {
-        // tiles after the first reuse the barriers: phase bookkeeping continues across tiles
-        const int tile_iter = (mt - blockIdx.x) / gridDim.x;
-        const uint32_t base_it = (uint32_t)tile_iter * (uint32_t)nstage_iters;
+    // Work units: (128-row tile, K piece).  ksplit > 1 (digit mode only) cuts K into pieces of whole 256-column
+    // cells; each piece recombines its own digits and the last piece of a tile to finish (ticket) adds the
+    // pieces in K order and applies the epilogue.
+    const int P = g.ksplit > 1 ? g.ksplit : 1, kcells = g.ksteps / 4;
+    const int nunits = g.ntiles * P;
+    uint32_t base_it = 0;                          // stage iterations of the units this CTA has finished
+    uint32_t b_loads = 0; int cur_piece = -1;      // resident-B bookkeeping (same in every role)
+    int unit_iter = 0;
+    for (int u = blockIdx.x; u < nunits; u += gridDim.x, unit_iter++) {
+        const int mt = u / P, piece = u - mt * P;
+        const int ks_lo = (piece * kcells / P) * 4, ks_hi = ((piece + 1) * kcells / P) * 4;
+        const int n_it = (ks_hi - ks_lo + Sk - 1) / Sk;
+        int n_it_run = n_it;
+        const bool new_b = BR && (unit_iter == 0 || piece != cur_piece);
         if (warp == 0 && lane == 0) {
             // ------------------------------ producer ------------------------------
-            for (int it = 0; it < nstage_iters; it++) {
+            if (new_b) {        // every MMA of the previous unit has completed (its epilogue ran before the CTA barrier)
+                const uint32_t bytes = (uint32_t)((ks_hi - ks_lo) / 4) * b_cell_bytes;
+                mb_expect(&S.bfull, bytes);
+                bulk_load(bres, g.b + (size_t)(ks_lo / 4) * b_cell_bytes, bytes, &S.bfull);
+            }
+            for (int it = 0; it < n_it; it++) {
                 const uint32_t git = base_it + it, slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
                 if (round > 0 && !mb_wait(&S.empty[slot], (round - 1) & 1, &S.abort_flag)) break;
-                const int ks0 = it * Sk, nk = min(Sk, g.ksteps - ks0);
+                const int ks0 = ks_lo + it * Sk, nk = min(Sk, ks_hi - ks0);
                 uint8_t* sa = ring + (size_t)slot * stage_bytes;
                 uint8_t* sb = sa + (size_t)Sk * a_cell;
-                mb_expect(&S.full[slot], (uint32_t)nk * (a_cell + b_cell));
+                mb_expect(&S.full[slot], (uint32_t)nk * (a_cell + (BR ? 0u : b_cell)));
                 bulk_load(sa, g.a + ((size_t)mt * g.ksteps + ks0) * a_cell, (uint32_t)nk * a_cell, &S.full[slot]);
-                bulk_load(sb, g.b + (size_t)ks0 * b_cell, (uint32_t)nk * b_cell, &S.full[slot]);
+                if (!BR) bulk_load(sb, g.b + (size_t)ks0 * b_cell, (uint32_t)nk * b_cell, &S.full[slot]);
             }
         } else if (warp == 1 && lane == 0) {
             // ------------------------------ MMA issuer ------------------------------
             // instruction descriptor: E2M1 x E2M1, UE4M3 scales, K-major both, N = NB, M = 128, K = 64
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | (8u << 24);
-            if (g.digit_mode && mt == (int)blockIdx.x) {
+            if (g.digit_mode && unit_iter == 0) {
                 // unit scales (E4M3 1.0) for every digit column: sixteen TMEM columns cover any N up to 256
-                for (int c = 0; c < 4; c++) tc_cp_sf(tmem + col_sfb + c * 4, smem_desc(s_u32(smem_raw + 512), 16, 128));
+                for (int c = 0; c < 4; c++) tc_cp_sf(tmem + col_sfb + c * 4, smem_desc(s_u32(smem_raw + 1024), 16, 128));
             }
-            for (int it = 0; it < nstage_iters; it++) {
+            if (new_b) { if (!mb_wait(&S.bfull, b_loads & 1u, &S.abort_flag)) n_it_run = 0; }
+            for (int it = 0; it < n_it_run; it++) {
                 const uint32_t git = base_it + it, slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
                 if (!mb_wait(&S.full[slot], round & 1, &S.abort_flag)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int ks0 = it * Sk, nk = min(Sk, g.ksteps - ks0);
-                const uint32_t sa = s_u32(ring + (size_t)slot * stage_bytes), sb = sa + (uint32_t)Sk * a_cell;
+                const int ks0 = ks_lo + it * Sk, nk = min(Sk, ks_hi - ks0);
+                const uint32_t sa = s_u32(ring + (size_t)slot * stage_bytes);
+                const uint32_t sb = BR ? s_u32(bres) + (uint32_t)(it * (Sk / 4)) * b_cell_bytes : sa + (uint32_t)Sk * a_cell;
                 for (int rep = 0; rep < ((g.dbg & 8) ? 4 : 1); rep++)
                 for (int k = 0; k < nk; k++) {
                     const uint32_t ta = tmem + col_sfa + (slot * HX_TC_MAX_SK + k) * 4;
@@ -155,14 +177,36 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
             tc_commit(&S.accum);                    // accumulator complete
         } else if (warp >= 2) {
             // ------------------------------ epilogue: TMEM -> registers -> global ------------------------------
-            if (mb_wait(&S.accum, (uint32_t)tile_iter & 1u, &S.abort_flag)) {
+            if (mb_wait(&S.accum, (uint32_t)unit_iter & 1u, &S.abort_flag)) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int sub = warp & 3;                          // TMEM lanes 32*sub .. 32*sub+31
-                const int row = mt * 128 + sub * 32 + lane;
+                const int rl = sub * 32 + lane, row = mt * 128 + rl;
                 if (g.digit_mode) {
                     const float tsr = g.pair64 ? (((row & 127) < 64) ? g.ts[0] : g.ts[1])
                                                : (row < g.bound0 ? g.ts[0] : (row < g.bound1 ? g.ts[1] : g.ts[2]));
-                    for (int t = 0; t < NB / 16; t++) {
+                    const int ntok = NB / 16;
+                    // final value of (token t, this row): tensor scale, then store / residual add / SwiGLU across the
+                    // gate (rows 0..63 of the tile) and up (rows 64..127) halves
+                    auto finalize = [&](int t, float v) {
+                        v *= tsr;
+                        if (g.swiglu) {
+                            S.swi[rl] = v;
+                            asm volatile("bar.sync 1, 128;" ::: "memory");
+                            if (rl < 64 && mt * 64 + rl < g.rows) {
+                                const float gt = S.swi[rl], up = S.swi[rl + 64];
+                                const float sgn = gt < 0.0f ? -1.0f : 1.0f;
+                                const float ex = __expf(-(sgn * gt));
+                                const float th = sgn * ((1.0f - ex) / (1.0f + ex));
+                                g.out[(size_t)t * g.ld_out + mt * 64 + rl] = gt * (0.5f * (1.0f + th)) * up;
+                            }
+                            asm volatile("bar.sync 1, 128;" ::: "memory");
+                        } else if (row < g.rows) {
+                            float* o = g.out + (size_t)t * g.ld_out + row;
+                            *o = g.resid ? *o + v : v;
+                        }
+                    };
+                    float* part = g.partial + ((size_t)(mt * P) * HX_TC_MAX_TOK) * 128;      // [piece][token][row in tile]
+                    for (int t = 0; t < ntok; t++) {
                         uint32_t r[16];
                         const uint32_t ta = tmem + ((uint32_t)(sub * 32) << 16) + (uint32_t)(t * 16);
                         asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -173,10 +217,25 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
                         float v = 0.0f;
 #pragma unroll
                         for (int j = 15; j >= 0; j--) v = fmaf(v, 0.25f, __uint_as_float(r[j]));
-                        v = v * g.col_scale[t] * tsr;
-                        if (row < g.rows) {
-                            float* o = g.out + (size_t)t * g.ld_out + row;
-                            *o = g.resid ? *o + v : v;
+                        v = v * g.col_scale[t];
+                        if (P > 1) part[((size_t)piece * HX_TC_MAX_TOK + t) * 128 + rl] = v;
+                        else finalize(t, v);
+                    }
+                    if (P > 1) {
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (tid == 64) {
+                            unsigned old;
+                            asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(g.tickets + mt) : "memory");
+                            S.ticket = old;
+                        }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (S.ticket == (unsigned)(P - 1)) {
+                            for (int t = 0; t < ntok; t++) {
+                                float v = 0.0f;
+                                for (int q = 0; q < P; q++) v += __ldcg(part + ((size_t)q * HX_TC_MAX_TOK + t) * 128 + rl);
+                                finalize(t, v);
+                            }
+                            if (tid == 64) g.tickets[mt] = 0u;
                         }
                     }
                 } else
@@ -194,7 +253,9 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             }
         }
-        // all roles meet before the next tile (the accumulator is reused)
+        base_it += (uint32_t)n_it;
+        if (new_b) { b_loads++; cur_piece = piece; }
+        // all roles meet before the next unit (the accumulator is reused)
         __syncthreads();
     }
     if (S.abort_flag && tid == 0 && g.err) *g.err = 1;
@@ -205,18 +266,32 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
 }  // namespace
 
 size_t hx_gemm_tc_smem(int ncols, int stage_ksteps) {
-    return 3072 + (size_t)HX_TC_STAGES * (stage_ksteps / 4) * (HX_T128_CELL + (size_t)ncols * 128 + 2048);
+    return 4096 + (size_t)HX_TC_STAGES * (stage_ksteps / 4) * (HX_T128_CELL + (size_t)ncols * 128 + 2048);
+}
+// resident-B variant: ring of A cells + the B cells of one K piece
+static size_t gemm_tc_smem_resident(int ncols, int stage_ksteps, int cells_per_piece) {
+    return 4096 + (size_t)HX_TC_STAGES * (stage_ksteps / 4) * HX_T128_CELL + (size_t)cells_per_piece * ncols * 128;
+}
+
+// One-time function attribute (call outside any stream capture).
+int hx_gemm_tc_prepare() {
+    static bool attr = false;
+    if (!attr) { HX_CUDA(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); attr = true; }
+    return HX_OK;
 }
 
 int hx_gemm_tc_launch(const HxGemmTC& g, cudaStream_t st) {
     HX_CHECK_ARG(g.a && g.b && (g.digit_mode ? (g.out && g.col_scale && g.ncols % 16 == 0) : g.y != nullptr) && g.ntiles > 0 && g.ksteps > 0);
     HX_CHECK_ARG(g.ncols >= 8 && g.ncols <= 256 && g.ncols % 8 == 0);
     HX_CHECK_ARG(g.stage_ksteps >= 4 && g.stage_ksteps <= HX_TC_MAX_SK && g.stage_ksteps % 4 == 0 && g.ksteps % 4 == 0);
-    const size_t smem = hx_gemm_tc_smem(g.ncols, g.stage_ksteps);
+    const int Pq = g.ksplit > 1 ? g.ksplit : 1, kc = g.ksteps / 4;
+    if (g.b_resident) HX_CHECK_ARG(g.digit_mode && g.stage_ksteps == 4);
+    const size_t smem = g.b_resident ? gemm_tc_smem_resident(g.ncols, g.stage_ksteps, (kc + Pq - 1) / Pq) : hx_gemm_tc_smem(g.ncols, g.stage_ksteps);
     if (smem > 227 * 1024) return hx_fail(HX_ERR_ARG, "tensor-core GEMM stage too large (%zu bytes of shared memory)", smem);
-    static bool attr = false;
-    if (!attr) { HX_CUDA(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); attr = true; }
-    int grid = g.ntiles; if (grid > 148) grid = 148;
+    { const int prc = hx_gemm_tc_prepare(); if (prc) return prc; }
+    const int P = g.ksplit > 1 ? g.ksplit : 1;
+    if (P > 1) HX_CHECK_ARG(g.digit_mode && g.partial && g.tickets && P <= g.ksteps / 4 && g.ncols / 16 <= HX_TC_MAX_TOK);
+    int grid = g.ntiles * P; if (grid > 148) grid = g.b_resident ? (148 / P) * P : 148;      // resident B: a CTA keeps one K piece
     k_gemm_tc<<<grid, 192, smem, st>>>(g);
     HX_COUNT_LAUNCH(1);
     HX_CUDA(cudaGetLastError());

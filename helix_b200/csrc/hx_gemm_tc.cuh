@@ -5,6 +5,7 @@
 #define HX_T128_CELL 18432         // one (128-row tile, 256-column group) cell of A: 16384 B codes + 4 x 512 B scales
 #define HX_TC_STAGES 4
 #define HX_TC_MAX_SK 8             // 64-column steps per ring stage (4 or 8)
+#define HX_TC_MAX_TOK 16           // tokens per launch in digit mode (16 digit columns each)
 
 struct HxGemmTC {
     const uint8_t* a;              // T128 cells, [tile][kstep]
@@ -22,7 +23,13 @@ struct HxGemmTC {
     int resid;                     // 1: add to out instead of storing
     float ts[3]; int bound0, bound1;   // per-row tensor scale: rows < bound0 ts[0], < bound1 ts[1], else ts[2]
     int pair64;                    // 1: ts[0] for rows with (row % 128) < 64, ts[1] for the others (gate/up tiles)
+    int swiglu;                    // 1: tiles hold 64 gate + 64 up rows; out[t][tile * 64 + r] = silu(gate_r) * up_r, rows = hidden size
+    int ksplit;                    // > 1: K pieces per tile (digit mode), merged in K order by the last piece to finish
+    float* partial;                // [ntiles][ksplit][HX_TC_MAX_TOK][128] partial sums of the pieces
+    unsigned* tickets;             // [ntiles], zero between launches
+    int b_resident;                // digit mode: keep the B cells of a CTA's K piece in shared memory (grid is a multiple of ksplit)
 };
 
 int hx_gemm_tc_launch(const HxGemmTC& g, cudaStream_t st);
+int hx_gemm_tc_prepare();      // sets the kernel's shared-memory attribute; call once outside stream capture
 size_t hx_gemm_tc_smem(int ncols, int stage_ksteps);

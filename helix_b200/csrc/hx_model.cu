@@ -88,8 +88,9 @@ struct hx_model {
     uint64_t decode_bytes = 0, committed_bytes = 0;
     int kv_len = 0;
     // batched prefill (chunks of HX_PF_TB tokens through the tcgen05 GEMM); buffers are created on first use
-    float *pf_x = nullptr, *pf_qkv = nullptr, *pf_ctx = nullptr, *pf_gu = nullptr, *pf_scale = nullptr; uint8_t* pf_cells = nullptr; int* pf_err = nullptr;
-    int pf_gu_ld = 0; bool pf_batched = true;
+    float *pf_x = nullptr, *pf_qkv = nullptr, *pf_ctx = nullptr, *pf_gu = nullptr, *pf_scale = nullptr; uint8_t* pf_cells = nullptr; int* pf_err = nullptr; float* pf_partial = nullptr; unsigned* pf_tickets = nullptr;
+    int pf_gu_ld = 0; bool pf_batched = true; size_t pf_partial_n = 0;
+    int* d_pf_pos = nullptr; cudaGraphExec_t g_pf_chunk = nullptr; bool pf_graph_failed = false; int pf_chunk_launches = 0;
 };
 
 namespace {
@@ -608,6 +609,7 @@ HX_API int hx_model_free(hx_model* m) {
     if (!m) return HX_OK;
     if (m->g_decode) cudaGraphExecDestroy(m->g_decode);
     if (m->g_prefill) cudaGraphExecDestroy(m->g_prefill);
+    if (m->g_pf_chunk) cudaGraphExecDestroy(m->g_pf_chunk);
     if (m->ev0) cudaEventDestroy(m->ev0);
     if (m->ev1) cudaEventDestroy(m->ev1);
     for (void* p : m->allocs) cudaFree(p);
@@ -865,10 +867,11 @@ HX_API int hx_decode_step(hx_model* m, const int32_t* ids, int pos, int32_t* nex
 // ---- batched prefill ---------------------------------------------------------------------------------
 static int pf_alloc(hx_model* m) {
     if (m->pf_x) return HX_OK;
+    { const int prc = hx_gemm_tc_prepare(); if (prc) return prc; }
     const hx_config& c = m->cfg;
     int maxK = c.d_model > m->QD ? c.d_model : m->QD; if (c.d_ff > maxK) maxK = c.d_ff;
     const size_t cells = (size_t)((maxK + 255) / 256) * (16 * HX_PF_TB) * 128;
-    m->pf_gu_ld = m->layers.empty() ? 128 : m->layers[0].gu.tiles128 * 128;
+    m->pf_gu_ld = m->layers.empty() ? 64 : m->layers[0].gu.tiles128 * 64;      // hidden size rounded up to whole tiles
     int rc;
     if ((rc = dalloc(m, &m->pf_x, (size_t)HX_PF_TB * c.d_model))) return rc;
     if ((rc = dalloc(m, &m->pf_qkv, (size_t)HX_PF_TB * (m->QD + 2 * m->KVD)))) return rc;
@@ -877,47 +880,93 @@ static int pf_alloc(hx_model* m) {
     if ((rc = dalloc(m, &m->pf_scale, (size_t)HX_PF_TB))) return rc;
     if ((rc = dalloc(m, &m->pf_cells, cells))) return rc;
     if ((rc = dalloc(m, &m->pf_err, (size_t)4))) return rc;
+    if ((rc = dalloc(m, &m->d_pf_pos, (size_t)4))) return rc;
     HX_CUDA(cudaMemsetAsync(m->pf_err, 0, 16, m->st));
+    {   // partial sums [tile][piece][token][128] of the most demanding linear, tickets per tile
+        size_t need = 0; int maxt = m->head.tiles128;
+        auto acc = [&](const Fused& f) { const int kc = f.ksteps / 4; int P = 1; if (2 * f.tiles128 <= 148) { P = 148 / f.tiles128; if (P > kc) P = kc; }
+                                      const size_t v = (size_t)f.tiles128 * P * HX_TC_MAX_TOK * 128; if (v > need) need = v; if (f.tiles128 > maxt) maxt = f.tiles128; };
+        for (auto& ly : m->layers) { acc(ly.qkv); acc(ly.o); acc(ly.gu); acc(ly.down); }
+        acc(m->head);
+        m->pf_partial_n = need;
+        if ((rc = dalloc(m, &m->pf_partial, need))) return rc;
+        if ((rc = dalloc(m, &m->pf_tickets, (size_t)maxt + 8))) return rc;
+        HX_CUDA(cudaMemsetAsync(m->pf_tickets, 0, ((size_t)maxt + 8) * 4, m->st));
+    }
     return HX_OK;
 }
 
 // one linear of a chunk: digits of `src` -> GEMM against f -> out (token-major)
 static int pf_linear(hx_model* m, const Fused& f, const float* src, int ld_src, int n, int swiglu, const float* g,
                      float* out, int ld_out, int rows, int resid, int pair64) {
-    hx_pf_digits(src, ld_src, n, f.K, swiglu, g, m->cfg.norm_eps, m->pf_cells, 16 * n, m->pf_scale, m->st);
+    hx_pf_digits(src, ld_src, n, f.K, 0, g, m->cfg.norm_eps, m->pf_cells, 16 * n, m->pf_scale, m->st);
     HxGemmTC q = {};
     q.a = f.t128; q.b = m->pf_cells; q.rows = rows; q.ntiles = f.tiles128; q.ksteps = f.ksteps; q.ncols = 16 * n; q.stage_ksteps = 4;
     q.err = m->pf_err; q.digit_mode = 1; q.col_scale = m->pf_scale; q.out = out; q.ld_out = ld_out; q.resid = resid;
-    q.ts[0] = f.ts[0]; q.ts[1] = f.ts[1]; q.ts[2] = f.ts[2]; q.bound0 = f.bound0; q.bound1 = f.bound1; q.pair64 = pair64;
+    q.ts[0] = f.ts[0]; q.ts[1] = f.ts[1]; q.ts[2] = f.ts[2]; q.bound0 = f.bound0; q.bound1 = f.bound1; q.pair64 = pair64; q.swiglu = swiglu;
+    // few tiles: cut K so that about one CTA per SM works (tiles * pieces <= 148).  Keeping the B cells of a piece
+    // resident (b_resident) with more, smaller units measured slower: a unit's epilogue is not overlapped with the
+    // next unit's loads.
+    const int kcells = f.ksteps / 4;
+    int P = 1;
+    if (2 * f.tiles128 <= 148) { P = 148 / f.tiles128; if (P > kcells) P = kcells; }
+    q.ksplit = P; q.partial = m->pf_partial; q.tickets = m->pf_tickets; q.b_resident = 0;
+    if ((size_t)f.tiles128 * P * HX_TC_MAX_TOK * 128 > m->pf_partial_n) return hx_fail(HX_ERR_ARG, "prefill: partial-sum buffer too small");
     return hx_gemm_tc_launch(q, m->st);
+}
+
+// The launches of one chunk of n tokens whose first position is *d_pf_pos; ends by advancing that position.
+static int pf_enqueue_chunk(hx_model* m, int n) {
+    const hx_config& c = m->cfg;
+    const int DH = c.head_dim, DM = c.d_model, QD = m->QD, KVD = m->KVD, cap = m->kv_cap;
+    const int ldq = QD + 2 * KVD;
+    const float att_scale = 1.0f / sqrtf((float)DH);
+    int rc;
+    hx_pf_embed(m->d_prompt, m->d_pf_pos, m->emb, m->pf_x, n, DM, m->st);
+    for (int L = 0; L < c.n_layers; L++) {
+        Layer& ly = m->layers[L];
+        float* kc = m->kc + (size_t)L * c.n_kv_heads * cap * DH; float* vc = m->vc + (size_t)L * c.n_kv_heads * cap * DH;
+        if ((rc = pf_linear(m, ly.qkv, m->pf_x, DM, n, 0, ly.in_g, m->pf_qkv, ldq, ly.qkv.N, 0, 0))) return rc;
+        hx_pf_qkpost(m->pf_qkv, ldq, n, m->d_pf_pos, c.n_heads, c.n_kv_heads, DH, ly.qn_g, ly.kn_g, c.norm_eps, m->cosT, m->sinT, kc, vc, cap, m->st);
+        if ((rc = hx_pf_attn(m->pf_qkv, ldq, n, m->d_pf_pos, c.n_heads, c.n_kv_heads, DH, kc, vc, cap, att_scale, m->pf_ctx, QD, m->st))) return rc;
+        if ((rc = pf_linear(m, ly.o, m->pf_ctx, QD, n, 0, nullptr, m->pf_x, DM, ly.o.N, 1, 0))) return rc;
+        if ((rc = pf_linear(m, ly.gu, m->pf_x, DM, n, 1, ly.post_g, m->pf_gu, m->pf_gu_ld, c.d_ff, 0, 1))) return rc;       // SwiGLU in the epilogue
+        if ((rc = pf_linear(m, ly.down, m->pf_gu, m->pf_gu_ld, n, 0, nullptr, m->pf_x, DM, ly.down.N, 1, 0))) return rc;
+    }
+    hx_pf_advance(m->d_pf_pos, n, m->st);
+    return HX_OK;
 }
 
 // Prompt positions [0, T) in chunks of HX_PF_TB tokens; ends like the token-by-token path: KV rows written,
 // logits of the last position in m->logits, its arg-max in d_tok / d_hist[T], *d_pos = T.
+// Full chunks replay one captured CUDA graph (the position lives in device memory); the last, shorter chunk
+// and the lm_head are launched directly.
 static int run_prefill_batched(hx_model* m, int T) {
     const hx_config& c = m->cfg;
-    const int DH = c.head_dim, DM = c.d_model, QD = m->QD, KVD = m->KVD, cap = m->kv_cap;
     int rc = pf_alloc(m); if (rc) return rc;
-    const int ldq = QD + 2 * KVD;
-    const float att_scale = 1.0f / sqrtf((float)DH);
-    for (int p0 = 0; p0 < T; p0 += HX_PF_TB) {
-        const int n = T - p0 < HX_PF_TB ? T - p0 : HX_PF_TB;
-        hx_pf_embed(m->d_prompt + p0, m->emb, m->pf_x, n, DM, m->st);
-        for (int L = 0; L < c.n_layers; L++) {
-            Layer& ly = m->layers[L];
-            float* kc = m->kc + (size_t)L * c.n_kv_heads * cap * DH; float* vc = m->vc + (size_t)L * c.n_kv_heads * cap * DH;
-            if ((rc = pf_linear(m, ly.qkv, m->pf_x, DM, n, 0, ly.in_g, m->pf_qkv, ldq, ly.qkv.N, 0, 0))) return rc;
-            hx_pf_qkpost(m->pf_qkv, ldq, n, p0, c.n_heads, c.n_kv_heads, DH, ly.qn_g, ly.kn_g, c.norm_eps, m->cosT, m->sinT, kc, vc, cap, m->st);
-            if ((rc = hx_pf_attn(m->pf_qkv, ldq, n, p0, c.n_heads, c.n_kv_heads, DH, kc, vc, cap, att_scale, m->pf_ctx, QD, m->st))) return rc;
-            if ((rc = pf_linear(m, ly.o, m->pf_ctx, QD, n, 0, nullptr, m->pf_x, DM, ly.o.N, 1, 0))) return rc;
-            if ((rc = pf_linear(m, ly.gu, m->pf_x, DM, n, 0, ly.post_g, m->pf_gu, m->pf_gu_ld, ly.gu.tiles128 * 128, 0, 1))) return rc;
-            if ((rc = pf_linear(m, ly.down, m->pf_gu, m->pf_gu_ld, n, 1, nullptr, m->pf_x, DM, ly.down.N, 1, 0))) return rc;
-        }
-        if (p0 + n == T) {        // logits and arg-max of the last position
-            if ((rc = pf_linear(m, m->head, m->pf_x + (size_t)(n - 1) * DM, DM, 1, 0, m->final_g, m->logits, 0, m->head.N, 0, 0))) return rc;
-            hx_pf_argmax(m->logits, c.vocab, m->d_tok, m->d_hist, m->d_pos, T - 1, m->st);
-        }
+    HX_CUDA(cudaMemsetAsync(m->d_pf_pos, 0, 4, m->st));
+    const int nfull = T / HX_PF_TB, rem = T - nfull * HX_PF_TB;
+    if (nfull > 1 && !m->g_pf_chunk && !m->pf_graph_failed) {
+        cudaGraph_t g = nullptr;
+        HX_CUDA(cudaStreamBeginCapture(m->st, cudaStreamCaptureModeThreadLocal));
+        const unsigned long long before = g_hx_launches;
+        rc = pf_enqueue_chunk(m, HX_PF_TB);
+        cudaError_t e = cudaStreamEndCapture(m->st, &g);
+        g_hx_launches = before;
+        if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+        if (e == cudaSuccess) e = cudaGraphInstantiate(&m->g_pf_chunk, g, 0);
+        if (g) cudaGraphDestroy(g);
+        if (e != cudaSuccess) { (void)cudaGetLastError(); m->g_pf_chunk = nullptr; m->pf_graph_failed = true; }
+        m->pf_chunk_launches = 2 + 11 * c.n_layers;
     }
+    for (int i = 0; i < nfull; i++) {
+        if (m->g_pf_chunk) { HX_CUDA(cudaGraphLaunch(m->g_pf_chunk, m->st)); HX_COUNT_LAUNCH(m->pf_chunk_launches); }
+        else if ((rc = pf_enqueue_chunk(m, HX_PF_TB))) return rc;
+    }
+    if (rem && (rc = pf_enqueue_chunk(m, rem))) return rc;
+    const int nlast = rem ? rem : HX_PF_TB;
+    if ((rc = pf_linear(m, m->head, m->pf_x + (size_t)(nlast - 1) * c.d_model, c.d_model, 1, 0, m->final_g, m->logits, 0, m->head.N, 0, 0))) return rc;
+    hx_pf_argmax(m->logits, c.vocab, m->d_tok, m->d_hist, m->d_pos, T - 1, m->st);
     HX_CUDA(cudaGetLastError());
     return HX_OK;
 }

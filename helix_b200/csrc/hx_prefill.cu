@@ -20,13 +20,13 @@ __device__ __forceinline__ float pf_silu_mul(float g, float u) {      // same fo
     return g * (0.5f * (1.0f + th)) * u;
 }
 
-__global__ void __launch_bounds__(256) k_pf_embed(const int* __restrict__ ids, const float* __restrict__ emb, float* __restrict__ X, int DM) {
-    const float4* src = reinterpret_cast<const float4*>(emb + (size_t)ids[blockIdx.x] * DM);
+__global__ void __launch_bounds__(256) k_pf_embed(const int* __restrict__ ids, const int* __restrict__ posp, const float* __restrict__ emb, float* __restrict__ X, int DM) {
+    const float4* src = reinterpret_cast<const float4*>(emb + (size_t)ids[*posp + blockIdx.x] * DM);
     float4* dst = reinterpret_cast<float4*>(X + (size_t)blockIdx.x * DM);
     for (int i = threadIdx.x; i < DM / 4; i += blockDim.x) dst[i] = src[i];
 }
 
-// One CTA per token.
+// grid (token, slice of K): every CTA of a token computes the token's statistics, then emits its slice of items.
 __global__ void __launch_bounds__(512) k_pf_digits(const float* __restrict__ src, int ld, int K, int swiglu, const float* __restrict__ g,
                                                     float eps, uint8_t* __restrict__ cells, int ncols, float* __restrict__ scale) {
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -55,12 +55,14 @@ __global__ void __launch_bounds__(512) k_pf_digits(const float* __restrict__ src
     float Sg = 1.0f;
     const float vmax = tmx * inv * 1.0000005f;
     if (vmax > 0.0f && vmax < INFINITY) Sg = __uint_as_float(__float_as_uint(vmax) & 0x7F800000u);
-    if (tid == 0) scale[t] = Sg;
+    if (tid == 0 && blockIdx.y == 0) scale[t] = Sg;
     const float mul = (inv / Sg) * 2147483648.0f;
     // pass 2: items of 8 consecutive elements -> sixteen digit words
     const int Kc = ((K + 255) / 256) * 256;
     const size_t cell_bytes = (size_t)ncols * 128;
-    for (int it = tid; it < Kc / 8; it += 512) {
+    const int nit = Kc / 8, per = (nit + gridDim.y - 1) / gridDim.y;
+    const int it_hi = min(nit, (int)(blockIdx.y + 1) * per);
+    for (int it = blockIdx.y * per + tid; it < it_hi; it += 512) {
         const int k = it * 8;
         uint32_t M[8]; uint32_t sg = 0u;
 #pragma unroll
@@ -88,11 +90,11 @@ __global__ void __launch_bounds__(512) k_pf_digits(const float* __restrict__ src
 }
 
 // grid (NH + 2 NKV, n_tok), block DH threads (DH <= 256)
-__global__ void __launch_bounds__(256) k_pf_qkpost(float* __restrict__ qkv, int ld, int pos0, int NH, int NKV, int DH,
+__global__ void __launch_bounds__(256) k_pf_qkpost(float* __restrict__ qkv, int ld, const int* __restrict__ posp, int NH, int NKV, int DH,
                                                     const float* __restrict__ qn_g, const float* __restrict__ kn_g, float eps,
                                                     const float* __restrict__ cosT, const float* __restrict__ sinT,
                                                     float* __restrict__ kc, float* __restrict__ vc, int cap) {
-    const int hs = blockIdx.x, t = blockIdx.y, e = threadIdx.x, half = DH >> 1, pos = pos0 + t;
+    const int hs = blockIdx.x, t = blockIdx.y, e = threadIdx.x, half = DH >> 1, pos = *posp + t;
     const int sec = hs < NH ? 0 : (hs < NH + NKV ? 1 : 2);
     float* row = qkv + (size_t)t * ld + (size_t)hs * DH;
     __shared__ float sm[256]; __shared__ float red[8];
@@ -120,66 +122,86 @@ __global__ void __launch_bounds__(256) k_pf_qkpost(float* __restrict__ qkv, int 
     }
 }
 
-// grid (NKV, n_tok), 128 threads, dynamic shared memory: GRP*DH queries + GRP*(pos0 + n_tok) scores
+// grid (NKV, n_tok), 128 threads.  Online softmax over tiles of PF_KT cached positions (m seeded -1e8 like
+// fused_decode_attn_kernel.hx:74-102), so shared memory does not grow with the context.
+#define PF_KT 64
 template <int GRP>
-__global__ void __launch_bounds__(128) k_pf_attn(const float* __restrict__ qkv, int ld, int pos0, int NH, int DH,
+__global__ void __launch_bounds__(128) k_pf_attn(const float* __restrict__ qkv, int ld, const int* __restrict__ posp, int NH, int DH,
                                                   const float* __restrict__ kc, const float* __restrict__ vc, int cap, float scale,
-                                                  float* __restrict__ ctx, int ld_ctx, int spitch) {
+                                                  float* __restrict__ ctx, int ld_ctx) {
     extern __shared__ float smf[];
     const int kvh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int T = pos0 + t + 1;
+    const int T = *posp + t + 1;
     float* sq = smf;                   // [GRP][DH]
-    float* sp = smf + GRP * DH;        // [GRP][spitch]
-    __shared__ float sm_m[GRP], sm_l[GRP];
+    float* sp = smf + GRP * DH;        // [GRP][PF_KT]
+    __shared__ float sm_m[GRP], sm_l[GRP], sm_r[GRP];
     for (int i = tid; i < GRP * DH; i += 128) sq[i] = qkv[(size_t)t * ld + (size_t)kvh * GRP * DH + i];
+    if (tid < GRP) { sm_m[tid] = -100000000.0f; sm_l[tid] = 0.0f; }
     __syncthreads();
     const float* kbase = kc + (size_t)kvh * cap * DH;
     const float* vbase = vc + (size_t)kvh * cap * DH;
-    // scores: a warp per key, lanes over the head dimension
-    for (int j = warp; j < T; j += 4) {
-        float dot[GRP];
+    float acc[GRP][2];                 // output dimensions tid and tid + 128
 #pragma unroll
-        for (int i = 0; i < GRP; i++) dot[i] = 0.0f;
-        for (int e = lane * 4; e < DH; e += 128) {
-            const float4 k4 = *reinterpret_cast<const float4*>(kbase + (size_t)j * DH + e);
+    for (int i = 0; i < GRP; i++) acc[i][0] = acc[i][1] = 0.0f;
+    for (int j0 = 0; j0 < T; j0 += PF_KT) {
+        const int nj = min(PF_KT, T - j0);
+        // scores: a warp per key, lanes over the head dimension
+        for (int j = warp; j < nj; j += 4) {
+            float dot[GRP];
 #pragma unroll
-            for (int i = 0; i < GRP; i++) {
-                const float4 q4 = *reinterpret_cast<const float4*>(sq + i * DH + e);
-                dot[i] = fmaf(q4.x, k4.x, dot[i]); dot[i] = fmaf(q4.y, k4.y, dot[i]);
-                dot[i] = fmaf(q4.z, k4.z, dot[i]); dot[i] = fmaf(q4.w, k4.w, dot[i]);
+            for (int i = 0; i < GRP; i++) dot[i] = 0.0f;
+            for (int e = lane * 4; e < DH; e += 128) {
+                const float4 k4 = *reinterpret_cast<const float4*>(kbase + (size_t)(j0 + j) * DH + e);
+#pragma unroll
+                for (int i = 0; i < GRP; i++) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(sq + i * DH + e);
+                    dot[i] = fmaf(q4.x, k4.x, dot[i]); dot[i] = fmaf(q4.y, k4.y, dot[i]);
+                    dot[i] = fmaf(q4.z, k4.z, dot[i]); dot[i] = fmaf(q4.w, k4.w, dot[i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < GRP; i++) { const float sv = hx_warp_sum(dot[i]); if (lane == 0) sp[i * PF_KT + j] = sv * scale; }
+        }
+        __syncthreads();
+        for (int i = warp; i < GRP; i += 4) {
+            float tm = -INFINITY;
+            for (int j = lane; j < nj; j += 32) tm = fmaxf(tm, sp[i * PF_KT + j]);
+            tm = hx_warp_max(tm);
+            const float mo = sm_m[i], mn = fmaxf(mo, tm);
+            float ls = 0.0f;
+            for (int j = lane; j < nj; j += 32) { const float pr = __expf(sp[i * PF_KT + j] - mn); sp[i * PF_KT + j] = pr; ls += pr; }
+            ls = hx_warp_sum(ls);
+            if (lane == 0) { const float rr = __expf(mo - mn); sm_r[i] = rr; sm_l[i] = sm_l[i] * rr + ls; sm_m[i] = mn; }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int d = tid + h * 128;
+            if (d < DH) {
+#pragma unroll
+                for (int i = 0; i < GRP; i++) acc[i][h] *= sm_r[i];
+                for (int j = 0; j < nj; j++) {
+                    const float vv = vbase[(size_t)(j0 + j) * DH + d];
+#pragma unroll
+                    for (int i = 0; i < GRP; i++) acc[i][h] = fmaf(sp[i * PF_KT + j], vv, acc[i][h]);
+                }
             }
         }
-#pragma unroll
-        for (int i = 0; i < GRP; i++) { const float s = hx_warp_sum(dot[i]); if (lane == 0) sp[i * spitch + j] = s * scale; }
+        __syncthreads();
     }
-    __syncthreads();
-    // softmax statistics: a warp per head (m seeded -1e8 like fused_decode_attn_kernel.hx:74-102)
-    for (int i = warp; i < GRP; i += 4) {
-        float m = -100000000.0f;
-        for (int j = lane; j < T; j += 32) m = fmaxf(m, sp[i * spitch + j]);
-        m = hx_warp_max(m);
-        float l = 0.0f;
-        for (int j = lane; j < T; j += 32) { const float p = __expf(sp[i * spitch + j] - m); sp[i * spitch + j] = p; l += p; }
-        l = hx_warp_sum(l);
-        if (lane == 0) { sm_m[i] = m; sm_l[i] = l; }
-    }
-    __syncthreads();
-    // P*V: thread per dimension, all heads of the group share the V row
-    for (int d = tid; d < DH; d += 128) {
-        float acc[GRP];
 #pragma unroll
-        for (int i = 0; i < GRP; i++) acc[i] = 0.0f;
-        for (int j = 0; j < T; j++) {
-            const float vv = vbase[(size_t)j * DH + d];
+    for (int h = 0; h < 2; h++) {
+        const int d = tid + h * 128;
+        if (d < DH) {
 #pragma unroll
-            for (int i = 0; i < GRP; i++) acc[i] = fmaf(sp[i * spitch + j], vv, acc[i]);
+            for (int i = 0; i < GRP; i++) ctx[(size_t)t * ld_ctx + (size_t)(kvh * GRP + i) * DH + d] = acc[i][h] / sm_l[i];
         }
-#pragma unroll
-        for (int i = 0; i < GRP; i++) ctx[(size_t)t * ld_ctx + (size_t)(kvh * GRP + i) * DH + d] = acc[i] / sm_l[i];
     }
 }
 
-__global__ void __launch_bounds__(1024) k_pf_argmax(const float* __restrict__ logits, int n, int* tok, int* hist, int* pos_out, int pos) {
+__global__ void k_pf_advance(int* posp, int n) { if (threadIdx.x == 0) *posp += n; }
+
+__global__ void __launch_bounds__(1024) k_pf_argmax(const float* __restrict__ logits, int n, int* tok, int* hist, int* pos_out, int pos) {   // pos: position of the logits row
     float bv = -INFINITY; int bi = INT_MAX;
     for (int i = threadIdx.x; i < n; i += 1024) { const float v = logits[i]; if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
     __shared__ float sv[1024]; __shared__ int si[1024];
@@ -200,44 +222,44 @@ __global__ void __launch_bounds__(1024) k_pf_argmax(const float* __restrict__ lo
 
 }  // namespace
 
-void hx_pf_embed(const int* ids, const float* emb, float* X, int n_tok, int DM, cudaStream_t st) {
-    k_pf_embed<<<n_tok, 256, 0, st>>>(ids, emb, X, DM);
+void hx_pf_embed(const int* ids, const int* posp, const float* emb, float* X, int n_tok, int DM, cudaStream_t st) {
+    k_pf_embed<<<n_tok, 256, 0, st>>>(ids, posp, emb, X, DM);
     HX_COUNT_LAUNCH(1);
 }
 
 void hx_pf_digits(const float* src, int ld, int n_tok, int K, int swiglu, const float* g, float eps,
                   uint8_t* cells, int ncols, float* scale, cudaStream_t st) {
-    k_pf_digits<<<n_tok, 512, 0, st>>>(src, ld, K, swiglu, g, eps, cells, ncols, scale);
+    const int slices = K >= 8192 ? 8 : 4;
+    k_pf_digits<<<dim3(n_tok, slices), 512, 0, st>>>(src, ld, K, swiglu, g, eps, cells, ncols, scale);
     HX_COUNT_LAUNCH(1);
 }
 
-void hx_pf_qkpost(float* qkv, int ld, int n_tok, int pos0, int NH, int NKV, int DH, const float* qn_g, const float* kn_g,
+void hx_pf_qkpost(float* qkv, int ld, int n_tok, const int* posp, int NH, int NKV, int DH, const float* qn_g, const float* kn_g,
                   float eps, const float* cosT, const float* sinT, float* kc, float* vc, int cap, cudaStream_t st) {
     const int threads = ((DH + 31) / 32) * 32;
-    k_pf_qkpost<<<dim3(NH + 2 * NKV, n_tok), threads, 0, st>>>(qkv, ld, pos0, NH, NKV, DH, qn_g, kn_g, eps, cosT, sinT, kc, vc, cap);
+    k_pf_qkpost<<<dim3(NH + 2 * NKV, n_tok), threads, 0, st>>>(qkv, ld, posp, NH, NKV, DH, qn_g, kn_g, eps, cosT, sinT, kc, vc, cap);
     HX_COUNT_LAUNCH(1);
 }
 
-int hx_pf_attn(const float* qkv, int ld, int n_tok, int pos0, int NH, int NKV, int DH, const float* kc, const float* vc,
+int hx_pf_attn(const float* qkv, int ld, int n_tok, const int* posp, int NH, int NKV, int DH, const float* kc, const float* vc,
                int cap, float scale, float* ctx, int ld_ctx, cudaStream_t st) {
-    const int GRP = NH / NKV, spitch = pos0 + n_tok + 1;
-    const size_t smem = ((size_t)GRP * DH + (size_t)GRP * spitch) * 4;
-    if (smem > 200 * 1024) return hx_fail(HX_ERR_ARG, "batched prefill attention: %d positions exceed its shared-memory score buffer", pos0 + n_tok);
+    const int GRP = NH / NKV;
+    if (DH > 256) return hx_fail(HX_ERR_ARG, "batched prefill attention: head_dim %d > 256", DH);
+    const size_t smem = ((size_t)GRP * DH + (size_t)GRP * PF_KT) * 4;
     dim3 grid(NKV, n_tok);
-#define HX_PF_ATTN(G)                                                                                                   \
-    case G: {                                                                                                           \
-        static size_t cur = 0;                                                                                          \
-        if (smem > 48 * 1024 && smem > cur) { HX_CUDA(cudaFuncSetAttribute(k_pf_attn<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); cur = 200 * 1024; } \
-        k_pf_attn<G><<<grid, 128, smem, st>>>(qkv, ld, pos0, NH, DH, kc, vc, cap, scale, ctx, ld_ctx, spitch);          \
-    } break;
+#define HX_PF_ATTN(G) case G: k_pf_attn<G><<<grid, 128, smem, st>>>(qkv, ld, posp, NH, DH, kc, vc, cap, scale, ctx, ld_ctx); break;
     switch (GRP) {
         HX_PF_ATTN(1) HX_PF_ATTN(2) HX_PF_ATTN(3) HX_PF_ATTN(4) HX_PF_ATTN(5) HX_PF_ATTN(6) HX_PF_ATTN(7) HX_PF_ATTN(8)
         default: return hx_fail(HX_ERR_ARG, "batched prefill attention: group of %d query heads per kv head not supported", GRP);
     }
 #undef HX_PF_ATTN
     HX_COUNT_LAUNCH(1);
-    HX_CUDA(cudaGetLastError());
     return HX_OK;
+}
+
+void hx_pf_advance(int* posp, int n, cudaStream_t st) {
+    k_pf_advance<<<1, 32, 0, st>>>(posp, n);
+    HX_COUNT_LAUNCH(1);
 }
 
 void hx_pf_argmax(const float* logits, int n, int* tok, int* hist, int* pos_out, int pos, cudaStream_t st) {
