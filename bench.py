@@ -172,6 +172,9 @@ def synth_image_on_host(shape, seed):
 
 def cpu_decode_tok_s(image, n_tokens, kv_cap=64):
     """tokens/s of the CPU restatement decoding n_tokens greedy tokens from an empty cache."""
+    if "oracle_lib" not in sys.modules:
+        # all host cores, also under torchrun (which exports OMP_NUM_THREADS=1); read when the OpenMP runtime starts
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as ol
     om = ol.OracleModel(image=image, kv_cap=kv_cap)
@@ -187,6 +190,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)    # torchrun exports 1; the CPU arm uses every host core
     import helix_b200 as hb
     shape = dict(hb.QWEN3_8B)
     image = synth_image_on_host(shape, seed=1)
@@ -224,7 +228,7 @@ def run_ours(args):
     shape = dict(hb.QWEN3_8B)
     if args.layers:
         shape["n_layers"] = args.layers                 # reduced-depth case for profiler captures; not a bench line
-    keep = 1 if (rank == 0 and not args.no_cpu_baseline) else 0
+    keep = 1 if (rank == 0 and args.gpus == 1 and not args.no_cpu_baseline) else 0
     model = hb.Model.synth(shape, seed=1, kv_cap=PROMPT_LEN + NEW_TOKENS + 8, flags=keep)
     cfgd = model.cfg.as_dict()
     rng = np.random.default_rng(2 + rank)
@@ -315,7 +319,7 @@ def run_ours(args):
            "api": "hx_decode_step per token: token id H2D, next id + f32 logits row D2H (what the reference worker reads back)"}
 
     cpu = None
-    if rank == 0 and not args.no_cpu_baseline:
+    if rank == 0 and args.gpus == 1 and not args.no_cpu_baseline:      # reported at N = 1 only
         image = model.v3_image()                       # the same weights, HXGW v3 bytes exported from HBM
         v1, cores = cpu_decode_tok_s(image, 1)
         n = int(max(2, min(16, 20.0 * v1)))
