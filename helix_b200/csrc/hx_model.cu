@@ -87,6 +87,10 @@ struct hx_model {
     std::vector<void*> allocs;
     uint64_t decode_bytes = 0, committed_bytes = 0;
     int kv_len = 0;
+    // tensor parallel: cfg holds THIS RANK's shard dimensions (heads, kv heads, hidden, vocabulary slice); gcfg the model's
+    hx_config gcfg{}; int tp_rank = 0, tp_world = 1;
+    float* tp_buf = nullptr; size_t tp_buf_floats = 0; float* tp_peer[8] = {nullptr}; bool tp_connected = false; unsigned tp_launches = 0;
+    float* x2 = nullptr; int tp_nbar = 0;
     // batched prefill (chunks of HX_PF_TB tokens through the tcgen05 GEMM); buffers are created on first use
     float *pf_x = nullptr, *pf_qkv = nullptr, *pf_ctx = nullptr, *pf_gu = nullptr, *pf_scale = nullptr; uint8_t* pf_cells = nullptr; int* pf_err = nullptr; float* pf_partial = nullptr; unsigned* pf_tickets = nullptr;
     int pf_gu_ld = 0; bool pf_batched = true; size_t pf_partial_n = 0;
@@ -107,12 +111,15 @@ int dalloc(hx_model* m, T** p, size_t n) {
 
 int alloc_fused(hx_model* m, Fused& f, int N, int K) {
     f.N = N; f.K = K; f.Kd = hx_kd(K);
-    int rc = dalloc(m, &f.codes, (size_t)N * (f.Kd / 2)); if (rc) return rc;
-    rc = dalloc(m, &f.scales, (size_t)N * (f.Kd / 16)); if (rc) return rc;
+    int rc = HX_OK;
     m->decode_bytes += f.bytes();
     f.KG = hx_t16_kgroups(K); f.ntiles = hx_t16_tiles(N);
-    rc = dalloc(m, &f.t16, hx_t16_bytes(N, K)); if (rc) return rc;
-    HX_CUDA(cudaMemsetAsync(f.t16, 0, hx_t16_bytes(N, K), m->st));
+    if (m->tp_world == 1) {       // the layouts of the other engines; a tensor-parallel shard only runs the tensor-core engine
+        rc = dalloc(m, &f.codes, (size_t)N * (f.Kd / 2)); if (rc) return rc;
+        rc = dalloc(m, &f.scales, (size_t)N * (f.Kd / 16)); if (rc) return rc;
+        rc = dalloc(m, &f.t16, hx_t16_bytes(N, K)); if (rc) return rc;
+        HX_CUDA(cudaMemsetAsync(f.t16, 0, hx_t16_bytes(N, K), m->st));
+    }
     f.ksteps = 4 * ((K + 255) / 256); f.tiles128 = (N + 127) / 128;     // whole 256-column cells, 128-row tiles
     if (m->want_t128) {
         const size_t tb = (size_t)f.tiles128 * (f.ksteps / 4) * HX_T128_CELL;
@@ -189,12 +196,24 @@ void put_rows(hx_model* m, const Committed& c, Fused& f, int row_mul, int row_of
 
 int build(hx_model* m, Source& s) {
     const hx_config& c = m->cfg;
-    const int NL = c.n_layers, DM = c.d_model, DH = c.head_dim, DFF = c.d_ff, NV = c.vocab;
+    const int NL = c.n_layers, DM = c.d_model, DH = c.head_dim, DFF = c.d_ff, NV = c.vocab;     // this rank's shard
     const int QD = m->QD, KVD = m->KVD;
+    // tensors are fetched whole (the per-tensor scale and the codes are those of the full tensor) and this rank's
+    // rows or columns are laid out: q/k/v/gate/up/lm_head split by rows, o/down by columns
+    const int W = m->tp_world, R = m->tp_rank;
+    const int gQD = m->gcfg.n_heads * DH, gKVD = m->gcfg.n_kv_heads * DH, gDFF = m->gcfg.d_ff, gNV = m->gcfg.vocab;
+    auto put = [&](const Committed& cm, Fused& f, int row_mul, int row_off, int rows_local, bool split_rows, int klen) {
+        if (W == 1) { put_rows(m, cm, f, row_mul, row_off); return; }
+        const int kwords = cm.Kpad / 7, kblk = cm.Kpad / 16;
+        const int r0 = split_rows ? R * rows_local : 0, k0 = split_rows ? 0 : R * klen;
+        const int grp = row_mul == 1 ? 1 : 64;
+        hx_repack_t128(cm.words + (size_t)r0 * kwords, cm.micro + (size_t)r0 * kblk, rows_local, split_rows ? cm.K : klen, cm.Kpad,
+                       f.t128, f.ksteps / 4, grp, row_mul, row_off, m->st, k0);
+    };
     const bool keep = (m->flags & HX_LOAD_KEEP_COMMITTED) != 0;
     // staging sized for the largest tensor
-    size_t maxel = (size_t)NV * DM;
-    const size_t cand[] = {(size_t)QD * DM, (size_t)DFF * DM, (size_t)DM * DFF, (size_t)DM * QD};
+    size_t maxel = (size_t)gNV * DM;
+    const size_t cand[] = {(size_t)gQD * DM, (size_t)gDFF * DM, (size_t)DM * gDFF, (size_t)DM * gQD};
     for (size_t v : cand) if (v > maxel) maxel = v;
     int rc;
     std::vector<void*> staging;
@@ -206,7 +225,7 @@ int build(hx_model* m, Source& s) {
     auto sfree = [&]() { for (void* p : staging) cudaFree(p); staging.clear(); };
     if (s.synth) { rc = salloc((void**)&s.f32tmp, maxel * 4); if (rc) { sfree(); return rc; } }
     if (!keep) {
-        const int shp[][2] = {{QD, DM}, {KVD, DM}, {DM, QD}, {DFF, DM}, {DM, DFF}, {NV, DM}};
+        const int shp[][2] = {{gQD, DM}, {gKVD, DM}, {DM, gQD}, {gDFF, DM}, {DM, gDFF}, {gNV, DM}};
         size_t wmax = 0, mmax = 0;
         for (auto& sh : shp) {
             const size_t kp = (size_t)hx_kpad(sh[1]);
@@ -232,38 +251,38 @@ int build(hx_model* m, Source& s) {
             if ((rc = alloc_fused(m, ly.qkv, QD + 2 * KVD, DM))) break;
             if ((rc = alloc_fused(m, ly.o, DM, QD))) break;
             if ((rc = alloc_fused(m, ly.gu, 2 * DFF, DM))) break;
-            if (DFF % 16) {   // tile-interleaved pairs need whole tiles for gate and for up
+            if (DFF % 16 && m->tp_world == 1) {   // tile-interleaved pairs need whole tiles for gate and for up
                 ly.gu.ntiles = 2 * hx_t16_tiles(DFF);
                 if ((rc = dalloc(m, &ly.gu.t16, (size_t)ly.gu.ntiles * ly.gu.KG * HX_T16_CELL))) break;
                 HX_CUDA(cudaMemsetAsync(ly.gu.t16, 0, (size_t)ly.gu.ntiles * ly.gu.KG * HX_T16_CELL, m->st));
             }
             if ((rc = alloc_fused(m, ly.down, DM, DFF))) break;
-            if ((rc = fetch_packed(m, s, b + T_Q, QD, DM, ly.c[T_Q], keep))) break;
-            put_rows(m, ly.c[T_Q], ly.qkv, 1, 0); ly.qkv.ts[0] = ly.c[T_Q].ts;
-            if ((rc = fetch_packed(m, s, b + T_K, KVD, DM, ly.c[T_K], keep))) break;
-            put_rows(m, ly.c[T_K], ly.qkv, 1, QD); ly.qkv.ts[1] = ly.c[T_K].ts;
-            if ((rc = fetch_packed(m, s, b + T_V, KVD, DM, ly.c[T_V], keep))) break;
-            put_rows(m, ly.c[T_V], ly.qkv, 1, QD + KVD); ly.qkv.ts[2] = ly.c[T_V].ts;
+            if ((rc = fetch_packed(m, s, b + T_Q, gQD, DM, ly.c[T_Q], keep))) break;
+            put(ly.c[T_Q], ly.qkv, 1, 0, QD, true, 0); ly.qkv.ts[0] = ly.c[T_Q].ts;
+            if ((rc = fetch_packed(m, s, b + T_K, gKVD, DM, ly.c[T_K], keep))) break;
+            put(ly.c[T_K], ly.qkv, 1, QD, KVD, true, 0); ly.qkv.ts[1] = ly.c[T_K].ts;
+            if ((rc = fetch_packed(m, s, b + T_V, gKVD, DM, ly.c[T_V], keep))) break;
+            put(ly.c[T_V], ly.qkv, 1, QD + KVD, KVD, true, 0); ly.qkv.ts[2] = ly.c[T_V].ts;
             ly.qkv.bound0 = QD; ly.qkv.bound1 = QD + KVD;
-            if ((rc = fetch_packed(m, s, b + T_O, DM, QD, ly.c[T_O], keep))) break;
-            put_rows(m, ly.c[T_O], ly.o, 1, 0); ly.o.ts[0] = ly.o.ts[1] = ly.o.ts[2] = ly.c[T_O].ts; ly.o.bound0 = ly.o.bound1 = DM;
-            if ((rc = fetch_packed(m, s, b + T_GATE, DFF, DM, ly.c[T_GATE], keep))) break;
-            put_rows(m, ly.c[T_GATE], ly.gu, 2, 0); ly.gu.ts[0] = ly.c[T_GATE].ts;
-            if ((rc = fetch_packed(m, s, b + T_UP, DFF, DM, ly.c[T_UP], keep))) break;
-            put_rows(m, ly.c[T_UP], ly.gu, 2, 1); ly.gu.ts[1] = ly.c[T_UP].ts; ly.gu.bound0 = ly.gu.bound1 = 2 * DFF;
-            if ((rc = fetch_packed(m, s, b + T_DOWN, DM, DFF, ly.c[T_DOWN], keep))) break;
-            put_rows(m, ly.c[T_DOWN], ly.down, 1, 0); ly.down.ts[0] = ly.down.ts[1] = ly.down.ts[2] = ly.c[T_DOWN].ts; ly.down.bound0 = ly.down.bound1 = DM;
+            if ((rc = fetch_packed(m, s, b + T_O, DM, gQD, ly.c[T_O], keep))) break;
+            put(ly.c[T_O], ly.o, 1, 0, DM, false, QD); ly.o.ts[0] = ly.o.ts[1] = ly.o.ts[2] = ly.c[T_O].ts; ly.o.bound0 = ly.o.bound1 = DM;
+            if ((rc = fetch_packed(m, s, b + T_GATE, gDFF, DM, ly.c[T_GATE], keep))) break;
+            put(ly.c[T_GATE], ly.gu, 2, 0, DFF, true, 0); ly.gu.ts[0] = ly.c[T_GATE].ts;
+            if ((rc = fetch_packed(m, s, b + T_UP, gDFF, DM, ly.c[T_UP], keep))) break;
+            put(ly.c[T_UP], ly.gu, 2, 1, DFF, true, 0); ly.gu.ts[1] = ly.c[T_UP].ts; ly.gu.bound0 = ly.gu.bound1 = 2 * DFF;
+            if ((rc = fetch_packed(m, s, b + T_DOWN, DM, gDFF, ly.c[T_DOWN], keep))) break;
+            put(ly.c[T_DOWN], ly.down, 1, 0, DM, false, DFF); ly.down.ts[0] = ly.down.ts[1] = ly.down.ts[2] = ly.c[T_DOWN].ts; ly.down.bound0 = ly.down.bound1 = DM;
             cudaError_t e = cudaStreamSynchronize(m->st);
             if (e != cudaSuccess) { rc = hx_fail(HX_ERR_CUDA, "layer %d ingest: %s", L, cudaGetErrorString(e)); break; }
         } while (0);
     }
     if (!rc) do {
         const int b = NL * T_PER_LAYER;
-        if ((rc = fetch_dense(m, s, b + 0, (size_t)NV * DM, &m->emb, false))) break;
+        if ((rc = fetch_dense(m, s, b + 0, (size_t)gNV * DM, &m->emb, false))) break;
         if ((rc = fetch_dense(m, s, b + 1, DM, &m->final_g, true))) break;
         if ((rc = alloc_fused(m, m->head, NV, DM))) break;
-        if ((rc = fetch_packed(m, s, b + 2, NV, DM, m->head_c, keep))) break;
-        put_rows(m, m->head_c, m->head, 1, 0);
+        if ((rc = fetch_packed(m, s, b + 2, gNV, DM, m->head_c, keep))) break;
+        put(m->head_c, m->head, 1, 0, NV, true, 0);
         m->head.ts[0] = m->head.ts[1] = m->head.ts[2] = m->head_c.ts; m->head.bound0 = m->head.bound1 = NV;
         cudaError_t e = cudaStreamSynchronize(m->st);
         if (e != cudaSuccess) rc = hx_fail(HX_ERR_CUDA, "head ingest: %s", cudaGetErrorString(e));
@@ -442,11 +461,16 @@ int build_phases(hx_model* m, bool from_prompt, bool with_head, HxPhase** out, i
         return p;
     };
     int maxK = 0;
+    // tensor parallel: o_proj and down leave per-rank partial sums; the next linear's prologue adds them to the residual
+    // stream, which alternates between two buffers (a CTA must not overwrite what another still reads)
+    const bool tp = m->tp_world > 1;
+    float* xcur = m->x; int nbar = 0;
     for (int L = 0; L < c.n_layers; L++) {
         Layer& ly = m->layers[L];
-        HxPhase a = linear(ly.qkv, m->x, m->qkv, HX_EPI_STORE, ly.qkv.N);
+        HxPhase a = linear(ly.qkv, xcur, m->qkv, HX_EPI_STORE, ly.qkv.N);
         a.norm = HX_NORM_RMS; a.g = ly.in_g; a.eps = c.norm_eps;
-        if (L == 0) { a.x = m->emb; a.tok = from_prompt ? m->d_prompt : m->d_tok; a.x_out = m->x; }
+        if (L == 0) { a.x = m->emb; a.tok = from_prompt ? m->d_prompt : m->d_tok; a.x_out = m->x; xcur = m->x; }
+        else if (tp) { a.tp_sum = 2; a.x_out = xcur == m->x ? m->x2 : m->x; xcur = a.x_out; }     // + down partials of the layer before
         // tensor-core path: the qkv epilogue norms and rotates q and k and writes k, v into the cache
         const bool fuse_qk = m->use_tc && (DH == 32 || DH == 64 || DH == 128);
         if (fuse_qk) {
@@ -462,7 +486,8 @@ int build_phases(hx_model* m, bool from_prompt, bool with_head, HxPhase** out, i
         at.ctx = m->ctx; at.NH = c.n_heads; at.NKV = c.n_kv_heads; at.DH = DH; at.cap = cap;
         at.nsplit = m->nsplit_persist; at.scale = 1.0f / sqrtf((float)DH); at.eps = c.norm_eps;
         v.push_back(at);
-        HxPhase o = linear(ly.o, m->ctx, m->x, HX_EPI_RESID, ly.o.N);
+        HxPhase o = linear(ly.o, m->ctx, xcur, HX_EPI_RESID, ly.o.N);
+        if (tp) { o.tp_partial = 1; o.tp_barrier = 1; o.tp_epoch = ++nbar; }
         // the o_proj prologue merges the attention splits itself (no merging CTA on the critical path)
         const bool defer_merge = fuse_qk && (size_t)c.n_heads * m->nsplit_persist <= 2304 && DH % 8 == 0;
         if (defer_merge) {
@@ -470,20 +495,24 @@ int build_phases(hx_model* m, bool from_prompt, bool with_head, HxPhase** out, i
             o.norm = HX_NORM_ATTN; o.NH = c.n_heads; o.NKV = c.n_kv_heads; o.DH = DH; o.nsplit = m->nsplit_persist;
         }
         v.push_back(o);
-        HxPhase gu = linear(ly.gu, m->x, m->h, HX_EPI_SWIGLU, c.d_ff);
+        HxPhase gu = linear(ly.gu, xcur, m->h, HX_EPI_SWIGLU, c.d_ff);
         gu.norm = HX_NORM_RMS; gu.g = ly.post_g; gu.eps = c.norm_eps;
+        if (tp) { gu.tp_sum = 1; gu.x_out = xcur == m->x ? m->x2 : m->x; xcur = gu.x_out; }                                   // + o partials
         v.push_back(gu);
-        HxPhase dn = linear(ly.down, m->h, m->x, HX_EPI_RESID, ly.down.N);
+        HxPhase dn = linear(ly.down, m->h, xcur, HX_EPI_RESID, ly.down.N);
+        if (tp) { dn.tp_partial = 2; dn.tp_barrier = 1; dn.tp_epoch = ++nbar; }
         v.push_back(dn);
         if (ly.down.K > maxK) maxK = ly.down.K;
         if (ly.o.K > maxK) maxK = ly.o.K;
         if (ly.qkv.K > maxK) maxK = ly.qkv.K;
     }
     if (with_head) {
-        HxPhase hd = linear(m->head, m->x, m->logits, HX_EPI_ARGMAX, m->head.N);
+        HxPhase hd = linear(m->head, xcur, m->logits, HX_EPI_ARGMAX, m->head.N);
         hd.norm = HX_NORM_RMS; hd.g = m->final_g; hd.eps = c.norm_eps;
+        if (tp && c.n_layers > 0) { hd.tp_sum = 2; hd.x_out = xcur == m->x ? m->x2 : m->x; }
         v.push_back(hd);
     }
+    m->tp_nbar = nbar;
     const int dig = 3 * hx_t16_kgroups(maxK) * HX_T16_KG * 2;
     if (dig > m->dig_bytes) m->dig_bytes = dig;
     HxPhase* d = nullptr;
@@ -503,7 +532,15 @@ int init_persist(hx_model* m) {
     m->nsplit_persist = sms / m->cfg.n_kv_heads; if (m->nsplit_persist < 1) m->nsplit_persist = 1;
     if (m->nsplit_persist > m->nsplit) m->nsplit_persist = m->nsplit;      // scratch is sized for nsplit
     if (256 % m->cfg.head_dim) return hx_fail(HX_ERR_ARG, "persistent decode needs head_dim dividing 256");
-    int rc = build_phases(m, false, true, &m->ph_decode, &m->nph_decode); if (rc) return rc;
+    int rc;
+    if (m->tp_world > 1) {
+        if ((rc = dalloc(m, &m->x2, (size_t)m->cfg.d_model))) return rc;
+        m->tp_buf_floats = (size_t)2 * m->tp_world * m->cfg.d_model + (size_t)4 * m->tp_world + 64;
+        if ((rc = dalloc(m, &m->tp_buf, m->tp_buf_floats))) return rc;
+        HX_CUDA(cudaMemset(m->tp_buf, 0, m->tp_buf_floats * 4));
+        m->tp_peer[m->tp_rank] = m->tp_buf;
+    }
+    rc = build_phases(m, false, true, &m->ph_decode, &m->nph_decode); if (rc) return rc;
     rc = build_phases(m, true, false, &m->ph_prefill, &m->nph_prefill); if (rc) return rc;
     if ((rc = dalloc(m, &m->d_bar, (size_t)2))) return rc;
     if ((rc = dalloc(m, &m->d_err, (size_t)4))) return rc;
@@ -537,6 +574,13 @@ int persist_step(hx_model* m, bool from_prompt, bool with_head) {
     P.tok_by_pos = from_prompt ? 1 : 0; P.advance_pos = from_prompt ? 1 : 0;
     P.dbg = m->d_dbg; P.dbg_all = m->d_dbg ? m->d_dbg + (size_t)16 * (m->nph_decode + 4) : nullptr; { const char* dc = getenv("HX_PERSIST_DBG"); P.dbg_cta = dc ? atoi(dc) - 1 : 0; if (P.dbg_cta < 0) P.dbg_cta = 0; }
     P.tc_partial = m->tc_partial; P.tc_cnt = m->tc_cnt; P.bdig_bytes = m->bdig_bytes; P.tc_ring = m->tc_ring;
+    P.tp_world = m->tp_world; P.tp_rank = m->tp_rank; P.tp_dm = m->cfg.d_model; P.tp_vocab_off = m->tp_rank * m->cfg.vocab;
+    if (m->tp_world > 1) {
+        if (!m->tp_connected) return hx_fail(HX_ERR_STATE, "tensor parallel: call hx_model_tp_connect before the first step");
+        for (int w = 0; w < m->tp_world; w++) P.tp_peer[w] = m->tp_peer[w];
+        P.tp_epoch_base = m->tp_launches * 4096u;        // every rank launches the same sequence of steps
+        m->tp_launches++;
+    }
     m->bar_count += (unsigned long long)m->grid_persist * (unsigned long long)(P.nphases - 1);
     if (m->use_tc) return hx_persist_tc_launch(P, m->grid_persist, m->st);
     return hx_persist_launch(P, m->grid_persist, m->st);
@@ -567,6 +611,7 @@ int finish_init(hx_model* m) {
         rc = init_persist(m);
         if (rc) return rc;
     }
+    if (m->tp_world > 1) return HX_OK;          // a shard only runs the persistent tensor-core engine
     rc = capture(m, false, true, &m->g_decode);
     if (rc && m->pdl) {     // programmatic edges not capturable on this driver: plain stream order
         m->pdl = false;
@@ -599,7 +644,12 @@ int check_cfg(const hx_config& c, int kv_cap, int batch, int tp_rank, int tp_siz
     if (c.d_model % 4 || c.d_ff % 4) return hx_fail(HX_ERR_ARG, "d_model and d_ff must be multiples of 4");
     if (kv_cap <= 0) return hx_fail(HX_ERR_ARG, "kv_cap must be positive");
     if (batch != 1) return hx_fail(HX_ERR_ARG, "batch %d: this build decodes one sequence per model instance", batch);
-    if (tp_size != 1 || tp_rank != 0) return hx_fail(HX_ERR_ARG, "tensor parallel shards are not built yet (tp_size must be 1)");
+    if (tp_size < 1 || tp_size > 8 || tp_rank < 0 || tp_rank >= tp_size) return hx_fail(HX_ERR_ARG, "tensor parallel rank %d of %d", tp_rank, tp_size);
+    if (tp_size > 1) {
+        if (c.n_heads % tp_size || c.n_kv_heads % tp_size || c.d_ff % tp_size || c.vocab % tp_size)
+            return hx_fail(HX_ERR_ARG, "tensor parallel %d: heads %d, kv heads %d, d_ff %d and vocab %d must be divisible", tp_size, c.n_heads, c.n_kv_heads, c.d_ff, c.vocab);
+        if ((c.n_heads / tp_size * c.head_dim) % 16 || (c.d_ff / tp_size) % 16) return hx_fail(HX_ERR_ARG, "tensor parallel %d: shard widths must be multiples of 16", tp_size);
+    }
     return HX_OK;
 }
 
@@ -624,13 +674,16 @@ HX_API int hx_model_synth(hx_model** out, const hx_config* cfg, uint64_t seed, i
     HX_CHECK_ARG(out && cfg);
     int rc = check_cfg(*cfg, kv_cap, batch, tp_rank, tp_size); if (rc) return rc;
     hx_model* m = new hx_model();
-    m->cfg = *cfg; m->QD = cfg->n_heads * cfg->head_dim; m->KVD = cfg->n_kv_heads * cfg->head_dim;
+        m->gcfg = *cfg; m->cfg = *cfg; m->tp_rank = tp_rank; m->tp_world = tp_size;
+        if (tp_size > 1) { m->cfg.n_heads /= tp_size; m->cfg.n_kv_heads /= tp_size; m->cfg.d_ff /= tp_size; m->cfg.vocab /= tp_size; }
+        m->QD = m->cfg.n_heads * m->cfg.head_dim; m->KVD = m->cfg.n_kv_heads * m->cfg.head_dim;
     m->kv_cap = kv_cap; m->batch = batch; m->flags = flags;
     { const char* dm = getenv("HX_DECODE"); const char* lm = getenv("HX_LINEAR");
       m->persist = !(dm && strcmp(dm, "graph") == 0);
       m->use_tc = m->persist && !(lm && strcmp(lm, "mma") == 0);
       m->want_t128 = m->use_tc;
-      { const char* pf = getenv("HX_PREFILL"); m->pf_batched = !(pf && strcmp(pf, "token") == 0); } }
+      { const char* pf = getenv("HX_PREFILL"); m->pf_batched = !(pf && strcmp(pf, "token") == 0); }
+      if (m->tp_world > 1) { m->persist = true; m->use_tc = true; m->want_t128 = true; m->pf_batched = false; } }
     cudaError_t e = cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking);
     if (e != cudaSuccess) { delete m; return hx_fail(HX_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
     Source s; s.synth = true; s.seed = seed;
@@ -688,13 +741,16 @@ HX_API int hx_model_load(hx_model** out, const char* path, int kv_cap, int batch
         if (rc) break;
         if (cur != len) { rc = hx_fail(HX_ERR_FORMAT, "v3 layout %llu != file %zu", (unsigned long long)cur, len); break; }
         m = new hx_model();
-        m->cfg = c; m->QD = c.n_heads * c.head_dim; m->KVD = c.n_kv_heads * c.head_dim;
+        m->gcfg = c; m->cfg = c; m->tp_rank = tp_rank; m->tp_world = tp_size;
+        if (tp_size > 1) { m->cfg.n_heads /= tp_size; m->cfg.n_kv_heads /= tp_size; m->cfg.d_ff /= tp_size; m->cfg.vocab /= tp_size; }
+        m->QD = m->cfg.n_heads * m->cfg.head_dim; m->KVD = m->cfg.n_kv_heads * m->cfg.head_dim;
         m->kv_cap = kv_cap; m->batch = batch; m->flags = flags;
     { const char* dm = getenv("HX_DECODE"); const char* lm = getenv("HX_LINEAR");
       m->persist = !(dm && strcmp(dm, "graph") == 0);
       m->use_tc = m->persist && !(lm && strcmp(lm, "mma") == 0);
       m->want_t128 = m->use_tc;
-      { const char* pf = getenv("HX_PREFILL"); m->pf_batched = !(pf && strcmp(pf, "token") == 0); } }
+      { const char* pf = getenv("HX_PREFILL"); m->pf_batched = !(pf && strcmp(pf, "token") == 0); }
+      if (m->tp_world > 1) { m->persist = true; m->use_tc = true; m->want_t128 = true; m->pf_batched = false; } }
         cudaError_t e = cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking);
         if (e != cudaSuccess) { rc = hx_fail(HX_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); break; }
         Source s; s.map = hb; s.maplen = len; s.desc = d;
@@ -735,6 +791,33 @@ HX_API int hx_model_phase_stamps_all(hx_model* m, unsigned long long* out, size_
     *nphases = m->nph_decode; *grid = m->grid_persist;
     return HX_OK;
 }
+// ---- tensor parallel: exchange-buffer handles ----------------------------------------------------------
+// The caller moves the 64-byte handles between the ranks' processes by any channel it has.
+HX_API int hx_model_tp_handle(hx_model* m, uint8_t handle[64]) {
+    HX_CHECK_ARG(m && handle);
+    if (m->tp_world < 2 || !m->tp_buf) return hx_fail(HX_ERR_STATE, "not a tensor-parallel shard");
+    cudaIpcMemHandle_t h;
+    HX_CUDA(cudaIpcGetMemHandle(&h, m->tp_buf));
+    static_assert(sizeof(h) == 64, "IPC handle size");
+    memcpy(handle, &h, 64);
+    return HX_OK;
+}
+HX_API int hx_model_tp_connect(hx_model* m, const uint8_t* handles, int world) {
+    HX_CHECK_ARG(m && handles);
+    if (world != m->tp_world || m->tp_world < 2) return hx_fail(HX_ERR_ARG, "tensor parallel: %d handles for a group of %d", world, m->tp_world);
+    if (m->tp_nbar >= 4095) return hx_fail(HX_ERR_ARG, "tensor parallel: too many layers for the barrier numbering");
+    for (int w = 0; w < world; w++) {
+        if (w == m->tp_rank) continue;
+        cudaIpcMemHandle_t h; memcpy(&h, handles + (size_t)w * 64, 64);
+        void* p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return hx_fail(HX_ERR_COMM, "cudaIpcOpenMemHandle(rank %d): %s", w, cudaGetErrorString(e));
+        m->tp_peer[w] = (float*)p;
+    }
+    m->tp_connected = true;
+    return HX_OK;
+}
+
 // Which decode engine this model runs: "persistent-tcgen05", "persistent-mma" or "graph".
 HX_API const char* hx_model_engine(const hx_model* m) {
     if (!m) return "";
@@ -853,7 +936,7 @@ static int set_pos_tok(hx_model* m, int pos, const int32_t* tok) {
 HX_API int hx_decode_step(hx_model* m, const int32_t* ids, int pos, int32_t* next_ids, float* logits) {
     HX_CHECK_ARG(m && ids);
     if (pos < 0 || pos >= m->kv_cap) return hx_fail(HX_ERR_STATE, "position %d outside the KV capacity %d", pos, m->kv_cap);
-    if (ids[0] < 0 || ids[0] >= m->cfg.vocab) return hx_fail(HX_ERR_ARG, "token %d outside the vocabulary", ids[0]);
+    if (ids[0] < 0 || ids[0] >= m->gcfg.vocab) return hx_fail(HX_ERR_ARG, "token %d outside the vocabulary", ids[0]);
     int rc = set_pos_tok(m, pos, ids); if (rc) return rc;
     if ((rc = step_decode(m))) return rc;
     if (next_ids) HX_CUDA(cudaMemcpyAsync(next_ids, m->d_tok, 4, cudaMemcpyDeviceToHost, m->st));
@@ -984,7 +1067,7 @@ static int run_prefill(hx_model* m, const int32_t* ids, int T) {
 HX_API int hx_prefill(hx_model* m, const int32_t* ids, int T, int32_t* next_ids, float* logits) {
     HX_CHECK_ARG(m && ids && T > 0);
     if (T > m->kv_cap) return hx_fail(HX_ERR_STATE, "prompt of %d tokens exceeds the KV capacity %d", T, m->kv_cap);
-    for (int i = 0; i < T; i++) if (ids[i] < 0 || ids[i] >= m->cfg.vocab) return hx_fail(HX_ERR_ARG, "token %d outside the vocabulary", ids[i]);
+    for (int i = 0; i < T; i++) if (ids[i] < 0 || ids[i] >= m->gcfg.vocab) return hx_fail(HX_ERR_ARG, "token %d outside the vocabulary", ids[i]);
     int rc = run_prefill(m, ids, T); if (rc) return rc;
     if (next_ids) HX_CUDA(cudaMemcpyAsync(next_ids, m->d_tok, 4, cudaMemcpyDeviceToHost, m->st));
     if (logits) HX_CUDA(cudaMemcpyAsync(logits, m->logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToHost, m->st));
@@ -1030,7 +1113,7 @@ HX_API int hx_generate_greedy(hx_model* m, const int32_t* prompt, int T, int n_n
                               float* ms_prefill, float* ms_decode) {
     HX_CHECK_ARG(m && prompt && T > 0 && n_new > 0 && out_ids);
     if (T + n_new - 1 > m->kv_cap) return hx_fail(HX_ERR_STATE, "%d prompt + %d new tokens exceed the KV capacity %d", T, n_new, m->kv_cap);
-    for (int i = 0; i < T; i++) if (prompt[i] < 0 || prompt[i] >= m->cfg.vocab) return hx_fail(HX_ERR_ARG, "token %d outside the vocabulary", prompt[i]);
+    for (int i = 0; i < T; i++) if (prompt[i] < 0 || prompt[i] >= m->gcfg.vocab) return hx_fail(HX_ERR_ARG, "token %d outside the vocabulary", prompt[i]);
     cudaEvent_t e0, e1, e2;
     HX_CUDA(cudaEventCreate(&e0)); HX_CUDA(cudaEventCreate(&e1)); HX_CUDA(cudaEventCreate(&e2));
     HX_CUDA(cudaEventRecord(e0, m->st));

@@ -52,6 +52,11 @@ struct alignas(16) HxPhase {
     // ---- attention ----
     const float* qkv; const float* qn_g; const float* kn_g; const float* cosT; const float* sinT;
     float* kc; float* vc; float* ctx;
+    // ---- tensor parallel (persistent tensor-core kernel) ----
+    int tp_partial;           // s + 1: the epilogue writes this rank's partial sums of all rows to slot s of every rank's exchange buffer
+    int tp_sum;               // s + 1: the input vector is x + the partial sums of all ranks in slot s; the sum is written to x_out
+    int tp_barrier;           // a cross-GPU barrier follows the grid barrier of this phase; tp_epoch counts them within a launch
+    int tp_epoch;
     int NH, NKV, DH, cap, nsplit; float scale;   // attention also uses eps (per-head RMSNorm)
 };
 
@@ -75,6 +80,9 @@ struct HxPersist {
     float* tc_partial; unsigned* tc_cnt;  // split-K scratch of the tensor-core linear phases
     int bdig_bytes;                       // shared-memory bytes for the digit columns of x (tensor-core path)
     int tc_ring;                          // ring depth of the tensor-core kernel (3..10 slots)
+    // tensor parallel: exchange buffers of all ranks (own entry = local), mapped through CUDA IPC.  Layout in floats:
+    // [2 slots][world][tp_dm] partial sums | [world][2] arg-max pairs | [world] barrier flags | [world] arg-max flags | go
+    float* tp_peer[8]; int tp_rank, tp_world, tp_dm; unsigned tp_epoch_base; int tp_vocab_off;
 };
 
 int hx_persist_launch(const HxPersist& p, int grid, cudaStream_t st);
@@ -85,5 +93,5 @@ int hx_persist_tc_ring(int bdig_bytes);               // ring depth that fits (0
 void hx_tc_split(int ntiles, int kcells, int grid, int* max_pieces, int* max_run);
 // committed layout -> T128 cells (hx_persist_tc.cu); destination row = (r/grp)*grp*row_mul + row_off*grp + r%grp
 void hx_repack_t128(const int32_t* words, const uint8_t* micro, int rows, int K, int Kpad, uint8_t* dst,
-                    int kcells, int grp, int row_mul, int row_off, cudaStream_t st);
+                    int kcells, int grp, int row_mul, int row_off, cudaStream_t st, int k0 = 0);
 size_t hx_persist_smem(int dig_bytes);

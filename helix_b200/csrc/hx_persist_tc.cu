@@ -45,7 +45,8 @@
 // of the committed data.  Cells of a tile are contiguous in K, tiles follow one another.
 __global__ void __launch_bounds__(256) k_repack_t128(const int32_t* __restrict__ words, const uint8_t* __restrict__ micro,
                                                       int rows, int K, int Kpad, uint8_t* __restrict__ dst, int kcells,
-                                                      int grp, int row_mul, int row_off) {
+                                                      int grp, int row_mul, int row_off, int k0) {
+    // K = columns taken from the source rows starting at column k0 (a multiple of 16): a K shard of the tensor
     const int kwords = Kpad / 7, kblk = Kpad / 16, ksteps = (K + 63) / 64;
     const size_t items = (size_t)rows * ksteps * 2;
     for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (size_t)gridDim.x * blockDim.x) {
@@ -59,7 +60,7 @@ __global__ void __launch_bounds__(256) k_repack_t128(const int32_t* __restrict__
         for (int j = 0; j < 32; j++) {
             const int e = ks * 64 + c * 32 + j;
             uint32_t code = 0u;
-            if (e < K) { const int wd = e / 7, s = e - wd * 7; code = ((uint32_t)wr[wd] >> (4 * s)) & 15u; }
+            if (e < K) { const int es = e + k0, wd = es / 7, s = es - wd * 7; code = ((uint32_t)wr[wd] >> (4 * s)) & 15u; }
             out[j >> 3] |= code << (4 * (j & 7));
         }
         uint8_t* cell = dst + ((size_t)(dr / 128) * kcells + (ks >> 2)) * HX_T128_CELL;
@@ -70,7 +71,7 @@ __global__ void __launch_bounds__(256) k_repack_t128(const int32_t* __restrict__
 #pragma unroll
             for (int b = 0; b < 4; b++) {
                 const int blk = ks * 4 + b;
-                const uint32_t v = (blk * 16 < K && blk < kblk) ? micro[(size_t)r * kblk + blk] : 0u;
+                const uint32_t v = (blk * 16 < K && blk + k0 / 16 < kblk) ? micro[(size_t)r * kblk + blk + k0 / 16] : 0u;
                 sv |= v << (8 * b);
             }
             *reinterpret_cast<uint32_t*>(cell + 16384 + (ks & 3) * 512 + (rl % 32) * 16 + (rl / 32) * 4) = sv;
@@ -79,10 +80,10 @@ __global__ void __launch_bounds__(256) k_repack_t128(const int32_t* __restrict__
 }
 
 void hx_repack_t128(const int32_t* words, const uint8_t* micro, int rows, int K, int Kpad, uint8_t* dst,
-                    int kcells, int grp, int row_mul, int row_off, cudaStream_t st) {
+                    int kcells, int grp, int row_mul, int row_off, cudaStream_t st, int k0) {
     const size_t items = (size_t)rows * ((K + 63) / 64) * 2;
     int g = (int)((items + 255) / 256); if (g > 148 * 16) g = 148 * 16; if (g < 1) g = 1;
-    k_repack_t128<<<g, 256, 0, st>>>(words, micro, rows, K, Kpad, dst, kcells, grp, row_mul, row_off);
+    k_repack_t128<<<g, 256, 0, st>>>(words, micro, rows, K, Kpad, dst, kcells, grp, row_mul, row_off, k0);
     HX_COUNT_LAUNCH(1);
 }
 
@@ -161,6 +162,33 @@ __device__ __forceinline__ TcPlan tc_plan(const HxPhase& ph, int cta, int grid) 
 }
 // CTA whose run holds cell x (contiguous runs)
 __device__ __forceinline__ int tc_owner(long long x, long long total, int grid) { return (int)(((x + 1) * grid + total - 1) / total) - 1; }
+
+// ---- tensor-parallel exchange buffer (floats / 32-bit words) ----
+__device__ __forceinline__ size_t tp_off_part(const HxPersist& P, int slot, int w) { return ((size_t)slot * P.tp_world + w) * P.tp_dm; }
+__device__ __forceinline__ size_t tp_off_am(const HxPersist& P) { return (size_t)2 * P.tp_world * P.tp_dm; }
+__device__ __forceinline__ size_t tp_off_flags(const HxPersist& P) { return tp_off_am(P) + 2 * P.tp_world; }
+__device__ __forceinline__ size_t tp_off_amflags(const HxPersist& P) { return tp_off_flags(P) + P.tp_world; }
+__device__ __forceinline__ size_t tp_off_go(const HxPersist& P) { return tp_off_amflags(P) + P.tp_world; }
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) { asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) { unsigned v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
+// Every rank writes `ep` into slot `rank` of each peer's flag array, then waits (bounded) until all peers have written
+// theirs here.  Epochs only grow, so a late reader still sees a value >= ep.  One thread per GPU calls this.
+__device__ __forceinline__ bool tp_handshake(const HxPersist& P, size_t flags_off, unsigned ep, volatile int* abort_flag) {
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    for (int w = 0; w < P.tp_world; w++)
+        if (w != P.tp_rank) st_release_sys(reinterpret_cast<unsigned*>(P.tp_peer[w] + flags_off) + P.tp_rank, ep);
+    const unsigned* mine = reinterpret_cast<const unsigned*>(P.tp_peer[P.tp_rank] + flags_off);
+    for (int w = 0; w < P.tp_world; w++) {
+        if (w == P.tp_rank) continue;
+        bool ok = false;
+        for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+            if ((int)(ld_acquire_sys(mine + w) - ep) >= 0) { ok = true; break; }
+            if ((i & 255) == 255 && *abort_flag) break;
+        }
+        if (!ok) return false;
+    }
+    return true;
+}
 
 struct SmemTc {
     uint64_t full[HX_TC_MAX_RING];
@@ -362,6 +390,18 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 const float* xin = ph.x;
                 if (ph.tok) xin = ph.x + (size_t)(ph.tok[P.tok_by_pos ? pos : 0]) * K;
                 const bool rms = ph.norm == HX_NORM_RMS;
+                // tensor parallel: the vector is x + the partial sums every rank left in its slot of the exchange buffer
+                const float* tpp = ph.tp_sum ? P.tp_peer[P.tp_rank] + tp_off_part(P, ph.tp_sum - 1, 0) : nullptr;
+                auto ldx4 = [&](int k) -> float4 {
+                    float4 r = __ldcg(reinterpret_cast<const float4*>(xin + k));
+                    if (tpp) {
+                        for (int w = 0; w < P.tp_world; w++) {
+                            const float4 q = __ldcg(reinterpret_cast<const float4*>(tpp + (size_t)w * P.tp_dm + k));
+                            r.x += q.x; r.y += q.y; r.z += q.z; r.w += q.w;
+                        }
+                    }
+                    return r;
+                };
                 const int nitems = tp.run * 32;
                 auto item_k = [&](int it) { int kc = tp.k0 + (it >> 5); if (kc >= tp.C) kc -= tp.C; return kc * 256 + (it & 31) * 8; };
                 float4 ia = make_float4(0.f, 0.f, 0.f, 0.f), ib = ia, ja = make_float4(1.f, 1.f, 1.f, 1.f), jb = ja;
@@ -369,8 +409,8 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 if (tid % (NCT / tpi0) < nitems && ph.norm != HX_NORM_ATTN) {
                     const int k = item_k(tid % (NCT / tpi0));
                     if (k < K) {
-                        ia = __ldcg(reinterpret_cast<const float4*>(xin + k));
-                        if (k + 4 < K) ib = __ldcg(reinterpret_cast<const float4*>(xin + k + 4));
+                        ia = ldx4(k);
+                        if (k + 4 < K) ib = ldx4(k + 4);
                         if (rms) { ja = *reinterpret_cast<const float4*>(ph.g + k); if (k + 4 < K) jb = *reinterpret_cast<const float4*>(ph.g + k + 4); }
                     }
                 }
@@ -416,7 +456,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                             const int k = k0 + u * NCT * 4;
                             v[u] = make_float4(0.f, 0.f, 0.f, 0.f); gq[u] = v[u];
                             if (k < K) {
-                                v[u] = __ldcg(reinterpret_cast<const float4*>(xin + k));
+                                v[u] = ldx4(k);
                                 if (rms) gq[u] = *reinterpret_cast<const float4*>(ph.g + k);
                             }
                         }
@@ -424,7 +464,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                         for (int u = 0; u < 3; u++) {
                             const int k = k0 + u * NCT * 4;
                             if (k < K) {
-                                if (ph.tok && ph.x_out && ((k >> 2) % grid) == cta) *reinterpret_cast<float4*>(ph.x_out + k) = v[u];
+                                if ((ph.tok || tpp) && ph.x_out && ((k >> 2) % grid) == cta) *reinterpret_cast<float4*>(ph.x_out + k) = v[u];
                                 if (rms) {
                                     ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
                                     mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v[u].x * gq[u].x), fabsf(v[u].y * gq[u].y)), fmaxf(fabsf(v[u].z * gq[u].z), fabsf(v[u].w * gq[u].w))));
@@ -498,8 +538,8 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                         if (it >= ipt) {                                   // not the item fetched ahead of pass 1
                             ia = make_float4(0.f, 0.f, 0.f, 0.f); ib = ia; ja = make_float4(1.f, 1.f, 1.f, 1.f); jb = ja;
                             if (k < K) {
-                                ia = __ldcg(reinterpret_cast<const float4*>(xin + k));
-                                if (k + 4 < K) ib = __ldcg(reinterpret_cast<const float4*>(xin + k + 4));
+                                ia = ldx4(k);
+                                if (k + 4 < K) ib = ldx4(k + 4);
                                 if (rms) { ja = *reinterpret_cast<const float4*>(ph.g + k); if (k + 4 < K) jb = *reinterpret_cast<const float4*>(ph.g + k + 4); }
                             }
                         }
@@ -624,8 +664,15 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                             const int row = tile * 128 + rl;
                             if (row < ph.N) {
                                 v *= (row < ph.bound0) ? ph.ts[0] : (row < ph.bound1 ? ph.ts[1] : ph.ts[2]);
-                                if (ph.epi == HX_EPI_RESID) v = __ldcg(ph.y + row) + v;
-                                ph.y[row] = v;
+                                if (ph.tp_partial) {
+                                    // row-split linear: this rank's partial sum of the row goes to every rank's buffer;
+                                    // the consumer's prologue adds them to the residual stream in rank order
+                                    const size_t o = tp_off_part(P, ph.tp_partial - 1, P.tp_rank) + row;
+                                    for (int w = 0; w < P.tp_world; w++) P.tp_peer[w][o] = v;
+                                } else {
+                                    if (ph.epi == HX_EPI_RESID) v = __ldcg(ph.y + row) + v;
+                                    ph.y[row] = v;
+                                }
                                 if (ph.epi == HX_EPI_ARGMAX && pz_better(v, row, best_v, best_i)) { best_v = v; best_i = row; }
                             }
                         }
@@ -661,6 +708,19 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                             const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
                             const int oi = __shfl_xor_sync(0xffffffffu, bi, d);
                             if (pz_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+                        }
+                        if (lane == 0 && P.tp_world > 1) {
+                            // vocabulary split over the ranks: exchange (value, global index) and take the best of all
+                            const size_t ao = tp_off_am(P) + 2 * P.tp_rank;
+                            const int gi = bi == INT_MAX ? INT_MAX : bi + P.tp_vocab_off;
+                            for (int w = 0; w < P.tp_world; w++) { P.tp_peer[w][ao] = bv; reinterpret_cast<int*>(P.tp_peer[w])[ao + 1] = gi; }
+                            if (!tp_handshake(P, tp_off_amflags(P), P.tp_epoch_base + 4095u, &S.abort_flag)) { S.abort_flag = 1; *P.err = 1; }
+                            bv = -INFINITY; bi = INT_MAX;
+                            const float* am = P.tp_peer[P.tp_rank] + tp_off_am(P);
+                            for (int w = 0; w < P.tp_world; w++) {
+                                const float ov = __ldcg(am + 2 * w); const int oi = __ldcg(reinterpret_cast<const int*>(am) + 2 * w + 1);
+                                if (pz_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+                            }
                         }
                         if (lane == 0) {
                             const int nt = (bi == INT_MAX) ? 0 : bi;
@@ -706,7 +766,8 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 consumer_sync();                 // every thread's results are ordered before thread 0's release below
                 bar_target += (unsigned long long)grid;
                 if (tid == 0) {
-                    asm volatile("red.release.gpu.global.add.u64 [%0], 1;" :: "l"(P.bar) : "memory");
+                    if (ph.tp_barrier) asm volatile("red.release.sys.global.add.u64 [%0], 1;" :: "l"(P.bar) : "memory");   // covers the stores to the peers
+                    else asm volatile("red.release.gpu.global.add.u64 [%0], 1;" :: "l"(P.bar) : "memory");
                     bool ok = false;
                     for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
                         unsigned long long v;
@@ -715,6 +776,25 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                         if ((i & 255) == 255 && S.abort_flag) break;
                     }
                     if (!ok) S.abort_flag = 1;
+                    if (ok && ph.tp_barrier) {
+                        // all CTAs of this GPU have arrived; CTA 0 meets the other GPUs, then lets the local CTAs go
+                        const unsigned ep = P.tp_epoch_base + (unsigned)ph.tp_epoch;
+                        unsigned* go = reinterpret_cast<unsigned*>(P.tp_peer[P.tp_rank] + tp_off_go(P));
+                        if (cta == 0) {
+                            if (!tp_handshake(P, tp_off_flags(P), ep, &S.abort_flag)) S.abort_flag = 1;
+                            asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(go), "r"(S.abort_flag ? 0xFFFFFFFFu : ep) : "memory");
+                        } else {
+                            bool ok2 = false;
+                            for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+                                unsigned v;
+                                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(go) : "memory");
+                                if (v == 0xFFFFFFFFu) break;                       // CTA 0 gave up
+                                if ((int)(v - ep) >= 0) { ok2 = true; break; }
+                                if ((i & 255) == 255 && S.abort_flag) break;
+                            }
+                            if (!ok2) S.abort_flag = 1;
+                        }
+                    }
                 }
                 asm volatile("cp.async.wait_all;" ::: "memory");
                 consumer_sync();

@@ -103,6 +103,8 @@ _SIGS = {
     "hx_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "hx_model_last_stats": (C.c_int, [C.c_void_p, C.POINTER(HxStepStats)]),
     "hx_model_engine": (C.c_char_p, [C.c_void_p]),
+    "hx_model_tp_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "hx_model_tp_connect": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
     "hx_model_set_profile": (C.c_int, [C.c_void_p, C.c_int]),
     "hx_decode_loop": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float)]),
     "hx_model_fill_kv": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64]),
@@ -240,17 +242,29 @@ class Model:
         self.vocab = c.vocab
 
     @classmethod
-    def load(cls, path, kv_cap=1024, flags=0):
+    def load(cls, path, kv_cap=1024, flags=0, tp_rank=0, tp_size=1):
         h = C.c_void_p()
-        check(lib().hx_model_load(C.byref(h), path.encode(), kv_cap, 1, flags, 0, 1))
+        check(lib().hx_model_load(C.byref(h), path.encode(), kv_cap, 1, flags, tp_rank, tp_size))
         return cls(h)
 
     @classmethod
-    def synth(cls, shape, seed=0, kv_cap=1024, flags=0, eps=1e-5):
+    def synth(cls, shape, seed=0, kv_cap=1024, flags=0, eps=1e-5, tp_rank=0, tp_size=1):
         cfg = _cfg(eps=eps, **shape)
         h = C.c_void_p()
-        check(lib().hx_model_synth(C.byref(h), C.byref(cfg), seed, kv_cap, 1, flags, 0, 1))
+        check(lib().hx_model_synth(C.byref(h), C.byref(cfg), seed, kv_cap, 1, flags, tp_rank, tp_size))
         return cls(h)
+
+    def tp_handle(self):
+        """64-byte handle of this shard's exchange buffer (to be gathered from all ranks)."""
+        b = (C.c_uint8 * 64)()
+        check(lib().hx_model_tp_handle(self.h, b))
+        return bytes(b)
+
+    def tp_connect(self, handles):
+        """handles: the 64-byte handles of all ranks in rank order."""
+        blob = b"".join(handles)
+        buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        check(lib().hx_model_tp_connect(self.h, buf, len(handles)))
 
     def close(self):
         if self.h:

@@ -255,6 +255,20 @@ int hx_image_close(void* module);
 unsigned long long hx_launch_count(void);
 
 /* ---------------------------------------------------------------- tensor parallel ------------- */
+/* One process per GPU; rank r of a group of tp_size builds its shard with hx_model_load / hx_model_synth
+ * (tp_rank, tp_size): q/k/v, gate/up and lm_head rows and o_proj/down_proj columns of its heads, hidden slice and
+ * vocabulary slice (column-split qkv/gate/up, row-split o/down as in the reference plan for the 32B shape).
+ * The all-reduce after o_proj and down_proj happens INSIDE the persistent decode kernel over NVLink peer memory:
+ * every rank stores its partial sums into all ranks' exchange buffers, a flag handshake orders them, and the next
+ * linear's prologue adds them in rank order (bit-identical residual stream on every rank).  The arg-max over the
+ * vocabulary slices is exchanged the same way.  hx_model_config reports the shard's dimensions; logits returned by
+ * hx_decode_step / hx_prefill are the shard's vocabulary slice [vocab / tp_size], token ids are global.
+ * Set-up: each rank calls hx_model_tp_handle, the caller gathers the 64-byte handles of all ranks (any channel),
+ * each rank calls hx_model_tp_connect with the table [tp_size][64].  All ranks must then issue the same sequence
+ * of prefill / decode calls.  Replaces the NCCL all-reduce of the reference plan (no reference code exists). */
+int hx_model_tp_handle(hx_model* m, uint8_t handle[64]);
+int hx_model_tp_connect(hx_model* m, const uint8_t* handles, int tp_size);
+
 /* NCCL is loaded at run time (libnccl.so.2).  id is NCCL's 128-byte unique id, created on rank 0
  * with hx_tp_unique_id and distributed by the caller (any out-of-band channel). */
 int hx_tp_unique_id(uint8_t id[128]);

@@ -1,0 +1,68 @@
+"""One rank of the tensor-parallel decode test (launched by tests/test_tp_gpu.py through torch.distributed.run).
+
+Every rank loads its shard of the same HXGW v3 file, the ranks exchange their 64-byte buffer handles over gloo,
+then decode teacher-forced and free-running; rank 0 compares the gathered logits slices and the tokens with the
+CPU restatement of the full model."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "tests"))
+import helix_b200 as hb                      # noqa: E402
+from helix_b200.lib import check, lib       # noqa: E402
+
+
+def main():
+    path, n_teacher, n_free = sys.argv[1], int(sys.argv[2]), int(sys.argv[3])
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    check(lib().hx_set_device(int(os.environ.get("LOCAL_RANK", rank))))
+    gm = hb.Model.load(path, kv_cap=96, tp_rank=rank, tp_size=world)
+    mine = torch.tensor(list(gm.tp_handle()), dtype=torch.uint8)
+    allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
+    dist.all_gather(allh, mine)
+    gm.tp_connect([bytes(h.tolist()) for h in allh])
+    dist.barrier()
+
+    om = None
+    if rank == 0:
+        import oracle_lib as ol
+        om = ol.OracleModel(path, kv_cap=96)
+    NVl = gm.cfg.vocab
+    ids = np.random.default_rng(5).integers(0, NVl * world, n_teacher)
+    worst = 0.0
+    for pos, t in enumerate(ids):
+        nx, lg = gm.decode_step(int(t), pos, want_logits=True)
+        parts = [torch.zeros(NVl, dtype=torch.float32) for _ in range(world)]
+        dist.all_gather(parts, torch.from_numpy(lg.copy()))
+        nxs = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(nxs, torch.tensor([nx], dtype=torch.int64))
+        assert all(int(v) == nx for v in nxs), "ranks disagree on the next token"
+        if rank == 0:
+            full = torch.cat(parts).numpy()
+            lo = om.decode(int(t), pos)
+            worst = max(worst, float(np.max(np.abs(full - lo))))
+            assert nx == int(np.argmax(full)), (pos, nx, int(np.argmax(full)))
+    # free-running greedy continuation on top of the cache
+    out, _ = gm.decode_loop(int(ids[-1]), n_teacher - 1, n_free)
+    if rank == 0:
+        want = []
+        tok = int(ids[-1])
+        for i in range(n_free):
+            tok = int(np.argmax(om.decode(tok, n_teacher - 1 + i)))
+            want.append(tok)
+        assert worst < 2e-4, worst
+        assert list(out) == want, (list(out), want)
+        print("TP-OK world=%d max-abs-logit-diff=%.3g" % (world, worst), flush=True)
+    dist.barrier()
+    gm.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
