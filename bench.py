@@ -229,9 +229,22 @@ def run_ours(args):
     if args.layers:
         shape["n_layers"] = args.layers                 # reduced-depth case for profiler captures; not a bench line
     keep = 1 if (rank == 0 and args.gpus == 1 and not args.no_cpu_baseline) else 0
-    model = hb.Model.synth(shape, seed=1, kv_cap=PROMPT_LEN + NEW_TOKENS + 8, flags=keep)
+    tp = args.parallelism == "tp" and args.gpus > 1
+    if tp:
+        import torch
+        model = hb.Model.synth(shape, seed=1, kv_cap=PROMPT_LEN + NEW_TOKENS + 8, tp_rank=rank, tp_size=args.gpus)
+        mine = torch.tensor(list(model.tp_handle()), dtype=torch.uint8)
+        allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(args.gpus)]
+        dist.all_gather(allh, mine)
+        model.tp_connect([bytes(h.tolist()) for h in allh])
+        dist.barrier()
+    else:
+        model = hb.Model.synth(shape, seed=1, kv_cap=PROMPT_LEN + NEW_TOKENS + 8, flags=keep)
     cfgd = model.cfg.as_dict()
-    rng = np.random.default_rng(2 + rank)
+    if tp:                                              # the shard reports its own slice; bytes are counted for the whole model
+        for k in ("n_heads", "n_kv_heads", "d_ff", "vocab"):
+            cfgd[k] = shape[k]
+    rng = np.random.default_rng(2 + (0 if tp else rank))
     prompt = rng.integers(0, shape["vocab"], PROMPT_LEN).astype(np.int32)
     model.prefill(prompt[:32])                         # warm-up (graph capture, first launches)
     check(L.hx_sync())
@@ -260,7 +273,8 @@ def run_ours(args):
     if dist is not None:
         dist.barrier()
     ms_max = all_max(dist, ms_total)
-    n_tok_all = args.gpus * args.steps * NEW_TOKENS
+    n_seq = 1 if tp else args.gpus
+    n_tok_all = n_seq * args.steps * NEW_TOKENS
     value = n_tok_all / (ms_max * 1e-3)
 
     wbytes, kvbytes_mid, embbytes = algorithmic_bytes_per_token(cfgd, PROMPT_LEN + NEW_TOKENS // 2)
@@ -285,6 +299,11 @@ def run_ours(args):
                     "peak_source": peak_src, "algorithmic_bytes_per_launch": token_bytes, "avg_launch_us": avg_ms * 1e3,
                     "token_bytes": {"weights": wbytes, "kv_mid_run": kvbytes_mid, "embedding_row": embbytes},
                     "whole_token_frac": token_bytes * value / args.gpus / 1e9 / peak}
+        if tp:      # every GPU streams 1/N of the weights and KV per launch
+            roofline["algorithmic_bytes_per_launch"] = token_bytes / args.gpus
+            roofline["achieved"] = achieved / args.gpus
+            roofline["frac"] = achieved / args.gpus / peak
+            roofline["traffic"] = None
     else:
         # per-kernel device time of the dominant kernel (k_linear), event pair around every launch
         model.set_profile(True)
@@ -314,9 +333,34 @@ def run_ours(args):
         for i in range(NEW_TOKENS):
             tok, lg = model.decode_step(tok, PROMPT_LEN + i, want_logits=True)
     e2e_s = all_max(dist, time.perf_counter() - t0)
-    e2e = None if args.no_e2e else {"value": args.gpus * e2e_steps * NEW_TOKENS / e2e_s, "unit": "tok/s",
+    e2e = None if args.no_e2e else {"value": n_seq * e2e_steps * NEW_TOKENS / e2e_s, "unit": "tok/s",
            "h2d_bytes_per_step": NEW_TOKENS * 4, "d2h_bytes_per_step": NEW_TOKENS * (4 + shape["vocab"] * 4),
            "api": "hx_decode_step per token: token id H2D, next id + f32 logits row D2H (what the reference worker reads back)"}
+
+    # the other half of the path: the NVFP4 quantizer on the single-matrix shape (12288 x 4096 f32), device resident
+    quant = None
+    if rank == 0 and not args.no_e2e:
+        rows, K = 12288, 4096
+        kp = L.hx_kpad(K)
+        w = (np.random.default_rng(7).standard_normal((rows, K), dtype=np.float32) * np.float32(0.02))
+        dw = hb.DeviceBuffer.from_array(w)
+        dW, dmic, dts = hb.DeviceBuffer(rows * (kp // 7) * 4), hb.DeviceBuffer(rows * (kp // 16)), hb.DeviceBuffer(4)
+        for _ in range(3):
+            check(L.hx_quantize_nvfp4(dw.ptr, rows, K, dW.ptr, dmic.ptr, None, dts.ptr, None))
+        check(L.hx_sync())
+        tq = time.perf_counter()
+        nrep = 20
+        for _ in range(nrep):
+            check(L.hx_quantize_nvfp4(dw.ptr, rows, K, dW.ptr, dmic.ptr, None, dts.ptr, None))
+        check(L.hx_sync())
+        dtq = (time.perf_counter() - tq) / nrep
+        alg = rows * K * 4 + rows * (kp // 7) * 4 + rows * (kp // 16)
+        quant = {"shape": [rows, K], "ms": dtq * 1e3, "gelem_per_s": rows * K / dtq / 1e9,
+                 "algorithmic_bytes": alg, "achieved_gb_s": alg / dtq / 1e9, "frac_of_hbm_peak": alg / dtq / 1e9 / peak,
+                 "note": "amax pass + quantize pass (k_amax, k_quantize), bit-exact with the reference quantizer; algorithmic bytes = "
+                         "one f32 read of the tensor + the committed layout written; the second read of the tensor mostly misses L2 (201 MB)"}
+        for b in (dw, dW, dmic, dts):
+            b.free()
 
     cpu = None
     if rank == 0 and args.gpus == 1 and not args.no_cpu_baseline:      # reported at N = 1 only
@@ -330,13 +374,16 @@ def run_ours(args):
         del image
     if rank == 0:
         line = {"metric": "nvfp4_decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak",
+                "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": WORKLOAD, "weights": "nvfp4 (e2m1 + e4m3/16 + f32 tensor scale), HBM resident",
-                           "kv_cache": "f32", "engine": engine, "layers": cfgd["n_layers"], "parallelism": f"replicas x{args.gpus} (one sequence per GPU)" if args.gpus > 1 else "single GPU",
+                           "kv_cache": "f32", "engine": engine, "layers": cfgd["n_layers"],
+                           "parallelism": (f"tp{args.gpus} (one sequence, exchange inside the decode kernel over NVLink peer memory)" if tp else
+                                           f"replicas x{args.gpus} (one sequence per GPU)") if args.gpus > 1 else "single GPU",
                            "l2": "weights (4.26 GB per token) exceed the 126 MB L2, no flush needed",
                            "tokens_per_step": NEW_TOKENS, "weight_bytes_decode_layout": dbytes, "weight_bytes_committed_layout": cbytes},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+                "quantizer": quant,
                 "prefill": {"tokens": PROMPT_LEN, "ms": prefill_s * 1e3, "tok_per_s": PROMPT_LEN / prefill_s,
                             "path": "chunks of 16 tokens, one tcgen05 block-scaled GEMM per linear (exact digit columns), host ids in"},
                 "ms_per_token": ms_max / args.steps / NEW_TOKENS, "last_tokens": [int(t) for t in toks[-4:]]}
@@ -354,6 +401,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallelism", default="replicas", choices=["replicas", "tp"],
+                    help="N > 1: independent replicas (one sequence per GPU, weak scaling) or one tensor-parallel group (strong)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the per-token host-buffer loop (profiler captures)")
     ap.add_argument("--layers", type=int, default=0, help="reduced depth for profiler captures (0 = the full 36)")
     ap.add_argument("--new-tokens", type=int, default=0, help="tokens per step for profiler captures (0 = 256)")

@@ -205,6 +205,9 @@ struct SmemTc {
     volatile int abort_flag;
 };
 
+// TP: compiled with the tensor-parallel exchange (partial sums, cross-GPU barrier, arg-max exchange); the single-GPU
+// instantiation carries none of it.
+template <bool TP>
 __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxPersist P) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     SmemTc& S = *reinterpret_cast<SmemTc*>(smem_raw);
@@ -391,10 +394,10 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 if (ph.tok) xin = ph.x + (size_t)(ph.tok[P.tok_by_pos ? pos : 0]) * K;
                 const bool rms = ph.norm == HX_NORM_RMS;
                 // tensor parallel: the vector is x + the partial sums every rank left in its slot of the exchange buffer
-                const float* tpp = ph.tp_sum ? P.tp_peer[P.tp_rank] + tp_off_part(P, ph.tp_sum - 1, 0) : nullptr;
+                const float* tpp = (TP && ph.tp_sum) ? P.tp_peer[P.tp_rank] + tp_off_part(P, ph.tp_sum - 1, 0) : nullptr;
                 auto ldx4 = [&](int k) -> float4 {
                     float4 r = __ldcg(reinterpret_cast<const float4*>(xin + k));
-                    if (tpp) {
+                    if (TP && tpp) {
                         for (int w = 0; w < P.tp_world; w++) {
                             const float4 q = __ldcg(reinterpret_cast<const float4*>(tpp + (size_t)w * P.tp_dm + k));
                             r.x += q.x; r.y += q.y; r.z += q.z; r.w += q.w;
@@ -405,9 +408,8 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 const int nitems = tp.run * 32;
                 auto item_k = [&](int it) { int kc = tp.k0 + (it >> 5); if (kc >= tp.C) kc -= tp.C; return kc * 256 + (it & 31) * 8; };
                 float4 ia = make_float4(0.f, 0.f, 0.f, 0.f), ib = ia, ja = make_float4(1.f, 1.f, 1.f, 1.f), jb = ja;
-                int tpi0 = 1; while (tpi0 < 4 && nitems * tpi0 * 2 <= NCT) tpi0 *= 2;      // threads per item in pass 2
-                if (tid % (NCT / tpi0) < nitems && ph.norm != HX_NORM_ATTN) {
-                    const int k = item_k(tid % (NCT / tpi0));
+                if (tid < nitems && ph.norm != HX_NORM_ATTN) {
+                    const int k = item_k(tid);
                     if (k < K) {
                         ia = ldx4(k);
                         if (k + 4 < K) ib = ldx4(k + 4);
@@ -528,44 +530,36 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                             *reinterpret_cast<uint32_t*>(dst + n * 128 + ((j ^ (n & 7)) << 4)) = word;
                         }
                     }
-                } else {
-                    // TPI threads of different warps share an item (each fetches it itself) and write 16 / TPI digit
-                    // rows each; the row loop is unrolled so that every shift amount is a constant.
-                    const int ipt = NCT / tpi0, sub = tid / ipt;
+                } else
 #pragma unroll 1
-                    for (int it = tid - sub * ipt; it < nitems; it += ipt) {
-                        const int k = item_k(it);
-                        if (it >= ipt) {                                   // not the item fetched ahead of pass 1
-                            ia = make_float4(0.f, 0.f, 0.f, 0.f); ib = ia; ja = make_float4(1.f, 1.f, 1.f, 1.f); jb = ja;
-                            if (k < K) {
-                                ia = ldx4(k);
-                                if (k + 4 < K) ib = ldx4(k + 4);
-                                if (rms) { ja = *reinterpret_cast<const float4*>(ph.g + k); if (k + 4 < K) jb = *reinterpret_cast<const float4*>(ph.g + k + 4); }
-                            }
+                for (int it = tid; it < nitems; it += NCT) {
+                    const int k = item_k(it);
+                    if (it != tid) {                                       // later items of a long run: fetched here
+                        ia = make_float4(0.f, 0.f, 0.f, 0.f); ib = ia; ja = make_float4(1.f, 1.f, 1.f, 1.f); jb = ja;
+                        if (k < K) {
+                            ia = ldx4(k);
+                            if (k + 4 < K) ib = ldx4(k + 4);
+                            if (rms) { ja = *reinterpret_cast<const float4*>(ph.g + k); if (k + 4 < K) jb = *reinterpret_cast<const float4*>(ph.g + k + 4); }
                         }
-                        const float v[8] = {ia.x * ja.x, ia.y * ja.y, ia.z * ja.z, ia.w * ja.w, ib.x * jb.x, ib.y * jb.y, ib.z * jb.z, ib.w * jb.w};
-                        uint32_t M[8]; uint32_t sg = 0u;
+                    }
+                    const float v[8] = {ia.x * ja.x, ia.y * ja.y, ia.z * ja.z, ia.w * ja.w, ib.x * jb.x, ib.y * jb.y, ib.z * jb.z, ib.w * jb.w};
+                    uint32_t M[8]; uint32_t sg = 0u;
 #pragma unroll
-                        for (int e = 0; e < 8; e++) {
-                            M[e] = __float2uint_rn(fabsf(v[e]) * mul);
-                            sg |= (v[e] < 0.0f ? 8u : 0u) << (4 * e);
-                        }
-                        // digit n of element e is bits 31-2n, 30-2n of M[e]; it lands on bits 4e+1, 4e of the word of row n
-                        const int j = (it >> 2) & 7, w = it & 3;           // 16-byte chunk and word of this item in its cell
-                        uint8_t* dst = digb + (size_t)(it >> 5) * 2048 + w * 4;
+                    for (int e = 0; e < 8; e++) {
+                        M[e] = __float2uint_rn(fabsf(v[e]) * mul);
+                        sg |= (v[e] < 0.0f ? 8u : 0u) << (4 * e);
+                    }
+                    // digit n of element e is bits 31-2n, 30-2n of M[e]; it lands on bits 4e+1, 4e of the word of row n
+                    const int j = (it >> 2) & 7, w = it & 3;               // 16-byte chunk and word of this item in its cell
+                    uint8_t* dst = digb + (size_t)(it >> 5) * 2048 + w * 4;
+#pragma unroll 2
+                    for (int n = 0; n < TC_NDIG; n++) {
+                        uint32_t word = 0u;
 #pragma unroll
-                        for (int n = 0; n < TC_NDIG; n++) {
-                            if ((n & (tpi0 - 1)) != sub) continue;         // uniform per warp
-                            uint32_t word = 0u;
-#pragma unroll
-                            for (int e = 0; e < 8; e++) {
-                                const int sh = 30 - 2 * n - 4 * e;
-                                word |= (sh >= 0 ? (M[e] >> sh) : (M[e] << (-sh))) & (3u << (4 * e));
-                            }
-                            const uint32_t nz = (word | (word >> 1)) & 0x11111111u;   // a zero digit carries no sign
-                            word |= sg & (nz << 3);
-                            *reinterpret_cast<uint32_t*>(dst + n * 128 + ((j ^ (n & 7)) << 4)) = word;
-                        }
+                        for (int e = 0; e < 8; e++) word |= ((M[e] >> (30 - 2 * n)) & 3u) << (4 * e);
+                        const uint32_t nz = (word | (word >> 1)) & 0x11111111u;   // a zero digit carries no sign
+                        word |= sg & (nz << 3);
+                        *reinterpret_cast<uint32_t*>(dst + n * 128 + ((j ^ (n & 7)) << 4)) = word;
                     }
                 }
                 STAMP(15);
@@ -664,7 +658,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                             const int row = tile * 128 + rl;
                             if (row < ph.N) {
                                 v *= (row < ph.bound0) ? ph.ts[0] : (row < ph.bound1 ? ph.ts[1] : ph.ts[2]);
-                                if (ph.tp_partial) {
+                                if (TP && ph.tp_partial) {
                                     // row-split linear: this rank's partial sum of the row goes to every rank's buffer;
                                     // the consumer's prologue adds them to the residual stream in rank order
                                     const size_t o = tp_off_part(P, ph.tp_partial - 1, P.tp_rank) + row;
@@ -709,7 +703,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                             const int oi = __shfl_xor_sync(0xffffffffu, bi, d);
                             if (pz_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
                         }
-                        if (lane == 0 && P.tp_world > 1) {
+                        if (TP && lane == 0 && P.tp_world > 1) {
                             // vocabulary split over the ranks: exchange (value, global index) and take the best of all
                             const size_t ao = tp_off_am(P) + 2 * P.tp_rank;
                             const int gi = bi == INT_MAX ? INT_MAX : bi + P.tp_vocab_off;
@@ -766,7 +760,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 consumer_sync();                 // every thread's results are ordered before thread 0's release below
                 bar_target += (unsigned long long)grid;
                 if (tid == 0) {
-                    if (ph.tp_barrier) asm volatile("red.release.sys.global.add.u64 [%0], 1;" :: "l"(P.bar) : "memory");   // covers the stores to the peers
+                    if (TP && ph.tp_barrier) asm volatile("red.release.sys.global.add.u64 [%0], 1;" :: "l"(P.bar) : "memory");   // covers the stores to the peers
                     else asm volatile("red.release.gpu.global.add.u64 [%0], 1;" :: "l"(P.bar) : "memory");
                     bool ok = false;
                     for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
@@ -776,7 +770,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                         if ((i & 255) == 255 && S.abort_flag) break;
                     }
                     if (!ok) S.abort_flag = 1;
-                    if (ok && ph.tp_barrier) {
+                    if (TP && ok && ph.tp_barrier) {
                         // all CTAs of this GPU have arrived; CTA 0 meets the other GPUs, then lets the local CTAs go
                         const unsigned ep = P.tp_epoch_base + (unsigned)ph.tp_epoch;
                         unsigned* go = reinterpret_cast<unsigned*>(P.tp_peer[P.tp_rank] + tp_off_go(P));
@@ -837,11 +831,13 @@ int hx_persist_tc_launch(const HxPersist& p, int grid, cudaStream_t st) {
     if (smem > 227 * 1024) return hx_fail(HX_ERR_ARG, "tensor-core decode needs %zu bytes of shared memory", smem);
     static bool attr = false;
     if (!attr) {
-        HX_CUDA(cudaFuncSetAttribute(k_decode_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        HX_CUDA(cudaFuncSetAttribute(k_decode_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        HX_CUDA(cudaFuncSetAttribute(k_decode_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         attr = true;
     }
     void* args[] = {(void*)&p};
-    HX_CUDA(cudaLaunchCooperativeKernel((void*)k_decode_tc, dim3(grid), dim3(PT), args, smem, st));
+    void* fn = p.tp_world > 1 ? (void*)k_decode_tc<true> : (void*)k_decode_tc<false>;
+    HX_CUDA(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(PT), args, smem, st));
     HX_COUNT_LAUNCH(1);
     return HX_OK;
 }
