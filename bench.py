@@ -29,6 +29,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 PROMPT_LEN, NEW_TOKENS = 512, 256
+BATCH_PROBE = 64                # sequences of the batched-throughput probe (BASELINE config 4 runs 64 per GPU)
 NCU_TRAFFIC_RATIO = 1.010      # measured DRAM bytes / algorithmic bytes of k_decode_tc (profiles/)
 WORKLOAD = "qwen3-8b-shape nvfp4 greedy decode, batch 1, 512-token prompt + 256 new tokens"
 
@@ -225,7 +226,7 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     L = lib()
     check(L.hx_set_device(local))
-    shape = dict(hb.QWEN3_8B)
+    shape = dict(hb.QWEN3_32B if args.model == "32b" else hb.QWEN3_8B)
     if args.layers:
         shape["n_layers"] = args.layers                 # reduced-depth case for profiler captures; not a bench line
     keep = 1 if (rank == 0 and args.gpus == 1 and not args.no_cpu_baseline) else 0
@@ -239,7 +240,7 @@ def run_ours(args):
         model.tp_connect([bytes(h.tolist()) for h in allh])
         dist.barrier()
     else:
-        model = hb.Model.synth(shape, seed=1, kv_cap=PROMPT_LEN + NEW_TOKENS + 8, flags=keep)
+        model = hb.Model.synth(shape, seed=1, kv_cap=PROMPT_LEN + NEW_TOKENS + 8, flags=keep, batch=BATCH_PROBE)
     cfgd = model.cfg.as_dict()
     if tp:                                              # the shard reports its own slice; bytes are counted for the whole model
         for k in ("n_heads", "n_kv_heads", "d_ff", "vocab"):
@@ -362,6 +363,18 @@ def run_ours(args):
         for b in (dw, dW, dmic, dts):
             b.free()
 
+    # batched throughput: 64 independent sequences sharing the weight copy, one token each per step
+    batched = None
+    if not tp and not args.no_e2e:
+        model.fill_kv(PROMPT_LEN, 11)                  # synthetic KV rows for every sequence up to the prompt length
+        bids = np.random.default_rng(9 + rank).integers(0, shape["vocab"], BATCH_PROBE).astype(np.int32)
+        model.decode_batch_loop(bids, PROMPT_LEN, 2)
+        _, bms = model.decode_batch_loop(bids, PROMPT_LEN, 8)
+        bms = all_max(dist, bms)
+        batched = {"sequences_per_gpu": BATCH_PROBE, "steps": 8, "ms_per_step": bms / 8,
+                   "tok_per_s": args.gpus * BATCH_PROBE * 8 / (bms * 1e-3),
+                   "path": "hx_decode_batch_loop: chunks of 16 sequences per tcgen05 GEMM, per-sequence KV append and attention"}
+
     cpu = None
     if rank == 0 and args.gpus == 1 and not args.no_cpu_baseline:      # reported at N = 1 only
         image = model.v3_image()                       # the same weights, HXGW v3 bytes exported from HBM
@@ -376,14 +389,14 @@ def run_ours(args):
         line = {"metric": "nvfp4_decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": WORKLOAD, "weights": "nvfp4 (e2m1 + e4m3/16 + f32 tensor scale), HBM resident",
+                "config": {"workload": WORKLOAD.replace("qwen3-8b", "qwen3-32b") if args.model == "32b" else WORKLOAD, "weights": "nvfp4 (e2m1 + e4m3/16 + f32 tensor scale), HBM resident",
                            "kv_cache": "f32", "engine": engine, "layers": cfgd["n_layers"],
                            "parallelism": (f"tp{args.gpus} (one sequence, exchange inside the decode kernel over NVLink peer memory)" if tp else
                                            f"replicas x{args.gpus} (one sequence per GPU)") if args.gpus > 1 else "single GPU",
                            "l2": "weights (4.26 GB per token) exceed the 126 MB L2, no flush needed",
                            "tokens_per_step": NEW_TOKENS, "weight_bytes_decode_layout": dbytes, "weight_bytes_committed_layout": cbytes},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-                "quantizer": quant,
+                "quantizer": quant, "batched_decode": batched,
                 "prefill": {"tokens": PROMPT_LEN, "ms": prefill_s * 1e3, "tok_per_s": PROMPT_LEN / prefill_s,
                             "path": "chunks of 16 tokens, one tcgen05 block-scaled GEMM per linear (exact digit columns), host ids in"},
                 "ms_per_token": ms_max / args.steps / NEW_TOKENS, "last_tokens": [int(t) for t in toks[-4:]]}
@@ -403,6 +416,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--parallelism", default="replicas", choices=["replicas", "tp"],
                     help="N > 1: independent replicas (one sequence per GPU, weak scaling) or one tensor-parallel group (strong)")
+    ap.add_argument("--model", default="8b", choices=["8b", "32b"], help="Qwen3-8B shape (the headline workload) or Qwen3-32B shape")
     ap.add_argument("--no-e2e", action="store_true", help="skip the per-token host-buffer loop (profiler captures)")
     ap.add_argument("--layers", type=int, default=0, help="reduced depth for profiler captures (0 = the full 36)")
     ap.add_argument("--new-tokens", type=int, default=0, help="tokens per step for profiler captures (0 = 256)")

@@ -94,6 +94,8 @@ struct hx_model {
     // batched prefill (chunks of HX_PF_TB tokens through the tcgen05 GEMM); buffers are created on first use
     float *pf_x = nullptr, *pf_qkv = nullptr, *pf_ctx = nullptr, *pf_gu = nullptr, *pf_scale = nullptr; uint8_t* pf_cells = nullptr; int* pf_err = nullptr; float* pf_partial = nullptr; unsigned* pf_tickets = nullptr;
     int pf_gu_ld = 0; bool pf_batched = true; size_t pf_partial_n = 0;
+    int *d_bids = nullptr, *d_bpos = nullptr, *d_bseq = nullptr, *d_bnext = nullptr; float* pf_logits = nullptr; int b_cap = 0;   // batched decode
+    cudaGraphExec_t g_bstep = nullptr; int g_bstep_n = 0;
     int* d_pf_pos = nullptr; cudaGraphExec_t g_pf_chunk = nullptr; bool pf_graph_failed = false; int pf_chunk_launches = 0;
 };
 
@@ -304,7 +306,7 @@ int alloc_state(hx_model* m) {
     if ((rc = dalloc(m, &m->logits, (size_t)c.vocab))) return rc;
     HX_CUDA(cudaMemset(m->ctx, 0, (size_t)QDd * 4));
     HX_CUDA(cudaMemset(m->h, 0, (size_t)DFFd * 4));
-    const size_t kvn = (size_t)c.n_layers * NKV * cap * DH;
+    const size_t kvn = (size_t)c.n_layers * NKV * cap * DH * (size_t)m->batch;      // [sequence][layer][kv head][position][dim]
     if ((rc = dalloc(m, &m->kc, kvn))) return rc;
     if ((rc = dalloc(m, &m->vc, kvn))) return rc;
     HX_CUDA(cudaMemset(m->kc, 0, kvn * 4));
@@ -643,7 +645,8 @@ int check_cfg(const hx_config& c, int kv_cap, int batch, int tp_rank, int tp_siz
     if (c.head_dim % 32 || c.head_dim > 256) return hx_fail(HX_ERR_ARG, "head_dim %d: need a multiple of 32 up to 256", c.head_dim);
     if (c.d_model % 4 || c.d_ff % 4) return hx_fail(HX_ERR_ARG, "d_model and d_ff must be multiples of 4");
     if (kv_cap <= 0) return hx_fail(HX_ERR_ARG, "kv_cap must be positive");
-    if (batch != 1) return hx_fail(HX_ERR_ARG, "batch %d: this build decodes one sequence per model instance", batch);
+    if (batch < 1 || batch > 1024) return hx_fail(HX_ERR_ARG, "batch %d: 1 .. 1024 sequences per model instance", batch);
+    if (batch > 1 && tp_size > 1) return hx_fail(HX_ERR_ARG, "batched decode and tensor parallel are not combined in this build");
     if (tp_size < 1 || tp_size > 8 || tp_rank < 0 || tp_rank >= tp_size) return hx_fail(HX_ERR_ARG, "tensor parallel rank %d of %d", tp_rank, tp_size);
     if (tp_size > 1) {
         if (c.n_heads % tp_size || c.n_kv_heads % tp_size || c.d_ff % tp_size || c.vocab % tp_size)
@@ -660,6 +663,7 @@ HX_API int hx_model_free(hx_model* m) {
     if (m->g_decode) cudaGraphExecDestroy(m->g_decode);
     if (m->g_prefill) cudaGraphExecDestroy(m->g_prefill);
     if (m->g_pf_chunk) cudaGraphExecDestroy(m->g_pf_chunk);
+    if (m->g_bstep) cudaGraphExecDestroy(m->g_bstep);
     if (m->ev0) cudaEventDestroy(m->ev0);
     if (m->ev1) cudaEventDestroy(m->ev1);
     for (void* p : m->allocs) cudaFree(p);
@@ -998,25 +1002,65 @@ static int pf_linear(hx_model* m, const Fused& f, const float* src, int ld_src, 
     return hx_gemm_tc_launch(q, m->st);
 }
 
-// The launches of one chunk of n tokens whose first position is *d_pf_pos; ends by advancing that position.
-static int pf_enqueue_chunk(hx_model* m, int n) {
+// The launches of the layers for one chunk of n tokens (ids[t] / wh say which token, position and sequence each is).
+static int pf_enqueue_layers(hx_model* m, int n, const int* ids, HxPfWhere wh) {
     const hx_config& c = m->cfg;
     const int DH = c.head_dim, DM = c.d_model, QD = m->QD, KVD = m->KVD, cap = m->kv_cap;
     const int ldq = QD + 2 * KVD;
     const float att_scale = 1.0f / sqrtf((float)DH);
     int rc;
-    hx_pf_embed(m->d_prompt, m->d_pf_pos, m->emb, m->pf_x, n, DM, m->st);
+    hx_pf_embed(ids, wh, m->emb, m->pf_x, n, DM, m->st);
     for (int L = 0; L < c.n_layers; L++) {
         Layer& ly = m->layers[L];
         float* kc = m->kc + (size_t)L * c.n_kv_heads * cap * DH; float* vc = m->vc + (size_t)L * c.n_kv_heads * cap * DH;
         if ((rc = pf_linear(m, ly.qkv, m->pf_x, DM, n, 0, ly.in_g, m->pf_qkv, ldq, ly.qkv.N, 0, 0))) return rc;
-        hx_pf_qkpost(m->pf_qkv, ldq, n, m->d_pf_pos, c.n_heads, c.n_kv_heads, DH, ly.qn_g, ly.kn_g, c.norm_eps, m->cosT, m->sinT, kc, vc, cap, m->st);
-        if ((rc = hx_pf_attn(m->pf_qkv, ldq, n, m->d_pf_pos, c.n_heads, c.n_kv_heads, DH, kc, vc, cap, att_scale, m->pf_ctx, QD, m->st))) return rc;
+        hx_pf_qkpost(m->pf_qkv, ldq, n, wh, c.n_heads, c.n_kv_heads, DH, ly.qn_g, ly.kn_g, c.norm_eps, m->cosT, m->sinT, kc, vc, cap, m->st);
+        if ((rc = hx_pf_attn(m->pf_qkv, ldq, n, wh, c.n_heads, c.n_kv_heads, DH, kc, vc, cap, att_scale, m->pf_ctx, QD, m->st))) return rc;
         if ((rc = pf_linear(m, ly.o, m->pf_ctx, QD, n, 0, nullptr, m->pf_x, DM, ly.o.N, 1, 0))) return rc;
         if ((rc = pf_linear(m, ly.gu, m->pf_x, DM, n, 1, ly.post_g, m->pf_gu, m->pf_gu_ld, c.d_ff, 0, 1))) return rc;       // SwiGLU in the epilogue
         if ((rc = pf_linear(m, ly.down, m->pf_gu, m->pf_gu_ld, n, 0, nullptr, m->pf_x, DM, ly.down.N, 1, 0))) return rc;
     }
+    return HX_OK;
+}
+
+// One prefill chunk of n tokens whose first position is *d_pf_pos; ends by advancing that position.
+static int pf_enqueue_chunk(hx_model* m, int n) {
+    HxPfWhere wh = {m->d_pf_pos, nullptr, nullptr, 0};
+    int rc = pf_enqueue_layers(m, n, m->d_prompt, wh); if (rc) return rc;
     hx_pf_advance(m->d_pf_pos, n, m->st);
+    return HX_OK;
+}
+
+// ---- batched decode: n_seq independent sequences, one token each, in chunks of HX_PF_TB ----------------
+static int bd_alloc(hx_model* m) {
+    int rc = pf_alloc(m); if (rc) return rc;
+    if (m->d_bids) return HX_OK;
+    m->b_cap = ((m->batch + HX_PF_TB - 1) / HX_PF_TB) * HX_PF_TB;
+    if ((rc = dalloc(m, &m->d_bids, (size_t)m->b_cap))) return rc;
+    if ((rc = dalloc(m, &m->d_bpos, (size_t)m->b_cap))) return rc;
+    if ((rc = dalloc(m, &m->d_bseq, (size_t)m->b_cap))) return rc;
+    if ((rc = dalloc(m, &m->d_bnext, (size_t)m->b_cap))) return rc;
+    if ((rc = dalloc(m, &m->pf_logits, (size_t)HX_PF_TB * m->cfg.vocab))) return rc;
+    std::vector<int> seq(m->b_cap);
+    for (int i = 0; i < m->b_cap; i++) seq[i] = i;
+    HX_CUDA(cudaMemcpy(m->d_bseq, seq.data(), (size_t)m->b_cap * 4, cudaMemcpyHostToDevice));
+    return HX_OK;
+}
+
+// One decode step of sequences 0..n_seq-1: tokens d_bids, positions d_bpos (advanced by one), next tokens to d_bnext and
+// back into d_bids.
+static int bd_enqueue_step(hx_model* m, int n_seq) {
+    const hx_config& c = m->cfg;
+    const size_t seq_stride = (size_t)c.n_layers * c.n_kv_heads * m->kv_cap * c.head_dim;
+    int rc;
+    for (int c0 = 0; c0 < n_seq; c0 += HX_PF_TB) {
+        const int n = n_seq - c0 < HX_PF_TB ? n_seq - c0 : HX_PF_TB;
+        HxPfWhere wh = {nullptr, m->d_bpos + c0, m->d_bseq + c0, seq_stride};
+        if ((rc = pf_enqueue_layers(m, n, m->d_bids + c0, wh))) return rc;
+        if ((rc = pf_linear(m, m->head, m->pf_x, c.d_model, n, 0, m->final_g, m->pf_logits, c.vocab, m->head.N, 0, 0))) return rc;
+        hx_pf_argmax_rows(m->pf_logits, c.vocab, c.vocab, n, m->d_bnext + c0, m->d_bpos + c0, m->st);
+    }
+    HX_CUDA(cudaMemcpyAsync(m->d_bids, m->d_bnext, (size_t)n_seq * 4, cudaMemcpyDeviceToDevice, m->st));
     return HX_OK;
 }
 
@@ -1139,11 +1183,69 @@ HX_API int hx_generate_greedy(hx_model* m, const int32_t* prompt, int T, int n_n
     return rc;
 }
 
+static int bd_check(hx_model* m, int n_seq) {
+    if (!m->use_tc || !m->head.t128 || m->tp_world > 1) return hx_fail(HX_ERR_STATE, "batched decode needs the tensor-core engine on one GPU");
+    if (n_seq < 1 || n_seq > m->batch) return hx_fail(HX_ERR_ARG, "%d sequences, the model was created for %d", n_seq, m->batch);
+    return bd_alloc(m);
+}
+
+HX_API int hx_decode_batch(hx_model* m, const int32_t* ids, const int32_t* pos, int n_seq, int32_t* next_ids) {
+    HX_CHECK_ARG(m && ids && pos && next_ids);
+    int rc = bd_check(m, n_seq); if (rc) return rc;
+    for (int i = 0; i < n_seq; i++) {
+        if (ids[i] < 0 || ids[i] >= m->gcfg.vocab) return hx_fail(HX_ERR_ARG, "token %d outside the vocabulary", ids[i]);
+        if (pos[i] < 0 || pos[i] >= m->kv_cap) return hx_fail(HX_ERR_STATE, "position %d outside the KV capacity %d", pos[i], m->kv_cap);
+    }
+    HX_CUDA(cudaMemcpyAsync(m->d_bids, ids, (size_t)n_seq * 4, cudaMemcpyHostToDevice, m->st));
+    HX_CUDA(cudaMemcpyAsync(m->d_bpos, pos, (size_t)n_seq * 4, cudaMemcpyHostToDevice, m->st));
+    if ((rc = bd_enqueue_step(m, n_seq))) return rc;
+    HX_CUDA(cudaMemcpyAsync(next_ids, m->d_bnext, (size_t)n_seq * 4, cudaMemcpyDeviceToHost, m->st));
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    return persist_check(m);
+}
+
+HX_API int hx_decode_batch_loop(hx_model* m, const int32_t* ids, int pos0, int n_seq, int n_steps, int32_t* out_ids, float* ms) {
+    HX_CHECK_ARG(m && ids && n_steps > 0);
+    int rc = bd_check(m, n_seq); if (rc) return rc;
+    if (pos0 < 0 || pos0 + n_steps > m->kv_cap) return hx_fail(HX_ERR_STATE, "steps %d..%d outside the KV capacity %d", pos0, pos0 + n_steps, m->kv_cap);
+    std::vector<int> p((size_t)n_seq, pos0);
+    HX_CUDA(cudaMemcpyAsync(m->d_bids, ids, (size_t)n_seq * 4, cudaMemcpyHostToDevice, m->st));
+    HX_CUDA(cudaMemcpyAsync(m->d_bpos, p.data(), (size_t)n_seq * 4, cudaMemcpyHostToDevice, m->st));
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    // one step captured once per batch size and replayed (tokens and positions live in device memory)
+    if (n_steps > 1 && (!m->g_bstep || m->g_bstep_n != n_seq)) {
+        if (m->g_bstep) { cudaGraphExecDestroy(m->g_bstep); m->g_bstep = nullptr; }
+        cudaGraph_t g = nullptr;
+        HX_CUDA(cudaStreamBeginCapture(m->st, cudaStreamCaptureModeThreadLocal));
+        const unsigned long long before = g_hx_launches;
+        rc = bd_enqueue_step(m, n_seq);
+        cudaError_t e = cudaStreamEndCapture(m->st, &g);
+        m->pf_chunk_launches = (int)(g_hx_launches - before);
+        g_hx_launches = before;
+        if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+        if (e == cudaSuccess) e = cudaGraphInstantiate(&m->g_bstep, g, 0);
+        if (g) cudaGraphDestroy(g);
+        if (e != cudaSuccess) { (void)cudaGetLastError(); m->g_bstep = nullptr; }
+        m->g_bstep_n = n_seq;
+    }
+    HX_CUDA(cudaEventRecord(m->ev0, m->st));
+    for (int s = 0; s < n_steps; s++) {
+        if (m->g_bstep && m->g_bstep_n == n_seq) { HX_CUDA(cudaGraphLaunch(m->g_bstep, m->st)); HX_COUNT_LAUNCH(m->pf_chunk_launches); }
+        else if ((rc = bd_enqueue_step(m, n_seq))) return rc;
+        if (out_ids) HX_CUDA(cudaMemcpyAsync(out_ids + (size_t)s * n_seq, m->d_bnext, (size_t)n_seq * 4, cudaMemcpyDeviceToHost, m->st));
+    }
+    HX_CUDA(cudaEventRecord(m->ev1, m->st));
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    float t = 0.0f; HX_CUDA(cudaEventElapsedTime(&t, m->ev0, m->ev1));
+    if (ms) *ms = t;
+    return persist_check(m);
+}
+
 HX_API int hx_model_fill_kv(hx_model* m, int T, uint64_t seed) {
     HX_CHECK_ARG(m && T >= 0 && T <= m->kv_cap);
     const hx_config& c = m->cfg;
     // whole cache gets values; only positions below the running length are ever read
-    const size_t n = (size_t)c.n_layers * c.n_kv_heads * m->kv_cap * c.head_dim;
+    const size_t n = (size_t)c.n_layers * c.n_kv_heads * m->kv_cap * c.head_dim * (size_t)m->batch;
     int rc = hx_launch_fill_normal(m->kc, n, 1.0f, seed * 2 + 1, m->st); if (rc) return rc;
     rc = hx_launch_fill_normal(m->vc, n, 1.0f, seed * 2 + 2, m->st); if (rc) return rc;
     HX_CUDA(cudaStreamSynchronize(m->st));

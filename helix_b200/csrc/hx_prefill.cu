@@ -20,8 +20,8 @@ __device__ __forceinline__ float pf_silu_mul(float g, float u) {      // same fo
     return g * (0.5f * (1.0f + th)) * u;
 }
 
-__global__ void __launch_bounds__(256) k_pf_embed(const int* __restrict__ ids, const int* __restrict__ posp, const float* __restrict__ emb, float* __restrict__ X, int DM) {
-    const float4* src = reinterpret_cast<const float4*>(emb + (size_t)ids[*posp + blockIdx.x] * DM);
+__global__ void __launch_bounds__(256) k_pf_embed(const int* __restrict__ ids, HxPfWhere wh, const float* __restrict__ emb, float* __restrict__ X, int DM) {
+    const float4* src = reinterpret_cast<const float4*>(emb + (size_t)ids[wh.pos_arr ? (int)blockIdx.x : *wh.posp + (int)blockIdx.x] * DM);
     float4* dst = reinterpret_cast<float4*>(X + (size_t)blockIdx.x * DM);
     for (int i = threadIdx.x; i < DM / 4; i += blockDim.x) dst[i] = src[i];
 }
@@ -90,11 +90,12 @@ __global__ void __launch_bounds__(512) k_pf_digits(const float* __restrict__ src
 }
 
 // grid (NH + 2 NKV, n_tok), block DH threads (DH <= 256)
-__global__ void __launch_bounds__(256) k_pf_qkpost(float* __restrict__ qkv, int ld, const int* __restrict__ posp, int NH, int NKV, int DH,
+__global__ void __launch_bounds__(256) k_pf_qkpost(float* __restrict__ qkv, int ld, HxPfWhere wh, int NH, int NKV, int DH,
                                                     const float* __restrict__ qn_g, const float* __restrict__ kn_g, float eps,
                                                     const float* __restrict__ cosT, const float* __restrict__ sinT,
                                                     float* __restrict__ kc, float* __restrict__ vc, int cap) {
-    const int hs = blockIdx.x, t = blockIdx.y, e = threadIdx.x, half = DH >> 1, pos = *posp + t;
+    const int hs = blockIdx.x, t = blockIdx.y, e = threadIdx.x, half = DH >> 1, pos = wh.pos_arr ? wh.pos_arr[t] : *wh.posp + t;
+    const size_t seq_off = wh.seq_arr ? (size_t)wh.seq_arr[t] * wh.seq_stride : 0;
     const int sec = hs < NH ? 0 : (hs < NH + NKV ? 1 : 2);
     float* row = qkv + (size_t)t * ld + (size_t)hs * DH;
     __shared__ float sm[256]; __shared__ float red[8];
@@ -117,7 +118,7 @@ __global__ void __launch_bounds__(256) k_pf_qkpost(float* __restrict__ qkv, int 
         if (sec == 0) row[e] = v;
         else {
             const int kvh = hs - NH - (sec == 2 ? NKV : 0);
-            (sec == 1 ? kc : vc)[((size_t)kvh * cap + pos) * DH + e] = v;
+            (sec == 1 ? kc : vc)[seq_off + ((size_t)kvh * cap + pos) * DH + e] = v;
         }
     }
 }
@@ -126,20 +127,21 @@ __global__ void __launch_bounds__(256) k_pf_qkpost(float* __restrict__ qkv, int 
 // fused_decode_attn_kernel.hx:74-102), so shared memory does not grow with the context.
 #define PF_KT 64
 template <int GRP>
-__global__ void __launch_bounds__(128) k_pf_attn(const float* __restrict__ qkv, int ld, const int* __restrict__ posp, int NH, int DH,
+__global__ void __launch_bounds__(128) k_pf_attn(const float* __restrict__ qkv, int ld, HxPfWhere wh, int NH, int DH,
                                                   const float* __restrict__ kc, const float* __restrict__ vc, int cap, float scale,
                                                   float* __restrict__ ctx, int ld_ctx) {
     extern __shared__ float smf[];
     const int kvh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int T = *posp + t + 1;
+    const int T = (wh.pos_arr ? wh.pos_arr[t] : *wh.posp + t) + 1;
+    const size_t seq_off = wh.seq_arr ? (size_t)wh.seq_arr[t] * wh.seq_stride : 0;
     float* sq = smf;                   // [GRP][DH]
     float* sp = smf + GRP * DH;        // [GRP][PF_KT]
     __shared__ float sm_m[GRP], sm_l[GRP], sm_r[GRP];
     for (int i = tid; i < GRP * DH; i += 128) sq[i] = qkv[(size_t)t * ld + (size_t)kvh * GRP * DH + i];
     if (tid < GRP) { sm_m[tid] = -100000000.0f; sm_l[tid] = 0.0f; }
     __syncthreads();
-    const float* kbase = kc + (size_t)kvh * cap * DH;
-    const float* vbase = vc + (size_t)kvh * cap * DH;
+    const float* kbase = kc + seq_off + (size_t)kvh * cap * DH;
+    const float* vbase = vc + seq_off + (size_t)kvh * cap * DH;
     float acc[GRP][2];                 // output dimensions tid and tid + 128
 #pragma unroll
     for (int i = 0; i < GRP; i++) acc[i][0] = acc[i][1] = 0.0f;
@@ -200,6 +202,23 @@ __global__ void __launch_bounds__(128) k_pf_attn(const float* __restrict__ qkv, 
 }
 
 __global__ void k_pf_advance(int* posp, int n) { if (threadIdx.x == 0) *posp += n; }
+// one CTA per token row: first maximum of logits[row][0..n) -> next[row]; the row's position advances by one
+__global__ void __launch_bounds__(1024) k_pf_argmax_rows(const float* __restrict__ logits, int n, int ld, int* __restrict__ next, int* __restrict__ pos_arr) {
+    const float* lg = logits + (size_t)blockIdx.x * ld;
+    float bv = -INFINITY; int bi = INT_MAX;
+    for (int i = threadIdx.x; i < n; i += 1024) { const float v = lg[i]; if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
+    __shared__ float sv[1024]; __shared__ int si[1024];
+    sv[threadIdx.x] = bv; si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int s = 512; s >= 1; s >>= 1) {
+        if (threadIdx.x < s) {
+            const float ov = sv[threadIdx.x + s]; const int oi = si[threadIdx.x + s];
+            if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) { sv[threadIdx.x] = ov; si[threadIdx.x] = oi; }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) { next[blockIdx.x] = si[0] == INT_MAX ? 0 : si[0]; if (pos_arr) pos_arr[blockIdx.x] += 1; }
+}
 
 __global__ void __launch_bounds__(1024) k_pf_argmax(const float* __restrict__ logits, int n, int* tok, int* hist, int* pos_out, int pos) {   // pos: position of the logits row
     float bv = -INFINITY; int bi = INT_MAX;
@@ -222,8 +241,8 @@ __global__ void __launch_bounds__(1024) k_pf_argmax(const float* __restrict__ lo
 
 }  // namespace
 
-void hx_pf_embed(const int* ids, const int* posp, const float* emb, float* X, int n_tok, int DM, cudaStream_t st) {
-    k_pf_embed<<<n_tok, 256, 0, st>>>(ids, posp, emb, X, DM);
+void hx_pf_embed(const int* ids, HxPfWhere wh, const float* emb, float* X, int n_tok, int DM, cudaStream_t st) {
+    k_pf_embed<<<n_tok, 256, 0, st>>>(ids, wh, emb, X, DM);
     HX_COUNT_LAUNCH(1);
 }
 
@@ -234,20 +253,20 @@ void hx_pf_digits(const float* src, int ld, int n_tok, int K, int swiglu, const 
     HX_COUNT_LAUNCH(1);
 }
 
-void hx_pf_qkpost(float* qkv, int ld, int n_tok, const int* posp, int NH, int NKV, int DH, const float* qn_g, const float* kn_g,
+void hx_pf_qkpost(float* qkv, int ld, int n_tok, HxPfWhere wh, int NH, int NKV, int DH, const float* qn_g, const float* kn_g,
                   float eps, const float* cosT, const float* sinT, float* kc, float* vc, int cap, cudaStream_t st) {
     const int threads = ((DH + 31) / 32) * 32;
-    k_pf_qkpost<<<dim3(NH + 2 * NKV, n_tok), threads, 0, st>>>(qkv, ld, posp, NH, NKV, DH, qn_g, kn_g, eps, cosT, sinT, kc, vc, cap);
+    k_pf_qkpost<<<dim3(NH + 2 * NKV, n_tok), threads, 0, st>>>(qkv, ld, wh, NH, NKV, DH, qn_g, kn_g, eps, cosT, sinT, kc, vc, cap);
     HX_COUNT_LAUNCH(1);
 }
 
-int hx_pf_attn(const float* qkv, int ld, int n_tok, const int* posp, int NH, int NKV, int DH, const float* kc, const float* vc,
+int hx_pf_attn(const float* qkv, int ld, int n_tok, HxPfWhere wh, int NH, int NKV, int DH, const float* kc, const float* vc,
                int cap, float scale, float* ctx, int ld_ctx, cudaStream_t st) {
     const int GRP = NH / NKV;
     if (DH > 256) return hx_fail(HX_ERR_ARG, "batched prefill attention: head_dim %d > 256", DH);
     const size_t smem = ((size_t)GRP * DH + (size_t)GRP * PF_KT) * 4;
     dim3 grid(NKV, n_tok);
-#define HX_PF_ATTN(G) case G: k_pf_attn<G><<<grid, 128, smem, st>>>(qkv, ld, posp, NH, DH, kc, vc, cap, scale, ctx, ld_ctx); break;
+#define HX_PF_ATTN(G) case G: k_pf_attn<G><<<grid, 128, smem, st>>>(qkv, ld, wh, NH, DH, kc, vc, cap, scale, ctx, ld_ctx); break;
     switch (GRP) {
         HX_PF_ATTN(1) HX_PF_ATTN(2) HX_PF_ATTN(3) HX_PF_ATTN(4) HX_PF_ATTN(5) HX_PF_ATTN(6) HX_PF_ATTN(7) HX_PF_ATTN(8)
         default: return hx_fail(HX_ERR_ARG, "batched prefill attention: group of %d query heads per kv head not supported", GRP);
@@ -264,5 +283,10 @@ void hx_pf_advance(int* posp, int n, cudaStream_t st) {
 
 void hx_pf_argmax(const float* logits, int n, int* tok, int* hist, int* pos_out, int pos, cudaStream_t st) {
     k_pf_argmax<<<1, 1024, 0, st>>>(logits, n, tok, hist, pos_out, pos);
+    HX_COUNT_LAUNCH(1);
+}
+
+void hx_pf_argmax_rows(const float* logits, int n, int ld, int rows, int* next, int* pos_arr, cudaStream_t st) {
+    k_pf_argmax_rows<<<rows, 1024, 0, st>>>(logits, n, ld, next, pos_arr);
     HX_COUNT_LAUNCH(1);
 }

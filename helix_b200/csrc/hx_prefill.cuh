@@ -5,10 +5,15 @@
 
 #define HX_PF_TB 16                // tokens per chunk: 16 digit columns each = the 256 columns of one MMA
 
+// Where the tokens of a chunk sit.  Prefill: consecutive positions of one sequence starting at *posp (device memory, so
+// that the launches of a chunk can be replayed as one CUDA graph).  Batched decode: token t is at position pos_arr[t] of
+// sequence seq_arr[t], whose KV cache starts seq_stride floats after the previous sequence's.
+struct HxPfWhere { const int* posp; const int* pos_arr; const int* seq_arr; size_t seq_stride; };
+
 // Positions are read from device memory (*posp = position of the chunk's first token) so that the launches of a
 // chunk can be replayed as one CUDA graph.
 // X[t][:] = emb[ids[*posp + t]][:]
-void hx_pf_embed(const int* ids, const int* posp, const float* emb, float* X, int n_tok, int DM, cudaStream_t st);
+void hx_pf_embed(const int* ids, HxPfWhere wh, const float* emb, float* X, int n_tok, int DM, cudaStream_t st);
 
 // Digit columns of a chunk of activation vectors, in the B-cell layout of the digit-mode GEMM.
 //   src [n_tok][ld] f32; swiglu != 0: the vector is silu(gate)*up read from gate/up tiles of 128 rows
@@ -21,12 +26,12 @@ void hx_pf_digits(const float* src, int ld, int n_tok, int K, int swiglu, const 
 
 // Per token and head of a chunk: RMSNorm (gains qn_g / kn_g, may be null) + rotate_half RoPE at position *posp + t on
 // q (in place) and k; k and v are written to the cache rows of their positions.
-void hx_pf_qkpost(float* qkv, int ld, int n_tok, const int* posp, int NH, int NKV, int DH, const float* qn_g, const float* kn_g,
+void hx_pf_qkpost(float* qkv, int ld, int n_tok, HxPfWhere wh, int NH, int NKV, int DH, const float* qn_g, const float* kn_g,
                   float eps, const float* cosT, const float* sinT, float* kc, float* vc, int cap, cudaStream_t st);
 
 // Causal attention of a chunk over the cache: query t (position *posp + t) attends to positions 0 .. *posp + t.
 // One CTA per (kv head, token); the query heads of a kv head share its K and V rows.
-int hx_pf_attn(const float* qkv, int ld, int n_tok, const int* posp, int NH, int NKV, int DH, const float* kc, const float* vc,
+int hx_pf_attn(const float* qkv, int ld, int n_tok, HxPfWhere wh, int NH, int NKV, int DH, const float* kc, const float* vc,
                int cap, float scale, float* ctx, int ld_ctx, cudaStream_t st);
 
 // *posp += n
@@ -34,3 +39,5 @@ void hx_pf_advance(int* posp, int n, cudaStream_t st);
 
 // First maximum of logits[0..n): index to *tok and hist[pos + 1]; *pos_out = pos + 1.
 void hx_pf_argmax(const float* logits, int n, int* tok, int* hist, int* pos_out, int pos, cudaStream_t st);
+// per-row arg-max of logits [rows][ld] (n valid columns) -> next[row]; pos_arr[row] += 1 when given
+void hx_pf_argmax_rows(const float* logits, int n, int ld, int rows, int* next, int* pos_arr, cudaStream_t st);

@@ -103,6 +103,8 @@ _SIGS = {
     "hx_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "hx_model_last_stats": (C.c_int, [C.c_void_p, C.POINTER(HxStepStats)]),
     "hx_model_engine": (C.c_char_p, [C.c_void_p]),
+    "hx_decode_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "hx_decode_batch_loop": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float)]),
     "hx_model_tp_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
     "hx_model_tp_connect": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
     "hx_model_set_profile": (C.c_int, [C.c_void_p, C.c_int]),
@@ -242,17 +244,31 @@ class Model:
         self.vocab = c.vocab
 
     @classmethod
-    def load(cls, path, kv_cap=1024, flags=0, tp_rank=0, tp_size=1):
+    def load(cls, path, kv_cap=1024, flags=0, tp_rank=0, tp_size=1, batch=1):
         h = C.c_void_p()
-        check(lib().hx_model_load(C.byref(h), path.encode(), kv_cap, 1, flags, tp_rank, tp_size))
+        check(lib().hx_model_load(C.byref(h), path.encode(), kv_cap, batch, flags, tp_rank, tp_size))
         return cls(h)
 
     @classmethod
-    def synth(cls, shape, seed=0, kv_cap=1024, flags=0, eps=1e-5, tp_rank=0, tp_size=1):
+    def synth(cls, shape, seed=0, kv_cap=1024, flags=0, eps=1e-5, tp_rank=0, tp_size=1, batch=1):
         cfg = _cfg(eps=eps, **shape)
         h = C.c_void_p()
-        check(lib().hx_model_synth(C.byref(h), C.byref(cfg), seed, kv_cap, 1, flags, tp_rank, tp_size))
+        check(lib().hx_model_synth(C.byref(h), C.byref(cfg), seed, kv_cap, batch, flags, tp_rank, tp_size))
         return cls(h)
+
+    def decode_batch(self, ids, pos):
+        """One token of each sequence i (KV slot i): ids[i] at pos[i]; returns the arg-max tokens."""
+        ids = np.ascontiguousarray(ids, np.int32); pos = np.ascontiguousarray(pos, np.int32)
+        out = np.zeros(len(ids), np.int32)
+        check(lib().hx_decode_batch(self.h, ids.ctypes.data, pos.ctypes.data, len(ids), out.ctypes.data))
+        return out
+
+    def decode_batch_loop(self, ids, pos0, n_steps):
+        ids = np.ascontiguousarray(ids, np.int32)
+        out = np.zeros((n_steps, len(ids)), np.int32)
+        ms = C.c_float()
+        check(lib().hx_decode_batch_loop(self.h, ids.ctypes.data, pos0, len(ids), n_steps, out.ctypes.data, C.byref(ms)))
+        return out, ms.value
 
     def tp_handle(self):
         """64-byte handle of this shard's exchange buffer (to be gathered from all ranks)."""

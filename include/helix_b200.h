@@ -234,6 +234,16 @@ int hx_model_set_profile(hx_model* m, int on);
  * region.  out_ids[batch*n_steps] may be NULL. */
 int hx_decode_loop(hx_model* m, const int32_t* ids, int pos0, int n_steps, int32_t* out_ids, float* ms);
 
+/* Batched decode (BASELINE config 4: independent sequences sharing one weight copy).  The model is created with
+ * batch = number of sequences; sequence i owns KV slot i.  One call decodes one token of each of n_seq sequences:
+ * ids[i] at position pos[i] (HOST arrays), arg-max to next_ids[i].  Internally chunks of 16 sequences go through every
+ * linear as one tcgen05 GEMM (the weights are streamed once per 16 tokens instead of once per token), attention and
+ * the KV append run per sequence.  The reference has no batch dimension (one sequence at a time). */
+int hx_decode_batch(hx_model* m, const int32_t* ids, const int32_t* pos, int n_seq, int32_t* next_ids);
+/* n_steps such steps from position pos0 for every sequence, feeding back the arg-max on the device; the step is
+ * captured once and replayed.  out_ids [n_steps][n_seq] may be NULL; *ms = device time of the loop. */
+int hx_decode_batch_loop(hx_model* m, const int32_t* ids, int pos0, int n_seq, int n_steps, int32_t* out_ids, float* ms);
+
 /* Fill the KV cache for positions [0, T) with seeded synthetic values (benchmark set-up for a long
  * context without running a long prefill). */
 int hx_model_fill_kv(hx_model* m, int T, uint64_t seed);
