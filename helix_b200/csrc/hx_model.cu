@@ -1253,11 +1253,6 @@ HX_API int hx_model_fill_kv(hx_model* m, int T, uint64_t seed) {
     return HX_OK;
 }
 
-// ---- tensor parallel (collectives are loaded on demand) ---------------------------------------------
-HX_API int hx_tp_unique_id(uint8_t id[128]) { (void)id; return hx_fail(HX_ERR_COMM, "tensor parallel is not built yet"); }
-HX_API int hx_tp_init(const uint8_t id[128], int rank, int world) { (void)id; (void)rank; (void)world; return hx_fail(HX_ERR_COMM, "tensor parallel is not built yet"); }
-HX_API int hx_tp_shutdown(void) { return HX_OK; }
-
 // ---- BASELINE config 1: quantize W, then y = dequant(W) x, host buffers in and out ---------------------
 HX_API int hx_roundtrip_host(const float* w, int rows, int K, const float* x, float* y, int* kpad_out) {
     HX_CHECK_ARG(w && x && y && rows > 0 && K > 0 && K % 4 == 0);

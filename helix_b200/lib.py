@@ -113,9 +113,6 @@ _SIGS = {
     "hx_image_open": (C.c_int, [C.POINTER(C.c_void_p), C.c_char_p]),
     "hx_image_launch": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_void_p]),
     "hx_image_close": (C.c_int, [C.c_void_p]),
-    "hx_tp_unique_id": (C.c_int, [C.c_void_p]),
-    "hx_tp_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
-    "hx_tp_shutdown": (C.c_int, []),
 }
 
 

@@ -279,12 +279,6 @@ unsigned long long hx_launch_count(void);
 int hx_model_tp_handle(hx_model* m, uint8_t handle[64]);
 int hx_model_tp_connect(hx_model* m, const uint8_t* handles, int tp_size);
 
-/* NCCL is loaded at run time (libnccl.so.2).  id is NCCL's 128-byte unique id, created on rank 0
- * with hx_tp_unique_id and distributed by the caller (any out-of-band channel). */
-int hx_tp_unique_id(uint8_t id[128]);
-int hx_tp_init(const uint8_t id[128], int rank, int world);
-int hx_tp_shutdown(void);
-
 #ifdef __cplusplus
 }
 #endif
