@@ -425,20 +425,31 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                     const int NS = ph.nsplit;
                     float mx = 0.0f;
                     for (int i = tid; i < ph.NH * NS; i += NCT) mx = fmaxf(mx, __ldcg(P.part_amax + i));
+                    // two heads per pass so that their statistics travel together (one L2 round trip instead of two)
                     #pragma unroll 1
-                    for (int h = warp; h < ph.NH; h += NCW) {
-                        float mv[2], lv[2];
+                    for (int h0 = warp; h0 < ph.NH; h0 += 2 * NCW) {
+                        float mv[2][2], lv[2][2];
 #pragma unroll
-                        for (int j = 0; j < 2; j++) {
-                            const int sidx = lane + 32 * j;
-                            mv[j] = sidx < NS ? __ldcg(P.part_m + (size_t)h * NS + sidx) : -INFINITY;
-                            lv[j] = sidx < NS ? __ldcg(P.part_l + (size_t)h * NS + sidx) : 0.0f;
+                        for (int u = 0; u < 2; u++) {
+                            const int h = h0 + u * NCW;
+#pragma unroll
+                            for (int j = 0; j < 2; j++) {
+                                const int sidx = lane + 32 * j;
+                                const bool ok = h < ph.NH && sidx < NS;
+                                mv[u][j] = ok ? __ldcg(P.part_m + (size_t)h * NS + sidx) : -INFINITY;
+                                lv[u][j] = ok ? __ldcg(P.part_l + (size_t)h * NS + sidx) : 0.0f;
+                            }
                         }
-                        const float M = hx_warp_max(fmaxf(mv[0], mv[1]));
-                        const float w0 = __expf(mv[0] - M), w1 = __expf(mv[1] - M);
-                        const float Lsum = hx_warp_sum(lv[0] * w0 + lv[1] * w1);
-                        if (lane < NS) S.wgt[h * NS + lane] = w0 / Lsum;
-                        if (lane + 32 < NS) S.wgt[h * NS + lane + 32] = w1 / Lsum;
+#pragma unroll
+                        for (int u = 0; u < 2; u++) {
+                            const int h = h0 + u * NCW;
+                            if (h >= ph.NH) break;
+                            const float M = hx_warp_max(fmaxf(mv[u][0], mv[u][1]));
+                            const float w0 = __expf(mv[u][0] - M), w1 = __expf(mv[u][1] - M);
+                            const float Lsum = hx_warp_sum(lv[u][0] * w0 + lv[u][1] * w1);
+                            if (lane < NS) S.wgt[h * NS + lane] = w0 / Lsum;
+                            if (lane + 32 < NS) S.wgt[h * NS + lane + 32] = w1 / Lsum;
+                        }
                     }
                     mx = hx_warp_max(mx);
                     if (lane == 0) S.red[NCW + warp] = mx;
