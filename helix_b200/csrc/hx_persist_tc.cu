@@ -589,6 +589,9 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
 #pragma unroll 1
                     for (int tile = t_first; tile <= t_last; tile++) {
                         const uint32_t buf = uc & 1u;
+                        // the residual row is final since the last barrier: fetch it while the MMAs of this piece run
+                        float yres = 0.0f;
+                        if (ph.epi == HX_EPI_RESID && !(TP && ph.tp_partial) && tile * 128 + rl < ph.N) yres = __ldcg(ph.y + tile * 128 + rl);
                         if (!mbar_wait(&S.acc_full[buf], (uc >> 1) & 1, &S.abort_flag)) break;   // flag is latched; leave with the others at the barrier
                         uc++;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -675,7 +678,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                                     const size_t o = tp_off_part(P, ph.tp_partial - 1, P.tp_rank) + row;
                                     for (int w = 0; w < P.tp_world; w++) P.tp_peer[w][o] = v;
                                 } else {
-                                    if (ph.epi == HX_EPI_RESID) v = __ldcg(ph.y + row) + v;
+                                    if (ph.epi == HX_EPI_RESID) v = yres + v;
                                     ph.y[row] = v;
                                 }
                                 if (ph.epi == HX_EPI_ARGMAX && pz_better(v, row, best_v, best_i)) { best_v = v; best_i = row; }
