@@ -592,6 +592,15 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                         // the residual row is final since the last barrier: fetch it while the MMAs of this piece run
                         float yres = 0.0f;
                         if (ph.epi == HX_EPI_RESID && !(TP && ph.tp_partial) && tile * 128 + rl < ph.N) yres = __ldcg(ph.y + tile * 128 + rl);
+                        // likewise the norm gain and the RoPE factors of this row (qkv epilogue)
+                        float pre_g = 1.0f, pre_cs = 1.0f, pre_sn = 0.0f;
+                        if (ph.epi == HX_EPI_QKV) {
+                            const int row = tile * 128 + rl, e = row % ph.DH, half = ph.DH >> 1;
+                            const int sec = row < ph.NH * ph.DH ? 0 : (row < (ph.NH + ph.NKV) * ph.DH ? 1 : 2);
+                            const float* gg = sec == 0 ? ph.qn_g : (sec == 1 ? ph.kn_g : nullptr);
+                            if (gg) pre_g = gg[e];
+                            if (ph.cosT) { pre_cs = ph.cosT[(size_t)pos * half + (e < half ? e : e - half)]; pre_sn = ph.sinT[(size_t)pos * half + (e < half ? e : e - half)]; }
+                        }
                         if (!mbar_wait(&S.acc_full[buf], (uc >> 1) & 1, &S.abort_flag)) break;   // flag is latched; leave with the others at the barrier
                         uc++;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -643,13 +652,12 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                                 for (int j = 0; j < (DH >> 5); j++) ssq += S.swi[w0 + j];
                                 epi_sync();
                             }
-                            if (gg) v = gg[e] * (v * rsqrtf(ssq / (float)DH + ph.eps));
+                            if (gg) v = pre_g * (v * rsqrtf(ssq / (float)DH + ph.eps));
                             if (ph.cosT) {                       // every thread meets the barriers, v rows keep their value
                                 S.swi[rl] = v;
                                 epi_sync();
                                 const float other = S.swi[e < half ? rl + half : rl - half];
-                                const float cs = ph.cosT[(size_t)pos * half + (e < half ? e : e - half)];
-                                const float sn = ph.sinT[(size_t)pos * half + (e < half ? e : e - half)];
+                                const float cs = pre_cs, sn = pre_sn;
                                 if (sec < 2) v = e < half ? v * cs - other * sn : v * cs + other * sn;
                                 epi_sync();
                             }
