@@ -321,10 +321,10 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
             for (int pi = 0; pi < P.nphases && ok; pi++) {
                 const HxPhase& ph = P.phases[pi];
                 if (ph.type == HX_PH_LINEAR_TC) {
+                    const TcPlan tp = tc_plan(ph, cta, grid);                    // worked out while the consumers build the digits
                     ok = mbar_wait(&S.b_ready, tcph & 1, &S.abort_flag);        // digit columns of this phase are in place
                     tcph++;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const TcPlan tp = tc_plan(S.ph[pi & 1], cta, grid);          // the consumers' copy is in place with the digits
                     int kc = tp.k0, dp = 0;              // K cell of the tile, its position among the digit cells
                     bool fresh = true;
                     uint32_t dcol = 0;
