@@ -53,6 +53,36 @@ __device__ __forceinline__ float pz_silu_mul(float g, float u) {
 }
 __device__ __forceinline__ bool pz_better(float av, int ai, float bv, int bi) { return av > bv || (av == bv && ai < bi); }
 
+// Digit rows of eight consecutive elements.  M[e] = |x_e| / S * 2^31 (32 bits = sixteen base-4 digits, most significant
+// first), sg = sign bits (bit 4e+3 set when x_e < 0).  row[n] = the 32-bit word of digit row n: nibble e holds digit n of
+// element e as an E2M1 code (value digit/2), with the sign bit on non-zero digits.  Each halfword is spread to one digit
+// per nibble, then an 8 x 8 nibble transpose turns "element-major" into "digit-major".
+__device__ __forceinline__ void hx_digit_rows(const uint32_t (&M)[8], uint32_t sg, uint32_t (&row)[16]) {
+    uint32_t hi[8], lo[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        uint32_t a = M[e] >> 16, b = M[e] & 0xFFFFu;
+        a = (a | (a << 8)) & 0x00FF00FFu; b = (b | (b << 8)) & 0x00FF00FFu;
+        a = (a | (a << 4)) & 0x0F0F0F0Fu; b = (b | (b << 4)) & 0x0F0F0F0Fu;
+        hi[e] = (a | (a << 2)) & 0x33333333u; lo[e] = (b | (b << 2)) & 0x33333333u;
+    }
+    auto transpose = [](uint32_t (&a)[8]) {
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) { const uint32_t t = ((a[i] >> 4) ^ a[i + 1]) & 0x0F0F0F0Fu; a[i + 1] ^= t; a[i] ^= t << 4; }
+#pragma unroll
+        for (int q = 0; q < 4; q++) { const int i = (q & 1) + (q >> 1) * 4; const uint32_t t = ((a[i] >> 8) ^ a[i + 2]) & 0x00FF00FFu; a[i + 2] ^= t; a[i] ^= t << 8; }
+#pragma unroll
+        for (int i = 0; i < 4; i++) { const uint32_t t = ((a[i] >> 16) ^ a[i + 4]) & 0x0000FFFFu; a[i + 4] ^= t; a[i] ^= t << 16; }
+    };
+    transpose(hi); transpose(lo);
+#pragma unroll
+    for (int n = 0; n < 16; n++) {
+        uint32_t w = n < 8 ? hi[7 - n] : lo[15 - n];
+        const uint32_t nz = (w | (w >> 1)) & 0x11111111u;       // a zero digit carries no sign
+        row[n] = w | (sg & (nz << 3));
+    }
+}
+
 struct AttPlan { int active, kv, split, t0, t1, n_old, rows_per_slot, nslots, has_new; };
 __device__ __forceinline__ AttPlan att_plan(const HxPhase& ph, int cta, int pos) {
     AttPlan a;

@@ -152,16 +152,22 @@ __device__ __forceinline__ TcPlan tc_plan(const HxPhase& ph, int cta, int grid) 
         } else { p.b0 = p.b1 = 0; }
     } else {
         p.geff = p.total < grid ? (int)p.total : grid;
-        if (cta < p.geff) { p.b0 = (long long)cta * p.total / p.geff; p.b1 = (long long)(cta + 1) * p.total / p.geff; }
-        else { p.b0 = p.b1 = 0; }
+        if (cta >= p.geff) { p.b0 = p.b1 = 0; }
+        else if (p.total * (p.geff + 1) < 0x7FFFFFFFLL) {       // 32-bit divisions (the usual case) are several times cheaper
+            const unsigned t32 = (unsigned)p.total, g32 = (unsigned)p.geff;
+            p.b0 = (unsigned)cta * t32 / g32; p.b1 = (unsigned)(cta + 1) * t32 / g32;
+        } else { p.b0 = (long long)cta * p.total / p.geff; p.b1 = (long long)(cta + 1) * p.total / p.geff; }
     }
-    p.k0 = (int)(p.b0 % p.C);
+    p.k0 = p.b0 < 0x7FFFFFFFLL ? (int)((unsigned)p.b0 % (unsigned)p.C) : (int)(p.b0 % p.C);
     const long long n = p.b1 - p.b0;
     p.run = n < p.C ? (int)n : p.C;
     return p;
 }
 // CTA whose run holds cell x (contiguous runs)
-__device__ __forceinline__ int tc_owner(long long x, long long total, int grid) { return (int)(((x + 1) * grid + total - 1) / total) - 1; }
+__device__ __forceinline__ int tc_owner(long long x, long long total, int grid) {
+    if ((x + 2) * grid + total < 0x7FFFFFFFLL) return (int)((((unsigned)x + 1u) * (unsigned)grid + (unsigned)total - 1u) / (unsigned)total) - 1;
+    return (int)(((x + 1) * grid + total - 1) / total) - 1;
+}
 
 // ---- tensor-parallel exchange buffer (floats / 32-bit words) ----
 __device__ __forceinline__ size_t tp_off_part(const HxPersist& P, int slot, int w) { return ((size_t)slot * P.tp_world + w) * P.tp_dm; }
@@ -563,15 +569,10 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                     // digit n of element e is bits 31-2n, 30-2n of M[e]; it lands on bits 4e+1, 4e of the word of row n
                     const int j = (it >> 2) & 7, w = it & 3;               // 16-byte chunk and word of this item in its cell
                     uint8_t* dst = digb + (size_t)(it >> 5) * 2048 + w * 4;
-#pragma unroll 2
-                    for (int n = 0; n < TC_NDIG; n++) {
-                        uint32_t word = 0u;
+                    uint32_t rowv[16];
+                    hx_digit_rows(M, sg, rowv);
 #pragma unroll
-                        for (int e = 0; e < 8; e++) word |= ((M[e] >> (30 - 2 * n)) & 3u) << (4 * e);
-                        const uint32_t nz = (word | (word >> 1)) & 0x11111111u;   // a zero digit carries no sign
-                        word |= sg & (nz << 3);
-                        *reinterpret_cast<uint32_t*>(dst + n * 128 + ((j ^ (n & 7)) << 4)) = word;
-                    }
+                    for (int n = 0; n < TC_NDIG; n++) *reinterpret_cast<uint32_t*>(dst + n * 128 + ((j ^ (n & 7)) << 4)) = rowv[n];
                 }
                 STAMP(15);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -582,7 +583,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                 // ---------- pieces of tiles: accumulator -> digits recombined -> (merge) -> epilogue ----------
                 ctr += (uint32_t)(tp.b1 - tp.b0);
                 // number of pieces this CTA produces: one per tile its run touches
-                const int t_first = (int)(tp.b0 / tp.C), t_last = tp.b1 > tp.b0 ? (int)((tp.b1 - 1) / tp.C) : t_first - 1;
+                const int t_first = (int)((unsigned)tp.b0 / (unsigned)tp.C), t_last = tp.b1 > tp.b0 ? (int)((unsigned)(tp.b1 - 1) / (unsigned)tp.C) : t_first - 1;
                 if (warp < EPI_WARPS) {
                     const float out_scale = Sg;       // x_n = Sg * sum_j 4^-j * (digit_j / 2), and digit/2 is the E2M1 value
                     const int rl = warp * 32 + lane;
