@@ -47,6 +47,8 @@ struct Fused {               // rows of one or more tensors in the dense decode 
 };
 struct Layer {
     float *in_g = nullptr, *post_g = nullptr, *qn_g = nullptr, *kn_g = nullptr;
+    // GPT-2 (arch 0): LayerNorm biases and linear biases; in_g / post_g are the LayerNorm gains, gu holds c_fc
+    float *ln1_b = nullptr, *ln2_b = nullptr, *b_qkv = nullptr, *b_o = nullptr, *b_fc = nullptr, *b_down = nullptr;
     Fused qkv, o, gu, down;
     Committed c[T_PER_LAYER];      // only packed slots used; kept when HX_LOAD_KEEP_COMMITTED
 };
@@ -62,6 +64,7 @@ struct hx_model {
     std::vector<Layer> layers;
     float* emb = nullptr;          // [NV][DM] f32
     float* final_g = nullptr;
+    float *final_b = nullptr, *wpe = nullptr;      // GPT-2: ln_f bias, learned position embedding [max_ctx][DM]
     Fused head; Committed head_c;
     // decode state
     float *x = nullptr, *qkv = nullptr, *q_rot = nullptr, *ctx = nullptr, *h = nullptr, *logits = nullptr;
@@ -375,6 +378,51 @@ struct ProfScope {
 
 // Enqueue one token step on m->st.  from_prompt: the input token is d_prompt[*pos] and no logits are
 // computed (prefill); otherwise the input token is *d_tok and the head + arg-max run.
+// GPT-2 block sequencing (forward_layer_gpt2, helixc/runtime/gpt2_infer.c:1131-1193, with a KV cache): LayerNorm ->
+// fused qkv (+bias) -> attention (scale 1/sqrt(DH), no RoPE, no QK norm) -> proj (+bias, residual) -> LayerNorm ->
+// c_fc (+bias, gelu_new) -> proj (+bias, residual); ln_f and the tied lm_head at the end.  The embedding kernel has
+// already added the learned position row.
+int enqueue_step_gpt2(hx_model* m, bool from_prompt, bool with_head, bool prof) {
+    (void)from_prompt;
+    const hx_config& c = m->cfg;
+    const int DH = c.head_dim, cap = m->kv_cap;
+    const bool pdl = m->pdl && !prof;
+    int rc;
+    for (int L = 0; L < c.n_layers; L++) {
+        Layer& ly = m->layers[L];
+        HxLinear a = lin(ly.qkv, m->x, m->qkv, HX_EPI_STORE);
+        a.norm = HX_NORM_LAYER; a.norm_g = ly.in_g; a.norm_b = ly.ln1_b; a.eps = c.norm_eps; a.bias = ly.b_qkv;
+        { ProfScope ps(m, CAT_GEMV, prof); if ((rc = hx_launch_linear(a, m->st, pdl))) return rc; }
+        HxAttn at = {};
+        at.qkv = m->qkv; at.q_rot = m->q_rot;
+        at.kc = m->kc + (size_t)L * c.n_kv_heads * cap * DH; at.vc = m->vc + (size_t)L * c.n_kv_heads * cap * DH;
+        at.pos = m->d_pos; at.NH = c.n_heads; at.NKV = c.n_kv_heads; at.DH = DH; at.cap = cap;
+        at.eps = c.norm_eps; at.scale = 1.0f / sqrtf((float)DH); at.nsplit = m->nsplit;
+        at.part_m = m->part_m; at.part_l = m->part_l; at.part_acc = m->part_acc; at.counters = m->attn_cnt; at.ctx = m->ctx;
+        { ProfScope ps(m, CAT_OTHER, prof); if ((rc = hx_launch_qk_prep(at, m->st, pdl))) return rc; }
+        { ProfScope ps(m, CAT_ATTN, prof); if ((rc = hx_launch_attn(at, m->st, pdl))) return rc; }
+        HxLinear o = lin(ly.o, m->ctx, m->x, HX_EPI_RESID); o.resid = m->x; o.bias = ly.b_o;
+        { ProfScope ps(m, CAT_GEMV, prof); if ((rc = hx_launch_linear(o, m->st, pdl))) return rc; }
+        HxLinear fc = lin(ly.gu, m->x, m->h, HX_EPI_GELU);
+        fc.norm = HX_NORM_LAYER; fc.norm_g = ly.post_g; fc.norm_b = ly.ln2_b; fc.eps = c.norm_eps; fc.bias = ly.b_fc;
+        { ProfScope ps(m, CAT_GEMV, prof); if ((rc = hx_launch_linear(fc, m->st, pdl))) return rc; }
+        HxLinear dn = lin(ly.down, m->h, m->x, HX_EPI_RESID); dn.resid = m->x; dn.bias = ly.b_down;
+        { ProfScope ps(m, CAT_GEMV, prof); if ((rc = hx_launch_linear(dn, m->st, pdl))) return rc; }
+    }
+    if (with_head) {
+        HxLinear hd = lin(m->head, m->x, m->logits, HX_EPI_ARGMAX);
+        hd.norm = HX_NORM_LAYER; hd.norm_g = m->final_g; hd.norm_b = m->final_b; hd.eps = c.norm_eps;
+        hd.part_val = m->am_val; hd.part_idx = m->am_idx; hd.counter = m->am_cnt; hd.next_tok = m->d_tok; hd.pos_inc = m->d_pos;
+        hd.hist = m->d_hist;
+        { ProfScope ps(m, CAT_GEMV, prof); if ((rc = hx_launch_linear(hd, m->st, pdl))) return rc; }
+    } else {
+        k_advance<<<1, 32, 0, m->st>>>(m->d_pos);
+        HX_COUNT_LAUNCH(1);
+        HX_CUDA(cudaGetLastError());
+    }
+    return HX_OK;
+}
+
 int enqueue_step(hx_model* m, bool from_prompt, bool with_head, bool prof = false) {
     const hx_config& c = m->cfg;
     const int DM = c.d_model, DH = c.head_dim, cap = m->kv_cap;
@@ -384,9 +432,10 @@ int enqueue_step(hx_model* m, bool from_prompt, bool with_head, bool prof = fals
         // the first kernel of a step follows the last kernel of the previous step
         const int* tok = from_prompt ? m->d_prompt : m->d_tok;
         ProfScope ps(m, CAT_OTHER, prof);
-        rc = hx_launch_embed(m->emb, nullptr, tok, m->d_pos, from_prompt ? 1 : 0, m->x, DM, m->st, pdl);
+        rc = hx_launch_embed(m->emb, c.arch == 0 ? m->wpe : nullptr, tok, m->d_pos, from_prompt ? 1 : 0, m->x, DM, m->st, pdl);
         if (rc) return rc;
     }
+    if (c.arch == 0) return enqueue_step_gpt2(m, from_prompt, with_head, prof);
     for (int L = 0; L < c.n_layers; L++) {
         Layer& ly = m->layers[L];
         HxLinear a = lin(ly.qkv, m->x, m->qkv, HX_EPI_STORE);
@@ -693,6 +742,80 @@ HX_API int hx_model_synth(hx_model** out, const hx_config* cfg, uint64_t seed, i
     Source s; s.synth = true; s.seed = seed;
     rc = build(m, s);
     if (!rc) rc = finish_init(m);
+    if (rc) { hx_model_free(m); return rc; }
+    *out = m;
+    return HX_OK;
+}
+
+// ---- GPT-2 (BASELINE config 2) -------------------------------------------------------------------------
+// The reference has no NVFP4 container for GPT-2 (its v3 packer matches Llama/Qwen3 tensor names only), so the
+// weights come as host f32 arrays, every linear as [out][in] (the transpose of the Conv1D storage, so that the
+// 16-element blocks run along K); the library quantizes them with the bit-exact quantizer.
+static int gpt2_upload(hx_model* m, float** dst, const float* src, size_t n) {
+    int rc = dalloc(m, dst, n); if (rc) return rc;
+    HX_CUDA(cudaMemcpyAsync(*dst, src, n * 4, cudaMemcpyHostToDevice, m->st));
+    return HX_OK;
+}
+static int gpt2_linear(hx_model* m, Fused& f, const float* w_host, int N, int K, float* stage, int32_t* wtmp, uint8_t* mtmp, float* tstmp) {
+    int rc = alloc_fused(m, f, N, K); if (rc) return rc;
+    HX_CUDA(cudaMemcpyAsync(stage, w_host, (size_t)N * K * 4, cudaMemcpyHostToDevice, m->st));
+    if ((rc = hx_quantize_nvfp4(stage, N, K, wtmp, mtmp, nullptr, tstmp, m->st))) return rc;
+    Committed c; c.rows = N; c.K = K; c.Kpad = hx_kpad(K); c.words = wtmp; c.micro = mtmp;
+    HX_CUDA(cudaMemcpyAsync(&c.ts, tstmp, 4, cudaMemcpyDeviceToHost, m->st));
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    put_rows(m, c, f, 1, 0);
+    f.ts[0] = f.ts[1] = f.ts[2] = c.ts; f.bound0 = f.bound1 = N;
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    return HX_OK;
+}
+
+HX_API int hx_model_gpt2(hx_model** out, const hx_config* cfg, const hx_gpt2_weights* w, int kv_cap) {
+    HX_CHECK_ARG(out && cfg && w && w->wte && w->wpe && w->lnf_g && w->lnf_b && w->layers);
+    const hx_config& c = *cfg;
+    if (c.arch != 0) return hx_fail(HX_ERR_ARG, "hx_model_gpt2 builds arch 0 (GPT-2), got %d", c.arch);
+    if (c.n_layers <= 0 || c.d_model <= 0 || c.n_heads <= 0 || c.d_ff <= 0 || c.vocab <= 0 || c.max_ctx <= 0)
+        return hx_fail(HX_ERR_ARG, "non-positive model dimension");
+    if (c.d_model % c.n_heads || c.head_dim != c.d_model / c.n_heads || c.n_kv_heads != c.n_heads)
+        return hx_fail(HX_ERR_ARG, "GPT-2: head_dim must be d_model / n_heads and n_kv_heads == n_heads");
+    if (c.head_dim % 32 || c.head_dim > 256 || c.d_model % 4 || c.d_ff % 4) return hx_fail(HX_ERR_ARG, "GPT-2: head_dim multiple of 32 (<= 256), widths multiples of 4");
+    if (kv_cap <= 0 || kv_cap > c.max_ctx) return hx_fail(HX_ERR_ARG, "kv_cap %d outside 1..max_ctx %d", kv_cap, c.max_ctx);
+    hx_model* m = new hx_model();
+    m->cfg = c; m->gcfg = c; m->cfg.qk_norm = 0; m->QD = c.d_model; m->KVD = c.d_model;
+    m->kv_cap = kv_cap; m->batch = 1; m->flags = 0;
+    m->persist = false; m->use_tc = false; m->want_t128 = false; m->pf_batched = false;     // per-op kernels in one CUDA graph
+    int rc = HX_OK;
+    float* stage = nullptr; int32_t* wtmp = nullptr; uint8_t* mtmp = nullptr; float* tstmp = nullptr;
+    do {
+        cudaError_t e = cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking);
+        if (e != cudaSuccess) { rc = hx_fail(HX_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); break; }
+        const int DM = c.d_model, DFF = c.d_ff, NV = c.vocab;
+        size_t maxel = (size_t)NV * DM; if ((size_t)3 * DM * DM > maxel) maxel = (size_t)3 * DM * DM; if ((size_t)DFF * DM > maxel) maxel = (size_t)DFF * DM;
+        const int kp = hx_kpad(DM > DFF ? DM : DFF);
+        size_t maxrows = (size_t)NV; if ((size_t)3 * DM > maxrows) maxrows = 3 * DM; if ((size_t)DFF > maxrows) maxrows = DFF;
+        if (cudaMalloc(&stage, maxel * 4) != cudaSuccess || cudaMalloc(&wtmp, maxrows * (kp / 7) * 4) != cudaSuccess ||
+            cudaMalloc(&mtmp, maxrows * (kp / 16)) != cudaSuccess || cudaMalloc(&tstmp, 256) != cudaSuccess) { rc = hx_fail(HX_ERR_NOMEM, "GPT-2 staging"); break; }
+        m->layers.resize(c.n_layers);
+        for (int L = 0; L < c.n_layers && !rc; L++) {
+            Layer& ly = m->layers[L]; const hx_gpt2_layer& hl = w->layers[L];
+            if (!hl.ln1_g || !hl.ln1_b || !hl.w_qkv || !hl.b_qkv || !hl.w_proj || !hl.b_proj || !hl.ln2_g || !hl.ln2_b || !hl.w_fc || !hl.b_fc || !hl.w_proj2 || !hl.b_proj2) {
+                rc = hx_fail(HX_ERR_ARG, "GPT-2 layer %d: null tensor", L); break; }
+            if ((rc = gpt2_upload(m, &ly.in_g, hl.ln1_g, DM)) || (rc = gpt2_upload(m, &ly.ln1_b, hl.ln1_b, DM)) ||
+                (rc = gpt2_upload(m, &ly.post_g, hl.ln2_g, DM)) || (rc = gpt2_upload(m, &ly.ln2_b, hl.ln2_b, DM)) ||
+                (rc = gpt2_upload(m, &ly.b_qkv, hl.b_qkv, (size_t)3 * DM)) || (rc = gpt2_upload(m, &ly.b_o, hl.b_proj, DM)) ||
+                (rc = gpt2_upload(m, &ly.b_fc, hl.b_fc, DFF)) || (rc = gpt2_upload(m, &ly.b_down, hl.b_proj2, DM))) break;
+            if ((rc = gpt2_linear(m, ly.qkv, hl.w_qkv, 3 * DM, DM, stage, wtmp, mtmp, tstmp))) break;
+            if ((rc = gpt2_linear(m, ly.o, hl.w_proj, DM, DM, stage, wtmp, mtmp, tstmp))) break;
+            if ((rc = gpt2_linear(m, ly.gu, hl.w_fc, DFF, DM, stage, wtmp, mtmp, tstmp))) break;
+            if ((rc = gpt2_linear(m, ly.down, hl.w_proj2, DM, DFF, stage, wtmp, mtmp, tstmp))) break;
+        }
+        if (rc) break;
+        if ((rc = gpt2_upload(m, &m->emb, w->wte, (size_t)NV * DM)) || (rc = gpt2_upload(m, &m->wpe, w->wpe, (size_t)c.max_ctx * DM)) ||
+            (rc = gpt2_upload(m, &m->final_g, w->lnf_g, DM)) || (rc = gpt2_upload(m, &m->final_b, w->lnf_b, DM))) break;
+        if ((rc = gpt2_linear(m, m->head, w->wte, NV, DM, stage, wtmp, mtmp, tstmp))) break;       // tied lm_head
+        HX_CUDA(cudaStreamSynchronize(m->st));
+        rc = finish_init(m);
+    } while (0);
+    cudaFree(stage); cudaFree(wtmp); cudaFree(mtmp); cudaFree(tstmp);
     if (rc) { hx_model_free(m); return rc; }
     *out = m;
     return HX_OK;

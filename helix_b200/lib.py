@@ -45,6 +45,18 @@ def _cfg(n_layers, d_model, n_heads, n_kv_heads, head_dim, d_ff, vocab, max_ctx=
 QWEN3_8B = dict(n_layers=36, d_model=4096, n_heads=32, n_kv_heads=8, head_dim=128, d_ff=12288, vocab=151936)
 QWEN3_32B = dict(n_layers=64, d_model=5120, n_heads=64, n_kv_heads=8, head_dim=128, d_ff=25600, vocab=151936)
 
+GPT2_124M = dict(n_layers=12, d_model=768, n_heads=12, d_ff=3072, vocab=50257, max_ctx=1024)
+_GPT2_LAYER_FIELDS = ("ln1_g", "ln1_b", "w_qkv", "b_qkv", "w_proj", "b_proj", "ln2_g", "ln2_b", "w_fc", "b_fc", "w_proj2", "b_proj2")
+
+
+class HxGpt2Layer(C.Structure):
+    _fields_ = [(k, C.c_void_p) for k in _GPT2_LAYER_FIELDS]
+
+
+class HxGpt2Weights(C.Structure):
+    _fields_ = [("wte", C.c_void_p), ("wpe", C.c_void_p), ("lnf_g", C.c_void_p), ("lnf_b", C.c_void_p), ("layers", C.POINTER(HxGpt2Layer))]
+
+
 HX_LOAD_KEEP_COMMITTED = 1
 HX_LOAD_VERIFY_SHA = 2
 HX_LOAD_FILE_EPS = 4
@@ -103,6 +115,7 @@ _SIGS = {
     "hx_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "hx_model_last_stats": (C.c_int, [C.c_void_p, C.POINTER(HxStepStats)]),
     "hx_model_engine": (C.c_char_p, [C.c_void_p]),
+    "hx_model_gpt2": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(HxConfig), C.POINTER(HxGpt2Weights), C.c_int]),
     "hx_decode_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "hx_decode_batch_loop": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float)]),
     "hx_model_tp_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
@@ -266,6 +279,27 @@ class Model:
         ms = C.c_float()
         check(lib().hx_decode_batch_loop(self.h, ids.ctypes.data, pos0, len(ids), n_steps, out.ctypes.data, C.byref(ms)))
         return out, ms.value
+
+    @classmethod
+    def gpt2(cls, shape, weights, kv_cap=256):
+        """shape: n_layers, d_model, n_heads, d_ff, vocab, max_ctx.  weights: dict with wte, wpe, lnf_g, lnf_b and
+        layers = list of dicts with the twelve per-layer tensors, all float32, linears as [out][in]."""
+        cfg = HxConfig(0, shape["n_layers"], shape["d_model"], shape["n_heads"], shape["n_heads"],
+                       shape["d_model"] // shape["n_heads"], shape["d_ff"], shape["vocab"], shape["max_ctx"], 0.0, 1e-5, 0)
+        keep = []
+
+        def ptr(a):
+            a = np.ascontiguousarray(a, np.float32); keep.append(a)
+            return a.ctypes.data
+
+        lay = (HxGpt2Layer * shape["n_layers"])()
+        for i, lw in enumerate(weights["layers"]):
+            for k in _GPT2_LAYER_FIELDS:
+                setattr(lay[i], k, ptr(lw[k]))
+        hw = HxGpt2Weights(ptr(weights["wte"]), ptr(weights["wpe"]), ptr(weights["lnf_g"]), ptr(weights["lnf_b"]), lay)
+        h = C.c_void_p()
+        check(lib().hx_model_gpt2(C.byref(h), C.byref(cfg), C.byref(hw), kv_cap))
+        return cls(h)
 
     def tp_handle(self):
         """64-byte handle of this shard's exchange buffer (to be gathered from all ranks)."""

@@ -183,6 +183,19 @@ int hx_model_load(hx_model** out, const char* path, int kv_cap, int batch, int f
 int hx_model_synth(hx_model** out, const hx_config* cfg, uint64_t seed, int kv_cap, int batch,
                    int flags, int tp_rank, int tp_size);
 
+/* GPT-2 (BASELINE config 2): LayerNorm, learned positions, fused qkv with biases, gelu_new MLP, tied lm_head.
+ * Host f32 tensors, every linear as [out][in] (transpose of the Conv1D storage); the library quantizes all linears
+ * and the lm_head copy of wte to NVFP4 with the bit-exact quantizer.  cfg: arch 0, n_kv_heads = n_heads,
+ * head_dim = d_model / n_heads, max_ctx = rows of wpe, norm_eps 1e-5.  Decodes with a KV cache through
+ * hx_prefill / hx_decode_step / hx_generate_greedy (the reference re-forwards the whole context every token,
+ * forward_layer_gpt2, gpt2_infer.c:1131-1193; it has no NVFP4 GPT-2 path). */
+typedef struct {
+    const float *ln1_g, *ln1_b, *w_qkv /*[3*DM][DM]*/, *b_qkv, *w_proj /*[DM][DM]*/, *b_proj,
+                *ln2_g, *ln2_b, *w_fc /*[DFF][DM]*/, *b_fc, *w_proj2 /*[DM][DFF]*/, *b_proj2;
+} hx_gpt2_layer;
+typedef struct { const float *wte /*[NV][DM]*/, *wpe /*[max_ctx][DM]*/, *lnf_g, *lnf_b; const hx_gpt2_layer* layers; } hx_gpt2_weights;
+int hx_model_gpt2(hx_model** out, const hx_config* cfg, const hx_gpt2_weights* w, int kv_cap);
+
 int hx_model_free(hx_model* m);
 int hx_model_config(const hx_model* m, hx_config* cfg);
 /* Bytes of weights read per decoded token in the decode layout (this rank's shard). */

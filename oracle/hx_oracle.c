@@ -677,3 +677,50 @@ ORC_API int orc_num_threads(void) {
     return 1;
 #endif
 }
+
+/* ---------------------------------------------------------------------------------------------------
+ * GPT-2 block with a KV cache (BASELINE config 2).  Restates forward_layer_gpt2, gpt2_infer.c:1131-1193
+ * (LayerNorm -> fused qkv + bias -> per-head softmax(q k^T * 1/sqrt(DH)) v -> proj + bias + residual ->
+ * LayerNorm -> c_fc + bias -> gelu_new -> proj + bias + residual), embed_gather :1201-1223 (wte row + wpe
+ * row), ln_f and the tied head.  The reference re-forwards the whole context every token; with causal
+ * attention that equals one position at a time over cached k and v, which is what is done here.
+ * Weights arrive as f32 (already dequantized by the caller), every linear [out][in]:
+ *   t[0..4] = wte, wpe, lnf_g, lnf_b, head_w; per layer 12 more: ln1_g ln1_b w_qkv b_qkv w_proj b_proj
+ *   ln2_g ln2_b w_fc b_fc w_proj2 b_proj2.  dims = NL DM NH DFF NV.  kc, vc: [NL][NH][cap][DH], caller-owned. */
+ORC_API int orc_gpt2_decode(const int* dims, const float* const* t, float* kc, float* vc, int cap, int tok, int pos, float* logits) {
+    const int NL = dims[0], DM = dims[1], NH = dims[2], DFF = dims[3], NV = dims[4], DH = DM / NH;
+    if (pos < 0 || pos >= cap || tok < 0 || tok >= NV) return 1;
+    float* x = (float*)malloc((size_t)DM * 4); float* h = (float*)malloc((size_t)DM * 4);
+    float* qkv = (float*)malloc((size_t)3 * DM * 4); float* ctx = (float*)malloc((size_t)DM * 4);
+    float* f = (float*)malloc((size_t)DFF * 4); float* g = (float*)malloc((size_t)DFF * 4); float* y = (float*)malloc((size_t)DM * 4);
+    float* sc = (float*)malloc((size_t)(pos + 1) * 4); float* pr = (float*)malloc((size_t)(pos + 1) * 4);
+    const float scale = 1.0f / sqrtf((float)DH);
+    for (int j = 0; j < DM; j++) x[j] = t[0][(long)tok * DM + j] + t[1][(long)pos * DM + j];
+    for (int L = 0; L < NL; L++) {
+        const float* const* w = t + 5 + 12 * L;
+        orc_layernorm(x, h, w[0], w[1], 1, DM, 1e-5f);
+        orc_gemv_abt(h, w[2], qkv, 3 * DM, DM);
+        for (int j = 0; j < 3 * DM; j++) qkv[j] = qkv[j] + w[3][j];
+        for (int hh = 0; hh < NH; hh++) {
+            float* kr = kc + (((long)L * NH + hh) * cap + pos) * DH; float* vr = vc + (((long)L * NH + hh) * cap + pos) * DH;
+            for (int d = 0; d < DH; d++) { kr[d] = qkv[DM + hh * DH + d]; vr[d] = qkv[2 * DM + hh * DH + d]; }
+            const float* q = qkv + hh * DH;
+            const float* kb = kc + ((long)L * NH + hh) * cap * DH; const float* vb = vc + ((long)L * NH + hh) * cap * DH;
+            for (int s = 0; s <= pos; s++) { float a = 0.0f; for (int d = 0; d < DH; d++) a = fmaf(q[d], kb[(long)s * DH + d], a); sc[s] = a * scale; }
+            orc_softmax_row(sc, pr, 1, pos + 1);
+            for (int d = 0; d < DH; d++) { float a = 0.0f; for (int s = 0; s <= pos; s++) a = fmaf(pr[s], vb[(long)s * DH + d], a); ctx[hh * DH + d] = a; }
+        }
+        orc_gemv_abt(ctx, w[4], y, DM, DM);
+        for (int j = 0; j < DM; j++) x[j] = x[j] + (y[j] + w[5][j]);
+        orc_layernorm(x, h, w[6], w[7], 1, DM, 1e-5f);
+        orc_gemv_abt(h, w[8], f, DFF, DM);
+        for (int j = 0; j < DFF; j++) f[j] = f[j] + w[9][j];
+        orc_gelu(f, g, DFF);
+        orc_gemv_abt(g, w[10], y, DM, DFF);
+        for (int j = 0; j < DM; j++) x[j] = x[j] + (y[j] + w[11][j]);
+    }
+    orc_layernorm(x, h, t[2], t[3], 1, DM, 1e-5f);
+    orc_gemv_abt(h, t[4], logits, NV, DM);
+    free(x); free(h); free(qkv); free(ctx); free(f); free(g); free(y); free(sc); free(pr);
+    return 0;
+}
