@@ -375,6 +375,26 @@ def run_ours(args):
                    "tok_per_s": args.gpus * BATCH_PROBE * 8 / (bms * 1e-3),
                    "path": "hx_decode_batch_loop: chunks of 16 sequences per tcgen05 GEMM, per-sequence KV append and attention"}
 
+    # config 2: GPT-2-124M shape, all linears NVFP4, 32-token prompt + 128 greedy tokens, batch 1
+    gpt2 = None
+    if rank == 0 and not args.no_e2e and not tp:
+        gs = dict(hb.GPT2_124M)
+        grng = np.random.default_rng(5)
+        gn = lambda *sh: grng.standard_normal(sh, dtype=np.float32) * np.float32(0.02)
+        one = lambda k: np.ones(k, np.float32)
+        DMg, DFg = gs["d_model"], gs["d_ff"]
+        gw = dict(wte=gn(gs["vocab"], DMg), wpe=gn(gs["max_ctx"], DMg), lnf_g=one(DMg), lnf_b=np.zeros(DMg, np.float32),
+                  layers=[dict(ln1_g=one(DMg), ln1_b=np.zeros(DMg, np.float32), w_qkv=gn(3 * DMg, DMg), b_qkv=gn(3 * DMg),
+                               w_proj=gn(DMg, DMg), b_proj=gn(DMg), ln2_g=one(DMg), ln2_b=np.zeros(DMg, np.float32),
+                               w_fc=gn(DFg, DMg), b_fc=gn(DFg), w_proj2=gn(DMg, DFg), b_proj2=gn(DMg)) for _ in range(gs["n_layers"])])
+        g2 = hb.Model.gpt2(gs, gw, kv_cap=192)
+        gp = grng.integers(0, gs["vocab"], 32).astype(np.int32)
+        g2.generate(gp, 16)
+        _, gms_p, gms_d = g2.generate(gp, 128)
+        gpt2 = {"shape": "gpt2-124m", "prompt": 32, "new_tokens": 128, "decode_tok_per_s": 127 / (gms_d * 1e-3), "prefill_ms": gms_p,
+                "engine": g2.engine(), "note": "per-op kernels in one CUDA graph per token (LayerNorm/bias/GELU fused into the NVFP4 GEMV)"}
+        g2.close(); del gw
+
     cpu = None
     if rank == 0 and args.gpus == 1 and not args.no_cpu_baseline:      # reported at N = 1 only
         image = model.v3_image()                       # the same weights, HXGW v3 bytes exported from HBM
@@ -396,7 +416,7 @@ def run_ours(args):
                            "l2": "weights (4.26 GB per token) exceed the 126 MB L2, no flush needed",
                            "tokens_per_step": NEW_TOKENS, "weight_bytes_decode_layout": dbytes, "weight_bytes_committed_layout": cbytes},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-                "quantizer": quant, "batched_decode": batched,
+                "quantizer": quant, "batched_decode": batched, "gpt2": gpt2,
                 "prefill": {"tokens": PROMPT_LEN, "ms": prefill_s * 1e3, "tok_per_s": PROMPT_LEN / prefill_s,
                             "path": "chunks of 16 tokens, one tcgen05 block-scaled GEMM per linear (exact digit columns), host ids in"},
                 "ms_per_token": ms_max / args.steps / NEW_TOKENS, "last_tokens": [int(t) for t in toks[-4:]]}
