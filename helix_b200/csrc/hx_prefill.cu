@@ -123,32 +123,36 @@ __global__ void __launch_bounds__(256) k_pf_qkpost(float* __restrict__ qkv, int 
     }
 }
 
-// grid (NKV, n_tok), 128 threads.  Online softmax over tiles of PF_KT cached positions (m seeded -1e8 like
-// fused_decode_attn_kernel.hx:74-102), so shared memory does not grow with the context.
-#define PF_KT 64
+// grid (NKV, n_tok), PF_AT threads.  Online softmax over tiles of PF_KT cached positions (m seeded -1e8 like
+// fused_decode_attn_kernel.hx:74-102), so shared memory does not grow with the context.  Scores: a warp per key;
+// P*V: thread (dimension, key subset), the subsets are added up through shared memory at the end.
+#define PF_KT 128
+#define PF_AT 512
 template <int GRP>
-__global__ void __launch_bounds__(128) k_pf_attn(const float* __restrict__ qkv, int ld, HxPfWhere wh, int NH, int DH,
-                                                  const float* __restrict__ kc, const float* __restrict__ vc, int cap, float scale,
-                                                  float* __restrict__ ctx, int ld_ctx) {
+__global__ void __launch_bounds__(PF_AT) k_pf_attn(const float* __restrict__ qkv, int ld, HxPfWhere wh, int NH, int DH,
+                                                    const float* __restrict__ kc, const float* __restrict__ vc, int cap, float scale,
+                                                    float* __restrict__ ctx, int ld_ctx) {
     extern __shared__ float smf[];
     const int kvh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int NW = PF_AT / 32;
     const int T = (wh.pos_arr ? wh.pos_arr[t] : *wh.posp + t) + 1;
     const size_t seq_off = wh.seq_arr ? (size_t)wh.seq_arr[t] * wh.seq_stride : 0;
     float* sq = smf;                   // [GRP][DH]
     float* sp = smf + GRP * DH;        // [GRP][PF_KT]
+    float* sacc = sp + GRP * PF_KT;    // [nsub][GRP][DH] partial outputs of the key subsets
     __shared__ float sm_m[GRP], sm_l[GRP], sm_r[GRP];
-    for (int i = tid; i < GRP * DH; i += 128) sq[i] = qkv[(size_t)t * ld + (size_t)kvh * GRP * DH + i];
+    for (int i = tid; i < GRP * DH; i += PF_AT) sq[i] = qkv[(size_t)t * ld + (size_t)kvh * GRP * DH + i];
     if (tid < GRP) { sm_m[tid] = -100000000.0f; sm_l[tid] = 0.0f; }
     __syncthreads();
     const float* kbase = kc + seq_off + (size_t)kvh * cap * DH;
     const float* vbase = vc + seq_off + (size_t)kvh * cap * DH;
-    float acc[GRP][2];                 // output dimensions tid and tid + 128
+    const int nsub = PF_AT / DH, d = tid % DH, ksub = tid / DH;      // DH divides PF_AT (32, 64, 128, 256)
+    float acc[GRP];
 #pragma unroll
-    for (int i = 0; i < GRP; i++) acc[i][0] = acc[i][1] = 0.0f;
+    for (int i = 0; i < GRP; i++) acc[i] = 0.0f;
     for (int j0 = 0; j0 < T; j0 += PF_KT) {
         const int nj = min(PF_KT, T - j0);
-        // scores: a warp per key, lanes over the head dimension
-        for (int j = warp; j < nj; j += 4) {
+        for (int j = warp; j < nj; j += NW) {
             float dot[GRP];
 #pragma unroll
             for (int i = 0; i < GRP; i++) dot[i] = 0.0f;
@@ -165,7 +169,7 @@ __global__ void __launch_bounds__(128) k_pf_attn(const float* __restrict__ qkv, 
             for (int i = 0; i < GRP; i++) { const float sv = hx_warp_sum(dot[i]); if (lane == 0) sp[i * PF_KT + j] = sv * scale; }
         }
         __syncthreads();
-        for (int i = warp; i < GRP; i += 4) {
+        for (int i = warp; i < GRP; i += NW) {
             float tm = -INFINITY;
             for (int j = lane; j < nj; j += 32) tm = fmaxf(tm, sp[i * PF_KT + j]);
             tm = hx_warp_max(tm);
@@ -176,28 +180,28 @@ __global__ void __launch_bounds__(128) k_pf_attn(const float* __restrict__ qkv, 
             if (lane == 0) { const float rr = __expf(mo - mn); sm_r[i] = rr; sm_l[i] = sm_l[i] * rr + ls; sm_m[i] = mn; }
         }
         __syncthreads();
+        if (ksub < nsub) {
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int d = tid + h * 128;
-            if (d < DH) {
+            for (int i = 0; i < GRP; i++) acc[i] *= sm_r[i];
+            #pragma unroll 4
+            for (int j = ksub; j < nj; j += nsub) {
+                const float vv = vbase[(size_t)(j0 + j) * DH + d];
 #pragma unroll
-                for (int i = 0; i < GRP; i++) acc[i][h] *= sm_r[i];
-                for (int j = 0; j < nj; j++) {
-                    const float vv = vbase[(size_t)(j0 + j) * DH + d];
-#pragma unroll
-                    for (int i = 0; i < GRP; i++) acc[i][h] = fmaf(sp[i * PF_KT + j], vv, acc[i][h]);
-                }
+                for (int i = 0; i < GRP; i++) acc[i] = fmaf(sp[i * PF_KT + j], vv, acc[i]);
             }
         }
         __syncthreads();
     }
+    if (ksub < nsub) {
 #pragma unroll
-    for (int h = 0; h < 2; h++) {
-        const int d = tid + h * 128;
-        if (d < DH) {
-#pragma unroll
-            for (int i = 0; i < GRP; i++) ctx[(size_t)t * ld_ctx + (size_t)(kvh * GRP + i) * DH + d] = acc[i][h] / sm_l[i];
-        }
+        for (int i = 0; i < GRP; i++) sacc[((size_t)ksub * GRP + i) * DH + d] = acc[i];
+    }
+    __syncthreads();
+    for (int o = tid; o < GRP * DH; o += PF_AT) {
+        const int i = o / DH, dd = o - i * DH;
+        float v = 0.0f;
+        for (int u = 0; u < nsub; u++) v += sacc[((size_t)u * GRP + i) * DH + dd];
+        ctx[(size_t)t * ld_ctx + (size_t)(kvh * GRP + i) * DH + dd] = v / sm_l[i];
     }
 }
 
@@ -264,9 +268,11 @@ int hx_pf_attn(const float* qkv, int ld, int n_tok, HxPfWhere wh, int NH, int NK
                int cap, float scale, float* ctx, int ld_ctx, cudaStream_t st) {
     const int GRP = NH / NKV;
     if (DH > 256) return hx_fail(HX_ERR_ARG, "batched prefill attention: head_dim %d > 256", DH);
-    const size_t smem = ((size_t)GRP * DH + (size_t)GRP * PF_KT) * 4;
+    if (PF_AT % DH) return hx_fail(HX_ERR_ARG, "batched prefill attention: head_dim %d does not divide %d", DH, PF_AT);
+    const size_t smem = ((size_t)GRP * DH + (size_t)GRP * PF_KT + (size_t)(PF_AT / DH) * GRP * DH) * 4;
+    if (smem > 48 * 1024) return hx_fail(HX_ERR_ARG, "batched prefill attention: %zu bytes of shared memory", smem);
     dim3 grid(NKV, n_tok);
-#define HX_PF_ATTN(G) case G: k_pf_attn<G><<<grid, 128, smem, st>>>(qkv, ld, wh, NH, DH, kc, vc, cap, scale, ctx, ld_ctx); break;
+#define HX_PF_ATTN(G) case G: k_pf_attn<G><<<grid, PF_AT, smem, st>>>(qkv, ld, wh, NH, DH, kc, vc, cap, scale, ctx, ld_ctx); break;
     switch (GRP) {
         HX_PF_ATTN(1) HX_PF_ATTN(2) HX_PF_ATTN(3) HX_PF_ATTN(4) HX_PF_ATTN(5) HX_PF_ATTN(6) HX_PF_ATTN(7) HX_PF_ATTN(8)
         default: return hx_fail(HX_ERR_ARG, "batched prefill attention: group of %d query heads per kv head not supported", GRP);
