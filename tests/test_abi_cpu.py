@@ -160,3 +160,22 @@ def test_bad_files_are_rejected_before_any_device_work(tmp_path, tiny_file):
                       ("short", lambda d: d[:40])]:
         p = str(tmp_path / name); open(p, "wb").write(bytes(mut(data)))
         assert L.hx_model_load(C.byref(h), p.encode(), 16, 1, 0, 0, 1) == 4, name       # HX_ERR_FORMAT
+
+
+def test_argument_checks_of_the_wider_entry_points_need_no_device(tiny_file):
+    """Shape and range checks come before any CUDA call: tensor-parallel shards, batch, GPT-2, no-alloc quantizer."""
+    L = hb.lib()
+    h = C.c_void_p()
+    # TINY has 4 heads / 2 kv heads: a group of 3 ranks does not divide them, rank outside the group is refused
+    assert L.hx_model_load(C.byref(h), tiny_file.encode(), 16, 1, 0, 0, 3) == 1           # HX_ERR_ARG
+    assert b"divisible" in L.hx_last_error()
+    assert L.hx_model_load(C.byref(h), tiny_file.encode(), 16, 1, 0, 2, 2) == 1
+    assert L.hx_model_load(C.byref(h), tiny_file.encode(), 16, 0, 0, 0, 1) == 1           # batch 0
+    assert L.hx_model_load(C.byref(h), tiny_file.encode(), 16, 4, 0, 0, 2) == 1           # batch and TP together
+    from helix_b200.lib import HxConfig, HxGpt2Weights
+    cfg = HxConfig(1, 2, 128, 4, 4, 32, 512, 300, 64, 0.0, 1e-5, 0)                       # arch 1 is not GPT-2
+    one = (C.c_float * 4)()
+    w = HxGpt2Weights(C.addressof(one), C.addressof(one), C.addressof(one), C.addressof(one), None)
+    assert L.hx_model_gpt2(C.byref(h), C.byref(cfg), C.byref(w), 16) == 1                 # null layer table
+    assert L.hx_quantize_nvfp4_noalloc(C.addressof(one), L.hx_noalloc_max_rows() + 1, 16, C.addressof(one), None, None, None, None) == 1
+    assert L.hx_decode_batch(None, None, None, 1, None) == 1
