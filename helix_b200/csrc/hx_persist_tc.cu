@@ -179,10 +179,12 @@ __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) { asm vo
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) { unsigned v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
 // Every rank writes `ep` into slot `rank` of each peer's flag array, then waits (bounded) until all peers have written
 // theirs here.  Epochs only grow, so a late reader still sees a value >= ep.  One thread per GPU calls this.
-__device__ __forceinline__ bool tp_handshake(const HxPersist& P, size_t flags_off, unsigned ep, volatile int* abort_flag) {
+__device__ __forceinline__ void tp_signal(const HxPersist& P, size_t flags_off, unsigned ep) {
     asm volatile("fence.acq_rel.sys;" ::: "memory");
     for (int w = 0; w < P.tp_world; w++)
         if (w != P.tp_rank) st_release_sys(reinterpret_cast<unsigned*>(P.tp_peer[w] + flags_off) + P.tp_rank, ep);
+}
+__device__ __forceinline__ bool tp_wait(const HxPersist& P, size_t flags_off, unsigned ep, volatile int* abort_flag) {
     const unsigned* mine = reinterpret_cast<const unsigned*>(P.tp_peer[P.tp_rank] + flags_off);
     for (int w = 0; w < P.tp_world; w++) {
         if (w == P.tp_rank) continue;
@@ -194,6 +196,10 @@ __device__ __forceinline__ bool tp_handshake(const HxPersist& P, size_t flags_of
         if (!ok) return false;
     }
     return true;
+}
+__device__ __forceinline__ bool tp_handshake(const HxPersist& P, size_t flags_off, unsigned ep, volatile int* abort_flag) {
+    tp_signal(P, flags_off, ep);
+    return tp_wait(P, flags_off, ep, abort_flag);
 }
 
 struct SmemTc {
@@ -794,23 +800,11 @@ __global__ void __launch_bounds__(PT, 1) k_decode_tc(const __grid_constant__ HxP
                     }
                     if (!ok) S.abort_flag = 1;
                     if (TP && ok && ph.tp_barrier) {
-                        // all CTAs of this GPU have arrived; CTA 0 meets the other GPUs, then lets the local CTAs go
+                        // all CTAs of this GPU have arrived: CTA 0 tells the other GPUs, and every CTA waits until each peer
+                        // has said the same (the peers' flags land in local memory, so the wait costs one NVLink crossing)
                         const unsigned ep = P.tp_epoch_base + (unsigned)ph.tp_epoch;
-                        unsigned* go = reinterpret_cast<unsigned*>(P.tp_peer[P.tp_rank] + tp_off_go(P));
-                        if (cta == 0) {
-                            if (!tp_handshake(P, tp_off_flags(P), ep, &S.abort_flag)) S.abort_flag = 1;
-                            asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(go), "r"(S.abort_flag ? 0xFFFFFFFFu : ep) : "memory");
-                        } else {
-                            bool ok2 = false;
-                            for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-                                unsigned v;
-                                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(go) : "memory");
-                                if (v == 0xFFFFFFFFu) break;                       // CTA 0 gave up
-                                if ((int)(v - ep) >= 0) { ok2 = true; break; }
-                                if ((i & 255) == 255 && S.abort_flag) break;
-                            }
-                            if (!ok2) S.abort_flag = 1;
-                        }
+                        if (cta == 0) tp_signal(P, tp_off_flags(P), ep);
+                        if (!tp_wait(P, tp_off_flags(P), ep, &S.abort_flag)) S.abort_flag = 1;
                     }
                 }
                 asm volatile("cp.async.wait_all;" ::: "memory");
