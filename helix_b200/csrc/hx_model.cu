@@ -582,6 +582,7 @@ int init_persist(hx_model* m) {
     m->grid_persist = sms;
     m->nsplit_persist = sms / m->cfg.n_kv_heads; if (m->nsplit_persist < 1) m->nsplit_persist = 1;
     if (m->nsplit_persist > m->nsplit) m->nsplit_persist = m->nsplit;      // scratch is sized for nsplit
+    if (const char* e = getenv("HX_ATT_SPLIT")) { const int v = atoi(e); if (v >= 1 && v <= m->nsplit_persist) m->nsplit_persist = v; }
     if (256 % m->cfg.head_dim) return hx_fail(HX_ERR_ARG, "persistent decode needs head_dim dividing 256");
     int rc;
     if (m->tp_world > 1) {
