@@ -748,7 +748,7 @@ HX_API int hx_model_synth(hx_model** out, const hx_config* cfg, uint64_t seed, i
     return HX_OK;
 }
 
-// ---- GPT-2 (BASELINE config 2) -------------------------------------------------------------------------
+// ---- GPT-2 (12 layers, d 768: the GPT-2-124M configuration) ---------------------------------------------
 // The reference has no NVFP4 container for GPT-2 (its v3 packer matches Llama/Qwen3 tensor names only), so the
 // weights come as host f32 arrays, every linear as [out][in] (the transpose of the Conv1D storage, so that the
 // 16-element blocks run along K); the library quantizes them with the bit-exact quantizer.
@@ -1377,7 +1377,35 @@ HX_API int hx_model_fill_kv(hx_model* m, int T, uint64_t seed) {
     return HX_OK;
 }
 
-// ---- BASELINE config 1: quantize W, then y = dequant(W) x, host buffers in and out ---------------------
+// Copy n cached positions [pos0, pos0 + n) of one (sequence, layer, kv head) between the cache and host arrays
+// of n * head_dim floats (K after QK-norm and RoPE, as the reference caches it).
+static int kv_span(hx_model* m, int seq, int layer, int kv_head, int pos0, int n, size_t* off) {
+    const hx_config& c = m->cfg;
+    if (seq < 0 || seq >= m->batch || layer < 0 || layer >= c.n_layers || kv_head < 0 || kv_head >= c.n_kv_heads)
+        return hx_fail(HX_ERR_ARG, "kv rows: sequence %d, layer %d, kv head %d outside the model", seq, layer, kv_head);
+    if (pos0 < 0 || n < 0 || pos0 + n > m->kv_cap) return hx_fail(HX_ERR_STATE, "kv rows %d..%d outside the KV capacity %d", pos0, pos0 + n, m->kv_cap);
+    const size_t seq_stride = (size_t)c.n_layers * c.n_kv_heads * m->kv_cap * c.head_dim;
+    *off = seq * seq_stride + (((size_t)layer * c.n_kv_heads + kv_head) * m->kv_cap + pos0) * c.head_dim;
+    return HX_OK;
+}
+HX_API int hx_model_kv_read(hx_model* m, int seq, int layer, int kv_head, int pos0, int n, float* k, float* v) {
+    HX_CHECK_ARG(m && k && v);
+    size_t off = 0; int rc = kv_span(m, seq, layer, kv_head, pos0, n, &off); if (rc) return rc;
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    HX_CUDA(cudaMemcpy(k, m->kc + off, (size_t)n * m->cfg.head_dim * 4, cudaMemcpyDeviceToHost));
+    HX_CUDA(cudaMemcpy(v, m->vc + off, (size_t)n * m->cfg.head_dim * 4, cudaMemcpyDeviceToHost));
+    return HX_OK;
+}
+HX_API int hx_model_kv_write(hx_model* m, int seq, int layer, int kv_head, int pos0, int n, const float* k, const float* v) {
+    HX_CHECK_ARG(m && k && v);
+    size_t off = 0; int rc = kv_span(m, seq, layer, kv_head, pos0, n, &off); if (rc) return rc;
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    HX_CUDA(cudaMemcpy(m->kc + off, k, (size_t)n * m->cfg.head_dim * 4, cudaMemcpyHostToDevice));
+    HX_CUDA(cudaMemcpy(m->vc + off, v, (size_t)n * m->cfg.head_dim * 4, cudaMemcpyHostToDevice));
+    return HX_OK;
+}
+
+// ---- single-matrix round trip: quantize W, then y = dequant(W) x, host buffers in and out ---------------
 HX_API int hx_roundtrip_host(const float* w, int rows, int K, const float* x, float* y, int* kpad_out) {
     HX_CHECK_ARG(w && x && y && rows > 0 && K > 0 && K % 4 == 0);
     const int Kpad = hx_kpad(K), Kd = hx_kd(K);

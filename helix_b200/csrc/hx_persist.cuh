@@ -58,6 +58,20 @@ struct alignas(16) HxPhase {
     int tp_barrier;           // a cross-GPU barrier follows the grid barrier of this phase; tp_epoch counts them within a launch
     int tp_epoch;
     int NH, NKV, DH, cap, nsplit; float scale;   // attention also uses eps (per-head RMSNorm)
+    // ---- dataflow engine (hx_decode_df.cu): vectors travel between CTAs as (value, epoch) pairs of 8 bytes; the epoch
+    // of the data a phase writes is ep_base + its index + 1, `*_dep` names the phase whose epoch tags an input ----
+    const unsigned long long* in_ll;       // input vector (linear: x; attention: q); null: x / tok or the attention partials
+    const unsigned long long* in_stat;     // per-tile sums of squares of the input (RMS norm), n_in_stat of them
+    int in_dep, n_in_stat;
+    unsigned long long* out_ll;            // output vector (residual stream, SwiGLU hidden, q)
+    unsigned long long* out_stat;          // per-tile sum of squares of the output (residual epilogue)
+    const unsigned long long* res_ll;      // residual rows added by the residual epilogue (null: row tok of x)
+    int res_dep;
+    unsigned long long* part_ll;           // split-K partial sums of pieces 1.. of every tile: [tile][piece - 1][128]
+    unsigned long long* kv_ll;             // this position's k and v rows [2 * NKV * DH] (qkv epilogue -> attention)
+    unsigned long long* pacc_ll;           // attention partial outputs [head][split][DH]
+    unsigned long long* pml_ll;            // attention partial (max, sum) lines [head][split][2]
+    unsigned long long* pax_ll;            // attention partial magnitude bounds [head][split]
 };
 
 struct HxPersist {
@@ -83,10 +97,19 @@ struct HxPersist {
     // tensor parallel: exchange buffers of all ranks (own entry = local), mapped through CUDA IPC.  Layout in floats:
     // [2 slots][world][tp_dm] partial sums | [world][2] arg-max pairs | [world] barrier flags | [world] arg-max flags | go
     float* tp_peer[8]; int tp_rank, tp_world, tp_dm; unsigned tp_epoch_base; int tp_vocab_off;
+    // dataflow engine
+    unsigned ep_base;                     // epochs of this launch are ep_base + 1 .. ep_base + nphases + 1
+    unsigned wait_limit;                  // polls before a bounded wait gives up
+    int inject_stall;                     // test hook: thread 0 of every CTA first waits on a word that nothing sets
+    unsigned long long* tp_x[8];          // tensor parallel: exchange buffers of all ranks as (value, epoch) pairs:
+                                          // [2 slots][world][tp_dm] partial rows | [world][2] arg-max pairs
+    unsigned* done_cnt;                   // ticket of the launches without an lm_head
 };
 
 int hx_persist_launch(const HxPersist& p, int grid, cudaStream_t st);
 int hx_persist_tc_launch(const HxPersist& p, int grid, cudaStream_t st);
+int hx_decode_df_launch(const HxPersist& p, int grid, cudaStream_t st);     // dataflow engine (hx_decode_df.cu)
+int hx_decode_df_prepare();                                                 // per-device function attributes
 size_t hx_persist_tc_smem(int bdig_bytes);            // shared memory besides the ring
 int hx_persist_tc_ring(int bdig_bytes);               // ring depth that fits (0: the digit columns do not fit)
 // how the tensor-core kernel cuts ntiles x kcells cells over `grid` CTAs: most pieces of one tile, most K cells of one CTA

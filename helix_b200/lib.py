@@ -123,6 +123,8 @@ _SIGS = {
     "hx_model_set_profile": (C.c_int, [C.c_void_p, C.c_int]),
     "hx_decode_loop": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float)]),
     "hx_model_fill_kv": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64]),
+    "hx_model_kv_read": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "hx_model_kv_write": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "hx_image_open": (C.c_int, [C.POINTER(C.c_void_p), C.c_char_p]),
     "hx_image_launch": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_void_p]),
     "hx_image_close": (C.c_int, [C.c_void_p]),
@@ -370,6 +372,16 @@ class Model:
 
     def fill_kv(self, T, seed=0):
         check(lib().hx_model_fill_kv(self.h, T, seed))
+
+    def kv_read(self, layer, kv_head, pos0, n, seq=0):
+        """Cached K and V rows [pos0, pos0 + n) of one (layer, kv head): two [n, head_dim] float32 arrays."""
+        k = np.empty((n, self.cfg.head_dim), np.float32); v = np.empty_like(k)
+        check(lib().hx_model_kv_read(self.h, seq, layer, kv_head, pos0, n, k.ctypes.data, v.ctypes.data))
+        return k, v
+
+    def kv_write(self, layer, kv_head, pos0, k, v, seq=0):
+        k = np.ascontiguousarray(k, np.float32); v = np.ascontiguousarray(v, np.float32)
+        check(lib().hx_model_kv_write(self.h, seq, layer, kv_head, pos0, k.shape[0], k.ctypes.data, v.ctypes.data))
 
     def v3_image(self):
         n = C.c_uint64()

@@ -107,7 +107,7 @@ int hx_pack_micro(const uint8_t* micro, int rows, int kblk, int32_t* dst, void* 
 int hx_gemv_nvfp4(const float* x, const int32_t* words, const int32_t* micro4, const float* ts,
                   float* y, int N, int Kpad, void* stream);
 
-/* Round trip of BASELINE config 1 with HOST buffers: quantize W [rows*K], then y = dequant(W) x.
+/* Single-matrix round trip (12288 x 4096 in the benchmark) with HOST buffers: quantize W [rows*K], then y = dequant(W) x.
  * x has K elements.  Returns Kpad through kpad_out when non-NULL. */
 int hx_roundtrip_host(const float* w, int rows, int K, const float* x, float* y, int* kpad_out);
 
@@ -183,7 +183,7 @@ int hx_model_load(hx_model** out, const char* path, int kv_cap, int batch, int f
 int hx_model_synth(hx_model** out, const hx_config* cfg, uint64_t seed, int kv_cap, int batch,
                    int flags, int tp_rank, int tp_size);
 
-/* GPT-2 (BASELINE config 2): LayerNorm, learned positions, fused qkv with biases, gelu_new MLP, tied lm_head.
+/* GPT-2 (the GPT-2-124M configuration): LayerNorm, learned positions, fused qkv with biases, gelu_new MLP, tied lm_head.
  * Host f32 tensors, every linear as [out][in] (transpose of the Conv1D storage); the library quantizes all linears
  * and the lm_head copy of wte to NVFP4 with the bit-exact quantizer.  cfg: arch 0, n_kv_heads = n_heads,
  * head_dim = d_model / n_heads, max_ctx = rows of wpe, norm_eps 1e-5.  Decodes with a KV cache through
@@ -247,7 +247,7 @@ int hx_model_set_profile(hx_model* m, int on);
  * region.  out_ids[batch*n_steps] may be NULL. */
 int hx_decode_loop(hx_model* m, const int32_t* ids, int pos0, int n_steps, int32_t* out_ids, float* ms);
 
-/* Batched decode (BASELINE config 4: independent sequences sharing one weight copy).  The model is created with
+/* Batched decode (independent sequences sharing one weight copy, 64 per GPU in the benchmark).  The model is created with
  * batch = number of sequences; sequence i owns KV slot i.  One call decodes one token of each of n_seq sequences:
  * ids[i] at position pos[i] (HOST arrays), arg-max to next_ids[i].  Internally chunks of 16 sequences go through every
  * linear as one tcgen05 GEMM (the weights are streamed once per 16 tokens instead of once per token), attention and
@@ -260,6 +260,13 @@ int hx_decode_batch_loop(hx_model* m, const int32_t* ids, int pos0, int n_seq, i
 /* Fill the KV cache for positions [0, T) with seeded synthetic values (benchmark set-up for a long
  * context without running a long prefill). */
 int hx_model_fill_kv(hx_model* m, int T, uint64_t seed);
+
+/* Read / write n cached positions [pos0, pos0 + n) of one (sequence, layer, kv head): k and v are HOST arrays of
+ * n * head_dim floats, K as cached (after QK-norm and RoPE).  The cache layout is the reference's
+ * [layer][kv head][position][head_dim], gpt2_infer.c:709-721; the reference keeps it device-private, these two calls
+ * exist so that a host can checkpoint / restore a sequence and so that tests can mirror a synthetic cache. */
+int hx_model_kv_read(hx_model* m, int seq, int layer, int kv_head, int pos0, int n, float* k, float* v);
+int hx_model_kv_write(hx_model* m, int seq, int layer, int kv_head, int pos0, int n, const float* k, const float* v);
 
 /* ---------------------------------------------------------------- kernel-entry image ---------- */
 /* helix_b200_kernels.fatbin exports, for sm_100a, the entry names and parameter lists of the kernels

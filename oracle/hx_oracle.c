@@ -10,9 +10,11 @@
  * the reference's own self-tests / known answers and against the reference sources compiled
  * unmodified (see oracle/Makefile, target `ref`).  The model-level forward (RMSNorm / RoPE / GQA
  * attention / SwiGLU sequencing) restates helixc/runtime/gpt2_infer.c and the kernel sources under
- * helixc/examples; the reference's own end-to-end goldens depend on model checkpoints and numpy
- * oracles that are not part of its repository, so the model-level logits are "parity unpinned"
- * beyond the per-op fixtures.
+ * helixc/examples and is PINNED by the reference's own GPU worker: gpt2_infer.c compiled unmodified,
+ * driving PTX emitted by the reference's own compiler (oracle/mint_ref_ptx.py), was run on a B200 on
+ * seeded models; its prefill logits are committed as tests/golden/ref_worker_logits.npz and
+ * reproduced by orc_model_prefill to 2e-5 (tests/test_oracle_golden.py), and its fused decode path
+ * yields orc_model_generate's tokens (tests/test_ref_worker_gpu.py).
  *
  * Build: gcc -O2 -fopenmp -shared -fPIC (no -march, no -ffast-math: the quantizer's float ops must
  * stay separately rounded, exactly as the reference's plain -O2 x86-64 build rounds them).
@@ -571,6 +573,16 @@ ORC_API void orc_model_dims(const OrcModel* m, int* out /* NL DM NH NKV DH DFF N
     out[0]=m->NL; out[1]=m->DM; out[2]=m->NH; out[3]=m->NKV; out[4]=m->DH; out[5]=m->DFF; out[6]=m->NV; out[7]=m->QD; out[8]=m->KVD;
 }
 ORC_API void orc_model_reset(OrcModel* m) { m->kv_len = 0; }
+/* Place n cached positions [pos0, pos0 + n) of (layer, kv head) into the cache: lets a test mirror a cache that
+ * was not produced by this model's own prefill.  Layout as gpt2_infer.c:709-721. */
+ORC_API int orc_model_kv_set(OrcModel* m, int L, int kv, int pos0, int n, const float* k, const float* v) {
+    if (L < 0 || L >= m->NL || kv < 0 || kv >= m->NKV || pos0 < 0 || n < 0 || pos0 + n > m->kv_cap) return 1;
+    size_t off = ((((size_t)L * m->NKV + kv) * m->kv_cap) + pos0) * m->DH;
+    memcpy(m->kc + off, k, (size_t)n * m->DH * 4);
+    memcpy(m->vc + off, v, (size_t)n * m->DH * 4);
+    if (pos0 + n > m->kv_len) m->kv_len = pos0 + n;
+    return 0;
+}
 
 static const float* dense_ptr(const OrcModel* m, int idx) { return (const float*)(m->map + m->desc[idx].data_off); }
 
@@ -679,7 +691,7 @@ ORC_API int orc_num_threads(void) {
 }
 
 /* ---------------------------------------------------------------------------------------------------
- * GPT-2 block with a KV cache (BASELINE config 2).  Restates forward_layer_gpt2, gpt2_infer.c:1131-1193
+ * GPT-2 block with a KV cache (the GPT-2-124M configuration).  Restates forward_layer_gpt2, gpt2_infer.c:1131-1193
  * (LayerNorm -> fused qkv + bias -> per-head softmax(q k^T * 1/sqrt(DH)) v -> proj + bias + residual ->
  * LayerNorm -> c_fc + bias -> gelu_new -> proj + bias + residual), embed_gather :1201-1223 (wte row + wpe
  * row), ln_f and the tied head.  The reference re-forwards the whole context every token; with causal

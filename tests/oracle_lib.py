@@ -73,6 +73,7 @@ def oracle():
     lib.orc_num_threads.restype = C.c_int
     lib.orc_model_close.argtypes = [C.c_void_p]
     lib.orc_model_reset.argtypes = [C.c_void_p]
+    lib.orc_model_kv_set.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p]
     lib.orc_model_dims.argtypes = [C.c_void_p, i32p]
     lib.orc_model_decode.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     lib.orc_model_prefill.argtypes = [C.c_void_p, i32p, C.c_int, C.c_void_p]
@@ -266,6 +267,10 @@ class OracleModel:
 
     def reset(self):
         self.lib.orc_model_reset(self.h)
+
+    def kv_set(self, layer, kv_head, pos0, k, v):
+        k = np.ascontiguousarray(k, np.float32); v = np.ascontiguousarray(v, np.float32)
+        assert self.lib.orc_model_kv_set(self.h, layer, kv_head, pos0, k.size // self.DH, k, v) == 0
 
     def decode(self, tok, pos, want_hidden=False):
         lg = np.zeros(self.NV, np.float32)

@@ -193,3 +193,26 @@ def test_decode_equals_online_attention_form(tiny_file):
     lg2 = m2.prefill(ids)
     assert np.array_equal(lg, lg2) and out[0] == int(np.argmax(lg))
     m.close(); m2.close()
+
+
+def test_model_level_restatement_against_the_reference_gpu_worker():
+    """ref_worker_logits.npz holds last-row logits computed by the UNMODIFIED reference worker (gpt2_infer.c with
+    its own compiler's PTX) on a B200 for three small seeded models (tests/golden/make_ref_worker_golden.py).  The
+    CPU restatement of the decode sequencing, run on the same seeded weights and prompt, must reproduce them."""
+    import tempfile
+    g = np.load(os.path.join(G, "ref_worker_logits.npz"))
+    names = sorted(k[len("logits_"):] for k in g.files if k.startswith("logits_"))
+    assert len(names) >= 3
+    for name in names:
+        NL, DM, NH, NKV, DH, DFF, NV = (int(v) for v in g["cfg_" + name])
+        cfg = dict(NL=NL, DM=DM, NH=NH, NKV=NKV, DH=DH, DFF=DFF, NV=NV)
+        with tempfile.TemporaryDirectory() as d:
+            path = os.path.join(d, "m.weights")
+            ol.write_v3(path, cfg, ol.synth_tensors(cfg, seed=int(g["seed_w"])))
+            ids = np.random.default_rng(int(g["seed_ids"])).integers(0, NV, int(g["n_prompt"])).astype(np.int32)
+            om = ol.OracleModel(path, kv_cap=64)
+            lo = om.prefill(ids)
+            om.close()
+        want = g["logits_" + name]
+        assert np.max(np.abs(lo - want)) < 2e-5, (name, float(np.max(np.abs(lo - want))))
+        assert int(np.argmax(lo)) == int(np.argmax(want))

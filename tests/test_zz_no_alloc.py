@@ -6,6 +6,7 @@ import pytest
 
 import helix_b200 as hb
 from helix_b200.lib import check
+import oracle_lib as ol
 
 pytestmark = pytest.mark.gpu
 
@@ -32,6 +33,16 @@ def test_matches_allocating_entry_twice_in_a_row(rows, K, seed):
         got = _run(L.hx_quantize_nvfp4_noalloc, w)
         for a, b in zip(got, want):
             assert np.array_equal(a.view(np.uint8), b.view(np.uint8))
+
+
+def test_matches_the_cpu_checker_directly():
+    """Independent of the allocating entry: codes, scale bytes and tensor scale against the CPU restatement."""
+    rng = np.random.default_rng(12)
+    w = (0.02 * rng.standard_normal((129, 1000))).astype(np.float32)
+    W, mic, ts, sc = ol.quantize(w)
+    gW, gmic, gsc, gts = _run(hb.lib().hx_quantize_nvfp4_noalloc, w)
+    assert np.array_equal(gW, W.ravel()) and np.array_equal(gmic, mic.ravel())
+    assert np.array_equal(gsc.view(np.uint32), sc.ravel().view(np.uint32)) and np.float32(gts[0]) == np.float32(ts)
 
 
 def test_leftovers_of_a_larger_call_are_not_read():
