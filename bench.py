@@ -289,11 +289,11 @@ def run_ours(args):
         n_launch = args.steps * NEW_TOKENS
         avg_ms = ms_total / n_launch
         achieved = token_bytes / (avg_ms * 1e-3) / 1e9
-        kname = "k_decode_tc" if engine.endswith("tcgen05") else "k_decode_persist"
+        kname = "k_decode_df" if engine.endswith("dataflow") else ("k_decode_tc" if engine.endswith("tcgen05") else "k_decode_persist")
         roofline = {"bound": "hbm", "kernel": f"{kname} (persistent cooperative kernel, one launch = one decoded token: all "
                     f"{4 * cfgd['n_layers'] + 1} linears, attention, norms, arg-max)",
                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": token_bytes * NCU_TRAFFIC_RATIO if kname == "k_decode_tc" else None,
+                    "traffic": token_bytes * NCU_TRAFFIC_RATIO if kname in ("k_decode_tc", "k_decode_df") else None,
                     "traffic_source": "ncu dram__bytes_read+write of one launch of the 4-layer case (profiles/"
                                       "k_decode_tc_qwen3-8b-shape_4layers.md) = 1.010 x its algorithmic bytes, scaled to "
                                       "this launch's algorithmic bytes (traffic grows with the layers streamed)",

@@ -100,6 +100,11 @@ struct hx_model {
     int *d_bids = nullptr, *d_bpos = nullptr, *d_bseq = nullptr, *d_bnext = nullptr; float* pf_logits = nullptr; int b_cap = 0;   // batched decode
     cudaGraphExec_t g_bstep = nullptr; int g_bstep_n = 0;
     int* d_pf_pos = nullptr; cudaGraphExec_t g_pf_chunk = nullptr; bool pf_graph_failed = false; int pf_chunk_launches = 0;
+    // dataflow engine (hx_decode_df.cu): vectors that cross CTAs as (value, epoch) pairs
+    bool use_df = false;
+    unsigned long long *xll[2] = {nullptr, nullptr}, *statll[2] = {nullptr, nullptr}, *qll = nullptr, *kvll = nullptr, *hll = nullptr;
+    unsigned long long *pacc_ll = nullptr, *pml_ll = nullptr, *pax_ll = nullptr, *part_ll[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    unsigned ep_count = 0, wait_limit = 1u << 24; int inject_stall = 0; unsigned* done_cnt = nullptr;
 };
 
 namespace {
@@ -514,8 +519,62 @@ int build_phases(hx_model* m, bool from_prompt, bool with_head, HxPhase** out, i
     int maxK = 0;
     // tensor parallel: o_proj and down leave per-rank partial sums; the next linear's prologue adds them to the residual
     // stream, which alternates between two buffers (a CTA must not overwrite what another still reads)
-    const bool tp = m->tp_world > 1;
+    const bool tp = m->tp_world > 1 && !m->use_df;
     float* xcur = m->x; int nbar = 0;
+    if (m->use_df) {
+        // Dataflow engine: the residual stream alternates between two pair buffers (xll[0] after o_proj, xll[1] after
+        // down), every other vector has one buffer per producing phase of a layer; `*_dep` is the index of the phase
+        // whose epoch tags an input.  With several ranks o_proj and down are row-split and their residual epilogue
+        // exchanges the partial rows (tp_partial = slot + 1).
+        const int ntile_dm = (c.d_model + 127) / 128;
+        const bool dtp = m->tp_world > 1;
+        int dep_x = -1;                                   // phase that produced the current residual stream (-1: the embedding row)
+        for (int L = 0; L < c.n_layers; L++) {
+            Layer& ly = m->layers[L];
+            float* kcl = m->kc + (size_t)L * c.n_kv_heads * cap * DH; float* vcl = m->vc + (size_t)L * c.n_kv_heads * cap * DH;
+            HxPhase a = linear(ly.qkv, nullptr, nullptr, HX_EPI_QKV, ly.qkv.N);
+            a.norm = HX_NORM_RMS; a.g = ly.in_g; a.eps = c.norm_eps;
+            if (dep_x < 0) { a.x = m->emb; a.tok = from_prompt ? m->d_prompt : m->d_tok; a.res_ld = c.d_model; }
+            else { a.in_ll = m->xll[1]; a.in_stat = m->statll[1]; a.n_in_stat = ntile_dm; a.in_dep = dep_x; }
+            a.qn_g = ly.qn_g; a.kn_g = ly.kn_g; a.cosT = m->cosT; a.sinT = m->sinT; a.kc = kcl; a.vc = vcl;
+            a.NH = c.n_heads; a.NKV = c.n_kv_heads; a.DH = DH; a.cap = cap;
+            a.out_ll = m->qll; a.kv_ll = m->kvll; a.part_ll = m->part_ll[0];
+            const int i_qkv = (int)v.size(); v.push_back(a);
+            HxPhase at = {};
+            at.type = HX_PH_ATTN; at.epi = HX_EPI_QKV; at.kc = kcl; at.vc = vcl;
+            at.NH = c.n_heads; at.NKV = c.n_kv_heads; at.DH = DH; at.cap = cap;
+            at.nsplit = m->nsplit_persist; at.scale = 1.0f / sqrtf((float)DH); at.eps = c.norm_eps;
+            at.in_ll = m->qll; at.kv_ll = m->kvll; at.in_dep = i_qkv;
+            at.pacc_ll = m->pacc_ll; at.pml_ll = m->pml_ll; at.pax_ll = m->pax_ll;
+            const int i_att = (int)v.size(); v.push_back(at);
+            HxPhase o = linear(ly.o, nullptr, nullptr, HX_EPI_RESID, ly.o.N);
+            o.norm = HX_NORM_ATTN; o.NH = c.n_heads; o.NKV = c.n_kv_heads; o.DH = DH; o.nsplit = m->nsplit_persist;
+            o.pacc_ll = m->pacc_ll; o.pml_ll = m->pml_ll; o.pax_ll = m->pax_ll; o.in_dep = i_att;
+            if (dep_x < 0) { o.x = m->emb; o.tok = from_prompt ? m->d_prompt : m->d_tok; o.res_ld = c.d_model; }
+            else { o.res_ll = m->xll[1]; o.res_dep = dep_x; }
+            o.out_ll = m->xll[0]; o.out_stat = m->statll[0]; o.part_ll = m->part_ll[1];
+            if (dtp) o.tp_partial = 1;
+            const int i_o = (int)v.size(); v.push_back(o);
+            HxPhase gu = linear(ly.gu, nullptr, nullptr, HX_EPI_SWIGLU, c.d_ff);
+            gu.norm = HX_NORM_RMS; gu.g = ly.post_g; gu.eps = c.norm_eps;
+            gu.in_ll = m->xll[0]; gu.in_stat = m->statll[0]; gu.n_in_stat = ntile_dm; gu.in_dep = i_o;
+            gu.out_ll = m->hll; gu.part_ll = m->part_ll[2];
+            const int i_gu = (int)v.size(); v.push_back(gu);
+            HxPhase dn = linear(ly.down, nullptr, nullptr, HX_EPI_RESID, ly.down.N);
+            dn.in_ll = m->hll; dn.in_dep = i_gu; dn.res_ll = m->xll[0]; dn.res_dep = i_o;
+            dn.out_ll = m->xll[1]; dn.out_stat = m->statll[1]; dn.part_ll = m->part_ll[3];
+            if (dtp) dn.tp_partial = 2;
+            dep_x = (int)v.size(); v.push_back(dn);
+        }
+        if (with_head) {
+            HxPhase hd = linear(m->head, nullptr, m->logits, HX_EPI_ARGMAX, m->head.N);
+            hd.norm = HX_NORM_RMS; hd.g = m->final_g; hd.eps = c.norm_eps;
+            if (dep_x < 0) { hd.x = m->emb; hd.tok = from_prompt ? m->d_prompt : m->d_tok; hd.res_ld = c.d_model; }
+            else { hd.in_ll = m->xll[1]; hd.in_stat = m->statll[1]; hd.n_in_stat = ntile_dm; hd.in_dep = dep_x; }
+            hd.part_ll = m->part_ll[4];
+            v.push_back(hd);
+        }
+    } else
     for (int L = 0; L < c.n_layers; L++) {
         Layer& ly = m->layers[L];
         HxPhase a = linear(ly.qkv, xcur, m->qkv, HX_EPI_STORE, ly.qkv.N);
@@ -557,7 +616,7 @@ int build_phases(hx_model* m, bool from_prompt, bool with_head, HxPhase** out, i
         if (ly.o.K > maxK) maxK = ly.o.K;
         if (ly.qkv.K > maxK) maxK = ly.qkv.K;
     }
-    if (with_head) {
+    if (with_head && !m->use_df) {
         HxPhase hd = linear(m->head, xcur, m->logits, HX_EPI_ARGMAX, m->head.N);
         hd.norm = HX_NORM_RMS; hd.g = m->final_g; hd.eps = c.norm_eps;
         if (tp && c.n_layers > 0) { hd.tp_sum = 2; hd.x_out = xcur == m->x ? m->x2 : m->x; }
@@ -585,9 +644,47 @@ int init_persist(hx_model* m) {
     if (const char* e = getenv("HX_ATT_SPLIT")) { const int v = atoi(e); if (v >= 1 && v <= m->nsplit_persist) m->nsplit_persist = v; }
     if (256 % m->cfg.head_dim) return hx_fail(HX_ERR_ARG, "persistent decode needs head_dim dividing 256");
     int rc;
+    {   // the dataflow engine needs the fused qkv epilogue (whole heads per tile) and room for the split weights
+        const hx_config& c = m->cfg;
+        const char* sy = getenv("HX_SYNC");
+        const bool fuse_qk = c.head_dim == 32 || c.head_dim == 64 || c.head_dim == 128;
+        m->use_df = m->use_tc && fuse_qk && (size_t)c.n_heads * m->nsplit_persist <= 2304 && !(sy && strcmp(sy, "barrier") == 0);
+    }
+    if (m->use_df) {
+        const hx_config& c = m->cfg;
+        const int DH = c.head_dim, QD = m->QD, KVD = m->KVD, ntile_dm = (c.d_model + 127) / 128;
+        auto ll = [&](unsigned long long** p, size_t n) -> int {
+            int r = dalloc(m, p, n + 2); if (r) return r;
+            HX_CUDA(cudaMemset(*p, 0, (n + 2) * 8));
+            return HX_OK;
+        };
+        for (int i = 0; i < 2; i++) { if ((rc = ll(&m->xll[i], (size_t)ntile_dm * 128))) return rc; if ((rc = ll(&m->statll[i], (size_t)ntile_dm))) return rc; }
+        if ((rc = ll(&m->qll, (size_t)QD + 128))) return rc;
+        if ((rc = ll(&m->kvll, (size_t)2 * KVD + 128))) return rc;
+        if ((rc = ll(&m->hll, (size_t)((c.d_ff + 63) / 64) * 64 + 128))) return rc;
+        const size_t hs = (size_t)c.n_heads * m->nsplit_persist;
+        if ((rc = ll(&m->pacc_ll, hs * DH))) return rc;
+        if ((rc = ll(&m->pml_ll, hs * 2))) return rc;
+        if ((rc = ll(&m->pax_ll, hs))) return rc;
+        auto parts = [&](const Fused& f) -> size_t {
+            int maxp = 1, maxrun = 1;
+            hx_tc_split(f.tiles128, f.ksteps / 4, m->grid_persist, &maxp, &maxrun);
+            return (size_t)f.tiles128 * maxp * 128;
+        };
+        size_t need[5] = {128, 128, 128, 128, parts(m->head)};
+        for (auto& ly : m->layers) {
+            const size_t v4[4] = {parts(ly.qkv), parts(ly.o), parts(ly.gu), parts(ly.down)};
+            for (int i = 0; i < 4; i++) if (v4[i] > need[i]) need[i] = v4[i];
+        }
+        for (int i = 0; i < 5; i++) if ((rc = ll(&m->part_ll[i], need[i]))) return rc;
+        if ((rc = dalloc(m, &m->done_cnt, (size_t)4))) return rc;
+        HX_CUDA(cudaMemset(m->done_cnt, 0, 16));
+        if ((rc = hx_decode_df_prepare())) return rc;
+    }
     if (m->tp_world > 1) {
         if ((rc = dalloc(m, &m->x2, (size_t)m->cfg.d_model))) return rc;
         m->tp_buf_floats = (size_t)2 * m->tp_world * m->cfg.d_model + (size_t)4 * m->tp_world + 64;
+        if (m->use_df) m->tp_buf_floats *= 2;            // the same layout in 8-byte (value, epoch) pairs
         if ((rc = dalloc(m, &m->tp_buf, m->tp_buf_floats))) return rc;
         HX_CUDA(cudaMemset(m->tp_buf, 0, m->tp_buf_floats * 4));
         m->tp_peer[m->tp_rank] = m->tp_buf;
@@ -604,7 +701,7 @@ int init_persist(hx_model* m) {
         if ((rc = dalloc(m, &m->tc_partial, m->tc_units_max * 128 + 128))) return rc;
         if ((rc = dalloc(m, &m->tc_cnt, (size_t)m->tc_tiles_max + 8))) return rc;
         HX_CUDA(cudaMemset(m->tc_cnt, 0, ((size_t)m->tc_tiles_max + 8) * 4));
-        m->tc_ring = hx_persist_tc_ring(m->bdig_bytes);
+        m->tc_ring = m->use_df ? hx_decode_df_ring(m->bdig_bytes) : hx_persist_tc_ring(m->bdig_bytes);
         if (const char* e = getenv("HX_TC_RING")) { const int r = atoi(e); if (r >= 3 && r < m->tc_ring) m->tc_ring = r; }
         if (m->tc_ring < 3)
             return hx_fail(HX_ERR_ARG, "tensor-core decode: K too large for shared memory (%zu bytes besides the ring)", hx_persist_tc_smem(m->bdig_bytes));
@@ -633,6 +730,13 @@ int persist_step(hx_model* m, bool from_prompt, bool with_head) {
         P.tp_epoch_base = m->tp_launches * 4096u;        // every rank launches the same sequence of steps
         m->tp_launches++;
     }
+    if (m->use_df) {
+        if (m->ep_count > 0xFFF00000u) return hx_fail(HX_ERR_STATE, "epoch counter of the decode engine exhausted: rebuild the model");
+        P.ep_base = m->ep_count; m->ep_count += (unsigned)P.nphases + 2u;
+        P.wait_limit = m->wait_limit; P.inject_stall = m->inject_stall; P.done_cnt = m->done_cnt;
+        for (int w = 0; w < m->tp_world; w++) P.tp_x[w] = reinterpret_cast<unsigned long long*>(m->tp_peer[w]);
+        return hx_decode_df_launch(P, m->grid_persist, m->st);
+    }
     m->bar_count += (unsigned long long)m->grid_persist * (unsigned long long)(P.nphases - 1);
     if (m->use_tc) return hx_persist_tc_launch(P, m->grid_persist, m->st);
     return hx_persist_launch(P, m->grid_persist, m->st);
@@ -649,7 +753,12 @@ int persist_check(hx_model* m) {
     int e = 0;
     HX_CUDA(cudaMemcpy(&e, m->d_err, 4, cudaMemcpyDeviceToHost));
     if (e) {
-        cudaMemset(m->d_err, 0, 4); cudaMemset(m->d_bar, 0, 8); m->bar_count = 0;
+        // every counter a launch leaves behind goes back to its idle value, so the next step starts clean (the pair
+        // buffers need nothing: epochs only grow)
+        cudaMemset(m->d_err, 0, 16); cudaMemset(m->d_bar, 0, 8); m->bar_count = 0;
+        cudaMemset(m->am_cnt, 0, 16); cudaMemset(m->attn_cnt, 0, (size_t)m->cfg.n_kv_heads * 4);
+        if (m->tc_cnt) cudaMemset(m->tc_cnt, 0, ((size_t)m->tc_tiles_max + 8) * 4);
+        if (m->done_cnt) cudaMemset(m->done_cnt, 0, 16);
         return hx_fail(HX_ERR_TIMEOUT, "a bounded wait in the persistent decode kernel ran out");
     }
     return HX_OK;
@@ -950,7 +1059,16 @@ HX_API int hx_model_tp_connect(hx_model* m, const uint8_t* handles, int world) {
 HX_API const char* hx_model_engine(const hx_model* m) {
     if (!m) return "";
     if (!m->persist) return "graph";
+    if (m->use_df) return "persistent-tcgen05-dataflow";
     return m->use_tc ? "persistent-tcgen05" : "persistent-mma";
+}
+// Test hook of the bounded waits: polls before a device-side wait gives up (0 = the default) and, with
+// inject_stall != 0, a wait at the start of every launch on a word that nothing writes.
+HX_API int hx_model_debug_waits(hx_model* m, unsigned wait_limit, int inject_stall) {
+    HX_CHECK_ARG(m);
+    m->wait_limit = wait_limit ? wait_limit : (1u << 24);
+    m->inject_stall = inject_stall;
+    return HX_OK;
 }
 HX_API int hx_model_set_profile(hx_model* m, int on) { HX_CHECK_ARG(m); m->profile = on != 0; return HX_OK; }
 

@@ -65,8 +65,8 @@ struct alignas(16) HxPhase {
     int in_dep, n_in_stat;
     unsigned long long* out_ll;            // output vector (residual stream, SwiGLU hidden, q)
     unsigned long long* out_stat;          // per-tile sum of squares of the output (residual epilogue)
-    const unsigned long long* res_ll;      // residual rows added by the residual epilogue (null: row tok of x)
-    int res_dep;
+    const unsigned long long* res_ll;      // residual rows added by the residual epilogue (null: row *tok of the table x)
+    int res_dep, res_ld;                   // res_ld: row length of the table x when tok is set
     unsigned long long* part_ll;           // split-K partial sums of pieces 1.. of every tile: [tile][piece - 1][128]
     unsigned long long* kv_ll;             // this position's k and v rows [2 * NKV * DH] (qkv epilogue -> attention)
     unsigned long long* pacc_ll;           // attention partial outputs [head][split][DH]
@@ -109,7 +109,8 @@ struct HxPersist {
 int hx_persist_launch(const HxPersist& p, int grid, cudaStream_t st);
 int hx_persist_tc_launch(const HxPersist& p, int grid, cudaStream_t st);
 int hx_decode_df_launch(const HxPersist& p, int grid, cudaStream_t st);     // dataflow engine (hx_decode_df.cu)
-int hx_decode_df_prepare();                                                 // per-device function attributes
+int hx_decode_df_prepare();
+int hx_decode_df_ring(int bdig_bytes);                                                 // per-device function attributes
 size_t hx_persist_tc_smem(int bdig_bytes);            // shared memory besides the ring
 int hx_persist_tc_ring(int bdig_bytes);               // ring depth that fits (0: the digit columns do not fit)
 // how the tensor-core kernel cuts ntiles x kcells cells over `grid` CTAs: most pieces of one tile, most K cells of one CTA

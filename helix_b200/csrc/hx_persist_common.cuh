@@ -426,7 +426,7 @@ __device__ __noinline__ bool attention_phase2(const HxPersist& P, const HxPhase&
 #pragma unroll
             for (int a = 0; a < NACC; a++) {
                 const int hd = (HD < NCT ? tid % HD : tid + a * NCT);
-                if (hd < HD && sub < nsub) {
+                if (hd < HD && sub < nsub && (HD >= NCT || a == 0)) {
                     const int i = hd / DH, d = hd - i * DH;
                     float v = acc[a] * S.att_r[i];
 #pragma unroll
@@ -457,7 +457,7 @@ __device__ __noinline__ bool attention_phase2(const HxPersist& P, const HxPhase&
 #pragma unroll
         for (int a = 0; a < NACC; a++) {
             const int hd = (HD < NCT ? tid : tid + a * NCT);
-            if (hd < HD && (HD >= NCT || tid < HD)) {
+            if (hd < HD && (HD >= NCT || (tid < HD && a == 0))) {
                 const int i = hd / DH, d = hd - i * DH;
                 const size_t hs = (size_t)(ap.kv * GRP + i) * ph.nsplit + ap.split;
                 P.part_acc[hs * DH + d] = acc[a];

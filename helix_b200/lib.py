@@ -115,6 +115,7 @@ _SIGS = {
     "hx_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "hx_model_last_stats": (C.c_int, [C.c_void_p, C.POINTER(HxStepStats)]),
     "hx_model_engine": (C.c_char_p, [C.c_void_p]),
+    "hx_model_debug_waits": (C.c_int, [C.c_void_p, C.c_uint, C.c_int]),
     "hx_model_gpt2": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(HxConfig), C.POINTER(HxGpt2Weights), C.c_int]),
     "hx_decode_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "hx_decode_batch_loop": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float)]),
@@ -361,6 +362,9 @@ class Model:
 
     def engine(self):
         return lib().hx_model_engine(self.h).decode()
+
+    def debug_waits(self, wait_limit=0, inject_stall=False):
+        check(lib().hx_model_debug_waits(self.h, int(wait_limit), 1 if inject_stall else 0))
 
     def set_profile(self, on):
         check(lib().hx_model_set_profile(self.h, 1 if on else 0))

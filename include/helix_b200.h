@@ -236,10 +236,17 @@ typedef struct {
     float    ms_other;
 } hx_step_stats;
 int hx_model_last_stats(const hx_model* m, hx_step_stats* st);
-/* Name of the decode engine in use: "persistent-tcgen05" (one cooperative launch per token, linear phases on
- * tcgen05.mma), "persistent-mma" (same kernel structure, mma.sync) or "graph" (one CUDA graph of per-op kernels;
- * the only engine for which hx_model_set_profile yields per-category times). */
+/* Name of the decode engine in use: "persistent-tcgen05-dataflow" (the default: one cooperative launch per token,
+ * linear phases on tcgen05.mma, CTAs hand results to one another as (value, epoch) pairs without grid barriers),
+ * "persistent-tcgen05" (the same with grid barriers, HX_SYNC=barrier), "persistent-mma" (mma.sync linears,
+ * HX_LINEAR=mma) or "graph" (one CUDA graph of per-op kernels, HX_DECODE=graph and GPT-2; the only engine for which
+ * hx_model_set_profile yields per-category times). */
 const char* hx_model_engine(const hx_model* m);
+/* Test hook of the bounded device-side waits.  Every wait of the decode kernels polls at most wait_limit times
+ * (0 restores the default, about ten seconds) and then makes the call return HX_ERR_TIMEOUT with the model still
+ * usable.  inject_stall != 0 makes every launch begin with a wait on a word that nothing writes, so that the
+ * time-out path can be exercised without faulting or hanging the GPU.  No reference counterpart. */
+int hx_model_debug_waits(hx_model* m, unsigned wait_limit, int inject_stall);
 int hx_model_set_profile(hx_model* m, int on);
 
 /* Run n_steps decode steps starting at position pos0 with the KV cache as it stands, feeding back
