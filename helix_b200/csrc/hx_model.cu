@@ -124,9 +124,12 @@ int alloc_fused(hx_model* m, Fused& f, int N, int K) {
     int rc = HX_OK;
     m->decode_bytes += f.bytes();
     f.KG = hx_t16_kgroups(K); f.ntiles = hx_t16_tiles(N);
-    if (m->tp_world == 1) {       // the layouts of the other engines; a tensor-parallel shard only runs the tensor-core engine
+    // one resident layout: the one the selected engine reads (D16 for the per-op graph engine, T16 for the mma.sync
+    // persistent engine, T128 for the tensor-core engines)
+    if (!m->persist) {
         rc = dalloc(m, &f.codes, (size_t)N * (f.Kd / 2)); if (rc) return rc;
         rc = dalloc(m, &f.scales, (size_t)N * (f.Kd / 16)); if (rc) return rc;
+    } else if (!m->use_tc) {
         rc = dalloc(m, &f.t16, hx_t16_bytes(N, K)); if (rc) return rc;
         HX_CUDA(cudaMemsetAsync(f.t16, 0, hx_t16_bytes(N, K), m->st));
     }
@@ -194,10 +197,12 @@ int fetch_dense(hx_model* m, Source& s, int idx, size_t n, float** out, bool is_
 }
 
 void put_rows(hx_model* m, const Committed& c, Fused& f, int row_mul, int row_off) {
-    hx_repack_rows(c.words, c.micro, c.rows, c.K, c.Kpad, f.codes, f.scales, row_mul, row_off, m->st);
+    if (f.codes) hx_repack_rows(c.words, c.micro, c.rows, c.K, c.Kpad, f.codes, f.scales, row_mul, row_off, m->st);
     // tile layout: plain offset, or gate/up interleaved tile by tile (16 rows of gate, 16 rows of up)
-    if (row_mul == 1) hx_repack_t16(c.words, c.micro, c.rows, c.K, c.Kpad, f.t16, f.KG, 1, 1, row_off, m->st);
-    else hx_repack_t16(c.words, c.micro, c.rows, c.K, c.Kpad, f.t16, f.KG, 16, row_mul, row_off, m->st);
+    if (f.t16) {
+        if (row_mul == 1) hx_repack_t16(c.words, c.micro, c.rows, c.K, c.Kpad, f.t16, f.KG, 1, 1, row_off, m->st);
+        else hx_repack_t16(c.words, c.micro, c.rows, c.K, c.Kpad, f.t16, f.KG, 16, row_mul, row_off, m->st);
+    }
     if (f.t128) {   // gate/up: 64 gate rows then the matching 64 up rows per 128-row tile
         if (row_mul == 1) hx_repack_t128(c.words, c.micro, c.rows, c.K, c.Kpad, f.t128, f.ksteps / 4, 1, 1, row_off, m->st);
         else hx_repack_t128(c.words, c.micro, c.rows, c.K, c.Kpad, f.t128, f.ksteps / 4, 64, row_mul, row_off, m->st);
@@ -261,7 +266,7 @@ int build(hx_model* m, Source& s) {
             if ((rc = alloc_fused(m, ly.qkv, QD + 2 * KVD, DM))) break;
             if ((rc = alloc_fused(m, ly.o, DM, QD))) break;
             if ((rc = alloc_fused(m, ly.gu, 2 * DFF, DM))) break;
-            if (DFF % 16 && m->tp_world == 1) {   // tile-interleaved pairs need whole tiles for gate and for up
+            if (DFF % 16 && ly.gu.t16) {          // tile-interleaved pairs need whole tiles for gate and for up
                 ly.gu.ntiles = 2 * hx_t16_tiles(DFF);
                 if ((rc = dalloc(m, &ly.gu.t16, (size_t)ly.gu.ntiles * ly.gu.KG * HX_T16_CELL))) break;
                 HX_CUDA(cudaMemsetAsync(ly.gu.t16, 0, (size_t)ly.gu.ntiles * ly.gu.KG * HX_T16_CELL, m->st));
@@ -772,7 +777,7 @@ int finish_init(hx_model* m) {
         rc = init_persist(m);
         if (rc) return rc;
     }
-    if (m->tp_world > 1) return HX_OK;          // a shard only runs the persistent tensor-core engine
+    if (m->persist) return HX_OK;               // the per-op launch graphs belong to the graph engine alone
     rc = capture(m, false, true, &m->g_decode);
     if (rc && m->pdl) {     // programmatic edges not capturable on this driver: plain stream order
         m->pdl = false;
@@ -1267,7 +1272,8 @@ static int pf_enqueue_layers(hx_model* m, int n, const int* ids, HxPfWhere wh) {
 
 // One prefill chunk of n tokens whose first position is *d_pf_pos; ends by advancing that position.
 static int pf_enqueue_chunk(hx_model* m, int n) {
-    HxPfWhere wh = {m->d_pf_pos, nullptr, nullptr, 0};
+    const hx_config& c = m->cfg;
+    HxPfWhere wh = {m->d_pf_pos, nullptr, nullptr, (size_t)c.n_layers * c.n_kv_heads * m->kv_cap * c.head_dim, m->d_pf_pos + 1};
     int rc = pf_enqueue_layers(m, n, m->d_prompt, wh); if (rc) return rc;
     hx_pf_advance(m->d_pf_pos, n, m->st);
     return HX_OK;
@@ -1297,7 +1303,7 @@ static int bd_enqueue_step(hx_model* m, int n_seq) {
     int rc;
     for (int c0 = 0; c0 < n_seq; c0 += HX_PF_TB) {
         const int n = n_seq - c0 < HX_PF_TB ? n_seq - c0 : HX_PF_TB;
-        HxPfWhere wh = {nullptr, m->d_bpos + c0, m->d_bseq + c0, seq_stride};
+        HxPfWhere wh = {nullptr, m->d_bpos + c0, m->d_bseq + c0, seq_stride, nullptr};
         if ((rc = pf_enqueue_layers(m, n, m->d_bids + c0, wh))) return rc;
         if ((rc = pf_linear(m, m->head, m->pf_x, c.d_model, n, 0, m->final_g, m->pf_logits, c.vocab, m->head.N, 0, 0))) return rc;
         hx_pf_argmax_rows(m->pf_logits, c.vocab, c.vocab, n, m->d_bnext + c0, m->d_bpos + c0, m->st);
@@ -1310,10 +1316,11 @@ static int bd_enqueue_step(hx_model* m, int n_seq) {
 // logits of the last position in m->logits, its arg-max in d_tok / d_hist[T], *d_pos = T.
 // Full chunks replay one captured CUDA graph (the position lives in device memory); the last, shorter chunk
 // and the lm_head are launched directly.
-static int run_prefill_batched(hx_model* m, int T) {
+static int run_prefill_batched(hx_model* m, int T, int seq) {
     const hx_config& c = m->cfg;
     int rc = pf_alloc(m); if (rc) return rc;
-    HX_CUDA(cudaMemsetAsync(m->d_pf_pos, 0, 4, m->st));
+    const int ps[2] = {0, seq};                      // first position of the chunk, KV slot of the sequence
+    HX_CUDA(cudaMemcpyAsync(m->d_pf_pos, ps, 8, cudaMemcpyHostToDevice, m->st));
     const int nfull = T / HX_PF_TB, rem = T - nfull * HX_PF_TB;
     if (nfull > 1 && !m->g_pf_chunk && !m->pf_graph_failed) {
         cudaGraph_t g = nullptr;
@@ -1340,10 +1347,11 @@ static int run_prefill_batched(hx_model* m, int T) {
     return HX_OK;
 }
 
-static int run_prefill(hx_model* m, const int32_t* ids, int T) {
+static int run_prefill(hx_model* m, const int32_t* ids, int T, int seq = 0) {
     // positions 0..T-2 without the head, position T-1 with it
     HX_CUDA(cudaMemcpyAsync(m->d_prompt, ids, (size_t)T * 4, cudaMemcpyHostToDevice, m->st));
-    if (m->use_tc && m->pf_batched && m->head.t128) return run_prefill_batched(m, T);
+    if (m->use_tc && m->pf_batched && m->head.t128) return run_prefill_batched(m, T, seq);
+    if (seq != 0) return hx_fail(HX_ERR_STATE, "prefill into KV slot %d needs the batched prefill path", seq);
     int rc = set_pos_tok(m, 0, nullptr); if (rc) return rc;
     for (int s = 0; s < T - 1; s++) if ((rc = step_prefill(m))) return rc;
     HX_CUDA(cudaMemcpyAsync(m->d_tok, m->d_prompt + (T - 1), 4, cudaMemcpyDeviceToDevice, m->st));
@@ -1361,6 +1369,19 @@ HX_API int hx_prefill(hx_model* m, const int32_t* ids, int T, int32_t* next_ids,
     if ((rc = persist_check(m))) return rc;
     m->kv_len = T;
     return HX_OK;
+}
+
+// Prefill one sequence of a batch into its own KV slot (the batched decode then continues all slots together).
+HX_API int hx_prefill_seq(hx_model* m, int seq, const int32_t* ids, int T, int32_t* next_id, float* logits) {
+    HX_CHECK_ARG(m && ids && T > 0);
+    if (seq < 0 || seq >= m->batch) return hx_fail(HX_ERR_ARG, "sequence %d outside the batch of %d", seq, m->batch);
+    if (T > m->kv_cap) return hx_fail(HX_ERR_STATE, "prompt of %d tokens exceeds the KV capacity %d", T, m->kv_cap);
+    for (int i = 0; i < T; i++) if (ids[i] < 0 || ids[i] >= m->gcfg.vocab) return hx_fail(HX_ERR_ARG, "token %d outside the vocabulary", ids[i]);
+    int rc = run_prefill(m, ids, T, seq); if (rc) return rc;
+    if (next_id) HX_CUDA(cudaMemcpyAsync(next_id, m->d_tok, 4, cudaMemcpyDeviceToHost, m->st));
+    if (logits) HX_CUDA(cudaMemcpyAsync(logits, m->logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToHost, m->st));
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    return persist_check(m);
 }
 
 HX_API int hx_decode_loop(hx_model* m, const int32_t* ids, int pos0, int n_steps, int32_t* out_ids, float* ms) {

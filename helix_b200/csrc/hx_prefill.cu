@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(256) k_pf_qkpost(float* __restrict__ qkv, int 
                                                     const float* __restrict__ cosT, const float* __restrict__ sinT,
                                                     float* __restrict__ kc, float* __restrict__ vc, int cap) {
     const int hs = blockIdx.x, t = blockIdx.y, e = threadIdx.x, half = DH >> 1, pos = wh.pos_arr ? wh.pos_arr[t] : *wh.posp + t;
-    const size_t seq_off = wh.seq_arr ? (size_t)wh.seq_arr[t] * wh.seq_stride : 0;
+    const size_t seq_off = wh.seq_arr ? (size_t)wh.seq_arr[t] * wh.seq_stride : (wh.seqp ? (size_t)(*wh.seqp) * wh.seq_stride : 0);
     const int sec = hs < NH ? 0 : (hs < NH + NKV ? 1 : 2);
     float* row = qkv + (size_t)t * ld + (size_t)hs * DH;
     __shared__ float sm[256]; __shared__ float red[8];
@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(PF_AT) k_pf_attn(const float* __restrict__ qkv
     const int kvh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int NW = PF_AT / 32;
     const int T = (wh.pos_arr ? wh.pos_arr[t] : *wh.posp + t) + 1;
-    const size_t seq_off = wh.seq_arr ? (size_t)wh.seq_arr[t] * wh.seq_stride : 0;
+    const size_t seq_off = wh.seq_arr ? (size_t)wh.seq_arr[t] * wh.seq_stride : (wh.seqp ? (size_t)(*wh.seqp) * wh.seq_stride : 0);
     float* sq = smf;                   // [GRP][DH]
     float* sp = smf + GRP * DH;        // [GRP][PF_KT]
     float* sacc = sp + GRP * PF_KT;    // [nsub][GRP][DH] partial outputs of the key subsets

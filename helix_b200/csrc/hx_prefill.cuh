@@ -8,7 +8,8 @@
 // Where the tokens of a chunk sit.  Prefill: consecutive positions of one sequence starting at *posp (device memory, so
 // that the launches of a chunk can be replayed as one CUDA graph).  Batched decode: token t is at position pos_arr[t] of
 // sequence seq_arr[t], whose KV cache starts seq_stride floats after the previous sequence's.
-struct HxPfWhere { const int* posp; const int* pos_arr; const int* seq_arr; size_t seq_stride; };
+// With pos_arr == null and seqp != null the whole chunk belongs to sequence *seqp (prefill into one KV slot of a batch).
+struct HxPfWhere { const int* posp; const int* pos_arr; const int* seq_arr; size_t seq_stride; const int* seqp; };
 
 // Positions are read from device memory (*posp = position of the chunk's first token) so that the launches of a
 // chunk can be replayed as one CUDA graph.

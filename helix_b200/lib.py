@@ -112,6 +112,7 @@ _SIGS = {
     "hx_model_reset": (C.c_int, [C.c_void_p]),
     "hx_decode_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "hx_prefill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "hx_prefill_seq": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "hx_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "hx_model_last_stats": (C.c_int, [C.c_void_p, C.POINTER(HxStepStats)]),
     "hx_model_engine": (C.c_char_p, [C.c_void_p]),
@@ -344,6 +345,14 @@ class Model:
         nxt = np.zeros(1, np.int32)
         lg = np.empty(self.vocab, np.float32) if want_logits else None
         check(lib().hx_prefill(self.h, ids.ctypes.data, len(ids), nxt.ctypes.data, lg.ctypes.data if want_logits else None))
+        return (int(nxt[0]), lg) if want_logits else int(nxt[0])
+
+    def prefill_seq(self, seq, ids, want_logits=False):
+        """Prompt of sequence `seq` of a batch into its KV slot; returns the arg-max token (and the logits)."""
+        ids = np.ascontiguousarray(ids, np.int32)
+        nxt = np.zeros(1, np.int32)
+        lg = np.empty(self.vocab, np.float32) if want_logits else None
+        check(lib().hx_prefill_seq(self.h, seq, ids.ctypes.data, len(ids), nxt.ctypes.data, lg.ctypes.data if want_logits else None))
         return (int(nxt[0]), lg) if want_logits else int(nxt[0])
 
     def generate(self, prompt, n_new):

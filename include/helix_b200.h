@@ -211,18 +211,23 @@ int hx_model_sha256(const hx_model* m, char hex[65]);
 /* Forget the KV cache (gpt2_infer.c:3354 resets kv_len per request). */
 int hx_model_reset(hx_model* m);
 
-/* One decode step for every sequence of the batch: ids[batch] are the tokens at position `pos`
- * (HOST pointer); on return next_ids[batch] (HOST, may be NULL) holds the arg-max token and, when
- * logits != NULL, logits[batch*vocab] (HOST) holds the f32 logits.
+/* One decode step of sequence 0 (KV slot 0; the other slots of a model created with batch > 1 are driven by
+ * hx_prefill_seq / hx_decode_batch): ids[0] is the token at position `pos` (HOST pointer); on return next_ids[0]
+ * (HOST, may be NULL) holds the arg-max token and, when logits != NULL, logits[vocab] (HOST) the f32 logits.
  * Replaces decode_step_llama + the host argmax, gpt2_infer.c:1341-1613, 1735-1739. */
 int hx_decode_step(hx_model* m, const int32_t* ids, int pos, int32_t* next_ids, float* logits);
 
-/* Prefill ids[batch*T] (HOST, row-major per sequence) into the KV cache and return the arg-max of
- * the last position (and its logits when logits != NULL).  Replaces forward_full, :1297-1333. */
+/* Prefill ids[T] (HOST) into KV slot 0 and return the arg-max of the last position in next_ids[0] (and its
+ * logits[vocab] when logits != NULL).  Replaces forward_full, :1297-1333. */
 int hx_prefill(hx_model* m, const int32_t* ids, int T, int32_t* next_ids, float* logits);
 
+/* hx_prefill for sequence `seq` of a model created with batch > 1: the prompt goes into that sequence's KV slot
+ * (chunks through the tcgen05 GEMM), next_id / logits as hx_prefill.  hx_decode_batch(_loop) then advances all slots
+ * together.  The reference runs one sequence at a time (run_generate, gpt2_infer.c:3123-3195). */
+int hx_prefill_seq(hx_model* m, int seq, const int32_t* ids, int T, int32_t* next_id, float* logits);
+
 /* Greedy generation, tokens never leave the GPU between steps: prefill the prompt, then n_new
- * steps feeding each arg-max back.  out_ids[batch*n_new] HOST.  Replaces run_generate, :3123-3195.
+ * steps feeding each arg-max back, on sequence 0.  out_ids[n_new] HOST.  Replaces run_generate, :3123-3195.
  * ms_decode (may be NULL) receives the device time of the decode steps alone. */
 int hx_generate_greedy(hx_model* m, const int32_t* prompt, int T, int n_new, int32_t* out_ids,
                        float* ms_prefill, float* ms_decode);
@@ -250,8 +255,8 @@ int hx_model_debug_waits(hx_model* m, unsigned wait_limit, int inject_stall);
 int hx_model_set_profile(hx_model* m, int on);
 
 /* Run n_steps decode steps starting at position pos0 with the KV cache as it stands, feeding back
- * the arg-max (first token ids[batch], HOST).  Used by the benchmark: inputs resident, one timed
- * region.  out_ids[batch*n_steps] may be NULL. */
+ * the arg-max (first token ids[0], HOST), on sequence 0.  Used by the benchmark: inputs resident, one timed
+ * region.  out_ids[n_steps] may be NULL. */
 int hx_decode_loop(hx_model* m, const int32_t* ids, int pos0, int n_steps, int32_t* out_ids, float* ms);
 
 /* Batched decode (independent sequences sharing one weight copy, 64 per GPU in the benchmark).  The model is created with

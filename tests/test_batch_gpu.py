@@ -31,3 +31,23 @@ def test_batched_decode_matches_single_sequence_checker(which, nseq, tiny_file, 
     again = gm.decode_batch(ids, pos)
     assert np.array_equal(again, np.array([want[i, G - (i % 3)] for i in range(nseq)]))
     gm.close(); om.close()
+
+
+def test_prefill_into_slots_then_batched_decode(ragged_file):
+    """Every sequence of a batch gets its own prompt through the chunked prefill into its own KV slot, then all slots
+    decode together; tokens must equal the checker's greedy continuation of each prompt on its own."""
+    nseq, G = 4, 6
+    om = ol.OracleModel(ragged_file, kv_cap=64)
+    rng = np.random.default_rng(77)
+    lens = [19, 16, 5, 33]                            # ragged chunks, one exact chunk, shorter than a chunk, two chunks + 1
+    prompts = [rng.integers(0, om.NV, n).astype(np.int32) for n in lens]
+    want = [om.generate(p, G + 1) for p in prompts]
+    gm = hb.Model.load(ragged_file, kv_cap=64, batch=nseq)
+    first = np.array([gm.prefill_seq(s, prompts[s]) for s in range(nseq)], np.int32)
+    assert list(first) == [int(w[0]) for w in want]
+    toks, pos = first.copy(), np.array(lens, np.int32)
+    for g in range(G):                                # ragged positions: each sequence continues at its own length
+        toks = gm.decode_batch(toks, pos)
+        assert list(toks) == [int(w[g + 1]) for w in want], g
+        pos += 1
+    gm.close(); om.close()
