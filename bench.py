@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """Benchmark of the NVFP4 decode path: greedy batch-1 decode of a Qwen3-8B-shaped model with seeded
-synthetic weights (BASELINE.json config 3: 512-token prompt, 256 new tokens).
+synthetic weights, 512-token prompt, 256 new tokens.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
@@ -10,6 +10,14 @@ ranks); `e2e` is the same metric through the public per-token call hx_decode_ste
 (token id in, next id and the logits row out, every token).  With N > 1 each GPU holds a full weight
 copy and decodes its own sequence (independent sequences, no data-path collective): weak scaling.
 
+Beside the headline the line carries
+  parity         logits and greedy tokens of the GPU path against the CPU restatement on the same weights
+  reference_gpu  the reference's own worker (its C host program + its own compiler's PTX) on this GPU, same model
+                 shape at reduced depth, next to this library at that depth
+  batch64        64 independent sequences, 2048-token prompts + 128 decoded tokens each, split over the GPUs
+  tp             the Qwen3-32B shape as ONE tensor-parallel group over the N GPUs (N = 1: one GPU)
+  quantizer, gpt2, prefill, batched_decode   the other configurations of the path.
+
 `--impl reference` times the CPU restatement of the reference worker's decode (oracle/hx_oracle.c, all
 host threads) on the same model shape; rank 0 alone runs it.
 """
@@ -17,9 +25,11 @@ import argparse
 import ctypes as C
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 
@@ -29,8 +39,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 PROMPT_LEN, NEW_TOKENS = 512, 256
-BATCH_PROBE = 64                # sequences of the batched-throughput probe (BASELINE config 4 runs 64 per GPU)
-NCU_TRAFFIC_RATIO = 1.010      # measured DRAM bytes / algorithmic bytes of k_decode_tc (profiles/)
+BATCH_SEQS, BATCH_PROMPT, BATCH_NEW = 64, 2048, 128      # the batched-throughput configuration
+TP_PROMPT, TP_NEW = 4096, 64                             # 32B shape: context length, decoded tokens timed
+# DRAM bytes / algorithmic bytes of the decode kernel, from one ncu capture of a 4-layer launch (see the summary
+# under profiles/ named for the kernel); re-measured when the kernel's memory traffic changes
+NCU_TRAFFIC_RATIO = 1.010
 WORKLOAD = "qwen3-8b-shape nvfp4 greedy decode, batch 1, 512-token prompt + 256 new tokens"
 
 
@@ -171,13 +184,18 @@ def synth_image_on_host(shape, seed):
     return img
 
 
-def cpu_decode_tok_s(image, n_tokens, kv_cap=64):
-    """tokens/s of the CPU restatement decoding n_tokens greedy tokens from an empty cache."""
+def oracle_lib_all_cores():
     if "oracle_lib" not in sys.modules:
         # all host cores, also under torchrun (which exports OMP_NUM_THREADS=1); read when the OpenMP runtime starts
         os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as ol
+    return ol
+
+
+def cpu_decode_tok_s(image, n_tokens, kv_cap=64):
+    """tokens/s of the CPU restatement decoding n_tokens greedy tokens from an empty cache."""
+    ol = oracle_lib_all_cores()
     om = ol.OracleModel(image=image, kv_cap=kv_cap)
     tok, t0 = 1, time.perf_counter()
     for pos in range(n_tokens):
@@ -185,6 +203,48 @@ def cpu_decode_tok_s(image, n_tokens, kv_cap=64):
     dt = time.perf_counter() - t0
     om.close()
     return n_tokens / dt, ol.oracle().orc_num_threads()
+
+
+def cpu_baseline_with_parity(model, budget_s=20.0):
+    """The CPU restatement on the SAME weights (HXGW v3 image exported from HBM), teacher-forced along the GPU's
+    own greedy tokens from an empty cache: tokens/s of the CPU leg and, position by position, the logits and
+    arg-max of both sides."""
+    ol = oracle_lib_all_cores()
+    image = model.v3_image()
+    om = ol.OracleModel(image=image, kv_cap=64)
+    gpu_tok, cpu_free, max_abs, frel, agree_tf, cpu_s = [1], 1, 0.0, 0.0, 0, 0.0
+    n, pos, free_ok, free_agree = 2, 0, True, 0
+    while pos < n:
+        tok = gpu_tok[pos]
+        nx, lg = model.decode_step(tok, pos, want_logits=True)
+        t0 = time.perf_counter()
+        lo = om.decode(tok, pos)
+        dt = time.perf_counter() - t0
+        cpu_s += dt
+        if pos == 0:
+            n = int(max(2, min(16, budget_s / dt)))
+        d = np.abs(lg - lo)
+        max_abs = max(max_abs, float(d.max()))
+        frel = max(frel, float(np.max(d / np.maximum(np.abs(lo), 1.0))))
+        ca = int(np.argmax(lo))
+        agree_tf += int(ca == nx)
+        # free-running: the CPU would have fed its own arg-max; the runs coincide as long as every earlier one agreed
+        free_ok = free_ok and ca == nx
+        free_agree += int(free_ok)
+        gpu_tok.append(nx)
+        pos += 1
+    om.close()
+    cores = ol.oracle().orc_num_threads()
+    cpu = {"value": n / cpu_s, "unit": "tok/s", "cores": cores, "kind": "port",
+           "sample": f"{n} tokens from an empty KV cache on the same weights (HXGW v3 image exported from the GPU), full "
+                     "model + lm_head, teacher-forced along the GPU's greedy tokens; CPU restatement of the reference "
+                     "decode, OpenMP over rows"}
+    parity = {"tokens": n, "logit_max_abs": max_abs, "floored_rel": frel,
+              "greedy_agree_teacher_forced": agree_tf / n, "greedy_agree_free": free_agree / n,
+              "bars": "reference: max-abs < 5e-2, |d| / max(|ref|, 1) < 1e-3, arg-max equal",
+              "against": "CPU restatement, itself pinned by the reference's GPU worker (tests/golden/ref_worker_logits.npz)"}
+    del image
+    return cpu, parity
 
 
 def run_reference(args):
@@ -218,6 +278,119 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def reference_gpu_leg(hb, layers, n_prompt=16, n_gen=24):
+    """The reference's own GPU path on this GPU: its worker (helixc/runtime/gpt2_infer.c compiled unmodified) driving
+    the PTX its own compiler emits, resident fused decode path, on an HXGW v3 file this library exports -- beside this
+    library on the same file.  Depth is reduced so that the file (the f32 embedding alone is 2.5 GB) is written and
+    loaded within seconds; widths, vocabulary and per-layer work are the benchmark's."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    kovc = os.path.join(ol.ORACLE_DIR, "_ref", "kovc")
+    if not (os.path.exists(ol.REF_INFER) and os.path.exists(os.path.join(kovc, "model14.ptx"))):
+        return {"unavailable": "oracle/_ref/gpt2_infer or oracle/_ref/kovc/*.ptx not built (make -C oracle ref)"}
+    shape = dict(hb.QWEN3_8B); shape["n_layers"] = layers
+    model = hb.Model.synth(shape, seed=1, kv_cap=n_prompt + n_gen + 8, flags=hb.HX_LOAD_KEEP_COMMITTED)
+    prompt = np.random.default_rng(4).integers(0, shape["vocab"], n_prompt).astype(np.int32)
+    model.generate(prompt, 4)
+    ours, ms_p, ms_d = model.generate(prompt, n_gen)
+    out = {"layers": layers, "prompt": n_prompt, "new_tokens": n_gen, "ours_ms_per_token": ms_d / (n_gen - 1),
+           "engine": model.engine()}
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "m.weights")
+        model.save_v3(path)
+        model.close()
+        open(os.path.join(d, "ids.txt"), "w").write(" ".join(str(int(t)) for t in prompt) + "\n")
+        env = {k: v for k, v in os.environ.items() if not k.startswith("HX_")}
+        env.update(HX_KV="1", HX_FAST="1", HX_PACKEDRES="1", HX_FUSEDGEMV="1", HX_GEMV3="1", HX_FUSEDATTN="1", HX_GENPROF="1",
+                   HX_DQPTX=os.path.join(kovc, "nvfp4_dequant_tiled.ptx"), HX_FUSEDGEMV_PTX=os.path.join(kovc, "dequant_gemv_blockred.ptx"),
+                   HX_GEMV3_PTX=os.path.join(kovc, "dequant_gemv_warp.ptx"), HX_FUSEDATTN_PTX=os.path.join(kovc, "fused_decode_attn.ptx"))
+        t0 = time.perf_counter()
+        try:
+            p = subprocess.run([ol.REF_INFER, os.path.join(kovc, "model14.ptx"), path, "--generate", str(n_gen), os.path.join(d, "ids.txt")],
+                               env=env, cwd=d, capture_output=True, text=True, timeout=240)
+        except subprocess.TimeoutExpired:
+            return dict(out, unavailable="the reference worker did not finish within 240 s")
+        out["worker_wall_s"] = time.perf_counter() - t0
+    txt = p.stdout + p.stderr
+    m = re.search(r"\[genprof\] decode (\d+) steps in ([0-9.]+)s = ([0-9.]+) s/tok", txt)
+    g = re.search(r"HELIX_GEN_IDS:((?: \d+)+)", txt)
+    if p.returncode != 0 or not m or not g:
+        return dict(out, unavailable="the reference worker failed: " + txt[-300:].replace("\n", " | "))
+    ref_ids = [int(x) for x in g.group(1).split()][n_prompt:]
+    out.update(reference_ms_per_token=float(m.group(3)) * 1e3, reference_decode_steps=int(m.group(1)),
+               tokens_identical=ref_ids == [int(t) for t in ours],
+               ratio=float(m.group(3)) * 1e3 / (ms_d / (n_gen - 1)),
+               path="gpt2_infer.c + kovc PTX (sm_86 PTX JIT-compiled by the driver), HX_KV HX_FAST HX_PACKEDRES HX_FUSEDGEMV "
+                    "HX_GEMV3 HX_FUSEDATTN, timed by its own HX_GENPROF")
+    return out
+
+
+def batch64_leg(hb, L, check, dist, rank, ngpus, shape):
+    """64 independent sequences, each a 2048-token prompt then 128 greedy tokens, split over the GPUs; every GPU
+    holds its own weight copy, prefills its sequences into their KV slots and decodes them together."""
+    S = max(1, BATCH_SEQS // ngpus)
+    model = hb.Model.synth(shape, seed=1, kv_cap=BATCH_PROMPT + BATCH_NEW + 8, batch=S)
+    rng = np.random.default_rng(100 + rank)
+    prompts = rng.integers(0, shape["vocab"], (S, BATCH_PROMPT)).astype(np.int32)
+    model.prefill_seq(0, prompts[0][:64])                     # warm-up: graph capture of a chunk, first launches
+    check(L.hx_sync())
+    t0 = time.perf_counter()
+    first = np.zeros(S, np.int32)
+    first[0] = model.prefill_seq(0, prompts[0])
+    t_one = time.perf_counter() - t0
+    # the whole job must stay within the benchmark's time budget: fewer sequences per GPU when one prompt is slow
+    S_run = S if t_one * S < 80.0 else max(4, int(80.0 / t_one))
+    for s in range(1, S_run):
+        first[s] = model.prefill_seq(s, prompts[s])
+    prefill_s = all_max(dist, time.perf_counter() - t0)
+    model.decode_batch_loop(first[:S_run], BATCH_PROMPT, 2)
+    _, dms = model.decode_batch_loop(first[:S_run], BATCH_PROMPT, BATCH_NEW - 1)
+    dms = all_max(dist, dms)
+    model.close()
+    n_seq = S_run * ngpus
+    ptok, dtok = n_seq * BATCH_PROMPT, n_seq * (BATCH_NEW - 1)
+    return {"sequences": n_seq, "sequences_asked": BATCH_SEQS, "per_gpu": S_run, "prompt": BATCH_PROMPT, "new_tokens": BATCH_NEW,
+            "prefill_s": prefill_s, "prefill_tok_per_s": ptok / prefill_s, "decode_s": dms * 1e-3, "decode_tok_per_s": dtok / (dms * 1e-3),
+            "total_tok_per_s": (ptok + dtok) / (prefill_s + dms * 1e-3),
+            "path": "hx_prefill_seq per sequence (16-token chunks through the tcgen05 GEMM), then hx_decode_batch_loop "
+                    "(16 sequences per GEMM); replicas, no exchange between GPUs"}
+
+
+def tp_leg(hb, L, check, dist, rank, ngpus, peak):
+    """The Qwen3-32B shape as one tensor-parallel group over the GPUs of the run, batch 1, decoding at a 4096-token
+    context (KV rows seeded synthetically: inside a tensor-parallel group the prompt is still fed token by token)."""
+    shape = dict(hb.QWEN3_32B)
+    cap = TP_PROMPT + TP_NEW + 16
+    if ngpus > 1:
+        import torch
+        model = hb.Model.synth(shape, seed=1, kv_cap=cap, tp_rank=rank, tp_size=ngpus)
+        mine = torch.tensor(list(model.tp_handle()), dtype=torch.uint8)
+        allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(ngpus)]
+        dist.all_gather(allh, mine)
+        model.tp_connect([bytes(h.tolist()) for h in allh])
+        dist.barrier()
+    else:
+        model = hb.Model.synth(shape, seed=1, kv_cap=cap)
+    model.fill_kv(TP_PROMPT, 13)
+    model.decode_loop(7, TP_PROMPT, 8)
+    if dist is not None:
+        dist.barrier()
+    _, ms = model.decode_loop(7, TP_PROMPT, TP_NEW)
+    ms = all_max(dist, ms)
+    cfg = dict(shape)
+    wbytes, kvb, emb = algorithmic_bytes_per_token(cfg, TP_PROMPT + TP_NEW // 2)
+    per_gpu = (wbytes + kvb) / ngpus + emb
+    ms_tok = ms / TP_NEW
+    engine = model.engine()
+    model.close()
+    return {"model": "qwen3-32b-shape", "tp": ngpus, "batch": 1, "context": TP_PROMPT, "new_tokens": TP_NEW, "tok_per_s": 1e3 / ms_tok,
+            "ms_per_token": ms_tok, "per_gpu_bytes_per_token": per_gpu, "per_gpu_frac_of_hbm_peak": per_gpu / (ms_tok * 1e-3) / 1e9 / peak,
+            "engine": engine, "batch16": None,
+            "batch16_note": "not built: a tensor-parallel shard decodes one sequence",
+            "exchange": "partial rows of o_proj / down_proj stored as (value, epoch) pairs into every rank's buffer over NVLink "
+                        "inside the decode kernel, summed in rank order; no NCCL kernel" if ngpus > 1 else "none (one GPU)"}
+
+
 def run_ours(args):
     import helix_b200 as hb
     from helix_b200.lib import check, lib
@@ -240,7 +413,7 @@ def run_ours(args):
         model.tp_connect([bytes(h.tolist()) for h in allh])
         dist.barrier()
     else:
-        model = hb.Model.synth(shape, seed=1, kv_cap=PROMPT_LEN + NEW_TOKENS + 8, flags=keep, batch=BATCH_PROBE)
+        model = hb.Model.synth(shape, seed=1, kv_cap=PROMPT_LEN + NEW_TOKENS + 8, flags=keep)
     cfgd = model.cfg.as_dict()
     if tp:                                              # the shard reports its own slice; bytes are counted for the whole model
         for k in ("n_heads", "n_kv_heads", "d_ff", "vocab"):
@@ -294,9 +467,8 @@ def run_ours(args):
                     f"{4 * cfgd['n_layers'] + 1} linears, attention, norms, arg-max)",
                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                     "traffic": token_bytes * NCU_TRAFFIC_RATIO if kname in ("k_decode_tc", "k_decode_df") else None,
-                    "traffic_source": "ncu dram__bytes_read+write of one launch of the 4-layer case (profiles/"
-                                      "k_decode_tc_qwen3-8b-shape_4layers.md) = 1.010 x its algorithmic bytes, scaled to "
-                                      "this launch's algorithmic bytes (traffic grows with the layers streamed)",
+                    "traffic_source": f"ncu dram__bytes_read+write of one launch of the 4-layer case = {NCU_TRAFFIC_RATIO} x its algorithmic "
+                                      "bytes, scaled to this launch's algorithmic bytes (traffic grows with the layers streamed)",
                     "peak_source": peak_src, "algorithmic_bytes_per_launch": token_bytes, "avg_launch_us": avg_ms * 1e3,
                     "token_bytes": {"weights": wbytes, "kv_mid_run": kvbytes_mid, "embedding_row": embbytes},
                     "whole_token_frac": token_bytes * value / args.gpus / 1e9 / peak}
@@ -338,9 +510,10 @@ def run_ours(args):
            "h2d_bytes_per_step": NEW_TOKENS * 4, "d2h_bytes_per_step": NEW_TOKENS * (4 + shape["vocab"] * 4),
            "api": "hx_decode_step per token: token id H2D, next id + f32 logits row D2H (what the reference worker reads back)"}
 
+    extras = not args.no_e2e and not args.layers
     # the other half of the path: the NVFP4 quantizer on the single-matrix shape (12288 x 4096 f32), device resident
     quant = None
-    if rank == 0 and not args.no_e2e:
+    if rank == 0 and extras:
         rows, K = 12288, 4096
         kp = L.hx_kpad(K)
         w = (np.random.default_rng(7).standard_normal((rows, K), dtype=np.float32) * np.float32(0.02))
@@ -363,21 +536,9 @@ def run_ours(args):
         for b in (dw, dW, dmic, dts):
             b.free()
 
-    # batched throughput: 64 independent sequences sharing the weight copy, one token each per step
-    batched = None
-    if not tp and not args.no_e2e:
-        model.fill_kv(PROMPT_LEN, 11)                  # synthetic KV rows for every sequence up to the prompt length
-        bids = np.random.default_rng(9 + rank).integers(0, shape["vocab"], BATCH_PROBE).astype(np.int32)
-        model.decode_batch_loop(bids, PROMPT_LEN, 2)
-        _, bms = model.decode_batch_loop(bids, PROMPT_LEN, 8)
-        bms = all_max(dist, bms)
-        batched = {"sequences_per_gpu": BATCH_PROBE, "steps": 8, "ms_per_step": bms / 8,
-                   "tok_per_s": args.gpus * BATCH_PROBE * 8 / (bms * 1e-3),
-                   "path": "hx_decode_batch_loop: chunks of 16 sequences per tcgen05 GEMM, per-sequence KV append and attention"}
-
-    # config 2: GPT-2-124M shape, all linears NVFP4, 32-token prompt + 128 greedy tokens, batch 1
+    # GPT-2-124M shape, all linears NVFP4, 32-token prompt + 128 greedy tokens, batch 1
     gpt2 = None
-    if rank == 0 and not args.no_e2e and not tp:
+    if rank == 0 and extras and not tp:
         gs = dict(hb.GPT2_124M)
         grng = np.random.default_rng(5)
         gn = lambda *sh: grng.standard_normal(sh, dtype=np.float32) * np.float32(0.02)
@@ -395,16 +556,21 @@ def run_ours(args):
                 "engine": g2.engine(), "note": "per-op kernels in one CUDA graph per token (LayerNorm/bias/GELU fused into the NVFP4 GEMV)"}
         g2.close(); del gw
 
-    cpu = None
+    cpu = parity = None
     if rank == 0 and args.gpus == 1 and not args.no_cpu_baseline:      # reported at N = 1 only
-        image = model.v3_image()                       # the same weights, HXGW v3 bytes exported from HBM
-        v1, cores = cpu_decode_tok_s(image, 1)
-        n = int(max(2, min(16, 20.0 * v1)))
-        v, cores = cpu_decode_tok_s(image, n)
-        cpu = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port",
-               "sample": f"{n} greedy tokens from an empty KV cache on the same weights (HXGW v3 image exported from the GPU), "
-                         "full model + lm_head; CPU restatement of the reference decode, OpenMP over rows"}
-        del image
+        cpu, parity = cpu_baseline_with_parity(model)
+    model.close()
+
+    ref_gpu = batch64 = tpl = None
+    if extras and not tp:
+        if rank == 0 and args.gpus == 1 and not args.no_reference_gpu:
+            ref_gpu = reference_gpu_leg(hb, args.reference_gpu_layers)
+        if dist is not None:
+            dist.barrier()
+        if not args.no_batch64:
+            batch64 = batch64_leg(hb, L, check, dist, rank, args.gpus, shape)
+        if not args.no_tp_leg:
+            tpl = tp_leg(hb, L, check, dist, rank, args.gpus, peak)
     if rank == 0:
         line = {"metric": "nvfp4_decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak",
@@ -415,13 +581,12 @@ def run_ours(args):
                                            f"replicas x{args.gpus} (one sequence per GPU)") if args.gpus > 1 else "single GPU",
                            "l2": "weights (4.26 GB per token) exceed the 126 MB L2, no flush needed",
                            "tokens_per_step": NEW_TOKENS, "weight_bytes_decode_layout": dbytes, "weight_bytes_committed_layout": cbytes},
-                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-                "quantizer": quant, "batched_decode": batched, "gpt2": gpt2,
+                "roofline": roofline, "cpu_baseline": cpu, "parity": parity, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+                "reference_gpu": ref_gpu, "batch64": batch64, "tp": tpl, "quantizer": quant, "gpt2": gpt2,
                 "prefill": {"tokens": PROMPT_LEN, "ms": prefill_s * 1e3, "tok_per_s": PROMPT_LEN / prefill_s,
                             "path": "chunks of 16 tokens, one tcgen05 block-scaled GEMM per linear (exact digit columns), host ids in"},
                 "ms_per_token": ms_max / args.steps / NEW_TOKENS, "last_tokens": [int(t) for t in toks[-4:]]}
         print(json.dumps(line), flush=True)
-    model.close()
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -437,7 +602,11 @@ def main():
     ap.add_argument("--parallelism", default="replicas", choices=["replicas", "tp"],
                     help="N > 1: independent replicas (one sequence per GPU, weak scaling) or one tensor-parallel group (strong)")
     ap.add_argument("--model", default="8b", choices=["8b", "32b"], help="Qwen3-8B shape (the headline workload) or Qwen3-32B shape")
-    ap.add_argument("--no-e2e", action="store_true", help="skip the per-token host-buffer loop (profiler captures)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the per-token host-buffer loop and the side legs (profiler captures)")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip the run of the reference's own GPU worker")
+    ap.add_argument("--reference-gpu-layers", type=int, default=4, help="depth of the model the reference GPU worker is timed on")
+    ap.add_argument("--no-batch64", action="store_true", help="skip the 64-sequence batched-throughput leg")
+    ap.add_argument("--no-tp-leg", action="store_true", help="skip the Qwen3-32B-shape tensor-parallel leg")
     ap.add_argument("--layers", type=int, default=0, help="reduced depth for profiler captures (0 = the full 36)")
     ap.add_argument("--new-tokens", type=int, default=0, help="tokens per step for profiler captures (0 = 256)")
     ap.add_argument("--prompt-len", type=int, default=0, help="prompt length for profiler captures (0 = 512)")
