@@ -42,7 +42,7 @@ PROMPT_LEN, NEW_TOKENS = 512, 256
 BATCH_SEQS, BATCH_PROMPT, BATCH_NEW = 64, 2048, 128      # the batched-throughput configuration
 TP_PROMPT, TP_NEW = 4096, 64                             # 32B shape: context length, decoded tokens timed
 # DRAM bytes / algorithmic bytes of the decode kernel, from one ncu capture of a 4-layer launch (see the summary
-# under profiles/ named for the kernel); re-measured when the kernel's memory traffic changes
+# kept with the ncu summaries of that kernel); re-measured when the kernel's memory traffic changes
 NCU_TRAFFIC_RATIO = 1.010
 WORKLOAD = "qwen3-8b-shape nvfp4 greedy decode, batch 1, 512-token prompt + 256 new tokens"
 

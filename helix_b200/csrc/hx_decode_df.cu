@@ -49,11 +49,13 @@
 
 typedef unsigned long long u64;
 
-// per-phase time stamps of one CTA, debug builds only (-DHX_DF_STAMPS)
-#ifdef HX_DF_STAMPS
+// per-phase time stamps of one CTA, debug builds only (-DHX_DEBUG_STAMPS)
+#ifdef HX_DEBUG_STAMPS
 #define DF_STAMP(i) do { if (P.dbg && cta == P.dbg_cta && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg[pi * 16 + (i)] = _t; } } while (0)
+#define DF_MARK(ev) do { if (P.dbg_all && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg_all[((size_t)pi * gridDim.x + blockIdx.x) * 4 + (ev)] = _t; } } while (0)
 #else
 #define DF_STAMP(i) do { } while (0)
+#define DF_MARK(ev) do { } while (0)
 #endif
 
 namespace {

@@ -701,7 +701,9 @@ int init_persist(hx_model* m) {
     HX_CUDA(cudaMemset(m->d_bar, 0, 16));
     HX_CUDA(cudaMemset(m->d_err, 0, 16));
     m->bar_count = 0;
-    if (getenv("HX_PERSIST_DBG")) { if ((rc = dalloc(m, &m->d_dbg, (size_t)16 * (m->nph_decode + 4) + (size_t)m->nph_decode * m->grid_persist))) return rc; }
+#ifdef HX_DEBUG_STAMPS
+    if (getenv("HX_PERSIST_DBG")) { if ((rc = dalloc(m, &m->d_dbg, (size_t)16 * (m->nph_decode + 4) + (size_t)4 * m->nph_decode * m->grid_persist))) return rc; }
+#endif
     if (m->use_tc) {
         if ((rc = dalloc(m, &m->tc_partial, m->tc_units_max * 128 + 128))) return rc;
         if ((rc = dalloc(m, &m->tc_cnt, (size_t)m->tc_tiles_max + 8))) return rc;
@@ -726,7 +728,9 @@ int persist_step(hx_model* m, bool from_prompt, bool with_head) {
     P.am_val = m->am_val; P.am_idx = m->am_idx; P.am_cnt = m->am_cnt; P.next_tok = m->d_tok; P.pos_inc = m->d_pos;
     P.hist = m->d_hist; P.logits = m->logits; P.dig_bytes = m->dig_bytes;
     P.tok_by_pos = from_prompt ? 1 : 0; P.advance_pos = from_prompt ? 1 : 0;
+#ifdef HX_DEBUG_STAMPS
     P.dbg = m->d_dbg; P.dbg_all = m->d_dbg ? m->d_dbg + (size_t)16 * (m->nph_decode + 4) : nullptr; { const char* dc = getenv("HX_PERSIST_DBG"); P.dbg_cta = dc ? atoi(dc) - 1 : 0; if (P.dbg_cta < 0) P.dbg_cta = 0; }
+#endif
     P.tc_partial = m->tc_partial; P.tc_cnt = m->tc_cnt; P.bdig_bytes = m->bdig_bytes; P.tc_ring = m->tc_ring;
     P.tp_world = m->tp_world; P.tp_rank = m->tp_rank; P.tp_dm = m->cfg.d_model; P.tp_vocab_off = m->tp_rank * m->cfg.vocab;
     if (m->tp_world > 1) {
@@ -1014,7 +1018,8 @@ HX_API int hx_model_weight_bytes(const hx_model* m, uint64_t* decode_layout, uin
 }
 HX_API int hx_model_reset(hx_model* m) { HX_CHECK_ARG(m); m->kv_len = 0; return HX_OK; }
 HX_API int hx_model_last_stats(const hx_model* m, hx_step_stats* st) { HX_CHECK_ARG(m && st); *st = m->stats; return HX_OK; }
-// Debug: per-phase time stamps of CTA 0 from the last persistent launch (4 per phase, nanoseconds).
+#ifdef HX_DEBUG_STAMPS
+// Debug builds only: per-phase time stamps of one CTA from the last persistent launch (16 per phase, nanoseconds).
 HX_API int hx_model_phase_stamps(hx_model* m, unsigned long long* out, int max_phases, int* nphases) {
     HX_CHECK_ARG(m && out && nphases);
     if (!m->d_dbg) return hx_fail(HX_ERR_STATE, "set HX_PERSIST_DBG=1 before creating the model");
@@ -1027,12 +1032,13 @@ HX_API int hx_model_phase_stamps(hx_model* m, unsigned long long* out, int max_p
 HX_API int hx_model_phase_stamps_all(hx_model* m, unsigned long long* out, size_t max_words, int* nphases, int* grid) {
     HX_CHECK_ARG(m && out && nphases && grid);
     if (!m->d_dbg) return hx_fail(HX_ERR_STATE, "set HX_PERSIST_DBG=1 before creating the model");
-    const size_t n = (size_t)m->nph_decode * m->grid_persist;
+    const size_t n = (size_t)4 * m->nph_decode * m->grid_persist;      // four events per CTA and phase
     HX_CHECK_ARG(n <= max_words);
     HX_CUDA(cudaMemcpy(out, m->d_dbg + (size_t)16 * (m->nph_decode + 4), n * 8, cudaMemcpyDeviceToHost));
     *nphases = m->nph_decode; *grid = m->grid_persist;
     return HX_OK;
 }
+#endif
 // ---- tensor parallel: exchange-buffer handles ----------------------------------------------------------
 // The caller moves the 64-byte handles between the ranks' processes by any channel it has.
 HX_API int hx_model_tp_handle(hx_model* m, uint8_t handle[64]) {

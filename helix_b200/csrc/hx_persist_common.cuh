@@ -97,8 +97,13 @@ __device__ __forceinline__ AttPlan att_plan(const HxPhase& ph, int cta, int pos)
     return a;
 }
 
+#ifdef HX_DEBUG_STAMPS
 #define STAMP_ALL() do { if (P.dbg_all && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg_all[(size_t)pi * gridDim.x + blockIdx.x] = _t; } } while (0)
 #define STAMP(i) do { if (P.dbg && cta == P.dbg_cta && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg[pi * 16 + (i)] = _t; } } while (0)
+#else
+#define STAMP_ALL() do { } while (0)
+#define STAMP(i) do { } while (0)
+#endif
 
 // ------------------------------------------------------------------------------------------------
 // Attention phase of one CTA: (kv head, split of the cached positions); the GRP query heads of the kv

@@ -1,4 +1,4 @@
-"""GPT-2 decode (BASELINE config 2: LayerNorm, learned positions, biases, gelu_new, tied head, all linears NVFP4) on
+"""GPT-2 decode (the GPT-2-124M configuration: LayerNorm, learned positions, biases, gelu_new, tied head, all linears NVFP4) on
 the GPU against the fp32 CPU restatement of the reference's GPT-2 block fed with the same quantized weights.
 The reference has no NVFP4 GPT-2 path: parity is defined as quantizing each linear as [out][in] with the reference
 quantizer, dequantizing on the host and running the fp32 GPT-2 arithmetic."""

@@ -72,7 +72,7 @@ def test_quantizer_nonfinite_inputs():
 
 
 def test_config1_full_size_bit_exact_and_roundtrip():
-    """BASELINE config 1: W 12288x4096 N(0,0.02) from a seed, x N(0,1); codes, scales and ts bit-exact,
+    """The single-matrix round trip: W 12288x4096 N(0,0.02) from a seed, x N(0,1); codes, scales and ts bit-exact,
     y = dequant(W) x within rel 1e-3 of the checker's ascending f32 GEMV (the reference's per-GEMV bar,
     cuda_launch.c:2088)."""
     rng = np.random.default_rng(1)
