@@ -30,7 +30,9 @@
 // and frees its tensor memory.  The host reports HX_ERR_TIMEOUT.
 #define HX_TC_MAX_RING 10
 #define RING_SLOTS ((uint32_t)P.tc_ring)
-#define NCW 16
+#ifndef NCW
+#define NCW 8
+#endif
 #define NCT (NCW * 32)
 #define PT (NCT + 64)               // + producer warp (16) + MMA warp (17)
 // mbar_wait (hx_persist_common.cuh) reads its limit from the word after the abort flag it is given
@@ -85,47 +87,18 @@ __device__ __forceinline__ bool consumer_sync_any(int flag) {
     return r != 0;
 }
 
-// This CTA's run of cells [b0, b1) of the phase (same split as hx_persist_tc.cu / hx_tc_split).
-struct TcPlan { long long b0, b1, total; int C, k0, run, geff, P; };
-__device__ __forceinline__ TcPlan tc_plan(const HxPhase& ph, int cta, int grid) {
-    TcPlan p;
-    p.C = ph.ksteps >> 2;
-    p.total = (long long)ph.ntiles * p.C;
-    p.P = 0; p.geff = grid;
-    if (2 * ph.ntiles <= grid) {
-        p.P = min(grid / ph.ntiles, p.C);
-        if (cta < ph.ntiles * p.P) {
-            const int tile = cta / p.P, q = cta - tile * p.P;
-            p.b0 = (long long)tile * p.C + (q * p.C) / p.P; p.b1 = (long long)tile * p.C + ((q + 1) * p.C) / p.P;
-        } else { p.b0 = p.b1 = 0; }
-    } else {
-        p.geff = p.total < grid ? (int)p.total : grid;
-        if (cta >= p.geff) { p.b0 = p.b1 = 0; }
-        else if (p.total * (p.geff + 1) < 0x7FFFFFFFLL) {
-            const unsigned t32 = (unsigned)p.total, g32 = (unsigned)p.geff;
-            p.b0 = (unsigned)cta * t32 / g32; p.b1 = (unsigned)(cta + 1) * t32 / g32;
-        } else { p.b0 = (long long)cta * p.total / p.geff; p.b1 = (long long)(cta + 1) * p.total / p.geff; }
-    }
-    p.k0 = p.b0 < 0x7FFFFFFFLL ? (int)((unsigned)p.b0 % (unsigned)p.C) : (int)(p.b0 % p.C);
-    const long long n = p.b1 - p.b0;
-    p.run = n < p.C ? (int)n : p.C;
-    return p;
-}
-__device__ __forceinline__ int tc_owner(long long x, long long total, int grid) {
-    if ((x + 2) * grid + total < 0x7FFFFFFFLL) return (int)((((unsigned)x + 1u) * (unsigned)grid + (unsigned)total - 1u) / (unsigned)total) - 1;
-    return (int)(((x + 1) * grid + total - 1) / total) - 1;
-}
-
 struct SmemDf {
     uint64_t full[HX_TC_MAX_RING];
     uint64_t empty[HX_TC_MAX_RING];
     uint64_t acc_full[2], acc_empty[2], b_ready;
     float red[NCW * 2];
-    float att_m[8], att_l[8], att_r[8]; unsigned att_ax[8];
+    float att_m[8], att_l[8], att_r[8];
     float wgt[2304];                // merge weights of the attention splits, [head][split] (o_proj prologue)
     float bv[NCW]; int bi[NCW];
     float swi[128];
     HxPhase ph[2];
+    AttPlan ap; int att_ns, ap_tile_rows, ap_ntiles;      // attention work split of this launch (depends on the position only)
+    int tile_off[8], tile_slot[8];                        // ring slots of the attention tile in flight (K: 0.., V: 4..)
     unsigned ticket;
     uint32_t tmem_base;
     volatile int abort_flag; unsigned wait_limit;      // adjacent: bounded waits read the limit at (&abort_flag)[1]
@@ -202,11 +175,10 @@ __device__ __forceinline__ void df_wait8(const u64* p, unsigned ep, float (&v)[8
 }
 
 // ---- attention work split: the number of splits follows the context length (about 64 positions each) ----
-__device__ __forceinline__ int df_nsplit(const HxPhase& ph, int pos) {
-    const int ns = (pos + 64) >> 6;
-    return ns < 1 ? 1 : (ns > ph.nsplit ? ph.nsplit : ns);
-}
-__device__ __forceinline__ AttPlan att_plan_df(const HxPhase& ph, int ns, int cta, int pos) {
+__device__ __noinline__ AttPlan att_plan_df(const HxPersist& P, int cta, int pos, int nring, int* ns_out, int* tile_rows, int* ntiles) {
+    int ns = (pos + 64) >> 6;
+    ns = ns < 1 ? 1 : (ns > P.att_nsplit ? P.att_nsplit : ns);
+    struct { int NKV, DH; } ph = {P.att_nkv, P.att_dh};
     AttPlan a;
     a.active = cta < ph.NKV * ns;
     a.kv = cta / ns; a.split = cta % ns;
@@ -216,167 +188,177 @@ __device__ __forceinline__ AttPlan att_plan_df(const HxPhase& ph, int ns, int ct
     else { a.has_new = (pos >= a.t0 && pos < a.t1); a.n_old = (a.t1 - a.t0) - a.has_new; }
     a.rows_per_slot = HX_RING_SLOT / (ph.DH * 4);
     a.nslots = (a.n_old + a.rows_per_slot - 1) / a.rows_per_slot;      // K slots == V slots
+    const AttPlan2 a2 = att_plan2(a, nring);
+    *ns_out = ns; *tile_rows = a2.tile_rows; *ntiles = a2.ntiles;
     return a;
 }
 
 // ------------------------------------------------------------------------------------------------
-// Attention phase of one CTA: (kv head, split of the cached positions).  q (normed, rotated) and this
-// position's k and v arrive as pairs from the qkv epilogue; older rows stream through the ring from the cache.
-// Per ring tile of positions: scores with one thread per (head, position), soft-max statistics by one warp
-// per head, P*V with one thread per (head, dimension).  The split's partial output, (max, sum) and magnitude
-// bound leave as pairs; the o_proj prologue merges the splits.
+// Attention phase of one CTA: (kv head, split of the cached positions); the split of the work depends on the
+// position only and is worked out once per launch (SmemDf::ap).  q (normed, rotated) and this position's k and v
+// arrive as pairs from the qkv epilogue; older rows stream through the ring from the cache.
+//  * scores: eight threads per (row, head), each holding its DH/8 query dimensions in registers, one shuffle
+//    tree per row;
+//  * soft-max statistics (online, m seeded -1e8 like the reference, fused_decode_attn_kernel.hx:74-102): one warp
+//    per head;
+//  * P*V: a thread owns four output dimensions of ALL heads of the group over a subset of the rows (a V row is read
+//    once, not once per head); the subsets are folded through shared memory.
+// The split's partial output and (max, sum) leave as pairs; the o_proj prologue merges the splits.
+// The phase runs once per layer from a cold instruction cache: loops stay rolled and waits have one site each.
 // ------------------------------------------------------------------------------------------------
+#define ATT_GP 8                       // stride of a row's probabilities (one float per head of the group, GRP <= 8)
+__device__ __forceinline__ void ring_adv(uint32_t& slot, uint32_t& par, uint32_t n, uint32_t nring) {
+    slot += n;
+    while (slot >= nring) { slot -= nring; par ^= 1u; }
+}
 template <int GRP>
 __device__ __noinline__ void attention_df(const HxPersist& P, const HxPhase& ph, SmemDf& S, uint8_t* ring, uint8_t* digb,
-                                          uint32_t& ctr, int pi, int pos) {
+                                          uint32_t& cslot, uint32_t& cpar, int pi, int pos) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, cta = blockIdx.x;
-    const int ns = df_nsplit(ph, pos);
-    const AttPlan ap = att_plan_df(ph, ns, cta, pos);
-    const AttPlan2 ap2 = att_plan2(ap, (int)RING_SLOTS);
+    (void)cta;
+    const int ns = S.att_ns;
+    const AttPlan ap = S.ap;
+    const int tr_rows = S.ap_tile_rows, ntiles = S.ap_ntiles;
     const unsigned ep = P.ep_base + (unsigned)pi + 1u, in_ep = P.ep_base + (unsigned)ph.in_dep + 1u;
     const int DH = ph.DH, rps = ap.rows_per_slot, KVD = ph.NKV * DH;
+    const uint32_t nring = RING_SLOTS;
     float* sq = reinterpret_cast<float*>(digb);                 // [GRP][DH] queries
     float* knew = sq + 8 * 256;                                  // [DH] current k
     float* vnew = knew + 256;                                    // [DH] current v
-    float* sp = vnew + 256;                                      // [GRP][160] scores / probabilities
-    float* accx = sp + 8 * 160;                                  // [nsub][GRP*DH] partial outputs (small heads only)
-    constexpr int spitch = 160;
+    float* sp = vnew + 256;                                      // [160 rows][ATT_GP] scores / probabilities
+    float* accx = sp + 160 * ATT_GP;                             // [row subset][GRP][DH] partial outputs
+    const float* ringf = reinterpret_cast<const float*>(ring);
     const int HD = GRP * DH;
-    constexpr int NACC = (GRP * 256 + NCT - 1) / NCT;           // (head, dim) pairs per thread when GRP*DH > NCT
-    const int nsub = HD < NCT ? NCT / HD : 1;                    // position subsets when threads outnumber the pairs
-    const int sub = HD < NCT ? tid / HD : 0;
-    float acc[NACC];
-#pragma unroll
-    for (int i = 0; i < NACC; i++) acc[i] = 0.0f;
-    if (ap.active && ap.t1 > ap.t0) {
-        for (int i = tid * 2; i < HD; i += NCT * 2) df_wait2(ph.in_ll + (size_t)ap.kv * HD + i, in_ep, sq[i], sq[i + 1], S, P);
-        if (ap.has_new) {
-            for (int e = tid * 2; e < DH; e += NCT * 2) {
-                df_wait2(ph.kv_ll + (size_t)ap.kv * DH + e, in_ep, knew[e], knew[e + 1], S, P);
-                df_wait2(ph.kv_ll + (size_t)KVD + (size_t)ap.kv * DH + e, in_ep, vnew[e], vnew[e + 1], S, P);
-            }
-        }
-        if (tid < 8) { S.att_m[tid] = -100000000.0f; S.att_l[tid] = 0.0f; S.att_ax[tid] = 0u; }
-        consumer_sync();
-        const int ntile = ap2.ntiles + ((ap.has_new && ap.n_old % ap2.tile_rows == 0) ? 1 : 0);
-        #pragma unroll 1
-        for (int s = 0; s < ntile; s++) {
-            const bool ring_tile = s < ap2.ntiles;
-            const int nr = ring_tile ? min(ap2.tile_rows, ap.n_old - s * ap2.tile_rows) : 0;
-            const int nsl = (nr + rps - 1) / rps;                       // ring slots of this tile (K, then as many of V)
-            const bool add_new = ap.has_new && (s == ntile - 1);       // the current position rides on the last tile
-            const float* kp[ATT2_TR]; uint32_t ks[ATT2_TR];
-#pragma unroll
-            for (int j = 0; j < ATT2_TR; j++) {
-                kp[j] = knew; ks[j] = 0;
-                if (j < nsl) {
-                    ks[j] = ctr % RING_SLOTS; const uint32_t round = ctr / RING_SLOTS; ctr++;
-                    mbar_wait(&S.full[ks[j]], round & 1, &S.abort_flag);
-                    kp[j] = reinterpret_cast<const float*>(ring + (size_t)ks[j] * HX_RING_SLOT);
-                }
-            }
-            const int ntot = nr + (add_new ? 1 : 0);
-            // scores: thread (head i, position r)
-            #pragma unroll 1
-            for (int it = tid; it < GRP * ntot; it += NCT) {
-                const int i = it / ntot, r = it - i * ntot;
-                const int j = (r >= rps) + (r >= 2 * rps) + (r >= 3 * rps);
-                const float* kr = (r < nr) ? (j == 0 ? kp[0] : j == 1 ? kp[1] : j == 2 ? kp[2] : kp[3]) + (size_t)(r - j * rps) * DH : knew;
-                const float* qi = sq + i * DH;
-                float d0 = 0.0f, d1 = 0.0f;
-                int e = (4 * r) % DH;
-                #pragma unroll 4
-                for (int jj = 0; jj < DH; jj += 4) {
-                    const float4 k4 = *reinterpret_cast<const float4*>(kr + e);
-                    const float4 q4 = *reinterpret_cast<const float4*>(qi + e);
-                    d0 = fmaf(q4.x, k4.x, d0); d1 = fmaf(q4.y, k4.y, d1); d0 = fmaf(q4.z, k4.z, d0); d1 = fmaf(q4.w, k4.w, d1);
-                    e += 4; if (e >= DH) e = 0;
-                }
-                sp[i * spitch + r] = (d0 + d1) * ph.scale;
-            }
-            consumer_sync();
-            if (tid < nsl) mbar_arrive(&S.empty[tid == 0 ? ks[0] : tid == 1 ? ks[1] : tid == 2 ? ks[2] : ks[3]]);
-            // online softmax state per head (fused_decode_attn_kernel.hx:74-102)
-            if (warp < GRP) {
-                const int i = warp;
-                float tm = -INFINITY;
-                for (int r = lane; r < ntot; r += 32) tm = fmaxf(tm, sp[i * spitch + r]);
-                tm = hx_warp_max(tm);
-                const float mo = S.att_m[i], mn = fmaxf(mo, tm);
-                float ls = 0.0f;
-                for (int r = lane; r < ntot; r += 32) { const float pr = __expf(sp[i * spitch + r] - mn); sp[i * spitch + r] = pr; ls += pr; }
-                ls = hx_warp_sum(ls);
-                if (lane == 0) { const float rr = __expf(mo - mn); S.att_r[i] = rr; S.att_l[i] = S.att_l[i] * rr + ls; S.att_m[i] = mn; }
-            }
-#pragma unroll
-            for (int j = 0; j < ATT2_TR; j++) {
-                kp[j] = vnew;
-                if (j < nsl) {
-                    ks[j] = ctr % RING_SLOTS; const uint32_t round = ctr / RING_SLOTS; ctr++;
-                    mbar_wait(&S.full[ks[j]], round & 1, &S.abort_flag);
-                    kp[j] = reinterpret_cast<const float*>(ring + (size_t)ks[j] * HX_RING_SLOT);
-                }
-            }
-            consumer_sync();
-            // P*V: thread (head, dimension) [x position subset]
-#pragma unroll
-            for (int a = 0; a < NACC; a++) {
-                const int hd = (HD < NCT ? tid % HD : tid + a * NCT);
-                if (hd < HD && sub < nsub && (HD >= NCT || a == 0)) {
-                    const int i = hd / DH, d = hd - i * DH;
-                    float v = acc[a] * S.att_r[i];
-#pragma unroll
-                    for (int j = 0; j < ATT2_TR; j++) {
-                        const int r1 = min(nr, (j + 1) * rps);
-                        const float* vj = kp[j] + d - (size_t)(j * rps) * DH;
-                        #pragma unroll 4
-                        for (int r = j * rps + sub; r < r1; r += nsub) v = fmaf(sp[i * spitch + r], vj[(size_t)r * DH], v);
-                    }
-                    if (add_new && (nr % nsub) == sub) v = fmaf(sp[i * spitch + nr], vnew[d], v);
-                    acc[a] = v;
-                }
-            }
-            consumer_sync();
-            if (tid < nsl) mbar_arrive(&S.empty[tid == 0 ? ks[0] : tid == 1 ? ks[1] : tid == 2 ? ks[2] : ks[3]]);
-        }
-        // this split's partial (position subsets folded through shared memory first)
-        if (nsub > 1) {
-            if (sub < nsub) accx[sub * HD + tid % HD] = acc[0];
-            consumer_sync();
-            if (tid < HD) {
-                float v = 0.0f;
-                for (int u = 0; u < nsub; u++) v += accx[u * HD + tid];
-                acc[0] = v;
-            }
-        }
-#pragma unroll
-        for (int a = 0; a < NACC; a++) {
-            const int hd = (HD < NCT ? tid : tid + a * NCT);
-            if (hd < HD && (HD >= NCT || (tid < HD && a == 0))) {
-                const int i = hd / DH, d = hd - i * DH;
-                const size_t hs = (size_t)(ap.kv * GRP + i) * ns + ap.split;
-                ll_st(ph.pacc_ll + hs * DH + d, acc[a], ep);
-                if (d == 0) { ll_st(ph.pml_ll + 2 * hs, S.att_m[i], ep); ll_st(ph.pml_ll + 2 * hs + 1, S.att_l[i], ep); }
-                atomicMax(&S.att_ax[i], __float_as_uint(fabsf(acc[a])));
-            }
-        }
-        consumer_sync();
-        if (tid < GRP) {              // bound of this split's contribution to the merged output: max |acc| / l
-            const size_t hs = (size_t)(ap.kv * GRP + tid) * ns + ap.split;
-            const float l = S.att_l[tid];
-            ll_st(ph.pax_ll + hs, l > 0.0f ? __uint_as_float(S.att_ax[tid]) / l : 0.0f, ep);
-        }
-    } else if (ap.active) {
+    // score pass: thread = (row group, head, part of 8)
+    constexpr int TPR = GRP * 8, NRG = NCT / TPR;
+    const int a_rg = tid / TPR, a_i = (tid >> 3) % GRP, a_p = tid & 7;
+    const int CPT = DH >> 5;                                     // float4 chunks of a row per score thread
+    // P*V pass: thread = (row subset, float4 chunk of the head dimension), all heads of the group
+    const int CH4 = DH >> 2, NSUB = NCT / CH4;
+    const int c_sub = tid / CH4, c_c = tid - c_sub * CH4;
+    if (!ap.active) return;
+    if (ap.t1 <= ap.t0) {
         // empty split: neutral partial
         for (int i = tid; i < GRP; i += NCT) {
-            const size_t hs = (size_t)(ap.kv * GRP + i) * ns + ap.split;
+            const int hs = (ap.kv * GRP + i) * ns + ap.split;
             ll_st(ph.pml_ll + 2 * hs, -100000000.0f, ep); ll_st(ph.pml_ll + 2 * hs + 1, 0.0f, ep);
-            ll_st(ph.pax_ll + hs, 0.0f, ep);
         }
-        for (int i = tid; i < GRP * DH; i += NCT) {
-            const size_t hs = (size_t)(ap.kv * GRP + i / DH) * ns + ap.split;
-            ll_st(ph.pacc_ll + hs * DH + i % DH, 0.0f, ep);
+        for (int i = tid; i < HD; i += NCT) {
+            const int hs = (ap.kv * GRP + i / DH) * ns + ap.split;
+            ll_st(ph.pacc_ll + (size_t)hs * DH + i % DH, 0.0f, ep);
         }
+        return;
+    }
+    float4 acc[GRP];
+#pragma unroll
+    for (int i = 0; i < GRP; i++) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    {
+        // q of the group, and k, v of this position when it falls into the split: one polling site
+        const int nq = HD >> 1, nkv = ap.has_new ? DH >> 1 : 0;
+        #pragma unroll 1
+        for (int i = tid; i < nq + 2 * nkv; i += NCT) {
+            const u64* src; float* dst;
+            if (i < nq) { src = ph.in_ll + (size_t)ap.kv * HD + 2 * i; dst = sq + 2 * i; }
+            else if (i < nq + nkv) { src = ph.kv_ll + (size_t)ap.kv * DH + 2 * (i - nq); dst = knew + 2 * (i - nq); }
+            else { src = ph.kv_ll + (size_t)KVD + (size_t)ap.kv * DH + 2 * (i - nq - nkv); dst = vnew + 2 * (i - nq - nkv); }
+            df_wait2(src, in_ep, dst[0], dst[1], S, P);
+        }
+    }
+    if (tid < 8) { S.att_m[tid] = -100000000.0f; S.att_l[tid] = 0.0f; }
+    consumer_sync();
+    DF_STAMP(7);
+    float4 qf[4];
+#pragma unroll
+    for (int c = 0; c < 4; c++) qf[c] = (c < CPT && a_rg < NRG) ? *reinterpret_cast<const float4*>(sq + a_i * DH + (a_p + 8 * c) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const int ntile = ntiles + ((ap.has_new && ap.n_old % tr_rows == 0) ? 1 : 0);
+    #pragma unroll 1
+    for (int s = 0; s < ntile; s++) {
+        const bool ring_tile = s < ntiles;
+        const int nr = ring_tile ? min(tr_rows, ap.n_old - s * tr_rows) : 0;
+        const int nsl = (nr + rps - 1) / rps;                       // ring slots of this tile (K, then as many of V)
+        const bool add_new = ap.has_new && (s == ntile - 1);       // the current position rides on the last tile
+        const int ntot = nr + (add_new ? 1 : 0);
+        // one thread per ring slot waits for the rows and publishes where they are: K slots 0.., V slots 4..
+        if (tid < 2 * nsl) {
+            uint32_t sl = cslot, pr = cpar;
+            ring_adv(sl, pr, (uint32_t)tid, nring);
+            mbar_wait(&S.full[sl], pr, &S.abort_flag);
+            S.tile_off[tid < nsl ? tid : 4 + tid - nsl] = (int)(sl * (HX_RING_SLOT / 4));
+            S.tile_slot[tid] = (int)sl;
+        }
+        ring_adv(cslot, cpar, (uint32_t)(2 * nsl), nring);
+        consumer_sync();
+        if (s == 0) DF_STAMP(8);
+        // scores
+        const int nk = (ntot + NRG - 1) / NRG;
+        #pragma unroll 3
+        for (int k = 0; k < nk; k++) {
+            const int r = a_rg + k * NRG;
+            const bool valid = a_rg < NRG && r < ntot;
+            const int j = (r >= rps) + (r >= 2 * rps) + (r >= 3 * rps);
+            const float* kr = (valid && r < nr) ? ringf + S.tile_off[j] + (r - j * rps) * DH : knew;
+            float d0 = 0.0f, d1 = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 4; c++) if (c < CPT) {
+                const float4 k4 = *reinterpret_cast<const float4*>(kr + (a_p + 8 * c) * 4);
+                d0 = fmaf(qf[c].x, k4.x, d0); d1 = fmaf(qf[c].y, k4.y, d1); d0 = fmaf(qf[c].z, k4.z, d0); d1 = fmaf(qf[c].w, k4.w, d1);
+            }
+            float d = d0 + d1;
+            d += __shfl_xor_sync(0xffffffffu, d, 1); d += __shfl_xor_sync(0xffffffffu, d, 2); d += __shfl_xor_sync(0xffffffffu, d, 4);
+            if (valid && a_p == 0) sp[r * ATT_GP + a_i] = d * ph.scale;
+        }
+        consumer_sync();
+        if (s == 0) DF_STAMP(9);
+        if (tid < nsl) mbar_arrive(&S.empty[S.tile_slot[tid]]);
+        // online softmax state per head
+        if (warp < GRP) {
+            const int i = warp;
+            float tm = -INFINITY;
+            for (int r = lane; r < ntot; r += 32) tm = fmaxf(tm, sp[r * ATT_GP + i]);
+            tm = hx_warp_max(tm);
+            const float mo = S.att_m[i], mn = fmaxf(mo, tm);
+            float ls = 0.0f;
+            for (int r = lane; r < ntot; r += 32) { const float pr = __expf(sp[r * ATT_GP + i] - mn); sp[r * ATT_GP + i] = pr; ls += pr; }
+            ls = hx_warp_sum(ls);
+            if (lane == 0) { const float rr = __expf(mo - mn); S.att_r[i] = rr; S.att_l[i] = S.att_l[i] * rr + ls; S.att_m[i] = mn; }
+        }
+        consumer_sync();
+        if (s == 0) DF_STAMP(10);
+        // P*V
+        {
+#pragma unroll
+            for (int i = 0; i < GRP; i++) { const float rr = S.att_r[i]; acc[i].x *= rr; acc[i].y *= rr; acc[i].z *= rr; acc[i].w *= rr; }
+            #pragma unroll 2
+            for (int r = c_sub; r < ntot; r += NSUB) {
+                const int j = (r >= rps) + (r >= 2 * rps) + (r >= 3 * rps);
+                const float* vr = (r < nr) ? ringf + S.tile_off[4 + j] + (r - j * rps) * DH : vnew;
+                const float4 v4 = *reinterpret_cast<const float4*>(vr + c_c * 4);
+                const float4 pa = *reinterpret_cast<const float4*>(sp + r * ATT_GP);
+                const float4 pb = GRP > 4 ? *reinterpret_cast<const float4*>(sp + r * ATT_GP + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float pw[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+#pragma unroll
+                for (int i = 0; i < GRP; i++) {
+                    acc[i].x = fmaf(pw[i], v4.x, acc[i].x); acc[i].y = fmaf(pw[i], v4.y, acc[i].y);
+                    acc[i].z = fmaf(pw[i], v4.z, acc[i].z); acc[i].w = fmaf(pw[i], v4.w, acc[i].w);
+                }
+            }
+        }
+        consumer_sync();
+        if (tid < nsl) mbar_arrive(&S.empty[S.tile_slot[nsl + tid]]);
+    }
+    DF_STAMP(11); DF_MARK(2);
+    // fold the row subsets and hand the split's partial over
+#pragma unroll
+    for (int i = 0; i < GRP; i++) *reinterpret_cast<float4*>(accx + (c_sub * GRP + i) * DH + c_c * 4) = acc[i];
+    consumer_sync();
+    #pragma unroll 1
+    for (int hd = tid; hd < HD; hd += NCT) {
+        const int i = hd / DH, d = hd - i * DH;
+        float O = 0.0f;
+        for (int u = 0; u < NSUB; u++) O += accx[(u * GRP + i) * DH + d];
+        const int hs = (ap.kv * GRP + i) * ns + ap.split;
+        ll_st(ph.pacc_ll + (size_t)hs * DH + d, O, ep);
+        if (d == 0) { ll_st(ph.pml_ll + 2 * hs, S.att_m[i], ep); ll_st(ph.pml_ll + 2 * hs + 1, S.att_l[i], ep); }
     }
 }
 
@@ -426,6 +408,8 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                 return true;
             };
             bool ok = true;
+            int a_ns, a_trows, a_ntiles;
+            const AttPlan ap = att_plan_df(P, cta, pos, (int)nring, &a_ns, &a_trows, &a_ntiles);
             HxPhase nxt = P.phases[0];
 #pragma unroll 1
             for (int pi = 0; pi < P.nphases && ok; pi++) {
@@ -447,18 +431,16 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                     }
                 }
                 if (ph.type == HX_PH_LINEAR_TC) {
-                    const TcPlan tp = tc_plan(ph, cta, grid);
-                    const uint8_t* src = ph.w + (size_t)tp.b0 * HX_T128_CELL;
+                    const int b0 = ph.plan[cta].b0, b1 = ph.plan[cta].b1;
+                    const uint8_t* src = ph.w + (size_t)b0 * HX_T128_CELL;
 #pragma unroll 1
-                    for (long long g = tp.b0; g < tp.b1 && ok; g++, src += HX_T128_CELL) ok = push(src, HX_T128_CELL);
+                    for (int g = b0; g < b1 && ok; g++, src += HX_T128_CELL) ok = push(src, HX_T128_CELL);
                 } else if (ph.type == HX_PH_ATTN) {
-                    const AttPlan ap = att_plan_df(ph, df_nsplit(ph, pos), cta, pos);
                     const size_t rowb = (size_t)ph.DH * 4;
                     // tiles of up to tr slots of K rows followed by as many of V rows (attention_df)
-                    const AttPlan2 ap2 = att_plan2(ap, (int)nring);
 #pragma unroll 1
-                    for (int t = 0; t < ap2.ntiles && ok; t++) {
-                        const int r0 = ap.t0 + t * ap2.tile_rows, nrt = min(ap2.tile_rows, ap.t0 + ap.n_old - r0);
+                    for (int t = 0; t < a_ntiles && ok; t++) {
+                        const int r0 = ap.t0 + t * a_trows, nrt = min(a_trows, ap.t0 + ap.n_old - r0);
 #pragma unroll 1
                         for (int kv2 = 0; kv2 < 2 && ok; kv2++) {
 #pragma unroll 1
@@ -487,11 +469,13 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
             const uint64_t b_base = tc_desc(smem_u32(digb), 16, 1024, TC_SW128);
             uint32_t slot = 0, par = 0, uc = 0, tcph = 0;
             bool ok = true;
+            int a_ns, a_trows, a_ntiles;
+            const AttPlan ap = att_plan_df(P, cta, pos, (int)nring, &a_ns, &a_trows, &a_ntiles);
 #pragma unroll 1
             for (int pi = 0; pi < P.nphases && ok; pi++) {
                 const HxPhase& ph = P.phases[pi];
                 if (ph.type == HX_PH_LINEAR_TC) {
-                    const TcPlan tp = tc_plan(ph, cta, grid);                    // worked out while the consumers build the digits
+                    const HxCtaPlan tp = ph.plan[cta];
                     ok = mbar_wait(&S.b_ready, tcph & 1, &S.abort_flag);        // digit columns of this phase are in place
                     tcph++;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -499,7 +483,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                     bool fresh = true;
                     uint32_t dcol = 0;
 #pragma unroll 1
-                    for (long long g = tp.b0; g < tp.b1 && ok; g++) {
+                    for (int g = tp.b0; g < tp.b1 && ok; g++) {
                         if (fresh) {
                             const uint32_t buf = uc & 1u;
                             if (uc >= 2) ok = mbar_wait(&S.acc_empty[buf], ((uc >> 1) - 1) & 1, &S.abort_flag);
@@ -530,16 +514,15 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                         }
                     }
                 } else if (ph.type == HX_PH_ATTN) {
-                    const AttPlan ap = att_plan_df(ph, df_nsplit(ph, pos), cta, pos);
-                    const uint32_t s2 = slot + 2u * (uint32_t)ap.nslots;       // ring slots the consumers use for K and V rows
-                    slot = s2 % nring; if ((s2 / nring) & 1u) par ^= 1u;
+                    ring_adv(slot, par, 2u * (uint32_t)ap.nslots, nring);         // ring slots the consumers use for K and V rows
                 }
             }
         }
     } else {
         // =============================== consumers ===============================
-        uint32_t ctr = 0, uc = 0;
+        uint32_t cslot = 0, cpar = 0, uc = 0;                 // ring cursor of the consumers (attention rows), accumulator use count
         float best_v = -INFINITY; int best_i = INT_MAX;
+        if (tid == 0) S.ap = att_plan_df(P, cta, pos, (int)nring, &S.att_ns, &S.ap_tile_rows, &S.ap_ntiles);
 
         constexpr int PH_CHUNKS = (int)(sizeof(HxPhase) / 16);
         if (tid < PH_CHUNKS) reinterpret_cast<uint4*>(&S.ph[0])[tid] = __ldg(reinterpret_cast<const uint4*>(P.phases) + tid);
@@ -549,109 +532,194 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
         for (int pi = 0; pi < P.nphases; pi++) {
             const HxPhase& ph = S.ph[pi & 1];
             const unsigned ep = P.ep_base + (unsigned)pi + 1u;
-            DF_STAMP(0);
+            DF_STAMP(0); DF_MARK(0);
             // the next descriptor travels to shared memory while this phase runs (its slot was last read a phase ago)
             if (pi + 1 < P.nphases && tid < PH_CHUNKS)
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(reinterpret_cast<uint4*>(&S.ph[(pi + 1) & 1]) + tid)),
                              "l"(reinterpret_cast<const uint4*>(P.phases + pi + 1) + tid) : "memory");
             if (ph.type == HX_PH_LINEAR_TC) {
                 // ---------- prologue: x -> (norm) -> sixteen base-4 digit columns in operand layout ----------
+                // Pass 1 stages the CTA's K slice of the input (times the norm gain) in shared memory behind the digit
+                // cells and finds its largest magnitude; pass 2 turns the staged values into digit words.  The code runs
+                // once per phase from a cold instruction cache, so it is kept small: one polling site, one digit site.
                 const int K = ph.K;
-                const TcPlan tp = tc_plan(ph, cta, grid);
+                const HxCtaPlan tp = ph.plan[cta];
                 const unsigned in_ep = P.ep_base + (unsigned)ph.in_dep + 1u;
                 const bool rms = ph.norm == HX_NORM_RMS;
                 const bool merge_in = ph.norm == HX_NORM_ATTN;
                 // layer 0: the embedding row of the token is the input of qkv and the residual of o_proj
                 const float* xrow = ph.tok ? ph.x + (size_t)(ph.tok[P.tok_by_pos ? pos : 0]) * (size_t)ph.res_ld : ph.x;
                 const int nitems = tp.run * 32;
-                auto item_k = [&](int it) { int kc = tp.k0 + (it >> 5); if (kc >= tp.C) kc -= tp.C; return kc * 256 + (it & 31) * 8; };
-                // one item = eight consecutive elements of the K cells this CTA streams, times the norm gain
-                auto load_item = [&](int k, float (&v)[8]) {
-#pragma unroll
-                    for (int e = 0; e < 8; e++) v[e] = 0.0f;
-                    if (k >= K) return;
-                    if (ph.in_ll) {
-                        if (k + 4 < K) df_wait8(ph.in_ll + k, in_ep, v, S, P);
-                        else { df_wait2(ph.in_ll + k, in_ep, v[0], v[1], S, P); df_wait2(ph.in_ll + k + 2, in_ep, v[2], v[3], S, P); }
-                    } else {
-                        const float4 a = __ldcg(reinterpret_cast<const float4*>(xrow + k));
-                        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-                        if (k + 4 < K) { const float4 b = __ldcg(reinterpret_cast<const float4*>(xrow + k + 4)); v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w; }
-                    }
-                    if (k + 4 >= K) { v[4] = v[5] = v[6] = v[7] = 0.0f; }
-                    if (rms) {
-                        const float4 ga = *reinterpret_cast<const float4*>(ph.g + k);
-                        v[0] *= ga.x; v[1] *= ga.y; v[2] *= ga.z; v[3] *= ga.w;
-                        if (k + 4 < K) { const float4 gb = *reinterpret_cast<const float4*>(ph.g + k + 4); v[4] *= gb.x; v[5] *= gb.y; v[6] *= gb.z; v[7] *= gb.w; }
-                    }
-                };
-                float inv = 1.0f, Sg = 1.0f;
-                float first[8];
-#pragma unroll
-                for (int e = 0; e < 8; e++) first[e] = 0.0f;
+                float* xs = reinterpret_cast<float*>(digb + (size_t)tp.run * 2048);
+                float ss = 0.0f, mx = 0.0f;
                 if (merge_in) {
                     // x is the merge of the attention splits: x[h*DH + d] = sum_s w[h][s] * acc[h][s][d] with
-                    // w[h][s] = exp(m_s - M_h) / sum_s l_s exp(m_s - M_h).  Weights of all heads go to shared memory;
-                    // the magnitude bound comes from the per-split bounds (the merge is a convex combination).
-                    const int NS = df_nsplit(ph, pos);
-                    float mx = 0.0f;
-                    for (int i = tid; i < ph.NH * NS; i += NCT) mx = fmaxf(mx, df_wait1(ph.pax_ll + i, in_ep, S, P));
+                    // w[h][s] = exp(m_s - M_h) / sum_s l_s exp(m_s - M_h).  Weights of all heads first: a warp takes heads
+                    // warp, warp + NCW, ... and polls the (max, sum) pairs of four of them together (lane = split).
+                    const int NS = S.att_ns, DHh = ph.DH;
+                    constexpr int HPW = 4;
                     #pragma unroll 1
-                    for (int h = warp; h < ph.NH; h += NCW) {
-                        float mv[2], lv[2];
+                    for (int hb = warp; hb < ph.NH; hb += NCW * HPW) {
+                        u64 wm[HPW][2], wl[HPW][2];
+                        const unsigned lim = S.abort_flag ? 1u : S.wait_limit;
+                        bool ok = false;
+                        #pragma unroll 1
+                        for (unsigned t = 0; t < lim && !ok; t++) {
+                            ok = true;
 #pragma unroll
-                        for (int j = 0; j < 2; j++) {
-                            const int sidx = lane + 32 * j;
-                            mv[j] = -INFINITY; lv[j] = 0.0f;
-                            if (sidx < NS) df_wait2(ph.pml_ll + 2 * ((size_t)h * NS + sidx), in_ep, mv[j], lv[j], S, P);
+                            for (int u = 0; u < HPW; u++)
+#pragma unroll
+                                for (int j = 0; j < 2; j++) {
+                                    const int h = hb + u * NCW, sidx = lane + 32 * j;
+                                    wm[u][j] = wl[u][j] = 0;
+                                    if (h < ph.NH && sidx < NS) {
+                                        ll_ld2(ph.pml_ll + 2 * (h * NS + sidx), wm[u][j], wl[u][j]);
+                                        ok = ok && ll_ok(wm[u][j], in_ep) && ll_ok(wl[u][j], in_ep);
+                                    }
+                                }
+                            ok = __all_sync(0xffffffffu, ok);
+                            if (!ok && (t & 63u) == 63u && df_gave_up(S, P)) break;
                         }
-                        const float M = hx_warp_max(fmaxf(mv[0], mv[1]));
-                        const float w0 = __expf(mv[0] - M), w1 = __expf(mv[1] - M);
-                        const float Lsum = hx_warp_sum(lv[0] * w0 + lv[1] * w1);
-                        if (lane < NS) S.wgt[h * NS + lane] = w0 / Lsum;
-                        if (lane + 32 < NS) S.wgt[h * NS + lane + 32] = w1 / Lsum;
-                    }
-                    mx = hx_warp_max(mx);
-                    if (lane == 0) S.red[NCW + warp] = mx;
-                    consumer_sync();
-                    float tmx = 0.0f;
+                        if (!ok) df_fail(S, P);
 #pragma unroll
-                    for (int i = 0; i < NCW; i++) tmx = fmaxf(tmx, S.red[NCW + i]);
-                    const float vmax = tmx * 1.0001f;                      // margin for the rounding of the merge
-                    if (vmax > 0.0f && vmax < INFINITY) Sg = __uint_as_float(__float_as_uint(vmax) & 0x7F800000u);
+                        for (int u = 0; u < HPW; u++) {
+                            const int h = hb + u * NCW;
+                            if (h >= ph.NH) break;
+                            const float m0 = lane < NS ? ll_val(wm[u][0]) : -INFINITY, m1 = lane + 32 < NS ? ll_val(wm[u][1]) : -INFINITY;
+                            const float l0 = lane < NS ? ll_val(wl[u][0]) : 0.0f, l1 = lane + 32 < NS ? ll_val(wl[u][1]) : 0.0f;
+                            const float M = hx_warp_max(fmaxf(m0, m1));
+                            const float w0 = __expf(m0 - M), w1 = __expf(m1 - M);
+                            const float Lsum = hx_warp_sum(l0 * w0 + l1 * w1);
+                            if (lane < NS) S.wgt[h * NS + lane] = w0 / Lsum;
+                            if (lane + 32 < NS) S.wgt[h * NS + lane + 32] = w1 / Lsum;
+                        }
+                    }
+                    consumer_sync();
+                    // two threads per item of eight elements; the pairs of up to SB splits are polled together
+                    const int half = tid & 1;
+                    constexpr int SB = 12;
+                    #pragma unroll 1
+                    for (int it = tid >> 1; it < nitems; it += NCT / 2) {
+                        int kc = tp.k0 + (it >> 5); if (kc >= tp.C) kc -= tp.C;
+                        const int k = kc * 256 + (it & 31) * 8 + 4 * half;
+                        float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+                        if (k < K) {
+                            const int h = k / DHh, d = k - h * DHh;
+                            const u64* pa = ph.pacc_ll + (size_t)(h * NS) * DHh + d;
+                            #pragma unroll 1
+                            for (int s0 = 0; s0 < NS; s0 += SB) {
+                                const int n = min(SB, NS - s0);
+                                u64 w[SB][4];
+                                const unsigned lim = S.abort_flag ? 1u : S.wait_limit;
+                                bool ok = false;
+                                #pragma unroll 1
+                                for (unsigned t = 0; t < lim && !ok; t++) {
+#pragma unroll
+                                    for (int c = 0; c < SB; c++) {
+                                        w[c][0] = w[c][1] = w[c][2] = w[c][3] = 0;
+                                        if (c < n) { const u64* q = pa + (size_t)((s0 + c) * DHh); ll_ld2(q, w[c][0], w[c][1]); ll_ld2(q + 2, w[c][2], w[c][3]); }
+                                    }
+                                    ok = true;
+#pragma unroll
+                                    for (int c = 0; c < SB; c++) if (c < n) ok = ok && ll_ok(w[c][0], in_ep) && ll_ok(w[c][1], in_ep) && ll_ok(w[c][2], in_ep) && ll_ok(w[c][3], in_ep);
+                                    if (!ok && (t & 63u) == 63u && df_gave_up(S, P)) break;
+                                }
+                                if (!ok) df_fail(S, P);
+#pragma unroll
+                                for (int c = 0; c < SB; c++) if (c < n) {
+                                    const float wg = S.wgt[h * NS + s0 + c];
+                                    o0 = fmaf(ll_val(w[c][0]), wg, o0); o1 = fmaf(ll_val(w[c][1]), wg, o1);
+                                    o2 = fmaf(ll_val(w[c][2]), wg, o2); o3 = fmaf(ll_val(w[c][3]), wg, o3);
+                                }
+                            }
+                        }
+                        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(o0), fabsf(o1)), fmaxf(fabsf(o2), fabsf(o3))));
+                        *reinterpret_cast<float4*>(xs + it * 8 + half * 4) = make_float4(o0, o1, o2, o3);
+                    }
                 } else {
                     // sum of squares of the whole input: per-tile sums published by the producing epilogue, added in tile
                     // order (every CTA gets the same bits); layer 0 reads the embedding row itself
-                    float ss = 0.0f, mx = 0.0f;
                     if (rms) {
                         if (ph.in_stat) {
-                            if (warp == 0) {
-                                float part = 0.0f;
-                                for (int t = lane; t < ph.n_in_stat; t += 32) part += df_wait1(ph.in_stat + t, in_ep, S, P);
-                                ss = part;
-                            }
+                            if (warp == 0) for (int t = lane; t < ph.n_in_stat; t += 32) ss += df_wait1(ph.in_stat + t, in_ep, S, P);
                         } else {
+                            #pragma unroll 1
                             for (int k = tid * 4; k < K; k += NCT * 4) {
                                 const float4 a = __ldcg(reinterpret_cast<const float4*>(xrow + k));
                                 ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
                             }
                         }
                     }
-                    // largest magnitude over this CTA's K slice; the first item of every thread stays in registers
-#pragma unroll 1
-                    for (int it = tid; it < nitems; it += NCT) {
-                        float v[8];
-                        load_item(item_k(it), v);
+                    // XI items of eight elements per thread and round: all their pairs are in flight together
+                    constexpr int XI = 2;
+                    #pragma unroll 1
+                    for (int it0 = tid; it0 < nitems; it0 += XI * NCT) {
+                        int ks[XI];
+                        u64 w[XI][8];
 #pragma unroll
-                        for (int e = 0; e < 8; e++) mx = fmaxf(mx, fabsf(v[e]));
-                        if (it == tid) {
+                        for (int j = 0; j < XI; j++) {
+                            const int it = it0 + j * NCT;
+                            int kc = tp.k0 + (it >> 5); if (kc >= tp.C) kc -= tp.C;
+                            ks[j] = it < nitems ? kc * 256 + (it & 31) * 8 : -1;
+                            if (ks[j] >= K) ks[j] = -1;
 #pragma unroll
-                            for (int e = 0; e < 8; e++) first[e] = v[e];
+                            for (int e = 0; e < 8; e++) w[j][e] = 0;
+                        }
+                        if (ph.in_ll) {
+                            const unsigned lim = S.abort_flag ? 1u : S.wait_limit;
+                            bool ok = false;
+                            #pragma unroll 1
+                            for (unsigned t = 0; t < lim && !ok; t++) {
+#pragma unroll
+                                for (int j = 0; j < XI; j++) if (ks[j] >= 0) {
+                                    const u64* pp = ph.in_ll + ks[j];
+                                    ll_ld2(pp, w[j][0], w[j][1]); ll_ld2(pp + 2, w[j][2], w[j][3]);
+                                    if (ks[j] + 4 < K) { ll_ld2(pp + 4, w[j][4], w[j][5]); ll_ld2(pp + 6, w[j][6], w[j][7]); }
+                                }
+                                ok = true;
+#pragma unroll
+                                for (int j = 0; j < XI; j++) if (ks[j] >= 0) {
+#pragma unroll
+                                    for (int e = 0; e < 8; e++) if (e < 4 || ks[j] + 4 < K) ok = ok && ll_ok(w[j][e], in_ep);
+                                }
+                                if (!ok && (t & 63u) == 63u && df_gave_up(S, P)) break;
+                            }
+                            if (!ok) df_fail(S, P);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < XI; j++) if (ks[j] >= 0) {
+                                const float4 a = __ldcg(reinterpret_cast<const float4*>(xrow + ks[j]));
+                                w[j][0] = __float_as_uint(a.x); w[j][1] = __float_as_uint(a.y); w[j][2] = __float_as_uint(a.z); w[j][3] = __float_as_uint(a.w);
+                                if (ks[j] + 4 < K) {
+                                    const float4 b = __ldcg(reinterpret_cast<const float4*>(xrow + ks[j] + 4));
+                                    w[j][4] = __float_as_uint(b.x); w[j][5] = __float_as_uint(b.y); w[j][6] = __float_as_uint(b.z); w[j][7] = __float_as_uint(b.w);
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < XI; j++) {
+                            const int it = it0 + j * NCT;
+                            if (it >= nitems) continue;
+                            float v[8];
+#pragma unroll
+                            for (int e = 0; e < 8; e++) v[e] = (ks[j] >= 0 && (e < 4 || ks[j] + 4 < K)) ? ll_val(w[j][e]) : 0.0f;
+                            if (rms && ks[j] >= 0) {
+                                const float4 ga = *reinterpret_cast<const float4*>(ph.g + ks[j]);
+                                v[0] *= ga.x; v[1] *= ga.y; v[2] *= ga.z; v[3] *= ga.w;
+                                if (ks[j] + 4 < K) { const float4 gb = *reinterpret_cast<const float4*>(ph.g + ks[j] + 4); v[4] *= gb.x; v[5] *= gb.y; v[6] *= gb.z; v[7] *= gb.w; }
+                            }
+#pragma unroll
+                            for (int e = 0; e < 8; e++) mx = fmaxf(mx, fabsf(v[e]));
+                            *reinterpret_cast<float4*>(xs + it * 8) = make_float4(v[0], v[1], v[2], v[3]);
+                            *reinterpret_cast<float4*>(xs + it * 8 + 4) = make_float4(v[4], v[5], v[6], v[7]);
                         }
                     }
-                    ss = hx_warp_sum(ss); mx = hx_warp_max(mx);
-                    if (lane == 0) { S.red[warp] = ss; S.red[NCW + warp] = mx; }
-                    consumer_sync();
+                }
+                ss = hx_warp_sum(ss); mx = hx_warp_max(mx);
+                if (lane == 0) { S.red[warp] = ss; S.red[NCW + warp] = mx; }
+                consumer_sync();
+                float inv = 1.0f, Sg = 1.0f;
+                {
                     float tss = 0.0f, tmx = 0.0f;
 #pragma unroll
                     for (int i = 0; i < NCW; i++) { tss += S.red[i]; tmx = fmaxf(tmx, S.red[NCW + i]); }
@@ -659,60 +727,12 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                     const float vmax = tmx * inv * 1.0000005f;            // margin for the rounding of x*g*inv
                     if (vmax > 0.0f && vmax < INFINITY) Sg = __uint_as_float(__float_as_uint(vmax) & 0x7F800000u);   // vmax/Sg in [1,2)
                 }
-                DF_STAMP(14);
+                DF_STAMP(14); DF_MARK(1);
                 const float mul = (inv / Sg) * 2147483648.0f;             // |x_n| / Sg * 2^31 < 2^32
-                if (merge_in) {
-                    // TPI threads share an item: each sums every TPI-th split, a butterfly adds them up (all lanes
-                    // end with the same bits), then each lane writes its share of the sixteen digit rows.
-                    const int NS = df_nsplit(ph, pos), DH = ph.DH;
-                    int tpi = 1; while (tpi < 8 && nitems * tpi * 2 <= NCT) tpi *= 2;
-                    const int sub = tid & (tpi - 1);
-#pragma unroll 1
-                    for (int it = tid / tpi; it < nitems; it += NCT / tpi) {
-                        const int k = item_k(it);
-                        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        if (k < K) {
-                            const int h = k / DH, d = k - h * DH;
-                            const u64* pa = ph.pacc_ll + ((size_t)h * NS) * DH + d;
-#pragma unroll 2
-                            for (int sp2 = sub; sp2 < NS; sp2 += tpi) {
-                                float a[8];
-                                df_wait8(pa + (size_t)sp2 * DH, in_ep, a, S, P);
-                                const float w = S.wgt[h * NS + sp2];
-#pragma unroll
-                                for (int e = 0; e < 8; e++) v[e] = fmaf(a[e], w, v[e]);
-                            }
-                        }
-                        for (int dlt = 1; dlt < tpi; dlt <<= 1) {
-#pragma unroll
-                            for (int e = 0; e < 8; e++) v[e] += __shfl_xor_sync(0xffffffffu, v[e], dlt);
-                        }
-                        uint32_t M[8]; uint32_t sg = 0u;
-#pragma unroll
-                        for (int e = 0; e < 8; e++) {
-                            M[e] = __float2uint_rn(fabsf(v[e]) * mul);
-                            sg |= (v[e] < 0.0f ? 8u : 0u) << (4 * e);
-                        }
-                        const int j = (it >> 2) & 7, w = it & 3;
-                        uint8_t* dst = digb + (size_t)(it >> 5) * 2048 + w * 4;
-#pragma unroll 2
-                        for (int n = sub; n < TC_NDIG; n += tpi) {
-                            uint32_t word = 0u;
-#pragma unroll
-                            for (int e = 0; e < 8; e++) word |= ((M[e] >> (30 - 2 * n)) & 3u) << (4 * e);
-                            const uint32_t nz = (word | (word >> 1)) & 0x11111111u;
-                            word |= sg & (nz << 3);
-                            *reinterpret_cast<uint32_t*>(dst + n * 128 + ((j ^ (n & 7)) << 4)) = word;
-                        }
-                    }
-                } else
-#pragma unroll 1
+                #pragma unroll 1
                 for (int it = tid; it < nitems; it += NCT) {
-                    float v[8];
-                    if (it == tid) {
-#pragma unroll
-                        for (int e = 0; e < 8; e++) v[e] = first[e];
-                    } else load_item(item_k(it), v);                       // later items of a long run: the pairs are final, one more read
+                    const float4 va = *reinterpret_cast<const float4*>(xs + it * 8), vb = *reinterpret_cast<const float4*>(xs + it * 8 + 4);
+                    const float v[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
                     uint32_t M[8]; uint32_t sg = 0u;
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
@@ -734,8 +754,8 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                 DF_STAMP(1);
 
                 // ---------- pieces of tiles: accumulator -> digits recombined -> merge -> epilogue ----------
-                ctr += (uint32_t)(tp.b1 - tp.b0);
-                const int t_first = (int)((unsigned)tp.b0 / (unsigned)tp.C), t_last = tp.b1 > tp.b0 ? (int)((unsigned)(tp.b1 - 1) / (unsigned)tp.C) : t_first - 1;
+                ring_adv(cslot, cpar, (uint32_t)(tp.b1 - tp.b0), nring);
+                const int t_first = tp.t_first, t_last = tp.t_last;
                 if (warp < EPI_WARPS) {
                     const float out_scale = Sg;       // x_n = Sg * sum_j 4^-j * (digit_j / 2), and digit/2 is the E2M1 value
                     const int rl = warp * 32 + lane;
@@ -743,11 +763,9 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
 #pragma unroll 1
                     for (int tile = t_first; tile <= t_last; tile++) {
                         const uint32_t buf = uc & 1u;
-                        // which CTAs share this tile; piece 0 merges
-                        const long long x0 = (long long)tile * tp.C;
-                        const int c0 = tp.P ? tile * tp.P : tc_owner(x0, tp.total, tp.geff);
-                        const int c1 = tp.P ? c0 + tp.P - 1 : tc_owner(x0 + tp.C - 1, tp.total, tp.geff);
-                        const bool merger = cta == c0;
+                        // the CTA holding a tile's first cell merges it (see HxCtaPlan)
+                        const bool merger = tile > t_first || tp.first_merger;
+                        const int others = tile == t_last ? tp.last_others : 0;
                         // operands of the epilogue that are final already travel while the MMAs of this piece run
                         float yres = 0.0f;
                         if (merger && ph.epi == HX_EPI_RESID && tile * 128 + rl < ph.N)
@@ -778,10 +796,10 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                         for (int j = TC_NDIG - 1; j >= 0; j--) v = fmaf(v, 0.25f, __uint_as_float(r[j]));
                         v *= out_scale;
                         if (!merger) {            // pieces 1.. hand their rows to the merger
-                            ll_st(ph.part_ll + ((size_t)tile * ph.pieces + (size_t)(cta - c0 - 1)) * 128 + rl, v, ep);
+                            ll_st(ph.part_ll + ((size_t)tile * ph.pieces + (size_t)tp.first_piece) * 128 + rl, v, ep);
                             continue;
                         }
-                        for (int q = 1; q <= c1 - c0; q++) v += df_wait1(ph.part_ll + ((size_t)tile * ph.pieces + (size_t)(q - 1)) * 128 + rl, ep, S, P);
+                        for (int q = 0; q < others; q++) v += df_wait1(ph.part_ll + ((size_t)tile * ph.pieces + (size_t)q) * 128 + rl, ep, S, P);
                         if (ph.epi == HX_EPI_QKV) {
                             // A tile holds 128 / DH whole heads (DH is 32, 64 or 128).  Per-head RMSNorm and rotate_half
                             // RoPE on q and k; q leaves as pairs, k and v as pairs and into the cache row of this position.
@@ -912,17 +930,17 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                 }
             } else if (ph.type == HX_PH_ATTN) {
                 switch (ph.NH / ph.NKV) {
-                    case 1: attention_df<1>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                    case 2: attention_df<2>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                    case 3: attention_df<3>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                    case 4: attention_df<4>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                    case 5: attention_df<5>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                    case 6: attention_df<6>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                    case 7: attention_df<7>(P, ph, S, ring, digb, ctr, pi, pos); break;
-                    default: attention_df<8>(P, ph, S, ring, digb, ctr, pi, pos); break;
+                    case 1: attention_df<1>(P, ph, S, ring, digb, cslot, cpar, pi, pos); break;
+                    case 2: attention_df<2>(P, ph, S, ring, digb, cslot, cpar, pi, pos); break;
+                    case 3: attention_df<3>(P, ph, S, ring, digb, cslot, cpar, pi, pos); break;
+                    case 4: attention_df<4>(P, ph, S, ring, digb, cslot, cpar, pi, pos); break;
+                    case 5: attention_df<5>(P, ph, S, ring, digb, cslot, cpar, pi, pos); break;
+                    case 6: attention_df<6>(P, ph, S, ring, digb, cslot, cpar, pi, pos); break;
+                    case 7: attention_df<7>(P, ph, S, ring, digb, cslot, cpar, pi, pos); break;
+                    default: attention_df<8>(P, ph, S, ring, digb, cslot, cpar, pi, pos); break;
                 }
             }
-            DF_STAMP(2);
+            DF_STAMP(2); DF_MARK(3);
             // ---------- phase boundary: the digit columns and the attention scratch are free again ----------
             asm volatile("cp.async.wait_all;" ::: "memory");
             if (consumer_sync_any(S.abort_flag)) goto aborted;
@@ -944,12 +962,14 @@ done:   ;
 }
 
 size_t df_smem_fixed(int bdig_bytes) {
-    const size_t att = (size_t)(8 * 256 + 256 + 256 + 8 * 160 + 8 * NCT) * 4;
-    const size_t d = (size_t)bdig_bytes > att ? (size_t)bdig_bytes : att;
-    return ((sizeof(SmemDf) + 15) & ~(size_t)15) + 512 + 1024 + d;      // + ring slots
+    return ((sizeof(SmemDf) + 15) & ~(size_t)15) + 512 + 1024 + (size_t)bdig_bytes;      // + ring slots
 }
 
 }  // namespace
+
+// Shared-memory scratch of the attention phase for a group of `grp` query heads per kv head (queries, the position's k
+// and v, probabilities, partial outputs of the row subsets); the digit columns share the space.
+int hx_decode_df_att_bytes(int grp) { return (8 * 256 + 256 + 256 + 160 * ATT_GP + NCT * 4 * grp) * 4; }
 
 // Ring depth that fits beside the digit columns (0 = does not fit).
 int hx_decode_df_ring(int bdig_bytes) {

@@ -103,8 +103,9 @@ struct hx_model {
     // dataflow engine (hx_decode_df.cu): vectors that cross CTAs as (value, epoch) pairs
     bool use_df = false;
     unsigned long long *xll[2] = {nullptr, nullptr}, *statll[2] = {nullptr, nullptr}, *qll = nullptr, *kvll = nullptr, *hll = nullptr;
-    unsigned long long *pacc_ll = nullptr, *pml_ll = nullptr, *pax_ll = nullptr, *part_ll[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    unsigned long long *pacc_ll = nullptr, *pml_ll = nullptr, *part_ll[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     unsigned ep_count = 0, wait_limit = 1u << 24; int inject_stall = 0; unsigned* done_cnt = nullptr;
+    std::vector<long long> plan_keys; std::vector<HxCtaPlan*> plan_tabs;
 };
 
 namespace {
@@ -511,11 +512,27 @@ int build_phases(hx_model* m, bool from_prompt, bool with_head, HxPhase** out, i
         if (m->use_tc) {
             p.type = HX_PH_LINEAR_TC; p.w = f.t128; p.ntiles = f.tiles128; p.ksteps = f.ksteps;
             int maxp = 1, maxrun = 1;
+            if (m->use_df) {
+                // per-CTA work split from a table (one per distinct tile grid, shared by the layers)
+                const long long key = ((long long)p.ntiles << 32) | (unsigned)(p.ksteps / 4);
+                size_t slot = 0;
+                for (; slot < m->plan_keys.size(); slot++) if (m->plan_keys[slot] == key) break;
+                std::vector<HxCtaPlan> tab((size_t)m->grid_persist);
+                hx_df_plan(p.ntiles, p.ksteps / 4, m->grid_persist, tab.data(), &maxp, &maxrun);
+                if (slot == m->plan_keys.size()) {
+                    HxCtaPlan* d = nullptr;
+                    if (dalloc(m, &d, tab.size()) == HX_OK && cudaMemcpy(d, tab.data(), tab.size() * sizeof(HxCtaPlan), cudaMemcpyHostToDevice) == cudaSuccess) {
+                        m->plan_keys.push_back(key); m->plan_tabs.push_back(d);
+                    }
+                }
+                p.plan = slot < m->plan_tabs.size() ? m->plan_tabs[slot] : nullptr;
+            } else
             hx_tc_split(p.ntiles, p.ksteps / 4, m->grid_persist, &maxp, &maxrun);
             p.pieces = maxp;
             if ((size_t)p.ntiles * maxp > m->tc_units_max) m->tc_units_max = (size_t)p.ntiles * maxp;
             if (p.ntiles > m->tc_tiles_max) m->tc_tiles_max = p.ntiles;
-            if (maxrun * 2048 > m->bdig_bytes) m->bdig_bytes = maxrun * 2048;
+            const int per_cell = m->use_df ? 3072 : 2048;       // digit cells (+ the staged input values of the dataflow engine)
+            if (maxrun * per_cell > m->bdig_bytes) m->bdig_bytes = maxrun * per_cell;
         }
         p.N = N; p.x = x; p.K = f.K; p.norm = HX_NORM_NONE; p.epi = epi; p.y = y;
         p.ts[0] = f.ts[0]; p.ts[1] = f.ts[1]; p.ts[2] = f.ts[2]; p.bound0 = f.bound0; p.bound1 = f.bound1;
@@ -550,11 +567,17 @@ int build_phases(hx_model* m, bool from_prompt, bool with_head, HxPhase** out, i
             at.NH = c.n_heads; at.NKV = c.n_kv_heads; at.DH = DH; at.cap = cap;
             at.nsplit = m->nsplit_persist; at.scale = 1.0f / sqrtf((float)DH); at.eps = c.norm_eps;
             at.in_ll = m->qll; at.kv_ll = m->kvll; at.in_dep = i_qkv;
-            at.pacc_ll = m->pacc_ll; at.pml_ll = m->pml_ll; at.pax_ll = m->pax_ll;
+            at.pacc_ll = m->pacc_ll; at.pml_ll = m->pml_ll;
             const int i_att = (int)v.size(); v.push_back(at);
             HxPhase o = linear(ly.o, nullptr, nullptr, HX_EPI_RESID, ly.o.N);
             o.norm = HX_NORM_ATTN; o.NH = c.n_heads; o.NKV = c.n_kv_heads; o.DH = DH; o.nsplit = m->nsplit_persist;
-            o.pacc_ll = m->pacc_ll; o.pml_ll = m->pml_ll; o.pax_ll = m->pax_ll; o.in_dep = i_att;
+            o.pacc_ll = m->pacc_ll; o.pml_ll = m->pml_ll; o.in_dep = i_att;
+            {   // the merged attention output of a CTA's K slice is staged in shared memory behind its digit cells
+                int maxp = 1, maxrun = 1;
+                std::vector<HxCtaPlan> tab((size_t)m->grid_persist);
+                hx_df_plan(o.ntiles, o.ksteps / 4, m->grid_persist, tab.data(), &maxp, &maxrun);
+                if (maxrun * 3072 > m->bdig_bytes) m->bdig_bytes = maxrun * 3072;
+            }
             if (dep_x < 0) { o.x = m->emb; o.tok = from_prompt ? m->d_prompt : m->d_tok; o.res_ld = c.d_model; }
             else { o.res_ll = m->xll[1]; o.res_dep = dep_x; }
             o.out_ll = m->xll[0]; o.out_stat = m->statll[0]; o.part_ll = m->part_ll[1];
@@ -670,10 +693,10 @@ int init_persist(hx_model* m) {
         const size_t hs = (size_t)c.n_heads * m->nsplit_persist;
         if ((rc = ll(&m->pacc_ll, hs * DH))) return rc;
         if ((rc = ll(&m->pml_ll, hs * 2))) return rc;
-        if ((rc = ll(&m->pax_ll, hs))) return rc;
         auto parts = [&](const Fused& f) -> size_t {
             int maxp = 1, maxrun = 1;
-            hx_tc_split(f.tiles128, f.ksteps / 4, m->grid_persist, &maxp, &maxrun);
+            std::vector<HxCtaPlan> tab((size_t)m->grid_persist);
+            hx_df_plan(f.tiles128, f.ksteps / 4, m->grid_persist, tab.data(), &maxp, &maxrun);
             return (size_t)f.tiles128 * maxp * 128;
         };
         size_t need[5] = {128, 128, 128, 128, parts(m->head)};
@@ -708,6 +731,7 @@ int init_persist(hx_model* m) {
         if ((rc = dalloc(m, &m->tc_partial, m->tc_units_max * 128 + 128))) return rc;
         if ((rc = dalloc(m, &m->tc_cnt, (size_t)m->tc_tiles_max + 8))) return rc;
         HX_CUDA(cudaMemset(m->tc_cnt, 0, ((size_t)m->tc_tiles_max + 8) * 4));
+        if (m->use_df) { const int att = hx_decode_df_att_bytes(m->cfg.n_heads / m->cfg.n_kv_heads); if (att > m->bdig_bytes) m->bdig_bytes = att; }
         m->tc_ring = m->use_df ? hx_decode_df_ring(m->bdig_bytes) : hx_persist_tc_ring(m->bdig_bytes);
         if (const char* e = getenv("HX_TC_RING")) { const int r = atoi(e); if (r >= 3 && r < m->tc_ring) m->tc_ring = r; }
         if (m->tc_ring < 3)
@@ -743,6 +767,7 @@ int persist_step(hx_model* m, bool from_prompt, bool with_head) {
         if (m->ep_count > 0xFFF00000u) return hx_fail(HX_ERR_STATE, "epoch counter of the decode engine exhausted: rebuild the model");
         P.ep_base = m->ep_count; m->ep_count += (unsigned)P.nphases + 2u;
         P.wait_limit = m->wait_limit; P.inject_stall = m->inject_stall; P.done_cnt = m->done_cnt;
+        P.att_nkv = m->cfg.n_kv_heads; P.att_nsplit = m->nsplit_persist; P.att_dh = m->cfg.head_dim;
         for (int w = 0; w < m->tp_world; w++) P.tp_x[w] = reinterpret_cast<unsigned long long*>(m->tp_peer[w]);
         return hx_decode_df_launch(P, m->grid_persist, m->st);
     }

@@ -29,6 +29,15 @@ void hx_repack_t16(const int32_t* words, const uint8_t* micro, int rows, int K, 
 
 enum { HX_PH_LINEAR = 0, HX_PH_ATTN = 1, HX_PH_LINEAR_TC = 2 };
 
+// What one CTA does in a tensor-core linear phase of the dataflow engine, worked out on the host (the kernel carries no
+// divisions for it): its run of cells [b0, b1) in storage order (tile-major, K-minor), the K cell of the first one, the
+// number of distinct K cells, the tiles the run touches, and its part in the split-K merge.  The CTA that holds the
+// first cell of a tile merges it: the first tile of a run is either merged here (first_merger) or handed to its merger
+// as piece first_piece; every later tile of the run starts here and is merged here; only the last tile can have pieces
+// in the CTAs that follow (last_others of them).
+struct alignas(16) HxCtaPlan { int b0, b1, k0, run, t_first, t_last, first_merger, first_piece, last_others, C, pad0, pad1; };
+void hx_df_plan(int ntiles, int kcells, int grid, HxCtaPlan* out /* [grid] */, int* max_pieces, int* max_run);
+
 struct alignas(16) HxPhase {
     int type;
     // ---- linear ----
@@ -68,10 +77,10 @@ struct alignas(16) HxPhase {
     const unsigned long long* res_ll;      // residual rows added by the residual epilogue (null: row *tok of the table x)
     int res_dep, res_ld;                   // res_ld: row length of the table x when tok is set
     unsigned long long* part_ll;           // split-K partial sums of pieces 1.. of every tile: [tile][piece - 1][128]
+    const HxCtaPlan* plan;                 // [grid] work split of this phase
     unsigned long long* kv_ll;             // this position's k and v rows [2 * NKV * DH] (qkv epilogue -> attention)
     unsigned long long* pacc_ll;           // attention partial outputs [head][split][DH]
     unsigned long long* pml_ll;            // attention partial (max, sum) lines [head][split][2]
-    unsigned long long* pax_ll;            // attention partial magnitude bounds [head][split]
 };
 
 struct HxPersist {
@@ -104,13 +113,15 @@ struct HxPersist {
     unsigned long long* tp_x[8];          // tensor parallel: exchange buffers of all ranks as (value, epoch) pairs:
                                           // [2 slots][world][tp_dm] partial rows | [world][2] arg-max pairs
     unsigned* done_cnt;                   // ticket of the launches without an lm_head
+    int att_nkv, att_nsplit, att_dh;      // attention geometry (the same in every layer): kv heads, most splits, head size
 };
 
 int hx_persist_launch(const HxPersist& p, int grid, cudaStream_t st);
 int hx_persist_tc_launch(const HxPersist& p, int grid, cudaStream_t st);
 int hx_decode_df_launch(const HxPersist& p, int grid, cudaStream_t st);     // dataflow engine (hx_decode_df.cu)
 int hx_decode_df_prepare();
-int hx_decode_df_ring(int bdig_bytes);                                                 // per-device function attributes
+int hx_decode_df_ring(int bdig_bytes);
+int hx_decode_df_att_bytes(int grp);                                                 // per-device function attributes
 size_t hx_persist_tc_smem(int bdig_bytes);            // shared memory besides the ring
 int hx_persist_tc_ring(int bdig_bytes);               // ring depth that fits (0: the digit columns do not fit)
 // how the tensor-core kernel cuts ntiles x kcells cells over `grid` CTAs: most pieces of one tile, most K cells of one CTA

@@ -114,6 +114,47 @@ void hx_tc_split(int ntiles, int C, int grid, int* max_pieces, int* max_run) {
     *max_pieces = mp; *max_run = mr < C ? mr : C;
 }
 
+// The same split, per CTA, for the dataflow engine (hx_decode_df.cu), which reads it from a table.
+void hx_df_plan(int ntiles, int C, int grid, HxCtaPlan* out, int* max_pieces, int* max_run) {
+    const long long total = (long long)ntiles * C;
+    int P = 0, geff = grid;
+    if (2 * ntiles <= grid) { P = grid / ntiles; if (P > C) P = C; }
+    else if (total < grid) geff = (int)total;
+    auto bounds = [&](int cta, long long& b0, long long& b1) {
+        b0 = b1 = 0;
+        if (P) { if (cta < ntiles * P) { const int tile = cta / P, q = cta - tile * P; b0 = (long long)tile * C + (q * C) / P; b1 = (long long)tile * C + ((q + 1) * C) / P; } }
+        else if (cta < geff) { b0 = (long long)cta * total / geff; b1 = (long long)(cta + 1) * total / geff; }
+    };
+    int mp = 1, mr = 1;
+    for (int cta = 0; cta < grid; cta++) {
+        HxCtaPlan p = {};
+        long long b0, b1; bounds(cta, b0, b1);
+        p.b0 = (int)b0; p.b1 = (int)b1; p.C = C;
+        p.k0 = (int)(b0 % C);
+        const long long n = b1 - b0;
+        p.run = n < C ? (int)n : C;
+        p.t_first = (int)(b0 / C); p.t_last = n > 0 ? (int)((b1 - 1) / C) : p.t_first - 1;
+        p.first_merger = (b0 % C) == 0 ? 1 : 0;
+        if (n > 0 && !p.first_merger) {            // piece index = CTAs between the tile's first cell and this one
+            int c = cta - 1; long long a0, a1;
+            for (;; c--) { bounds(c, a0, a1); if (a0 <= (long long)p.t_first * C) break; }
+            p.first_piece = cta - c - 1;
+        }
+        if (n > 0) {                               // pieces of the last tile in the CTAs that follow
+            const long long tile_end = (long long)(p.t_last + 1) * C;
+            int others = 0; long long a0, a1 = b1;
+            for (int c = cta + 1; a1 < tile_end && c < grid; c++) { bounds(c, a0, a1); if (a1 > a0) others++; }
+            p.last_others = others;
+            if (others + 1 > mp) mp = others + 1;
+            if (!p.first_merger && p.first_piece + 1 > mp) mp = p.first_piece + 1;
+        }
+        if (p.run > mr) mr = p.run;
+        out[cta] = p;
+    }
+    if (max_pieces) *max_pieces = mp;
+    if (max_run) *max_run = mr;
+}
+
 // ------------------------------------------------------------------------------------------------
 namespace {
 
