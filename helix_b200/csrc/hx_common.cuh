@@ -27,6 +27,16 @@ int  hx_fail(int code, const char* fmt, ...);
         if (!(cond)) return hx_fail(HX_ERR_ARG, "bad argument: %s (%s:%d)", #cond, __FILE__, __LINE__); \
     } while (0)
 
+// A function attribute belongs to the device that is current when it is set, so "done once" is tracked per
+// device: returns true the first time it is called for `seen` on the current device (devices 0..63).
+#include <atomic>
+static inline bool hx_first_on_device(std::atomic<unsigned long long>& seen) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev > 63) return true;
+    const unsigned long long bit = 1ull << dev;
+    return (seen.fetch_or(bit) & bit) == 0;
+}
+
 // Count of kernels this library launched (reported by the benchmark as gpu_launches).
 extern unsigned long long g_hx_launches;
 #define HX_COUNT_LAUNCH(n) (g_hx_launches += (n))

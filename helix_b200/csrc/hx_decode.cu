@@ -309,11 +309,9 @@ int hx_launch_linear(const HxLinear& a, cudaStream_t st, bool pdl) {
     HX_CHECK_ARG((((uintptr_t)a.x) & 15) == 0 && (((uintptr_t)a.codes) & 15) == 0 && (((uintptr_t)a.scales) & 1) == 0);
     const size_t smem = hx_linear_smem_bytes(a.Kd);
     if (smem > 200 * 1024) return hx_fail(HX_ERR_ARG, "K=%d too large for the shared-memory staging of x", a.K);
-    static bool attr_set = false;
-    if (!attr_set) {
+    static std::atomic<unsigned long long> attr_seen{0};
+    if (hx_first_on_device(attr_seen))
         HX_CUDA(cudaFuncSetAttribute(k_linear<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_set = true;
-    }
     const int R = 4;
     const int ngroups = (a.N + R - 1) / R;
     int grid = (ngroups + LIN_WARPS - 1) / LIN_WARPS;

@@ -275,8 +275,8 @@ static size_t gemm_tc_smem_resident(int ncols, int stage_ksteps, int cells_per_p
 
 // One-time function attribute (call outside any stream capture).
 int hx_gemm_tc_prepare() {
-    static bool attr = false;
-    if (!attr) { HX_CUDA(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); attr = true; }
+    static std::atomic<unsigned long long> attr_seen{0};
+    if (hx_first_on_device(attr_seen)) HX_CUDA(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     return HX_OK;
 }
 

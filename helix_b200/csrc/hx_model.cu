@@ -761,19 +761,23 @@ int persist_step(hx_model* m, bool from_prompt, bool with_head) {
         if (!m->tp_connected) return hx_fail(HX_ERR_STATE, "tensor parallel: call hx_model_tp_connect before the first step");
         for (int w = 0; w < m->tp_world; w++) P.tp_peer[w] = m->tp_peer[w];
         P.tp_epoch_base = m->tp_launches * 4096u;        // every rank launches the same sequence of steps
-        m->tp_launches++;
     }
     if (m->use_df) {
         if (m->ep_count > 0xFFF00000u) return hx_fail(HX_ERR_STATE, "epoch counter of the decode engine exhausted: rebuild the model");
-        P.ep_base = m->ep_count; m->ep_count += (unsigned)P.nphases + 2u;
+        P.ep_base = m->ep_count;
         P.wait_limit = m->wait_limit; P.inject_stall = m->inject_stall; P.done_cnt = m->done_cnt;
         P.att_nkv = m->cfg.n_kv_heads; P.att_nsplit = m->nsplit_persist; P.att_dh = m->cfg.head_dim;
         for (int w = 0; w < m->tp_world; w++) P.tp_x[w] = reinterpret_cast<unsigned long long*>(m->tp_peer[w]);
-        return hx_decode_df_launch(P, m->grid_persist, m->st);
+        const int rc = hx_decode_df_launch(P, m->grid_persist, m->st);
+        if (rc == HX_OK) m->ep_count += (unsigned)P.nphases + 2u;      // the counters move only with a launch that ran
+        return rc;
     }
-    m->bar_count += (unsigned long long)m->grid_persist * (unsigned long long)(P.nphases - 1);
-    if (m->use_tc) return hx_persist_tc_launch(P, m->grid_persist, m->st);
-    return hx_persist_launch(P, m->grid_persist, m->st);
+    const int rc = m->use_tc ? hx_persist_tc_launch(P, m->grid_persist, m->st) : hx_persist_launch(P, m->grid_persist, m->st);
+    if (rc == HX_OK) {
+        m->bar_count += (unsigned long long)m->grid_persist * (unsigned long long)(P.nphases - 1);
+        if (m->tp_world > 1) m->tp_launches++;
+    }
+    return rc;
 }
 
 // After a synchronize: did any bounded wait of the persistent kernel run out?
@@ -859,6 +863,8 @@ HX_API int hx_model_free(hx_model* m) {
     if (m->g_bstep) cudaGraphExecDestroy(m->g_bstep);
     if (m->ev0) cudaEventDestroy(m->ev0);
     if (m->ev1) cudaEventDestroy(m->ev1);
+    for (int w = 0; w < 8; w++)                      // mappings of the peers' exchange buffers
+        if (m->tp_peer[w] && w != m->tp_rank) cudaIpcCloseMemHandle(m->tp_peer[w]);
     for (void* p : m->allocs) cudaFree(p);
     for (cudaEvent_t e : m->prof_ev) cudaEventDestroy(e);
     if (m->st) cudaStreamDestroy(m->st);
@@ -1078,6 +1084,7 @@ HX_API int hx_model_tp_handle(hx_model* m, uint8_t handle[64]) {
 HX_API int hx_model_tp_connect(hx_model* m, const uint8_t* handles, int world) {
     HX_CHECK_ARG(m && handles);
     if (world != m->tp_world || m->tp_world < 2) return hx_fail(HX_ERR_ARG, "tensor parallel: %d handles for a group of %d", world, m->tp_world);
+    if (m->tp_connected) return hx_fail(HX_ERR_STATE, "tensor parallel: the group is already connected");
     if (m->tp_nbar >= 4095) return hx_fail(HX_ERR_ARG, "tensor parallel: too many layers for the barrier numbering");
     for (int w = 0; w < world; w++) {
         if (w == m->tp_rank) continue;

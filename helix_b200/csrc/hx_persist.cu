@@ -462,11 +462,9 @@ size_t hx_persist_smem(int dig_bytes) {
 int hx_persist_launch(const HxPersist& p, int grid, cudaStream_t st) {
     const size_t smem = hx_persist_smem(p.dig_bytes);
     if (smem > 227 * 1024) return hx_fail(HX_ERR_ARG, "persistent decode needs %zu bytes of shared memory", smem);
-    static bool attr = false;
-    if (!attr) {
+    static std::atomic<unsigned long long> attr_seen{0};
+    if (hx_first_on_device(attr_seen))
         HX_CUDA(cudaFuncSetAttribute(k_decode_persist, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        attr = true;
-    }
     void* args[] = {(void*)&p};
     HX_CUDA(cudaLaunchCooperativeKernel((void*)k_decode_persist, dim3(grid), dim3(PT), args, smem, st));
     HX_COUNT_LAUNCH(1);

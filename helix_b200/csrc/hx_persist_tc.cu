@@ -887,11 +887,10 @@ int hx_persist_tc_launch(const HxPersist& p, int grid, cudaStream_t st) {
     if (p.tc_ring < 3 || p.tc_ring > HX_TC_MAX_RING) return hx_fail(HX_ERR_ARG, "tensor-core decode: ring depth %d", p.tc_ring);
     const size_t smem = hx_persist_tc_smem(p.bdig_bytes) + (size_t)p.tc_ring * HX_RING_SLOT;
     if (smem > 227 * 1024) return hx_fail(HX_ERR_ARG, "tensor-core decode needs %zu bytes of shared memory", smem);
-    static bool attr = false;
-    if (!attr) {
+    static std::atomic<unsigned long long> attr_seen{0};
+    if (hx_first_on_device(attr_seen)) {
         HX_CUDA(cudaFuncSetAttribute(k_decode_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         HX_CUDA(cudaFuncSetAttribute(k_decode_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        attr = true;
     }
     void* args[] = {(void*)&p};
     void* fn = p.tp_world > 1 ? (void*)k_decode_tc<true> : (void*)k_decode_tc<false>;

@@ -125,13 +125,15 @@ __global__ void __launch_bounds__(QTHREADS) k_quantize(const float* __restrict__
 HX_API int hx_kpad(int K) { return ((K + 111) / 112) * 112; }
 HX_API int hx_kd(int K) { return ((K + 63) / 64) * 64; }
 
-// One scratch word per device for the amax; zeroed before every use on the caller's stream.
+// Scratch for the tensor's amax: 64 words per device handed out in turn, so calls that overlap on different
+// streams do not share a word (up to 64 of them in flight per device); zeroed before every use on the caller's stream.
 static unsigned* amax_scratch() {
     static unsigned* p[64] = {0};
+    static std::atomic<unsigned> turn{0};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
     if (!p[dev] && cudaMalloc(&p[dev], 256) != cudaSuccess) return nullptr;
-    return p[dev];
+    return p[dev] + (turn.fetch_add(1u) & 63u);
 }
 
 HX_API int hx_quantize_nvfp4(const float* w, int rows, int K, int32_t* words, uint8_t* micro, float* sc,

@@ -66,7 +66,9 @@ int hx_kpad(int K);
  *   micro  [rows*(Kpad/16)] uint8, E4M3 scale code per 16 elements along K     (may be NULL)
  *   sc     [rows*(Kpad/16)] f32, e4m3_decode(micro)*ts                          (may be NULL)
  *   ts     [1] f32 per-tensor scale amax/(6*448), 1.0 for an all-zero tensor    (may be NULL)
- * stream is a cudaStream_t (NULL = default stream); the call is asynchronous. */
+ * stream is a cudaStream_t (NULL = default stream); the call is asynchronous.  The first call on a device
+ * allocates 256 bytes for the tensor maxima (64 words handed out in turn): calls on different streams may
+ * overlap as long as no more than 64 are in flight on one device. */
 int hx_quantize_nvfp4(const float* w, int rows, int K, int32_t* words, uint8_t* micro, float* sc,
                       float* ts, void* stream);
 
