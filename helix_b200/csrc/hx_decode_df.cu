@@ -54,7 +54,7 @@ typedef unsigned long long u64;
 // per-phase time stamps of one CTA, debug builds only (-DHX_DEBUG_STAMPS)
 #ifdef HX_DEBUG_STAMPS
 #define DF_STAMP(i) do { if (P.dbg && cta == P.dbg_cta && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg[pi * 16 + (i)] = _t; } } while (0)
-#define DF_MARK(ev) do { if (P.dbg_all && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg_all[((size_t)pi * gridDim.x + blockIdx.x) * 4 + (ev)] = _t; } } while (0)
+#define DF_MARK(ev) do { if (P.dbg_all && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg_all[((size_t)pi * gridDim.x + blockIdx.x) * 8 + (ev)] = _t; } } while (0)
 #else
 #define DF_STAMP(i) do { } while (0)
 #define DF_MARK(ev) do { } while (0)
@@ -141,6 +141,24 @@ __device__ __forceinline__ float df_wait1(const u64* p, unsigned ep, SmemDf& S, 
     }
     df_fail(S, P);
     return ll_val(w);
+}
+// Up to four pairs `stride` apart, all in flight together; returns their values added to `acc` in index order.
+__device__ __forceinline__ float df_wait_add4(const u64* p, size_t stride, int n, unsigned ep, float acc, SmemDf& S, const HxPersist& P) {
+    const unsigned lim = S.abort_flag ? 1u : S.wait_limit;
+    u64 w[4] = {0, 0, 0, 0};
+    bool ok = false;
+    for (unsigned i = 0; i < lim && !ok; i++) {
+        ok = true;
+#pragma unroll
+        for (int c = 0; c < 4; c++) if (c < n) w[c] = ll_ld(p + (size_t)c * stride);
+#pragma unroll
+        for (int c = 0; c < 4; c++) if (c < n) ok = ok && ll_ok(w[c], ep);
+        if (!ok && (i & 63u) == 63u && df_gave_up(S, P)) break;
+    }
+    if (!ok) df_fail(S, P);
+#pragma unroll
+    for (int c = 0; c < 4; c++) if (c < n) acc += ll_val(w[c]);
+    return acc;
 }
 // Two pairs at a 16-byte aligned address.
 __device__ __forceinline__ void df_wait2(const u64* p, unsigned ep, float& a, float& b, SmemDf& S, const HxPersist& P) {
@@ -266,7 +284,7 @@ __device__ __noinline__ void attention_df(const HxPersist& P, const HxPhase& ph,
     }
     if (tid < 8) { S.att_m[tid] = -100000000.0f; S.att_l[tid] = 0.0f; }
     consumer_sync();
-    DF_STAMP(7);
+    DF_STAMP(7); DF_MARK(1);
     float4 qf[4];
 #pragma unroll
     for (int c = 0; c < 4; c++) qf[c] = (c < CPT && a_rg < NRG) ? *reinterpret_cast<const float4*>(sq + a_i * DH + (a_p + 8 * c) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -288,7 +306,7 @@ __device__ __noinline__ void attention_df(const HxPersist& P, const HxPhase& ph,
         }
         ring_adv(cslot, cpar, (uint32_t)(2 * nsl), nring);
         consumer_sync();
-        if (s == 0) DF_STAMP(8);
+        if (s == 0) { DF_STAMP(8); DF_MARK(2); }
         // scores
         const int nk = (ntot + NRG - 1) / NRG;
         #pragma unroll 3
@@ -346,7 +364,7 @@ __device__ __noinline__ void attention_df(const HxPersist& P, const HxPhase& ph,
         consumer_sync();
         if (tid < nsl) mbar_arrive(&S.empty[S.tile_slot[nsl + tid]]);
     }
-    DF_STAMP(11); DF_MARK(2);
+    DF_STAMP(11); DF_MARK(3);
     // fold the row subsets and hand the split's partial over
 #pragma unroll
     for (int i = 0; i < GRP; i++) *reinterpret_cast<float4*>(accx + (c_sub * GRP + i) * DH + c_c * 4) = acc[i];
@@ -715,6 +733,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                         }
                     }
                 }
+                DF_MARK(1);
                 ss = hx_warp_sum(ss); mx = hx_warp_max(mx);
                 if (lane == 0) { S.red[warp] = ss; S.red[NCW + warp] = mx; }
                 consumer_sync();
@@ -727,7 +746,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                     const float vmax = tmx * inv * 1.0000005f;            // margin for the rounding of x*g*inv
                     if (vmax > 0.0f && vmax < INFINITY) Sg = __uint_as_float(__float_as_uint(vmax) & 0x7F800000u);   // vmax/Sg in [1,2)
                 }
-                DF_STAMP(14); DF_MARK(1);
+                DF_STAMP(14);
                 const float mul = (inv / Sg) * 2147483648.0f;             // |x_n| / Sg * 2^31 < 2^32
                 #pragma unroll 1
                 for (int it = tid; it < nitems; it += NCT) {
@@ -751,7 +770,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 consumer_sync();
                 if (tid == 0) mbar_arrive(&S.b_ready);
-                DF_STAMP(1);
+                DF_STAMP(1); DF_MARK(2);
 
                 // ---------- pieces of tiles: accumulator -> digits recombined -> merge -> epilogue ----------
                 ring_adv(cslot, cpar, (uint32_t)(tp.b1 - tp.b0), nring);
@@ -780,6 +799,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                         }
                         mbar_wait(&S.acc_full[buf], (uc >> 1) & 1, &S.abort_flag);
                         uc++;
+                        if (tile == t_last) DF_MARK(3);
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         uint32_t r[16];
                         const uint32_t ta = tmem + ((uint32_t)(warp * 32) << 16) + TM_D0 + buf * TC_NDIG;
@@ -799,7 +819,10 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                             ll_st(ph.part_ll + ((size_t)tile * ph.pieces + (size_t)tp.first_piece) * 128 + rl, v, ep);
                             continue;
                         }
-                        for (int q = 0; q < others; q++) v += df_wait1(ph.part_ll + ((size_t)tile * ph.pieces + (size_t)q) * 128 + rl, ep, S, P);
+                        #pragma unroll 1
+                        for (int q = 0; q < others; q += 4)
+                            v = df_wait_add4(ph.part_ll + ((size_t)tile * ph.pieces + (size_t)q) * 128 + rl, 128, min(4, others - q), ep, v, S, P);
+                        if (tile == t_last) DF_MARK(4);
                         if (ph.epi == HX_EPI_QKV) {
                             // A tile holds 128 / DH whole heads (DH is 32, 64 or 128).  Per-head RMSNorm and rotate_half
                             // RoPE on q and k; q leaves as pairs, k and v as pairs and into the cache row of this position.
@@ -940,11 +963,11 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                     default: attention_df<8>(P, ph, S, ring, digb, cslot, cpar, pi, pos); break;
                 }
             }
-            DF_STAMP(2); DF_MARK(3);
+            DF_STAMP(2); DF_MARK(5);
             // ---------- phase boundary: the digit columns and the attention scratch are free again ----------
             asm volatile("cp.async.wait_all;" ::: "memory");
             if (consumer_sync_any(S.abort_flag)) goto aborted;
-            DF_STAMP(3);
+            DF_STAMP(3); DF_MARK(6);
         }
         if (P.advance_pos && tid == 0) {
             // no lm_head in this launch: the last CTA to finish advances the position

@@ -98,6 +98,7 @@ struct hx_model {
     float *pf_x = nullptr, *pf_qkv = nullptr, *pf_ctx = nullptr, *pf_gu = nullptr, *pf_scale = nullptr; uint8_t* pf_cells = nullptr; int* pf_err = nullptr; float* pf_partial = nullptr; unsigned* pf_tickets = nullptr;
     int pf_gu_ld = 0; bool pf_batched = true; size_t pf_partial_n = 0;
     int *d_bids = nullptr, *d_bpos = nullptr, *d_bseq = nullptr, *d_bnext = nullptr; float* pf_logits = nullptr; int b_cap = 0;   // batched decode
+    int* sp_next = nullptr; float* sp_margin = nullptr;                                   // speculative decode: verify rows
     cudaGraphExec_t g_bstep = nullptr; int g_bstep_n = 0;
     int* d_pf_pos = nullptr; cudaGraphExec_t g_pf_chunk = nullptr; bool pf_graph_failed = false; int pf_chunk_launches = 0;
     // dataflow engine (hx_decode_df.cu): vectors that cross CTAs as (value, epoch) pairs
@@ -725,7 +726,7 @@ int init_persist(hx_model* m) {
     HX_CUDA(cudaMemset(m->d_err, 0, 16));
     m->bar_count = 0;
 #ifdef HX_DEBUG_STAMPS
-    if (getenv("HX_PERSIST_DBG")) { if ((rc = dalloc(m, &m->d_dbg, (size_t)16 * (m->nph_decode + 4) + (size_t)4 * m->nph_decode * m->grid_persist))) return rc; }
+    if (getenv("HX_PERSIST_DBG")) { if ((rc = dalloc(m, &m->d_dbg, (size_t)16 * (m->nph_decode + 4) + (size_t)8 * m->nph_decode * m->grid_persist))) return rc; }
 #endif
     if (m->use_tc) {
         if ((rc = dalloc(m, &m->tc_partial, m->tc_units_max * 128 + 128))) return rc;
@@ -1063,7 +1064,7 @@ HX_API int hx_model_phase_stamps(hx_model* m, unsigned long long* out, int max_p
 HX_API int hx_model_phase_stamps_all(hx_model* m, unsigned long long* out, size_t max_words, int* nphases, int* grid) {
     HX_CHECK_ARG(m && out && nphases && grid);
     if (!m->d_dbg) return hx_fail(HX_ERR_STATE, "set HX_PERSIST_DBG=1 before creating the model");
-    const size_t n = (size_t)4 * m->nph_decode * m->grid_persist;      // four events per CTA and phase
+    const size_t n = (size_t)8 * m->nph_decode * m->grid_persist;      // eight events per CTA and phase
     HX_CHECK_ARG(n <= max_words);
     HX_CUDA(cudaMemcpy(out, m->d_dbg + (size_t)16 * (m->nph_decode + 4), n * 8, cudaMemcpyDeviceToHost));
     *nphases = m->nph_decode; *grid = m->grid_persist;
@@ -1326,7 +1327,7 @@ static int bd_alloc(hx_model* m) {
     if ((rc = dalloc(m, &m->d_bpos, (size_t)m->b_cap))) return rc;
     if ((rc = dalloc(m, &m->d_bseq, (size_t)m->b_cap))) return rc;
     if ((rc = dalloc(m, &m->d_bnext, (size_t)m->b_cap))) return rc;
-    if ((rc = dalloc(m, &m->pf_logits, (size_t)HX_PF_TB * m->cfg.vocab))) return rc;
+    if (!m->pf_logits && (rc = dalloc(m, &m->pf_logits, (size_t)HX_PF_TB * m->cfg.vocab))) return rc;
     std::vector<int> seq(m->b_cap);
     for (int i = 0; i < m->b_cap; i++) seq[i] = i;
     HX_CUDA(cudaMemcpy(m->d_bseq, seq.data(), (size_t)m->b_cap * 4, cudaMemcpyHostToDevice));
@@ -1479,6 +1480,148 @@ HX_API int hx_generate_greedy(hx_model* m, const int32_t* prompt, int T, int n_n
             m->stats.kernel_launches = (uint32_t)((T - 1) * kernels_per_step(m, false) + n_new * kernels_per_step(m, true));
             m->kv_len = T + n_new - 1;
         }
+    }
+    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
+    return rc;
+}
+
+// ---- prompt-lookup speculative decode ------------------------------------------------------------------
+// The drafter of the reference (pld_draft, gpt2_infer.c:2972-2994): the longest suffix ids[T-k..T), k from k_max
+// down to k_min, is looked up backwards in ids[0..T-1); the tokens following the most recent match (at most m
+// of them, those before T) are the draft.  A match with nothing after it keeps the scan going.  Host only.
+HX_API int hx_pld_draft(const int32_t* ids, int T, int k_min, int k_max, int m, int32_t* draft) {
+    if (!ids || !draft || T < k_min + 1 || k_min < 1) return 0;
+    if (m > HX_SPEC_DRAFT_MAX) m = HX_SPEC_DRAFT_MAX;
+    if (m < 1) return 0;
+    if (k_max > T - 1) k_max = T - 1;
+    for (int k = k_max; k >= k_min; k--) {
+        const int32_t* suffix = ids + (T - k);
+        for (int start = T - k - 1; start >= 0; start--) {
+            if (memcmp(ids + start, suffix, (size_t)k * sizeof(int32_t)) != 0) continue;
+            int n = 0;
+            for (int src = start + k; n < m && src < T; src++) draft[n++] = ids[src];
+            if (n > 0) return n;
+        }
+    }
+    return 0;
+}
+
+static int spec_alloc(hx_model* m) {
+    if (!m->use_tc || !m->pf_batched || !m->head.t128 || m->tp_world > 1 || m->cfg.arch == 0)
+        return hx_fail(HX_ERR_STATE, "speculative decode needs the tensor-core engine with batched prefill on one GPU");
+    int rc = pf_alloc(m); if (rc) return rc;
+    if (!m->pf_logits && (rc = dalloc(m, &m->pf_logits, (size_t)HX_PF_TB * m->cfg.vocab))) return rc;
+    if (!m->sp_next && (rc = dalloc(m, &m->sp_next, (size_t)HX_PF_TB))) return rc;
+    if (!m->sp_margin && (rc = dalloc(m, &m->sp_margin, (size_t)HX_PF_TB))) return rc;
+    return HX_OK;
+}
+
+// The verify forward (forward_verify, gpt2_infer.c:3011-3074): the n window tokens sit at positions pos..pos+n-1
+// behind the resident prefix [0, pos); their K/V rows go into the cache at those positions, every row attends
+// [0, its own position], and every row gets its logits.  Here that is one prefill chunk that starts at `pos`
+// plus the head on all n rows; the arg-max and its margin over the runner-up are taken on the device.
+static int spec_verify(hx_model* m, const int32_t* win, int n, int pos, int32_t* a, float* margin) {
+    const hx_config& c = m->cfg;
+    const int ps[2] = {pos, 0};
+    HX_CUDA(cudaMemcpyAsync(m->d_prompt, win, (size_t)n * 4, cudaMemcpyHostToDevice, m->st));
+    HX_CUDA(cudaMemcpyAsync(m->d_pf_pos, ps, 8, cudaMemcpyHostToDevice, m->st));
+    HxPfWhere wh = {m->d_pf_pos, nullptr, nullptr, (size_t)c.n_layers * c.n_kv_heads * m->kv_cap * c.head_dim, m->d_pf_pos + 1};
+    int rc = pf_enqueue_layers(m, n, m->d_prompt, wh); if (rc) return rc;
+    if ((rc = pf_linear(m, m->head, m->pf_x, c.d_model, n, 0, m->final_g, m->pf_logits, c.vocab, m->head.N, 0, 0))) return rc;
+    hx_pf_top2_rows(m->pf_logits, c.vocab, c.vocab, n, m->sp_next, m->sp_margin, m->st);
+    HX_CUDA(cudaMemcpyAsync(a, m->sp_next, (size_t)n * 4, cudaMemcpyDeviceToHost, m->st));
+    HX_CUDA(cudaMemcpyAsync(margin, m->sp_margin, (size_t)n * 4, cudaMemcpyDeviceToHost, m->st));
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    return persist_check(m);
+}
+
+// One plain decode step of token `tok` at position `pos`; the next token comes back to the host.
+static int spec_single(hx_model* m, int32_t tok, int pos, int32_t* next) {
+    int rc = set_pos_tok(m, pos, &tok); if (rc) return rc;
+    if ((rc = step_decode(m))) return rc;
+    HX_CUDA(cudaMemcpyAsync(next, m->d_tok, 4, cudaMemcpyDeviceToHost, m->st));
+    HX_CUDA(cudaStreamSynchronize(m->st));
+    return persist_check(m);
+}
+
+// Greedy generation with prompt-lookup drafts (run_generate's HX_SPEC path and spec_step, gpt2_infer.c:3076-3118,
+// 3150-3161).  The output is the plain greedy sequence: a draft is accepted only where it equals the model's own
+// arg-max.  The verify rows come from the batched GEMM path, whose sums are ordered differently from the decode
+// kernel's, so an arg-max of a verify row is only used when it leads the runner-up by more than `min_margin`
+// (a near tie is left to the plain decode step, which then decides exactly as hx_generate_greedy does).
+HX_API int hx_generate_spec(hx_model* m, const int32_t* prompt, int T, int n_new, const hx_spec_config* cfg_in,
+                            int32_t* out_ids, hx_spec_stats* stats_out, float* ms_prefill, float* ms_decode) {
+    HX_CHECK_ARG(m && prompt && T > 0 && n_new > 0 && out_ids);
+    if (T + n_new - 1 > m->kv_cap) return hx_fail(HX_ERR_STATE, "%d prompt + %d new tokens exceed the KV capacity %d", T, n_new, m->kv_cap);
+    for (int i = 0; i < T; i++) if (prompt[i] < 0 || prompt[i] >= m->gcfg.vocab) return hx_fail(HX_ERR_ARG, "token %d outside the vocabulary", prompt[i]);
+    hx_spec_config cfg = {3, 1, 6, 1e-3f};                       // the reference's defaults (HX_SPEC_K, HX_SPEC_KMIN, HX_SPEC_M)
+    if (cfg_in) cfg = *cfg_in;
+    HX_CHECK_ARG(cfg.k_min >= 1 && cfg.k_max >= cfg.k_min && cfg.m >= 1 && cfg.min_margin >= 0.0f);
+    int rc = spec_alloc(m); if (rc) return rc;
+    const int m_cap = HX_PF_TB - 1 < HX_SPEC_DRAFT_MAX ? HX_PF_TB - 1 : HX_SPEC_DRAFT_MAX;   // window = last token + drafts = one chunk
+    const int M = cfg.m < m_cap ? cfg.m : m_cap;
+    hx_spec_stats stt = {0, 0, 0, 0, 0, 0, 0, 0};
+    std::vector<int32_t> ids(prompt, prompt + T);
+    ids.reserve((size_t)T + n_new);
+    cudaEvent_t e0, e1, e2;
+    HX_CUDA(cudaEventCreate(&e0)); HX_CUDA(cudaEventCreate(&e1)); HX_CUDA(cudaEventCreate(&e2));
+    cudaEventRecord(e0, m->st);
+    int32_t first = 0;
+    rc = run_prefill(m, prompt, T);
+    if (!rc) {
+        cudaMemcpyAsync(&first, m->d_tok, 4, cudaMemcpyDeviceToHost, m->st);
+        cudaEventRecord(e1, m->st);
+        if (cudaStreamSynchronize(m->st) != cudaSuccess) rc = hx_fail(HX_ERR_CUDA, "generate: %s", cudaGetErrorString(cudaGetLastError()));
+        else rc = persist_check(m);
+    }
+    if (!rc) ids.push_back(first);
+    int emitted = 1;
+    while (!rc && emitted < n_new) {
+        const int Tc = (int)ids.size(), pos = Tc - 1;            // ids[pos] is confirmed, its K/V row is not written yet
+        int32_t draft[HX_SPEC_DRAFT_MAX], a[HX_PF_TB]; float margin[HX_PF_TB];
+        int dn = hx_pld_draft(ids.data(), Tc, cfg.k_min, cfg.k_max, M, draft);
+        if (Tc >= cfg.k_min + 1) stt.steps++;                     // counted where the reference's drafter counts
+        if (dn > 0) { stt.hits++; stt.drafted += dn; }
+        if (pos + dn >= m->kv_cap) { dn = m->kv_cap - 1 - pos; if (dn < 0) dn = 0; }
+        int commit = 0;
+        if (dn > 0) {
+            int32_t win[HX_PF_TB];
+            win[0] = ids[pos];
+            for (int i = 0; i < dn; i++) win[1 + i] = draft[i];
+            if ((rc = spec_verify(m, win, dn + 1, pos, a, margin))) break;
+            stt.forwards++;
+            if (margin[0] > cfg.min_margin) {
+                commit = 1;
+                for (int i = 1; i <= dn; i++) {
+                    if (draft[i - 1] != a[i - 1]) break;
+                    if (!(margin[i] > cfg.min_margin)) { stt.near_ties++; break; }
+                    commit = i + 1;
+                }
+                if (commit > n_new - emitted) commit = n_new - emitted;
+                stt.accepted += commit - 1; stt.emitted += commit;     // counted like the reference: verify steps only
+            } else stt.near_ties++;
+        }
+        if (commit == 0) {                                        // no draft, or the first verify row was a near tie
+            if ((rc = spec_single(m, ids[pos], pos, &a[0]))) break;
+            stt.single_steps++;
+            commit = 1;
+        }
+        for (int i = 0; i < commit; i++) ids.push_back(a[i]);
+        emitted += commit;
+    }
+    if (!rc) {
+        cudaEventRecord(e2, m->st);
+        cudaEventSynchronize(e2);
+        float p = 0, d = 0; cudaEventElapsedTime(&p, e0, e1); cudaEventElapsedTime(&d, e1, e2);
+        if (ms_prefill) *ms_prefill = p;
+        if (ms_decode) *ms_decode = d;
+        memcpy(out_ids, ids.data() + T, (size_t)n_new * 4);
+        if (stats_out) *stats_out = stt;
+        m->kv_len = T + n_new - 1;
+        // leave the device-side cursor where hx_generate_greedy leaves it: last token, next position
+        const int32_t last = ids.back();
+        rc = set_pos_tok(m, T + n_new - 1, &last);
+        if (!rc && cudaStreamSynchronize(m->st) != cudaSuccess) rc = hx_fail(HX_ERR_CUDA, "generate: %s", cudaGetErrorString(cudaGetLastError()));
     }
     cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
     return rc;

@@ -224,6 +224,31 @@ __global__ void __launch_bounds__(1024) k_pf_argmax_rows(const float* __restrict
     if (threadIdx.x == 0) { next[blockIdx.x] = si[0] == INT_MAX ? 0 : si[0]; if (pos_arr) pos_arr[blockIdx.x] += 1; }
 }
 
+// one CTA per token row: first maximum -> next[row], and how far the runner-up lies below it -> margin[row]
+// (0 when two entries tie for the maximum).  The speculative decoder trusts a row only above a margin.
+__global__ void __launch_bounds__(1024) k_pf_top2_rows(const float* __restrict__ logits, int n, int ld, int* __restrict__ next, float* __restrict__ margin) {
+    const float* lg = logits + (size_t)blockIdx.x * ld;
+    float bv = -INFINITY, b2 = -INFINITY; int bi = INT_MAX;
+    for (int i = threadIdx.x; i < n; i += 1024) {
+        const float v = lg[i];
+        if (v > bv || (v == bv && i < bi)) { b2 = fmaxf(b2, bv); bv = v; bi = i; }
+        else b2 = fmaxf(b2, v);
+    }
+    __shared__ float sv[1024], s2[1024]; __shared__ int si[1024];
+    sv[threadIdx.x] = bv; s2[threadIdx.x] = b2; si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int s = 512; s >= 1; s >>= 1) {
+        if (threadIdx.x < s) {
+            const float ov = sv[threadIdx.x + s], o2 = s2[threadIdx.x + s]; const int oi = si[threadIdx.x + s];
+            const float mv = sv[threadIdx.x], m2 = s2[threadIdx.x];
+            if (ov > mv || (ov == mv && oi < si[threadIdx.x])) { sv[threadIdx.x] = ov; si[threadIdx.x] = oi; s2[threadIdx.x] = fmaxf(fmaxf(m2, o2), mv); }
+            else s2[threadIdx.x] = fmaxf(fmaxf(m2, o2), ov);
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) { next[blockIdx.x] = si[0] == INT_MAX ? 0 : si[0]; margin[blockIdx.x] = sv[0] - s2[0]; }
+}
+
 __global__ void __launch_bounds__(1024) k_pf_argmax(const float* __restrict__ logits, int n, int* tok, int* hist, int* pos_out, int pos) {   // pos: position of the logits row
     float bv = -INFINITY; int bi = INT_MAX;
     for (int i = threadIdx.x; i < n; i += 1024) { const float v = logits[i]; if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
@@ -289,6 +314,11 @@ void hx_pf_advance(int* posp, int n, cudaStream_t st) {
 
 void hx_pf_argmax(const float* logits, int n, int* tok, int* hist, int* pos_out, int pos, cudaStream_t st) {
     k_pf_argmax<<<1, 1024, 0, st>>>(logits, n, tok, hist, pos_out, pos);
+    HX_COUNT_LAUNCH(1);
+}
+
+void hx_pf_top2_rows(const float* logits, int n, int ld, int rows, int* next, float* margin, cudaStream_t st) {
+    k_pf_top2_rows<<<rows, 1024, 0, st>>>(logits, n, ld, next, margin);
     HX_COUNT_LAUNCH(1);
 }
 

@@ -41,4 +41,5 @@ void hx_pf_advance(int* posp, int n, cudaStream_t st);
 // First maximum of logits[0..n): index to *tok and hist[pos + 1]; *pos_out = pos + 1.
 void hx_pf_argmax(const float* logits, int n, int* tok, int* hist, int* pos_out, int pos, cudaStream_t st);
 // per-row arg-max of logits [rows][ld] (n valid columns) -> next[row]; pos_arr[row] += 1 when given
+void hx_pf_top2_rows(const float* logits, int n, int ld, int rows, int* next, float* margin, cudaStream_t st);
 void hx_pf_argmax_rows(const float* logits, int n, int ld, int rows, int* next, int* pos_arr, cudaStream_t st);

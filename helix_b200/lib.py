@@ -36,6 +36,22 @@ class HxStepStats(C.Structure):
                 ("ms_attn", C.c_float), ("ms_other", C.c_float)]
 
 
+class HxPackReport(C.Structure):
+    _fields_ = [("tensors", C.c_int), ("packed", C.c_int), ("bytes", C.c_uint64), ("worst_rms", C.c_double), ("worst_name", C.c_char * 128),
+                ("f32_exact", C.c_int), ("verified", C.c_int), ("ms_pack", C.c_float), ("ms_verify", C.c_float)]
+
+
+class HxSpecConfig(C.Structure):
+    _fields_ = [("k_max", C.c_int), ("k_min", C.c_int), ("m", C.c_int), ("min_margin", C.c_float)]
+
+
+class HxSpecStats(C.Structure):
+    _fields_ = [(n, C.c_long) for n in ("steps", "hits", "drafted", "accepted", "emitted", "forwards", "single_steps", "near_ties")]
+
+    def as_dict(self):
+        return {n: int(getattr(self, n)) for n, _ in self._fields_}
+
+
 def _cfg(n_layers, d_model, n_heads, n_kv_heads, head_dim, d_ff, vocab, max_ctx=40960, theta=1e6, eps=1e-5):
     return HxConfig(1, n_layers, d_model, n_heads, n_kv_heads, head_dim, d_ff, vocab, max_ctx, theta, eps, 1)
 
@@ -114,6 +130,10 @@ _SIGS = {
     "hx_prefill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "hx_prefill_seq": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "hx_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "hx_pack_qwen3": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int, C.POINTER(HxPackReport)]),
+    "hx_pld_draft": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "hx_generate_spec": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(HxSpecConfig), C.c_void_p, C.POINTER(HxSpecStats),
+                                   C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "hx_model_last_stats": (C.c_int, [C.c_void_p, C.POINTER(HxStepStats)]),
     "hx_model_engine": (C.c_char_p, [C.c_void_p]),
     "hx_model_debug_waits": (C.c_int, [C.c_void_p, C.c_uint, C.c_int]),
@@ -362,6 +382,17 @@ class Model:
         check(lib().hx_generate_greedy(self.h, prompt.ctypes.data, len(prompt), n_new, out.ctypes.data, C.byref(a), C.byref(b)))
         return out, a.value, b.value
 
+    def generate_spec(self, prompt, n_new, k_max=3, k_min=1, m=6, min_margin=1e-3):
+        """Prompt-lookup speculative greedy decode: (tokens, counters, ms_prefill, ms_decode)."""
+        prompt = np.ascontiguousarray(prompt, np.int32)
+        out = np.zeros(n_new, np.int32)
+        cfg = HxSpecConfig(k_max, k_min, m, min_margin)
+        st = HxSpecStats()
+        a, b = C.c_float(), C.c_float()
+        check(lib().hx_generate_spec(self.h, prompt.ctypes.data, len(prompt), n_new, C.byref(cfg), out.ctypes.data, C.byref(st),
+                                     C.byref(a), C.byref(b)))
+        return out, st.as_dict(), a.value, b.value
+
     def decode_loop(self, tok, pos0, n_steps):
         ids = np.array([tok], np.int32)
         out = np.zeros(n_steps, np.int32)
@@ -410,3 +441,19 @@ class Model:
         b = C.create_string_buffer(65)
         check(lib().hx_model_sha256(self.h, b))
         return b.value.decode()
+
+
+def pld_draft(ids, k_min=1, k_max=3, m=6):
+    """The host-side n-gram drafter of the speculative decoder: the draft tokens for the sequence `ids`."""
+    ids = np.ascontiguousarray(ids, np.int32)
+    out = np.zeros(16, np.int32)
+    n = lib().hx_pld_draft(ids.ctypes.data, len(ids), k_min, k_max, m, out.ctypes.data)
+    return out[:n].copy()
+
+
+def pack_qwen3(model_dir, out_path, verify=True):
+    """Safetensors checkpoint directory -> HXGW v3 NVFP4 file on the GPU; returns the report as a dict."""
+    rep = HxPackReport()
+    check(lib().hx_pack_qwen3(os.fsencode(model_dir), os.fsencode(out_path), 1 if verify else 0, C.byref(rep)))
+    return dict(tensors=rep.tensors, packed=rep.packed, bytes=rep.bytes, worst_rms=rep.worst_rms, worst_name=rep.worst_name.decode(),
+                f32_exact=bool(rep.f32_exact), verified=bool(rep.verified), ms_pack=rep.ms_pack, ms_verify=rep.ms_verify)

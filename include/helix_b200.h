@@ -140,6 +140,23 @@ int hx_gemm_nvfp4_tc(const uint8_t* a_t128, int rows, int K, const uint8_t* b_ce
 int hx_gemm_nvfp4_tc_bench(const uint8_t* a_t128, int rows, int K, const uint8_t* b_cells, int ncols, float* y,
                            int stage_ksteps, int reps, float* ms_per_launch);
 
+/* ---------------------------------------------------------------- importer -------------------- */
+/* Safetensors checkpoint directory (config.json + model.safetensors, or model.safetensors.index.json and its
+ * shards; F32 or BF16 tensors) -> HXGW v3 NVFP4 file, quantized on the GPU.  Replaces pack_qwen3,
+ * helixc/runtime/gpt2_pack.c:587-733: same tensor order, header, descriptors and bytes.  With verify != 0 the
+ * written file is read back like the reference does (:692-732): every packed tensor dequantized from the file
+ * must stay within 0.15 relative RMS error of its source and every dense tensor must be bit-exact, else
+ * HX_ERR_FORMAT.  Uses the current device; synchronous. */
+typedef struct {
+    int tensors, packed;       /* tensors written, of them NVFP4-packed */
+    uint64_t bytes;            /* size of the file */
+    double worst_rms;          /* worst rmse / rms_w over the packed tensors (0 without verify) */
+    char worst_name[128];
+    int f32_exact, verified;
+    float ms_pack, ms_verify;
+} hx_pack_report;
+int hx_pack_qwen3(const char* model_dir, const char* out_path, int verify, hx_pack_report* report);
+
 /* ---------------------------------------------------------------- SHA-256 / receipt ----------- */
 /* FIPS 180-4.  Replaces sha256 / sha256_hex / sha256_file, gpt2_infer.c:137-213. */
 int hx_sha256(const void* data, size_t n, uint8_t out[32]);
@@ -233,6 +250,31 @@ int hx_prefill_seq(hx_model* m, int seq, const int32_t* ids, int T, int32_t* nex
  * ms_decode (may be NULL) receives the device time of the decode steps alone. */
 int hx_generate_greedy(hx_model* m, const int32_t* prompt, int T, int n_new, int32_t* out_ids,
                        float* ms_prefill, float* ms_decode);
+
+/* Prompt-lookup speculative greedy decode (the reference's HX_SPEC path: pld_draft, forward_verify, spec_step,
+ * helixc/runtime/gpt2_infer.c:2972-3118, driven from run_generate :3150-3161).  The tokens written to out_ids are
+ * the plain greedy sequence of hx_generate_greedy; a step that finds the last k_max..k_min tokens earlier in the
+ * sequence verifies the (at most m, at most 15) tokens that followed them in one batched forward and keeps the
+ * leading ones the model agrees with, plus the model's own next token.
+ * Differences from the reference: no EOS stop (n_new tokens are always produced, as in hx_generate_greedy); a
+ * verify row is used only if its best logit leads the runner-up by more than min_margin, because the batched rows
+ * and the single-token kernel add their products in different orders -- a closer call is left to the plain step.
+ * cfg NULL = {3, 1, 6, 1e-3f}.  Counters steps..forwards are the reference's [specprof] counters. */
+#define HX_SPEC_DRAFT_MAX 16
+typedef struct { int k_max, k_min, m; float min_margin; } hx_spec_config;
+typedef struct {
+    long steps;        /* drafter calls */
+    long hits;         /* of them, with a draft */
+    long drafted;      /* draft tokens proposed */
+    long accepted;     /* draft tokens kept */
+    long emitted;      /* tokens produced by verify forwards */
+    long forwards;     /* verify forwards */
+    long single_steps; /* plain decode steps (no draft, or a near tie on the first verify row) */
+    long near_ties;    /* verify rows not trusted */
+} hx_spec_stats;
+int hx_pld_draft(const int32_t* ids, int T, int k_min, int k_max, int m, int32_t* draft);   /* host only; returns the draft length */
+int hx_generate_spec(hx_model* m, const int32_t* prompt, int T, int n_new, const hx_spec_config* cfg,
+                     int32_t* out_ids, hx_spec_stats* stats, float* ms_prefill, float* ms_decode);
 
 /* Device time accounting of the last hx_generate_greedy / hx_decode_loop call. */
 typedef struct {

@@ -682,6 +682,61 @@ ORC_API int orc_model_generate(OrcModel* m, const int* ids, int T, int n_new, in
     return 0;
 }
 
+/* Prompt-lookup drafter: pld_draft, gpt2_infer.c:2972-2994.  For k = k_max (capped to T-1) down to k_min the
+ * last k tokens are searched for backwards from candidate start T-k-1; the first candidate that is followed by
+ * at least one token before T gives the draft (those tokens, at most m, cap 16).  Returns the draft length. */
+ORC_API int orc_pld_draft(const int* ids, int T, int k_min, int k_max, int m, int* draft) {
+    if (T < k_min + 1) return 0;
+    if (m > 16) m = 16;
+    if (m < 1) return 0;
+    int k = k_max > T - 1 ? T - 1 : k_max;
+    while (k >= k_min) {
+        int j = T - k - 1;
+        while (j >= 0) {
+            int same = 1, t = 0;
+            while (t < k && same) { same = ids[j + t] == ids[T - k + t]; t++; }
+            if (same) {
+                int n = 0, src = j + k;
+                while (n < m && src < T) draft[n++] = ids[src++];
+                if (n > 0) return n;
+            }
+            j--;
+        }
+        k--;
+    }
+    return 0;
+}
+
+/* One speculative generation at the level of tokens: spec_step + run_generate's HX_SPEC loop, gpt2_infer.c:3076-3118,
+ * 3150-3161, with the verify forward replaced by what it is defined to equal -- the plain greedy continuation
+ * `greedy` (n_new tokens after the T prompt tokens).  Produces the counters of the reference's [specprof] line for
+ * that sequence: stats = {steps, hits, drafted, accepted, emitted, forwards}.  kv_cap clamps a draft like :3084. */
+ORC_API void orc_spec_counters(const int* prompt, int T, const int* greedy, int n_new, int k_min, int k_max, int m,
+                               int kv_cap, long* stats) {
+    int* ids = (int*)malloc((size_t)(T + n_new) * sizeof(int));
+    memcpy(ids, prompt, (size_t)T * sizeof(int));
+    for (int i = 0; i < 6; i++) stats[i] = 0;
+    int len = T, step = 0;
+    ids[len++] = greedy[0]; step = 1;                      /* step 0 is the prefill forward */
+    while (step < n_new) {
+        int draft[16];
+        int pos = len - 1;
+        int dn = orc_pld_draft(ids, len, k_min, k_max, m, draft);
+        if (len >= k_min + 1) stats[0]++;
+        if (dn > 0) { stats[1]++; stats[2] += dn; }
+        if (pos + dn >= kv_cap) { dn = kv_cap - 1 - pos; if (dn < 0) dn = 0; }
+        if (dn == 0) { ids[len] = greedy[len - T]; len++; step++; continue; }
+        /* the verify rows' arg-maxes are the greedy tokens that follow (t, d_1..d_i) while the drafts are right */
+        int commit = 1;
+        for (int i = 1; i <= dn; i++) { if (draft[i - 1] == greedy[len - T + i - 1]) commit = i + 1; else break; }
+        if (commit > n_new - step) commit = n_new - step;
+        for (int i = 0; i < commit; i++) { ids[len] = greedy[len - T]; len++; }
+        stats[3] += commit - 1; stats[4] += commit; stats[5]++;
+        step += commit;
+    }
+    free(ids);
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

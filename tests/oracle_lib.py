@@ -78,6 +78,10 @@ def oracle():
     lib.orc_model_decode.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     lib.orc_model_prefill.argtypes = [C.c_void_p, i32p, C.c_int, C.c_void_p]
     lib.orc_model_generate.argtypes = [C.c_void_p, i32p, C.c_int, C.c_int, i32p, C.c_void_p]
+    lib.orc_pld_draft.argtypes = [i32p, C.c_int, C.c_int, C.c_int, C.c_int, i32p]
+    lib.orc_pld_draft.restype = C.c_int
+    lib.orc_spec_counters.argtypes = [i32p, C.c_int, i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    lib.orc_spec_counters.restype = None
     _orc = lib
     return lib
 
@@ -216,22 +220,49 @@ def write_v3(path, cfg, tensors, quant=None):
     return cur
 
 
-def write_safetensors(path, tensors):
-    """Minimal single-file safetensors writer (F32), enough for the reference importer
-    (gpt2_pack.c:45-207 reads the JSON header, dtype, shape and data_offsets)."""
+def to_bf16_bits(t):
+    """f32 -> the upper 16 bits, round to nearest even (what a BF16 checkpoint stores)."""
+    u = np.ascontiguousarray(t, np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def from_bf16_bits(b):
+    return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def write_safetensors(path, tensors, dtype="F32"):
+    """Minimal safetensors writer (F32 or BF16), enough for the reference importer (gpt2_pack.c:45-207 reads the
+    JSON header, dtype, shape and data_offsets)."""
     import json
-    hdr, off = {}, 0
+    hdr, off, blobs = {"__metadata__": {"format": "pt"}}, 0, []
     for name, t in tensors.items():
-        n = t.size * 4
-        hdr[name] = {"dtype": "F32", "shape": list(t.shape), "data_offsets": [off, off + n]}
-        off += n
+        b = (to_bf16_bits(t) if dtype == "BF16" else np.ascontiguousarray(t, np.float32)).tobytes()
+        hdr[name] = {"dtype": dtype, "shape": list(t.shape), "data_offsets": [off, off + len(b)]}
+        off += len(b); blobs.append(b)
     js = json.dumps(hdr, separators=(",", ":")).encode()
     js += b" " * ((8 - len(js) % 8) % 8)
     with open(path, "wb") as f:
         f.write(struct.pack("<Q", len(js)))
         f.write(js)
-        for t in tensors.values():
-            f.write(np.ascontiguousarray(t, np.float32).tobytes())
+        for b in blobs:
+            f.write(b)
+
+
+def write_sharded_checkpoint(d, cfg, tensors, n_shards=2, dtype="BF16"):
+    """A checkpoint directory the way the hub lays it out: config.json, model-0000i-of-0000n.safetensors and
+    model.safetensors.index.json with the weight_map."""
+    import json
+    names = list(tensors)
+    per = (len(names) + n_shards - 1) // n_shards
+    wmap = {}
+    for s in range(n_shards):
+        fn = "model-%05d-of-%05d.safetensors" % (s + 1, n_shards)
+        part = {n: tensors[n] for n in names[s * per:(s + 1) * per]}
+        write_safetensors(os.path.join(d, fn), part, dtype)
+        for n in part:
+            wmap[n] = fn
+    json.dump({"metadata": {"total_size": 0}, "weight_map": wmap}, open(os.path.join(d, "model.safetensors.index.json"), "w"))
+    write_qwen3_config(os.path.join(d, "config.json"), cfg)
 
 
 def write_qwen3_config(path, cfg):
@@ -290,3 +321,21 @@ class OracleModel:
         out = np.zeros(n_new, np.int32)
         assert self.lib.orc_model_generate(self.h, ids, len(ids), n_new, out, None) == 0
         return out
+
+
+def pld_draft(ids, k_min=1, k_max=3, m=6):
+    ids = np.ascontiguousarray(ids, np.int32)
+    out = np.zeros(16, np.int32)
+    n = oracle().orc_pld_draft(ids, len(ids), k_min, k_max, m, out)
+    return out[:n].copy()
+
+
+SPEC_COUNTERS = ("steps", "hits", "drafted", "accepted", "emitted", "forwards")
+
+
+def spec_counters(prompt, greedy, k_min=1, k_max=3, m=6, kv_cap=1 << 30):
+    """The reference's [specprof] counters for a prompt whose plain greedy continuation is `greedy`."""
+    prompt = np.ascontiguousarray(prompt, np.int32); greedy = np.ascontiguousarray(greedy, np.int32)
+    st = (C.c_long * 6)()
+    oracle().orc_spec_counters(prompt, len(prompt), greedy, len(greedy), k_min, k_max, m, kv_cap, st)
+    return dict(zip(SPEC_COUNTERS, [int(v) for v in st]))

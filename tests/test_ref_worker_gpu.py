@@ -112,3 +112,40 @@ def test_worker_fused_decode_tokens_against_the_cpu_restatement(case, image):
     rc, out = run_worker(image, case["path"], ["--generate", str(N_GEN), d + "/ids.txt", d + "/oracle_gen.txt"], FUSED, d)
     assert "TOKEN_FOR_TOKEN_MATCH" in out and "GPT2_GENERATE_MATCH_PASS" in out and rc == 0, out[-3000:]
     assert "fused dequant-GEMV module ON" in out and "HX_GEMV3 ACTIVE" in out, out[-3000:]
+
+
+N_SPEC = 48
+
+
+@pytest.mark.parametrize("image", ["kovc", "ours"])
+def test_worker_speculative_decode_against_this_library(case, image):
+    """The worker's HX_SPEC path (pld_draft / forward_verify / spec_step, gpt2_infer.c:2972-3118) on a prompt that
+    repeats: its tokens are the plain greedy tokens, and its [specprof] counters equal both the token-level replay of
+    its accept rule (oracle_lib.spec_counters) and the counters of hx_generate_spec on the same file."""
+    import re
+    if case["cfg"]["NH"] * case["cfg"]["DH"] != case["cfg"]["DM"]:
+        pytest.skip("the worker's KV decode path needs n_heads * head_dim == d_model")
+    d = case["dir"]
+    base = np.random.default_rng(SEED_IDS + 1).integers(0, case["cfg"]["NV"], 5).astype(np.int32)
+    prompt = np.concatenate([base, base, base[:3]]).astype(np.int32)
+    om = ol.OracleModel(case["path"], kv_cap=128)
+    greedy = om.generate(prompt, N_SPEC)
+    om.close()
+    open(d + "/ids_spec.txt", "w").write(" ".join(str(int(t)) for t in prompt) + "\n")
+    open(d + "/oracle_gen_spec.txt", "w").write(" ".join(str(int(t)) for t in list(prompt) + list(greedy)) + "\n")
+    rc, out = run_worker(image, case["path"], ["--generate", str(N_SPEC), d + "/ids_spec.txt", d + "/oracle_gen_spec.txt"],
+                         dict(HX_KV="1", HX_FAST="1", HX_SPEC="1"), d)
+    assert "TOKEN_FOR_TOKEN_MATCH" in out and rc == 0, out[-3000:]
+    mt = re.search(r"\[specprof\] steps=(\d+) hits=(\d+) drafted=(\d+) accepted=(\d+) emitted=(\d+) forwards=(\d+)", out)
+    assert mt, out[-3000:]
+    worker = dict(zip(ol.SPEC_COUNTERS, [int(v) for v in mt.groups()]))
+    replay = ol.spec_counters(prompt, greedy)
+    print(f"{case['name']} [{image}] worker specprof {worker}")
+    assert worker == replay
+    assert worker["accepted"] > 0                        # the toy models repeat themselves: drafts are accepted
+    gm = hb.Model.load(case["path"], kv_cap=128)
+    spec, st, _, _ = gm.generate_spec(prompt, N_SPEC)
+    gm.close()
+    assert list(spec) == list(greedy)
+    if st["near_ties"] == 0:
+        assert {k: st[k] for k in ol.SPEC_COUNTERS} == worker
