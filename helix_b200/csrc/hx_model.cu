@@ -1523,7 +1523,9 @@ static int spec_alloc(hx_model* m) {
 static int spec_verify(hx_model* m, const int32_t* win, int n, int pos, int32_t* a, float* margin) {
     const hx_config& c = m->cfg;
     const int ps[2] = {pos, 0};
-    HX_CUDA(cudaMemcpyAsync(m->d_prompt, win, (size_t)n * 4, cudaMemcpyHostToDevice, m->st));
+    if (pos < 0 || pos + n > m->kv_cap) return hx_fail(HX_ERR_STATE, "verify window [%d, %d) outside the KV capacity %d", pos, pos + n, m->kv_cap);
+    // the chunk kernels index the token buffer by position, as the prompt is laid out: the window goes to its positions
+    HX_CUDA(cudaMemcpyAsync(m->d_prompt + pos, win, (size_t)n * 4, cudaMemcpyHostToDevice, m->st));
     HX_CUDA(cudaMemcpyAsync(m->d_pf_pos, ps, 8, cudaMemcpyHostToDevice, m->st));
     HxPfWhere wh = {m->d_pf_pos, nullptr, nullptr, (size_t)c.n_layers * c.n_kv_heads * m->kv_cap * c.head_dim, m->d_pf_pos + 1};
     int rc = pf_enqueue_layers(m, n, m->d_prompt, wh); if (rc) return rc;

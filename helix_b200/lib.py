@@ -375,6 +375,10 @@ class Model:
         check(lib().hx_prefill_seq(self.h, seq, ids.ctypes.data, len(ids), nxt.ctypes.data, lg.ctypes.data if want_logits else None))
         return (int(nxt[0]), lg) if want_logits else int(nxt[0])
 
+    def reset(self):
+        """Forget the cached positions (the next prefill starts a new sequence)."""
+        check(lib().hx_model_reset(self.h))
+
     def generate(self, prompt, n_new):
         prompt = np.ascontiguousarray(prompt, np.int32)
         out = np.zeros(n_new, np.int32)
