@@ -55,9 +55,16 @@ typedef unsigned long long u64;
 #ifdef HX_DEBUG_STAMPS
 #define DF_STAMP(i) do { if (P.dbg && cta == P.dbg_cta && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg[pi * 16 + (i)] = _t; } } while (0)
 #define DF_MARK(ev) do { if (P.dbg_all && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); P.dbg_all[((size_t)pi * gridDim.x + blockIdx.x) * 8 + (ev)] = _t; } } while (0)
+#define DF_GT(v) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v))
+#define DF_MMA_T0() unsigned long long _w0; DF_GT(_w0)
+#define DF_MMA_T1() do { unsigned long long _w1; DF_GT(_w1); dbg_wait += _w1 - _w0; } while (0)
+#define DF_MMA_OUT() do { if (P.dbg_all) { unsigned long long _t; DF_GT(_t); P.dbg_all[((size_t)pi * gridDim.x + blockIdx.x) * 8 + 7] = _t; P.dbg_all[((size_t)pi * gridDim.x + blockIdx.x) * 8 + 6] = dbg_wait; } } while (0)
 #else
 #define DF_STAMP(i) do { } while (0)
 #define DF_MARK(ev) do { } while (0)
+#define DF_MMA_T0() do { } while (0)
+#define DF_MMA_T1() do { } while (0)
+#define DF_MMA_OUT() do { } while (0)
 #endif
 
 namespace {
@@ -229,6 +236,62 @@ __device__ __forceinline__ void ring_adv(uint32_t& slot, uint32_t& par, uint32_t
     slot += n;
     while (slot >= nring) { slot -= nring; par ^= 1u; }
 }
+// The splits of a head merged into the attention output, by one CTA per head: the CTA of (kv head, split s) takes
+// the heads s, s + ns, ... of its group once its own partial is out.  out[d] = sum_s w_s acc_s[d] with
+// w_s = exp(m_s - M) / sum_s l_s exp(m_s - M); splits are added in split order, so the result does not depend on
+// timing.  The o_proj phase then reads a plain vector.
+__device__ __noinline__ void attention_merge_df(const HxPersist& P, const HxPhase& ph, SmemDf& S, int kv, int split, int ns, int grp, unsigned ep) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int DH = ph.DH;
+    float* wm = S.wgt; float* wl = S.wgt + 1152;                  // ns <= 1152 (the host checks heads * splits <= 2304)
+    #pragma unroll 1
+    for (int i = split; i < grp; i += ns) {
+        const int h = kv * grp + i;
+        if (warp == 0) {
+            const u64* pml = ph.pml_ll + 2 * (size_t)h * ns;
+            float M = -INFINITY;
+            #pragma unroll 1
+            for (int s = lane; s < ns; s += 32) { float m, l; df_wait2(pml + 2 * s, ep, m, l, S, P); wm[s] = m; wl[s] = l; M = fmaxf(M, m); }
+            M = hx_warp_max(M);
+            float L = 0.0f;
+            #pragma unroll 1
+            for (int s = lane; s < ns; s += 32) { const float w = __expf(wm[s] - M); wm[s] = w; L = fmaf(wl[s], w, L); }
+            L = hx_warp_sum(L);
+            #pragma unroll 1
+            for (int s = lane; s < ns; s += 32) wm[s] = wm[s] / L;
+        }
+        consumer_sync();
+        constexpr int SB = 12;
+        #pragma unroll 1
+        for (int d2 = tid; d2 < (DH >> 1); d2 += NCT) {
+            const u64* pa = ph.pacc_ll + (size_t)h * ns * DH + 2 * d2;
+            float o0 = 0.0f, o1 = 0.0f;
+            #pragma unroll 1
+            for (int s0 = 0; s0 < ns; s0 += SB) {
+                const int n = min(SB, ns - s0);
+                u64 w[SB][2];
+                const unsigned lim = S.abort_flag ? 1u : S.wait_limit;
+                bool ok = false;
+                #pragma unroll 1
+                for (unsigned t = 0; t < lim && !ok; t++) {
+#pragma unroll
+                    for (int c = 0; c < SB; c++) { w[c][0] = w[c][1] = 0; if (c < n) ll_ld2(pa + (size_t)(s0 + c) * DH, w[c][0], w[c][1]); }
+                    ok = true;
+#pragma unroll
+                    for (int c = 0; c < SB; c++) if (c < n) ok = ok && ll_ok(w[c][0], ep) && ll_ok(w[c][1], ep);
+                    if (!ok && (t & 63u) == 63u && df_gave_up(S, P)) break;
+                }
+                if (!ok) df_fail(S, P);
+#pragma unroll
+                for (int c = 0; c < SB; c++) if (c < n) { const float wg = wm[s0 + c]; o0 = fmaf(ll_val(w[c][0]), wg, o0); o1 = fmaf(ll_val(w[c][1]), wg, o1); }
+            }
+            ll_st(ph.out_ll + (size_t)h * DH + 2 * d2, o0, ep);
+            ll_st(ph.out_ll + (size_t)h * DH + 2 * d2 + 1, o1, ep);
+        }
+        consumer_sync();                                            // the weights are reused by the next head
+    }
+}
+
 template <int GRP>
 __device__ __noinline__ void attention_df(const HxPersist& P, const HxPhase& ph, SmemDf& S, uint8_t* ring, uint8_t* digb,
                                           uint32_t& cslot, uint32_t& cpar, int pi, int pos) {
@@ -265,6 +328,7 @@ __device__ __noinline__ void attention_df(const HxPersist& P, const HxPhase& ph,
             const int hs = (ap.kv * GRP + i / DH) * ns + ap.split;
             ll_st(ph.pacc_ll + (size_t)hs * DH + i % DH, 0.0f, ep);
         }
+        attention_merge_df(P, ph, S, ap.kv, ap.split, ns, GRP, ep);
         return;
     }
     float4 acc[GRP];
@@ -378,6 +442,8 @@ __device__ __noinline__ void attention_df(const HxPersist& P, const HxPhase& ph,
         ll_st(ph.pacc_ll + (size_t)hs * DH + d, O, ep);
         if (d == 0) { ll_st(ph.pml_ll + 2 * hs, S.att_m[i], ep); ll_st(ph.pml_ll + 2 * hs + 1, S.att_l[i], ep); }
     }
+    DF_MARK(4);
+    attention_merge_df(P, ph, S, ap.kv, ap.split, ns, GRP, ep);
 }
 
 template <bool TP>
@@ -497,6 +563,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                     ok = mbar_wait(&S.b_ready, tcph & 1, &S.abort_flag);        // digit columns of this phase are in place
                     tcph++;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    unsigned long long dbg_wait = 0; (void)dbg_wait;
                     int kc = tp.k0, dp = 0;              // K cell of the tile, its position among the digit cells
                     bool fresh = true;
                     uint32_t dcol = 0;
@@ -508,7 +575,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                             if (!ok) break;
                             dcol = tmem + TM_D0 + buf * TC_NDIG;
                         }
-                        ok = mbar_wait(&S.full[slot], par, &S.abort_flag);
+                        { DF_MMA_T0(); ok = mbar_wait(&S.full[slot], par, &S.abort_flag); DF_MMA_T1(); }
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         // descriptors advance in 16-byte units: a K step is 32 B of a swizzled row, a scale chunk 512 B
@@ -531,6 +598,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                             uc++; kc = 0; fresh = true;
                         }
                     }
+                    DF_MMA_OUT();
                 } else if (ph.type == HX_PH_ATTN) {
                     ring_adv(slot, par, 2u * (uint32_t)ap.nslots, nring);         // ring slots the consumers use for K and V rows
                 }
@@ -564,172 +632,72 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
                 const HxCtaPlan tp = ph.plan[cta];
                 const unsigned in_ep = P.ep_base + (unsigned)ph.in_dep + 1u;
                 const bool rms = ph.norm == HX_NORM_RMS;
-                const bool merge_in = ph.norm == HX_NORM_ATTN;
                 // layer 0: the embedding row of the token is the input of qkv and the residual of o_proj
                 const float* xrow = ph.tok ? ph.x + (size_t)(ph.tok[P.tok_by_pos ? pos : 0]) * (size_t)ph.res_ld : ph.x;
                 const int nitems = tp.run * 32;
                 float* xs = reinterpret_cast<float*>(digb + (size_t)tp.run * 2048);
                 float ss = 0.0f, mx = 0.0f;
-                if (merge_in) {
-                    // x is the merge of the attention splits: x[h*DH + d] = sum_s w[h][s] * acc[h][s][d] with
-                    // w[h][s] = exp(m_s - M_h) / sum_s l_s exp(m_s - M_h).  Weights of all heads first: a warp takes heads
-                    // warp, warp + NCW, ... and polls the (max, sum) pairs of four of them together (lane = split).
-                    const int NS = S.att_ns, DHh = ph.DH;
-                    constexpr int HPW = 4;
-                    #pragma unroll 1
-                    for (int hb = warp; hb < ph.NH; hb += NCW * HPW) {
-                        u64 wm[HPW][2], wl[HPW][2];
-                        const unsigned lim = S.abort_flag ? 1u : S.wait_limit;
-                        bool ok = false;
+                {
+                    // Sum of squares of the whole input: per-tile sums published by the producing epilogue, added in tile
+                    // order (every CTA gets the same bits); layer 0 reads the embedding row itself.
+                    if (rms && !ph.in_stat) {
                         #pragma unroll 1
-                        for (unsigned t = 0; t < lim && !ok; t++) {
-                            ok = true;
-#pragma unroll
-                            for (int u = 0; u < HPW; u++)
-#pragma unroll
-                                for (int j = 0; j < 2; j++) {
-                                    const int h = hb + u * NCW, sidx = lane + 32 * j;
-                                    wm[u][j] = wl[u][j] = 0;
-                                    if (h < ph.NH && sidx < NS) {
-                                        ll_ld2(ph.pml_ll + 2 * (h * NS + sidx), wm[u][j], wl[u][j]);
-                                        ok = ok && ll_ok(wm[u][j], in_ep) && ll_ok(wl[u][j], in_ep);
-                                    }
-                                }
-                            ok = __all_sync(0xffffffffu, ok);
-                            if (!ok && (t & 63u) == 63u && df_gave_up(S, P)) break;
-                        }
-                        if (!ok) df_fail(S, P);
-#pragma unroll
-                        for (int u = 0; u < HPW; u++) {
-                            const int h = hb + u * NCW;
-                            if (h >= ph.NH) break;
-                            const float m0 = lane < NS ? ll_val(wm[u][0]) : -INFINITY, m1 = lane + 32 < NS ? ll_val(wm[u][1]) : -INFINITY;
-                            const float l0 = lane < NS ? ll_val(wl[u][0]) : 0.0f, l1 = lane + 32 < NS ? ll_val(wl[u][1]) : 0.0f;
-                            const float M = hx_warp_max(fmaxf(m0, m1));
-                            const float w0 = __expf(m0 - M), w1 = __expf(m1 - M);
-                            const float Lsum = hx_warp_sum(l0 * w0 + l1 * w1);
-                            if (lane < NS) S.wgt[h * NS + lane] = w0 / Lsum;
-                            if (lane + 32 < NS) S.wgt[h * NS + lane + 32] = w1 / Lsum;
+                        for (int k = tid * 4; k < K; k += NCT * 4) {
+                            const float4 a = __ldcg(reinterpret_cast<const float4*>(xrow + k));
+                            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
                         }
                     }
-                    consumer_sync();
-                    // two threads per item of eight elements; the pairs of up to SB splits are polled together
-                    const int half = tid & 1;
-                    constexpr int SB = 12;
+                    // A unit is two consecutive elements (one 16-byte load), so a warp's load is 512 contiguous bytes.  UI
+                    // units per thread and round are in flight together, with the norm gains fetched before the wait and,
+                    // in the first round of warp 0, the per-tile sums of squares polled in the same breath.
+                    constexpr int UI = 8;
+                    const int nunits = nitems * 4;
                     #pragma unroll 1
-                    for (int it = tid >> 1; it < nitems; it += NCT / 2) {
-                        int kc = tp.k0 + (it >> 5); if (kc >= tp.C) kc -= tp.C;
-                        const int k = kc * 256 + (it & 31) * 8 + 4 * half;
-                        float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
-                        if (k < K) {
-                            const int h = k / DHh, d = k - h * DHh;
-                            const u64* pa = ph.pacc_ll + (size_t)(h * NS) * DHh + d;
-                            #pragma unroll 1
-                            for (int s0 = 0; s0 < NS; s0 += SB) {
-                                const int n = min(SB, NS - s0);
-                                u64 w[SB][4];
-                                const unsigned lim = S.abort_flag ? 1u : S.wait_limit;
-                                bool ok = false;
-                                #pragma unroll 1
-                                for (unsigned t = 0; t < lim && !ok; t++) {
+                    for (int u0 = tid; u0 < nunits; u0 += UI * NCT) {
+                        int kk[UI]; float2 gg[UI]; u64 w[UI][2];
 #pragma unroll
-                                    for (int c = 0; c < SB; c++) {
-                                        w[c][0] = w[c][1] = w[c][2] = w[c][3] = 0;
-                                        if (c < n) { const u64* q = pa + (size_t)((s0 + c) * DHh); ll_ld2(q, w[c][0], w[c][1]); ll_ld2(q + 2, w[c][2], w[c][3]); }
-                                    }
-                                    ok = true;
-#pragma unroll
-                                    for (int c = 0; c < SB; c++) if (c < n) ok = ok && ll_ok(w[c][0], in_ep) && ll_ok(w[c][1], in_ep) && ll_ok(w[c][2], in_ep) && ll_ok(w[c][3], in_ep);
-                                    if (!ok && (t & 63u) == 63u && df_gave_up(S, P)) break;
-                                }
-                                if (!ok) df_fail(S, P);
-#pragma unroll
-                                for (int c = 0; c < SB; c++) if (c < n) {
-                                    const float wg = S.wgt[h * NS + s0 + c];
-                                    o0 = fmaf(ll_val(w[c][0]), wg, o0); o1 = fmaf(ll_val(w[c][1]), wg, o1);
-                                    o2 = fmaf(ll_val(w[c][2]), wg, o2); o3 = fmaf(ll_val(w[c][3]), wg, o3);
-                                }
-                            }
+                        for (int j = 0; j < UI; j++) {
+                            const int u = u0 + j * NCT;
+                            int kc = tp.k0 + (u >> 7); if (kc >= tp.C) kc -= tp.C;
+                            const int k = kc * 256 + (u & 127) * 2;
+                            kk[j] = (u < nunits && k < K) ? k : -1;
+                            gg[j] = (rms && kk[j] >= 0) ? *reinterpret_cast<const float2*>(ph.g + k) : make_float2(1.0f, 1.0f);
+                            w[j][0] = w[j][1] = 0;
                         }
-                        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(o0), fabsf(o1)), fmaxf(fabsf(o2), fabsf(o3))));
-                        *reinterpret_cast<float4*>(xs + it * 8 + half * 4) = make_float4(o0, o1, o2, o3);
-                    }
-                } else {
-                    // sum of squares of the whole input: per-tile sums published by the producing epilogue, added in tile
-                    // order (every CTA gets the same bits); layer 0 reads the embedding row itself
-                    if (rms) {
-                        if (ph.in_stat) {
-                            if (warp == 0) for (int t = lane; t < ph.n_in_stat; t += 32) ss += df_wait1(ph.in_stat + t, in_ep, S, P);
-                        } else {
-                            #pragma unroll 1
-                            for (int k = tid * 4; k < K; k += NCT * 4) {
-                                const float4 a = __ldcg(reinterpret_cast<const float4*>(xrow + k));
-                                ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
-                            }
-                        }
-                    }
-                    // XI items of eight elements per thread and round: all their pairs are in flight together
-                    constexpr int XI = 2;
-                    #pragma unroll 1
-                    for (int it0 = tid; it0 < nitems; it0 += XI * NCT) {
-                        int ks[XI];
-                        u64 w[XI][8];
-#pragma unroll
-                        for (int j = 0; j < XI; j++) {
-                            const int it = it0 + j * NCT;
-                            int kc = tp.k0 + (it >> 5); if (kc >= tp.C) kc -= tp.C;
-                            ks[j] = it < nitems ? kc * 256 + (it & 31) * 8 : -1;
-                            if (ks[j] >= K) ks[j] = -1;
-#pragma unroll
-                            for (int e = 0; e < 8; e++) w[j][e] = 0;
-                        }
+                        const bool stat_round = rms && ph.in_stat != nullptr && warp == 0 && u0 == tid;
+                        const bool st_a = stat_round && lane < ph.n_in_stat, st_b = stat_round && lane + 32 < ph.n_in_stat;
+                        u64 sa = 0, sb = 0;
                         if (ph.in_ll) {
                             const unsigned lim = S.abort_flag ? 1u : S.wait_limit;
                             bool ok = false;
                             #pragma unroll 1
                             for (unsigned t = 0; t < lim && !ok; t++) {
 #pragma unroll
-                                for (int j = 0; j < XI; j++) if (ks[j] >= 0) {
-                                    const u64* pp = ph.in_ll + ks[j];
-                                    ll_ld2(pp, w[j][0], w[j][1]); ll_ld2(pp + 2, w[j][2], w[j][3]);
-                                    if (ks[j] + 4 < K) { ll_ld2(pp + 4, w[j][4], w[j][5]); ll_ld2(pp + 6, w[j][6], w[j][7]); }
-                                }
-                                ok = true;
+                                for (int j = 0; j < UI; j++) if (kk[j] >= 0) ll_ld2(ph.in_ll + kk[j], w[j][0], w[j][1]);
+                                if (st_a) sa = ll_ld(ph.in_stat + lane);
+                                if (st_b) sb = ll_ld(ph.in_stat + lane + 32);
+                                ok = (!st_a || ll_ok(sa, in_ep)) && (!st_b || ll_ok(sb, in_ep));
 #pragma unroll
-                                for (int j = 0; j < XI; j++) if (ks[j] >= 0) {
-#pragma unroll
-                                    for (int e = 0; e < 8; e++) if (e < 4 || ks[j] + 4 < K) ok = ok && ll_ok(w[j][e], in_ep);
-                                }
+                                for (int j = 0; j < UI; j++) if (kk[j] >= 0) ok = ok && ll_ok(w[j][0], in_ep) && ll_ok(w[j][1], in_ep);
                                 if (!ok && (t & 63u) == 63u && df_gave_up(S, P)) break;
                             }
                             if (!ok) df_fail(S, P);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < XI; j++) if (ks[j] >= 0) {
-                                const float4 a = __ldcg(reinterpret_cast<const float4*>(xrow + ks[j]));
-                                w[j][0] = __float_as_uint(a.x); w[j][1] = __float_as_uint(a.y); w[j][2] = __float_as_uint(a.z); w[j][3] = __float_as_uint(a.w);
-                                if (ks[j] + 4 < K) {
-                                    const float4 b = __ldcg(reinterpret_cast<const float4*>(xrow + ks[j] + 4));
-                                    w[j][4] = __float_as_uint(b.x); w[j][5] = __float_as_uint(b.y); w[j][6] = __float_as_uint(b.z); w[j][7] = __float_as_uint(b.w);
-                                }
+                            for (int j = 0; j < UI; j++) if (kk[j] >= 0) {
+                                const float2 a = __ldcg(reinterpret_cast<const float2*>(xrow + kk[j]));
+                                w[j][0] = __float_as_uint(a.x); w[j][1] = __float_as_uint(a.y);
                             }
                         }
+                        if (st_a) ss += ll_val(sa);
+                        if (st_b) ss += ll_val(sb);
 #pragma unroll
-                        for (int j = 0; j < XI; j++) {
-                            const int it = it0 + j * NCT;
-                            if (it >= nitems) continue;
-                            float v[8];
-#pragma unroll
-                            for (int e = 0; e < 8; e++) v[e] = (ks[j] >= 0 && (e < 4 || ks[j] + 4 < K)) ? ll_val(w[j][e]) : 0.0f;
-                            if (rms && ks[j] >= 0) {
-                                const float4 ga = *reinterpret_cast<const float4*>(ph.g + ks[j]);
-                                v[0] *= ga.x; v[1] *= ga.y; v[2] *= ga.z; v[3] *= ga.w;
-                                if (ks[j] + 4 < K) { const float4 gb = *reinterpret_cast<const float4*>(ph.g + ks[j] + 4); v[4] *= gb.x; v[5] *= gb.y; v[6] *= gb.z; v[7] *= gb.w; }
-                            }
-#pragma unroll
-                            for (int e = 0; e < 8; e++) mx = fmaxf(mx, fabsf(v[e]));
-                            *reinterpret_cast<float4*>(xs + it * 8) = make_float4(v[0], v[1], v[2], v[3]);
-                            *reinterpret_cast<float4*>(xs + it * 8 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                        for (int j = 0; j < UI; j++) {
+                            const int u = u0 + j * NCT;
+                            if (u >= nunits) continue;
+                            const float v0 = kk[j] >= 0 ? ll_val(w[j][0]) * gg[j].x : 0.0f, v1 = kk[j] >= 0 ? ll_val(w[j][1]) * gg[j].y : 0.0f;
+                            mx = fmaxf(mx, fmaxf(fabsf(v0), fabsf(v1)));
+                            *reinterpret_cast<float2*>(xs + u * 2) = make_float2(v0, v1);
                         }
                     }
                 }
@@ -967,7 +935,7 @@ __global__ void __launch_bounds__(PT, 1) k_decode_df(const __grid_constant__ HxP
             // ---------- phase boundary: the digit columns and the attention scratch are free again ----------
             asm volatile("cp.async.wait_all;" ::: "memory");
             if (consumer_sync_any(S.abort_flag)) goto aborted;
-            DF_STAMP(3); DF_MARK(6);
+            DF_STAMP(3);
         }
         if (P.advance_pos && tid == 0) {
             // no lm_head in this launch: the last CTA to finish advances the position

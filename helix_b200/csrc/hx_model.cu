@@ -104,7 +104,7 @@ struct hx_model {
     // dataflow engine (hx_decode_df.cu): vectors that cross CTAs as (value, epoch) pairs
     bool use_df = false;
     unsigned long long *xll[2] = {nullptr, nullptr}, *statll[2] = {nullptr, nullptr}, *qll = nullptr, *kvll = nullptr, *hll = nullptr;
-    unsigned long long *pacc_ll = nullptr, *pml_ll = nullptr, *part_ll[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    unsigned long long *pacc_ll = nullptr, *pml_ll = nullptr, *ctxll = nullptr, *part_ll[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     unsigned ep_count = 0, wait_limit = 1u << 24; int inject_stall = 0; unsigned* done_cnt = nullptr;
     std::vector<long long> plan_keys; std::vector<HxCtaPlan*> plan_tabs;
 };
@@ -568,12 +568,11 @@ int build_phases(hx_model* m, bool from_prompt, bool with_head, HxPhase** out, i
             at.NH = c.n_heads; at.NKV = c.n_kv_heads; at.DH = DH; at.cap = cap;
             at.nsplit = m->nsplit_persist; at.scale = 1.0f / sqrtf((float)DH); at.eps = c.norm_eps;
             at.in_ll = m->qll; at.kv_ll = m->kvll; at.in_dep = i_qkv;
-            at.pacc_ll = m->pacc_ll; at.pml_ll = m->pml_ll;
+            at.pacc_ll = m->pacc_ll; at.pml_ll = m->pml_ll; at.out_ll = m->ctxll;       // splits merged by one CTA per head
             const int i_att = (int)v.size(); v.push_back(at);
             HxPhase o = linear(ly.o, nullptr, nullptr, HX_EPI_RESID, ly.o.N);
-            o.norm = HX_NORM_ATTN; o.NH = c.n_heads; o.NKV = c.n_kv_heads; o.DH = DH; o.nsplit = m->nsplit_persist;
-            o.pacc_ll = m->pacc_ll; o.pml_ll = m->pml_ll; o.in_dep = i_att;
-            {   // the merged attention output of a CTA's K slice is staged in shared memory behind its digit cells
+            o.in_ll = m->ctxll; o.in_dep = i_att;
+            {   // the CTA's K slice of the input is staged in shared memory behind its digit cells
                 int maxp = 1, maxrun = 1;
                 std::vector<HxCtaPlan> tab((size_t)m->grid_persist);
                 hx_df_plan(o.ntiles, o.ksteps / 4, m->grid_persist, tab.data(), &maxp, &maxrun);
@@ -677,7 +676,8 @@ int init_persist(hx_model* m) {
         const hx_config& c = m->cfg;
         const char* sy = getenv("HX_SYNC");
         const bool fuse_qk = c.head_dim == 32 || c.head_dim == 64 || c.head_dim == 128;
-        m->use_df = m->use_tc && fuse_qk && (size_t)c.n_heads * m->nsplit_persist <= 2304 && !(sy && strcmp(sy, "barrier") == 0);
+        // (the prologue polls at most 64 per-tile sums of squares: d_model up to 8192)
+        m->use_df = m->use_tc && fuse_qk && (size_t)c.n_heads * m->nsplit_persist <= 2304 && c.d_model <= 8192 && !(sy && strcmp(sy, "barrier") == 0);
     }
     if (m->use_df) {
         const hx_config& c = m->cfg;
@@ -694,6 +694,7 @@ int init_persist(hx_model* m) {
         const size_t hs = (size_t)c.n_heads * m->nsplit_persist;
         if ((rc = ll(&m->pacc_ll, hs * DH))) return rc;
         if ((rc = ll(&m->pml_ll, hs * 2))) return rc;
+        if ((rc = ll(&m->ctxll, (size_t)QD + 128))) return rc;
         auto parts = [&](const Fused& f) -> size_t {
             int maxp = 1, maxrun = 1;
             std::vector<HxCtaPlan> tab((size_t)m->grid_persist);
