@@ -201,7 +201,10 @@ __device__ __forceinline__ void df_wait8(const u64* p, unsigned ep, float (&v)[8
 
 // ---- attention work split: the number of splits follows the context length (about 64 positions each) ----
 __device__ __noinline__ AttPlan att_plan_df(const HxPersist& P, int cta, int pos, int nring, int* ns_out, int* tile_rows, int* ntiles) {
-    int ns = (pos + 64) >> 6;
+#ifndef DF_SPLIT_ROWS_LOG2
+#define DF_SPLIT_ROWS_LOG2 4          // about 16 cached positions per attention split while CTAs are left (measured best: 8..16)
+#endif
+    int ns = (pos + (1 << DF_SPLIT_ROWS_LOG2)) >> DF_SPLIT_ROWS_LOG2;
     ns = ns < 1 ? 1 : (ns > P.att_nsplit ? P.att_nsplit : ns);
     struct { int NKV, DH; } ph = {P.att_nkv, P.att_dh};
     AttPlan a;
