@@ -43,7 +43,7 @@ BATCH_SEQS, BATCH_PROMPT, BATCH_NEW = 64, 2048, 128      # the batched-throughpu
 TP_PROMPT, TP_NEW = 4096, 64                             # 32B shape: context length, decoded tokens timed
 # DRAM bytes / algorithmic bytes of the decode kernel, from one ncu capture of a 4-layer launch (see the summary
 # kept with the ncu summaries of that kernel); re-measured when the kernel's memory traffic changes
-NCU_TRAFFIC_RATIO = 1.010
+NCU_TRAFFIC_RATIO = 1.012
 WORKLOAD = "qwen3-8b-shape nvfp4 greedy decode, batch 1, 512-token prompt + 256 new tokens"
 
 
@@ -556,6 +556,30 @@ def run_ours(args):
                 "engine": g2.engine(), "note": "per-op kernels in one CUDA graph per token (LayerNorm/bias/GELU fused into the NVFP4 GEMV)"}
         g2.close(); del gw
 
+    # prompt-lookup speculative decode: the same tokens as plain greedy are required.  (a) the benchmark's own model:
+    # with random weights and a 151 936-token vocabulary nothing ever repeats, so the drafter finds nothing and the
+    # path is the plain one; (b) a narrow 3-layer model (the width of the parity tests) whose greedy continuation falls
+    # into loops, like a real model quoting its prompt: drafts hit and several tokens come out of one verify forward.
+    spec = None
+    if rank == 0 and extras and not tp:
+        def spec_run(mdl, vocab, n_sp):
+            base = np.random.default_rng(11).integers(0, vocab, 24).astype(np.int32)
+            sp_prompt = np.concatenate([base, base, base[:16]]).astype(np.int32)
+            mdl.reset()
+            plain_ids, _, plain_ms = mdl.generate(sp_prompt, n_sp)
+            mdl.reset()
+            spec_ids, st, _, spec_ms = mdl.generate_spec(sp_prompt, n_sp)
+            return {"prompt": int(len(sp_prompt)), "new_tokens": n_sp, "tokens_identical_to_greedy": bool(list(plain_ids) == list(spec_ids)),
+                    "plain_tok_per_s": (n_sp - 1) / (plain_ms * 1e-3), "spec_tok_per_s": (n_sp - 1) / (spec_ms * 1e-3), "counters": st,
+                    "tokens_per_verify_forward": st["emitted"] / st["forwards"] if st["forwards"] else None}
+        spec = {"benchmark_model": spec_run(model, shape["vocab"], 96)}
+        small = dict(n_layers=3, d_model=512, n_heads=4, n_kv_heads=1, head_dim=128, d_ff=768, vocab=2011)
+        sm = hb.Model.synth(small, seed=3, kv_cap=512)
+        spec["small_model_d512_vocab_2011"] = spec_run(sm, small["vocab"], 256)
+        sm.close()
+        spec["note"] = ("a verify forward is one 16-token chunk of the batched prefill path plus the head on every row; it pays when "
+                        "about three drafted tokens are accepted per hit")
+
     cpu = parity = None
     if rank == 0 and args.gpus == 1 and not args.no_cpu_baseline:      # reported at N = 1 only
         cpu, parity = cpu_baseline_with_parity(model)
@@ -582,7 +606,7 @@ def run_ours(args):
                            "l2": "weights (4.26 GB per token) exceed the 126 MB L2, no flush needed",
                            "tokens_per_step": NEW_TOKENS, "weight_bytes_decode_layout": dbytes, "weight_bytes_committed_layout": cbytes},
                 "roofline": roofline, "cpu_baseline": cpu, "parity": parity, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-                "reference_gpu": ref_gpu, "batch64": batch64, "tp": tpl, "quantizer": quant, "gpt2": gpt2,
+                "reference_gpu": ref_gpu, "batch64": batch64, "tp": tpl, "speculative": spec, "quantizer": quant, "gpt2": gpt2,
                 "prefill": {"tokens": PROMPT_LEN, "ms": prefill_s * 1e3, "tok_per_s": PROMPT_LEN / prefill_s,
                             "path": "chunks of 16 tokens, one tcgen05 block-scaled GEMM per linear (exact digit columns), host ids in"},
                 "ms_per_token": ms_max / args.steps / NEW_TOKENS, "last_tokens": [int(t) for t in toks[-4:]]}
