@@ -536,6 +536,22 @@ def run_ours(args):
         for b in (dw, dW, dmic, dts):
             b.free()
 
+    # what the tensor pipe can issue for the MMA of this library (no vendor figure exists for it at small N): the
+    # denominator of the batched GEMM's tensor-side roofline
+    tprobe = None
+    if rank == 0 and extras:
+        c16, _ = hb.probe_mxf4_rate(16, True)
+        c256, tf256 = hb.probe_mxf4_rate(256, False)
+        c256s, tf256s = hb.probe_mxf4_rate(256, True)
+        lin_weights = (algorithmic_bytes_per_token(shape, 0)[0] / 0.5625) - shape["vocab"] * shape["d_model"]      # all linears but the head
+        useful = PROMPT_LEN / prefill_s * 2.0 * lin_weights / 1e12
+        tprobe = {"mma": "tcgen05.mma kind::mxf4nvf4 block16, M128 x N x K64, operands in shared memory, one issuing thread per SM",
+                  "clk_per_mma_n16_with_scale_copies": c16, "clk_per_mma_n256": c256, "clk_per_mma_n256_with_scale_copies": c256s,
+                  "attainable_tflops_n256": tf256, "attainable_tflops_n256_with_scale_copies": tf256s,
+                  "prefill_useful_tflops": useful, "prefill_issued_tflops": useful * 16.0,
+                  "prefill_issued_frac_of_attainable": useful * 16.0 / tf256s,
+                  "note": "the prefill issues sixteen exact digit columns per activation, so its issued work is 16 x the useful work"}
+
     # GPT-2-124M shape, all linears NVFP4, 32-token prompt + 128 greedy tokens, batch 1
     gpt2 = None
     if rank == 0 and extras and not tp:
@@ -606,7 +622,7 @@ def run_ours(args):
                            "l2": "weights (4.26 GB per token) exceed the 126 MB L2, no flush needed",
                            "tokens_per_step": NEW_TOKENS, "weight_bytes_decode_layout": dbytes, "weight_bytes_committed_layout": cbytes},
                 "roofline": roofline, "cpu_baseline": cpu, "parity": parity, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-                "reference_gpu": ref_gpu, "batch64": batch64, "tp": tpl, "speculative": spec, "quantizer": quant, "gpt2": gpt2,
+                "reference_gpu": ref_gpu, "batch64": batch64, "tp": tpl, "speculative": spec, "tensor_probe": tprobe, "quantizer": quant, "gpt2": gpt2,
                 "prefill": {"tokens": PROMPT_LEN, "ms": prefill_s * 1e3, "tok_per_s": PROMPT_LEN / prefill_s,
                             "path": "chunks of 16 tokens, one tcgen05 block-scaled GEMM per linear (exact digit columns), host ids in"},
                 "ms_per_token": ms_max / args.steps / NEW_TOKENS, "last_tokens": [int(t) for t in toks[-4:]]}

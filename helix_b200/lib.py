@@ -41,6 +41,11 @@ class HxPackReport(C.Structure):
                 ("f32_exact", C.c_int), ("verified", C.c_int), ("ms_pack", C.c_float), ("ms_verify", C.c_float)]
 
 
+class HxSampleConfig(C.Structure):
+    _fields_ = [("temperature", C.c_double), ("top_p", C.c_double), ("min_p", C.c_double), ("rep_penalty", C.c_double),
+                ("freq_penalty", C.c_double), ("pres_penalty", C.c_double), ("top_k", C.c_int), ("seed", C.c_uint64)]
+
+
 class HxSpecConfig(C.Structure):
     _fields_ = [("k_max", C.c_int), ("k_min", C.c_int), ("m", C.c_int), ("min_margin", C.c_float)]
 
@@ -130,6 +135,14 @@ _SIGS = {
     "hx_prefill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "hx_prefill_seq": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "hx_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "hx_sampler_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int]),
+    "hx_sampler_configure": (C.c_int, [C.c_void_p, C.POINTER(HxSampleConfig)]),
+    "hx_sampler_reset": (C.c_int, [C.c_void_p, C.POINTER(HxSampleConfig), C.c_void_p, C.c_int]),
+    "hx_sampler_next": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),
+    "hx_sampler_count": (C.c_int, [C.c_void_p, C.c_int32]),
+    "hx_sampler_free": (C.c_int, [C.c_void_p]),
+    "hx_serve": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "hx_probe_mxf4_rate": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "hx_pack_qwen3": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int, C.POINTER(HxPackReport)]),
     "hx_pld_draft": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "hx_generate_spec": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(HxSpecConfig), C.c_void_p, C.POINTER(HxSpecStats),
@@ -461,3 +474,46 @@ def pack_qwen3(model_dir, out_path, verify=True):
     check(lib().hx_pack_qwen3(os.fsencode(model_dir), os.fsencode(out_path), 1 if verify else 0, C.byref(rep)))
     return dict(tensors=rep.tensors, packed=rep.packed, bytes=rep.bytes, worst_rms=rep.worst_rms, worst_name=rep.worst_name.decode(),
                 f32_exact=bool(rep.f32_exact), verified=bool(rep.verified), ms_pack=rep.ms_pack, ms_verify=rep.ms_verify)
+
+
+def probe_mxf4_rate(ncols, with_scale_copies=False):
+    """(SM cycles per M128 x N x K64 block-scaled FP4 MMA, TFLOP/s over all SMs) measured on the current device."""
+    clk, tf = C.c_double(), C.c_double()
+    check(lib().hx_probe_mxf4_rate(int(ncols), 1 if with_scale_copies else 0, C.byref(clk), C.byref(tf)))
+    return clk.value, tf.value
+
+
+def worker_path():
+    """The serve worker process (hx_worker <weights> --serve [--emit-fd N] [--max-ctx M])."""
+    return os.path.join(_HERE, "hx_worker")
+
+
+class Sampler:
+    """The reference's seeded sampler on host logits (include/helix_b200.h, hx_sampler_*)."""
+
+    def __init__(self, vocab):
+        self.h = C.c_void_p()
+        check(lib().hx_sampler_create(C.byref(self.h), vocab))
+
+    def reset(self, prompt=(), temperature=0.0, top_p=1.0, min_p=0.0, rep_penalty=1.0, freq_penalty=0.0, pres_penalty=0.0, top_k=0, seed=0):
+        cfg = HxSampleConfig(temperature, top_p, min_p, rep_penalty, freq_penalty, pres_penalty, top_k, seed)
+        ids = np.ascontiguousarray(prompt, np.int32)
+        check(lib().hx_sampler_reset(self.h, C.byref(cfg), ids.ctypes.data, len(ids)))
+
+    def configure(self, temperature=0.0, top_p=1.0, min_p=0.0, rep_penalty=1.0, freq_penalty=0.0, pres_penalty=0.0, top_k=0, seed=0):
+        cfg = HxSampleConfig(temperature, top_p, min_p, rep_penalty, freq_penalty, pres_penalty, top_k, seed)
+        check(lib().hx_sampler_configure(self.h, C.byref(cfg)))
+
+    def next(self, logits):
+        lg = np.ascontiguousarray(logits, np.float32)
+        out = C.c_int32()
+        check(lib().hx_sampler_next(self.h, lg.ctypes.data, C.byref(out)))
+        return int(out.value)
+
+    def count(self, tok):
+        check(lib().hx_sampler_count(self.h, int(tok)))
+
+    def close(self):
+        if self.h:
+            lib().hx_sampler_free(self.h)
+            self.h = None

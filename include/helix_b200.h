@@ -140,6 +140,13 @@ int hx_gemm_nvfp4_tc(const uint8_t* a_t128, int rows, int K, const uint8_t* b_ce
 int hx_gemm_nvfp4_tc_bench(const uint8_t* a_t128, int rows, int K, const uint8_t* b_cells, int ncols, float* y,
                            int stage_ksteps, int reps, float* ms_per_launch);
 
+/* ---------------------------------------------------------------- measurement ----------------- */
+/* Issue rate of the MMA this library uses (tcgen05.mma kind::mxf4nvf4 block16, M = 128, K = 64, N = ncols, a multiple
+ * of 16 up to 256), operands resident in shared memory, one issuing thread per SM; with_scale_copies adds the four
+ * scale-factor copies of a weight cell.  clk_per_mma in SM cycles, tflops for all SMs at the current clock.  No
+ * counterpart in the reference; it is the tensor-side denominator of the batched GEMM's roofline. */
+int hx_probe_mxf4_rate(int ncols, int with_scale_copies, double* clk_per_mma, double* tflops);
+
 /* ---------------------------------------------------------------- importer -------------------- */
 /* Safetensors checkpoint directory (config.json + model.safetensors, or model.safetensors.index.json and its
  * shards; F32 or BF16 tensors) -> HXGW v3 NVFP4 file, quantized on the GPU.  Replaces pack_qwen3,
@@ -323,6 +330,37 @@ int hx_model_fill_kv(hx_model* m, int T, uint64_t seed);
  * exist so that a host can checkpoint / restore a sequence and so that tests can mirror a synthetic cache. */
 int hx_model_kv_read(hx_model* m, int seq, int layer, int kv_head, int pos0, int n, float* k, float* v);
 int hx_model_kv_write(hx_model* m, int seq, int layer, int kv_head, int pos0, int n, const float* k, const float* v);
+
+/* ---------------------------------------------------------------- serve worker ---------------- */
+/* The reference's seeded sampler (sample_next, helixc/runtime/gpt2_infer.c:1660-1711; PCG32 :1632-1644), host code
+ * on host logits, double precision, the reference's order of operations: repetition penalty, frequency / presence
+ * penalties, temperature, top-k, soft-max, sort by (-p, id), top-p, min-p, renormalise, one draw.  temperature <= 0
+ * is the arg-max (first maximum).  hx_sampler_reset = sample_reset (:1651-1657) with the limits of
+ * sample_cfg_from_json (:1729-1732); call hx_sampler_count for every token generated while sampling, as the serve
+ * loop does (:3374). */
+typedef struct hx_sampler hx_sampler;
+typedef struct {
+    double temperature, top_p, min_p, rep_penalty, freq_penalty, pres_penalty;   /* neutral: 0, 1, 0, 1, 0, 0 */
+    int top_k;                                                                    /* 0 = all */
+    uint64_t seed;
+} hx_sample_config;
+int hx_sampler_create(hx_sampler** s, int vocab);          /* generator unseeded, no counts: the reference's state at start-up */
+int hx_sampler_configure(hx_sampler* s, const hx_sample_config* cfg);   /* parameters only: counts and generator untouched */
+int hx_sampler_reset(hx_sampler* s, const hx_sample_config* cfg, const int32_t* prompt, int n_prompt);
+int hx_sampler_next(hx_sampler* s, const float* logits, int32_t* id);
+int hx_sampler_count(hx_sampler* s, int32_t id);
+int hx_sampler_free(hx_sampler* s);
+
+/* The request loop of the reference's --serve mode (run_serve, gpt2_infer.c:3284-3400) on model m: one JSON frame
+ * per line from in_fd ({"ids":[..],"n_gen":N, sampling fields} or {"cmd":"quit"}), newline-delimited JSON events to
+ * out_fd: hello, tokenize, forward_begin + token per generated token, done; error events for a bad frame, a context
+ * beyond max_ctx, or a "prompt" frame (no tokenizer is linked).  The event fields are the reference's (:845-1121);
+ * its per-op telemetry and logit lens describe its own launch sequence and are not emitted.  No EOS or stop-string
+ * handling (both need the tokenizer's pieces).  As in the reference, the sampler state is reset at the start of a
+ * request only if the previous frame sampled, and with that frame's seed (run_serve resets before it parses the
+ * frame's own sampling fields).  Returns when the stream ends or a quit frame arrives.  m must have a
+ * KV capacity of at least max_ctx rounded up to 64.  helix_b200/hx_worker wraps this call in a process. */
+int hx_serve(hx_model* m, int in_fd, int out_fd, int max_ctx);
 
 /* ---------------------------------------------------------------- kernel-entry image ---------- */
 /* helix_b200_kernels.fatbin exports, for sm_100a, the entry names and parameter lists of the kernels

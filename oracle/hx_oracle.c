@@ -737,6 +737,65 @@ ORC_API void orc_spec_counters(const int* prompt, int T, const int* greedy, int 
     free(ids);
 }
 
+/* Seeded sampler: sample_next, gpt2_infer.c:1660-1711, with its PCG32 (:1632-1644).  Double precision throughout:
+ * penalties on the raw logits of tokens seen before, temperature, candidates sorted by (-value, id), soft-max over
+ * the top-k, top-p keeping the crossing token, min-p relative to the best, renormalise, one draw u in [0,1), first
+ * index whose running sum exceeds u. */
+static uint64_t orc_pcg_state, orc_pcg_inc;
+ORC_API void orc_pcg_seed(uint64_t seed) {
+    orc_pcg_state = 0u; orc_pcg_inc = (54u << 1) | 1u;
+    orc_pcg_state = orc_pcg_state * 6364136223846793005ULL + orc_pcg_inc;
+    orc_pcg_state += seed;
+    orc_pcg_state = orc_pcg_state * 6364136223846793005ULL + orc_pcg_inc;
+}
+ORC_API uint32_t orc_pcg_next(void) {
+    uint64_t old = orc_pcg_state;
+    orc_pcg_state = old * 6364136223846793005ULL + orc_pcg_inc;
+    uint32_t xs = (uint32_t)(((old >> 18) ^ old) >> 27), rot = (uint32_t)(old >> 59);
+    return (xs >> rot) | (xs << ((32 - rot) & 31));
+}
+typedef struct { int id; double v; } OrcCand;
+static int orc_cand_cmp(const void* a, const void* b) {
+    const OrcCand* x = (const OrcCand*)a; const OrcCand* y = (const OrcCand*)b;
+    if (x->v > y->v) return -1;
+    if (x->v < y->v) return 1;
+    return (x->id < y->id) ? -1 : (x->id > y->id) ? 1 : 0;
+}
+ORC_API int orc_sample_next(const float* logits, int nv, const unsigned short* counts, double temp, double top_p, double min_p,
+                            double rep_pen, double freq_pen, double pres_pen, int top_k) {
+    OrcCand* cand = (OrcCand*)malloc((size_t)nv * sizeof(OrcCand));
+    double invt = 1.0 / temp;
+    for (int i = 0; i < nv; i++) {
+        double x = (double)logits[i];
+        int c = counts ? (int)counts[i] : 0;
+        if (c > 0 && rep_pen != 1.0) x = (x > 0.0) ? x / rep_pen : x * rep_pen;
+        if (c > 0) x -= freq_pen * (double)c + pres_pen;
+        cand[i].id = i; cand[i].v = x * invt;
+    }
+    qsort(cand, (size_t)nv, sizeof(OrcCand), orc_cand_cmp);
+    int n = (top_k > 0 && top_k < nv) ? top_k : nv;
+    double mx = cand[0].v, sum = 0.0;
+    for (int i = 0; i < n; i++) { cand[i].v = exp(cand[i].v - mx); sum += cand[i].v; }
+    for (int i = 0; i < n; i++) cand[i].v /= sum;
+    if (top_p < 1.0) {
+        double cum = 0.0; int keep = n;
+        for (int i = 0; i < n; i++) { cum += cand[i].v; if (cum >= top_p) { keep = i + 1; break; } }
+        n = keep;
+    }
+    if (min_p > 0.0) {
+        double floor_p = min_p * cand[0].v; int keep = n;
+        for (int i = 0; i < n; i++) if (cand[i].v < floor_p) { keep = i; break; }
+        n = keep > 0 ? keep : 1;
+    }
+    double rsum = 0.0;
+    for (int i = 0; i < n; i++) rsum += cand[i].v;
+    double u = (double)orc_pcg_next() / 4294967296.0, cum2 = 0.0;
+    int pick = cand[n - 1].id;
+    for (int i = 0; i < n; i++) { cum2 += cand[i].v / rsum; if (cum2 > u) { pick = cand[i].id; break; } }
+    free(cand);
+    return pick;
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

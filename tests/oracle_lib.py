@@ -79,6 +79,10 @@ def oracle():
     lib.orc_model_prefill.argtypes = [C.c_void_p, i32p, C.c_int, C.c_void_p]
     lib.orc_model_generate.argtypes = [C.c_void_p, i32p, C.c_int, C.c_int, i32p, C.c_void_p]
     lib.orc_pld_draft.argtypes = [i32p, C.c_int, C.c_int, C.c_int, C.c_int, i32p]
+    lib.orc_pcg_seed.argtypes = [C.c_uint64]; lib.orc_pcg_seed.restype = None
+    lib.orc_pcg_next.argtypes = []; lib.orc_pcg_next.restype = C.c_uint32
+    lib.orc_sample_next.argtypes = [f32p, C.c_int, C.c_void_p] + [C.c_double] * 6 + [C.c_int]
+    lib.orc_sample_next.restype = C.c_int
     lib.orc_pld_draft.restype = C.c_int
     lib.orc_spec_counters.argtypes = [i32p, C.c_int, i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.orc_spec_counters.restype = None
