@@ -182,12 +182,18 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
                 const int sub = warp & 3;                          // TMEM lanes 32*sub .. 32*sub+31
                 const int rl = sub * 32 + lane, row = mt * 128 + rl;
                 if (g.digit_mode) {
+                    const int ntok = NB / 16;
                     const float tsr = g.pair64 ? (((row & 127) < 64) ? g.ts[0] : g.ts[1])
                                                : (row < g.bound0 ? g.ts[0] : (row < g.bound1 ? g.ts[1] : g.ts[2]));
-                    const int ntok = NB / 16;
                     // final value of (token t, this row): tensor scale, then store / residual add / SwiGLU across the
                     // gate (rows 0..63 of the tile) and up (rows 64..127) halves
-                    auto finalize = [&](int t, float v) {
+                    // residual linears: the old values of this row for every token are fetched up front, all loads in
+                    // flight together (one dependent round trip per token was most of a short GEMM's time)
+                    float prev[HX_TC_MAX_TOK];
+#pragma unroll
+                    for (int t = 0; t < HX_TC_MAX_TOK; t++)
+                        prev[t] = (g.resid && !g.swiglu && t < ntok && row < g.rows) ? __ldcg(g.out + (size_t)t * g.ld_out + row) : 0.0f;
+                    auto finalize = [&](int t, float v, float old) {
                         v *= tsr;
                         if (g.swiglu) {
                             S.swi[rl] = v;
@@ -201,12 +207,18 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
                             }
                             asm volatile("bar.sync 1, 128;" ::: "memory");
                         } else if (row < g.rows) {
-                            float* o = g.out + (size_t)t * g.ld_out + row;
-                            *o = g.resid ? *o + v : v;
+                            g.out[(size_t)t * g.ld_out + row] = g.resid ? old + v : v;
                         }
                     };
+                    // the tokens' digit scales, fetched once (a load per token between the stores below would be a dependent
+                    // round trip each)
+                    float cs[HX_TC_MAX_TOK];
+#pragma unroll
+                    for (int t = 0; t < HX_TC_MAX_TOK; t++) cs[t] = t < ntok ? __ldg(g.col_scale + t) : 0.0f;
                     float* part = g.partial + ((size_t)(mt * P) * HX_TC_MAX_TOK) * 128;      // [piece][token][row in tile]
-                    for (int t = 0; t < ntok; t++) {
+#pragma unroll
+                    for (int t = 0; t < HX_TC_MAX_TOK; t++) {
+                        if (t >= ntok) break;
                         uint32_t r[16];
                         const uint32_t ta = tmem + ((uint32_t)(sub * 32) << 16) + (uint32_t)(t * 16);
                         asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -217,9 +229,9 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
                         float v = 0.0f;
 #pragma unroll
                         for (int j = 15; j >= 0; j--) v = fmaf(v, 0.25f, __uint_as_float(r[j]));
-                        v = v * g.col_scale[t];
+                        v = v * cs[t];
                         if (P > 1) part[((size_t)piece * HX_TC_MAX_TOK + t) * 128 + rl] = v;
-                        else finalize(t, v);
+                        else finalize(t, v, prev[t]);
                     }
                     if (P > 1) {
                         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -230,11 +242,17 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
                         }
                         asm volatile("bar.sync 1, 128;" ::: "memory");
                         if (S.ticket == (unsigned)(P - 1)) {
-                            for (int t = 0; t < ntok; t++) {
-                                float v = 0.0f;
-                                for (int q = 0; q < P; q++) v += __ldcg(part + ((size_t)q * HX_TC_MAX_TOK + t) * 128 + rl);
-                                finalize(t, v);
+                            // the pieces of all tokens: sixteen loads in flight per piece, added in piece order per token
+                            float sum[HX_TC_MAX_TOK];
+#pragma unroll
+                            for (int t = 0; t < HX_TC_MAX_TOK; t++) sum[t] = 0.0f;
+                            for (int q = 0; q < P; q++) {
+#pragma unroll
+                                for (int t = 0; t < HX_TC_MAX_TOK; t++)
+                                    if (t < ntok) sum[t] += __ldcg(part + ((size_t)q * HX_TC_MAX_TOK + t) * 128 + rl);
                             }
+#pragma unroll
+                            for (int t = 0; t < HX_TC_MAX_TOK; t++) if (t < ntok) finalize(t, sum[t], prev[t]);
                             if (tid == 64) g.tickets[mt] = 0u;
                         }
                     }
