@@ -159,11 +159,72 @@ const char* find_key(const char* s, const char* key) {
     return p;
 }
 
+// JSON string escaping of a byte string (jesc, :822-843): quotes, backslashes, \n \r \t, other control bytes as
+// \u00XX, everything else verbatim
+std::string jesc(const std::string& in) {
+    static const char* H = "0123456789abcdef";
+    std::string out;
+    for (unsigned char c : in) {
+        switch (c) {
+            case '"': out += "\\\""; break;
+            case '\\': out += "\\\\"; break;
+            case '\n': out += "\\n"; break;
+            case '\r': out += "\\r"; break;
+            case '\t': out += "\\t"; break;
+            default:
+                if (c < 0x20) { out += "\\u00"; out.push_back(H[(c >> 4) & 0xF]); out.push_back(H[c & 0xF]); }
+                else out.push_back((char)c);
+        }
+    }
+    return out;
+}
+
+// the JSON string that starts at p (after its opening quote): escapes \n \t \r \" \\ \/ and \uXXXX (as UTF-8)
+// undone (parse_req_json, :3238-3266)
+std::string json_unescape(const char* p) {
+    std::string out;
+    while (*p && *p != '"') {
+        if (*p == '\\' && p[1]) {
+            p++;
+            switch (*p) {
+                case 'n': out.push_back('\n'); break; case 't': out.push_back('\t'); break; case 'r': out.push_back('\r'); break;
+                case '"': out.push_back('"'); break; case '\\': out.push_back('\\'); break; case '/': out.push_back('/'); break;
+                case 'u': {
+                    unsigned v = 0;
+                    for (int i = 0; i < 4 && p[1]; i++) {
+                        p++; const char h = *p; v <<= 4;
+                        if (h >= '0' && h <= '9') v |= (unsigned)(h - '0'); else if (h >= 'a' && h <= 'f') v |= (unsigned)(h - 'a' + 10);
+                        else if (h >= 'A' && h <= 'F') v |= (unsigned)(h - 'A' + 10);
+                    }
+                    if (v < 0x80) out.push_back((char)v);
+                    else if (v < 0x800) { out.push_back((char)(0xC0 | (v >> 6))); out.push_back((char)(0x80 | (v & 0x3F))); }
+                    else { out.push_back((char)(0xE0 | (v >> 12))); out.push_back((char)(0x80 | ((v >> 6) & 0x3F))); out.push_back((char)(0x80 | (v & 0x3F))); }
+                    break;
+                }
+                default: out.push_back(*p); break;
+            }
+            p++;
+        } else out.push_back(*p++);
+    }
+    return out;
+}
+
+std::string decode_ids(const hx_tokenizer* tok, const int32_t* ids, int n) {
+    if (!tok || n <= 0) return std::string();
+    size_t len = 0;
+    hx_tokenizer_decode(tok, ids, n, nullptr, 0, &len);           // sizes the text (the call reports the short buffer)
+    std::string out(len, '\0');
+    if (len) hx_tokenizer_decode(tok, ids, n, &out[0], len, &len);
+    return out;
+}
+
 double now_s() { struct timespec ts; clock_gettime(CLOCK_MONOTONIC, &ts); return (double)ts.tv_sec + (double)ts.tv_nsec * 1e-9; }
 
 }  // namespace
 
-HX_API int hx_serve(hx_model* m, int in_fd, int out_fd, int max_ctx) {
+HX_API int hx_serve(hx_model* m, int in_fd, int out_fd, int max_ctx) { return hx_serve_text(m, nullptr, 0, -1, in_fd, out_fd, max_ctx); }
+
+HX_API int hx_serve_text(hx_model* m, const hx_tokenizer* tok, int with_specials, int eos_id, int in_fd, int out_fd, int max_ctx) {
     HX_CHECK_ARG(m && in_fd >= 0 && out_fd >= 0);
     hx_config cfg;
     int rc = hx_model_config(m, &cfg); if (rc) return rc;
@@ -195,7 +256,16 @@ HX_API int hx_serve(hx_model* m, int in_fd, int out_fd, int max_ctx) {
             }
         }
         if (!has_prompt && ids.empty()) { em.error("load", "bad request json", false); continue; }
-        if (has_prompt) { em.error("tokenize", "no in-process tokenizer and no pre-tokenized ids", false); continue; }
+        if (has_prompt && !tok) { em.error("tokenize", "no in-process tokenizer and no pre-tokenized ids", false); continue; }
+        if (has_prompt) {
+            const std::string text = json_unescape(find_key(line, "prompt") + 1);
+            ids.resize(text.size() + 8);
+            int nid = 0;
+            if (hx_tokenizer_encode(tok, text.data(), text.size(), with_specials, ids.data(), (int)ids.size(), &nid) != HX_OK || nid <= 0) {
+                em.error("tokenize", "empty/failed tokenization", false); continue;
+            }
+            ids.resize((size_t)nid);
+        }
         bool bad_id = false;
         for (int32_t t : ids) if (t < 0 || t >= cfg.vocab) bad_id = true;
         if (bad_id) { em.error("tokenize", "token id outside the vocabulary", false); continue; }
@@ -213,7 +283,9 @@ HX_API int hx_serve(hx_model* m, int in_fd, int out_fd, int max_ctx) {
         {
             std::string s = "{\"_ev\":\"tokenize\",\"seq\":" + std::to_string(em.seq++) + ",\"ids\":[";
             for (int i = 0; i < T0; i++) { if (i) s += ","; s += std::to_string(ids[i]); }
-            s += "],\"strings\":[],\"n_prompt\":" + std::to_string(T0) + ",\"s_pad\":" + std::to_string(((T0 + 63) / 64) * 64) + "}\n";
+            s += "],\"strings\":[";
+            if (tok) for (int i = 0; i < T0; i++) { if (i) s += ","; s += "\"" + jesc(decode_ids(tok, &ids[i], 1)) + "\""; }
+            s += "],\"n_prompt\":" + std::to_string(T0) + ",\"s_pad\":" + std::to_string(((T0 + 63) / 64) * 64) + "}\n";
             em.raw(s);
         }
         hx_sample_config sc = {0.0, 1.0, 0.0, 1.0, 0.0, 0.0, 0, 0};
@@ -235,6 +307,28 @@ HX_API int hx_serve(hx_model* m, int in_fd, int out_fd, int max_ctx) {
         prev = sc;
         if (prev.temperature < 0.0) prev.temperature = 0.0;
 
+        // stop sequences: up to four of up to 31 bytes, matched against the tail of the decoded text (stops_parse /
+        // stops_hit, :1043-1094); they need the tokenizer's pieces
+        std::vector<std::string> stops;
+        if (tok && (p = find_key(line, "stop")) && *p == '[') {
+            p++;
+            while (stops.size() < 4) {
+                while (*p == ' ' || *p == ',') p++;
+                if (*p != '"') break;
+                p++;
+                std::string st;
+                while (*p && *p != '"' && st.size() < 31) {
+                    if (*p == '\\' && p[1]) { p++; st.push_back(*p == 'n' ? '\n' : (*p == 't' ? '\t' : *p)); p++; }
+                    else st.push_back(*p++);
+                }
+                while (*p && *p != '"') p++;
+                if (*p == '"') p++;
+                if (!st.empty()) stops.push_back(st);
+                while (*p == ' ') p++;
+                if (*p != ',') break;
+            }
+        }
+        std::string tail;
         hx_model_reset(m);                                           // KV is per request: a fresh prefill fills it
         std::vector<int32_t> gen;
         int nonfinite = 0, T = T0;
@@ -251,18 +345,33 @@ HX_API int hx_serve(hx_model* m, int in_fd, int out_fd, int max_ctx) {
             for (int i = 0; i < cfg.vocab; i++) if (!isfinite(logits[i])) { nonfinite = 1; break; }
             int32_t nxt = 0;
             hx_sampler_next(smp, logits.data(), &nxt);
-            snprintf(b, sizeof b, "{\"_ev\":\"token\",\"seq\":%ld,\"step\":%d,\"id\":%d,\"string\":\"\",\"logit\":%.5f,\"context_len\":%d}\n",
-                     em.seq++, step, nxt, (double)logits[nxt], T + 1);
-            em.raw(b);
+            const std::string piece = decode_ids(tok, &nxt, 1);
+            {
+                std::string esc = jesc(piece);
+                if (esc.size() > 255) esc.resize(255);               // the reference escapes a piece into 256 bytes
+                std::string ev = "{\"_ev\":\"token\",\"seq\":" + std::to_string(em.seq++) + ",\"step\":" + std::to_string(step) + ",\"id\":" +
+                                 std::to_string(nxt) + ",\"string\":\"" + esc + "\"";
+                snprintf(b, sizeof b, ",\"logit\":%.5f,\"context_len\":%d}\n", (double)logits[nxt], T + 1);
+                em.raw(ev + b);
+            }
             gen.push_back(nxt); ids.push_back(nxt); T++;
             if (sc.temperature > 0.0) hx_sampler_count(smp, nxt);
+            bool stop_now = false;
+            if (!stops.empty()) {
+                tail += piece;
+                if (tail.size() > 255) tail.erase(0, tail.size() - 255);
+                for (auto& st : stops) if (tail.size() >= st.size() && tail.compare(tail.size() - st.size(), st.size(), st) == 0) stop_now = true;
+            }
+            if (stop_now || (eos_id >= 0 && nxt == eos_id)) break;
         }
         if (failed) continue;
         const double secs = now_s() - t0;
         std::string s = "{\"_ev\":\"done\",\"seq\":" + std::to_string(em.seq++) + ",\"n_prompt\":" + std::to_string(T0) + ",\"n_gen\":" +
                         std::to_string((int)gen.size()) + ",\"n_total\":" + std::to_string(T);
-        snprintf(b, sizeof b, ",\"seconds\":%.3f,\"tok_per_s\":%.3f,\"text\":\"\",\"gen_ids\":[", secs, secs > 0 ? (double)gen.size() / secs : 0.0);
+        snprintf(b, sizeof b, ",\"seconds\":%.3f,\"tok_per_s\":%.3f,\"text\":\"", secs, secs > 0 ? (double)gen.size() / secs : 0.0);
         s += b;
+        s += jesc(decode_ids(tok, gen.data(), (int)gen.size()));
+        s += "\",\"gen_ids\":[";
         for (size_t i = 0; i < gen.size(); i++) { if (i) s += ","; s += std::to_string(gen[i]); }
         s += "],\"nonfinite\":" + std::to_string(nonfinite) + "}\n";
         em.raw(s);

@@ -135,6 +135,12 @@ _SIGS = {
     "hx_prefill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "hx_prefill_seq": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "hx_generate_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "hx_tokenizer_load": (C.c_int, [C.POINTER(C.c_void_p), C.c_char_p, C.c_char_p]),
+    "hx_tokenizer_free": (C.c_int, [C.c_void_p]),
+    "hx_tokenizer_vocab_size": (C.c_int, [C.c_void_p]),
+    "hx_tokenizer_encode": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t, C.c_int, C.c_void_p, C.c_int, C.POINTER(C.c_int)]),
+    "hx_tokenizer_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "hx_serve_text": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "hx_sampler_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int]),
     "hx_sampler_configure": (C.c_int, [C.c_void_p, C.POINTER(HxSampleConfig)]),
     "hx_sampler_reset": (C.c_int, [C.c_void_p, C.POINTER(HxSampleConfig), C.c_void_p, C.c_int]),
@@ -516,4 +522,36 @@ class Sampler:
     def close(self):
         if self.h:
             lib().hx_sampler_free(self.h)
+            self.h = None
+
+
+class Tokenizer:
+    """GPT-2 byte-level BPE over a vocab.json and a merges.txt (include/helix_b200.h, hx_tokenizer_*)."""
+
+    def __init__(self, vocab_json, merges_txt):
+        self.h = C.c_void_p()
+        check(lib().hx_tokenizer_load(C.byref(self.h), os.fsencode(vocab_json), os.fsencode(merges_txt)))
+
+    def vocab_size(self):
+        return lib().hx_tokenizer_vocab_size(self.h)
+
+    def encode(self, text, with_specials=False):
+        data = text if isinstance(text, (bytes, bytearray)) else text.encode("utf-8")
+        ids = np.zeros(len(data) + 8, np.int32)
+        n = C.c_int()
+        check(lib().hx_tokenizer_encode(self.h, bytes(data), len(data), 1 if with_specials else 0, ids.ctypes.data, len(ids), C.byref(n)))
+        return ids[:n.value].copy()
+
+    def decode(self, ids):
+        ids = np.ascontiguousarray(ids, np.int32)
+        n = C.c_size_t()
+        lib().hx_tokenizer_decode(self.h, ids.ctypes.data, len(ids), None, 0, C.byref(n))      # sizes the text
+        buf = C.create_string_buffer(max(1, n.value))
+        if n.value:
+            check(lib().hx_tokenizer_decode(self.h, ids.ctypes.data, len(ids), buf, n.value, C.byref(n)))
+        return buf.raw[:n.value]
+
+    def close(self):
+        if self.h:
+            lib().hx_tokenizer_free(self.h)
             self.h = None

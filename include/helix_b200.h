@@ -331,6 +331,19 @@ int hx_model_fill_kv(hx_model* m, int T, uint64_t seed);
 int hx_model_kv_read(hx_model* m, int seq, int layer, int kv_head, int pos0, int n, float* k, float* v);
 int hx_model_kv_write(hx_model* m, int seq, int layer, int kv_head, int pos0, int n, const float* k, const float* v);
 
+/* ---------------------------------------------------------------- tokenizer ------------------- */
+/* GPT-2 byte-level BPE from a vocab.json and a merges.txt (helixc/runtime/gpt2_tok.c: load_vocab :251-297,
+ * load_merges :355-386, encode_bytes :532-640, encode_bytes_special :500-530, decode_range :660-671).  Host code.
+ * with_specials != 0 splits vocabulary entries of the form <...> off the text first (tok_enable_specials, :485-499).
+ * encode: *n_ids is the token count of the text; HX_ERR_ARG when it exceeds max_ids.  decode: the bytes the ids stand
+ * for, no terminator; *len is their number; HX_ERR_ARG when it exceeds cap; unknown ids contribute nothing. */
+typedef struct hx_tokenizer hx_tokenizer;
+int hx_tokenizer_load(hx_tokenizer** t, const char* vocab_json, const char* merges_txt);
+int hx_tokenizer_free(hx_tokenizer* t);
+int hx_tokenizer_vocab_size(const hx_tokenizer* t);
+int hx_tokenizer_encode(const hx_tokenizer* t, const char* text, size_t n, int with_specials, int32_t* ids, int max_ids, int* n_ids);
+int hx_tokenizer_decode(const hx_tokenizer* t, const int32_t* ids, int n, char* out, size_t cap, size_t* len);
+
 /* ---------------------------------------------------------------- serve worker ---------------- */
 /* The reference's seeded sampler (sample_next, helixc/runtime/gpt2_infer.c:1660-1711; PCG32 :1632-1644), host code
  * on host logits, double precision, the reference's order of operations: repetition penalty, frequency / presence
@@ -354,13 +367,17 @@ int hx_sampler_free(hx_sampler* s);
 /* The request loop of the reference's --serve mode (run_serve, gpt2_infer.c:3284-3400) on model m: one JSON frame
  * per line from in_fd ({"ids":[..],"n_gen":N, sampling fields} or {"cmd":"quit"}), newline-delimited JSON events to
  * out_fd: hello, tokenize, forward_begin + token per generated token, done; error events for a bad frame, a context
- * beyond max_ctx, or a "prompt" frame (no tokenizer is linked).  The event fields are the reference's (:845-1121);
- * its per-op telemetry and logit lens describe its own launch sequence and are not emitted.  No EOS or stop-string
- * handling (both need the tokenizer's pieces).  As in the reference, the sampler state is reset at the start of a
+ * beyond max_ctx, or a "prompt" frame (this entry has no tokenizer; see hx_serve_text).  The event fields are the reference's (:845-1121);
+ * its per-op telemetry and logit lens describe its own launch sequence and are not emitted.  As in the reference, the sampler state is reset at the start of a
  * request only if the previous frame sampled, and with that frame's seed (run_serve resets before it parses the
  * frame's own sampling fields).  Returns when the stream ends or a quit frame arrives.  m must have a
  * KV capacity of at least max_ctx rounded up to 64.  helix_b200/hx_worker wraps this call in a process. */
 int hx_serve(hx_model* m, int in_fd, int out_fd, int max_ctx);
+/* The same loop with a tokenizer (the reference's --vocab / --merges): "prompt" frames are tokenized (with the control
+ * tokens split off when with_specials != 0, the reference's HX_SPECIALS), tokenize.strings, token.string and
+ * done.text carry the decoded pieces, "stop":[..] sequences (up to four of up to 31 bytes, matched on the decoded
+ * tail, :1043-1094) and eos_id >= 0 (the reference's HX_EOS) end a request early. */
+int hx_serve_text(hx_model* m, const hx_tokenizer* tok, int with_specials, int eos_id, int in_fd, int out_fd, int max_ctx);
 
 /* ---------------------------------------------------------------- kernel-entry image ---------- */
 /* helix_b200_kernels.fatbin exports, for sm_100a, the entry names and parameter lists of the kernels

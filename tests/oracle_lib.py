@@ -16,6 +16,8 @@ ORACLE_SO = os.path.join(ORACLE_DIR, "_build", "libhx_oracle.so")
 REF_SO = os.path.join(ORACLE_DIR, "_ref", "libhelix_ref.so")
 REF_PACK = os.path.join(ORACLE_DIR, "_ref", "gpt2_pack")
 REF_INFER = os.path.join(ORACLE_DIR, "_ref", "gpt2_infer")
+REF_TOK = os.path.join(ORACLE_DIR, "_ref", "gpt2_tok")
+REF_INFER_SERVE = os.path.join(ORACLE_DIR, "_ref", "gpt2_infer_serve")
 
 f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")

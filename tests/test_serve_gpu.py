@@ -126,3 +126,72 @@ def test_same_stream_as_the_reference_worker(ours, model_file, tmp_path):
             assert (r["where"], r["message"], r["fatal"]) == (o["where"], o["message"], o["fatal"])
     print(f"serve: {len(ref)} events equal; chosen-token logits differ by at most {worst:.3g}")
     assert worst < 2e-4
+
+
+# ---- with a tokenizer: "prompt" frames, decoded pieces in the events, stop strings, control tokens ------------------
+import tok_fixture as tf   # noqa: E402
+
+TEXT_FRAMES = [
+    {"prompt": "hello world, the quick brown fox", "n_gen": 6, "request_id": "t1", "detail": "token"},
+    {"prompt": "<|im_start|>user\nit's 42<|im_end|>\n", "n_gen": 5, "request_id": "t2", "detail": "token"},
+    {"prompt": "naïve café 日本語", "n_gen": 12, "request_id": "t3", "detail": "token", "stop": ["\n", "fox"]},
+    {"ids": [5, 6, 7], "n_gen": 3, "request_id": "t4", "detail": "token"},
+    {"cmd": "quit"},
+]
+
+
+@pytest.fixture(scope="module")
+def text_setup(tmp_path_factory):
+    d = str(tmp_path_factory.mktemp("serve_text"))
+    vpath, mpath, nv = tf.write_files(d)
+    cfg = dict(CFG, NV=((nv + 63) // 64) * 64)                      # the reference's GEMMs want widths in multiples of 64
+    path = d + "/m.weights"
+    ol.write_v3(path, cfg, ol.synth_tensors(cfg, seed=43))
+    return d, vpath, mpath, path, cfg
+
+
+def run_text(cmd, env, cwd):
+    stdin = "".join(json.dumps(f) + "\n" for f in TEXT_FRAMES)
+    # pieces of a byte-level vocabulary need not be valid UTF-8: the stream is read as bytes, one byte per character
+    p = subprocess.run(cmd, input=stdin.encode(), capture_output=True, timeout=600, env=env, cwd=cwd)
+    assert b"GPT2_SERVE_READY" in p.stderr, p.stderr[-3000:]
+    return events(p.stdout.decode("latin-1"))
+
+
+def test_text_frames(text_setup):
+    d, vpath, mpath, path, cfg = text_setup
+    env = dict(os.environ, HX_SPECIALS="1")
+    ours = run_text([hb.worker_path(), path, "--serve", "--max-ctx", str(MAX_CTX), "--vocab", vpath, "--merges", mpath], env, d)
+    tk = hb.Tokenizer(vpath, mpath)
+    toks = [e for e in ours if e["_ev"] == "tokenize"]
+    assert toks[0]["ids"] == list(tk.encode(TEXT_FRAMES[0]["prompt"]))
+    assert "".join(toks[0]["strings"]).encode("latin-1") == TEXT_FRAMES[0]["prompt"].encode()
+    assert toks[1]["ids"] == list(tk.encode(TEXT_FRAMES[1]["prompt"], with_specials=True)) and toks[1]["strings"][0] == "<|im_start|>"
+    done = [e for e in ours if e["_ev"] == "done"]
+    for dn in done:
+        assert dn["text"].encode("latin-1") == tk.decode(dn["gen_ids"])
+    # the stop strings end request t3 at the first piece that completes one of them, and never later than n_gen
+    gen3 = done[2]["gen_ids"]
+    text3 = tk.decode(gen3)
+    assert len(gen3) <= 12 and (len(gen3) == 12 or text3.endswith(b"\n") or text3.endswith(b"fox"))
+    tk.close()
+    if not (have_worker() and os.path.exists(ol.REF_INFER_SERVE)):
+        pytest.skip("the reference serve worker with its tokenizer is not built")
+    renv = {k: v for k, v in os.environ.items() if not k.startswith("HX_")}
+    renv.pop("LD_LIBRARY_PATH", None)
+    renv.update({k: os.path.join(KOVC, v + ".ptx") for k, v in SIDE.items()})
+    renv.update(HX_KV="1", HX_SPECIALS="1")
+    ref = run_text([ol.REF_INFER_SERVE, os.path.join(KOVC, "model14.ptx"), path, "--serve", "--max-ctx", str(MAX_CTX), "--vocab", vpath,
+                    "--merges", mpath], renv, d)
+    assert [e["_ev"] for e in ref] == [e["_ev"] for e in ours]
+    for r, o in zip(ref, ours):
+        ev = r["_ev"]
+        if ev == "tokenize":
+            assert (r["ids"], r["strings"], r["n_prompt"], r["s_pad"]) == (o["ids"], o["strings"], o["n_prompt"], o["s_pad"])
+        elif ev == "token":
+            assert (r["step"], r["id"], r["string"], r["context_len"]) == (o["step"], o["id"], o["string"], o["context_len"])
+            assert abs(r["logit"] - o["logit"]) < 2e-4
+        elif ev == "done":
+            for k in ("n_prompt", "n_gen", "n_total", "text", "gen_ids", "nonfinite"):
+                assert r[k] == o[k], k
+    print(f"serve with tokenizer: {len(ref)} events equal to the reference worker's")
