@@ -97,6 +97,7 @@ struct hx_model {
     // batched prefill (chunks of HX_PF_TB tokens through the tcgen05 GEMM); buffers are created on first use
     float *pf_x = nullptr, *pf_qkv = nullptr, *pf_ctx = nullptr, *pf_gu = nullptr, *pf_scale = nullptr; uint8_t* pf_cells = nullptr; int* pf_err = nullptr; float* pf_partial = nullptr; unsigned* pf_tickets = nullptr;
     int pf_gu_ld = 0; bool pf_batched = true; size_t pf_partial_n = 0;
+    float* pf_part = nullptr; size_t tp_pf_off = 0, tp_pf_area = 0; unsigned tp_pf_ep = 0;      // tensor-parallel chunk exchange
     int *d_bids = nullptr, *d_bpos = nullptr, *d_bseq = nullptr, *d_bnext = nullptr; float* pf_logits = nullptr; int b_cap = 0;   // batched decode
     int* sp_next = nullptr; float* sp_margin = nullptr;                                   // speculative decode: verify rows
     cudaGraphExec_t g_bstep = nullptr; int g_bstep_n = 0;
@@ -679,6 +680,7 @@ int init_persist(hx_model* m) {
         // (the prologue polls at most 64 per-tile sums of squares: d_model up to 8192)
         m->use_df = m->use_tc && fuse_qk && (size_t)c.n_heads * m->nsplit_persist <= 2304 && c.d_model <= 8192 && !(sy && strcmp(sy, "barrier") == 0);
     }
+    if (m->tp_world > 1 && !m->use_df) m->pf_batched = false;       // the chunk exchange of a shard belongs to the pair engine
     if (m->use_df) {
         const hx_config& c = m->cfg;
         const int DH = c.head_dim, QD = m->QD, KVD = m->KVD, ntile_dm = (c.d_model + 127) / 128;
@@ -715,6 +717,11 @@ int init_persist(hx_model* m) {
         if ((rc = dalloc(m, &m->x2, (size_t)m->cfg.d_model))) return rc;
         m->tp_buf_floats = (size_t)2 * m->tp_world * m->cfg.d_model + (size_t)4 * m->tp_world + 64;
         if (m->use_df) m->tp_buf_floats *= 2;            // the same layout in 8-byte (value, epoch) pairs
+        // behind it: the exchange areas of the batched prefill, two buffers (used in turn) of one slot per rank
+        m->tp_buf_floats = (m->tp_buf_floats + 3) & ~(size_t)3;
+        m->tp_pf_off = m->tp_buf_floats / 2;                                       // in pairs
+        m->tp_pf_area = (size_t)HX_PF_TB * m->cfg.d_model;                         // pairs per slot
+        m->tp_buf_floats += (size_t)2 * 2 * m->tp_world * m->tp_pf_area;
         if ((rc = dalloc(m, &m->tp_buf, m->tp_buf_floats))) return rc;
         HX_CUDA(cudaMemset(m->tp_buf, 0, m->tp_buf_floats * 4));
         m->tp_peer[m->tp_rank] = m->tp_buf;
@@ -888,7 +895,7 @@ HX_API int hx_model_synth(hx_model** out, const hx_config* cfg, uint64_t seed, i
       m->use_tc = m->persist && !(lm && strcmp(lm, "mma") == 0);
       m->want_t128 = m->use_tc;
       { const char* pf = getenv("HX_PREFILL"); m->pf_batched = !(pf && strcmp(pf, "token") == 0); }
-      if (m->tp_world > 1) { m->persist = true; m->use_tc = true; m->want_t128 = true; m->pf_batched = false; } }
+      if (m->tp_world > 1) { m->persist = true; m->use_tc = true; m->want_t128 = true; } }
     cudaError_t e = cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking);
     if (e != cudaSuccess) { delete m; return hx_fail(HX_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
     Source s; s.synth = true; s.seed = seed;
@@ -1029,7 +1036,7 @@ HX_API int hx_model_load(hx_model** out, const char* path, int kv_cap, int batch
       m->use_tc = m->persist && !(lm && strcmp(lm, "mma") == 0);
       m->want_t128 = m->use_tc;
       { const char* pf = getenv("HX_PREFILL"); m->pf_batched = !(pf && strcmp(pf, "token") == 0); }
-      if (m->tp_world > 1) { m->persist = true; m->use_tc = true; m->want_t128 = true; m->pf_batched = false; } }
+      if (m->tp_world > 1) { m->persist = true; m->use_tc = true; m->want_t128 = true; } }
         cudaError_t e = cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking);
         if (e != cudaSuccess) { rc = hx_fail(HX_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); break; }
         Source s; s.map = hb; s.maplen = len; s.desc = d;
@@ -1253,6 +1260,7 @@ static int pf_alloc(hx_model* m) {
     if ((rc = dalloc(m, &m->pf_gu, (size_t)HX_PF_TB * m->pf_gu_ld))) return rc;
     if ((rc = dalloc(m, &m->pf_scale, (size_t)HX_PF_TB))) return rc;
     if ((rc = dalloc(m, &m->pf_cells, cells))) return rc;
+    if (m->tp_world > 1 && (rc = dalloc(m, &m->pf_part, (size_t)HX_PF_TB * c.d_model))) return rc;
     if ((rc = dalloc(m, &m->pf_err, (size_t)4))) return rc;
     if ((rc = dalloc(m, &m->d_pf_pos, (size_t)4))) return rc;
     HX_CUDA(cudaMemsetAsync(m->pf_err, 0, 16, m->st));
@@ -1289,6 +1297,20 @@ static int pf_linear(hx_model* m, const Fused& f, const float* src, int ld_src, 
     return hx_gemm_tc_launch(q, m->st);
 }
 
+// Tensor-parallel shard: pf_part (this rank's partial rows of a row-split linear for the n tokens of the chunk) summed over
+// the ranks into pf_x.  Every rank issues the same sequence of exchanges, so the epoch and the buffer (two, in turn: a
+// rank cannot be two exchanges ahead of a peer it has to read from) agree without any negotiation.
+static int pf_tp_reduce(hx_model* m, int n) {
+    if (!m->tp_connected) return hx_fail(HX_ERR_STATE, "tensor parallel: call hx_model_tp_connect before the first step");
+    if (m->tp_pf_ep > 0xFFFFFF00u) return hx_fail(HX_ERR_STATE, "epoch counter of the prefill exchange exhausted: rebuild the model");
+    const unsigned ep = ++m->tp_pf_ep;
+    unsigned long long* areas[8] = {nullptr};
+    for (int w = 0; w < m->tp_world; w++)
+        areas[w] = reinterpret_cast<unsigned long long*>(m->tp_peer[w]) + m->tp_pf_off + (size_t)(ep & 1u) * m->tp_world * m->tp_pf_area;
+    hx_pf_tp_reduce(m->pf_part, m->pf_x, areas, m->tp_rank, m->tp_world, n * m->cfg.d_model, m->tp_pf_area, ep, m->wait_limit, m->pf_err, m->st);
+    return HX_OK;
+}
+
 // The launches of the layers for one chunk of n tokens (ids[t] / wh say which token, position and sequence each is).
 static int pf_enqueue_layers(hx_model* m, int n, const int* ids, HxPfWhere wh) {
     const hx_config& c = m->cfg;
@@ -1303,9 +1325,15 @@ static int pf_enqueue_layers(hx_model* m, int n, const int* ids, HxPfWhere wh) {
         if ((rc = pf_linear(m, ly.qkv, m->pf_x, DM, n, 0, ly.in_g, m->pf_qkv, ldq, ly.qkv.N, 0, 0))) return rc;
         hx_pf_qkpost(m->pf_qkv, ldq, n, wh, c.n_heads, c.n_kv_heads, DH, ly.qn_g, ly.kn_g, c.norm_eps, m->cosT, m->sinT, kc, vc, cap, m->st);
         if ((rc = hx_pf_attn(m->pf_qkv, ldq, n, wh, c.n_heads, c.n_kv_heads, DH, kc, vc, cap, att_scale, m->pf_ctx, QD, m->st))) return rc;
-        if ((rc = pf_linear(m, ly.o, m->pf_ctx, QD, n, 0, nullptr, m->pf_x, DM, ly.o.N, 1, 0))) return rc;
+        if (m->tp_world > 1) {
+            if ((rc = pf_linear(m, ly.o, m->pf_ctx, QD, n, 0, nullptr, m->pf_part, DM, ly.o.N, 0, 0))) return rc;
+            if ((rc = pf_tp_reduce(m, n))) return rc;
+        } else if ((rc = pf_linear(m, ly.o, m->pf_ctx, QD, n, 0, nullptr, m->pf_x, DM, ly.o.N, 1, 0))) return rc;
         if ((rc = pf_linear(m, ly.gu, m->pf_x, DM, n, 1, ly.post_g, m->pf_gu, m->pf_gu_ld, c.d_ff, 0, 1))) return rc;       // SwiGLU in the epilogue
-        if ((rc = pf_linear(m, ly.down, m->pf_gu, m->pf_gu_ld, n, 0, nullptr, m->pf_x, DM, ly.down.N, 1, 0))) return rc;
+        if (m->tp_world > 1) {
+            if ((rc = pf_linear(m, ly.down, m->pf_gu, m->pf_gu_ld, n, 0, nullptr, m->pf_part, DM, ly.down.N, 0, 0))) return rc;
+            if ((rc = pf_tp_reduce(m, n))) return rc;
+        } else if ((rc = pf_linear(m, ly.down, m->pf_gu, m->pf_gu_ld, n, 0, nullptr, m->pf_x, DM, ly.down.N, 1, 0))) return rc;
     }
     return HX_OK;
 }
@@ -1390,6 +1418,20 @@ static int run_prefill_batched(hx_model* m, int T, int seq) {
 static int run_prefill(hx_model* m, const int32_t* ids, int T, int seq = 0) {
     // positions 0..T-2 without the head, position T-1 with it
     HX_CUDA(cudaMemcpyAsync(m->d_prompt, ids, (size_t)T * 4, cudaMemcpyHostToDevice, m->st));
+    if (m->tp_world > 1 && m->use_tc && m->pf_batched && m->head.t128 && m->use_df) {
+        // a shard: positions [0, T-1) in chunks (the exchanges are epoch-numbered kernel arguments, so no graph replay),
+        // the last position through the decode kernel, which holds the arg-max over the ranks' vocabulary slices
+        if (seq != 0) return hx_fail(HX_ERR_STATE, "a tensor-parallel shard holds one sequence");
+        int rc = pf_alloc(m); if (rc) return rc;
+        const int Tc = T - 1;
+        const int ps[2] = {0, 0};
+        HX_CUDA(cudaMemcpyAsync(m->d_pf_pos, ps, 8, cudaMemcpyHostToDevice, m->st));
+        for (int t0 = 0; t0 < Tc; t0 += HX_PF_TB)
+            if ((rc = pf_enqueue_chunk(m, Tc - t0 < HX_PF_TB ? Tc - t0 : HX_PF_TB))) return rc;
+        if ((rc = set_pos_tok(m, T - 1, nullptr))) return rc;
+        HX_CUDA(cudaMemcpyAsync(m->d_tok, m->d_prompt + (T - 1), 4, cudaMemcpyDeviceToDevice, m->st));
+        return step_decode(m);
+    }
     if (m->use_tc && m->pf_batched && m->head.t128) return run_prefill_batched(m, T, seq);
     if (seq != 0) return hx_fail(HX_ERR_STATE, "prefill into KV slot %d needs the batched prefill path", seq);
     int rc = set_pos_tok(m, 0, nullptr); if (rc) return rc;

@@ -205,6 +205,35 @@ __global__ void __launch_bounds__(PF_AT) k_pf_attn(const float* __restrict__ qkv
     }
 }
 
+// Tensor-parallel chunk: the partial rows of a row-split linear (o_proj, down_proj) summed over the ranks and added to
+// the residual stream.  Every rank stores its [n][DM] partial as 8-byte (value, epoch) pairs into every peer's
+// exchange area (plain NVLink stores), then adds the ranks' values in rank order -- the same bits on every rank.  A
+// matching epoch proves the value beside it (an aligned 8-byte store is single-copy atomic).  Waits are bounded.
+struct HxPfPeers { unsigned long long* p[8]; };
+__global__ void __launch_bounds__(256) k_pf_tp_reduce(const float* __restrict__ part, float* __restrict__ x, HxPfPeers peers, int rank, int world,
+                                                      int count, size_t area_pairs, unsigned ep, unsigned wait_limit, int* err) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)count; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = part[i];
+        const unsigned long long w64 = ((unsigned long long)ep << 32) | (unsigned long long)__float_as_uint(v);
+        for (int w = 0; w < world; w++)
+            if (w != rank) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(peers.p[w] + (size_t)rank * area_pairs + i), "l"(w64) : "memory");
+        float sum = 0.0f;
+        for (int w = 0; w < world; w++) {
+            if (w == rank) { sum += v; continue; }
+            const unsigned long long* src = peers.p[rank] + (size_t)w * area_pairs + i;
+            unsigned long long got = 0; bool ok = false;
+            for (unsigned t = 0; t < wait_limit; t++) {
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(got) : "l"(src) : "memory");
+                if ((unsigned)(got >> 32) == ep) { ok = true; break; }
+                if ((t & 1023u) == 1023u && *reinterpret_cast<volatile int*>(err) != 0) break;
+            }
+            if (!ok) { *err = 1; }
+            sum += __uint_as_float((unsigned)got);
+        }
+        x[i] += sum;
+    }
+}
+
 __global__ void k_pf_advance(int* posp, int n) { if (threadIdx.x == 0) *posp += n; }
 // one CTA per token row: first maximum of logits[row][0..n) -> next[row]; the row's position advances by one
 __global__ void __launch_bounds__(1024) k_pf_argmax_rows(const float* __restrict__ logits, int n, int ld, int* __restrict__ next, int* __restrict__ pos_arr) {
@@ -305,6 +334,15 @@ int hx_pf_attn(const float* qkv, int ld, int n_tok, HxPfWhere wh, int NH, int NK
 #undef HX_PF_ATTN
     HX_COUNT_LAUNCH(1);
     return HX_OK;
+}
+
+void hx_pf_tp_reduce(const float* part, float* x, unsigned long long* const* peer_areas, int rank, int world, int count, size_t area_pairs,
+                     unsigned ep, unsigned wait_limit, int* err, cudaStream_t st) {
+    HxPfPeers pe = {};
+    for (int w = 0; w < world && w < 8; w++) pe.p[w] = peer_areas[w];
+    int g = (count + 255) / 256; if (g > 148 * 4) g = 148 * 4;
+    k_pf_tp_reduce<<<g, 256, 0, st>>>(part, x, pe, rank, world, count, area_pairs, ep, wait_limit, err);
+    HX_COUNT_LAUNCH(1);
 }
 
 void hx_pf_advance(int* posp, int n, cudaStream_t st) {

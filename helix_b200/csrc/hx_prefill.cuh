@@ -41,5 +41,9 @@ void hx_pf_advance(int* posp, int n, cudaStream_t st);
 // First maximum of logits[0..n): index to *tok and hist[pos + 1]; *pos_out = pos + 1.
 void hx_pf_argmax(const float* logits, int n, int* tok, int* hist, int* pos_out, int pos, cudaStream_t st);
 // per-row arg-max of logits [rows][ld] (n valid columns) -> next[row]; pos_arr[row] += 1 when given
+// Tensor parallel: x[i] += sum over the ranks of part[i] (i < count), the ranks' values exchanged as (value, epoch)
+// pairs through peer_areas[w] (rank r writes slot r of every peer; slots are area_pairs pairs apart).
+void hx_pf_tp_reduce(const float* part, float* x, unsigned long long* const* peer_areas, int rank, int world, int count, size_t area_pairs,
+                     unsigned ep, unsigned wait_limit, int* err, cudaStream_t st);
 void hx_pf_top2_rows(const float* logits, int n, int ld, int rows, int* next, float* margin, cudaStream_t st);
 void hx_pf_argmax_rows(const float* logits, int n, int ld, int rows, int* next, int* pos_arr, cudaStream_t st);

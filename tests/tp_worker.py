@@ -34,6 +34,21 @@ def main():
         import oracle_lib as ol
         om = ol.OracleModel(path, kv_cap=96)
     NVl = gm.cfg.vocab
+    # batched prefill inside the group: chunks of 16 positions with the partial rows of o_proj / down_proj exchanged per
+    # chunk, the last position through the decode kernel; 37 tokens = two full chunks, a ragged one and the last token
+    pids = np.random.default_rng(8).integers(0, NVl * world, 37).astype(np.int32)
+    nxp, lgp = gm.prefill(pids, want_logits=True)
+    parts = [torch.zeros(NVl, dtype=torch.float32) for _ in range(world)]
+    dist.all_gather(parts, torch.from_numpy(lgp.copy()))
+    pf_err = 0.0
+    if rank == 0:
+        full = torch.cat(parts).numpy()
+        lo = om.prefill(pids)
+        pf_err = float(np.max(np.abs(full - lo)))
+        assert pf_err < 2e-4, pf_err
+        assert nxp == int(np.argmax(lo)), (nxp, int(np.argmax(lo)))
+        om.reset() if hasattr(om, "reset") else None
+    gm.reset()
     ids = np.random.default_rng(5).integers(0, NVl * world, n_teacher)
     worst = 0.0
     for pos, t in enumerate(ids):
@@ -58,7 +73,7 @@ def main():
             want.append(tok)
         assert worst < 2e-4, worst
         assert list(out) == want, (list(out), want)
-        print("TP-OK world=%d max-abs-logit-diff=%.3g" % (world, worst), flush=True)
+        print("TP-OK world=%d max-abs-logit-diff=%.3g prefill-max-abs=%.3g" % (world, worst, pf_err), flush=True)
     dist.barrier()
     gm.close()
     dist.destroy_process_group()
