@@ -41,6 +41,7 @@ sys.path.insert(0, ROOT)
 PROMPT_LEN, NEW_TOKENS = 512, 256
 BATCH_SEQS, BATCH_PROMPT, BATCH_NEW = 64, 2048, 128      # the batched-throughput configuration
 TP_PROMPT, TP_NEW = 4096, 64                             # 32B shape: context length, decoded tokens timed
+TP_BATCH, TP_BATCH_STEPS = 16, 16                        # 32B shape: sequences decoded together inside the group, steps timed
 # DRAM bytes / algorithmic bytes of the decode kernel, from one ncu capture of a 4-layer launch (see the summary
 # kept with the ncu summaries of that kernel); re-measured when the kernel's memory traffic changes
 NCU_TRAFFIC_RATIO = 1.012
@@ -364,14 +365,14 @@ def tp_leg(hb, L, check, dist, rank, ngpus, peak):
     cap = TP_PROMPT + TP_NEW + 16
     if ngpus > 1:
         import torch
-        model = hb.Model.synth(shape, seed=1, kv_cap=cap, tp_rank=rank, tp_size=ngpus)
+        model = hb.Model.synth(shape, seed=1, kv_cap=cap, tp_rank=rank, tp_size=ngpus, batch=TP_BATCH)
         mine = torch.tensor(list(model.tp_handle()), dtype=torch.uint8)
         allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(ngpus)]
         dist.all_gather(allh, mine)
         model.tp_connect([bytes(h.tolist()) for h in allh])
         dist.barrier()
     else:
-        model = hb.Model.synth(shape, seed=1, kv_cap=cap)
+        model = hb.Model.synth(shape, seed=1, kv_cap=cap, batch=TP_BATCH)
     prompt = np.random.default_rng(17).integers(0, shape["vocab"], TP_PROMPT).astype(np.int32)
     model.prefill(prompt[:64])                        # warm-up of the chunk path
     model.reset()
@@ -390,12 +391,23 @@ def tp_leg(hb, L, check, dist, rank, ngpus, peak):
     per_gpu = (wbytes + kvb) / ngpus + emb
     ms_tok = ms / TP_NEW
     engine = model.engine()
+    # sixteen sequences through the group at the same context (their cache rows seeded synthetically: sixteen 4096-token
+    # prefills would take minutes), one token each per step: the batched GEMM path with the row-split linears' partial
+    # rows and the per-sequence arg-max exchanged between the ranks
+    model.fill_kv(TP_PROMPT, 13)
+    ids16 = np.random.default_rng(19).integers(0, shape["vocab"], TP_BATCH).astype(np.int32)
+    model.decode_batch_loop(ids16, TP_PROMPT, 2)
+    if dist is not None:
+        dist.barrier()
+    _, ms16 = model.decode_batch_loop(ids16, TP_PROMPT, TP_BATCH_STEPS)
+    ms16 = all_max(dist, ms16)
+    batch16 = {"sequences": TP_BATCH, "steps": TP_BATCH_STEPS, "context": TP_PROMPT, "tok_per_s": TP_BATCH * TP_BATCH_STEPS / (ms16 * 1e-3),
+               "ms_per_step": ms16 / TP_BATCH_STEPS, "kv": "synthetic rows", "path": "hx_decode_batch_loop inside the group"}
     model.close()
     return {"model": "qwen3-32b-shape", "tp": ngpus, "batch": 1, "context": TP_PROMPT, "new_tokens": TP_NEW,
             "prefill_s": pf_s, "prefill_tok_per_s": TP_PROMPT / pf_s, "tok_per_s": 1e3 / ms_tok,
             "ms_per_token": ms_tok, "per_gpu_bytes_per_token": per_gpu, "per_gpu_frac_of_hbm_peak": per_gpu / (ms_tok * 1e-3) / 1e9 / peak,
-            "engine": engine, "batch16": None,
-            "batch16_note": "not built: a tensor-parallel shard decodes one sequence",
+            "engine": engine, "batch16": batch16,
             "exchange": "partial rows of o_proj / down_proj stored as (value, epoch) pairs into every rank's buffer over NVLink "
                         "inside the decode kernel, summed in rank order; no NCCL kernel" if ngpus > 1 else "none (one GPU)"}
 

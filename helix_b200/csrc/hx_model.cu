@@ -852,7 +852,6 @@ int check_cfg(const hx_config& c, int kv_cap, int batch, int tp_rank, int tp_siz
     if (c.d_model % 4 || c.d_ff % 4) return hx_fail(HX_ERR_ARG, "d_model and d_ff must be multiples of 4");
     if (kv_cap <= 0) return hx_fail(HX_ERR_ARG, "kv_cap must be positive");
     if (batch < 1 || batch > 1024) return hx_fail(HX_ERR_ARG, "batch %d: 1 .. 1024 sequences per model instance", batch);
-    if (batch > 1 && tp_size > 1) return hx_fail(HX_ERR_ARG, "batched decode and tensor parallel are not combined in this build");
     if (tp_size < 1 || tp_size > 8 || tp_rank < 0 || tp_rank >= tp_size) return hx_fail(HX_ERR_ARG, "tensor parallel rank %d of %d", tp_rank, tp_size);
     if (tp_size > 1) {
         if (c.n_heads % tp_size || c.n_kv_heads % tp_size || c.d_ff % tp_size || c.vocab % tp_size)
@@ -1374,7 +1373,16 @@ static int bd_enqueue_step(hx_model* m, int n_seq) {
         HxPfWhere wh = {nullptr, m->d_bpos + c0, m->d_bseq + c0, seq_stride, nullptr};
         if ((rc = pf_enqueue_layers(m, n, m->d_bids + c0, wh))) return rc;
         if ((rc = pf_linear(m, m->head, m->pf_x, c.d_model, n, 0, m->final_g, m->pf_logits, c.vocab, m->head.N, 0, 0))) return rc;
-        hx_pf_argmax_rows(m->pf_logits, c.vocab, c.vocab, n, m->d_bnext + c0, m->d_bpos + c0, m->st);
+        if (m->tp_world > 1) {
+            // every rank holds a slice of the vocabulary: local first maximum, then the best over the ranks
+            if (!m->tp_connected) return hx_fail(HX_ERR_STATE, "tensor parallel: call hx_model_tp_connect before the first step");
+            const unsigned ep = ++m->tp_pf_ep;
+            unsigned long long* areas[8] = {nullptr};
+            for (int w = 0; w < m->tp_world; w++)
+                areas[w] = reinterpret_cast<unsigned long long*>(m->tp_peer[w]) + m->tp_pf_off + (size_t)(ep & 1u) * m->tp_world * m->tp_pf_area;
+            hx_pf_tp_argmax_rows(m->pf_logits, c.vocab, c.vocab, n, m->tp_rank * c.vocab, areas, m->tp_rank, m->tp_world, m->tp_pf_area, ep,
+                                 m->wait_limit, m->pf_err, m->d_bnext + c0, m->d_bpos + c0, m->st);
+        } else hx_pf_argmax_rows(m->pf_logits, c.vocab, c.vocab, n, m->d_bnext + c0, m->d_bpos + c0, m->st);
     }
     HX_CUDA(cudaMemcpyAsync(m->d_bids, m->d_bnext, (size_t)n_seq * 4, cudaMemcpyDeviceToDevice, m->st));
     return HX_OK;
@@ -1421,13 +1429,29 @@ static int run_prefill(hx_model* m, const int32_t* ids, int T, int seq = 0) {
     if (m->tp_world > 1 && m->use_tc && m->pf_batched && m->head.t128 && m->use_df) {
         // a shard: positions [0, T-1) in chunks (the exchanges are epoch-numbered kernel arguments, so no graph replay),
         // the last position through the decode kernel, which holds the arg-max over the ranks' vocabulary slices
-        if (seq != 0) return hx_fail(HX_ERR_STATE, "a tensor-parallel shard holds one sequence");
         int rc = pf_alloc(m); if (rc) return rc;
-        const int Tc = T - 1;
-        const int ps[2] = {0, 0};
+        const hx_config& c = m->cfg;
+        const bool slot = seq != 0 || m->batch > 1;       // a slot of a batch: everything through the chunk path
+        const int Tc = slot ? T : T - 1;
+        const int ps[2] = {0, seq};
         HX_CUDA(cudaMemcpyAsync(m->d_pf_pos, ps, 8, cudaMemcpyHostToDevice, m->st));
-        for (int t0 = 0; t0 < Tc; t0 += HX_PF_TB)
-            if ((rc = pf_enqueue_chunk(m, Tc - t0 < HX_PF_TB ? Tc - t0 : HX_PF_TB))) return rc;
+        int nlast = 0;
+        for (int t0 = 0; t0 < Tc; t0 += HX_PF_TB) {
+            nlast = Tc - t0 < HX_PF_TB ? Tc - t0 : HX_PF_TB;
+            if ((rc = pf_enqueue_chunk(m, nlast))) return rc;
+        }
+        if (slot) {
+            // the head on the last position, then the first maximum over the ranks' vocabulary slices
+            if ((rc = pf_linear(m, m->head, m->pf_x + (size_t)(nlast - 1) * c.d_model, c.d_model, 1, 0, m->final_g, m->logits, 0, m->head.N, 0, 0))) return rc;
+            const unsigned ep = ++m->tp_pf_ep;
+            unsigned long long* areas[8] = {nullptr};
+            for (int w = 0; w < m->tp_world; w++)
+                areas[w] = reinterpret_cast<unsigned long long*>(m->tp_peer[w]) + m->tp_pf_off + (size_t)(ep & 1u) * m->tp_world * m->tp_pf_area;
+            hx_pf_tp_argmax_rows(m->logits, c.vocab, c.vocab, 1, m->tp_rank * c.vocab, areas, m->tp_rank, m->tp_world, m->tp_pf_area, ep,
+                                 m->wait_limit, m->pf_err, m->d_tok, nullptr, m->st);
+            HX_CUDA(cudaGetLastError());
+            return HX_OK;
+        }
         if ((rc = set_pos_tok(m, T - 1, nullptr))) return rc;
         HX_CUDA(cudaMemcpyAsync(m->d_tok, m->d_prompt + (T - 1), 4, cudaMemcpyDeviceToDevice, m->st));
         return step_decode(m);
@@ -1673,7 +1697,8 @@ HX_API int hx_generate_spec(hx_model* m, const int32_t* prompt, int T, int n_new
 }
 
 static int bd_check(hx_model* m, int n_seq) {
-    if (!m->use_tc || !m->head.t128 || m->tp_world > 1) return hx_fail(HX_ERR_STATE, "batched decode needs the tensor-core engine on one GPU");
+    if (!m->use_tc || !m->head.t128 || (m->tp_world > 1 && !(m->use_df && m->pf_batched)))
+        return hx_fail(HX_ERR_STATE, "batched decode needs the tensor-core engine (and, in a tensor-parallel group, the pair engine)");
     if (n_seq < 1 || n_seq > m->batch) return hx_fail(HX_ERR_ARG, "%d sequences, the model was created for %d", n_seq, m->batch);
     return bd_alloc(m);
 }
@@ -1702,7 +1727,7 @@ HX_API int hx_decode_batch_loop(hx_model* m, const int32_t* ids, int pos0, int n
     HX_CUDA(cudaMemcpyAsync(m->d_bpos, p.data(), (size_t)n_seq * 4, cudaMemcpyHostToDevice, m->st));
     HX_CUDA(cudaStreamSynchronize(m->st));
     // one step captured once per batch size and replayed (tokens and positions live in device memory)
-    if (n_steps > 1 && (!m->g_bstep || m->g_bstep_n != n_seq)) {
+    if (n_steps > 1 && m->tp_world == 1 && (!m->g_bstep || m->g_bstep_n != n_seq)) {       // (a shard's exchanges carry epoch arguments)
         if (m->g_bstep) { cudaGraphExecDestroy(m->g_bstep); m->g_bstep = nullptr; }
         cudaGraph_t g = nullptr;
         HX_CUDA(cudaStreamBeginCapture(m->st, cudaStreamCaptureModeThreadLocal));

@@ -234,6 +234,51 @@ __global__ void __launch_bounds__(256) k_pf_tp_reduce(const float* __restrict__ 
     }
 }
 
+// Tensor-parallel batched decode: one CTA per sequence takes the first maximum of this rank's vocabulary slice, the ranks
+// exchange (value, global index) as pairs, and every rank keeps the best of all (greater value, or equal value and smaller
+// index -- the first maximum of the whole vocabulary); the sequence's position advances by one.
+__global__ void __launch_bounds__(1024) k_pf_tp_argmax_rows(const float* __restrict__ logits, int n, int ld, int vocab_off, HxPfPeers peers, int rank, int world,
+                                                            size_t area_pairs, unsigned ep, unsigned wait_limit, int* err, int* __restrict__ next, int* __restrict__ pos_arr) {
+    const float* lg = logits + (size_t)blockIdx.x * ld;
+    float bv = -INFINITY; int bi = INT_MAX;
+    for (int i = threadIdx.x; i < n; i += 1024) { const float v = lg[i]; if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
+    __shared__ float sv[1024]; __shared__ int si[1024];
+    sv[threadIdx.x] = bv; si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int s = 512; s >= 1; s >>= 1) {
+        if (threadIdx.x < s) {
+            const float ov = sv[threadIdx.x + s]; const int oi = si[threadIdx.x + s];
+            if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) { sv[threadIdx.x] = ov; si[threadIdx.x] = oi; }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        float fv = sv[0]; int fi = si[0] == INT_MAX ? INT_MAX : si[0] + vocab_off;
+        const size_t o = 2 * (size_t)blockIdx.x;
+        const unsigned long long wv = ((unsigned long long)ep << 32) | (unsigned long long)__float_as_uint(fv);
+        const unsigned long long wi = ((unsigned long long)ep << 32) | (unsigned long long)(unsigned)fi;
+        for (int w = 0; w < world; w++) if (w != rank) {
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(peers.p[w] + (size_t)rank * area_pairs + o), "l"(wv) : "memory");
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(peers.p[w] + (size_t)rank * area_pairs + o + 1), "l"(wi) : "memory");
+        }
+        for (int w = 0; w < world; w++) if (w != rank) {
+            unsigned long long gv = 0, gi = 0; bool ok = false;
+            const unsigned long long* src = peers.p[rank] + (size_t)w * area_pairs + o;
+            for (unsigned t = 0; t < wait_limit; t++) {
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(gv) : "l"(src) : "memory");
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(gi) : "l"(src + 1) : "memory");
+                if ((unsigned)(gv >> 32) == ep && (unsigned)(gi >> 32) == ep) { ok = true; break; }
+                if ((t & 1023u) == 1023u && *reinterpret_cast<volatile int*>(err) != 0) break;
+            }
+            if (!ok) { *err = 1; continue; }
+            const float ov = __uint_as_float((unsigned)gv); const int oi = (int)(unsigned)gi;
+            if (ov > fv || (ov == fv && oi < fi)) { fv = ov; fi = oi; }
+        }
+        next[blockIdx.x] = fi == INT_MAX ? 0 : fi;
+        if (pos_arr) pos_arr[blockIdx.x] += 1;
+    }
+}
+
 __global__ void k_pf_advance(int* posp, int n) { if (threadIdx.x == 0) *posp += n; }
 // one CTA per token row: first maximum of logits[row][0..n) -> next[row]; the row's position advances by one
 __global__ void __launch_bounds__(1024) k_pf_argmax_rows(const float* __restrict__ logits, int n, int ld, int* __restrict__ next, int* __restrict__ pos_arr) {
@@ -342,6 +387,14 @@ void hx_pf_tp_reduce(const float* part, float* x, unsigned long long* const* pee
     for (int w = 0; w < world && w < 8; w++) pe.p[w] = peer_areas[w];
     int g = (count + 255) / 256; if (g > 148 * 4) g = 148 * 4;
     k_pf_tp_reduce<<<g, 256, 0, st>>>(part, x, pe, rank, world, count, area_pairs, ep, wait_limit, err);
+    HX_COUNT_LAUNCH(1);
+}
+
+void hx_pf_tp_argmax_rows(const float* logits, int n, int ld, int rows, int vocab_off, unsigned long long* const* peer_areas, int rank, int world,
+                          size_t area_pairs, unsigned ep, unsigned wait_limit, int* err, int* next, int* pos_arr, cudaStream_t st) {
+    HxPfPeers pe = {};
+    for (int w = 0; w < world && w < 8; w++) pe.p[w] = peer_areas[w];
+    k_pf_tp_argmax_rows<<<rows, 1024, 0, st>>>(logits, n, ld, vocab_off, pe, rank, world, area_pairs, ep, wait_limit, err, next, pos_arr);
     HX_COUNT_LAUNCH(1);
 }
 

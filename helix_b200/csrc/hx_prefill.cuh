@@ -45,5 +45,8 @@ void hx_pf_argmax(const float* logits, int n, int* tok, int* hist, int* pos_out,
 // pairs through peer_areas[w] (rank r writes slot r of every peer; slots are area_pairs pairs apart).
 void hx_pf_tp_reduce(const float* part, float* x, unsigned long long* const* peer_areas, int rank, int world, int count, size_t area_pairs,
                      unsigned ep, unsigned wait_limit, int* err, cudaStream_t st);
+// Tensor parallel: per row the first maximum over the ranks' vocabulary slices (this rank's slice starts at vocab_off).
+void hx_pf_tp_argmax_rows(const float* logits, int n, int ld, int rows, int vocab_off, unsigned long long* const* peer_areas, int rank, int world,
+                          size_t area_pairs, unsigned ep, unsigned wait_limit, int* err, int* next, int* pos_arr, cudaStream_t st);
 void hx_pf_top2_rows(const float* logits, int n, int ld, int rows, int* next, float* margin, cudaStream_t st);
 void hx_pf_argmax_rows(const float* logits, int n, int ld, int rows, int* next, int* pos_arr, cudaStream_t st);

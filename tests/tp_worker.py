@@ -76,6 +76,32 @@ def main():
         print("TP-OK world=%d max-abs-logit-diff=%.3g prefill-max-abs=%.3g" % (world, worst, pf_err), flush=True)
     dist.barrier()
     gm.close()
+
+    # a batch of three sequences inside the group: prompts of different lengths into their own KV slots, then batched
+    # decode steps; the arg-max over the ranks' vocabulary slices is taken per sequence
+    gb = hb.Model.load(path, kv_cap=96, tp_rank=rank, tp_size=world, batch=3)
+    mine = torch.tensor(list(gb.tp_handle()), dtype=torch.uint8)
+    allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
+    dist.all_gather(allh, mine)
+    gb.tp_connect([bytes(h.tolist()) for h in allh])
+    dist.barrier()
+    rngb = np.random.default_rng(31)
+    prompts = [rngb.integers(0, NVl * world, n).astype(np.int32) for n in (5, 17, 20)]
+    toks = np.array([gb.prefill_seq(i, p) for i, p in enumerate(prompts)], np.int32)
+    pos = np.array([len(p) for p in prompts], np.int32)
+    got = [toks.copy()]
+    for step in range(6):
+        toks = gb.decode_batch(toks, pos + step)
+        got.append(toks.copy())
+    got = np.stack(got, 1)                                   # [sequence][7 tokens]
+    if rank == 0:
+        for i, p in enumerate(prompts):
+            om.reset()
+            want = om.generate(p, 7)
+            assert list(got[i]) == [int(t) for t in want], (i, list(got[i]), list(want))
+        print("TP-BATCH-OK world=%d" % world, flush=True)
+    dist.barrier()
+    gb.close()
     dist.destroy_process_group()
 
 
