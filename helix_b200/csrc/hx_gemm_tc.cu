@@ -9,10 +9,11 @@
 // forward_layer_llama, helixc/runtime/gpt2_infer.c:1231-1287) or several exact base-8 digit columns
 // of one f32 vector (decode, replaces fused_gemv :2281-2297).
 //
-// One CTA per 128-row tile of A.  Warp 0 streams A and B cells into a shared-memory ring with
-// cp.async.bulk; warp 1 copies the scale factors to TMEM (tcgen05.cp) and issues
-// tcgen05.mma.kind::mxf4nvf4.block_scale (M=128, N=ncols, K=64 per instruction); warps 2-5 read the
-// accumulator with tcgen05.ld and store it.  Tensor-bound for large N, HBM-bound for small N.
+// Work units of one 128-row tile of A (times a piece of K), a CTA per SM walking through its units.  Warp 0
+// streams A (and B) cells into a shared-memory ring with cp.async.bulk; warp 1 copies the scale factors to TMEM
+// (tcgen05.cp) and issues tcgen05.mma.kind::mxf4nvf4.block_scale (M=128, N=ncols, K=64 per instruction); warps
+// 2-9 read the accumulator with tcgen05.ld and store it while the next unit's MMAs run.  In the batched
+// prefill the B cells of a CTA's K piece stay in shared memory, so only the weights stream.  Tensor-bound for large N, HBM-bound for small N.
 //
 // "T128" layout of A: per (128-row tile, group of 256 columns = four MMA K steps) one 18432-byte cell:
 // 128 rows x 128 bytes of codes in the canonical K-major 128-byte-swizzle operand layout (row r at
@@ -70,26 +71,60 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 }
 
 struct TcSmem {
-    uint64_t full[HX_TC_STAGES], empty[HX_TC_STAGES], accum, bfull;
+    uint64_t full[HX_TC_STAGES], empty[HX_TC_STAGES], accum, acc_free, bfull[HX_TC_RES_CELLS];
     uint32_t tmem_base;
-    unsigned ticket;
-    float swi[128];
+    unsigned ticket[2];
     volatile int abort_flag;
 };
+#define TC_THREADS 320          // warp 0 loads, warp 1 issues the MMAs, warps 2-9 read the accumulator
+#define TC_HDR 1536u            // header + the chunk of unit scales
+#define TC_SWI (HX_TC_MAX_TOK * 128 * 4)      // SwiGLU exchange: [token][row of the tile]
 
-__global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGemmTC g) {
+__device__ __forceinline__ void tc_ld16(uint32_t (&r)[16], uint32_t taddr) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ float tc_digits(const uint32_t (&r)[16]) {       // sum_j 4^-j r[j]
+    float v = 0.0f;
+#pragma unroll
+    for (int j = 15; j >= 0; j--) v = fmaf(v, 0.25f, __uint_as_float(r[j]));
+    return v;
+}
+
+// The three roles run through the CTA's work units on their own and meet only at mbarriers: `full`/`empty` per ring
+// slot between the loader and the MMA issuer, `accum` (accumulator complete) and `acc_free` (accumulator read out)
+// between the issuer and the eight epilogue warps.  The epilogue empties the accumulator into registers first (two
+// warps per quarter of the TMEM lanes, half of the tokens each, the next token's load in flight while the digits of
+// the current one are recombined) and frees it, so the MMAs of the next unit run under its stores.
+//
+// Work units: (128-row tile, K piece, group of 16 tokens).  K is cut into pieces of whole 256-column cells (digit
+// mode); each piece recombines its own digits and leaves them in `partial`, and the last piece of a (tile, group)
+// to finish (a ticket) adds the pieces in K order and applies the epilogue.  The ticket of a unit is drawn after
+// its partial sums are stored and looked at one unit later, so its round trip is hidden by the next unit's MMAs.
+// With resident B the grid is a multiple of pieces x groups: a CTA keeps one (piece, group) and loads its B cells once,
+// and the CTAs of the groups walk through the same tiles together, so a weight cell comes from DRAM once.
+__global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant__ HxGemmTC g) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     TcSmem& S = *reinterpret_cast<TcSmem*>(smem_raw);
     // swizzled operands need 1024-byte aligned cells (the swizzle is a function of the shared-memory address)
     static_assert(sizeof(TcSmem) <= 1024, "header overlaps the unit-scale chunk");
-    uint8_t* ring = smem_raw + (((s_u32(smem_raw) + 1536u + 1023u) & ~1023u) - s_u32(smem_raw));
+    float* swi = reinterpret_cast<float*>(smem_raw + TC_HDR);
+    uint8_t* ring = smem_raw + (((s_u32(smem_raw) + TC_HDR + TC_SWI + 1023u) & ~1023u) - s_u32(smem_raw));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int NB = g.ncols, Sk = g.stage_ksteps;
-    // a stage holds Sk K steps = Sk/4 cells of 256 columns
-    const uint32_t b_cell_bytes = (uint32_t)NB * 128u + (g.digit_mode ? 0u : 2048u);       // one 256-column cell of B
-    const uint32_t a_cell = HX_T128_CELL / 4, b_cell = b_cell_bytes / 4;                     // bytes per K step
-    // b_resident: the B cells of this CTA's K piece stay in shared memory across its units (the ring holds A only)
+    const int Sk = g.stage_ksteps;
+    const int P = g.ksplit > 1 ? g.ksplit : 1, kcells = g.ksteps / 4;
+    const int G = (g.ncols + 255) / 256, PG = P * G;
+    const int nunits = g.ntiles * PG;
+    // b_resident: the B cells of this CTA's (K piece, token group) stay in shared memory across its units (the ring
+    // holds A only).  Otherwise there is one group, and the ring holds the A and the B cells of a stage.
     const int BR = g.b_resident;
+    const int grp = BR ? ((int)blockIdx.x % PG) % G : 0;
+    const int NB = min(256, g.ncols - 256 * grp);                                            // columns of this CTA's MMAs
+    const uint32_t b_src_cell = (uint32_t)g.ncols * 128u + (g.digit_mode ? 0u : 2048u);      // one 256-column cell of B in memory
+    const uint32_t b_cell_bytes = BR ? (uint32_t)NB * 128u : b_src_cell;                      // ... and in shared memory
+    const uint32_t a_cell = HX_T128_CELL / 4, b_cell = b_cell_bytes / 4;                     // bytes per K step
     const uint32_t stage_bytes = (uint32_t)Sk * (a_cell + (BR ? 0u : b_cell));
     uint8_t* bres = ring + (size_t)HX_TC_STAGES * stage_bytes;      // [cells of a piece][NB * 128]
 
@@ -97,7 +132,8 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (tid == 0) {
         for (int i = 0; i < HX_TC_STAGES; i++) { mb_init(&S.full[i], 1); mb_init(&S.empty[i], 1); }
-        mb_init(&S.accum, 1); mb_init(&S.bfull, 1);
+        for (int i = 0; i < HX_TC_RES_CELLS; i++) mb_init(&S.bfull[i], 1);
+        mb_init(&S.accum, 1); mb_init(&S.acc_free, 8);
         S.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -109,159 +145,162 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = S.tmem_base;
-    // TMEM columns: [0, 256) accumulator (ncols used), then per ring slot Sk*4 columns of SFA and of SFB
+    // TMEM columns: [0, 256) accumulator (NB used), then per ring slot Sk*4 columns of SFA and of SFB
     const uint32_t col_sfa = 256, col_sfb = 256 + HX_TC_STAGES * HX_TC_MAX_SK * 4;
+    // unit u of this CTA: tile u / PG and, with `combo` = u % PG, piece combo / G (and group combo % G = grp)
+#define TC_UNIT(u) const int mt = (u) / PG, piece = ((u) - mt * PG) / G; \
+                   const int ks_lo = (piece * kcells / P) * 4, ks_hi = ((piece + 1) * kcells / P) * 4
 
-    // Work units: (128-row tile, K piece).  ksplit > 1 (digit mode only) cuts K into pieces of whole 256-column
-    // cells; each piece recombines its own digits and the last piece of a tile to finish (ticket) adds the
-    // pieces in K order and applies the epilogue.
-    const int P = g.ksplit > 1 ? g.ksplit : 1, kcells = g.ksteps / 4;
-    const int nunits = g.ntiles * P;
-    uint32_t base_it = 0;                          // stage iterations of the units this CTA has finished
-    uint32_t b_loads = 0; int cur_piece = -1;      // resident-B bookkeeping (same in every role)
-    int unit_iter = 0;
-    for (int u = blockIdx.x; u < nunits; u += gridDim.x, unit_iter++) {
-        const int mt = u / P, piece = u - mt * P;
-        const int ks_lo = (piece * kcells / P) * 4, ks_hi = ((piece + 1) * kcells / P) * 4;
-        const int n_it = (ks_hi - ks_lo + Sk - 1) / Sk;
-        int n_it_run = n_it;
-        const bool new_b = BR && (unit_iter == 0 || piece != cur_piece);
-        if (warp == 0 && lane == 0) {
-            // ------------------------------ producer ------------------------------
-            if (new_b) {        // every MMA of the previous unit has completed (its epilogue ran before the CTA barrier)
-                const uint32_t bytes = (uint32_t)((ks_hi - ks_lo) / 4) * b_cell_bytes;
-                mb_expect(&S.bfull, bytes);
-                bulk_load(bres, g.b + (size_t)(ks_lo / 4) * b_cell_bytes, bytes, &S.bfull);
+    if (warp == 0) {
+        // ------------------------------ loader ------------------------------
+        if (lane == 0) {
+            uint32_t git = 0;
+            bool ok = true;
+            if (BR) {
+                const int piece0 = ((int)blockIdx.x % PG) / G;
+                const int c_lo = piece0 * kcells / P, c_hi = (piece0 + 1) * kcells / P;
+                for (int c = c_lo; c < c_hi; c++) {
+                    mb_expect(&S.bfull[c - c_lo], b_cell_bytes);
+                    bulk_load(bres + (size_t)(c - c_lo) * b_cell_bytes, g.b + (size_t)c * b_src_cell + (size_t)grp * 32768u, b_cell_bytes, &S.bfull[c - c_lo]);
+                }
             }
-            for (int it = 0; it < n_it; it++) {
-                const uint32_t git = base_it + it, slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
-                if (round > 0 && !mb_wait(&S.empty[slot], (round - 1) & 1, &S.abort_flag)) break;
-                const int ks0 = ks_lo + it * Sk, nk = min(Sk, ks_hi - ks0);
-                uint8_t* sa = ring + (size_t)slot * stage_bytes;
-                uint8_t* sb = sa + (size_t)Sk * a_cell;
-                mb_expect(&S.full[slot], (uint32_t)nk * (a_cell + (BR ? 0u : b_cell)));
-                bulk_load(sa, g.a + ((size_t)mt * g.ksteps + ks0) * a_cell, (uint32_t)nk * a_cell, &S.full[slot]);
-                if (!BR) bulk_load(sb, g.b + (size_t)ks0 * b_cell, (uint32_t)nk * b_cell, &S.full[slot]);
+            for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x) {
+                TC_UNIT(u);
+                for (int ks0 = ks_lo; ks0 < ks_hi; ks0 += Sk, git++) {
+                    const uint32_t slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
+                    if (round > 0 && !mb_wait(&S.empty[slot], (round - 1) & 1, &S.abort_flag)) { ok = false; break; }
+                    const int nk = min(Sk, ks_hi - ks0);
+                    uint8_t* sa = ring + (size_t)slot * stage_bytes;
+                    uint8_t* sb = sa + (size_t)Sk * a_cell;
+                    mb_expect(&S.full[slot], (uint32_t)nk * (a_cell + (BR ? 0u : b_cell)));
+                    bulk_load(sa, g.a + ((size_t)mt * g.ksteps + ks0) * a_cell, (uint32_t)nk * a_cell, &S.full[slot]);
+                    if (!BR) bulk_load(sb, g.b + (size_t)ks0 * b_cell, (uint32_t)nk * b_cell, &S.full[slot]);
+                }
             }
-        } else if (warp == 1 && lane == 0) {
-            // ------------------------------ MMA issuer ------------------------------
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
             // instruction descriptor: E2M1 x E2M1, UE4M3 scales, K-major both, N = NB, M = 128, K = 64
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | (8u << 24);
-            if (g.digit_mode && unit_iter == 0) {
+            uint32_t git = 0;
+            bool ok = true;
+            if (g.digit_mode) {
                 // unit scales (E4M3 1.0) for every digit column: sixteen TMEM columns cover any N up to 256
                 for (int c = 0; c < 4; c++) tc_cp_sf(tmem + col_sfb + c * 4, smem_desc(s_u32(smem_raw + 1024), 16, 128));
             }
-            if (new_b) { if (!mb_wait(&S.bfull, b_loads & 1u, &S.abort_flag)) n_it_run = 0; }
-            for (int it = 0; it < n_it_run; it++) {
-                const uint32_t git = base_it + it, slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
-                if (!mb_wait(&S.full[slot], round & 1, &S.abort_flag)) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int ks0 = ks_lo + it * Sk, nk = min(Sk, ks_hi - ks0);
-                const uint32_t sa = s_u32(ring + (size_t)slot * stage_bytes);
-                const uint32_t sb = BR ? s_u32(bres) + (uint32_t)(it * (Sk / 4)) * b_cell_bytes : sa + (uint32_t)Sk * a_cell;
-                for (int rep = 0; rep < ((g.dbg & 8) ? 4 : 1); rep++)
-                for (int k = 0; k < nk; k++) {
-                    const uint32_t ta = tmem + col_sfa + (slot * HX_TC_MAX_SK + k) * 4;
-                    const uint32_t tb = tmem + col_sfb + (slot * HX_TC_MAX_SK + k) * 4;
-                    const uint32_t acell = sa + (uint32_t)(k >> 2) * HX_T128_CELL, bcell = sb + (uint32_t)(k >> 2) * b_cell_bytes;
-                    const uint32_t e = (uint32_t)(k & 3);
-                    if (!(g.dbg & 1) || (it == 0 && k == 0)) {
+            int unit_iter = 0;
+            for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x, unit_iter++) {
+                TC_UNIT(u);
+                (void)mt;
+                if (unit_iter > 0) {      // the epilogue has read the previous unit's accumulator out
+                    if (!mb_wait(&S.acc_free, (uint32_t)(unit_iter - 1) & 1u, &S.abort_flag)) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                }
+                for (int ks0 = ks_lo; ks0 < ks_hi; ks0 += Sk, git++) {
+                    const uint32_t slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
+                    if (BR && unit_iter == 0 && !mb_wait(&S.bfull[(ks0 - ks_lo) / 4], 0, &S.abort_flag)) { ok = false; break; }
+                    if (!mb_wait(&S.full[slot], round & 1, &S.abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const int nk = min(Sk, ks_hi - ks0);
+                    const uint32_t sa = s_u32(ring + (size_t)slot * stage_bytes);
+                    const uint32_t sb = BR ? s_u32(bres) + (uint32_t)((ks0 - ks_lo) / 4) * b_cell_bytes : sa + (uint32_t)Sk * a_cell;
+                    for (int k = 0; k < nk; k++) {
+                        const uint32_t ta = tmem + col_sfa + (slot * HX_TC_MAX_SK + k) * 4;
+                        const uint32_t tb = tmem + col_sfb + (slot * HX_TC_MAX_SK + k) * 4;
+                        const uint32_t acell = sa + (uint32_t)(k >> 2) * HX_T128_CELL, bcell = sb + (uint32_t)(k >> 2) * b_cell_bytes;
+                        const uint32_t e = (uint32_t)(k & 3);
                         tc_cp_sf(ta, smem_desc(acell + 16384 + e * 512, 16, 128));
                         if (!g.digit_mode) tc_cp_sf(tb, smem_desc(bcell + (uint32_t)NB * 128u + e * 512, 16, 128));
+                        tc_mma(tmem, smem_desc(acell + e * 32, 16, 1024, SW128), smem_desc(bcell + e * 32, 16, 1024, SW128), idesc,
+                               ta, g.digit_mode ? tmem + col_sfb : tb, (ks0 > ks_lo || k > 0) ? 1u : 0u);
                     }
-                    tc_mma(tmem + ((g.dbg & 4) ? (uint32_t)(k & 3) * 64u : 0u), smem_desc(acell + e * 32, 16, 1024, SW128), smem_desc(bcell + e * 32, 16, 1024, SW128), idesc,
-                           (g.dbg & 2) ? tmem + col_sfa : ta, ((g.dbg & 2) || g.digit_mode) ? tmem + col_sfb : tb, (it > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(&S.empty[slot]);          // the slot is free once these MMAs have read it
                 }
-                tc_commit(&S.empty[slot]);          // the slot is free once these MMAs have read it
+                if (ok) tc_commit(&S.accum);            // accumulator complete
             }
-            tc_commit(&S.accum);                    // accumulator complete
-        } else if (warp >= 2) {
-            // ------------------------------ epilogue: TMEM -> registers -> global ------------------------------
-            if (mb_wait(&S.accum, (uint32_t)unit_iter & 1u, &S.abort_flag)) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int sub = warp & 3;                          // TMEM lanes 32*sub .. 32*sub+31
-                const int rl = sub * 32 + lane, row = mt * 128 + rl;
-                if (g.digit_mode) {
-                    const int ntok = NB / 16;
-                    const float tsr = g.pair64 ? (((row & 127) < 64) ? g.ts[0] : g.ts[1])
-                                               : (row < g.bound0 ? g.ts[0] : (row < g.bound1 ? g.ts[1] : g.ts[2]));
-                    // final value of (token t, this row): tensor scale, then store / residual add / SwiGLU across the
-                    // gate (rows 0..63 of the tile) and up (rows 64..127) halves
-                    // residual linears: the old values of this row for every token are fetched up front, all loads in
-                    // flight together (one dependent round trip per token was most of a short GEMM's time)
-                    float prev[HX_TC_MAX_TOK];
+        }
+    } else {
+        // ------------------------------ epilogue: TMEM -> registers -> global ------------------------------
+        const int ew = warp - 2, sub = warp & 3, half = ew >> 2;      // TMEM lanes 32*sub .. 32*sub+31; tokens 8*half .. 8*half+7 of the group
+        const int rl = sub * 32 + lane, etid = tid - 64;
+        const uint32_t bar_half = 1u + (uint32_t)half;               // named barriers: 1, 2 = the four warps of a half; 3 = all eight
+        constexpr int TH = HX_TC_MAX_TOK / 2;
+        const int ntok = NB / 16, tok0 = grp * HX_TC_MAX_TOK + half * TH;      // this thread's tokens: tok0 .. tok0+TH-1 of the launch
+        const int tleft = ntok - half * TH;                                     // ... of which tleft exist
+        const int ptok = G * HX_TC_MAX_TOK;                                     // token slots of a piece in `partial`
+        float cs[TH];
 #pragma unroll
-                    for (int t = 0; t < HX_TC_MAX_TOK; t++)
-                        prev[t] = (g.resid && !g.swiglu && t < ntok && row < g.rows) ? __ldcg(g.out + (size_t)t * g.ld_out + row) : 0.0f;
-                    auto finalize = [&](int t, float v, float old) {
-                        v *= tsr;
-                        if (g.swiglu) {
-                            S.swi[rl] = v;
-                            asm volatile("bar.sync 1, 128;" ::: "memory");
-                            if (rl < 64 && mt * 64 + rl < g.rows) {
-                                const float gt = S.swi[rl], up = S.swi[rl + 64];
-                                const float sgn = gt < 0.0f ? -1.0f : 1.0f;
-                                const float ex = __expf(-(sgn * gt));
-                                const float th = sgn * ((1.0f - ex) / (1.0f + ex));
-                                g.out[(size_t)t * g.ld_out + mt * 64 + rl] = gt * (0.5f * (1.0f + th)) * up;
-                            }
-                            asm volatile("bar.sync 1, 128;" ::: "memory");
-                        } else if (row < g.rows) {
-                            g.out[(size_t)t * g.ld_out + row] = g.resid ? old + v : v;
-                        }
-                    };
-                    // the tokens' digit scales, fetched once (a load per token between the stores below would be a dependent
-                    // round trip each)
-                    float cs[HX_TC_MAX_TOK];
+        for (int t = 0; t < TH; t++) cs[t] = (g.digit_mode && t < tleft) ? __ldg(g.col_scale + tok0 + t) : 0.0f;
+        // final values of tile mtf: tensor scale, then store / residual add / SwiGLU across the gate (rows 0..63 of the
+        // tile) and up (rows 64..127) halves
+        bool dead = false;      // a wait ran out: keep to the barrier protocol, touch nothing
+        auto finalize = [&](int mtf, const float (&val)[TH], const float (&prev)[TH]) {
+            const int row = mtf * 128 + rl;
+            const float tsr = g.pair64 ? ((rl < 64) ? g.ts[0] : g.ts[1])
+                                       : (row < g.bound0 ? g.ts[0] : (row < g.bound1 ? g.ts[1] : g.ts[2]));
+            if (g.swiglu) {
 #pragma unroll
-                    for (int t = 0; t < HX_TC_MAX_TOK; t++) cs[t] = t < ntok ? __ldg(g.col_scale + t) : 0.0f;
-                    float* part = g.partial + ((size_t)(mt * P) * HX_TC_MAX_TOK) * 128;      // [piece][token][row in tile]
+                for (int t = 0; t < TH; t++) swi[(half * TH + t) * 128 + rl] = val[t] * tsr;
+                asm volatile("bar.sync %0, 128;" :: "r"(bar_half) : "memory");
+                if (rl < 64 && mtf * 64 + rl < g.rows && !dead) {
 #pragma unroll
-                    for (int t = 0; t < HX_TC_MAX_TOK; t++) {
-                        if (t >= ntok) break;
-                        uint32_t r[16];
-                        const uint32_t ta = tmem + ((uint32_t)(sub * 32) << 16) + (uint32_t)(t * 16);
-                        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                                       "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                                     : "r"(ta));
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        float v = 0.0f;
-#pragma unroll
-                        for (int j = 15; j >= 0; j--) v = fmaf(v, 0.25f, __uint_as_float(r[j]));
-                        v = v * cs[t];
-                        if (P > 1) part[((size_t)piece * HX_TC_MAX_TOK + t) * 128 + rl] = v;
-                        else finalize(t, v, prev[t]);
+                    for (int t = 0; t < TH; t++) {
+                        if (t >= tleft) break;
+                        const float gt = swi[(half * TH + t) * 128 + rl], up = swi[(half * TH + t) * 128 + rl + 64];
+                        const float sgn = gt < 0.0f ? -1.0f : 1.0f;
+                        const float ex = __expf(-(sgn * gt));
+                        const float th = sgn * ((1.0f - ex) / (1.0f + ex));
+                        g.out[(size_t)(tok0 + t) * g.ld_out + mtf * 64 + rl] = gt * (0.5f * (1.0f + th)) * up;
                     }
-                    if (P > 1) {
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        if (tid == 64) {
-                            unsigned old;
-                            asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(g.tickets + mt) : "memory");
-                            S.ticket = old;
-                        }
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        if (S.ticket == (unsigned)(P - 1)) {
-                            // the pieces of all tokens: sixteen loads in flight per piece, added in piece order per token
-                            float sum[HX_TC_MAX_TOK];
+                }
+                asm volatile("bar.sync %0, 128;" :: "r"(bar_half) : "memory");
+            } else if (row < g.rows && !dead) {
 #pragma unroll
-                            for (int t = 0; t < HX_TC_MAX_TOK; t++) sum[t] = 0.0f;
-                            for (int q = 0; q < P; q++) {
+                for (int t = 0; t < TH; t++) {
+                    if (t >= tleft) break;
+                    const float v = val[t] * tsr;
+                    g.out[(size_t)(tok0 + t) * g.ld_out + row] = g.resid ? prev[t] + v : v;
+                }
+            }
+        };
+        auto load_prev = [&](int mtf, float (&prev)[TH]) {      // residual linears: the old values of this row
+            const int row = mtf * 128 + rl;
 #pragma unroll
-                                for (int t = 0; t < HX_TC_MAX_TOK; t++)
-                                    if (t < ntok) sum[t] += __ldcg(part + ((size_t)q * HX_TC_MAX_TOK + t) * 128 + rl);
-                            }
+            for (int t = 0; t < TH; t++)
+                prev[t] = (g.resid && !g.swiglu && t < tleft && row < g.rows) ? __ldcg(g.out + (size_t)(tok0 + t) * g.ld_out + row) : 0.0f;
+        };
+        // the ticket drawn for tile mtf said that its other pieces are done: add all pieces in K order and finish the tile
+        auto merge = [&](int mtf) {
+            float val[TH], prev[TH];
+            load_prev(mtf, prev);
+            const float* part = g.partial + ((size_t)mtf * P * ptok + tok0) * 128 + rl;      // [piece][token][row in tile]
 #pragma unroll
-                            for (int t = 0; t < HX_TC_MAX_TOK; t++) if (t < ntok) finalize(t, sum[t], prev[t]);
-                            if (tid == 64) g.tickets[mt] = 0u;
-                        }
-                    }
-                } else
-                for (int c0 = 0; c0 < NB; c0 += 8) {
+            for (int t = 0; t < TH; t++) val[t] = 0.0f;
+            for (int q = 0; q < P; q++) {
+#pragma unroll
+                for (int t = 0; t < TH; t++)
+                    if (t < tleft) val[t] += __ldcg(part + ((size_t)q * ptok + t) * 128);
+            }
+            if (etid == 0 && !dead) g.tickets[mtf * G + grp] = 0u;
+            finalize(mtf, val, prev);
+        };
+        int unit_iter = 0, pend_mt = -1;
+        unsigned pend_ticket = 0;                        // meaningful in the thread that draws the tickets
+        for (int u = blockIdx.x; u < nunits; u += gridDim.x, unit_iter++) {
+            TC_UNIT(u);
+            (void)ks_lo; (void)ks_hi;
+            const int row = mt * 128 + rl;
+            float prev[TH];
+            if (g.digit_mode && P == 1) load_prev(mt, prev);      // fetched before the accumulator is ready
+            if (dead || !mb_wait(&S.accum, (uint32_t)unit_iter & 1u, &S.abort_flag)) dead = true;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tlane = tmem + ((uint32_t)(sub * 32) << 16);
+            if (!g.digit_mode) {
+                for (int c0 = half * 8; c0 < NB && !dead; c0 += 16) {
                     uint32_t r[8];
-                    const uint32_t ta = tmem + ((uint32_t)(sub * 32) << 16) + (uint32_t)c0;
                     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(ta));
+                                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(tlane + (uint32_t)c0));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (row < g.rows) {
 #pragma unroll
@@ -269,26 +308,69 @@ __global__ void __launch_bounds__(192, 1) k_gemm_tc(const __grid_constant__ HxGe
                     }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mb_arrive(&S.acc_free);
+                continue;
             }
+            // ---- digit mode: this thread's row and tokens: sixteen digit accumulators each -> one value
+            float val[TH];
+            {
+                uint32_t ra[16], rb[16];
+                const uint32_t tcol = tlane + (uint32_t)(half * TH * 16);
+                const int tleft = dead ? 0 : ntok - half * TH;       // (shadows the outer count: nothing is read after a failed wait)
+                if (0 < tleft) tc_ld16(ra, tcol);
+#pragma unroll
+                for (int t = 0; t < TH; t += 2) {
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (t + 1 < tleft) tc_ld16(rb, tcol + (uint32_t)((t + 1) * 16));
+                    val[t] = t < tleft ? tc_digits(ra) * cs[t] : 0.0f;
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (t + 2 < TH && t + 2 < tleft) tc_ld16(ra, tcol + (uint32_t)((t + 2) * 16));
+                    val[t + 1] = t + 1 < tleft ? tc_digits(rb) * cs[t + 1] : 0.0f;
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mb_arrive(&S.acc_free);       // the issuer may overwrite the accumulator
+            if (P == 1) { finalize(mt, val, prev); continue; }
+            // K pieces: leave this piece's values, look at the ticket of the previous unit, draw this unit's
+            float* part = g.partial + (((size_t)mt * P + piece) * ptok + tok0) * 128 + rl;
+#pragma unroll
+            for (int t = 0; t < TH; t++)
+                if (t < tleft && !dead) part[(size_t)t * 128] = val[t];
+            if (etid == 0 && pend_mt >= 0) S.ticket[unit_iter & 1] = pend_ticket;
+            asm volatile("bar.sync 3, 256;" ::: "memory");
+            const bool fin = pend_mt >= 0 && S.ticket[unit_iter & 1] == (unsigned)(P - 1);
+            if (etid == 0 && !dead)
+                asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(pend_ticket) : "l"(g.tickets + mt * G + grp) : "memory");
+            if (fin) merge(pend_mt);
+            pend_mt = mt;
         }
-        base_it += (uint32_t)n_it;
-        if (new_b) { b_loads++; cur_piece = piece; }
-        // all roles meet before the next unit (the accumulator is reused)
-        __syncthreads();
+        if (pend_mt >= 0) {      // the last unit's ticket
+            if (etid == 0) S.ticket[unit_iter & 1] = pend_ticket;
+            asm volatile("bar.sync 3, 256;" ::: "memory");
+            if (S.ticket[unit_iter & 1] == (unsigned)(P - 1)) merge(pend_mt);
+        }
     }
-    if (S.abort_flag && tid == 0 && g.err) *g.err = 1;
+#undef TC_UNIT
     __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" :: "r"(tmem) : "memory");
+    if (S.abort_flag && tid == 0 && g.err) *g.err = 1;
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" :: "r"(tmem) : "memory");
+    }
 }
 
 }  // namespace
 
+// header, SwiGLU exchange and the slack of the 1024-byte alignment of the ring
+#define TC_FRONT (((TC_HDR + TC_SWI + 1023u) & ~1023u) + 1024u)
 size_t hx_gemm_tc_smem(int ncols, int stage_ksteps) {
-    return 4096 + (size_t)HX_TC_STAGES * (stage_ksteps / 4) * (HX_T128_CELL + (size_t)ncols * 128 + 2048);
+    return TC_FRONT + (size_t)HX_TC_STAGES * (stage_ksteps / 4) * (HX_T128_CELL + (size_t)ncols * 128 + 2048);
 }
 // resident-B variant: ring of A cells + the B cells of one K piece
 static size_t gemm_tc_smem_resident(int ncols, int stage_ksteps, int cells_per_piece) {
-    return 4096 + (size_t)HX_TC_STAGES * (stage_ksteps / 4) * HX_T128_CELL + (size_t)cells_per_piece * ncols * 128;
+    return TC_FRONT + (size_t)HX_TC_STAGES * (stage_ksteps / 4) * HX_T128_CELL + (size_t)cells_per_piece * ncols * 128;
 }
 
 // One-time function attribute (call outside any stream capture).
@@ -300,17 +382,21 @@ int hx_gemm_tc_prepare() {
 
 int hx_gemm_tc_launch(const HxGemmTC& g, cudaStream_t st) {
     HX_CHECK_ARG(g.a && g.b && (g.digit_mode ? (g.out && g.col_scale && g.ncols % 16 == 0) : g.y != nullptr) && g.ntiles > 0 && g.ksteps > 0);
-    HX_CHECK_ARG(g.ncols >= 8 && g.ncols <= 256 && g.ncols % 8 == 0);
+    HX_CHECK_ARG(g.ncols >= 8 && g.ncols <= (g.digit_mode ? 256 * HX_TC_MAX_GROUPS : 256) && g.ncols % 8 == 0);
     HX_CHECK_ARG(g.stage_ksteps >= 4 && g.stage_ksteps <= HX_TC_MAX_SK && g.stage_ksteps % 4 == 0 && g.ksteps % 4 == 0);
     const int Pq = g.ksplit > 1 ? g.ksplit : 1, kc = g.ksteps / 4;
     if (g.b_resident) HX_CHECK_ARG(g.digit_mode && g.stage_ksteps == 4);
-    const size_t smem = g.b_resident ? gemm_tc_smem_resident(g.ncols, g.stage_ksteps, (kc + Pq - 1) / Pq) : hx_gemm_tc_smem(g.ncols, g.stage_ksteps);
+    const int nb_max = g.ncols < 256 ? g.ncols : 256;
+    const size_t smem = g.b_resident ? gemm_tc_smem_resident(nb_max, g.stage_ksteps, (kc + Pq - 1) / Pq) : hx_gemm_tc_smem(g.ncols, g.stage_ksteps);
+    if (g.b_resident) HX_CHECK_ARG((kc + Pq - 1) / Pq <= HX_TC_RES_CELLS);
     if (smem > 227 * 1024) return hx_fail(HX_ERR_ARG, "tensor-core GEMM stage too large (%zu bytes of shared memory)", smem);
     { const int prc = hx_gemm_tc_prepare(); if (prc) return prc; }
     const int P = g.ksplit > 1 ? g.ksplit : 1;
-    if (P > 1) HX_CHECK_ARG(g.digit_mode && g.partial && g.tickets && P <= g.ksteps / 4 && g.ncols / 16 <= HX_TC_MAX_TOK);
-    int grid = g.ntiles * P; if (grid > 148) grid = g.b_resident ? (148 / P) * P : 148;      // resident B: a CTA keeps one K piece
-    k_gemm_tc<<<grid, 192, smem, st>>>(g);
+    if (P > 1) HX_CHECK_ARG(g.digit_mode && g.partial && g.tickets && P <= g.ksteps / 4 && P <= 148);
+    const int G = (g.ncols + 255) / 256;
+    if (G > 1) HX_CHECK_ARG(g.b_resident && P * G <= 148);
+    int grid = g.ntiles * P * G; if (grid > 148) grid = g.b_resident ? (148 / (P * G)) * (P * G) : 148;      // resident B: a CTA keeps one (K piece, token group)
+    k_gemm_tc<<<grid, TC_THREADS, smem, st>>>(g);
     HX_COUNT_LAUNCH(1);
     HX_CUDA(cudaGetLastError());
     return HX_OK;
@@ -345,7 +431,6 @@ HX_API int hx_gemm_nvfp4_tc_bench(const uint8_t* a_t128, int rows, int K, const 
     HxGemmTC g = {};
     g.a = a_t128; g.b = b_cells; g.y = y; g.rows = rows; g.ntiles = (rows + 127) / 128; g.ksteps = K / 64;
     g.ncols = ncols; g.stage_ksteps = stage_ksteps > 0 ? stage_ksteps : 4;
-    { const char* d = getenv("HX_TC_DBG"); g.dbg = d ? atoi(d) : 0; }
     int* derr = nullptr;
     HX_CUDA(cudaMalloc(&derr, 4));
     HX_CUDA(cudaMemset(derr, 0, 4));

@@ -5,15 +5,16 @@
 #define HX_T128_CELL 18432         // one (128-row tile, 256-column group) cell of A: 16384 B codes + 4 x 512 B scales
 #define HX_TC_STAGES 4
 #define HX_TC_MAX_SK 8             // 64-column steps per ring stage (4 or 8)
-#define HX_TC_MAX_TOK 16           // tokens per launch in digit mode (16 digit columns each)
+#define HX_TC_RES_CELLS 4          // B cells of 256 columns x 256 digit columns that fit beside the ring of A cells
+#define HX_TC_MAX_TOK 16           // tokens per work unit in digit mode (16 digit columns each = the 256 columns of an MMA)
+#define HX_TC_MAX_GROUPS 4         // groups of HX_TC_MAX_TOK tokens per launch (resident B)
 
 struct HxGemmTC {
     const uint8_t* a;              // T128 cells, [tile][kstep]
-    const uint8_t* b;              // B cells, [256-column group]: ncols x 128 B swizzled codes + 4 x 512 B scale chunks
+    const uint8_t* b;              // B cells, [256-column group of K]: ncols x 128 B swizzled codes + 4 x 512 B scale chunks
     float* y;                      // [rows][ncols]
     int rows, ntiles, ksteps, ncols, stage_ksteps;
     int* err;                      // set when a bounded wait ran out
-    int dbg;                       // timing probes (bit 0: copy scale factors once, bit 1: fixed scale columns)
     // ---- digit mode (batched prefill): B holds sixteen base-4 digit columns per token with unit scales (cells of
     // ncols x 128 bytes, no scale chunks); the epilogue recombines them per token:
     //   out[t * ld_out + row] (+)= col_scale[t] * ts(row) * sum_j 4^-j D[row][16 t + j]
@@ -25,9 +26,10 @@ struct HxGemmTC {
     int pair64;                    // 1: ts[0] for rows with (row % 128) < 64, ts[1] for the others (gate/up tiles)
     int swiglu;                    // 1: tiles hold 64 gate + 64 up rows; out[t][tile * 64 + r] = silu(gate_r) * up_r, rows = hidden size
     int ksplit;                    // > 1: K pieces per tile (digit mode), merged in K order by the last piece to finish
-    float* partial;                // [ntiles][ksplit][HX_TC_MAX_TOK][128] partial sums of the pieces
-    unsigned* tickets;             // [ntiles], zero between launches
-    int b_resident;                // digit mode: keep the B cells of a CTA's K piece in shared memory (grid is a multiple of ksplit)
+    float* partial;                // [ntiles][ksplit][groups * HX_TC_MAX_TOK][128] partial sums of the pieces (groups = ceil(ncols / 256))
+    unsigned* tickets;             // [ntiles][groups], zero between launches
+    int b_resident;                // digit mode: keep the B cells of a CTA's K piece in shared memory (grid is a multiple of ksplit;
+                                   // a piece of at most HX_TC_RES_CELLS cells at 256 columns)
 };
 
 int hx_gemm_tc_launch(const HxGemmTC& g, cudaStream_t st);

@@ -95,7 +95,7 @@ struct hx_model {
     float* tp_buf = nullptr; size_t tp_buf_floats = 0; float* tp_peer[8] = {nullptr}; bool tp_connected = false; unsigned tp_launches = 0;
     float* x2 = nullptr; int tp_nbar = 0;
     // batched prefill (chunks of HX_PF_TB tokens through the tcgen05 GEMM); buffers are created on first use
-    float *pf_x = nullptr, *pf_qkv = nullptr, *pf_ctx = nullptr, *pf_gu = nullptr, *pf_scale = nullptr; uint8_t* pf_cells = nullptr; int* pf_err = nullptr; float* pf_partial = nullptr; unsigned* pf_tickets = nullptr;
+    float *pf_x = nullptr, *pf_qkv = nullptr, *pf_ctx = nullptr, *pf_gu = nullptr, *pf_scale = nullptr; uint8_t* pf_cells = nullptr; int* pf_err = nullptr; float* pf_partial = nullptr; unsigned* pf_tickets = nullptr; float* pf_att_part = nullptr; unsigned* pf_att_tickets = nullptr;
     int pf_gu_ld = 0; bool pf_batched = true; size_t pf_partial_n = 0;
     float* pf_part = nullptr; size_t tp_pf_off = 0, tp_pf_area = 0; unsigned tp_pf_ep = 0;      // tensor-parallel chunk exchange
     int *d_bids = nullptr, *d_bpos = nullptr, *d_bseq = nullptr, *d_bnext = nullptr; float* pf_logits = nullptr; int b_cap = 0;   // batched decode
@@ -1245,6 +1245,16 @@ HX_API int hx_decode_step(hx_model* m, const int32_t* ids, int pos, int32_t* nex
 }
 
 // ---- batched prefill ---------------------------------------------------------------------------------
+static_assert(HX_PF_TB <= HX_TC_MAX_GROUPS * HX_TC_MAX_TOK && HX_PF_TB % HX_TC_MAX_TOK == 0, "a chunk is whole token groups of the GEMM");
+// K pieces of a linear in the chunk GEMM: pieces small enough for their digit cells to stay in shared memory, and
+// with few row tiles enough of them for about one unit per SM.
+static int pf_pieces(const Fused& f) {
+    const int kcells = f.ksteps / 4;
+    int P = (kcells + HX_TC_RES_CELLS - 1) / HX_TC_RES_CELLS;
+    if (2 * f.tiles128 <= 148) { int q = 148 / f.tiles128; if (q > kcells) q = kcells; if (q > P) P = q; }
+    return P < 1 ? 1 : P;
+}
+
 static int pf_alloc(hx_model* m) {
     if (m->pf_x) return HX_OK;
     { const int prc = hx_gemm_tc_prepare(); if (prc) return prc; }
@@ -1262,17 +1272,20 @@ static int pf_alloc(hx_model* m) {
     if (m->tp_world > 1 && (rc = dalloc(m, &m->pf_part, (size_t)HX_PF_TB * c.d_model))) return rc;
     if ((rc = dalloc(m, &m->pf_err, (size_t)4))) return rc;
     if ((rc = dalloc(m, &m->d_pf_pos, (size_t)4))) return rc;
+    if ((rc = dalloc(m, &m->pf_att_part, hx_pf_attn_scratch(HX_PF_TB, c.n_heads, c.n_kv_heads, c.head_dim)))) return rc;
+    if ((rc = dalloc(m, &m->pf_att_tickets, (size_t)HX_PF_TB * c.n_kv_heads))) return rc;
+    HX_CUDA(cudaMemsetAsync(m->pf_att_tickets, 0, (size_t)HX_PF_TB * c.n_kv_heads * 4, m->st));
     HX_CUDA(cudaMemsetAsync(m->pf_err, 0, 16, m->st));
     {   // partial sums [tile][piece][token][128] of the most demanding linear, tickets per tile
         size_t need = 0; int maxt = m->head.tiles128;
-        auto acc = [&](const Fused& f) { const int kc = f.ksteps / 4; int P = 1; if (2 * f.tiles128 <= 148) { P = 148 / f.tiles128; if (P > kc) P = kc; }
-                                      const size_t v = (size_t)f.tiles128 * P * HX_TC_MAX_TOK * 128; if (v > need) need = v; if (f.tiles128 > maxt) maxt = f.tiles128; };
+        auto acc = [&](const Fused& f) { const size_t v = (size_t)f.tiles128 * pf_pieces(f) * HX_PF_TB * 128; if (v > need) need = v; if (f.tiles128 > maxt) maxt = f.tiles128; };
         for (auto& ly : m->layers) { acc(ly.qkv); acc(ly.o); acc(ly.gu); acc(ly.down); }
         acc(m->head);
         m->pf_partial_n = need;
         if ((rc = dalloc(m, &m->pf_partial, need))) return rc;
-        if ((rc = dalloc(m, &m->pf_tickets, (size_t)maxt + 8))) return rc;
-        HX_CUDA(cudaMemsetAsync(m->pf_tickets, 0, ((size_t)maxt + 8) * 4, m->st));
+        const size_t ntk = (size_t)maxt * HX_TC_MAX_GROUPS + 8;
+        if ((rc = dalloc(m, &m->pf_tickets, ntk))) return rc;
+        HX_CUDA(cudaMemsetAsync(m->pf_tickets, 0, ntk * 4, m->st));
     }
     return HX_OK;
 }
@@ -1285,14 +1298,10 @@ static int pf_linear(hx_model* m, const Fused& f, const float* src, int ld_src, 
     q.a = f.t128; q.b = m->pf_cells; q.rows = rows; q.ntiles = f.tiles128; q.ksteps = f.ksteps; q.ncols = 16 * n; q.stage_ksteps = 4;
     q.err = m->pf_err; q.digit_mode = 1; q.col_scale = m->pf_scale; q.out = out; q.ld_out = ld_out; q.resid = resid;
     q.ts[0] = f.ts[0]; q.ts[1] = f.ts[1]; q.ts[2] = f.ts[2]; q.bound0 = f.bound0; q.bound1 = f.bound1; q.pair64 = pair64; q.swiglu = swiglu;
-    // few tiles: cut K so that about one CTA per SM works (tiles * pieces <= 148).  Keeping the B cells of a piece
-    // resident (b_resident) with more, smaller units measured slower: a unit's epilogue is not overlapped with the
-    // next unit's loads.
-    const int kcells = f.ksteps / 4;
-    int P = 1;
-    if (2 * f.tiles128 <= 148) { P = 148 / f.tiles128; if (P > kcells) P = kcells; }
-    q.ksplit = P; q.partial = m->pf_partial; q.tickets = m->pf_tickets; q.b_resident = 0;
-    if ((size_t)f.tiles128 * P * HX_TC_MAX_TOK * 128 > m->pf_partial_n) return hx_fail(HX_ERR_ARG, "prefill: partial-sum buffer too small");
+    const int P = pf_pieces(f);
+    if (P > 148) return hx_fail(HX_ERR_ARG, "prefill: %d input columns are more than the chunk GEMM cuts into pieces", f.K);
+    q.ksplit = P; q.partial = m->pf_partial; q.tickets = m->pf_tickets; q.b_resident = 1;
+    if ((size_t)f.tiles128 * P * HX_PF_TB * 128 > m->pf_partial_n) return hx_fail(HX_ERR_ARG, "prefill: partial-sum buffer too small");
     return hx_gemm_tc_launch(q, m->st);
 }
 
@@ -1323,7 +1332,7 @@ static int pf_enqueue_layers(hx_model* m, int n, const int* ids, HxPfWhere wh) {
         float* kc = m->kc + (size_t)L * c.n_kv_heads * cap * DH; float* vc = m->vc + (size_t)L * c.n_kv_heads * cap * DH;
         if ((rc = pf_linear(m, ly.qkv, m->pf_x, DM, n, 0, ly.in_g, m->pf_qkv, ldq, ly.qkv.N, 0, 0))) return rc;
         hx_pf_qkpost(m->pf_qkv, ldq, n, wh, c.n_heads, c.n_kv_heads, DH, ly.qn_g, ly.kn_g, c.norm_eps, m->cosT, m->sinT, kc, vc, cap, m->st);
-        if ((rc = hx_pf_attn(m->pf_qkv, ldq, n, wh, c.n_heads, c.n_kv_heads, DH, kc, vc, cap, att_scale, m->pf_ctx, QD, m->st))) return rc;
+        if ((rc = hx_pf_attn(m->pf_qkv, ldq, n, wh, c.n_heads, c.n_kv_heads, DH, kc, vc, cap, att_scale, m->pf_ctx, QD, m->pf_att_part, m->pf_att_tickets, m->st))) return rc;
         if (m->tp_world > 1) {
             if ((rc = pf_linear(m, ly.o, m->pf_ctx, QD, n, 0, nullptr, m->pf_part, DM, ly.o.N, 0, 0))) return rc;
             if ((rc = pf_tp_reduce(m, n))) return rc;
@@ -1627,7 +1636,7 @@ HX_API int hx_generate_spec(hx_model* m, const int32_t* prompt, int T, int n_new
     if (cfg_in) cfg = *cfg_in;
     HX_CHECK_ARG(cfg.k_min >= 1 && cfg.k_max >= cfg.k_min && cfg.m >= 1 && cfg.min_margin >= 0.0f);
     int rc = spec_alloc(m); if (rc) return rc;
-    const int m_cap = HX_PF_TB - 1 < HX_SPEC_DRAFT_MAX ? HX_PF_TB - 1 : HX_SPEC_DRAFT_MAX;   // window = last token + drafts = one chunk
+    const int m_cap = HX_TC_MAX_TOK - 1 < HX_SPEC_DRAFT_MAX ? HX_TC_MAX_TOK - 1 : HX_SPEC_DRAFT_MAX;   // window = last token + drafts = one token group of the GEMM
     const int M = cfg.m < m_cap ? cfg.m : m_cap;
     hx_spec_stats stt = {0, 0, 0, 0, 0, 0, 0, 0};
     std::vector<int32_t> ids(prompt, prompt + T);

@@ -123,50 +123,87 @@ __global__ void __launch_bounds__(256) k_pf_qkpost(float* __restrict__ qkv, int 
     }
 }
 
-// grid (NKV, n_tok), PF_AT threads.  Online softmax over tiles of PF_KT cached positions (m seeded -1e8 like
-// fused_decode_attn_kernel.hx:74-102), so shared memory does not grow with the context.  Scores: a warp per key;
-// P*V: thread (dimension, key subset), the subsets are added up through shared memory at the end.
+// grid (NKV, n_tok, NS), PF_AT threads: CTA (kv head, token, s) covers the s-th run of whole key tiles of the token's
+// context (NS runs at most, fewer for a short context; CTAs without a run leave at once).  Online softmax over tiles
+// of PF_KT cached positions (m seeded -1e8 like fused_decode_attn_kernel.hx:74-102), so shared memory does not grow
+// with the context.  Scores: a warp takes four keys at a time, the 4 x GRP dot products are reduced across the lanes
+// together (each exchange halves the values a lane carries).  P*V: thread (dimension, run of keys inside the tile);
+// the runs are added up through shared memory at the end.  With more than one active run per (token, kv head) each
+// CTA leaves (sum, m, l) in `part`, and the last one to finish (a ticket per (token, kv head)) merges them.
 #define PF_KT 128
 #define PF_AT 512
+#define PF_NS_MAX 16
 template <int GRP>
 __global__ void __launch_bounds__(PF_AT) k_pf_attn(const float* __restrict__ qkv, int ld, HxPfWhere wh, int NH, int DH,
                                                     const float* __restrict__ kc, const float* __restrict__ vc, int cap, float scale,
-                                                    float* __restrict__ ctx, int ld_ctx) {
+                                                    float* __restrict__ ctx, int ld_ctx, float* __restrict__ part, unsigned* __restrict__ tickets) {
     extern __shared__ float smf[];
-    const int kvh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kvh = blockIdx.x, t = blockIdx.y, s = blockIdx.z, NS = gridDim.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int NW = PF_AT / 32;
+    constexpr int GP = GRP <= 1 ? 1 : (GRP <= 2 ? 2 : (GRP <= 4 ? 4 : 8));      // GRP rounded up to a power of two
+    constexpr int NP = 4 * GP;                                                   // values reduced together (4 keys x GP heads)
+    constexpr int LG = NP == 4 ? 2 : (NP == 8 ? 3 : (NP == 16 ? 4 : 5));
     const int T = (wh.pos_arr ? wh.pos_arr[t] : *wh.posp + t) + 1;
+    const int tiles = (T + PF_KT - 1) / PF_KT, per = ((tiles + NS - 1) / NS) * PF_KT;      // keys per run: whole tiles
+    const int n_act = (T + per - 1) / per;
+    if (s >= n_act) return;
+    const int j_lo = s * per, j_hi = min(T, j_lo + per);
     const size_t seq_off = wh.seq_arr ? (size_t)wh.seq_arr[t] * wh.seq_stride : (wh.seqp ? (size_t)(*wh.seqp) * wh.seq_stride : 0);
     float* sq = smf;                   // [GRP][DH]
     float* sp = smf + GRP * DH;        // [GRP][PF_KT]
-    float* sacc = sp + GRP * PF_KT;    // [nsub][GRP][DH] partial outputs of the key subsets
+    float* sacc = sp + GRP * PF_KT;    // [nsub][GRP][DH] partial outputs of the key runs
     __shared__ float sm_m[GRP], sm_l[GRP], sm_r[GRP];
+    __shared__ unsigned sm_ticket;
     for (int i = tid; i < GRP * DH; i += PF_AT) sq[i] = qkv[(size_t)t * ld + (size_t)kvh * GRP * DH + i];
     if (tid < GRP) { sm_m[tid] = -100000000.0f; sm_l[tid] = 0.0f; }
     __syncthreads();
     const float* kbase = kc + seq_off + (size_t)kvh * cap * DH;
     const float* vbase = vc + seq_off + (size_t)kvh * cap * DH;
     const int nsub = PF_AT / DH, d = tid % DH, ksub = tid / DH;      // DH divides PF_AT (32, 64, 128, 256)
+    const int krun = PF_KT / nsub;                                   // keys of a tile per P*V thread: a multiple of 4
     float acc[GRP];
 #pragma unroll
     for (int i = 0; i < GRP; i++) acc[i] = 0.0f;
-    for (int j0 = 0; j0 < T; j0 += PF_KT) {
-        const int nj = min(PF_KT, T - j0);
-        for (int j = warp; j < nj; j += NW) {
-            float dot[GRP];
+    for (int j0 = j_lo; j0 < j_hi; j0 += PF_KT) {
+        const int nj = min(PF_KT, j_hi - j0);
+        for (int jb = warp; jb < nj; jb += 4 * NW) {
+            float v[NP];
 #pragma unroll
-            for (int i = 0; i < GRP; i++) dot[i] = 0.0f;
+            for (int i = 0; i < NP; i++) v[i] = 0.0f;
             for (int e = lane * 4; e < DH; e += 128) {
-                const float4 k4 = *reinterpret_cast<const float4*>(kbase + (size_t)(j0 + j) * DH + e);
+                float4 k4[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int j = jb + u * NW;
+                    k4[u] = j < nj ? *reinterpret_cast<const float4*>(kbase + (size_t)(j0 + j) * DH + e) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
 #pragma unroll
                 for (int i = 0; i < GRP; i++) {
                     const float4 q4 = *reinterpret_cast<const float4*>(sq + i * DH + e);
-                    dot[i] = fmaf(q4.x, k4.x, dot[i]); dot[i] = fmaf(q4.y, k4.y, dot[i]);
-                    dot[i] = fmaf(q4.z, k4.z, dot[i]); dot[i] = fmaf(q4.w, k4.w, dot[i]);
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        float a = v[u * GP + i];
+                        a = fmaf(q4.x, k4[u].x, a); a = fmaf(q4.y, k4[u].y, a); a = fmaf(q4.z, k4[u].z, a); a = fmaf(q4.w, k4[u].w, a);
+                        v[u * GP + i] = a;
+                    }
                 }
             }
+            // lanes with the exchange bit set keep the upper half of the values, the others the lower half
 #pragma unroll
-            for (int i = 0; i < GRP; i++) { const float sv = hx_warp_sum(dot[i]); if (lane == 0) sp[i * PF_KT + j] = sv * scale; }
+            for (int st = 0; st < 5; st++) {
+                const int o = 16 >> st;
+                if (st < LG) {
+                    const int h = NP >> (st + 1);
+                    const bool up = (lane & o) != 0;
+#pragma unroll
+                    for (int k = 0; k < h; k++) {
+                        const float send = up ? v[k] : v[k + h], keep = up ? v[k + h] : v[k];
+                        v[k] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+                    }
+                } else v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+            }
+            const int idx = lane >> (5 - LG), u = idx / GP, i = idx - u * GP, j = jb + u * NW;
+            if ((lane & ((1 << (5 - LG)) - 1)) == 0 && i < GRP && j < nj) sp[i * PF_KT + j] = v[0] * scale;
         }
         __syncthreads();
         for (int i = warp; i < GRP; i += NW) {
@@ -175,7 +212,10 @@ __global__ void __launch_bounds__(PF_AT) k_pf_attn(const float* __restrict__ qkv
             tm = hx_warp_max(tm);
             const float mo = sm_m[i], mn = fmaxf(mo, tm);
             float ls = 0.0f;
-            for (int j = lane; j < nj; j += 32) { const float pr = __expf(sp[i * PF_KT + j] - mn); sp[i * PF_KT + j] = pr; ls += pr; }
+            for (int j = lane; j < PF_KT; j += 32) {
+                const float pr = j < nj ? __expf(sp[i * PF_KT + j] - mn) : 0.0f;
+                sp[i * PF_KT + j] = pr; ls += pr;
+            }
             ls = hx_warp_sum(ls);
             if (lane == 0) { const float rr = __expf(mo - mn); sm_r[i] = rr; sm_l[i] = sm_l[i] * rr + ls; sm_m[i] = mn; }
         }
@@ -183,11 +223,19 @@ __global__ void __launch_bounds__(PF_AT) k_pf_attn(const float* __restrict__ qkv
         if (ksub < nsub) {
 #pragma unroll
             for (int i = 0; i < GRP; i++) acc[i] *= sm_r[i];
-            #pragma unroll 4
-            for (int j = ksub; j < nj; j += nsub) {
-                const float vv = vbase[(size_t)(j0 + j) * DH + d];
+            const int jlo = ksub * krun;
+            for (int jj = 0; jj < krun; jj += 4) {
+                const int j = jlo + jj;
+                if (j >= nj) break;
+                float vv[4];
 #pragma unroll
-                for (int i = 0; i < GRP; i++) acc[i] = fmaf(sp[i * PF_KT + j], vv, acc[i]);
+                for (int u = 0; u < 4; u++) vv[u] = j + u < nj ? vbase[(size_t)(j0 + j + u) * DH + d] : 0.0f;
+#pragma unroll
+                for (int i = 0; i < GRP; i++) {
+                    const float4 p4 = *reinterpret_cast<const float4*>(sp + i * PF_KT + j);
+                    acc[i] = fmaf(p4.x, vv[0], acc[i]); acc[i] = fmaf(p4.y, vv[1], acc[i]);
+                    acc[i] = fmaf(p4.z, vv[2], acc[i]); acc[i] = fmaf(p4.w, vv[3], acc[i]);
+                }
             }
         }
         __syncthreads();
@@ -197,12 +245,45 @@ __global__ void __launch_bounds__(PF_AT) k_pf_attn(const float* __restrict__ qkv
         for (int i = 0; i < GRP; i++) sacc[((size_t)ksub * GRP + i) * DH + d] = acc[i];
     }
     __syncthreads();
+    if (n_act == 1) {
+        for (int o = tid; o < GRP * DH; o += PF_AT) {
+            const int i = o / DH, dd = o - i * DH;
+            float v = 0.0f;
+            for (int u = 0; u < nsub; u++) v += sacc[((size_t)u * GRP + i) * DH + dd];
+            ctx[(size_t)t * ld_ctx + (size_t)(kvh * GRP + i) * DH + dd] = v / sm_l[i];
+        }
+        return;
+    }
+    // several runs: leave (sum, m, l) of this run; the last CTA of the (token, kv head) merges the runs in order
+    const int PW = GRP * (DH + 2);
+    float* mine = part + ((size_t)(t * gridDim.x + kvh) * NS + s) * PW;
     for (int o = tid; o < GRP * DH; o += PF_AT) {
         const int i = o / DH, dd = o - i * DH;
         float v = 0.0f;
         for (int u = 0; u < nsub; u++) v += sacc[((size_t)u * GRP + i) * DH + dd];
-        ctx[(size_t)t * ld_ctx + (size_t)(kvh * GRP + i) * DH + dd] = v / sm_l[i];
+        mine[o] = v;
     }
+    if (tid < GRP) { mine[GRP * DH + tid] = sm_m[tid]; mine[GRP * DH + GRP + tid] = sm_l[tid]; }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) sm_ticket = atomicAdd(tickets + t * gridDim.x + kvh, 1u);
+    __syncthreads();
+    if (sm_ticket != (unsigned)(n_act - 1)) return;
+    __threadfence();
+    const float* all = part + (size_t)(t * gridDim.x + kvh) * NS * PW;
+    for (int o = tid; o < GRP * DH; o += PF_AT) {
+        const int i = o / DH;
+        float mx = -INFINITY;
+        for (int r = 0; r < n_act; r++) mx = fmaxf(mx, __ldcg(all + (size_t)r * PW + GRP * DH + i));
+        float num = 0.0f, den = 0.0f;
+        for (int r = 0; r < n_act; r++) {
+            const float w = __expf(__ldcg(all + (size_t)r * PW + GRP * DH + i) - mx);
+            num = fmaf(w, __ldcg(all + (size_t)r * PW + o), num);
+            den = fmaf(w, __ldcg(all + (size_t)r * PW + GRP * DH + GRP + i), den);
+        }
+        ctx[(size_t)t * ld_ctx + (size_t)kvh * GRP * DH + o] = num / den;
+    }
+    if (tid == 0) tickets[t * gridDim.x + kvh] = 0u;
 }
 
 // Tensor-parallel chunk: the partial rows of a row-split linear (o_proj, down_proj) summed over the ranks and added to
@@ -363,15 +444,25 @@ void hx_pf_qkpost(float* qkv, int ld, int n_tok, HxPfWhere wh, int NH, int NKV, 
     HX_COUNT_LAUNCH(1);
 }
 
+size_t hx_pf_attn_scratch(int n_tok, int NH, int NKV, int DH) {
+    return (size_t)n_tok * NKV * PF_NS_MAX * (NH / NKV) * (DH + 2);
+}
+
 int hx_pf_attn(const float* qkv, int ld, int n_tok, HxPfWhere wh, int NH, int NKV, int DH, const float* kc, const float* vc,
-               int cap, float scale, float* ctx, int ld_ctx, cudaStream_t st) {
+               int cap, float scale, float* ctx, int ld_ctx, float* part, unsigned* tickets, cudaStream_t st) {
     const int GRP = NH / NKV;
     if (DH > 256) return hx_fail(HX_ERR_ARG, "batched prefill attention: head_dim %d > 256", DH);
     if (PF_AT % DH) return hx_fail(HX_ERR_ARG, "batched prefill attention: head_dim %d does not divide %d", DH, PF_AT);
     const size_t smem = ((size_t)GRP * DH + (size_t)GRP * PF_KT + (size_t)(PF_AT / DH) * GRP * DH) * 4;
     if (smem > 48 * 1024) return hx_fail(HX_ERR_ARG, "batched prefill attention: %zu bytes of shared memory", smem);
-    dim3 grid(NKV, n_tok);
-#define HX_PF_ATTN(G) case G: k_pf_attn<G><<<grid, PF_AT, smem, st>>>(qkv, ld, wh, NH, DH, kc, vc, cap, scale, ctx, ld_ctx); break;
+    // runs of key tiles per (token, kv head): enough CTAs for four per SM, no more than the cache has tiles
+    int ns = (4 * 148 + NKV * n_tok - 1) / (NKV * n_tok);
+    const int cap_tiles = (cap + PF_KT - 1) / PF_KT;
+    if (ns > cap_tiles) ns = cap_tiles;
+    if (ns > PF_NS_MAX) ns = PF_NS_MAX;
+    if (ns < 1 || !part || !tickets) ns = 1;
+    dim3 grid(NKV, n_tok, ns);
+#define HX_PF_ATTN(G) case G: k_pf_attn<G><<<grid, PF_AT, smem, st>>>(qkv, ld, wh, NH, DH, kc, vc, cap, scale, ctx, ld_ctx, part, tickets); break;
     switch (GRP) {
         HX_PF_ATTN(1) HX_PF_ATTN(2) HX_PF_ATTN(3) HX_PF_ATTN(4) HX_PF_ATTN(5) HX_PF_ATTN(6) HX_PF_ATTN(7) HX_PF_ATTN(8)
         default: return hx_fail(HX_ERR_ARG, "batched prefill attention: group of %d query heads per kv head not supported", GRP);

@@ -3,7 +3,7 @@
 #pragma once
 #include "hx_common.cuh"
 
-#define HX_PF_TB 16                // tokens per chunk: 16 digit columns each = the 256 columns of one MMA
+#define HX_PF_TB 64                // tokens per chunk: four groups of 16 tokens x 16 digit columns = the 256 columns of one MMA
 
 // Where the tokens of a chunk sit.  Prefill: consecutive positions of one sequence starting at *posp (device memory, so
 // that the launches of a chunk can be replayed as one CUDA graph).  Batched decode: token t is at position pos_arr[t] of
@@ -31,9 +31,12 @@ void hx_pf_qkpost(float* qkv, int ld, int n_tok, HxPfWhere wh, int NH, int NKV, 
                   float eps, const float* cosT, const float* sinT, float* kc, float* vc, int cap, cudaStream_t st);
 
 // Causal attention of a chunk over the cache: query t (position *posp + t) attends to positions 0 .. *posp + t.
-// One CTA per (kv head, token); the query heads of a kv head share its K and V rows.
+// CTAs per (kv head, token, run of key tiles); the query heads of a kv head share its K and V rows.  `part`
+// (hx_pf_attn_scratch floats) and `tickets` (n_tok * NKV words, zero between launches) carry the runs' partial
+// results; without them one CTA walks the whole context.
+size_t hx_pf_attn_scratch(int n_tok, int NH, int NKV, int DH);
 int hx_pf_attn(const float* qkv, int ld, int n_tok, HxPfWhere wh, int NH, int NKV, int DH, const float* kc, const float* vc,
-               int cap, float scale, float* ctx, int ld_ctx, cudaStream_t st);
+               int cap, float scale, float* ctx, int ld_ctx, float* part, unsigned* tickets, cudaStream_t st);
 
 // *posp += n
 void hx_pf_advance(int* posp, int n, cudaStream_t st);

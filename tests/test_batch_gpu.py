@@ -1,4 +1,4 @@
-"""Batched decode of independent sequences (chunks of 16 through the tcgen05 GEMM) against the CPU restatement run one
+"""Batched decode of independent sequences (chunks of 64 through the tcgen05 GEMM) against the CPU restatement run one
 sequence at a time."""
 import numpy as np
 import pytest
@@ -9,7 +9,7 @@ import oracle_lib as ol
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("which,nseq", [("tiny", 20), ("ragged", 5), ("wide", 16)])
+@pytest.mark.parametrize("which,nseq", [("tiny", 20), ("ragged", 5), ("wide", 16), ("tiny", 70), ("wide", 40)])
 def test_batched_decode_matches_single_sequence_checker(which, nseq, tiny_file, ragged_file, wide_file):
     path = dict(tiny=tiny_file, ragged=ragged_file, wide=wide_file)[which]
     T, G = 9, 7                                       # teacher-forced prompt positions, then free-running steps

@@ -1,4 +1,4 @@
-"""Batched prefill (chunks of 16 tokens through the tcgen05 GEMM in digit mode) against the fp32 CPU restatement
+"""Batched prefill (chunks of 64 tokens = four groups of 16 through the tcgen05 GEMM in digit mode) against the fp32 CPU restatement
 and against the token-by-token path of the same library."""
 import os
 
@@ -12,15 +12,16 @@ pytestmark = pytest.mark.gpu
 LOGIT_TOL = 2e-4
 
 
-@pytest.mark.parametrize("which,T", [("tiny", 16), ("tiny", 37), ("ragged", 37), ("wide", 50), ("ragged", 5)])
+@pytest.mark.parametrize("which,T", [("tiny", 16), ("tiny", 37), ("ragged", 37), ("wide", 50), ("ragged", 5),
+                                     ("tiny", 64), ("ragged", 70), ("wide", 150), ("tiny", 200)])
 def test_batched_prefill_matches_checker_and_token_path(which, T, tiny_file, ragged_file, wide_file):
     path = dict(tiny=tiny_file, ragged=ragged_file, wide=wide_file)[which]
-    om = ol.OracleModel(path, kv_cap=96)
+    om = ol.OracleModel(path, kv_cap=T + 32)
     ids = np.random.default_rng(100 + T).integers(0, om.NV, T).astype(np.int32)
     lo = om.prefill(ids)
     want = om.generate(ids, 24)
 
-    gm = hb.Model.load(path, kv_cap=96)
+    gm = hb.Model.load(path, kv_cap=T + 32)
     assert gm.engine().startswith("persistent-tcgen05")
     nx, lg = gm.prefill(ids, want_logits=True)
     assert np.max(np.abs(lo - lg)) < LOGIT_TOL
@@ -31,7 +32,7 @@ def test_batched_prefill_matches_checker_and_token_path(which, T, tiny_file, rag
 
     os.environ["HX_PREFILL"] = "token"                # same library, prompt fed position by position
     try:
-        tm = hb.Model.load(path, kv_cap=96)
+        tm = hb.Model.load(path, kv_cap=T + 32)
         nx2, lg2 = tm.prefill(ids, want_logits=True)
         tm.close()
     finally:
