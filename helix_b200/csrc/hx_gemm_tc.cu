@@ -28,6 +28,14 @@
 
 #define TC_WAIT_LIMIT (1u << 22)
 
+// Timing probes of a debug build (-DTC_STAMPS): CTA 0 leaves globaltimer values in tc_stamps[role][unit][event].
+#ifdef TC_STAMPS
+__device__ unsigned long long tc_stamps[3][32][8];
+#define TC_MARK(role, unit, ev) do { if (blockIdx.x == 0 && (unit) < 32) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); tc_stamps[role][unit][ev] = t_; } } while (0)
+#else
+#define TC_MARK(role, unit, ev) do { } while (0)
+#endif
+
 namespace {
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -71,25 +79,27 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 }
 
 struct TcSmem {
-    uint64_t full[HX_TC_STAGES], empty[HX_TC_STAGES], accum, acc_free, bfull[HX_TC_RES_CELLS];
+    uint64_t full[HX_TC_STAGES], empty[HX_TC_STAGES], accum, acc_free, part_done, tk_ready, bfull[HX_TC_RES_CELLS];
     uint32_t tmem_base;
     unsigned ticket[2];
     volatile int abort_flag;
 };
-#define TC_THREADS 320          // warp 0 loads, warp 1 issues the MMAs, warps 2-9 read the accumulator
+#define TC_THREADS 352          // warp 0 loads, warp 1 issues the MMAs, warps 2-9 read the accumulator, warp 10 draws the tickets
 #define TC_HDR 1536u            // header + the chunk of unit scales
 #define TC_SWI (HX_TC_MAX_TOK * 128 * 4)      // SwiGLU exchange: [token][row of the tile]
 
-__device__ __forceinline__ void tc_ld16(uint32_t (&r)[16], uint32_t taddr) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+__device__ __forceinline__ void tc_ld32(uint32_t (&r)[32], uint32_t taddr) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                   "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr));
 }
-__device__ __forceinline__ float tc_digits(const uint32_t (&r)[16]) {       // sum_j 4^-j r[j]
+template <int OFF, int N>
+__device__ __forceinline__ float tc_digits(const uint32_t (&r)[N]) {       // sum_j 4^-j r[OFF + j]
     float v = 0.0f;
 #pragma unroll
-    for (int j = 15; j >= 0; j--) v = fmaf(v, 0.25f, __uint_as_float(r[j]));
+    for (int j = 15; j >= 0; j--) v = fmaf(v, 0.25f, __uint_as_float(r[OFF + j]));
     return v;
 }
 
@@ -101,8 +111,9 @@ __device__ __forceinline__ float tc_digits(const uint32_t (&r)[16]) {       // s
 //
 // Work units: (128-row tile, K piece, group of 16 tokens).  K is cut into pieces of whole 256-column cells (digit
 // mode); each piece recombines its own digits and leaves them in `partial`, and the last piece of a (tile, group)
-// to finish (a ticket) adds the pieces in K order and applies the epilogue.  The ticket of a unit is drawn after
-// its partial sums are stored and looked at one unit later, so its round trip is hidden by the next unit's MMAs.
+// to finish (a ticket) adds the pieces in K order and applies the epilogue.  The ticket of a unit is drawn by a
+// warp of its own after the unit's partial sums are stored and looked at one unit later, so neither its round trip
+// nor the wait for the stores holds up an epilogue warp.
 // With resident B the grid is a multiple of pieces x groups: a CTA keeps one (piece, group) and loads its B cells once,
 // and the CTAs of the groups walk through the same tiles together, so a weight cell comes from DRAM once.
 __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant__ HxGemmTC g) {
@@ -133,7 +144,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
     if (tid == 0) {
         for (int i = 0; i < HX_TC_STAGES; i++) { mb_init(&S.full[i], 1); mb_init(&S.empty[i], 1); }
         for (int i = 0; i < HX_TC_RES_CELLS; i++) mb_init(&S.bfull[i], 1);
-        mb_init(&S.accum, 1); mb_init(&S.acc_free, 8);
+        mb_init(&S.accum, 1); mb_init(&S.acc_free, 8); mb_init(&S.part_done, 8); mb_init(&S.tk_ready, 1);
         S.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -164,8 +175,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                     bulk_load(bres + (size_t)(c - c_lo) * b_cell_bytes, g.b + (size_t)c * b_src_cell + (size_t)grp * 32768u, b_cell_bytes, &S.bfull[c - c_lo]);
                 }
             }
-            for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x) {
+            int lu = 0;
+            for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x, lu++) {
                 TC_UNIT(u);
+                TC_MARK(0, lu, 0);
                 for (int ks0 = ks_lo; ks0 < ks_hi; ks0 += Sk, git++) {
                     const uint32_t slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
                     if (round > 0 && !mb_wait(&S.empty[slot], (round - 1) & 1, &S.abort_flag)) { ok = false; break; }
@@ -185,6 +198,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | (8u << 24);
             uint32_t git = 0;
             bool ok = true;
+            const uint64_t dA0 = smem_desc(s_u32(ring), 16, 1024, SW128), dS0 = smem_desc(s_u32(ring) + 16384, 16, 128);
+            const uint64_t dB0 = smem_desc(s_u32(bres), 16, 1024, SW128);
             if (g.digit_mode) {
                 // unit scales (E4M3 1.0) for every digit column: sixteen TMEM columns cover any N up to 256
                 for (int c = 0; c < 4; c++) tc_cp_sf(tmem + col_sfb + c * 4, smem_desc(s_u32(smem_raw + 1024), 16, 128));
@@ -193,18 +208,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x, unit_iter++) {
                 TC_UNIT(u);
                 (void)mt;
+                TC_MARK(1, unit_iter, 0);
                 if (unit_iter > 0) {      // the epilogue has read the previous unit's accumulator out
                     if (!mb_wait(&S.acc_free, (uint32_t)(unit_iter - 1) & 1u, &S.abort_flag)) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
+                TC_MARK(1, unit_iter, 1);
                 for (int ks0 = ks_lo; ks0 < ks_hi; ks0 += Sk, git++) {
                     const uint32_t slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
                     if (BR && unit_iter == 0 && !mb_wait(&S.bfull[(ks0 - ks_lo) / 4], 0, &S.abort_flag)) { ok = false; break; }
                     if (!mb_wait(&S.full[slot], round & 1, &S.abort_flag)) { ok = false; break; }
+                    if (ks0 == ks_lo) TC_MARK(1, unit_iter, 2);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const int nk = min(Sk, ks_hi - ks0);
                     const uint32_t sa = s_u32(ring + (size_t)slot * stage_bytes);
                     const uint32_t sb = BR ? s_u32(bres) + (uint32_t)((ks0 - ks_lo) / 4) * b_cell_bytes : sa + (uint32_t)Sk * a_cell;
+                    if (BR && nk == 4) {
+                        // one cell of A against one resident cell of B: the four descriptors differ by constants (the
+                        // address field counts 16-byte units), so the issuing thread spends a few instructions per MMA
+                        const uint64_t dA = dA0 + (uint64_t)((slot * stage_bytes) >> 4), dS = dS0 + (uint64_t)((slot * stage_bytes) >> 4);
+                        const uint64_t dB = dB0 + (uint64_t)(((uint32_t)((ks0 - ks_lo) / 4) * b_cell_bytes) >> 4);
+                        const uint32_t ta = tmem + col_sfa + slot * HX_TC_MAX_SK * 4;
+#pragma unroll
+                        for (int k = 0; k < 4; k++) tc_cp_sf(ta + k * 4, dS + (uint64_t)(k * 32));
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            tc_mma(tmem, dA + (uint64_t)(k * 2), dB + (uint64_t)(k * 2), idesc, ta + k * 4, tmem + col_sfb, (k > 0 || ks0 > ks_lo) ? 1u : 0u);
+                    } else
                     for (int k = 0; k < nk; k++) {
                         const uint32_t ta = tmem + col_sfa + (slot * HX_TC_MAX_SK + k) * 4;
                         const uint32_t tb = tmem + col_sfb + (slot * HX_TC_MAX_SK + k) * 4;
@@ -218,9 +248,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                     tc_commit(&S.empty[slot]);          // the slot is free once these MMAs have read it
                 }
                 if (ok) tc_commit(&S.accum);            // accumulator complete
+                TC_MARK(1, unit_iter, 3);
             }
         }
-    } else {
+    } else if (warp < 10) {
         // ------------------------------ epilogue: TMEM -> registers -> global ------------------------------
         const int ew = warp - 2, sub = warp & 3, half = ew >> 2;      // TMEM lanes 32*sub .. 32*sub+31; tokens 8*half .. 8*half+7 of the group
         const int rl = sub * 32 + lane, etid = tid - 64;
@@ -228,7 +259,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
         constexpr int TH = HX_TC_MAX_TOK / 2;
         const int ntok = NB / 16, tok0 = grp * HX_TC_MAX_TOK + half * TH;      // this thread's tokens: tok0 .. tok0+TH-1 of the launch
         const int tleft = ntok - half * TH;                                     // ... of which tleft exist
-        const int ptok = G * HX_TC_MAX_TOK;                                     // token slots of a piece in `partial`
+        constexpr int ptok = HX_TC_MAX_GROUPS * HX_TC_MAX_TOK;                  // token slots of a piece in `partial` (a constant: the loads of a merge differ by immediates)
         float cs[TH];
 #pragma unroll
         for (int t = 0; t < TH; t++) cs[t] = (g.digit_mode && t < tleft) ? __ldg(g.col_scale + tok0 + t) : 0.0f;
@@ -270,30 +301,58 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             for (int t = 0; t < TH; t++)
                 prev[t] = (g.resid && !g.swiglu && t < tleft && row < g.rows) ? __ldcg(g.out + (size_t)(tok0 + t) * g.ld_out + row) : 0.0f;
         };
-        // the ticket drawn for tile mtf said that its other pieces are done: add all pieces in K order and finish the tile
+        // the ticket drawn for tile mtf said that its other pieces are done: add all pieces in K order and finish the tile.
+        // Eight values per thread, the loads of four pieces in flight together.  SwiGLU tiles: thread (row r of 64, half of
+        // the lanes' quarter pair) takes four tokens and fetches the gate row r and the up row r + 64 of each, so no
+        // exchange between warps is needed.
         auto merge = [&](int mtf) {
+            if (etid == 0) g.tickets[mtf * G + grp] = 0u;
+            const bool sw = g.swiglu != 0;
+            const int r0 = sw ? (rl & 63) : rl, tb = sw ? (rl >> 6) * (TH / 2) : 0;
+            const float* part = g.partial + ((size_t)mtf * P * ptok + tok0 + tb) * 128 + r0;      // [piece][token][row in tile]
             float val[TH], prev[TH];
-            load_prev(mtf, prev);
-            const float* part = g.partial + ((size_t)mtf * P * ptok + tok0) * 128 + rl;      // [piece][token][row in tile]
+            if (!sw) load_prev(mtf, prev);
 #pragma unroll
-            for (int t = 0; t < TH; t++) val[t] = 0.0f;
-            for (int q = 0; q < P; q++) {
+            for (int i = 0; i < TH; i++) val[i] = 0.0f;
+            for (int q0 = 0; q0 < P; q0 += 4) {
+                float pv[4][TH];
 #pragma unroll
-                for (int t = 0; t < TH; t++)
-                    if (t < tleft) val[t] += __ldcg(part + ((size_t)q * ptok + t) * 128);
+                for (int qq = 0; qq < 4; qq++)
+#pragma unroll
+                    for (int i = 0; i < TH; i++) {
+                        const int tt = sw ? tb + (i & 3) : i;                                   // token of value i
+                        const int off = sw ? (i & 3) * 128 + (i >> 2) * 64 : i * 128;           // its place from `part`
+                        pv[qq][i] = (q0 + qq < P && tt < tleft) ? __ldcg(part + (size_t)(q0 + qq) * ptok * 128 + off) : 0.0f;
+                    }
+#pragma unroll
+                for (int qq = 0; qq < 4; qq++)
+                    if (q0 + qq < P) {
+#pragma unroll
+                        for (int i = 0; i < TH; i++) val[i] += pv[qq][i];
+                    }
             }
-            if (etid == 0 && !dead) g.tickets[mtf * G + grp] = 0u;
-            finalize(mtf, val, prev);
+            if (!sw) { finalize(mtf, val, prev); return; }
+            if (mtf * 64 + r0 >= g.rows) return;
+#pragma unroll
+            for (int i = 0; i < TH / 2; i++) {
+                if (tb + i >= tleft) break;
+                const float gt = val[i] * g.ts[0], up = val[i + TH / 2] * g.ts[1];
+                const float sgn = gt < 0.0f ? -1.0f : 1.0f;
+                const float ex = __expf(-(sgn * gt));
+                const float th = sgn * ((1.0f - ex) / (1.0f + ex));
+                g.out[(size_t)(tok0 + tb + i) * g.ld_out + mtf * 64 + r0] = gt * (0.5f * (1.0f + th)) * up;
+            }
         };
         int unit_iter = 0, pend_mt = -1;
-        unsigned pend_ticket = 0;                        // meaningful in the thread that draws the tickets
         for (int u = blockIdx.x; u < nunits; u += gridDim.x, unit_iter++) {
             TC_UNIT(u);
             (void)ks_lo; (void)ks_hi;
             const int row = mt * 128 + rl;
             float prev[TH];
             if (g.digit_mode && P == 1) load_prev(mt, prev);      // fetched before the accumulator is ready
+            if (etid == 0) TC_MARK(2, unit_iter, 0);
             if (dead || !mb_wait(&S.accum, (uint32_t)unit_iter & 1u, &S.abort_flag)) dead = true;
+            if (etid == 0) TC_MARK(2, unit_iter, 1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tlane = tmem + ((uint32_t)(sub * 32) << 16);
             if (!g.digit_mode) {
@@ -315,41 +374,62 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             // ---- digit mode: this thread's row and tokens: sixteen digit accumulators each -> one value
             float val[TH];
             {
-                uint32_t ra[16], rb[16];
+                // two tokens per load; columns past the group's last token belong to the accumulator's allocation all the
+                // same, and what is read there is dropped
                 const uint32_t tcol = tlane + (uint32_t)(half * TH * 16);
                 const int tleft = dead ? 0 : ntok - half * TH;       // (shadows the outer count: nothing is read after a failed wait)
-                if (0 < tleft) tc_ld16(ra, tcol);
+                uint32_t ra[32], rb[32];
 #pragma unroll
-                for (int t = 0; t < TH; t += 2) {
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (t + 1 < tleft) tc_ld16(rb, tcol + (uint32_t)((t + 1) * 16));
-                    val[t] = t < tleft ? tc_digits(ra) * cs[t] : 0.0f;
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (t + 2 < TH && t + 2 < tleft) tc_ld16(ra, tcol + (uint32_t)((t + 2) * 16));
-                    val[t + 1] = t + 1 < tleft ? tc_digits(rb) * cs[t + 1] : 0.0f;
+                for (int t = 0; t < TH; t += 4) {      // two loads in flight per wait
+                    if (t < tleft) {
+                        tc_ld32(ra, tcol + (uint32_t)(t * 16));
+                        tc_ld32(rb, tcol + (uint32_t)((t + 2) * 16));
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    }
+                    val[t] = t < tleft ? tc_digits<0>(ra) * cs[t] : 0.0f;
+                    val[t + 1] = t + 1 < tleft ? tc_digits<16>(ra) * cs[t + 1] : 0.0f;
+                    val[t + 2] = t + 2 < tleft ? tc_digits<0>(rb) * cs[t + 2] : 0.0f;
+                    val[t + 3] = t + 3 < tleft ? tc_digits<16>(rb) * cs[t + 3] : 0.0f;
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mb_arrive(&S.acc_free);       // the issuer may overwrite the accumulator
+            if (etid == 0) TC_MARK(2, unit_iter, 2);
             if (P == 1) { finalize(mt, val, prev); continue; }
             // K pieces: leave this piece's values, look at the ticket of the previous unit, draw this unit's
             float* part = g.partial + (((size_t)mt * P + piece) * ptok + tok0) * 128 + rl;
 #pragma unroll
             for (int t = 0; t < TH; t++)
                 if (t < tleft && !dead) part[(size_t)t * 128] = val[t];
-            if (etid == 0 && pend_mt >= 0) S.ticket[unit_iter & 1] = pend_ticket;
-            asm volatile("bar.sync 3, 256;" ::: "memory");
-            const bool fin = pend_mt >= 0 && S.ticket[unit_iter & 1] == (unsigned)(P - 1);
-            if (etid == 0 && !dead)
-                asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(pend_ticket) : "l"(g.tickets + mt * G + grp) : "memory");
-            if (fin) merge(pend_mt);
+            __syncwarp();
+            if (lane == 0) mb_arrive(&S.part_done);      // this warp's partial sums are written: the ticket may be drawn
+            if (etid == 0) TC_MARK(2, unit_iter, 3);
+            if (pend_mt >= 0) {                          // the previous unit's ticket has long arrived
+                if (dead || !mb_wait(&S.tk_ready, (uint32_t)(unit_iter - 1) & 1u, &S.abort_flag)) dead = true;
+                const bool fin = !dead && S.ticket[(unit_iter - 1) & 1] == (unsigned)(P - 1);
+                if (fin) merge(pend_mt);
+                if (etid == 0) TC_MARK(2, unit_iter, 4 + (fin ? 1 : 0));
+            }
             pend_mt = mt;
         }
         if (pend_mt >= 0) {      // the last unit's ticket
-            if (etid == 0) S.ticket[unit_iter & 1] = pend_ticket;
-            asm volatile("bar.sync 3, 256;" ::: "memory");
-            if (S.ticket[unit_iter & 1] == (unsigned)(P - 1)) merge(pend_mt);
+            if (dead || !mb_wait(&S.tk_ready, (uint32_t)(unit_iter - 1) & 1u, &S.abort_flag)) dead = true;
+            if (!dead && S.ticket[(unit_iter - 1) & 1] == (unsigned)(P - 1)) merge(pend_mt);
+        }
+    } else if (lane == 0 && P > 1) {
+        // ------------------------------ tickets ------------------------------
+        // One atomic per unit, after the epilogue warps have stored the unit's partial sums: the count of the (tile, group)'s
+        // pieces that are done.  The release of the atomic waits for those stores, which is why no epilogue warp issues it.
+        int unit_iter = 0;
+        for (int u = blockIdx.x; u < nunits; u += gridDim.x, unit_iter++) {
+            TC_UNIT(u);
+            (void)piece; (void)ks_lo; (void)ks_hi;
+            if (!mb_wait(&S.part_done, (uint32_t)unit_iter & 1u, &S.abort_flag)) break;
+            unsigned old;
+            asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(g.tickets + mt * G + grp) : "memory");
+            S.ticket[unit_iter & 1] = old;
+            mb_arrive(&S.tk_ready);
         }
     }
 #undef TC_UNIT

@@ -3,8 +3,12 @@
 #include "hx_common.cuh"
 
 #define HX_T128_CELL 18432         // one (128-row tile, 256-column group) cell of A: 16384 B codes + 4 x 512 B scales
+#ifndef HX_TC_STAGES
 #define HX_TC_STAGES 4
+#endif
+#ifndef HX_TC_MAX_SK
 #define HX_TC_MAX_SK 8             // 64-column steps per ring stage (4 or 8)
+#endif
 #define HX_TC_RES_CELLS 4          // B cells of 256 columns x 256 digit columns that fit beside the ring of A cells
 #define HX_TC_MAX_TOK 16           // tokens per work unit in digit mode (16 digit columns each = the 256 columns of an MMA)
 #define HX_TC_MAX_GROUPS 4         // groups of HX_TC_MAX_TOK tokens per launch (resident B)
@@ -26,7 +30,7 @@ struct HxGemmTC {
     int pair64;                    // 1: ts[0] for rows with (row % 128) < 64, ts[1] for the others (gate/up tiles)
     int swiglu;                    // 1: tiles hold 64 gate + 64 up rows; out[t][tile * 64 + r] = silu(gate_r) * up_r, rows = hidden size
     int ksplit;                    // > 1: K pieces per tile (digit mode), merged in K order by the last piece to finish
-    float* partial;                // [ntiles][ksplit][groups * HX_TC_MAX_TOK][128] partial sums of the pieces (groups = ceil(ncols / 256))
+    float* partial;                // [ntiles][ksplit][HX_TC_MAX_GROUPS * HX_TC_MAX_TOK][128] partial sums of the pieces
     unsigned* tickets;             // [ntiles][groups], zero between launches
     int b_resident;                // digit mode: keep the B cells of a CTA's K piece in shared memory (grid is a multiple of ksplit;
                                    // a piece of at most HX_TC_RES_CELLS cells at 256 columns)

@@ -1332,7 +1332,7 @@ static int pf_enqueue_layers(hx_model* m, int n, const int* ids, HxPfWhere wh) {
         float* kc = m->kc + (size_t)L * c.n_kv_heads * cap * DH; float* vc = m->vc + (size_t)L * c.n_kv_heads * cap * DH;
         if ((rc = pf_linear(m, ly.qkv, m->pf_x, DM, n, 0, ly.in_g, m->pf_qkv, ldq, ly.qkv.N, 0, 0))) return rc;
         hx_pf_qkpost(m->pf_qkv, ldq, n, wh, c.n_heads, c.n_kv_heads, DH, ly.qn_g, ly.kn_g, c.norm_eps, m->cosT, m->sinT, kc, vc, cap, m->st);
-        if ((rc = hx_pf_attn(m->pf_qkv, ldq, n, wh, c.n_heads, c.n_kv_heads, DH, kc, vc, cap, att_scale, m->pf_ctx, QD, m->pf_att_part, m->pf_att_tickets, m->st))) return rc;
+        if ((rc = hx_pf_attn(m->pf_qkv, ldq, n, wh, c.n_heads, c.n_kv_heads, DH, kc, vc, cap, att_scale, m->pf_ctx, QD, m->pf_att_part, m->pf_att_tickets, m->pf_err, m->st))) return rc;
         if (m->tp_world > 1) {
             if ((rc = pf_linear(m, ly.o, m->pf_ctx, QD, n, 0, nullptr, m->pf_part, DM, ly.o.N, 0, 0))) return rc;
             if ((rc = pf_tp_reduce(m, n))) return rc;

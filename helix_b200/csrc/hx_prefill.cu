@@ -10,6 +10,7 @@
 #include "hx_prefill.cuh"
 #include "hx_kernels.cuh"
 #include <math.h>
+#include <atomic>
 
 namespace {
 
@@ -123,167 +124,247 @@ __global__ void __launch_bounds__(256) k_pf_qkpost(float* __restrict__ qkv, int 
     }
 }
 
-// grid (NKV, n_tok, NS), PF_AT threads: CTA (kv head, token, s) covers the s-th run of whole key tiles of the token's
-// context (NS runs at most, fewer for a short context; CTAs without a run leave at once).  Online softmax over tiles
-// of PF_KT cached positions (m seeded -1e8 like fused_decode_attn_kernel.hx:74-102), so shared memory does not grow
-// with the context.  Scores: a warp takes four keys at a time, the 4 x GRP dot products are reduced across the lanes
-// together (each exchange halves the values a lane carries).  P*V: thread (dimension, run of keys inside the tile);
-// the runs are added up through shared memory at the end.  With more than one active run per (token, kv head) each
-// CTA leaves (sum, m, l) in `part`, and the last one to finish (a ticket per (token, kv head)) merges them.
-#define PF_KT 128
+// ---- causal attention of a chunk over the cache ------------------------------------------------------------------
+// grid (NKV, groups of TG tokens, NS), PF_AT threads: CTA (kv head, token group, s) covers the s-th run of whole key
+// tiles of the group's context (NS runs at most, fewer for a short context; CTAs without a run leave at once).
+// The K and V rows of a tile are contiguous in the cache, so one thread brings each tile into a ring of PF_ST
+// shared-memory stages with two bulk copies (cp.async.bulk, completion on an mbarrier), PF_ST - 1 tiles ahead of the
+// arithmetic: the loads of a CTA never wait for its softmax.  In a prefill chunk (one sequence, consecutive positions)
+// the TG = 4 tokens of a group share every tile; in batched decode every token has a cache of its own (TG = 1).
+// Per token: online softmax over the tiles (m seeded -1e8 like fused_decode_attn_kernel.hx:74-102).  Scores: a warp
+// takes four keys at a time against every (token, head) query, the 4 x GRP dot products of a token are reduced across
+// the lanes together (each exchange halves the values a lane carries).  Softmax step: a warp per (token, head).
+// P*V: thread (dimension, run of keys inside the tile), a V value serving all tokens and heads; the runs are added
+// up through shared memory at the end.  With more than one active run per (token group, kv head) each CTA leaves (sum, m, l) in
+// `part`, and the last one to finish (a ticket per (token group, kv head)) merges them.  Waits are bounded: after a
+// wait that ran out the CTA keeps to its barriers, writes nothing and raises *err.
 #define PF_AT 512
+#define PF_ST 3
 #define PF_NS_MAX 16
-template <int GRP>
-__global__ void __launch_bounds__(PF_AT) k_pf_attn(const float* __restrict__ qkv, int ld, HxPfWhere wh, int NH, int DH,
+#define PF_TILE_BYTES 32768          // K rows of a tile (and as many V rows)
+#define PF_AT_WAIT (1u << 22)
+__device__ __forceinline__ uint32_t pf_s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool pf_mb_wait(uint64_t* b, uint32_t parity) {
+    for (uint32_t i = 0; i < PF_AT_WAIT; i++) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(pf_s32(b)), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+template <int GRP, int TG>
+__global__ void __launch_bounds__(PF_AT) k_pf_attn(const float* __restrict__ qkv, int ld, HxPfWhere wh, int n_tok, int NH, int DH,
                                                     const float* __restrict__ kc, const float* __restrict__ vc, int cap, float scale,
-                                                    float* __restrict__ ctx, int ld_ctx, float* __restrict__ part, unsigned* __restrict__ tickets) {
-    extern __shared__ float smf[];
-    const int kvh = blockIdx.x, t = blockIdx.y, s = blockIdx.z, NS = gridDim.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+                                                    float* __restrict__ ctx, int ld_ctx, float* __restrict__ part, unsigned* __restrict__ tickets, int* err) {
+    extern __shared__ __align__(128) float smf[];
+    const int kvh = blockIdx.x, t0 = blockIdx.y * TG, s = blockIdx.z, NS = gridDim.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int NW = PF_AT / 32;
     constexpr int GP = GRP <= 1 ? 1 : (GRP <= 2 ? 2 : (GRP <= 4 ? 4 : 8));      // GRP rounded up to a power of two
     constexpr int NP = 4 * GP;                                                   // values reduced together (4 keys x GP heads)
     constexpr int LG = NP == 4 ? 2 : (NP == 8 ? 3 : (NP == 16 ? 4 : 5));
-    const int T = (wh.pos_arr ? wh.pos_arr[t] : *wh.posp + t) + 1;
-    const int tiles = (T + PF_KT - 1) / PF_KT, per = ((tiles + NS - 1) / NS) * PF_KT;      // keys per run: whole tiles
-    const int n_act = (T + per - 1) / per;
+    const int KT = min(128, PF_TILE_BYTES / (DH * 4));                           // keys per tile (32 .. 128, a multiple of 32)
+    const int ntk = min(TG, n_tok - t0);                                         // tokens of this group
+    const int pos0 = wh.pos_arr ? wh.pos_arr[t0] : *wh.posp + t0;                // TG > 1 only with consecutive positions
+    const int Tmax = pos0 + ntk;                                                 // context of the group's last token
+    const int tiles = (Tmax + KT - 1) / KT, per = ((tiles + NS - 1) / NS) * KT;  // keys per run: whole tiles
+    const int n_act = (Tmax + per - 1) / per;
     if (s >= n_act) return;
-    const int j_lo = s * per, j_hi = min(T, j_lo + per);
-    const size_t seq_off = wh.seq_arr ? (size_t)wh.seq_arr[t] * wh.seq_stride : (wh.seqp ? (size_t)(*wh.seqp) * wh.seq_stride : 0);
-    float* sq = smf;                   // [GRP][DH]
-    float* sp = smf + GRP * DH;        // [GRP][PF_KT]
-    float* sacc = sp + GRP * PF_KT;    // [nsub][GRP][DH] partial outputs of the key runs
-    __shared__ float sm_m[GRP], sm_l[GRP], sm_r[GRP];
+    const int j_lo = s * per, j_hi = min(Tmax, j_lo + per);
+    const size_t seq_off = wh.seq_arr ? (size_t)wh.seq_arr[t0] * wh.seq_stride : (wh.seqp ? (size_t)(*wh.seqp) * wh.seq_stride : 0);
+    // shared memory: ring [PF_ST][K tile | V tile], then q, p and the P*V partial outputs
+    float* ringf = smf;
+    const int stage_f = 2 * (PF_TILE_BYTES / 4);
+    float* sq = smf + PF_ST * stage_f;         // [TG][GRP][DH]
+    float* sp = sq + TG * GRP * DH;            // [TG][GRP][128]
+    float* sacc = sp + TG * GRP * 128;              // [nsub][GRP][DH] partial outputs of the key runs inside a tile
+    __shared__ float sm_m[TG][GRP], sm_l[TG][GRP], sm_r[TG][GRP];
     __shared__ unsigned sm_ticket;
-    for (int i = tid; i < GRP * DH; i += PF_AT) sq[i] = qkv[(size_t)t * ld + (size_t)kvh * GRP * DH + i];
-    if (tid < GRP) { sm_m[tid] = -100000000.0f; sm_l[tid] = 0.0f; }
+    __shared__ int sm_abort;
+    __shared__ __align__(8) uint64_t full[PF_ST];
+    for (int i = tid; i < ntk * GRP * DH; i += PF_AT) {
+        const int tk = i / (GRP * DH), r = i - tk * GRP * DH;
+        sq[i] = qkv[(size_t)(t0 + tk) * ld + (size_t)kvh * GRP * DH + r];
+    }
+    if (tid < TG * GRP) { sm_m[tid / GRP][tid % GRP] = -100000000.0f; sm_l[tid / GRP][tid % GRP] = 0.0f; }
+    if (tid == 0) {
+        sm_abort = 0;
+        for (int i = 0; i < PF_ST; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(pf_s32(&full[i])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     __syncthreads();
     const float* kbase = kc + seq_off + (size_t)kvh * cap * DH;
     const float* vbase = vc + seq_off + (size_t)kvh * cap * DH;
+    const int ntile = (j_hi - j_lo + KT - 1) / KT;
+    auto issue = [&](int it) {       // thread 0: tile `it` of this run into its stage
+        const int j0 = j_lo + it * KT, nj = min(KT, j_hi - j0);
+        const uint32_t bytes = (uint32_t)nj * DH * 4;
+        float* st = ringf + (size_t)(it % PF_ST) * stage_f;
+        uint64_t* bar = &full[it % PF_ST];
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(pf_s32(bar)), "r"(2 * bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     :: "r"(pf_s32(st)), "l"(kbase + (size_t)j0 * DH), "r"(bytes), "r"(pf_s32(bar)) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     :: "r"(pf_s32(st + PF_TILE_BYTES / 4)), "l"(vbase + (size_t)j0 * DH), "r"(bytes), "r"(pf_s32(bar)) : "memory");
+    };
+    if (tid == 0) for (int it = 0; it < PF_ST - 1 && it < ntile; it++) issue(it);
     const int nsub = PF_AT / DH, d = tid % DH, ksub = tid / DH;      // DH divides PF_AT (32, 64, 128, 256)
-    const int krun = PF_KT / nsub;                                   // keys of a tile per P*V thread: a multiple of 4
-    float acc[GRP];
+    const int krun = KT / nsub;                                      // keys of a tile per P*V thread: a multiple of 4
+    float acc[TG][GRP];
 #pragma unroll
-    for (int i = 0; i < GRP; i++) acc[i] = 0.0f;
-    for (int j0 = j_lo; j0 < j_hi; j0 += PF_KT) {
-        const int nj = min(PF_KT, j_hi - j0);
-        for (int jb = warp; jb < nj; jb += 4 * NW) {
-            float v[NP];
+    for (int tk = 0; tk < TG; tk++)
 #pragma unroll
-            for (int i = 0; i < NP; i++) v[i] = 0.0f;
+        for (int i = 0; i < GRP; i++) acc[tk][i] = 0.0f;
+    for (int it = 0; it < ntile; it++) {
+        const int j0 = j_lo + it * KT, njt = min(KT, j_hi - j0);
+        // every thread is past tile it - 1 (the barrier that ended it), so its stage may be refilled
+        if (tid == 0 && it + PF_ST - 1 < ntile) issue(it + PF_ST - 1);
+        if (!pf_mb_wait(&full[it % PF_ST], (uint32_t)(it / PF_ST) & 1u)) sm_abort = 1;
+        const float* kt = ringf + (size_t)(it % PF_ST) * stage_f;
+        const float* vt = kt + PF_TILE_BYTES / 4;
+        const int njm = min(njt, pos0 + ntk - j0);          // keys of the tile the group's last token may see (> 0)
+        // ---- scores of all tokens: a warp takes four keys at a time against every (token, head) query
+        for (int jb = warp; jb < njm; jb += 4 * NW) {
+            float v[TG][NP];
+#pragma unroll
+            for (int tk = 0; tk < TG; tk++)
+#pragma unroll
+                for (int i = 0; i < NP; i++) v[tk][i] = 0.0f;
             for (int e = lane * 4; e < DH; e += 128) {
                 float4 k4[4];
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const int j = jb + u * NW;
-                    k4[u] = j < nj ? *reinterpret_cast<const float4*>(kbase + (size_t)(j0 + j) * DH + e) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    k4[u] = j < njm ? *reinterpret_cast<const float4*>(kt + (size_t)j * DH + e) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 }
 #pragma unroll
-                for (int i = 0; i < GRP; i++) {
-                    const float4 q4 = *reinterpret_cast<const float4*>(sq + i * DH + e);
+                for (int tk = 0; tk < TG; tk++) {
+                    if (tk >= ntk) break;
 #pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        float a = v[u * GP + i];
-                        a = fmaf(q4.x, k4[u].x, a); a = fmaf(q4.y, k4[u].y, a); a = fmaf(q4.z, k4[u].z, a); a = fmaf(q4.w, k4[u].w, a);
-                        v[u * GP + i] = a;
+                    for (int i = 0; i < GRP; i++) {
+                        const float4 q4 = *reinterpret_cast<const float4*>(sq + (tk * GRP + i) * DH + e);
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            float a = v[tk][u * GP + i];
+                            a = fmaf(q4.x, k4[u].x, a); a = fmaf(q4.y, k4[u].y, a); a = fmaf(q4.z, k4[u].z, a); a = fmaf(q4.w, k4[u].w, a);
+                            v[tk][u * GP + i] = a;
+                        }
                     }
                 }
             }
-            // lanes with the exchange bit set keep the upper half of the values, the others the lower half
 #pragma unroll
-            for (int st = 0; st < 5; st++) {
-                const int o = 16 >> st;
-                if (st < LG) {
-                    const int h = NP >> (st + 1);
-                    const bool up = (lane & o) != 0;
+            for (int tk = 0; tk < TG; tk++) {
+                if (tk >= ntk) break;
+                // lanes with the exchange bit set keep the upper half of the values, the others the lower half
 #pragma unroll
-                    for (int k = 0; k < h; k++) {
-                        const float send = up ? v[k] : v[k + h], keep = up ? v[k + h] : v[k];
-                        v[k] = keep + __shfl_xor_sync(0xffffffffu, send, o);
-                    }
-                } else v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+                for (int st = 0; st < 5; st++) {
+                    const int o = 16 >> st;
+                    if (st < LG) {
+                        const int h = NP >> (st + 1);
+                        const bool up = (lane & o) != 0;
+#pragma unroll
+                        for (int k = 0; k < h; k++) {
+                            const float send = up ? v[tk][k] : v[tk][k + h], keep = up ? v[tk][k + h] : v[tk][k];
+                            v[tk][k] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+                        }
+                    } else v[tk][0] += __shfl_xor_sync(0xffffffffu, v[tk][0], o);
+                }
+                const int idx = lane >> (5 - LG), u = idx / GP, i = idx - u * GP, j = jb + u * NW;
+                if ((lane & ((1 << (5 - LG)) - 1)) == 0 && i < GRP && j < njm) sp[(tk * GRP + i) * 128 + j] = v[tk][0] * scale;
             }
-            const int idx = lane >> (5 - LG), u = idx / GP, i = idx - u * GP, j = jb + u * NW;
-            if ((lane & ((1 << (5 - LG)) - 1)) == 0 && i < GRP && j < nj) sp[i * PF_KT + j] = v[0] * scale;
         }
         __syncthreads();
-        for (int i = warp; i < GRP; i += NW) {
+        // ---- softmax step of every (token, head) row: a warp per row; keys a token may not see count as absent
+        for (int r = warp; r < ntk * GRP; r += NW) {
+            const int tk = r / GRP, i = r - tk * GRP;
+            const int nj = max(0, min(njt, pos0 + tk + 1 - j0));
             float tm = -INFINITY;
-            for (int j = lane; j < nj; j += 32) tm = fmaxf(tm, sp[i * PF_KT + j]);
+            for (int j = lane; j < nj; j += 32) tm = fmaxf(tm, sp[r * 128 + j]);
             tm = hx_warp_max(tm);
-            const float mo = sm_m[i], mn = fmaxf(mo, tm);
+            const float mo = sm_m[tk][i], mn = fmaxf(mo, tm);
             float ls = 0.0f;
-            for (int j = lane; j < PF_KT; j += 32) {
-                const float pr = j < nj ? __expf(sp[i * PF_KT + j] - mn) : 0.0f;
-                sp[i * PF_KT + j] = pr; ls += pr;
+            for (int j = lane; j < KT; j += 32) {
+                const float pr = j < nj ? __expf(sp[r * 128 + j] - mn) : 0.0f;
+                sp[r * 128 + j] = pr; ls += pr;
             }
             ls = hx_warp_sum(ls);
-            if (lane == 0) { const float rr = __expf(mo - mn); sm_r[i] = rr; sm_l[i] = sm_l[i] * rr + ls; sm_m[i] = mn; }
+            if (lane == 0) { const float rr = __expf(mo - mn); sm_r[tk][i] = rr; sm_l[tk][i] = sm_l[tk][i] * rr + ls; sm_m[tk][i] = mn; }
         }
         __syncthreads();
-        if (ksub < nsub) {
+        // ---- P*V: a V value is fetched once for all tokens and heads
+        {
 #pragma unroll
-            for (int i = 0; i < GRP; i++) acc[i] *= sm_r[i];
+            for (int tk = 0; tk < TG; tk++)
+#pragma unroll
+                for (int i = 0; i < GRP; i++) acc[tk][i] *= (tk < ntk ? sm_r[tk][i] : 1.0f);
             const int jlo = ksub * krun;
             for (int jj = 0; jj < krun; jj += 4) {
                 const int j = jlo + jj;
-                if (j >= nj) break;
+                if (j >= njm) break;
                 float vv[4];
 #pragma unroll
-                for (int u = 0; u < 4; u++) vv[u] = j + u < nj ? vbase[(size_t)(j0 + j + u) * DH + d] : 0.0f;
+                for (int u = 0; u < 4; u++) vv[u] = j + u < njm ? vt[(size_t)(j + u) * DH + d] : 0.0f;
 #pragma unroll
-                for (int i = 0; i < GRP; i++) {
-                    const float4 p4 = *reinterpret_cast<const float4*>(sp + i * PF_KT + j);
-                    acc[i] = fmaf(p4.x, vv[0], acc[i]); acc[i] = fmaf(p4.y, vv[1], acc[i]);
-                    acc[i] = fmaf(p4.z, vv[2], acc[i]); acc[i] = fmaf(p4.w, vv[3], acc[i]);
+                for (int tk = 0; tk < TG; tk++) {
+                    if (tk >= ntk) break;
+#pragma unroll
+                    for (int i = 0; i < GRP; i++) {
+                        const float4 p4 = *reinterpret_cast<const float4*>(sp + (tk * GRP + i) * 128 + j);
+                        acc[tk][i] = fmaf(p4.x, vv[0], acc[tk][i]); acc[tk][i] = fmaf(p4.y, vv[1], acc[tk][i]);
+                        acc[tk][i] = fmaf(p4.z, vv[2], acc[tk][i]); acc[tk][i] = fmaf(p4.w, vv[3], acc[tk][i]);
+                    }
                 }
             }
         }
         __syncthreads();
     }
-    if (ksub < nsub) {
+    const bool bad = sm_abort != 0;       // (every thread passed a barrier after the last write of the flag)
+    if (bad && tid == 0 && err) *err = 1;
+    const int PW = GRP * (DH + 2);
+    // per token: add the key runs inside the tiles up, then either the result or this run's (sum, m, l)
 #pragma unroll
-        for (int i = 0; i < GRP; i++) sacc[((size_t)ksub * GRP + i) * DH + d] = acc[i];
-    }
-    __syncthreads();
-    if (n_act == 1) {
+    for (int tk = 0; tk < TG; tk++) {
+        if (tk >= ntk) break;
+        const int t = t0 + tk;
+#pragma unroll
+        for (int i = 0; i < GRP; i++) sacc[((size_t)ksub * GRP + i) * DH + d] = acc[tk][i];
+        __syncthreads();
+        float* mine = part + ((size_t)(t * gridDim.x + kvh) * NS + s) * PW;
         for (int o = tid; o < GRP * DH; o += PF_AT) {
             const int i = o / DH, dd = o - i * DH;
             float v = 0.0f;
             for (int u = 0; u < nsub; u++) v += sacc[((size_t)u * GRP + i) * DH + dd];
-            ctx[(size_t)t * ld_ctx + (size_t)(kvh * GRP + i) * DH + dd] = v / sm_l[i];
+            if (bad) continue;
+            if (n_act == 1) ctx[(size_t)t * ld_ctx + (size_t)(kvh * GRP + i) * DH + dd] = v / sm_l[tk][i];
+            else mine[o] = v;
         }
-        return;
+        if (n_act > 1 && tid < GRP && !bad) { mine[GRP * DH + tid] = sm_m[tk][tid]; mine[GRP * DH + GRP + tid] = sm_l[tk][tid]; }
+        __syncthreads();
     }
-    // several runs: leave (sum, m, l) of this run; the last CTA of the (token, kv head) merges the runs in order
-    const int PW = GRP * (DH + 2);
-    float* mine = part + ((size_t)(t * gridDim.x + kvh) * NS + s) * PW;
-    for (int o = tid; o < GRP * DH; o += PF_AT) {
-        const int i = o / DH, dd = o - i * DH;
-        float v = 0.0f;
-        for (int u = 0; u < nsub; u++) v += sacc[((size_t)u * GRP + i) * DH + dd];
-        mine[o] = v;
-    }
-    if (tid < GRP) { mine[GRP * DH + tid] = sm_m[tid]; mine[GRP * DH + GRP + tid] = sm_l[tid]; }
+    if (n_act == 1) return;
+    // several runs: the last CTA of the (token group, kv head) merges the runs in order
     __threadfence();
     __syncthreads();
-    if (tid == 0) sm_ticket = atomicAdd(tickets + t * gridDim.x + kvh, 1u);
+    if (tid == 0) sm_ticket = atomicAdd(tickets + blockIdx.y * gridDim.x + kvh, 1u);
     __syncthreads();
     if (sm_ticket != (unsigned)(n_act - 1)) return;
     __threadfence();
-    const float* all = part + (size_t)(t * gridDim.x + kvh) * NS * PW;
-    for (int o = tid; o < GRP * DH; o += PF_AT) {
-        const int i = o / DH;
-        float mx = -INFINITY;
-        for (int r = 0; r < n_act; r++) mx = fmaxf(mx, __ldcg(all + (size_t)r * PW + GRP * DH + i));
-        float num = 0.0f, den = 0.0f;
-        for (int r = 0; r < n_act; r++) {
-            const float w = __expf(__ldcg(all + (size_t)r * PW + GRP * DH + i) - mx);
-            num = fmaf(w, __ldcg(all + (size_t)r * PW + o), num);
-            den = fmaf(w, __ldcg(all + (size_t)r * PW + GRP * DH + GRP + i), den);
+    for (int tk = 0; tk < ntk; tk++) {
+        const int t = t0 + tk;
+        const float* all = part + (size_t)(t * gridDim.x + kvh) * NS * PW;
+        for (int o = tid; o < GRP * DH; o += PF_AT) {
+            const int i = o / DH;
+            float mx = -INFINITY;
+            for (int r = 0; r < n_act; r++) mx = fmaxf(mx, __ldcg(all + (size_t)r * PW + GRP * DH + i));
+            float num = 0.0f, den = 0.0f;
+            for (int r = 0; r < n_act; r++) {
+                const float w = __expf(__ldcg(all + (size_t)r * PW + GRP * DH + i) - mx);
+                num = fmaf(w, __ldcg(all + (size_t)r * PW + o), num);
+                den = fmaf(w, __ldcg(all + (size_t)r * PW + GRP * DH + GRP + i), den);
+            }
+            if (!bad) ctx[(size_t)t * ld_ctx + (size_t)kvh * GRP * DH + o] = num / den;
         }
-        ctx[(size_t)t * ld_ctx + (size_t)kvh * GRP * DH + o] = num / den;
     }
-    if (tid == 0) tickets[t * gridDim.x + kvh] = 0u;
+    if (tid == 0) tickets[blockIdx.y * gridDim.x + kvh] = 0u;
 }
 
 // Tensor-parallel chunk: the partial rows of a row-split linear (o_proj, down_proj) summed over the ranks and added to
@@ -448,26 +529,45 @@ size_t hx_pf_attn_scratch(int n_tok, int NH, int NKV, int DH) {
     return (size_t)n_tok * NKV * PF_NS_MAX * (NH / NKV) * (DH + 2);
 }
 
+template <int GRP, int TG>
+static int pf_attn_launch(dim3 grid, size_t smem, cudaStream_t st, const float* qkv, int ld, HxPfWhere wh, int n_tok, int NH, int DH, const float* kc,
+                          const float* vc, int cap, float scale, float* ctx, int ld_ctx, float* part, unsigned* tickets, int* err) {
+    static std::atomic<unsigned long long> attr_seen{0};
+    if (hx_first_on_device(attr_seen)) HX_CUDA(cudaFuncSetAttribute(k_pf_attn<GRP, TG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));      // the kernel has some static shared memory too
+    k_pf_attn<GRP, TG><<<grid, PF_AT, smem, st>>>(qkv, ld, wh, n_tok, NH, DH, kc, vc, cap, scale, ctx, ld_ctx, part, tickets, err);
+    return HX_OK;
+}
+
 int hx_pf_attn(const float* qkv, int ld, int n_tok, HxPfWhere wh, int NH, int NKV, int DH, const float* kc, const float* vc,
-               int cap, float scale, float* ctx, int ld_ctx, float* part, unsigned* tickets, cudaStream_t st) {
+               int cap, float scale, float* ctx, int ld_ctx, float* part, unsigned* tickets, int* err, cudaStream_t st) {
     const int GRP = NH / NKV;
-    if (DH > 256) return hx_fail(HX_ERR_ARG, "batched prefill attention: head_dim %d > 256", DH);
+    if (DH > 256 || DH % 32) return hx_fail(HX_ERR_ARG, "batched prefill attention: head_dim %d is not a multiple of 32 up to 256", DH);
     if (PF_AT % DH) return hx_fail(HX_ERR_ARG, "batched prefill attention: head_dim %d does not divide %d", DH, PF_AT);
-    const size_t smem = ((size_t)GRP * DH + (size_t)GRP * PF_KT + (size_t)(PF_AT / DH) * GRP * DH) * 4;
-    if (smem > 48 * 1024) return hx_fail(HX_ERR_ARG, "batched prefill attention: %zu bytes of shared memory", smem);
-    // runs of key tiles per (token, kv head): enough CTAs for four per SM, no more than the cache has tiles
-    int ns = (4 * 148 + NKV * n_tok - 1) / (NKV * n_tok);
-    const int cap_tiles = (cap + PF_KT - 1) / PF_KT;
+    if (!part || !tickets) return hx_fail(HX_ERR_ARG, "batched prefill attention: no scratch for the key runs");
+    // a prefill chunk (one sequence, consecutive positions): four tokens share the tiles of a CTA
+    auto smem_of = [&](int tg) { return (size_t)PF_ST * 2 * PF_TILE_BYTES + ((size_t)tg * GRP * DH + (size_t)tg * GRP * 128 + (size_t)(PF_AT / DH) * GRP * DH) * 4; };
+    const size_t smem_max = 226 * 1024;
+    const int TG = (wh.pos_arr || smem_of(4) > smem_max) ? 1 : 4;
+    const int groups = (n_tok + TG - 1) / TG;
+    const size_t smem = smem_of(TG);
+    if (smem > smem_max) return hx_fail(HX_ERR_ARG, "batched prefill attention: %zu bytes of shared memory", smem);
+    // runs of key tiles per (token group, kv head): about two CTAs per SM, no more than the cache has tiles
+    const int KT = 128 < PF_TILE_BYTES / (DH * 4) ? 128 : PF_TILE_BYTES / (DH * 4);
+    int ns = (2 * 148 + NKV * groups - 1) / (NKV * groups);
+    const int cap_tiles = (cap + KT - 1) / KT;
     if (ns > cap_tiles) ns = cap_tiles;
     if (ns > PF_NS_MAX) ns = PF_NS_MAX;
-    if (ns < 1 || !part || !tickets) ns = 1;
-    dim3 grid(NKV, n_tok, ns);
-#define HX_PF_ATTN(G) case G: k_pf_attn<G><<<grid, PF_AT, smem, st>>>(qkv, ld, wh, NH, DH, kc, vc, cap, scale, ctx, ld_ctx, part, tickets); break;
+    if (ns < 1) ns = 1;
+    dim3 grid(NKV, groups, ns);
+    int rc;
+#define HX_PF_ATTN(G) case G: rc = TG == 1 ? pf_attn_launch<G, 1>(grid, smem, st, qkv, ld, wh, n_tok, NH, DH, kc, vc, cap, scale, ctx, ld_ctx, part, tickets, err) \
+                                            : pf_attn_launch<G, 4>(grid, smem, st, qkv, ld, wh, n_tok, NH, DH, kc, vc, cap, scale, ctx, ld_ctx, part, tickets, err); break;
     switch (GRP) {
         HX_PF_ATTN(1) HX_PF_ATTN(2) HX_PF_ATTN(3) HX_PF_ATTN(4) HX_PF_ATTN(5) HX_PF_ATTN(6) HX_PF_ATTN(7) HX_PF_ATTN(8)
         default: return hx_fail(HX_ERR_ARG, "batched prefill attention: group of %d query heads per kv head not supported", GRP);
     }
 #undef HX_PF_ATTN
+    if (rc) return rc;
     HX_COUNT_LAUNCH(1);
     return HX_OK;
 }

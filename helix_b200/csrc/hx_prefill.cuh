@@ -31,12 +31,12 @@ void hx_pf_qkpost(float* qkv, int ld, int n_tok, HxPfWhere wh, int NH, int NKV, 
                   float eps, const float* cosT, const float* sinT, float* kc, float* vc, int cap, cudaStream_t st);
 
 // Causal attention of a chunk over the cache: query t (position *posp + t) attends to positions 0 .. *posp + t.
-// CTAs per (kv head, token, run of key tiles); the query heads of a kv head share its K and V rows.  `part`
-// (hx_pf_attn_scratch floats) and `tickets` (n_tok * NKV words, zero between launches) carry the runs' partial
-// results; without them one CTA walks the whole context.
+// CTAs per (kv head, group of tokens, run of key tiles); the query heads of a kv head share its K and V rows, and so do
+// the tokens of a group in a prefill chunk.  `part` (hx_pf_attn_scratch floats) and `tickets` (n_tok * NKV words, zero
+// between launches) carry the runs' partial results; *err is raised when a bounded wait ran out.
 size_t hx_pf_attn_scratch(int n_tok, int NH, int NKV, int DH);
 int hx_pf_attn(const float* qkv, int ld, int n_tok, HxPfWhere wh, int NH, int NKV, int DH, const float* kc, const float* vc,
-               int cap, float scale, float* ctx, int ld_ctx, float* part, unsigned* tickets, cudaStream_t st);
+               int cap, float scale, float* ctx, int ld_ctx, float* part, unsigned* tickets, int* err, cudaStream_t st);
 
 // *posp += n
 void hx_pf_advance(int* posp, int n, cudaStream_t st);
