@@ -214,6 +214,81 @@ __global__ void __launch_bounds__(PF_AT) k_pf_attn(const float* __restrict__ qkv
     for (int tk = 0; tk < TG; tk++)
 #pragma unroll
         for (int i = 0; i < GRP; i++) acc[tk][i] = 0.0f;
+    // Batched decode at head_dim 128 (tiles of 64 keys): a leaner arrangement of the same arithmetic.  Scores: thread (key,
+    // eighth of the row) with its slice of q in registers -- chunk c * 8 + eighth of the row, so that the eight lanes of a
+    // key read eight different bank groups -- and three exchanges per head.  P*V: a warp per four keys, a lane per
+    // float4 of the row; the sixteen warps' sums are added up through the (then idle) ring at the end.
+    constexpr bool kLean = TG == 1 && GRP <= 4;
+    const bool lean = kLean && DH == 128;
+    float acc4[kLean ? GRP : 1][4];
+#pragma unroll
+    for (int i = 0; i < (kLean ? GRP : 1); i++) acc4[i][0] = acc4[i][1] = acc4[i][2] = acc4[i][3] = 0.0f;
+    if (lean) {
+        const int key = tid >> 3, pt = tid & 7;
+        float4 qr[kLean ? GRP : 1][4];
+#pragma unroll
+        for (int i = 0; i < (kLean ? GRP : 1); i++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) qr[i][c] = *reinterpret_cast<const float4*>(sq + i * 128 + (c * 8 + pt) * 4);
+        for (int it = 0; it < ntile; it++) {
+            const int j0 = j_lo + it * 64, nj = min(64, j_hi - j0);
+            if (tid == 0 && it + PF_ST - 1 < ntile) issue(it + PF_ST - 1);
+            if (!pf_mb_wait(&full[it % PF_ST], (uint32_t)(it / PF_ST) & 1u)) sm_abort = 1;
+            const float* kt = ringf + (size_t)(it % PF_ST) * stage_f;
+            const float* vt = kt + PF_TILE_BYTES / 4;
+            {
+                float4 k4[4];
+#pragma unroll
+                for (int c = 0; c < 4; c++) k4[c] = *reinterpret_cast<const float4*>(kt + key * 128 + (c * 8 + pt) * 4);
+                float dot[kLean ? GRP : 1];
+#pragma unroll
+                for (int i = 0; i < (kLean ? GRP : 1); i++) {
+                    float a = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        a = fmaf(qr[i][c].x, k4[c].x, a); a = fmaf(qr[i][c].y, k4[c].y, a); a = fmaf(qr[i][c].z, k4[c].z, a); a = fmaf(qr[i][c].w, k4[c].w, a);
+                    }
+                    a += __shfl_xor_sync(0xffffffffu, a, 1); a += __shfl_xor_sync(0xffffffffu, a, 2); a += __shfl_xor_sync(0xffffffffu, a, 4);
+                    dot[i] = a;
+                }
+#pragma unroll
+                for (int i = 0; i < (kLean ? GRP : 1); i++)
+                    if (pt == i && key < nj) sp[i * 128 + key] = dot[i] * scale;
+            }
+            __syncthreads();
+            for (int i = warp; i < GRP; i += NW) {
+                const float s0 = lane < nj ? sp[i * 128 + lane] : -INFINITY, s1 = lane + 32 < nj ? sp[i * 128 + lane + 32] : -INFINITY;
+                const float tm = hx_warp_max(fmaxf(s0, s1));
+                const float mo = sm_m[0][i], mn = fmaxf(mo, tm);
+                const float p0 = lane < nj ? __expf(s0 - mn) : 0.0f, p1 = lane + 32 < nj ? __expf(s1 - mn) : 0.0f;
+                sp[i * 128 + lane] = p0; sp[i * 128 + lane + 32] = p1;
+                const float ls = hx_warp_sum(p0 + p1);
+                if (lane == 0) { const float rr = __expf(mo - mn); sm_r[0][i] = rr; sm_l[0][i] = sm_l[0][i] * rr + ls; sm_m[0][i] = mn; }
+            }
+            __syncthreads();
+            {
+                float4 p4[kLean ? GRP : 1];
+#pragma unroll
+                for (int i = 0; i < (kLean ? GRP : 1); i++) {
+                    const float rr = sm_r[0][i];
+                    acc4[i][0] *= rr; acc4[i][1] *= rr; acc4[i][2] *= rr; acc4[i][3] *= rr;
+                    p4[i] = *reinterpret_cast<const float4*>(sp + i * 128 + warp * 4);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int j = warp * 4 + u;
+                    const float4 v4 = j < nj ? *reinterpret_cast<const float4*>(vt + j * 128 + lane * 4) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                    for (int i = 0; i < (kLean ? GRP : 1); i++) {
+                        const float pj = u == 0 ? p4[i].x : (u == 1 ? p4[i].y : (u == 2 ? p4[i].z : p4[i].w));
+                        acc4[i][0] = fmaf(pj, v4.x, acc4[i][0]); acc4[i][1] = fmaf(pj, v4.y, acc4[i][1]);
+                        acc4[i][2] = fmaf(pj, v4.z, acc4[i][2]); acc4[i][3] = fmaf(pj, v4.w, acc4[i][3]);
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    } else
     for (int it = 0; it < ntile; it++) {
         const int j0 = j_lo + it * KT, njt = min(KT, j_hi - j0);
         // every thread is past tile it - 1 (the barrier that ended it), so its stage may be refilled
@@ -325,14 +400,23 @@ __global__ void __launch_bounds__(PF_AT) k_pf_attn(const float* __restrict__ qkv
     for (int tk = 0; tk < TG; tk++) {
         if (tk >= ntk) break;
         const int t = t0 + tk;
+        // (lean arrangement: one partial output per warp, in the ring, which no copy writes any more)
+        const float* red = lean ? ringf : sacc;
+        const int nred = lean ? NW : nsub;
+        if (lean) {
 #pragma unroll
-        for (int i = 0; i < GRP; i++) sacc[((size_t)ksub * GRP + i) * DH + d] = acc[tk][i];
+            for (int i = 0; i < (kLean ? GRP : 1); i++)
+                *reinterpret_cast<float4*>(ringf + ((size_t)warp * GRP + i) * DH + lane * 4) = make_float4(acc4[i][0], acc4[i][1], acc4[i][2], acc4[i][3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < GRP; i++) sacc[((size_t)ksub * GRP + i) * DH + d] = acc[tk][i];
+        }
         __syncthreads();
         float* mine = part + ((size_t)(t * gridDim.x + kvh) * NS + s) * PW;
         for (int o = tid; o < GRP * DH; o += PF_AT) {
             const int i = o / DH, dd = o - i * DH;
             float v = 0.0f;
-            for (int u = 0; u < nsub; u++) v += sacc[((size_t)u * GRP + i) * DH + dd];
+            for (int u = 0; u < nred; u++) v += red[((size_t)u * GRP + i) * DH + dd];
             if (bad) continue;
             if (n_act == 1) ctx[(size_t)t * ld_ctx + (size_t)(kvh * GRP + i) * DH + dd] = v / sm_l[tk][i];
             else mine[o] = v;

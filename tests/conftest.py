@@ -17,6 +17,8 @@ TINY = dict(NL=2, DM=128, NH=4, NKV=2, DH=32, DFF=256, NV=300)
 RAGGED = dict(NL=3, DM=192, NH=6, NKV=2, DH=32, DFF=328, NV=1001)
 # GQA group of 8 and head_dim 128, the Qwen3-32B head geometry at toy width
 WIDE = dict(NL=2, DM=256, NH=8, NKV=1, DH=128, DFF=512, NV=512)
+# GQA group of 4 and head_dim 128, the Qwen3-8B head geometry at toy width
+GQA4 = dict(NL=2, DM=256, NH=8, NKV=2, DH=128, DFF=512, NV=512)
 
 
 @pytest.fixture(scope="session")
@@ -44,3 +46,8 @@ def ragged_file(tmp_path_factory):
 @pytest.fixture(scope="session")
 def wide_file(tmp_path_factory):
     return make_model_file(tmp_path_factory, WIDE, 12, "wide")
+
+
+@pytest.fixture(scope="session")
+def gqa4_file(tmp_path_factory):
+    return make_model_file(tmp_path_factory, GQA4, 13, "gqa4")

@@ -33,16 +33,23 @@ def test_batched_decode_matches_single_sequence_checker(which, nseq, tiny_file, 
     gm.close(); om.close()
 
 
-def test_prefill_into_slots_then_batched_decode(ragged_file):
+@pytest.mark.parametrize("which,lens", [
+    ("ragged", [19, 16, 5, 33]),                      # ragged chunks, a quarter chunk, shorter than a token group, half a chunk + 1
+    ("ragged", [64, 129, 70, 3]),                     # one exact chunk, two chunks + 1, a chunk and a bit
+    ("gqa4", [200, 61, 130, 257, 9]),                 # head_dim 128 in groups of 4: several key tiles and runs per sequence
+    ("wide", [150, 66]),
+])
+def test_prefill_into_slots_then_batched_decode(which, lens, ragged_file, gqa4_file, wide_file):
     """Every sequence of a batch gets its own prompt through the chunked prefill into its own KV slot, then all slots
     decode together; tokens must equal the checker's greedy continuation of each prompt on its own."""
-    nseq, G = 4, 6
-    om = ol.OracleModel(ragged_file, kv_cap=64)
+    path = dict(ragged=ragged_file, gqa4=gqa4_file, wide=wide_file)[which]
+    nseq, G = len(lens), 6
+    cap = max(lens) + 16
+    om = ol.OracleModel(path, kv_cap=cap)
     rng = np.random.default_rng(77)
-    lens = [19, 16, 5, 33]                            # ragged chunks, one exact chunk, shorter than a chunk, two chunks + 1
     prompts = [rng.integers(0, om.NV, n).astype(np.int32) for n in lens]
     want = [om.generate(p, G + 1) for p in prompts]
-    gm = hb.Model.load(ragged_file, kv_cap=64, batch=nseq)
+    gm = hb.Model.load(path, kv_cap=cap, batch=nseq)
     first = np.array([gm.prefill_seq(s, prompts[s]) for s in range(nseq)], np.int32)
     assert list(first) == [int(w[0]) for w in want]
     toks, pos = first.copy(), np.array(lens, np.int32)

@@ -13,9 +13,9 @@ LOGIT_TOL = 2e-4
 
 
 @pytest.mark.parametrize("which,T", [("tiny", 16), ("tiny", 37), ("ragged", 37), ("wide", 50), ("ragged", 5),
-                                     ("tiny", 64), ("ragged", 70), ("wide", 150), ("tiny", 200)])
-def test_batched_prefill_matches_checker_and_token_path(which, T, tiny_file, ragged_file, wide_file):
-    path = dict(tiny=tiny_file, ragged=ragged_file, wide=wide_file)[which]
+                                     ("tiny", 64), ("ragged", 70), ("wide", 150), ("tiny", 200), ("gqa4", 300)])
+def test_batched_prefill_matches_checker_and_token_path(which, T, tiny_file, ragged_file, wide_file, gqa4_file):
+    path = dict(tiny=tiny_file, ragged=ragged_file, wide=wide_file, gqa4=gqa4_file)[which]
     om = ol.OracleModel(path, kv_cap=T + 32)
     ids = np.random.default_rng(100 + T).integers(0, om.NV, T).astype(np.int32)
     lo = om.prefill(ids)
