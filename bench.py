@@ -353,13 +353,13 @@ def batch64_leg(hb, L, check, dist, rank, ngpus, shape):
     return {"sequences": n_seq, "sequences_asked": BATCH_SEQS, "per_gpu": S_run, "prompt": BATCH_PROMPT, "new_tokens": BATCH_NEW,
             "prefill_s": prefill_s, "prefill_tok_per_s": ptok / prefill_s, "decode_s": dms * 1e-3, "decode_tok_per_s": dtok / (dms * 1e-3),
             "total_tok_per_s": (ptok + dtok) / (prefill_s + dms * 1e-3),
-            "path": "hx_prefill_seq per sequence (16-token chunks through the tcgen05 GEMM), then hx_decode_batch_loop "
-                    "(16 sequences per GEMM); replicas, no exchange between GPUs"}
+            "path": "hx_prefill_seq per sequence (64-token chunks through the tcgen05 GEMM), then hx_decode_batch_loop "
+                    "(64 sequences per pass over the weights); replicas, no exchange between GPUs"}
 
 
 def tp_leg(hb, L, check, dist, rank, ngpus, peak):
     """The Qwen3-32B shape as one tensor-parallel group over the GPUs of the run, batch 1: the 4096-token prompt is
-    prefilled in chunks of 16 positions (the partial rows of o_proj / down_proj exchanged per chunk), then tokens are
+    prefilled in chunks of 64 positions (the partial rows of o_proj / down_proj exchanged per chunk), then tokens are
     decoded at that context."""
     shape = dict(hb.QWEN3_32B)
     cap = TP_PROMPT + TP_NEW + 16
@@ -614,7 +614,7 @@ def run_ours(args):
         sm = hb.Model.synth(small, seed=3, kv_cap=512)
         spec["small_model_d512_vocab_2011"] = spec_run(sm, small["vocab"], 256)
         sm.close()
-        spec["note"] = ("a verify forward is one 16-token chunk of the batched prefill path plus the head on every row; it pays when "
+        spec["note"] = ("a verify forward is one chunk of the batched prefill path (the last token and the drafts, 16 rows at most) plus the head on every row; it pays when "
                         "about three drafted tokens are accepted per hit")
 
     cpu = parity = None
@@ -645,7 +645,7 @@ def run_ours(args):
                 "roofline": roofline, "cpu_baseline": cpu, "parity": parity, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
                 "reference_gpu": ref_gpu, "batch64": batch64, "tp": tpl, "speculative": spec, "tensor_probe": tprobe, "quantizer": quant, "gpt2": gpt2,
                 "prefill": {"tokens": PROMPT_LEN, "ms": prefill_s * 1e3, "tok_per_s": PROMPT_LEN / prefill_s,
-                            "path": "chunks of 16 tokens, one tcgen05 block-scaled GEMM per linear (exact digit columns), host ids in"},
+                            "path": "chunks of 64 tokens, one tcgen05 block-scaled GEMM per linear (exact digit columns), host ids in"},
                 "ms_per_token": ms_max / args.steps / NEW_TOKENS, "last_tokens": [int(t) for t in toks[-4:]]}
         print(json.dumps(line), flush=True)
     if dist is not None:

@@ -312,8 +312,8 @@ int hx_decode_loop(hx_model* m, const int32_t* ids, int pos0, int n_steps, int32
 
 /* Batched decode (independent sequences sharing one weight copy, 64 per GPU in the benchmark).  The model is created with
  * batch = number of sequences; sequence i owns KV slot i.  One call decodes one token of each of n_seq sequences:
- * ids[i] at position pos[i] (HOST arrays), arg-max to next_ids[i].  Internally chunks of 16 sequences go through every
- * linear as one tcgen05 GEMM (the weights are streamed once per 16 tokens instead of once per token), attention and
+ * ids[i] at position pos[i] (HOST arrays), arg-max to next_ids[i].  Internally chunks of 64 sequences go through every
+ * linear as one tcgen05 GEMM (the weights are streamed once per 64 tokens instead of once per token), attention and
  * the KV append run per sequence.  The reference has no batch dimension (one sequence at a time). */
 int hx_decode_batch(hx_model* m, const int32_t* ids, const int32_t* pos, int n_seq, int32_t* next_ids);
 /* n_steps such steps from position pos0 for every sequence, feeding back the arg-max on the device; the step is

@@ -22,7 +22,7 @@ def main():
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     dist.init_process_group("gloo", rank=rank, world_size=world)
     check(lib().hx_set_device(int(os.environ.get("LOCAL_RANK", rank))))
-    gm = hb.Model.load(path, kv_cap=96, tp_rank=rank, tp_size=world)
+    gm = hb.Model.load(path, kv_cap=256, tp_rank=rank, tp_size=world)
     mine = torch.tensor(list(gm.tp_handle()), dtype=torch.uint8)
     allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
     dist.all_gather(allh, mine)
@@ -32,11 +32,11 @@ def main():
     om = None
     if rank == 0:
         import oracle_lib as ol
-        om = ol.OracleModel(path, kv_cap=96)
+        om = ol.OracleModel(path, kv_cap=256)
     NVl = gm.cfg.vocab
-    # batched prefill inside the group: chunks of 16 positions with the partial rows of o_proj / down_proj exchanged per
-    # chunk, the last position through the decode kernel; 37 tokens = two full chunks, a ragged one and the last token
-    pids = np.random.default_rng(8).integers(0, NVl * world, 37).astype(np.int32)
+    # batched prefill inside the group: chunks of 64 positions with the partial rows of o_proj / down_proj exchanged per
+    # chunk, the last position through the decode kernel; 150 tokens = two full chunks, a ragged one and the last token
+    pids = np.random.default_rng(8).integers(0, NVl * world, 150).astype(np.int32)
     nxp, lgp = gm.prefill(pids, want_logits=True)
     parts = [torch.zeros(NVl, dtype=torch.float32) for _ in range(world)]
     dist.all_gather(parts, torch.from_numpy(lgp.copy()))
@@ -79,14 +79,14 @@ def main():
 
     # a batch of three sequences inside the group: prompts of different lengths into their own KV slots, then batched
     # decode steps; the arg-max over the ranks' vocabulary slices is taken per sequence
-    gb = hb.Model.load(path, kv_cap=96, tp_rank=rank, tp_size=world, batch=3)
+    gb = hb.Model.load(path, kv_cap=256, tp_rank=rank, tp_size=world, batch=3)
     mine = torch.tensor(list(gb.tp_handle()), dtype=torch.uint8)
     allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
     dist.all_gather(allh, mine)
     gb.tp_connect([bytes(h.tolist()) for h in allh])
     dist.barrier()
     rngb = np.random.default_rng(31)
-    prompts = [rngb.integers(0, NVl * world, n).astype(np.int32) for n in (5, 17, 20)]
+    prompts = [rngb.integers(0, NVl * world, n).astype(np.int32) for n in (5, 81, 20)]
     toks = np.array([gb.prefill_seq(i, p) for i, p in enumerate(prompts)], np.int32)
     pos = np.array([len(p) for p in prompts], np.int32)
     got = [toks.copy()]
