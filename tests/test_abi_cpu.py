@@ -171,7 +171,6 @@ def test_argument_checks_of_the_wider_entry_points_need_no_device(tiny_file):
     assert b"divisible" in L.hx_last_error()
     assert L.hx_model_load(C.byref(h), tiny_file.encode(), 16, 1, 0, 2, 2) == 1
     assert L.hx_model_load(C.byref(h), tiny_file.encode(), 16, 0, 0, 0, 1) == 1           # batch 0
-    assert L.hx_model_load(C.byref(h), tiny_file.encode(), 16, 4, 0, 0, 2) == 1           # batch and TP together
     from helix_b200.lib import HxConfig, HxGpt2Weights
     cfg = HxConfig(1, 2, 128, 4, 4, 32, 512, 300, 64, 0.0, 1e-5, 0)                       # arch 1 is not GPT-2
     one = (C.c_float * 4)()
