@@ -41,5 +41,5 @@ def test_tp_matches_full_model(which, tiny_file, tmp_path_factory):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr",
            "127.0.0.1", "--master-port", "29533", os.path.join(HERE, "tp_worker.py"), path, "12", "12"]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
-    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-6000:]
     assert "TP-OK world=%d" % world in r.stdout and "TP-BATCH-OK world=%d" % world in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

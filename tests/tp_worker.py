@@ -48,6 +48,7 @@ def main():
         assert pf_err < 2e-4, pf_err
         assert nxp == int(np.argmax(lo)), (nxp, int(np.argmax(lo)))
         om.reset() if hasattr(om, "reset") else None
+    dist.barrier()          # rank 0 was busy with the checker: nobody starts a step (a bounded wait) before it is back
     gm.reset()
     ids = np.random.default_rng(5).integers(0, NVl * world, n_teacher)
     worst = 0.0
