@@ -653,6 +653,25 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def chunk_probe(args):
+    """A small, bounded case of the chunk kernels (k_gemm_tc at 64 tokens, k_pf_attn in both modes) for profiler captures."""
+    import helix_b200 as hb
+    shape = dict(hb.QWEN3_8B)
+    shape["n_layers"] = args.layers or 2
+    ctx = 2048
+    m = hb.Model.synth(shape, seed=1, kv_cap=ctx + 256, batch=64)
+    m.fill_kv(ctx, 7)
+    ids = np.random.default_rng(1).integers(0, shape["vocab"], 64).astype(np.int32)
+    nxt = ids
+    for _ in range(2):
+        nxt = m.decode_batch(ids, np.full(64, ctx, np.int32))
+    prompt = np.random.default_rng(2).integers(0, shape["vocab"], 512).astype(np.int32)
+    first = m.prefill_seq(0, prompt)
+    m.close()
+    print(json.dumps({"probe": "chunk path", "layers": shape["n_layers"], "sequences": 64, "context": ctx,
+                      "next": [int(v) for v in nxt[:4]], "prefill_next": int(first)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -671,6 +690,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="reduced depth for profiler captures (0 = the full 36)")
     ap.add_argument("--new-tokens", type=int, default=0, help="tokens per step for profiler captures (0 = 256)")
     ap.add_argument("--prompt-len", type=int, default=0, help="prompt length for profiler captures (0 = 512)")
+    ap.add_argument("--chunk-probe", action="store_true",
+                    help="profiler capture of the chunk path at --layers depth (default 2): 64 sequences at 2048 positions "
+                         "(synthetic KV rows), two batched decode steps, then a 512-token prefill; prints no bench line")
     args = ap.parse_args()
     global PROMPT_LEN, NEW_TOKENS
     if args.new_tokens:
@@ -679,7 +701,9 @@ def main():
         PROMPT_LEN = args.prompt_len
     reduced = bool(args.layers or args.new_tokens or args.prompt_len)
     args.warmup = max(args.warmup, 3) if (args.impl == "ours" and not reduced) else args.warmup
-    if args.impl == "reference":
+    if args.chunk_probe:
+        chunk_probe(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

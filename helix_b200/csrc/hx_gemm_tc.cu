@@ -31,7 +31,8 @@
 // Timing probes of a debug build (-DTC_STAMPS): CTA 0 leaves globaltimer values in tc_stamps[role][unit][event].
 #ifdef TC_STAMPS
 __device__ unsigned long long tc_stamps[3][32][8];
-#define TC_MARK(role, unit, ev) do { if (blockIdx.x == 0 && (unit) < 32) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); tc_stamps[role][unit][ev] = t_; } } while (0)
+__device__ long long tc_clocks[3][32][8];
+#define TC_MARK(role, unit, ev) do { if (blockIdx.x == 0 && (unit) < 32) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); tc_stamps[role][unit][ev] = t_; tc_clocks[role][unit][ev] = clock64(); } } while (0)
 #else
 #define TC_MARK(role, unit, ev) do { } while (0)
 #endif
@@ -205,6 +206,54 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                 for (int c = 0; c < 4; c++) tc_cp_sf(tmem + col_sfb + c * 4, smem_desc(s_u32(smem_raw + 1024), 16, 128));
             }
             int unit_iter = 0;
+            if (BR && Sk == 4) {
+                // One (piece, group) for the whole CTA: its stages form one sequence, a cell of A against a resident cell of
+                // B each.  The four descriptors of a cell differ by constants (the address field counts 16-byte units), and
+                // the scale factors of stage s + 1 are copied before the MMAs of stage s are issued, so that no MMA waits
+                // for the copy in front of it.
+                const int piece0 = ((int)blockIdx.x % PG) / G;
+                const int ncell = (piece0 + 1) * kcells / P - piece0 * kcells / P;
+                const int nu = ((int)blockIdx.x < nunits) ? (nunits - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+                const uint32_t total = (uint32_t)(nu * ncell);
+                auto copy_sf = [&](uint32_t gi) -> bool {       // stage gi has landed: its scale factors to TMEM
+                    const uint32_t slot = gi % HX_TC_STAGES, round = gi / HX_TC_STAGES;
+                    if (gi < (uint32_t)ncell && !mb_wait(&S.bfull[gi], 0, &S.abort_flag)) return false;
+                    if (!mb_wait(&S.full[slot], round & 1, &S.abort_flag)) return false;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t dS = dS0 + (uint64_t)((slot * stage_bytes) >> 4);
+                    const uint32_t ta = tmem + col_sfa + slot * HX_TC_MAX_SK * 4;
+#pragma unroll
+                    for (int k = 0; k < 4; k++) tc_cp_sf(ta + k * 4, dS + (uint64_t)(k * 32));
+                    return true;
+                };
+                ok = total > 0 && copy_sf(0);
+                int ci = 0;
+                for (git = 0; git < total && ok; git++) {
+                    if (ci == 0) {
+                        TC_MARK(1, unit_iter, 0);
+                        if (unit_iter > 0) {      // the epilogue has read the previous unit's accumulator out
+                            if (!mb_wait(&S.acc_free, (uint32_t)(unit_iter - 1) & 1u, &S.abort_flag)) break;
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        }
+                        TC_MARK(1, unit_iter, 1);
+                    }
+                    if (git + 1 < total && !copy_sf(git + 1)) { ok = false; break; }
+                    if (ci == 0) TC_MARK(1, unit_iter, 2);
+                    const uint32_t slot = git % HX_TC_STAGES;
+                    const uint64_t dA = dA0 + (uint64_t)((slot * stage_bytes) >> 4);
+                    const uint64_t dB = dB0 + (uint64_t)(((uint32_t)ci * b_cell_bytes) >> 4);
+                    const uint32_t ta = tmem + col_sfa + slot * HX_TC_MAX_SK * 4;
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        tc_mma(tmem, dA + (uint64_t)(k * 2), dB + (uint64_t)(k * 2), idesc, ta + k * 4, tmem + col_sfb, (k > 0 || ci > 0) ? 1u : 0u);
+                    tc_commit(&S.empty[slot]);          // the slot is free once these MMAs have read it
+                    if (++ci == ncell) {
+                        tc_commit(&S.accum);            // accumulator complete
+                        TC_MARK(1, unit_iter, 3);
+                        ci = 0; unit_iter++;
+                    }
+                }
+            } else
             for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x, unit_iter++) {
                 TC_UNIT(u);
                 (void)mt;
@@ -223,18 +272,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                     const int nk = min(Sk, ks_hi - ks0);
                     const uint32_t sa = s_u32(ring + (size_t)slot * stage_bytes);
                     const uint32_t sb = BR ? s_u32(bres) + (uint32_t)((ks0 - ks_lo) / 4) * b_cell_bytes : sa + (uint32_t)Sk * a_cell;
-                    if (BR && nk == 4) {
-                        // one cell of A against one resident cell of B: the four descriptors differ by constants (the
-                        // address field counts 16-byte units), so the issuing thread spends a few instructions per MMA
-                        const uint64_t dA = dA0 + (uint64_t)((slot * stage_bytes) >> 4), dS = dS0 + (uint64_t)((slot * stage_bytes) >> 4);
-                        const uint64_t dB = dB0 + (uint64_t)(((uint32_t)((ks0 - ks_lo) / 4) * b_cell_bytes) >> 4);
-                        const uint32_t ta = tmem + col_sfa + slot * HX_TC_MAX_SK * 4;
-#pragma unroll
-                        for (int k = 0; k < 4; k++) tc_cp_sf(ta + k * 4, dS + (uint64_t)(k * 32));
-#pragma unroll
-                        for (int k = 0; k < 4; k++)
-                            tc_mma(tmem, dA + (uint64_t)(k * 2), dB + (uint64_t)(k * 2), idesc, ta + k * 4, tmem + col_sfb, (k > 0 || ks0 > ks_lo) ? 1u : 0u);
-                    } else
                     for (int k = 0; k < nk; k++) {
                         const uint32_t ta = tmem + col_sfa + (slot * HX_TC_MAX_SK + k) * 4;
                         const uint32_t tb = tmem + col_sfb + (slot * HX_TC_MAX_SK + k) * 4;
