@@ -215,19 +215,20 @@ __global__ void __launch_bounds__(PF_AT) k_pf_attn(const float* __restrict__ qkv
 #pragma unroll
         for (int i = 0; i < GRP; i++) acc[tk][i] = 0.0f;
     // Batched decode at head_dim 128 (tiles of 64 keys): a leaner arrangement of the same arithmetic.  Scores: thread (key,
-    // eighth of the row) with its slice of q in registers -- chunk c * 8 + eighth of the row, so that the eight lanes of a
+    // eighth of the row) with its slice of q in registers (groups of up to four heads) -- chunk c * 8 + eighth of the row, so that the eight lanes of a
     // key read eight different bank groups -- and three exchanges per head.  P*V: a warp per four keys, a lane per
     // float4 of the row; the sixteen warps' sums are added up through the (then idle) ring at the end.
-    constexpr bool kLean = TG == 1 && GRP <= 4;
+    constexpr bool kLean = TG == 1;
+    constexpr bool kQreg = GRP <= 4;       // larger groups read q from shared memory (eight lanes, one 128-byte row: a broadcast)
     const bool lean = kLean && DH == 128;
     float acc4[kLean ? GRP : 1][4];
 #pragma unroll
     for (int i = 0; i < (kLean ? GRP : 1); i++) acc4[i][0] = acc4[i][1] = acc4[i][2] = acc4[i][3] = 0.0f;
     if (lean) {
         const int key = tid >> 3, pt = tid & 7;
-        float4 qr[kLean ? GRP : 1][4];
+        float4 qr[(kLean && kQreg) ? GRP : 1][4];
 #pragma unroll
-        for (int i = 0; i < (kLean ? GRP : 1); i++)
+        for (int i = 0; i < ((kLean && kQreg) ? GRP : 1); i++)
 #pragma unroll
             for (int c = 0; c < 4; c++) qr[i][c] = *reinterpret_cast<const float4*>(sq + i * 128 + (c * 8 + pt) * 4);
         for (int it = 0; it < ntile; it++) {
@@ -246,7 +247,8 @@ __global__ void __launch_bounds__(PF_AT) k_pf_attn(const float* __restrict__ qkv
                     float a = 0.0f;
 #pragma unroll
                     for (int c = 0; c < 4; c++) {
-                        a = fmaf(qr[i][c].x, k4[c].x, a); a = fmaf(qr[i][c].y, k4[c].y, a); a = fmaf(qr[i][c].z, k4[c].z, a); a = fmaf(qr[i][c].w, k4[c].w, a);
+                        const float4 q4 = kQreg ? qr[kQreg ? i : 0][c] : *reinterpret_cast<const float4*>(sq + i * 128 + (c * 8 + pt) * 4);
+                        a = fmaf(q4.x, k4[c].x, a); a = fmaf(q4.y, k4[c].y, a); a = fmaf(q4.z, k4[c].z, a); a = fmaf(q4.w, k4[c].w, a);
                     }
                     a += __shfl_xor_sync(0xffffffffu, a, 1); a += __shfl_xor_sync(0xffffffffu, a, 2); a += __shfl_xor_sync(0xffffffffu, a, 4);
                     dot[i] = a;
