@@ -517,6 +517,7 @@ def run_ours(args):
                     "per_token_ms": {"gemv": gemv_ms_tok, "attention": st["ms_attn"] / 32, "other": st["ms_other"] / 32}}
 
     # end to end through the per-token public call, host buffers both ways
+    pin_lg, pin_io = hb.PinnedArray(shape["vocab"], np.float32), hb.PinnedArray(2, np.int32)      # page-locked host buffers
     check(L.hx_sync())
     if dist is not None:
         dist.barrier()
@@ -525,11 +526,12 @@ def run_ours(args):
     for _ in range(e2e_steps):
         tok = first
         for i in range(NEW_TOKENS):
-            tok, lg = model.decode_step(tok, PROMPT_LEN + i, want_logits=True)
+            tok, lg = model.decode_step(tok, PROMPT_LEN + i, out=pin_lg.array, io=pin_io.array)
     e2e_s = all_max(dist, time.perf_counter() - t0)
+    pin_lg.free(); pin_io.free()
     e2e = None if args.no_e2e else {"value": n_seq * e2e_steps * NEW_TOKENS / e2e_s, "unit": "tok/s",
            "h2d_bytes_per_step": NEW_TOKENS * 4, "d2h_bytes_per_step": NEW_TOKENS * (4 + shape["vocab"] * 4),
-           "api": "hx_decode_step per token: token id H2D, next id + f32 logits row D2H (what the reference worker reads back)"}
+           "api": "hx_decode_step per token with page-locked host buffers: token id H2D, next id + f32 logits row D2H (what the reference worker reads back)"}
 
     extras = not args.no_e2e and not args.layers
     # the other half of the path: the NVFP4 quantizer on the single-matrix shape (12288 x 4096 f32), device resident

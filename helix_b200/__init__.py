@@ -6,9 +6,9 @@ the tests and the benchmark.  There is no CPU fallback: every call fails with ``
 library or a GPU is missing.
 """
 from .lib import (HxError, HxConfig, Model, lib, lib_path, fatbin_path, quantize_host, roundtrip_host,
-                  DeviceBuffer, KernelImage, launch_count, QWEN3_8B, QWEN3_32B, GPT2_124M,
+                  DeviceBuffer, PinnedArray, KernelImage, launch_count, QWEN3_8B, QWEN3_32B, GPT2_124M,
                   HX_LOAD_KEEP_COMMITTED, HX_LOAD_VERIFY_SHA, HX_LOAD_FILE_EPS, pld_draft, pack_qwen3, probe_mxf4_rate, Sampler, worker_path, Tokenizer)
 
 __all__ = ["HxError", "HxConfig", "Model", "lib", "lib_path", "fatbin_path", "quantize_host",
-           "roundtrip_host", "DeviceBuffer", "KernelImage", "launch_count", "QWEN3_8B", "QWEN3_32B", "GPT2_124M",
+           "roundtrip_host", "DeviceBuffer", "PinnedArray", "KernelImage", "launch_count", "QWEN3_8B", "QWEN3_32B", "GPT2_124M",
            "HX_LOAD_KEEP_COMMITTED", "HX_LOAD_VERIFY_SHA", "HX_LOAD_FILE_EPS", "pld_draft", "pack_qwen3", "probe_mxf4_rate", "Sampler", "worker_path", "Tokenizer"]

@@ -82,6 +82,7 @@ struct hx_model {
     float* tc_partial = nullptr; unsigned* tc_cnt = nullptr; int bdig_bytes = 0, tc_ring = 0; size_t tc_units_max = 0; int tc_tiles_max = 0;
     HxPhase *ph_decode = nullptr, *ph_prefill = nullptr; int nph_decode = 0, nph_prefill = 0;
     unsigned long long* d_bar = nullptr; unsigned long long bar_count = 0; int* d_err = nullptr;
+    int* h_flags = nullptr;        // page-locked: [0] the chunk kernels' error word, [1] the decode kernel's, fetched with a step's results
     int grid_persist = 0, dig_bytes = 0, nsplit_persist = 1;
     unsigned long long* d_dbg = nullptr;
     bool profile = false;
@@ -789,8 +790,21 @@ int persist_step(hx_model* m, bool from_prompt, bool with_head) {
     return rc;
 }
 
+// Before the synchronize that ends a step: the two error words travel with the step's results, so that looking at
+// them afterwards costs no round trip of its own.
+static void flags_enqueue(hx_model* m) {
+    if (!m->h_flags && cudaMallocHost((void**)&m->h_flags, 16) != cudaSuccess) { (void)cudaGetLastError(); m->h_flags = nullptr; return; }
+    m->h_flags[0] = m->h_flags[1] = 0;
+    if (m->pf_err) cudaMemcpyAsync(&m->h_flags[0], m->pf_err, 4, cudaMemcpyDeviceToHost, m->st);
+    if (m->persist) cudaMemcpyAsync(&m->h_flags[1], m->d_err, 4, cudaMemcpyDeviceToHost, m->st);
+    m->h_flags[2] = 1;       // fetched: valid after the next synchronize of the stream
+}
+
 // After a synchronize: did any bounded wait of the persistent kernel run out?
 int persist_check(hx_model* m) {
+    const bool fetched = m->h_flags && m->h_flags[2] == 1;
+    if (fetched) m->h_flags[2] = 0;
+    if (fetched && !m->h_flags[0] && !m->h_flags[1]) return HX_OK;
     if (m->pf_err) {
         int pe = 0;
         HX_CUDA(cudaMemcpy(&pe, m->pf_err, 4, cudaMemcpyDeviceToHost));
@@ -874,6 +888,7 @@ HX_API int hx_model_free(hx_model* m) {
     for (int w = 0; w < 8; w++)                      // mappings of the peers' exchange buffers
         if (m->tp_peer[w] && w != m->tp_rank) cudaIpcCloseMemHandle(m->tp_peer[w]);
     for (void* p : m->allocs) cudaFree(p);
+    if (m->h_flags) cudaFreeHost(m->h_flags);
     for (cudaEvent_t e : m->prof_ev) cudaEventDestroy(e);
     if (m->st) cudaStreamDestroy(m->st);
     delete m;
@@ -1238,6 +1253,7 @@ HX_API int hx_decode_step(hx_model* m, const int32_t* ids, int pos, int32_t* nex
     if ((rc = step_decode(m))) return rc;
     if (next_ids) HX_CUDA(cudaMemcpyAsync(next_ids, m->d_tok, 4, cudaMemcpyDeviceToHost, m->st));
     if (logits) HX_CUDA(cudaMemcpyAsync(logits, m->logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToHost, m->st));
+    flags_enqueue(m);
     HX_CUDA(cudaStreamSynchronize(m->st));
     if ((rc = persist_check(m))) return rc;
     m->kv_len = pos + 1;

@@ -198,6 +198,23 @@ def launch_count():
     return int(lib().hx_launch_count())
 
 
+class PinnedArray:
+    """Page-locked host memory (hx_host_alloc) seen as a numpy array: the host side of the per-token calls."""
+
+    def __init__(self, count, dtype=np.float32):
+        dt = np.dtype(dtype)
+        self.ptr = C.c_void_p()
+        self.nbytes = int(count) * dt.itemsize
+        check(lib().hx_host_alloc(C.byref(self.ptr), self.nbytes))
+        self.array = np.ctypeslib.as_array(C.cast(self.ptr, C.POINTER(C.c_uint8)), shape=(self.nbytes,)).view(dt)
+
+    def free(self):
+        if self.ptr:
+            self.array = None
+            check(lib().hx_host_free(self.ptr))
+            self.ptr = C.c_void_p()
+
+
 class DeviceBuffer:
     """A device allocation owned through the C ABI."""
 
@@ -372,12 +389,15 @@ class Model:
         check(lib().hx_model_weight_bytes(self.h, C.byref(a), C.byref(b)))
         return a.value, b.value
 
-    def decode_step(self, tok, pos, want_logits=False):
-        ids = np.array([tok], np.int32)
-        nxt = np.zeros(1, np.int32)
-        lg = np.empty(self.vocab, np.float32) if want_logits else None
-        check(lib().hx_decode_step(self.h, ids.ctypes.data, pos, nxt.ctypes.data, lg.ctypes.data if want_logits else None))
-        return (int(nxt[0]), lg) if want_logits else int(nxt[0])
+    def decode_step(self, tok, pos, want_logits=False, out=None, io=None):
+        """One token.  `out` (float32 array of the vocabulary size, e.g. PinnedArray.array) receives the logits instead of a
+        fresh array; `io` (int32 array of two words, pinned) carries the token id in and the next id out."""
+        if io is None:
+            io = np.zeros(2, np.int32)
+        io[0] = tok
+        lg = out if out is not None else (np.empty(self.vocab, np.float32) if want_logits else None)
+        check(lib().hx_decode_step(self.h, io.ctypes.data, pos, io.ctypes.data + 4, lg.ctypes.data if lg is not None else None))
+        return (int(io[1]), lg) if lg is not None else int(io[1])
 
     def prefill(self, ids, want_logits=False):
         ids = np.ascontiguousarray(ids, np.int32)
