@@ -4,16 +4,19 @@
 //
 // A = weights, E2M1 codes with one UE4M3 scale per 16 elements along K: exactly the information of
 // the committed NVFP4 layout (helixc/runtime/gpt2_pack.c:350-373), so the weights feed the tensor
-// cores without any per-weight instruction.  B = activations as E2M1 columns with UE4M3 block scales:
-// either the activation quantized once to NVFP4 (batched prefill, replaces tiled_matmul_abt of
-// forward_layer_llama, helixc/runtime/gpt2_infer.c:1231-1287) or several exact base-8 digit columns
-// of one f32 vector (decode, replaces fused_gemv :2281-2297).
+// cores without any per-weight instruction.  B = activations as E2M1 columns: in digit mode (the chunk
+// paths: batched prefill, batched decode, the verify forward; replaces tiled_matmul_abt of
+// forward_layer_llama, helixc/runtime/gpt2_infer.c:1231-1287) sixteen exact base-4 digit columns per token
+// with unit block scales, recombined in the epilogue; in raw mode (hx_gemm_nvfp4_tc) any E2M1 columns with
+// their own UE4M3 block scales, the accumulators stored as they are.
 //
-// Work units of one 128-row tile of A (times a piece of K), a CTA per SM walking through its units.  Warp 0
-// streams A (and B) cells into a shared-memory ring with cp.async.bulk; warp 1 copies the scale factors to TMEM
-// (tcgen05.cp) and issues tcgen05.mma.kind::mxf4nvf4.block_scale (M=128, N=ncols, K=64 per instruction); warps
-// 2-9 read the accumulator with tcgen05.ld and store it while the next unit's MMAs run.  In the batched
-// prefill the B cells of a CTA's K piece stay in shared memory, so only the weights stream.  Tensor-bound for large N, HBM-bound for small N.
+// Work units of one 128-row tile of A (times a piece of K and a group of 16 tokens), a CTA per SM walking
+// through its units.  Warp 0 streams A (and, in raw mode, B) cells into a shared-memory ring with
+// cp.async.bulk; warp 1 copies the scale factors to TMEM (tcgen05.cp) and issues
+// tcgen05.mma.kind::mxf4nvf4.block_scale (M=128, N=ncols of the group, K=64 per instruction); warps 2-9 read
+// the accumulator with tcgen05.ld and store it while the next unit's MMAs run; warp 10 counts the finished K
+// pieces of a tile.  In digit mode the B cells of a CTA's (K piece, token group) stay in shared memory, so
+// only the weights stream: once per launch from DRAM.
 //
 // "T128" layout of A: per (128-row tile, group of 256 columns = four MMA K steps) one 18432-byte cell:
 // 128 rows x 128 bytes of codes in the canonical K-major 128-byte-swizzle operand layout (row r at
@@ -265,7 +268,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                 TC_MARK(1, unit_iter, 1);
                 for (int ks0 = ks_lo; ks0 < ks_hi; ks0 += Sk, git++) {
                     const uint32_t slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
-                    if (BR && unit_iter == 0 && !mb_wait(&S.bfull[(ks0 - ks_lo) / 4], 0, &S.abort_flag)) { ok = false; break; }
                     if (!mb_wait(&S.full[slot], round & 1, &S.abort_flag)) { ok = false; break; }
                     if (ks0 == ks_lo) TC_MARK(1, unit_iter, 2);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
