@@ -83,43 +83,42 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 }
 
 struct TcSmem {
-    uint64_t full[HX_TC_STAGES], empty[HX_TC_STAGES], accum, acc_free, part_done, tk_ready, bfull[HX_TC_RES_CELLS];
+    uint64_t full[HX_TC_STAGES], empty[HX_TC_STAGES], accum[2], acc_free[2], part_done, tk_ready, bfull[HX_TC_RES_CELLS];
     uint32_t tmem_base;
     unsigned ticket[2];
     volatile int abort_flag;
 };
-#define TC_THREADS 352          // warp 0 loads, warp 1 issues the MMAs, warps 2-9 read the accumulator, warp 10 draws the tickets
+#define TC_EPI_Q 3              // epilogue warps per quarter of the TMEM lanes: each takes eight tokens (or every third group of eight columns)
+#define TC_THREADS ((3 + 4 * TC_EPI_Q) * 32)      // warp 0 loads, warp 1 issues the MMAs, warps 2-13 read the accumulators, warp 14 draws the tickets
 #define TC_HDR 1536u            // header + the chunk of unit scales
 #define TC_SWI (HX_TC_MAX_TOK * 128 * 4)      // SwiGLU exchange: [token][row of the tile]
+#define TC_DIGIT_CELL (HX_TC_GROUP_COLS * 128)      // digit cell of one token group: 240 rows of 128 bytes
 
-__device__ __forceinline__ void tc_ld32(uint32_t (&r)[32], uint32_t taddr) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
-                   "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr));
-}
-template <int OFF, int N>
-__device__ __forceinline__ float tc_digits(const uint32_t (&r)[N]) {       // sum_j 4^-j r[OFF + j]
-    float v = 0.0f;
-#pragma unroll
-    for (int j = 15; j >= 0; j--) v = fmaf(v, 0.25f, __uint_as_float(r[OFF + j]));
-    return v;
+__device__ __forceinline__ void tc_ld8(uint32_t (&r)[8], uint32_t taddr) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr));
 }
 
-// The three roles run through the CTA's work units on their own and meet only at mbarriers: `full`/`empty` per ring
-// slot between the loader and the MMA issuer, `accum` (accumulator complete) and `acc_free` (accumulator read out)
-// between the issuer and the eight epilogue warps.  The epilogue empties the accumulator into registers first (two
-// warps per quarter of the TMEM lanes, half of the tokens each, the next token's load in flight while the digits of
-// the current one are recombined) and frees it, so the MMAs of the next unit run under its stores.
+// The roles run through the CTA's work units on their own and meet only at mbarriers: `full`/`empty` per ring slot
+// between the loader and the MMA issuer, `accum` (accumulator complete) and `acc_free` (accumulator read out) between
+// the issuer and the twelve epilogue warps.
 //
-// Work units: (128-row tile, K piece, group of 16 tokens).  K is cut into pieces of whole 256-column cells (digit
-// mode); each piece recombines its own digits and leaves them in `partial`, and the last piece of a (tile, group)
-// to finish (a ticket) adds the pieces in K order and applies the epilogue.  The ticket of a unit is drawn by a
-// warp of its own after the unit's partial sums are stored and looked at one unit later, so neither its round trip
-// nor the wait for the stores holds up an epilogue warp.
-// With resident B the grid is a multiple of pieces x groups: a CTA keeps one (piece, group) and loads its B cells once,
-// and the CTAs of the groups walk through the same tiles together, so a weight cell comes from DRAM once.
+// Digit mode (the chunk paths).  Work units: (128-row tile, K piece, group of 24 tokens).  An activation enters as ten
+// balanced base-9 digits (-4 .. 4: E2M1 values) of the 30-bit integer |x| / scale * 2^29, digit d of token t in column
+// 24 d + t of the group: 240 columns per MMA, whose cost does not depend on the column count.  Two accumulators of 240
+// columns fill TMEM together with one set of scale-factor columns, so the MMAs of a unit run while the accumulator of
+// the unit before is read out: per token and row the ten digit accumulators are folded by Horner's rule
+// (v = 9 v + D_d, most significant digit first) -- f32-accurate, not exact: the digits' own resolution is 2^-29 of
+// the largest element.  K is cut into pieces of whole 256-column cells; each piece leaves its values in `partial`, and
+// the last piece of a (tile, group) to finish (a ticket) adds the pieces in K order and applies the epilogue, so the
+// result does not depend on the order the CTAs finish in.  The ticket of a unit is drawn by a warp of its own after the
+// unit's partial sums are stored and looked at one unit later, so neither its round trip nor the wait for the stores
+// holds up an epilogue warp.  The grid is a multiple of pieces x groups: a CTA keeps one (piece, group), loads its
+// digit cells once, and the CTAs of the groups walk through the same tiles together, so a weight cell comes from
+// DRAM once.
+//
+// Raw mode (hx_gemm_nvfp4_tc): one accumulator, the ring holds the A and the B cells of a stage, the accumulators
+// are stored as they are.
 __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant__ HxGemmTC g) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     TcSmem& S = *reinterpret_cast<TcSmem*>(smem_raw);
@@ -130,25 +129,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int Sk = g.stage_ksteps;
     const int P = g.ksplit > 1 ? g.ksplit : 1, kcells = g.ksteps / 4;
-    const int G = (g.ncols + 255) / 256, PG = P * G;
+    const bool DG = g.digit_mode != 0;      // digit mode: resident digit cells, two accumulators
+    const int G = DG ? (g.ntok + HX_TC_MAX_TOK - 1) / HX_TC_MAX_TOK : 1, PG = P * G;
     const int nunits = g.ntiles * PG;
-    // b_resident: the B cells of this CTA's (K piece, token group) stay in shared memory across its units (the ring
-    // holds A only).  Otherwise there is one group, and the ring holds the A and the B cells of a stage.
-    const int BR = g.b_resident;
-    const int grp = BR ? ((int)blockIdx.x % PG) % G : 0;
-    const int NB = min(256, g.ncols - 256 * grp);                                            // columns of this CTA's MMAs
-    const uint32_t b_src_cell = (uint32_t)g.ncols * 128u + (g.digit_mode ? 0u : 2048u);      // one 256-column cell of B in memory
-    const uint32_t b_cell_bytes = BR ? (uint32_t)NB * 128u : b_src_cell;                      // ... and in shared memory
+    const int grp = ((int)blockIdx.x % PG) % G;
+    const int NB = DG ? HX_TC_GROUP_COLS : g.ncols;                                         // columns of this CTA's MMAs
+    const uint32_t b_src_cell = DG ? (uint32_t)G * TC_DIGIT_CELL : (uint32_t)g.ncols * 128u + 2048u;      // one 256-column cell of B in memory
+    const uint32_t b_cell_bytes = DG ? (uint32_t)TC_DIGIT_CELL : b_src_cell;                // ... and in shared memory
     const uint32_t a_cell = HX_T128_CELL / 4, b_cell = b_cell_bytes / 4;                     // bytes per K step
-    const uint32_t stage_bytes = (uint32_t)Sk * (a_cell + (BR ? 0u : b_cell));
-    uint8_t* bres = ring + (size_t)HX_TC_STAGES * stage_bytes;      // [cells of a piece][NB * 128]
+    const uint32_t stage_bytes = (uint32_t)Sk * (a_cell + (DG ? 0u : b_cell));
+    uint8_t* bres = ring + (size_t)HX_TC_STAGES * stage_bytes;      // digit mode: [cells of a piece][240 * 128]
 
     if (tid < 128) reinterpret_cast<uint32_t*>(smem_raw + 1024)[tid] = 0x38383838u;      // a chunk of unit scales (digit mode)
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (tid == 0) {
         for (int i = 0; i < HX_TC_STAGES; i++) { mb_init(&S.full[i], 1); mb_init(&S.empty[i], 1); }
         for (int i = 0; i < HX_TC_RES_CELLS; i++) mb_init(&S.bfull[i], 1);
-        mb_init(&S.accum, 1); mb_init(&S.acc_free, 8); mb_init(&S.part_done, 8); mb_init(&S.tk_ready, 1);
+        for (int i = 0; i < 2; i++) { mb_init(&S.accum[i], 1); mb_init(&S.acc_free[i], 4 * TC_EPI_Q); }
+        mb_init(&S.part_done, 4 * TC_EPI_Q); mb_init(&S.tk_ready, 1);
         S.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -160,8 +158,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = S.tmem_base;
-    // TMEM columns: [0, 256) accumulator (NB used), then per ring slot Sk*4 columns of SFA and of SFB
-    const uint32_t col_sfa = 256, col_sfb = 256 + HX_TC_STAGES * HX_TC_MAX_SK * 4;
+    // TMEM columns.  Raw mode: [0, 256) accumulator, then per ring slot Sk*4 columns of SFA and of SFB.  Digit mode:
+    // two accumulators of 240 columns, sixteen columns for the scale factors of the stage at hand (the tensor pipe works
+    // through copies and MMAs in the order they were issued, so the copy of the next stage follows the MMAs of this one),
+    // sixteen for the unit scales of the digit columns.
+    const uint32_t col_sfa = DG ? 2u * HX_TC_GROUP_COLS : 256u;
+    const uint32_t col_sfb = DG ? 2u * HX_TC_GROUP_COLS + 16u : 256u + HX_TC_STAGES * HX_TC_MAX_SK * 4;
+    static_assert(2 * HX_TC_GROUP_COLS + 32 <= 512, "two accumulators and the scale factors fill TMEM");
     // unit u of this CTA: tile u / PG and, with `combo` = u % PG, piece combo / G (and group combo % G = grp)
 #define TC_UNIT(u) const int mt = (u) / PG, piece = ((u) - mt * PG) / G; \
                    const int ks_lo = (piece * kcells / P) * 4, ks_hi = ((piece + 1) * kcells / P) * 4
@@ -171,12 +174,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
         if (lane == 0) {
             uint32_t git = 0;
             bool ok = true;
-            if (BR) {
+            if (DG) {
                 const int piece0 = ((int)blockIdx.x % PG) / G;
                 const int c_lo = piece0 * kcells / P, c_hi = (piece0 + 1) * kcells / P;
                 for (int c = c_lo; c < c_hi; c++) {
                     mb_expect(&S.bfull[c - c_lo], b_cell_bytes);
-                    bulk_load(bres + (size_t)(c - c_lo) * b_cell_bytes, g.b + (size_t)c * b_src_cell + (size_t)grp * 32768u, b_cell_bytes, &S.bfull[c - c_lo]);
+                    bulk_load(bres + (size_t)(c - c_lo) * b_cell_bytes, g.b + (size_t)c * b_src_cell + (size_t)grp * TC_DIGIT_CELL, b_cell_bytes, &S.bfull[c - c_lo]);
                 }
             }
             int lu = 0;
@@ -189,9 +192,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                     const int nk = min(Sk, ks_hi - ks0);
                     uint8_t* sa = ring + (size_t)slot * stage_bytes;
                     uint8_t* sb = sa + (size_t)Sk * a_cell;
-                    mb_expect(&S.full[slot], (uint32_t)nk * (a_cell + (BR ? 0u : b_cell)));
+                    mb_expect(&S.full[slot], (uint32_t)nk * (a_cell + (DG ? 0u : b_cell)));
                     bulk_load(sa, g.a + ((size_t)mt * g.ksteps + ks0) * a_cell, (uint32_t)nk * a_cell, &S.full[slot]);
-                    if (!BR) bulk_load(sb, g.b + (size_t)ks0 * b_cell, (uint32_t)nk * b_cell, &S.full[slot]);
+                    if (!DG) bulk_load(sb, g.b + (size_t)ks0 * b_cell, (uint32_t)nk * b_cell, &S.full[slot]);
                 }
             }
         }
@@ -202,56 +205,44 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | (8u << 24);
             uint32_t git = 0;
             bool ok = true;
-            const uint64_t dA0 = smem_desc(s_u32(ring), 16, 1024, SW128), dS0 = smem_desc(s_u32(ring) + 16384, 16, 128);
-            const uint64_t dB0 = smem_desc(s_u32(bres), 16, 1024, SW128);
-            if (g.digit_mode) {
+            int unit_iter = 0;
+            if (DG) {
+                // One (piece, group) for the whole CTA: its stages form one sequence, a cell of A against a resident cell of
+                // B each.  The four descriptors of a cell differ by constants (the address field counts 16-byte units).
+                const uint64_t dA0 = smem_desc(s_u32(ring), 16, 1024, SW128), dS0 = smem_desc(s_u32(ring) + 16384, 16, 128);
+                const uint64_t dB0 = smem_desc(s_u32(bres), 16, 1024, SW128);
                 // unit scales (E4M3 1.0) for every digit column: sixteen TMEM columns cover any N up to 256
                 for (int c = 0; c < 4; c++) tc_cp_sf(tmem + col_sfb + c * 4, smem_desc(s_u32(smem_raw + 1024), 16, 128));
-            }
-            int unit_iter = 0;
-            if (BR && Sk == 4) {
-                // One (piece, group) for the whole CTA: its stages form one sequence, a cell of A against a resident cell of
-                // B each.  The four descriptors of a cell differ by constants (the address field counts 16-byte units), and
-                // the scale factors of stage s + 1 are copied before the MMAs of stage s are issued, so that no MMA waits
-                // for the copy in front of it.
                 const int piece0 = ((int)blockIdx.x % PG) / G;
                 const int ncell = (piece0 + 1) * kcells / P - piece0 * kcells / P;
                 const int nu = ((int)blockIdx.x < nunits) ? (nunits - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
                 const uint32_t total = (uint32_t)(nu * ncell);
-                auto copy_sf = [&](uint32_t gi) -> bool {       // stage gi has landed: its scale factors to TMEM
-                    const uint32_t slot = gi % HX_TC_STAGES, round = gi / HX_TC_STAGES;
-                    if (gi < (uint32_t)ncell && !mb_wait(&S.bfull[gi], 0, &S.abort_flag)) return false;
-                    if (!mb_wait(&S.full[slot], round & 1, &S.abort_flag)) return false;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t dS = dS0 + (uint64_t)((slot * stage_bytes) >> 4);
-                    const uint32_t ta = tmem + col_sfa + slot * HX_TC_MAX_SK * 4;
-#pragma unroll
-                    for (int k = 0; k < 4; k++) tc_cp_sf(ta + k * 4, dS + (uint64_t)(k * 32));
-                    return true;
-                };
-                ok = total > 0 && copy_sf(0);
                 int ci = 0;
                 for (git = 0; git < total && ok; git++) {
+                    const uint32_t acc = tmem + (uint32_t)(unit_iter & 1) * HX_TC_GROUP_COLS;
                     if (ci == 0) {
                         TC_MARK(1, unit_iter, 0);
-                        if (unit_iter > 0) {      // the epilogue has read the previous unit's accumulator out
-                            if (!mb_wait(&S.acc_free, (uint32_t)(unit_iter - 1) & 1u, &S.abort_flag)) break;
+                        if (unit_iter >= 2) {      // the epilogue has read this accumulator's previous unit out
+                            if (!mb_wait(&S.acc_free[unit_iter & 1], (uint32_t)((unit_iter >> 1) - 1) & 1u, &S.abort_flag)) break;
                             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         }
                         TC_MARK(1, unit_iter, 1);
                     }
-                    if (git + 1 < total && !copy_sf(git + 1)) { ok = false; break; }
+                    const uint32_t slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
+                    if (git < (uint32_t)ncell && !mb_wait(&S.bfull[git], 0, &S.abort_flag)) { ok = false; break; }
+                    if (!mb_wait(&S.full[slot], round & 1, &S.abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     if (ci == 0) TC_MARK(1, unit_iter, 2);
-                    const uint32_t slot = git % HX_TC_STAGES;
-                    const uint64_t dA = dA0 + (uint64_t)((slot * stage_bytes) >> 4);
+                    const uint64_t dA = dA0 + (uint64_t)((slot * stage_bytes) >> 4), dS = dS0 + (uint64_t)((slot * stage_bytes) >> 4);
                     const uint64_t dB = dB0 + (uint64_t)(((uint32_t)ci * b_cell_bytes) >> 4);
-                    const uint32_t ta = tmem + col_sfa + slot * HX_TC_MAX_SK * 4;
+#pragma unroll
+                    for (int k = 0; k < 4; k++) tc_cp_sf(tmem + col_sfa + k * 4, dS + (uint64_t)(k * 32));
 #pragma unroll
                     for (int k = 0; k < 4; k++)
-                        tc_mma(tmem, dA + (uint64_t)(k * 2), dB + (uint64_t)(k * 2), idesc, ta + k * 4, tmem + col_sfb, (k > 0 || ci > 0) ? 1u : 0u);
+                        tc_mma(acc, dA + (uint64_t)(k * 2), dB + (uint64_t)(k * 2), idesc, tmem + col_sfa + k * 4, tmem + col_sfb, (k > 0 || ci > 0) ? 1u : 0u);
                     tc_commit(&S.empty[slot]);          // the slot is free once these MMAs have read it
                     if (++ci == ncell) {
-                        tc_commit(&S.accum);            // accumulator complete
+                        tc_commit(&S.accum[unit_iter & 1]);            // accumulator complete
                         TC_MARK(1, unit_iter, 3);
                         ci = 0; unit_iter++;
                     }
@@ -260,71 +251,69 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x, unit_iter++) {
                 TC_UNIT(u);
                 (void)mt;
-                TC_MARK(1, unit_iter, 0);
                 if (unit_iter > 0) {      // the epilogue has read the previous unit's accumulator out
-                    if (!mb_wait(&S.acc_free, (uint32_t)(unit_iter - 1) & 1u, &S.abort_flag)) break;
+                    if (!mb_wait(&S.acc_free[0], (uint32_t)(unit_iter - 1) & 1u, &S.abort_flag)) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
-                TC_MARK(1, unit_iter, 1);
                 for (int ks0 = ks_lo; ks0 < ks_hi; ks0 += Sk, git++) {
                     const uint32_t slot = git % HX_TC_STAGES, round = git / HX_TC_STAGES;
                     if (!mb_wait(&S.full[slot], round & 1, &S.abort_flag)) { ok = false; break; }
-                    if (ks0 == ks_lo) TC_MARK(1, unit_iter, 2);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const int nk = min(Sk, ks_hi - ks0);
                     const uint32_t sa = s_u32(ring + (size_t)slot * stage_bytes);
-                    const uint32_t sb = BR ? s_u32(bres) + (uint32_t)((ks0 - ks_lo) / 4) * b_cell_bytes : sa + (uint32_t)Sk * a_cell;
+                    const uint32_t sb = sa + (uint32_t)Sk * a_cell;
                     for (int k = 0; k < nk; k++) {
                         const uint32_t ta = tmem + col_sfa + (slot * HX_TC_MAX_SK + k) * 4;
                         const uint32_t tb = tmem + col_sfb + (slot * HX_TC_MAX_SK + k) * 4;
                         const uint32_t acell = sa + (uint32_t)(k >> 2) * HX_T128_CELL, bcell = sb + (uint32_t)(k >> 2) * b_cell_bytes;
                         const uint32_t e = (uint32_t)(k & 3);
                         tc_cp_sf(ta, smem_desc(acell + 16384 + e * 512, 16, 128));
-                        if (!g.digit_mode) tc_cp_sf(tb, smem_desc(bcell + (uint32_t)NB * 128u + e * 512, 16, 128));
+                        tc_cp_sf(tb, smem_desc(bcell + (uint32_t)NB * 128u + e * 512, 16, 128));
                         tc_mma(tmem, smem_desc(acell + e * 32, 16, 1024, SW128), smem_desc(bcell + e * 32, 16, 1024, SW128), idesc,
-                               ta, g.digit_mode ? tmem + col_sfb : tb, (ks0 > ks_lo || k > 0) ? 1u : 0u);
+                               ta, tb, (ks0 > ks_lo || k > 0) ? 1u : 0u);
                     }
                     tc_commit(&S.empty[slot]);          // the slot is free once these MMAs have read it
                 }
-                if (ok) tc_commit(&S.accum);            // accumulator complete
-                TC_MARK(1, unit_iter, 3);
+                if (ok) tc_commit(&S.accum[0]);         // accumulator complete
             }
         }
-    } else if (warp < 10) {
+    } else if (warp < 2 + 4 * TC_EPI_Q) {
         // ------------------------------ epilogue: TMEM -> registers -> global ------------------------------
-        const int ew = warp - 2, sub = warp & 3, half = ew >> 2;      // TMEM lanes 32*sub .. 32*sub+31; tokens 8*half .. 8*half+7 of the group
+        const int ew = warp - 2, sub = warp & 3, third = ew >> 2;      // TMEM lanes 32*sub .. 32*sub+31; tokens 8*third .. 8*third+7 of the group
         const int rl = sub * 32 + lane, etid = tid - 64;
-        const uint32_t bar_half = 1u + (uint32_t)half;               // named barriers: 1, 2 = the four warps of a half; 3 = all eight
-        constexpr int TH = HX_TC_MAX_TOK / 2;
-        const int ntok = NB / 16, tok0 = grp * HX_TC_MAX_TOK + half * TH;      // this thread's tokens: tok0 .. tok0+TH-1 of the launch
-        const int tleft = ntok - half * TH;                                     // ... of which tleft exist
-        constexpr int ptok = HX_TC_MAX_GROUPS * HX_TC_MAX_TOK;                  // token slots of a piece in `partial` (a constant: the loads of a merge differ by immediates)
+        const uint32_t bar_third = 1u + (uint32_t)third;             // named barriers 1 .. 3: the four warps that share a set of tokens
+        constexpr int TH = HX_TC_MAX_TOK / TC_EPI_Q;
+        static_assert(TH == 8, "a warp reads its tokens' digit accumulators as eight columns per digit");
+        const int ntok = DG ? min(HX_TC_MAX_TOK, g.ntok - grp * HX_TC_MAX_TOK) : 0;      // tokens of this CTA's group
+        const int tok0 = grp * HX_TC_MAX_TOK + third * TH;             // this thread's tokens: tok0 .. tok0+TH-1 of the launch
+        const int tleft = ntok - third * TH;                           // ... of which tleft exist
+        constexpr int ptok = HX_TC_NTOK;                               // token slots of a piece in `partial` (a constant: the loads of a merge differ by immediates)
         float cs[TH];
 #pragma unroll
-        for (int t = 0; t < TH; t++) cs[t] = (g.digit_mode && t < tleft) ? __ldg(g.col_scale + tok0 + t) : 0.0f;
+        for (int t = 0; t < TH; t++) cs[t] = (DG && t < tleft) ? __ldg(g.col_scale + tok0 + t) : 0.0f;
+        bool dead = false;      // a wait ran out: keep to the barrier protocol, touch nothing
         // final values of tile mtf: tensor scale, then store / residual add / SwiGLU across the gate (rows 0..63 of the
         // tile) and up (rows 64..127) halves
-        bool dead = false;      // a wait ran out: keep to the barrier protocol, touch nothing
         auto finalize = [&](int mtf, const float (&val)[TH], const float (&prev)[TH]) {
             const int row = mtf * 128 + rl;
             const float tsr = g.pair64 ? ((rl < 64) ? g.ts[0] : g.ts[1])
                                        : (row < g.bound0 ? g.ts[0] : (row < g.bound1 ? g.ts[1] : g.ts[2]));
             if (g.swiglu) {
 #pragma unroll
-                for (int t = 0; t < TH; t++) swi[(half * TH + t) * 128 + rl] = val[t] * tsr;
-                asm volatile("bar.sync %0, 128;" :: "r"(bar_half) : "memory");
+                for (int t = 0; t < TH; t++) swi[(third * TH + t) * 128 + rl] = val[t] * tsr;
+                asm volatile("bar.sync %0, 128;" :: "r"(bar_third) : "memory");
                 if (rl < 64 && mtf * 64 + rl < g.rows && !dead) {
 #pragma unroll
                     for (int t = 0; t < TH; t++) {
                         if (t >= tleft) break;
-                        const float gt = swi[(half * TH + t) * 128 + rl], up = swi[(half * TH + t) * 128 + rl + 64];
+                        const float gt = swi[(third * TH + t) * 128 + rl], up = swi[(third * TH + t) * 128 + rl + 64];
                         const float sgn = gt < 0.0f ? -1.0f : 1.0f;
                         const float ex = __expf(-(sgn * gt));
                         const float th = sgn * ((1.0f - ex) / (1.0f + ex));
                         g.out[(size_t)(tok0 + t) * g.ld_out + mtf * 64 + rl] = gt * (0.5f * (1.0f + th)) * up;
                     }
                 }
-                asm volatile("bar.sync %0, 128;" :: "r"(bar_half) : "memory");
+                asm volatile("bar.sync %0, 128;" :: "r"(bar_third) : "memory");
             } else if (row < g.rows && !dead) {
 #pragma unroll
                 for (int t = 0; t < TH; t++) {
@@ -345,7 +334,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
         // the lanes' quarter pair) takes four tokens and fetches the gate row r and the up row r + 64 of each, so no
         // exchange between warps is needed.
         auto merge = [&](int mtf) {
-            if (etid == 0) g.tickets[mtf * G + grp] = 0u;
+            if (etid == 0 && !dead) g.tickets[mtf * G + grp] = 0u;
             const bool sw = g.swiglu != 0;
             const int r0 = sw ? (rl & 63) : rl, tb = sw ? (rl >> 6) * (TH / 2) : 0;
             const float* part = g.partial + ((size_t)mtf * P * ptok + tok0 + tb) * 128 + r0;      // [piece][token][row in tile]
@@ -359,8 +348,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                 for (int qq = 0; qq < 4; qq++)
 #pragma unroll
                     for (int i = 0; i < TH; i++) {
-                        const int tt = sw ? tb + (i & 3) : i;                                   // token of value i
-                        const int off = sw ? (i & 3) * 128 + (i >> 2) * 64 : i * 128;           // its place from `part`
+                        const int tt = sw ? tb + (i % (TH / 2)) : i;                            // token of value i
+                        const int off = sw ? (i % (TH / 2)) * 128 + (i / (TH / 2)) * 64 : i * 128;   // its place from `part`
                         pv[qq][i] = (q0 + qq < P && tt < tleft) ? __ldcg(part + (size_t)(q0 + qq) * ptok * 128 + off) : 0.0f;
                     }
 #pragma unroll
@@ -371,7 +360,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                     }
             }
             if (!sw) { finalize(mtf, val, prev); return; }
-            if (mtf * 64 + r0 >= g.rows) return;
+            if (mtf * 64 + r0 >= g.rows || dead) return;
 #pragma unroll
             for (int i = 0; i < TH / 2; i++) {
                 if (tb + i >= tleft) break;
@@ -387,18 +376,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
             TC_UNIT(u);
             (void)ks_lo; (void)ks_hi;
             const int row = mt * 128 + rl;
+            const int ab = DG ? (unit_iter & 1) : 0;                                   // accumulator of this unit
+            const uint32_t aph = DG ? (uint32_t)(unit_iter >> 1) & 1u : (uint32_t)unit_iter & 1u;
             float prev[TH];
-            if (g.digit_mode && P == 1) load_prev(mt, prev);      // fetched before the accumulator is ready
+            if (DG && P == 1) load_prev(mt, prev);      // fetched before the accumulator is ready
             if (etid == 0) TC_MARK(2, unit_iter, 0);
-            if (dead || !mb_wait(&S.accum, (uint32_t)unit_iter & 1u, &S.abort_flag)) dead = true;
+            if (dead || !mb_wait(&S.accum[ab], aph, &S.abort_flag)) dead = true;
             if (etid == 0) TC_MARK(2, unit_iter, 1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tlane = tmem + ((uint32_t)(sub * 32) << 16);
-            if (!g.digit_mode) {
-                for (int c0 = half * 8; c0 < NB && !dead; c0 += 16) {
+            if (!DG) {
+                for (int c0 = third * 8; c0 < NB && !dead; c0 += 8 * TC_EPI_Q) {
                     uint32_t r[8];
-                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(tlane + (uint32_t)c0));
+                    tc_ld8(r, tlane + (uint32_t)c0);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (row < g.rows) {
 #pragma unroll
@@ -407,49 +397,57 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mb_arrive(&S.acc_free);
+                if (lane == 0) mb_arrive(&S.acc_free[0]);
                 continue;
             }
-            // ---- digit mode: this thread's row and tokens: sixteen digit accumulators each -> one value
+            // ---- digit mode: this thread's row and eight tokens: ten digit accumulators each, most significant first,
+            // folded by v = 9 v + D (two digits' loads in flight per wait)
             float val[TH];
             {
-                // two tokens per load; columns past the group's last token belong to the accumulator's allocation all the
-                // same, and what is read there is dropped
-                const uint32_t tcol = tlane + (uint32_t)(half * TH * 16);
-                const int tleft = dead ? 0 : ntok - half * TH;       // (shadows the outer count: nothing is read after a failed wait)
-                uint32_t ra[32], rb[32];
+                const uint32_t tcol = tlane + (uint32_t)(ab * HX_TC_GROUP_COLS + third * TH);
+                const bool any = !dead && tleft > 0;
 #pragma unroll
-                for (int t = 0; t < TH; t += 4) {      // two loads in flight per wait
-                    if (t < tleft) {
-                        tc_ld32(ra, tcol + (uint32_t)(t * 16));
-                        tc_ld32(rb, tcol + (uint32_t)((t + 2) * 16));
+                for (int t = 0; t < TH; t++) val[t] = 0.0f;
+                uint32_t ra[8], rb[8];
+#pragma unroll
+                for (int d = 0; d < HX_TC_DIGITS; d += 2) {
+                    if (any) {
+                        tc_ld8(ra, tcol + (uint32_t)(d * HX_TC_MAX_TOK));
+                        tc_ld8(rb, tcol + (uint32_t)((d + 1) * HX_TC_MAX_TOK));
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int t = 0; t < TH; t++) {
+                            val[t] = fmaf(val[t], 9.0f, __uint_as_float(ra[t]));
+                            val[t] = fmaf(val[t], 9.0f, __uint_as_float(rb[t]));
+                        }
                     }
-                    val[t] = t < tleft ? tc_digits<0>(ra) * cs[t] : 0.0f;
-                    val[t + 1] = t + 1 < tleft ? tc_digits<16>(ra) * cs[t + 1] : 0.0f;
-                    val[t + 2] = t + 2 < tleft ? tc_digits<0>(rb) * cs[t + 2] : 0.0f;
-                    val[t + 3] = t + 3 < tleft ? tc_digits<16>(rb) * cs[t + 3] : 0.0f;
                 }
+#pragma unroll
+                for (int t = 0; t < TH; t++) val[t] = (any && t < tleft) ? val[t] * cs[t] : 0.0f;
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mb_arrive(&S.acc_free);       // the issuer may overwrite the accumulator
+            if (lane == 0) mb_arrive(&S.acc_free[ab]);       // the issuer may overwrite this accumulator
             if (etid == 0) TC_MARK(2, unit_iter, 2);
             if (P == 1) { finalize(mt, val, prev); continue; }
-            // K pieces: leave this piece's values, look at the ticket of the previous unit, draw this unit's
+            // K pieces: leave this piece's values, look at the ticket of the previous unit
             float* part = g.partial + (((size_t)mt * P + piece) * ptok + tok0) * 128 + rl;
 #pragma unroll
             for (int t = 0; t < TH; t++)
                 if (t < tleft && !dead) part[(size_t)t * 128] = val[t];
+            // The previous unit's ticket has long arrived.  It is looked at BEFORE this warp reports its partial sums: the
+            // ticket of this unit cannot be drawn without that report, so the ticket barrier is never two phases ahead of a
+            // warp that still has to wait on it, and no warp reports twice before another has reported once.
+            bool fin = false;
+            if (pend_mt >= 0) {
+                if (dead || !mb_wait(&S.tk_ready, (uint32_t)(unit_iter - 1) & 1u, &S.abort_flag)) dead = true;
+                fin = !dead && S.ticket[(unit_iter - 1) & 1] == (unsigned)(P - 1);
+            }
             __syncwarp();
             if (lane == 0) mb_arrive(&S.part_done);      // this warp's partial sums are written: the ticket may be drawn
             if (etid == 0) TC_MARK(2, unit_iter, 3);
-            if (pend_mt >= 0) {                          // the previous unit's ticket has long arrived
-                if (dead || !mb_wait(&S.tk_ready, (uint32_t)(unit_iter - 1) & 1u, &S.abort_flag)) dead = true;
-                const bool fin = !dead && S.ticket[(unit_iter - 1) & 1] == (unsigned)(P - 1);
-                if (fin) merge(pend_mt);
-                if (etid == 0) TC_MARK(2, unit_iter, 4 + (fin ? 1 : 0));
-            }
+            if (fin) merge(pend_mt);
+            if (etid == 0) TC_MARK(2, unit_iter, 4 + (fin ? 1 : 0));
             pend_mt = mt;
         }
         if (pend_mt >= 0) {      // the last unit's ticket
@@ -487,9 +485,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_tc(const __grid_constant
 size_t hx_gemm_tc_smem(int ncols, int stage_ksteps) {
     return TC_FRONT + (size_t)HX_TC_STAGES * (stage_ksteps / 4) * (HX_T128_CELL + (size_t)ncols * 128 + 2048);
 }
-// resident-B variant: ring of A cells + the B cells of one K piece
-static size_t gemm_tc_smem_resident(int ncols, int stage_ksteps, int cells_per_piece) {
-    return TC_FRONT + (size_t)HX_TC_STAGES * (stage_ksteps / 4) * HX_T128_CELL + (size_t)cells_per_piece * ncols * 128;
+// digit mode: ring of A cells + the digit cells of one (K piece, token group)
+static size_t gemm_tc_smem_digits(int stage_ksteps, int cells_per_piece) {
+    return TC_FRONT + (size_t)HX_TC_STAGES * (stage_ksteps / 4) * HX_T128_CELL + (size_t)cells_per_piece * TC_DIGIT_CELL;
 }
 
 // One-time function attribute (call outside any stream capture).
@@ -500,21 +498,26 @@ int hx_gemm_tc_prepare() {
 }
 
 int hx_gemm_tc_launch(const HxGemmTC& g, cudaStream_t st) {
-    HX_CHECK_ARG(g.a && g.b && (g.digit_mode ? (g.out && g.col_scale && g.ncols % 16 == 0) : g.y != nullptr) && g.ntiles > 0 && g.ksteps > 0);
-    HX_CHECK_ARG(g.ncols >= 8 && g.ncols <= (g.digit_mode ? 256 * HX_TC_MAX_GROUPS : 256) && g.ncols % 8 == 0);
+    HX_CHECK_ARG(g.a && g.b && g.ntiles > 0 && g.ksteps > 0);
     HX_CHECK_ARG(g.stage_ksteps >= 4 && g.stage_ksteps <= HX_TC_MAX_SK && g.stage_ksteps % 4 == 0 && g.ksteps % 4 == 0);
-    const int Pq = g.ksplit > 1 ? g.ksplit : 1, kc = g.ksteps / 4;
-    if (g.b_resident) HX_CHECK_ARG(g.digit_mode && g.stage_ksteps == 4);
-    const int nb_max = g.ncols < 256 ? g.ncols : 256;
-    const size_t smem = g.b_resident ? gemm_tc_smem_resident(nb_max, g.stage_ksteps, (kc + Pq - 1) / Pq) : hx_gemm_tc_smem(g.ncols, g.stage_ksteps);
-    if (g.b_resident) HX_CHECK_ARG((kc + Pq - 1) / Pq <= HX_TC_RES_CELLS);
+    const int P = g.ksplit > 1 ? g.ksplit : 1, kc = g.ksteps / 4;
+    size_t smem;
+    int G = 1;
+    if (g.digit_mode) {
+        HX_CHECK_ARG(g.out && g.col_scale && g.b_resident && g.stage_ksteps == 4 && g.ntok >= 1 && g.ntok <= HX_TC_NTOK);
+        HX_CHECK_ARG((kc + P - 1) / P <= HX_TC_RES_CELLS && P <= kc);
+        if (P > 1) HX_CHECK_ARG(g.partial && g.tickets);
+        G = (g.ntok + HX_TC_MAX_TOK - 1) / HX_TC_MAX_TOK;
+        HX_CHECK_ARG(P * G <= 148);
+        smem = gemm_tc_smem_digits(g.stage_ksteps, (kc + P - 1) / P);
+    } else {
+        HX_CHECK_ARG(g.y != nullptr && P == 1 && !g.b_resident);
+        HX_CHECK_ARG(g.ncols >= 8 && g.ncols <= 256 && g.ncols % 8 == 0);
+        smem = hx_gemm_tc_smem(g.ncols, g.stage_ksteps);
+    }
     if (smem > 227 * 1024) return hx_fail(HX_ERR_ARG, "tensor-core GEMM stage too large (%zu bytes of shared memory)", smem);
     { const int prc = hx_gemm_tc_prepare(); if (prc) return prc; }
-    const int P = g.ksplit > 1 ? g.ksplit : 1;
-    if (P > 1) HX_CHECK_ARG(g.digit_mode && g.partial && g.tickets && P <= g.ksteps / 4 && P <= 148);
-    const int G = (g.ncols + 255) / 256;
-    if (G > 1) HX_CHECK_ARG(g.b_resident && P * G <= 148);
-    int grid = g.ntiles * P * G; if (grid > 148) grid = g.b_resident ? (148 / (P * G)) * (P * G) : 148;      // resident B: a CTA keeps one (K piece, token group)
+    int grid = g.ntiles * P * G; if (grid > 148) grid = g.digit_mode ? (148 / (P * G)) * (P * G) : 148;      // digit mode: a CTA keeps one (K piece, token group)
     k_gemm_tc<<<grid, TC_THREADS, smem, st>>>(g);
     HX_COUNT_LAUNCH(1);
     HX_CUDA(cudaGetLastError());

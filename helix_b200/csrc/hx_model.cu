@@ -1261,7 +1261,7 @@ HX_API int hx_decode_step(hx_model* m, const int32_t* ids, int pos, int32_t* nex
 }
 
 // ---- batched prefill ---------------------------------------------------------------------------------
-static_assert(HX_PF_TB <= HX_TC_MAX_GROUPS * HX_TC_MAX_TOK && HX_PF_TB % HX_TC_MAX_TOK == 0, "a chunk is whole token groups of the GEMM");
+static_assert(HX_PF_TB <= HX_TC_MAX_GROUPS * HX_TC_MAX_TOK && HX_PF_TB <= HX_TC_NTOK, "a chunk fits the token groups of the GEMM");
 // K pieces of a linear in the chunk GEMM: pieces small enough for their digit cells to stay in shared memory, and
 // with few row tiles enough of them for about one unit per SM.
 static int pf_pieces(const Fused& f) {
@@ -1276,7 +1276,7 @@ static int pf_alloc(hx_model* m) {
     { const int prc = hx_gemm_tc_prepare(); if (prc) return prc; }
     const hx_config& c = m->cfg;
     int maxK = c.d_model > m->QD ? c.d_model : m->QD; if (c.d_ff > maxK) maxK = c.d_ff;
-    const size_t cells = (size_t)((maxK + 255) / 256) * (16 * HX_PF_TB) * 128;
+    const size_t cells = (size_t)((maxK + 255) / 256) * HX_TC_MAX_GROUPS * (HX_TC_GROUP_COLS * 128);
     m->pf_gu_ld = m->layers.empty() ? 64 : m->layers[0].gu.tiles128 * 64;      // hidden size rounded up to whole tiles
     int rc;
     if ((rc = dalloc(m, &m->pf_x, (size_t)HX_PF_TB * c.d_model))) return rc;
@@ -1309,9 +1309,9 @@ static int pf_alloc(hx_model* m) {
 // one linear of a chunk: digits of `src` -> GEMM against f -> out (token-major)
 static int pf_linear(hx_model* m, const Fused& f, const float* src, int ld_src, int n, int swiglu, const float* g,
                      float* out, int ld_out, int rows, int resid, int pair64) {
-    hx_pf_digits(src, ld_src, n, f.K, 0, g, m->cfg.norm_eps, m->pf_cells, 16 * n, m->pf_scale, m->st);
+    hx_pf_digits(src, ld_src, n, f.K, 0, g, m->cfg.norm_eps, m->pf_cells, m->pf_scale, m->st);
     HxGemmTC q = {};
-    q.a = f.t128; q.b = m->pf_cells; q.rows = rows; q.ntiles = f.tiles128; q.ksteps = f.ksteps; q.ncols = 16 * n; q.stage_ksteps = 4;
+    q.a = f.t128; q.b = m->pf_cells; q.rows = rows; q.ntiles = f.tiles128; q.ksteps = f.ksteps; q.ntok = n; q.stage_ksteps = 4;
     q.err = m->pf_err; q.digit_mode = 1; q.col_scale = m->pf_scale; q.out = out; q.ld_out = ld_out; q.resid = resid;
     q.ts[0] = f.ts[0]; q.ts[1] = f.ts[1]; q.ts[2] = f.ts[2]; q.bound0 = f.bound0; q.bound1 = f.bound1; q.pair64 = pair64; q.swiglu = swiglu;
     const int P = pf_pieces(f);
@@ -1652,7 +1652,7 @@ HX_API int hx_generate_spec(hx_model* m, const int32_t* prompt, int T, int n_new
     if (cfg_in) cfg = *cfg_in;
     HX_CHECK_ARG(cfg.k_min >= 1 && cfg.k_max >= cfg.k_min && cfg.m >= 1 && cfg.min_margin >= 0.0f);
     int rc = spec_alloc(m); if (rc) return rc;
-    const int m_cap = HX_TC_MAX_TOK - 1 < HX_SPEC_DRAFT_MAX ? HX_TC_MAX_TOK - 1 : HX_SPEC_DRAFT_MAX;   // window = last token + drafts = one token group of the GEMM
+    const int m_cap = 15 < HX_SPEC_DRAFT_MAX ? 15 : HX_SPEC_DRAFT_MAX;   // window = last token + drafts: sixteen rows at most, one token group of the GEMM
     const int M = cfg.m < m_cap ? cfg.m : m_cap;
     hx_spec_stats stt = {0, 0, 0, 0, 0, 0, 0, 0};
     std::vector<int32_t> ids(prompt, prompt + T);

@@ -8,6 +8,7 @@
 // kernel, hx_persist_tc.cu); the GEMM epilogue recombines the sixteen accumulators of a token.
 // Norm, RoPE, KV append and attention are small f32 kernels over the chunk.
 #include "hx_prefill.cuh"
+#include "hx_gemm_tc.cuh"
 #include "hx_kernels.cuh"
 #include <math.h>
 #include <atomic>
@@ -28,8 +29,12 @@ __global__ void __launch_bounds__(256) k_pf_embed(const int* __restrict__ ids, H
 }
 
 // grid (token, slice of K): every CTA of a token computes the token's statistics, then emits its slice of items.
+// A value becomes the integer M = round(|x| / S * 2^29) < 2^30 (S: the power of two at or below the vector's largest
+// element) and that integer ten balanced base-9 digits (-4 .. 4), least significant first: r = M mod 9, M = M div 9,
+// and a remainder above 4 becomes r - 9 with a carry.  A negative value has all its digits negated.  Digit d (d = 0:
+// weight 9^9) of token t lies in row 24 d + t % 24 of the token group t / 24 of a cell, as the E2M1 code of its value.
 __global__ void __launch_bounds__(512) k_pf_digits(const float* __restrict__ src, int ld, int K, int swiglu, const float* __restrict__ g,
-                                                    float eps, uint8_t* __restrict__ cells, int ncols, float* __restrict__ scale) {
+                                                    float eps, uint8_t* __restrict__ cells, int groups, float* __restrict__ scale) {
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* x = src + (size_t)t * ld;
     __shared__ float red[32];
@@ -56,36 +61,43 @@ __global__ void __launch_bounds__(512) k_pf_digits(const float* __restrict__ src
     float Sg = 1.0f;
     const float vmax = tmx * inv * 1.0000005f;
     if (vmax > 0.0f && vmax < INFINITY) Sg = __uint_as_float(__float_as_uint(vmax) & 0x7F800000u);
-    if (tid == 0 && blockIdx.y == 0) scale[t] = Sg;
-    const float mul = (inv / Sg) * 2147483648.0f;
-    // pass 2: items of 8 consecutive elements -> sixteen digit words
+    if (tid == 0 && blockIdx.y == 0) scale[t] = Sg * (1.0f / HX_TC_DIGIT_UNIT);
+    const float mul = (inv / Sg) * HX_TC_DIGIT_UNIT;
+    // pass 2: items of 8 consecutive elements -> one word per digit
     const int Kc = ((K + 255) / 256) * 256;
-    const size_t cell_bytes = (size_t)ncols * 128;
+    const size_t cell_bytes = (size_t)groups * (HX_TC_GROUP_COLS * 128);
+    const int tg = t / HX_TC_MAX_TOK, tl = t - tg * HX_TC_MAX_TOK;
     const int nit = Kc / 8, per = (nit + gridDim.y - 1) / gridDim.y;
     const int it_hi = min(nit, (int)(blockIdx.y + 1) * per);
     for (int it = blockIdx.y * per + tid; it < it_hi; it += 512) {
         const int k = it * 8;
-        uint32_t M[8]; uint32_t sg = 0u;
+        uint32_t word[HX_TC_DIGITS];
+#pragma unroll
+        for (int n = 0; n < HX_TC_DIGITS; n++) word[n] = 0u;
 #pragma unroll
         for (int e = 0; e < 8; e++) {
             float v = 0.0f;
             if (k + e < K) { v = value(k + e); if (g) v *= g[k + e]; }
-            M[e] = __float2uint_rn(fabsf(v) * mul);
-            sg |= (v < 0.0f ? 8u : 0u) << (4 * e);
+            uint32_t m = __float2uint_rn(fabsf(v) * mul);
+            const uint32_t neg = v < 0.0f ? 8u : 0u;
+#pragma unroll
+            for (int n = HX_TC_DIGITS - 1; n >= 0; n--) {
+                const uint32_t q = __umulhi(m, 0x38E38E39u) >> 1;      // m / 9
+                uint32_t r = m - 9u * q;                                // 0 .. 8
+                const bool up = r > 4u;                                 // balanced: 5 .. 8 are -4 .. -1 of the next power
+                m = q + (up ? 1u : 0u);
+                const uint32_t mag = up ? 9u - r : r;                   // 0 .. 4
+                const uint32_t code = (0x65420u >> (4u * mag)) & 0xFu;  // E2M1 codes of 0, 1, 2, 3, 4
+                const uint32_t sgn = (mag != 0u && (up != (neg != 0u))) ? 8u : 0u;
+                word[n] |= (code | sgn) << (4 * e);
+            }
         }
         const int j = (it >> 2) & 7, w = it & 3;
-        uint8_t* dst = cells + (size_t)(it >> 5) * cell_bytes + (size_t)(t * 16) * 128 + w * 4;
+        uint8_t* dst = cells + (size_t)(it >> 5) * cell_bytes + (size_t)tg * (HX_TC_GROUP_COLS * 128) + w * 4;
 #pragma unroll
-        for (int n = 0; n < 16; n++) {
-            uint32_t word = 0u;
-#pragma unroll
-            for (int e = 0; e < 8; e++) {
-                const int sh = 30 - 2 * n - 4 * e;
-                word |= (sh >= 0 ? (M[e] >> sh) : (M[e] << (-sh))) & (3u << (4 * e));
-            }
-            const uint32_t nz = (word | (word >> 1)) & 0x11111111u;
-            word |= sg & (nz << 3);
-            *reinterpret_cast<uint32_t*>(dst + n * 128 + ((j ^ (n & 7)) << 4)) = word;     // (16 t + n) & 7 == n & 7
+        for (int n = 0; n < HX_TC_DIGITS; n++) {
+            const int row = n * HX_TC_MAX_TOK + tl;
+            *reinterpret_cast<uint32_t*>(dst + (size_t)row * 128 + ((j ^ (row & 7)) << 4)) = word[n];
         }
     }
 }
@@ -598,9 +610,10 @@ void hx_pf_embed(const int* ids, HxPfWhere wh, const float* emb, float* X, int n
 }
 
 void hx_pf_digits(const float* src, int ld, int n_tok, int K, int swiglu, const float* g, float eps,
-                  uint8_t* cells, int ncols, float* scale, cudaStream_t st) {
+                  uint8_t* cells, float* scale, cudaStream_t st) {
     const int slices = K >= 8192 ? 8 : 4;
-    k_pf_digits<<<dim3(n_tok, slices), 512, 0, st>>>(src, ld, K, swiglu, g, eps, cells, ncols, scale);
+    const int groups = (n_tok + HX_TC_MAX_TOK - 1) / HX_TC_MAX_TOK;
+    k_pf_digits<<<dim3(n_tok, slices), 512, 0, st>>>(src, ld, K, swiglu, g, eps, cells, groups, scale);
     HX_COUNT_LAUNCH(1);
 }
 

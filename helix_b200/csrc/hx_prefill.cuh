@@ -3,7 +3,7 @@
 #pragma once
 #include "hx_common.cuh"
 
-#define HX_PF_TB 64                // tokens per chunk: four groups of 16 tokens x 16 digit columns = the 256 columns of one MMA
+#define HX_PF_TB 64                // tokens per chunk: three groups of up to 24 tokens x 10 digit columns = the 240 columns of one MMA
 
 // Where the tokens of a chunk sit.  Prefill: consecutive positions of one sequence starting at *posp (device memory, so
 // that the launches of a chunk can be replayed as one CUDA graph).  Batched decode: token t is at position pos_arr[t] of
@@ -20,10 +20,11 @@ void hx_pf_embed(const int* ids, HxPfWhere wh, const float* emb, float* X, int n
 //   src [n_tok][ld] f32; swiglu != 0: the vector is silu(gate)*up read from gate/up tiles of 128 rows
 //   (64 gate rows then the 64 matching up rows), K = hidden size;
 //   g != null: RMSNorm with gain g and eps first;
-//   cells: K rounded up to 256 columns, per 256-column cell ncols x 128 bytes, row 16*t + j = digit j of token t;
-//   scale[t] = power of two with x_n = scale * sum_j (digit_j / 2) 4^-j.
+//   cells: K rounded up to 256 columns; per 256-column cell and group of 24 tokens 240 rows of 128 bytes, row 24 d + t % 24 =
+//   digit d of token t (ten balanced base-9 digits, most significant first, as E2M1 codes);
+//   scale[t]: x_n = scale[t] * sum_d digit_d 9^(9-d)  (a power of two).
 void hx_pf_digits(const float* src, int ld, int n_tok, int K, int swiglu, const float* g, float eps,
-                  uint8_t* cells, int ncols, float* scale, cudaStream_t st);
+                  uint8_t* cells, float* scale, cudaStream_t st);
 
 // Per token and head of a chunk: RMSNorm (gains qn_g / kn_g, may be null) + rotate_half RoPE at position *posp + t on
 // q (in place) and k; k and v are written to the cache rows of their positions.
