@@ -571,9 +571,9 @@ def run_ours(args):
         tprobe = {"mma": "tcgen05.mma kind::mxf4nvf4 block16, M128 x N x K64, operands in shared memory, one issuing thread per SM",
                   "clk_per_mma_n16_with_scale_copies": c16, "clk_per_mma_n256": c256, "clk_per_mma_n256_with_scale_copies": c256s,
                   "attainable_tflops_n256": tf256, "attainable_tflops_n256_with_scale_copies": tf256s,
-                  "prefill_useful_tflops": useful, "prefill_issued_tflops": useful * 16.0,
-                  "prefill_issued_frac_of_attainable": useful * 16.0 / tf256s,
-                  "note": "the prefill issues sixteen exact digit columns per activation, so its issued work is 16 x the useful work"}
+                  "prefill_useful_tflops": useful, "prefill_issued_tflops": useful * 10.0,
+                  "prefill_issued_frac_of_attainable": useful * 10.0 / (tf256s * 240.0 / 256.0),
+                  "note": "the prefill issues ten digit columns per activation (balanced base 9), 240 columns per MMA, so its issued work is 10 x the useful work"}
 
     # GPT-2-124M shape, all linears NVFP4, 32-token prompt + 128 greedy tokens, batch 1
     gpt2 = None
@@ -647,7 +647,7 @@ def run_ours(args):
                 "roofline": roofline, "cpu_baseline": cpu, "parity": parity, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
                 "reference_gpu": ref_gpu, "batch64": batch64, "tp": tpl, "speculative": spec, "tensor_probe": tprobe, "quantizer": quant, "gpt2": gpt2,
                 "prefill": {"tokens": PROMPT_LEN, "ms": prefill_s * 1e3, "tok_per_s": PROMPT_LEN / prefill_s,
-                            "path": "chunks of 64 tokens, one tcgen05 block-scaled GEMM per linear (exact digit columns), host ids in"},
+                            "path": "chunks of 64 tokens, one tcgen05 block-scaled GEMM per linear (ten base-9 digit columns per activation), host ids in"},
                 "ms_per_token": ms_max / args.steps / NEW_TOKENS, "last_tokens": [int(t) for t in toks[-4:]]}
         print(json.dumps(line), flush=True)
     if dist is not None:

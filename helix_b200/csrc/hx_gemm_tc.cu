@@ -6,8 +6,8 @@
 // the committed NVFP4 layout (helixc/runtime/gpt2_pack.c:350-373), so the weights feed the tensor
 // cores without any per-weight instruction.  B = activations as E2M1 columns: in digit mode (the chunk
 // paths: batched prefill, batched decode, the verify forward; replaces tiled_matmul_abt of
-// forward_layer_llama, helixc/runtime/gpt2_infer.c:1231-1287) sixteen exact base-4 digit columns per token
-// with unit block scales, recombined in the epilogue; in raw mode (hx_gemm_nvfp4_tc) any E2M1 columns with
+// forward_layer_llama, helixc/runtime/gpt2_infer.c:1231-1287) ten balanced base-9 digit columns per token
+// with unit block scales, folded in the epilogue; in raw mode (hx_gemm_nvfp4_tc) any E2M1 columns with
 // their own UE4M3 block scales, the accumulators stored as they are.
 //
 // Work units of one 128-row tile of A (times a piece of K and a group of 16 tokens), a CTA per SM walking

@@ -3,9 +3,11 @@
 // Replaces forward_layer_llama / forward_full (helixc/runtime/gpt2_infer.c:1231-1333): where the reference runs
 // f32 tiled_matmul_abt over a dequantized weight copy per layer, a chunk of HX_PF_TB prompt tokens here is one
 // block-scaled NVFP4 GEMM per linear with the weights read in their packed form.  The activations enter the FP4
-// tensor path exactly: after the optional RMSNorm each vector is x = S * sum_j (d_j/2) 4^-j with sixteen base-4
-// digits carrying the sign, every digit row being an E2M1 column with unit block scale (the scheme of the decode
-// kernel, hx_persist_tc.cu); the GEMM epilogue recombines the sixteen accumulators of a token.
+// tensor path as digits: after the optional RMSNorm each element is x = s * sum_d digit_d 9^(9-d) with ten balanced
+// base-9 digits (-4 .. 4: E2M1 values, sign included) of the integer |x| / S * 2^29 (S: the power of two at or below
+// the vector's largest element, s = S * 2^-29), every digit row being an E2M1 column with unit block scale; the GEMM
+// epilogue folds the ten accumulators of a token.  The digits resolve 2^-29 of the vector's largest element, beyond
+// what an f32 dot product keeps.  (The decode kernel uses sixteen exact base-4 digits: there the column count is free.)
 // Norm, RoPE, KV append and attention are small f32 kernels over the chunk.
 #include "hx_prefill.cuh"
 #include "hx_gemm_tc.cuh"
