@@ -1267,7 +1267,11 @@ static_assert(HX_PF_TB <= HX_TC_MAX_GROUPS * HX_TC_MAX_TOK && HX_PF_TB <= HX_TC_
 static int pf_pieces(const Fused& f) {
     const int kcells = f.ksteps / 4;
     int P = (kcells + HX_TC_RES_CELLS - 1) / HX_TC_RES_CELLS;
-    if (2 * f.tiles128 <= 148) { int q = 148 / f.tiles128; if (q > kcells) q = kcells; if (q > P) P = q; }
+    if (2 * f.tiles128 <= 148) {
+        int q = 148 / f.tiles128; if (q > kcells) q = kcells;
+        if (q > 148 / HX_TC_MAX_GROUPS) q = 148 / HX_TC_MAX_GROUPS;      // pieces x token groups is the least grid
+        if (q > P) P = q;
+    }
     return P < 1 ? 1 : P;
 }
 
